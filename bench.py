@@ -1,0 +1,360 @@
+"""Benchmark: 27B-class Q4_K_M decode tokens/s through the packed-quant matmul path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A *step* is one decode token step (batch B, default 1) through the 64-layer stack of
+``ferric_b200.stack`` -- per layer the fused q|k|v, o, gate|up+SwiGLU (Q4_K) and down (Q6_K)
+products with their norms; 13.36 GB of weights streamed per step, sharded tensor-parallel over N
+GPUs with two f32 all-reduces per layer.  Weights are synthetic (random-init blocks of the named
+shapes and value distributions, generated on the device); the working set per GPU is far larger
+than L2, so every step reads its weights from HBM.
+
+Prints ONE JSON line (rank 0).  `value` is device-timed with inputs resident; `e2e` is the same
+step driven through host buffers (pinned-host -> device copy of the activations, device -> host
+read of the result, every step).  `roofline` is measured live for the dominant kernel, the Q4_K
+gate|up GEMV.  `cpu_baseline` times the CPU oracle port on this box's host cores on a bounded
+sample.  ``--impl reference`` runs only that CPU path, in the same units.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_LAYERS, HIDDEN, N_FF, Q_OUT, KV_OUT = 64, 5120, 17408, 5120, 1024
+WORKLOAD = ("configs[4] at batch {b}: 64 x configs[1] layer (q|k|v 7168x5120, o 5120x5120, gate|up 34816x5120 Q4_K; "
+            "down 5120x17408 Q6_K), f32 activations")
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch kernels directly instead of replaying a CUDA graph")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-matrix table")
+    return ap.parse_args()
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU leg: the oracle port of the reference's CPU path, all host threads, on a bounded sample.
+# ------------------------------------------------------------------------------------------------
+class CpuLayer:
+    """ONE layer's four products on the host cores through the oracle port (weights built once)."""
+
+    def __init__(self, batch: int):
+        from ferric_b200 import synth
+        from oracle import oracle as O
+
+        self.O, self.cores, self.batch = O, os.cpu_count() or 1, batch
+        mats = [(synth.GGML_Q4_K, Q_OUT + 2 * KV_OUT, HIDDEN), (synth.GGML_Q4_K, HIDDEN, Q_OUT),
+                (synth.GGML_Q4_K, 2 * N_FF, HIDDEN), (synth.GGML_Q6_K, HIDDEN, N_FF)]
+        self.data = [(ty, r, c, synth.matrix(ty, r, c, seed=4 + i), synth.activations(batch, c, seed=4 + i))
+                     for i, (ty, r, c) in enumerate(mats)]
+
+    def seconds(self, mode_name: str = "dequant_dot") -> float:
+        O = self.O
+        mode = {"dequant_dot": O.MODE_DEQUANT_DOT, "fused": O.MODE_FUSED}[mode_name]
+        t0 = time.perf_counter()
+        for ty, r, c, raw, x in self.data:
+            y = O.matmul_q(raw, ty, r, c, x, threads=self.cores, mode=mode)
+            if r == 2 * N_FF:
+                O.swiglu(y, N_FF)
+        return time.perf_counter() - t0
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's CPU implementation of the path (oracle port; the Rust
+    reference cannot be built in this image), timed on the host cores in the bench's own units."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    batch = args.batch
+    times = []
+    layer = CpuLayer(batch)
+    cores = layer.cores
+    spent = 0.0
+    for i in range(args.warmup + args.steps):
+        t = layer.seconds()
+        spent += t
+        if i >= args.warmup:
+            times.append(t)
+        if spent > 120 and len(times) >= 3:  # keep the whole run within a few minutes
+            break
+    per_layer = statistics.median(times)
+    step_s = per_layer * args.layers
+    value = batch / step_s
+    sample = (f"1 of {args.layers} layers per step (4 products, 208.8 MB of weights), dequantise-then-dot order, "
+              f"{cores} threads; step time = {args.layers} x layer time")
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup, "ms_per_step": step_s * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD.format(b=batch), "batch": batch, "layers": args.layers, "parallelism": "cpu"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks during the timed region (read-only NVML queries)
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nv:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from ferric_b200 import Context, QMatrix
+    from ferric_b200.stack import DecodeStack, TPPlan
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback on this path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    ctx = Context(local)
+    plan = TPPlan.make(world, rank, HIDDEN, N_FF, Q_OUT, KV_OUT)
+    allreduce = (lambda t: dist.all_reduce(t)) if world > 1 else None
+    stack = DecodeStack(ctx, plan, n_layers=args.layers, batch=B, all_reduce=allreduce)
+    stack.build_synthetic(seed=4)
+    g = torch.Generator(device=dev).manual_seed(4)
+    x0 = torch.randn((B, HIDDEN), device=dev, generator=g)
+    if world > 1:
+        dist.broadcast(x0, 0)
+    stack.h.copy_(x0)
+    if not args.no_graph:
+        stack.capture()
+    else:
+        stack.step()
+    launches_per_step = stack.launches_per_step
+
+    # ---- device-timed: inputs resident ----------------------------------------------------
+    for _ in range(W):
+        stack.h.copy_(x0)
+        stack.run()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        ev0.record()
+        for _ in range(K):
+            stack.run()
+        ev1.record()
+        torch.cuda.synchronize(dev)
+    barrier()
+    elapsed_ms = max_over_ranks(ev0.elapsed_time(ev1))
+    finite = bool(torch.isfinite(stack.h).all().item())
+    ms_per_step = elapsed_ms / K
+    value = B * 1e3 / ms_per_step
+
+    # ---- end to end: host buffers in and out, every step -----------------------------------
+    xh = torch.empty((B, HIDDEN), dtype=torch.float32).pin_memory()
+    yh = torch.empty((B, HIDDEN), dtype=torch.float32).pin_memory()
+    xh.copy_(x0.cpu())
+    for _ in range(3):
+        stack.step_host(xh, yh)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        stack.step_host(xh, yh)
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    e2e = {"value": B * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": xh.numel() * 4,
+           "d2h_bytes_per_step": yh.numel() * 4, "ms_per_step": e2e_s * 1e3 / K}
+
+    # ---- roofline of the dominant kernel: the Q4_K gate|up GEMV with the SwiGLU epilogue ----
+    peak, peak_kind = measured_peak()
+    L0 = stack.layers[0]
+    m = L0.wgu.prepare(stack.xn)
+    reps = 3
+    for L in stack.layers:                                   # warm-up pass over every matrix
+        L.wgu.matmul_prepared(m, out=stack.f, swiglu=True)
+    torch.cuda.synchronize(dev)
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for _ in range(reps):
+        for L in stack.layers:                               # 64 distinct 100 MB matrices: always cold in L2
+            L.wgu.matmul_prepared(m, out=stack.f, swiglu=True)
+    r1.record()
+    torch.cuda.synchronize(dev)
+    n_launch = reps * len(stack.layers)
+    us_per_launch = r0.elapsed_time(r1) * 1e3 / n_launch
+    algo_bytes = L0.wgu.nbytes() + B * HIDDEN * 4 + B * plan.ff_rows * 4
+    achieved = algo_bytes / (us_per_launch * 1e-6) / 1e9
+    traffic = None
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            t = json.load(f).get("gemv_q4k_swiglu", {})
+            if t.get("rows") == L0.wgu.rows() and t.get("cols") == L0.wgu.cols() and t.get("m") == B:
+                traffic = t.get("dram_bytes_per_launch")
+    except Exception:
+        pass
+    roofline = {"kernel": "gemv_q4k_kernel<swiglu>", "shape": [L0.wgu.rows(), L0.wgu.cols(), B], "bound": "hbm",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                "algorithmic_bytes_per_launch": algo_bytes, "us_per_launch": us_per_launch, "traffic": traffic}
+
+    # whole-step HBM efficiency, for context: weight bytes per step per GPU / device time
+    step_gbs = stack.weight_bytes_per_step() / (ms_per_step * 1e-3) / 1e9
+
+    extras = None
+    if rank == 0 and world == 1 and not args.no_extras:
+        extras = per_matrix_table(torch, ctx, stack, QMatrix, B, peak)
+
+    cpu = None
+    if rank == 0 and world == 1:
+        layer = CpuLayer(B)
+        cores = layer.cores
+        t_layer = min(layer.seconds() for _ in range(3))
+        t_fused = min(layer.seconds("fused") for _ in range(2))
+        cpu = {"value": B / (t_layer * args.layers), "unit": "tokens/s", "cores": cores, "kind": "port",
+               "sample": f"1 of {args.layers} layers (208.8 MB of weights), best of 3, dequantise-then-dot order, "
+                         f"{cores} threads; step time = {args.layers} x layer time",
+               "fused_order_value": B / (t_fused * args.layers)}
+
+    if rank == 0:
+        line = {
+            "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD.format(b=B), "batch": B, "layers": args.layers,
+                       "parallelism": f"tp{world}", "cuda_graph": not args.no_graph,
+                       "l2": f"{stack.weight_bytes_per_step() / 1e9:.2f} GB of weights per GPU per step, larger than L2",
+                       "all_reduce": "nccl" if world > 1 else "none"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": int(launches_per_step * K), "launches_per_step": int(launches_per_step),
+            "clocks": clocks.summary(), "step_weight_gbs_per_gpu": step_gbs, "output_finite": finite,
+            "extras": extras,
+        }
+        print(json.dumps(line), flush=True)
+    stack.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def per_matrix_table(torch, ctx, stack, QMatrix, B, peak):
+    """GB/s of each product of the layer (prepare + GEMV, cold: cycling over all layers' copies)."""
+    out = {}
+    p = stack.plan
+    cases = [("qkv_q4k_7168x5120", "wqkv", stack.xn, stack.qkv), ("o_q4k_5120x5120", "wo", stack.qkv[:, :p.q_rows], stack.o),
+             ("gate_up_swiglu_q4k_34816x5120", "wgu", stack.xn, stack.f), ("down_q6k_5120x17408", "wdown", stack.f, stack.d)]
+    for name, attr, x, y in cases:
+        def once():
+            for L in stack.layers:
+                w = getattr(L, attr)
+                if attr == "wgu":
+                    w.try_matmul_swiglu(x, out=y)
+                else:
+                    w.matmul(x, out=y)
+        once()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        once()
+        once()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (2 * len(stack.layers))
+        w = getattr(stack.layers[0], attr)
+        nbytes = w.nbytes() + x.shape[0] * x.shape[1] * 4 + y.numel() * 4
+        out[name] = {"us": us, "GB/s": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak, "launches": 2}
+    return out
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

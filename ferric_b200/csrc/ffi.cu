@@ -1,0 +1,641 @@
+// The C ABI (include/ferric_cuda.h): argument checking, ownership, stream plumbing.
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <new>
+
+#include "../../include/ferric_cuda.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ferric {
+
+static thread_local char g_last_error[512] = "";
+
+void set_last_error(const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_last_error, sizeof g_last_error, fmt, ap);
+    va_end(ap);
+}
+
+int32_t cuda_fail(cudaError_t e, const char* what)
+{
+    set_last_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return e == cudaErrorMemoryAllocation ? kErrOom : kErrCuda;
+}
+
+}  // namespace ferric
+
+using namespace ferric;
+
+struct ferric_cuda_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    uint64_t launches = 0;
+    GemvTuning tune;
+    cudaDeviceProp prop;
+};
+
+struct ferric_qmatrix {
+    uint32_t ty = 0;
+    int device = 0;
+    DeviceWeights w;
+    void* storage = nullptr;
+    size_t storage_bytes = 0;
+};
+
+namespace {
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int dev)
+    {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard()
+    {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+bool block_info(uint32_t ty, size_t* vals, size_t* bytes)
+{
+    switch (ty) {
+    case kGgmlQ8_0: *vals = 32; *bytes = 34; return true;
+    case kGgmlQ4K: *vals = 256; *bytes = 144; return true;
+    case kGgmlQ6K: *vals = 256; *bytes = 210; return true;
+    default: return false;
+    }
+}
+
+int32_t ensure_scratch(ferric_cuda_ctx* ctx, size_t bytes)
+{
+    if (bytes <= ctx->scratch_bytes) return kOk;
+    // Stream-ordered, so a buffer still read by queued kernels is released only after them.
+    if (ctx->scratch) FERRIC_CUDA_TRY(cudaFreeAsync(ctx->scratch, ctx->stream));
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+    size_t want = bytes + bytes / 4 + 4096;
+    FERRIC_CUDA_TRY(cudaMallocAsync(&ctx->scratch, want, ctx->stream));
+    ctx->scratch_bytes = want;
+    return kOk;
+}
+
+int32_t check_matmul_args(const ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const void* x, size_t m,
+                          size_t x_cols, const void* y)
+{
+    if (!ctx || !qm) {
+        set_last_error("NULL context or matrix handle");
+        return kErrInvalidArg;
+    }
+    if (qm->device != ctx->device) {
+        set_last_error("matrix lives on device %d, context on device %d", qm->device, ctx->device);
+        return kErrInvalidArg;
+    }
+    if (x_cols != qm->w.cols) {
+        set_last_error("inner dim mismatch: x[..,%zu] vs W[..,%zu]", x_cols, qm->w.cols);
+        return kErrShape;
+    }
+    if (m > 0 && ((!x && qm->w.cols > 0) || (!y && qm->w.rows > 0))) {
+        set_last_error("NULL activation or result buffer");
+        return kErrInvalidArg;
+    }
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 3)) {
+        set_last_error("activation buffer must be 16-byte aligned (result 4-byte)");
+        return kErrInvalidArg;
+    }
+    return kOk;
+}
+
+int32_t build_matrix(ferric_cuda_ctx* ctx, const uint8_t* bytes, bool on_device, size_t len, uint32_t ty,
+                     size_t rows, size_t cols, size_t row0, size_t nrows, size_t col0, size_t ncols,
+                     ferric_qmatrix** out)
+{
+    if (!ctx || !out) {
+        set_last_error("NULL context or output pointer");
+        return kErrInvalidArg;
+    }
+    *out = nullptr;
+    size_t vals, bbytes;
+    if (!block_info(ty, &vals, &bbytes)) {
+        set_last_error("QMatrix: no native matmul for ggml type %u", ty);
+        return kErrUnsupportedType;
+    }
+    if (cols % vals != 0) {
+        set_last_error("cols (%zu) must be a multiple of %zu for ggml type %u", cols, vals, ty);
+        return kErrShape;
+    }
+    if (len != rows * (cols / vals) * bbytes) {
+        set_last_error("unexpected byte length %zu for [%zu, %zu] of ggml type %u (want %zu)", len, rows, cols, ty,
+                       rows * (cols / vals) * bbytes);
+        return kErrShape;
+    }
+    if (row0 + nrows > rows || col0 + ncols > cols || col0 % vals != 0 || ncols % vals != 0) {
+        set_last_error("sub-matrix [%zu+%zu, %zu+%zu] outside [%zu, %zu] or not block aligned", row0, nrows, col0,
+                       ncols, rows, cols);
+        return kErrShape;
+    }
+    if (len > 0 && !bytes) {
+        set_last_error("NULL weight bytes");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+
+    ferric_qmatrix* qm = new (std::nothrow) ferric_qmatrix;
+    if (!qm) return kErrOom;
+    qm->ty = ty;
+    qm->device = ctx->device;
+    qm->w.rows = nrows;
+    qm->w.cols = ncols;
+    qm->w.nblk = ncols / vals;
+    size_t src_nblk = cols / vals, blk0 = col0 / vals;
+
+    size_t bytes_needed, d_off = 0;
+    if (ty == kGgmlQ8_0) {
+        d_off = (nrows * ncols + 255) / 256 * 256;
+        bytes_needed = d_off + nrows * qm->w.nblk * 2;
+    } else {
+        bytes_needed = qm->w.row_tiles() * qm->w.nblk * 16 * bbytes;
+    }
+    if (bytes_needed == 0) bytes_needed = 16;
+    cudaError_t e = cudaMalloc(&qm->storage, bytes_needed);
+    if (e != cudaSuccess) {
+        delete qm;
+        return cuda_fail(e, "cudaMalloc(weights)");
+    }
+    qm->storage_bytes = bytes_needed;
+    if (ty == kGgmlQ8_0) {
+        qm->w.q8_qs = reinterpret_cast<int8_t*>(qm->storage);
+        qm->w.q8_d = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(qm->storage) + d_off);
+    } else {
+        qm->w.units = reinterpret_cast<uint8_t*>(qm->storage);
+    }
+
+    int32_t rc = kOk;
+    void* staging = nullptr;
+    do {
+        // rows past `nrows` in the last 16-row tile stay zero (d = 0 -> they contribute nothing)
+        if ((e = cudaMemsetAsync(qm->storage, 0, bytes_needed, ctx->stream)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemsetAsync"); break; }
+        const uint8_t* src = bytes;
+        if (!on_device && len > 0) {
+            // stage only the row range that is needed
+            size_t row_bytes = src_nblk * bbytes, off = row0 * row_bytes, n = nrows * row_bytes;
+            if (n > 0) {
+                if ((e = cudaMalloc(&staging, n)) != cudaSuccess) { rc = cuda_fail(e, "cudaMalloc(staging)"); break; }
+                if ((e = cudaMemcpyAsync(staging, bytes + off, n, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemcpyAsync(weights)"); break; }
+            }
+            src = reinterpret_cast<const uint8_t*>(staging);
+            row0 = 0;
+        }
+        if (nrows > 0 && qm->w.nblk > 0) {
+            rc = launch_repack(ctx->stream, ty, src, qm->w, src_nblk, row0, blk0);
+            ctx->launches++;
+        }
+        if (rc != kOk) break;
+        // the host bytes / staging buffer must not be needed after return
+        if ((e = cudaStreamSynchronize(ctx->stream)) != cudaSuccess) { rc = cuda_fail(e, "cudaStreamSynchronize"); break; }
+    } while (0);
+    if (staging) cudaFree(staging);
+    if (rc != kOk) {
+        cudaFree(qm->storage);
+        delete qm;
+        return rc;
+    }
+    *out = qm;
+    return kOk;
+}
+
+// phases: 1 = prepare activation fragments, 2 = product from prepared fragments, 3 = both
+int32_t run_matmul(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x, size_t m, size_t ldx, float* y,
+                   size_t ldy, Epilogue epi, int phases = 3)
+{
+    if (m == 0 || qm->w.rows == 0) return kOk;
+    const size_t out_cols = epi == kEpiSwiglu ? qm->w.rows / 2 : qm->w.rows;
+    if (ldx == 0) ldx = qm->w.cols;
+    if (ldy == 0) ldy = out_cols;
+    if (ldx < qm->w.cols || ldy < out_cols || (ldx & 3)) {
+        set_last_error("row strides (ldx %zu, ldy %zu) must cover the rows and ldx be a multiple of 4", ldx, ldy);
+        return kErrShape;
+    }
+    if (qm->ty == kGgmlQ8_0) {
+        if (!(phases & 2)) return kOk;
+        if (!x) {
+            set_last_error("Q8_0 has no prepared form: pass the activations");
+            return kErrInvalidArg;
+        }
+        ctx->launches++;
+        return launch_gemv_q8_0(ctx->stream, qm->w, x, m, ldx, y, ldy, ctx->tune);
+    }
+    if (qm->w.nblk == 0) {  // cols == 0: an empty sum
+        if (phases & 2) FERRIC_CUDA_TRY(cudaMemset2DAsync(y, ldy * sizeof(float), 0, out_cols * sizeof(float), m, ctx->stream));
+        return kOk;
+    }
+    const size_t need = frag_bytes(qm->ty, qm->w, m);
+    int32_t rc = kOk;
+    if (phases & 1) {
+        if ((rc = ensure_scratch(ctx, need)) != kOk) return rc;
+        if ((rc = launch_prep(ctx->stream, qm->ty, qm->w, x, m, ldx, ctx->scratch)) != kOk) return rc;
+        ctx->launches++;
+    }
+    if (phases & 2) {
+        if (ctx->scratch_bytes < need) {
+            set_last_error("no prepared activations on this context for m = %zu", m);
+            return kErrInvalidArg;
+        }
+        rc = launch_gemv(ctx->stream, qm->ty, qm->w, ctx->scratch, m, y, ldy, epi, ctx->tune);
+        ctx->launches++;
+    }
+    return rc;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* ferric_cuda_last_error(void) { return g_last_error; }
+
+int32_t ferric_gguf_type_size(uint32_t ty, size_t n, size_t* out_bytes)
+{
+    if (!out_bytes) {
+        set_last_error("NULL output pointer");
+        return kErrInvalidArg;
+    }
+    switch (ty) {
+    case FERRIC_GGML_F32: *out_bytes = n * 4; return kOk;
+    case FERRIC_GGML_F16: *out_bytes = n * 2; return kOk;
+    case FERRIC_GGML_BF16: *out_bytes = n * 2; return kOk;
+    case FERRIC_GGML_Q8_0: *out_bytes = n / 32 * 34; return kOk;
+    case FERRIC_GGML_Q4_K: *out_bytes = n / 256 * 144; return kOk;
+    case FERRIC_GGML_Q6_K: *out_bytes = n / 256 * 210; return kOk;
+    default:
+        set_last_error("unsupported ggml type %u", ty);
+        return kErrUnsupportedType;
+    }
+}
+
+int32_t ferric_cuda_qmatrix_block_bytes(uint32_t ty, size_t* vals, size_t* bytes)
+{
+    if (!vals || !bytes) {
+        set_last_error("NULL output pointer");
+        return kErrInvalidArg;
+    }
+    if (!block_info(ty, vals, bytes)) return kUnsupported;
+    return kOk;
+}
+
+int32_t ferric_cuda_ctx_create_on_stream(int device, void* cuda_stream, ferric_cuda_ctx** out)
+{
+    if (!out) {
+        set_last_error("NULL output pointer");
+        return kErrInvalidArg;
+    }
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        set_last_error("no CUDA device available (%s); this backend has no CPU fallback",
+                       e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+        return kErrCuda;
+    }
+    if (device < 0 || device >= count) {
+        set_last_error("device %d out of range [0, %d)", device, count);
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+    ferric_cuda_ctx* ctx = new (std::nothrow) ferric_cuda_ctx;
+    if (!ctx) return kErrOom;
+    ctx->device = device;
+    ctx->stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    if ((e = cudaGetDeviceProperties(&ctx->prop, device)) != cudaSuccess) {
+        delete ctx;
+        return cuda_fail(e, "cudaGetDeviceProperties");
+    }
+    if (ctx->prop.major < 10) {
+        set_last_error("device %d is sm_%d%d; this library holds sm_100a code only", device, ctx->prop.major,
+                       ctx->prop.minor);
+        delete ctx;
+        return kErrCuda;
+    }
+    ctx->tune.sm_count = ctx->prop.multiProcessorCount;
+    if (const char* s = getenv("FERRIC_CUDA_GEMV_WK")) ctx->tune.wk = atoi(s);
+    *out = ctx;
+    return kOk;
+}
+
+int32_t ferric_cuda_ctx_create(int device, ferric_cuda_ctx** out)
+{
+    int32_t rc = ferric_cuda_ctx_create_on_stream(device, nullptr, out);
+    if (rc != kOk) return rc;
+    DeviceGuard guard(device);
+    cudaError_t e = cudaStreamCreateWithFlags(&(*out)->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete *out;
+        *out = nullptr;
+        return cuda_fail(e, "cudaStreamCreateWithFlags");
+    }
+    (*out)->owns_stream = true;
+    return kOk;
+}
+
+int32_t ferric_cuda_ctx_set_stream(ferric_cuda_ctx* ctx, void* cuda_stream)
+{
+    if (!ctx) {
+        set_last_error("NULL context");
+        return kErrInvalidArg;
+    }
+    if (ctx->owns_stream) {
+        DeviceGuard guard(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+        cudaStreamDestroy(ctx->stream);
+        ctx->owns_stream = false;
+    }
+    ctx->stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    return kOk;
+}
+
+void* ferric_cuda_ctx_stream(const ferric_cuda_ctx* ctx) { return ctx ? ctx->stream : nullptr; }
+
+int32_t ferric_cuda_ctx_sync(ferric_cuda_ctx* ctx)
+{
+    if (!ctx) {
+        set_last_error("NULL context");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    FERRIC_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return kOk;
+}
+
+void ferric_cuda_ctx_free(ferric_cuda_ctx* ctx)
+{
+    if (!ctx) return;
+    DeviceGuard guard(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+int32_t ferric_cuda_ctx_caps(const ferric_cuda_ctx* ctx, ferric_cuda_caps* out)
+{
+    if (!ctx || !out) {
+        set_last_error("NULL context or output pointer");
+        return kErrInvalidArg;
+    }
+    out->device = ctx->device;
+    out->sm_count = ctx->prop.multiProcessorCount;
+    out->cc_major = ctx->prop.major;
+    out->cc_minor = ctx->prop.minor;
+    out->l2_bytes = (uint64_t)ctx->prop.l2CacheSize;
+    out->total_mem_bytes = (uint64_t)ctx->prop.totalGlobalMem;
+    out->max_smem_per_block = (uint64_t)ctx->prop.sharedMemPerBlockOptin;
+    return kOk;
+}
+
+int32_t ferric_cuda_ctx_reserve_scratch(ferric_cuda_ctx* ctx, size_t bytes)
+{
+    if (!ctx) {
+        set_last_error("NULL context");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    return ensure_scratch(ctx, bytes);
+}
+
+uint64_t ferric_cuda_ctx_launches(const ferric_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int32_t ferric_cuda_qmatrix_from_bytes(ferric_cuda_ctx* ctx, const uint8_t* bytes, size_t len, uint32_t ty,
+                                       size_t rows, size_t cols, ferric_qmatrix** out)
+{
+    return build_matrix(ctx, bytes, false, len, ty, rows, cols, 0, rows, 0, cols, out);
+}
+
+int32_t ferric_cuda_qmatrix_from_bytes_view(ferric_cuda_ctx* ctx, const uint8_t* bytes, size_t len, uint32_t ty,
+                                            size_t rows, size_t cols, size_t row0, size_t nrows, size_t col0,
+                                            size_t ncols, ferric_qmatrix** out)
+{
+    return build_matrix(ctx, bytes, false, len, ty, rows, cols, row0, nrows, col0, ncols, out);
+}
+
+int32_t ferric_cuda_qmatrix_from_device_bytes(ferric_cuda_ctx* ctx, const uint8_t* bytes_dev, size_t len, uint32_t ty,
+                                              size_t rows, size_t cols, ferric_qmatrix** out)
+{
+    return build_matrix(ctx, bytes_dev, true, len, ty, rows, cols, 0, rows, 0, cols, out);
+}
+
+size_t ferric_cuda_qmatrix_rows(const ferric_qmatrix* qm) { return qm ? qm->w.rows : 0; }
+size_t ferric_cuda_qmatrix_cols(const ferric_qmatrix* qm) { return qm ? qm->w.cols : 0; }
+size_t ferric_cuda_qmatrix_nbytes(const ferric_qmatrix* qm)
+{
+    if (!qm) return 0;
+    size_t vals, bytes;
+    block_info(qm->ty, &vals, &bytes);
+    return qm->w.rows * (qm->w.cols / vals) * bytes;
+}
+size_t ferric_cuda_qmatrix_n_shards(const ferric_qmatrix* qm) { return qm ? 1 : 0; }
+uint32_t ferric_cuda_qmatrix_ggml_type(const ferric_qmatrix* qm) { return qm ? qm->ty : 0; }
+
+void ferric_cuda_qmatrix_free(ferric_qmatrix* qm)
+{
+    if (!qm) return;
+    DeviceGuard guard(qm->device);
+    cudaFree(qm->storage);
+    delete qm;
+}
+
+size_t ferric_cuda_qmatrix_scratch_bytes(const ferric_qmatrix* qm, size_t m)
+{
+    return qm ? frag_bytes(qm->ty, qm->w, m) : 0;
+}
+
+int32_t ferric_cuda_matmul_q(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_dev, size_t m,
+                             size_t x_cols, float* y_dev)
+{
+    int32_t rc = check_matmul_args(ctx, qm, x_dev, m, x_cols, y_dev);
+    if (rc != kOk) return rc;
+    DeviceGuard guard(ctx->device);
+    return run_matmul(ctx, qm, x_dev, m, 0, y_dev, 0, kEpiStore);
+}
+
+int32_t ferric_cuda_matmul_q_swiglu(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_dev, size_t m,
+                                    size_t x_cols, float* y_dev)
+{
+    int32_t rc = check_matmul_args(ctx, qm, x_dev, m, x_cols, y_dev);
+    if (rc != kOk) return rc;
+    if (qm->ty == kGgmlQ8_0 || qm->w.rows % 32 != 0) return kUnsupported;
+    DeviceGuard guard(ctx->device);
+    return run_matmul(ctx, qm, x_dev, m, 0, y_dev, 0, kEpiSwiglu);
+}
+
+int32_t ferric_cuda_matmul_q_ld(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_dev, size_t m,
+                                size_t x_cols, size_t ldx, float* y_dev, size_t ldy)
+{
+    int32_t rc = check_matmul_args(ctx, qm, x_dev, m, x_cols, y_dev);
+    if (rc != kOk) return rc;
+    DeviceGuard guard(ctx->device);
+    return run_matmul(ctx, qm, x_dev, m, ldx, y_dev, ldy, kEpiStore);
+}
+
+int32_t ferric_cuda_prepare_x(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_dev, size_t m,
+                              size_t x_cols, size_t ldx)
+{
+    float dummy;
+    int32_t rc = check_matmul_args(ctx, qm, x_dev, m, x_cols, &dummy);
+    if (rc != kOk) return rc;
+    DeviceGuard guard(ctx->device);
+    return run_matmul(ctx, qm, x_dev, m, ldx, nullptr, 0, kEpiStore, 1);
+}
+
+int32_t ferric_cuda_matmul_q_prepared(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, size_t m, float* y_dev,
+                                      size_t ldy, int32_t swiglu)
+{
+    if (!ctx || !qm || (m > 0 && !y_dev && qm->w.rows > 0)) {
+        set_last_error("NULL context, matrix or result buffer");
+        return kErrInvalidArg;
+    }
+    if (qm->ty == kGgmlQ8_0) {
+        set_last_error("Q8_0 has no prepared form");
+        return kUnsupported;
+    }
+    if (swiglu && qm->w.rows % 32 != 0) return kUnsupported;
+    DeviceGuard guard(ctx->device);
+    return run_matmul(ctx, qm, nullptr, m, 0, y_dev, ldy, swiglu ? kEpiSwiglu : kEpiStore, 2);
+}
+
+int32_t ferric_cuda_add_rmsnorm(ferric_cuda_ctx* ctx, const float* a_dev, const float* b_dev, const float* weight_dev,
+                                float eps, size_t rows, size_t d, float* sum_dev, float* norm_dev)
+{
+    if (!ctx || (rows * d > 0 && (!a_dev || !norm_dev))) {
+        set_last_error("NULL context or buffer");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    ctx->launches++;
+    return launch_add_rmsnorm(ctx->stream, a_dev, b_dev, weight_dev, eps, rows, d, sum_dev, norm_dev);
+}
+
+int32_t ferric_cuda_matmul_q_host(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_host, size_t m,
+                                  size_t x_cols, float* y_host)
+{
+    if (!ctx || !qm) {
+        set_last_error("NULL context or matrix handle");
+        return kErrInvalidArg;
+    }
+    if (x_cols != qm->w.cols) {
+        set_last_error("inner dim mismatch: x[..,%zu] vs W[..,%zu]", x_cols, qm->w.cols);
+        return kErrShape;
+    }
+    if (m == 0) return kOk;
+    if (!x_host || !y_host) {
+        set_last_error("NULL activation or result buffer");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    size_t xb = m * x_cols * sizeof(float), yb = m * qm->w.rows * sizeof(float);
+    size_t xoff = (xb + 255) / 256 * 256;
+    void* buf = nullptr;
+    FERRIC_CUDA_TRY(cudaMallocAsync(&buf, xoff + yb + 16, ctx->stream));
+    float* xd = reinterpret_cast<float*>(buf);
+    float* yd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(buf) + xoff);
+    int32_t rc = kOk;
+    cudaError_t e;
+    do {
+        if (xb && (e = cudaMemcpyAsync(xd, x_host, xb, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemcpyAsync(x)"); break; }
+        if ((rc = run_matmul(ctx, qm, xd, m, 0, yd, 0, kEpiStore)) != kOk) break;
+        if (yb && (e = cudaMemcpyAsync(y_host, yd, yb, cudaMemcpyDeviceToHost, ctx->stream)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemcpyAsync(y)"); break; }
+    } while (0);
+    cudaFreeAsync(buf, ctx->stream);
+    e = cudaStreamSynchronize(ctx->stream);
+    if (rc == kOk && e != cudaSuccess) rc = cuda_fail(e, "cudaStreamSynchronize");
+    return rc;
+}
+
+int32_t ferric_cuda_swiglu(ferric_cuda_ctx* ctx, const float* gu_dev, size_t t, size_t d, float* out_dev)
+{
+    if (!ctx || (t * d > 0 && (!gu_dev || !out_dev))) {
+        set_last_error("NULL context or buffer");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    ctx->launches++;
+    return launch_swiglu(ctx->stream, gu_dev, t, d, out_dev);
+}
+
+int32_t ferric_cuda_dequant_f32(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, float* out_dev)
+{
+    if (!ctx || !qm || (!out_dev && qm->w.rows * qm->w.cols > 0)) {
+        set_last_error("NULL context, matrix or output");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    ctx->launches++;
+    return launch_dequant_weights(ctx->stream, qm->ty, qm->w, out_dev, false);
+}
+
+int32_t ferric_cuda_dequant_bf16(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, uint16_t* out_dev)
+{
+    if (!ctx || !qm || (!out_dev && qm->w.rows * qm->w.cols > 0)) {
+        set_last_error("NULL context, matrix or output");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    ctx->launches++;
+    return launch_dequant_weights(ctx->stream, qm->ty, qm->w, out_dev, true);
+}
+
+int32_t ferric_gguf_deq_raw(ferric_cuda_ctx* ctx, const uint8_t* raw, size_t raw_len, size_t n, uint32_t ty,
+                            float* out)
+{
+    if (!ctx) {
+        set_last_error("NULL context");
+        return kErrInvalidArg;
+    }
+    size_t vals, bbytes;
+    if (!block_info(ty, &vals, &bbytes)) {
+        set_last_error("unsupported ggml type %u", ty);
+        return kErrUnsupportedType;
+    }
+    size_t need = n / vals * bbytes;
+    if (raw_len < need) {
+        set_last_error("raw buffer too short: %zu bytes for %zu elements of type %u (need %zu)", raw_len, n, ty, need);
+        return kErrShape;
+    }
+    if (n == 0) return kOk;
+    if (!raw || !out) {
+        set_last_error("NULL buffer");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    size_t roff = (need + 255) / 256 * 256 + 256;
+    void* buf = nullptr;
+    FERRIC_CUDA_TRY(cudaMallocAsync(&buf, roff + n * sizeof(float), ctx->stream));
+    uint8_t* rd = reinterpret_cast<uint8_t*>(buf);
+    float* od = reinterpret_cast<float*>(rd + roff);
+    int32_t rc = kOk;
+    cudaError_t e;
+    do {
+        // elements past the last whole block stay zero, as in the reference (vec![0.0; n])
+        if ((e = cudaMemsetAsync(od, 0, n * sizeof(float), ctx->stream)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemsetAsync"); break; }
+        if (need && (e = cudaMemcpyAsync(rd, raw, need, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemcpyAsync(raw)"); break; }
+        if ((rc = launch_dequant_raw(ctx->stream, ty, rd, n, od, false)) != kOk) break;
+        ctx->launches++;
+        if ((e = cudaMemcpyAsync(out, od, n * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemcpyAsync(out)"); break; }
+    } while (0);
+    cudaFreeAsync(buf, ctx->stream);
+    e = cudaStreamSynchronize(ctx->stream);
+    if (rc == kOk && e != cudaSuccess) rc = cuda_fail(e, "cudaStreamSynchronize");
+    return rc;
+}
+
+}  // extern "C"

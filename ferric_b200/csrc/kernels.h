@@ -1,0 +1,55 @@
+// Internal launch interface between the C ABI (ffi.cu) and the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace ferric {
+
+constexpr uint32_t kGgmlQ8_0 = 8, kGgmlQ4K = 12, kGgmlQ6K = 14;
+
+// One packed weight matrix in device memory.  rows x cols logical; nblk = blocks per row
+// (256-weight super-blocks for Q4_K/Q6_K, 32-weight blocks for Q8_0).
+struct DeviceWeights {
+    uint8_t* units = nullptr;    // Q4_K / Q6_K: ceil(rows/16) * nblk units, zero padded past `rows`
+    int8_t* q8_qs = nullptr;     // Q8_0: [rows][cols] int8
+    uint16_t* q8_d = nullptr;    // Q8_0: [rows][cols/32] f16 bits
+    size_t rows = 0, cols = 0, nblk = 0;
+    size_t row_tiles() const { return (rows + 15) / 16; }
+};
+
+enum Epilogue : int { kEpiStore = 0, kEpiSwiglu = 1 };
+
+// Tunables read once from the environment (FERRIC_CUDA_*), the counterpart of the reference's
+// FERRIC_* kernel-selection flags (docs/FLAGS.md, crates/ferric-tensor/src/dtype.rs:2173-2187).
+struct GemvTuning {
+    int wk = 0;        // warps of a CTA that split K (0 = choose from the shape)
+    int sm_count = 148;
+};
+
+int32_t launch_repack(cudaStream_t st, uint32_t ty, const uint8_t* src, DeviceWeights& w, size_t src_nblk,
+                      size_t row0, size_t blk0);
+int32_t launch_dequant_weights(cudaStream_t st, uint32_t ty, const DeviceWeights& w, void* out, bool bf16);
+int32_t launch_dequant_raw(cudaStream_t st, uint32_t ty, const uint8_t* raw, size_t n, void* out, bool bf16);
+
+// Bytes of activation-fragment scratch a matmul with m activation rows needs for this matrix.
+size_t frag_bytes(uint32_t ty, const DeviceWeights& w, size_t m);
+// x[m, cols] (f32, row stride ldx) -> tensor-core B fragments in `frag`.
+int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* x, size_t m, size_t ldx,
+                    void* frag);
+// y[m, rows] (row stride ldy) = x . W^T from prepared fragments.  With kEpiSwiglu the matrix is
+// [gate rows | up rows] and y is [m, rows/2] = silu(gate) * up.
+int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const void* frag, size_t m, float* y,
+                    size_t ldy, Epilogue epi, const GemvTuning& tune);
+// Q8_0 needs no fragments: y = x . W^T straight from f32 activations.
+int32_t launch_gemv_q8_0(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y,
+                         size_t ldy, const GemvTuning& tune);
+// out[t, d] = silu(gu[t, d]) * gu[t, d + ..] on a [t, 2d] tensor (the unfused twin).
+int32_t launch_swiglu(cudaStream_t st, const float* gu, size_t t, size_t d, float* out);
+
+// (sum, norm) = (a + b, rmsnorm(a + b) * weight); b and weight may be null (no add / unit weight),
+// sum may be null.
+int32_t launch_add_rmsnorm(cudaStream_t st, const float* a, const float* b, const float* weight, float eps,
+                           size_t rows, size_t d, float* sum, float* norm);
+
+}  // namespace ferric

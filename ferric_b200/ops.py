@@ -1,0 +1,289 @@
+"""Python mirror of the reference's QMatrix / matmul_q operator interface (see package docstring)."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+
+GGML_F32, GGML_F16, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K, GGML_BF16 = 0, 1, 8, 12, 14, 30
+
+
+class FerricError(RuntimeError):
+    """A failing C-ABI call: ``status`` is the FERRIC_* code, the text is ferric_cuda_last_error().
+
+    Stands for the reference's ``Err(String)`` (unsupported type) and its ``assert!`` panics
+    (shape errors), crates/ferric-tensor/src/dtype.rs:855, :1389-1390, :1429.
+    """
+
+    def __init__(self, status: int, where: str):
+        msg = _lib.load().ferric_cuda_last_error().decode("utf-8", "replace")
+        super().__init__(f"{where}: {_lib.STATUS_NAMES[status] if 0 <= status < 8 else status}: {msg}")
+        self.status = status
+
+
+def _check(status: int, where: str) -> None:
+    if status != _lib.OK:
+        raise FerricError(status, where)
+
+
+def type_size(ggml_type: int, n: int) -> int:
+    """``ferric_gguf::type_size`` (crates/ferric-gguf/src/lib.rs:471-494)."""
+    out = C.c_size_t(0)
+    _check(_lib.load().ferric_gguf_type_size(ggml_type, n, C.byref(out)), "type_size")
+    return out.value
+
+
+def _as_u8(raw) -> np.ndarray:
+    if isinstance(raw, np.ndarray):
+        return np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1)
+    return np.frombuffer(raw, dtype=np.uint8)
+
+
+class Context:
+    """A device + stream, the counterpart of ``ferric_core::Context`` (crates/ferric-core/src/lib.rs:19-43).
+
+    ``stream=None`` makes the context own a stream; ``stream="torch"`` binds it to torch's current
+    stream on that device so operator calls order with surrounding torch work.
+    """
+
+    def __init__(self, device: int = 0, stream: Optional[object] = "torch"):
+        self._lib = _lib.load()
+        self.device = int(device)
+        h = C.c_void_p()
+        if stream is None:
+            _check(self._lib.ferric_cuda_ctx_create(self.device, C.byref(h)), "Context")
+        else:
+            if stream == "torch":
+                stream = torch.cuda.current_stream(self.device).cuda_stream
+            _check(self._lib.ferric_cuda_ctx_create_on_stream(self.device, C.c_void_p(int(stream)), C.byref(h)),
+                   "Context")
+        self._h = h
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.ferric_cuda_ctx_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_stream(self, cuda_stream: int) -> None:
+        _check(self._lib.ferric_cuda_ctx_set_stream(self._h, C.c_void_p(int(cuda_stream))), "set_stream")
+
+    def use_torch_stream(self) -> None:
+        self.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def sync(self) -> None:
+        _check(self._lib.ferric_cuda_ctx_sync(self._h), "sync")
+
+    def caps(self) -> dict:
+        c = _lib.Caps()
+        _check(self._lib.ferric_cuda_ctx_caps(self._h, C.byref(c)), "caps")
+        return {k: getattr(c, k) for k, _ in _lib.Caps._fields_}
+
+    def launches(self) -> int:
+        return int(self._lib.ferric_cuda_ctx_launches(self._h))
+
+    def reserve_scratch(self, nbytes: int) -> None:
+        _check(self._lib.ferric_cuda_ctx_reserve_scratch(self._h, nbytes), "reserve_scratch")
+
+    def deq_raw(self, raw, n: int, ggml_type: int) -> np.ndarray:
+        """``ferric_gguf::deq_raw`` (crates/ferric-gguf/src/lib.rs:497-520), decoded on the device."""
+        raw = _as_u8(raw)
+        out = np.empty(n, dtype=np.float32)
+        _check(self._lib.ferric_gguf_deq_raw(self._h, raw.ctypes.data, raw.size, n, ggml_type, out.ctypes.data),
+               "deq_raw")
+        return out
+
+    def add_rmsnorm(self, a: torch.Tensor, b: Optional[torch.Tensor] = None, weight: Optional[torch.Tensor] = None,
+                    eps: float = 1e-6, sum_out: Optional[torch.Tensor] = None,
+                    norm_out: Optional[torch.Tensor] = None):
+        """``a.add_rmsnorm(b, weight, eps) -> (sum, norm)`` (crates/ferric-tensor/src/lib.rs:372-384);
+        ``b=None`` is plain ``rmsnorm`` (:346-353), ``weight=None`` the weightless form (:340-344)."""
+        a = a.contiguous()
+        d = a.shape[-1]
+        rows = a.numel() // d
+        if norm_out is None:
+            norm_out = torch.empty_like(a)
+        if b is not None and sum_out is None:
+            sum_out = torch.empty_like(a)
+        _check(self._lib.ferric_cuda_add_rmsnorm(
+            self._h, a.data_ptr(), b.contiguous().data_ptr() if b is not None else None,
+            weight.contiguous().data_ptr() if weight is not None else None, float(eps), rows, d,
+            sum_out.data_ptr() if sum_out is not None else None, norm_out.data_ptr()), "add_rmsnorm")
+        return (sum_out if sum_out is not None else a), norm_out
+
+    def swiglu(self, gu: torch.Tensor, d: int) -> torch.Tensor:
+        """``Tensor::swiglu`` (crates/ferric-tensor/src/lib.rs:726-737)."""
+        gu = gu.contiguous()
+        t = gu.numel() // (2 * d)
+        out = torch.empty((t, d), dtype=torch.float32, device=gu.device)
+        _check(self._lib.ferric_cuda_swiglu(self._h, gu.data_ptr(), t, d, out.data_ptr()), "swiglu")
+        return out
+
+
+class QMatrix:
+    """A packed-quant weight matrix (``ferric_tensor::QMatrix``, crates/ferric-tensor/src/dtype.rs:865-931)."""
+
+    def __init__(self, ctx: Context, handle: C.c_void_p):
+        self.ctx = ctx
+        self._lib = ctx._lib
+        self._h = handle
+
+    @staticmethod
+    def block_bytes(ggml_type: int):
+        """(values per block, bytes per block) or None (crates/ferric-tensor/src/dtype.rs:873-889)."""
+        v, b = C.c_size_t(0), C.c_size_t(0)
+        rc = _lib.load().ferric_cuda_qmatrix_block_bytes(ggml_type, C.byref(v), C.byref(b))
+        if rc == _lib.UNSUPPORTED:
+            return None
+        _check(rc, "block_bytes")
+        return v.value, b.value
+
+    @classmethod
+    def from_bytes(cls, ctx: Context, raw, ggml_type: int, rows: int, cols: int) -> "QMatrix":
+        """``QMatrix::from_bytes`` (crates/ferric-tensor/src/dtype.rs:893-908): raw GGUF block bytes, [out, in]."""
+        raw = _as_u8(raw)
+        h = C.c_void_p()
+        _check(ctx._lib.ferric_cuda_qmatrix_from_bytes(ctx._h, raw.ctypes.data, raw.size, ggml_type, rows, cols,
+                                                       C.byref(h)), "QMatrix.from_bytes")
+        return cls(ctx, h)
+
+    @classmethod
+    def from_bytes_view(cls, ctx: Context, raw, ggml_type: int, rows: int, cols: int, row0: int, nrows: int,
+                        col0: int, ncols: int) -> "QMatrix":
+        """A tensor-parallel shard (row range x K range) of the full tensor's bytes."""
+        raw = _as_u8(raw)
+        h = C.c_void_p()
+        _check(ctx._lib.ferric_cuda_qmatrix_from_bytes_view(ctx._h, raw.ctypes.data, raw.size, ggml_type, rows, cols,
+                                                            row0, nrows, col0, ncols, C.byref(h)),
+               "QMatrix.from_bytes_view")
+        return cls(ctx, h)
+
+    @classmethod
+    def from_device_bytes(cls, ctx: Context, raw: torch.Tensor, ggml_type: int, rows: int, cols: int) -> "QMatrix":
+        """As ``from_bytes`` for block bytes already in device memory (a uint8 CUDA tensor)."""
+        assert raw.is_cuda and raw.dtype == torch.uint8 and raw.is_contiguous()
+        h = C.c_void_p()
+        _check(ctx._lib.ferric_cuda_qmatrix_from_device_bytes(ctx._h, raw.data_ptr(), raw.numel(), ggml_type, rows,
+                                                              cols, C.byref(h)), "QMatrix.from_device_bytes")
+        return cls(ctx, h)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.ferric_cuda_qmatrix_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def rows(self) -> int:
+        return int(self._lib.ferric_cuda_qmatrix_rows(self._h))
+
+    def cols(self) -> int:
+        return int(self._lib.ferric_cuda_qmatrix_cols(self._h))
+
+    def nbytes(self) -> int:
+        return int(self._lib.ferric_cuda_qmatrix_nbytes(self._h))
+
+    def n_shards(self) -> int:
+        return int(self._lib.ferric_cuda_qmatrix_n_shards(self._h))
+
+    def ggml_type(self) -> int:
+        return int(self._lib.ferric_cuda_qmatrix_ggml_type(self._h))
+
+    def scratch_bytes(self, m: int) -> int:
+        return int(self._lib.ferric_cuda_qmatrix_scratch_bytes(self._h, m))
+
+    # -- operators -------------------------------------------------------------------------
+    def _x2d(self, x: torch.Tensor, allow_row_stride: bool = False) -> torch.Tensor:
+        if not x.is_cuda or x.dtype != torch.float32:
+            raise TypeError("activations must be a float32 CUDA tensor")
+        if x.dim() == 1:
+            x = x[None, :]
+        if allow_row_stride and x.dim() == 2 and x.stride(1) == 1 and x.stride(0) >= x.shape[1] \
+                and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0:
+            return x
+        return x.contiguous()
+
+    def matmul(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``x.matmul_q(&w)``: y[m, rows] = x[m, cols] . W^T (crates/ferric-tensor/src/dtype.rs:935-944).
+
+        A column slice of a wider row-major tensor is consumed in place (row stride passed through);
+        ``out`` may likewise be a column slice of a wider result tensor."""
+        x = self._x2d(x, allow_row_stride=True)
+        m = x.shape[0]
+        y = out if out is not None else torch.empty((m, self.rows()), dtype=torch.float32, device=x.device)
+        assert y.stride(-1) == 1
+        ldx = x.stride(0) if m > 1 else 0
+        ldy = y.stride(0) if (y.dim() == 2 and m > 1) else 0
+        _check(self._lib.ferric_cuda_matmul_q_ld(self.ctx._h, self._h, x.data_ptr(), m, x.shape[1], ldx,
+                                                 y.data_ptr(), ldy), "matmul_q")
+        return y
+
+    def prepare(self, x: torch.Tensor) -> int:
+        """First half of ``matmul``: convert x into the context's activation scratch; returns m."""
+        x = self._x2d(x, allow_row_stride=True)
+        m = x.shape[0]
+        _check(self._lib.ferric_cuda_prepare_x(self.ctx._h, self._h, x.data_ptr(), m, x.shape[1],
+                                               x.stride(0) if m > 1 else 0), "prepare_x")
+        return m
+
+    def matmul_prepared(self, m: int, out: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
+        """Second half of ``matmul`` / ``try_matmul_swiglu`` on the activations last prepared on the context."""
+        n = self.rows() // 2 if swiglu else self.rows()
+        y = out if out is not None else torch.empty((m, n), dtype=torch.float32,
+                                                    device=torch.device("cuda", self.ctx.device))
+        ldy = y.stride(0) if (y.dim() == 2 and m > 1) else 0
+        _check(self._lib.ferric_cuda_matmul_q_prepared(self.ctx._h, self._h, m, y.data_ptr(), ldy, int(swiglu)),
+               "matmul_q_prepared")
+        return y
+
+    def matmul_host(self, x: np.ndarray) -> np.ndarray:
+        """The same product with host buffers (copies in, runs, copies out, synchronises)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        if x.ndim == 1:
+            x = x[None, :]
+        y = np.empty((x.shape[0], self.rows()), dtype=np.float32)
+        _check(self._lib.ferric_cuda_matmul_q_host(self.ctx._h, self._h, x.ctypes.data, x.shape[0], x.shape[1],
+                                                   y.ctypes.data), "matmul_q_host")
+        return y
+
+    def try_matmul_swiglu(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """``x.try_matmul_swiglu(&w)`` (crates/ferric-tensor/src/dtype.rs:949-959); None when not fusable."""
+        x = self._x2d(x)
+        m = x.shape[0]
+        y = out if out is not None else torch.empty((m, self.rows() // 2), dtype=torch.float32, device=x.device)
+        rc = self._lib.ferric_cuda_matmul_q_swiglu(self.ctx._h, self._h, x.data_ptr(), m, x.shape[1], y.data_ptr())
+        if rc == _lib.UNSUPPORTED:
+            return None
+        _check(rc, "matmul_q_swiglu")
+        return y
+
+    def gate_up_swiglu(self, x: torch.Tensor) -> torch.Tensor:
+        """``Proj::gate_up_swiglu`` (crates/ferric-llama/src/qwen3.rs:219-227): fused if possible."""
+        y = self.try_matmul_swiglu(x)
+        if y is not None:
+            return y
+        return self.ctx.swiglu(self.matmul(x), self.rows() // 2)
+
+    def dequant(self, bf16: bool = False) -> torch.Tensor:
+        """deq_raw of the loaded weight on the device: f32 [rows, cols], or bf16 bit patterns (int16 view)."""
+        dev = torch.device("cuda", self.ctx.device)
+        if bf16:
+            out = torch.empty((self.rows(), self.cols()), dtype=torch.bfloat16, device=dev)
+            _check(self._lib.ferric_cuda_dequant_bf16(self.ctx._h, self._h, out.data_ptr()), "dequant_bf16")
+        else:
+            out = torch.empty((self.rows(), self.cols()), dtype=torch.float32, device=dev)
+            _check(self._lib.ferric_cuda_dequant_f32(self.ctx._h, self._h, out.data_ptr()), "dequant_f32")
+        return out

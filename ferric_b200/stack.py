@@ -1,0 +1,192 @@
+"""The 27B-class decode layer stack: the callers of the packed-quant matmul path.
+
+One layer is the matmul sequence of ``Qwen35::forward_cached`` (crates/ferric-llama/src/qwen35.rs:953-1014,
+ffn :834-840): rmsnorm -> fused q|k|v projection -> [mixer] -> o projection -> add_rmsnorm ->
+fused gate|up + SwiGLU -> down projection -> add.  Attention / GDN and the KV cache are outside this
+backend's scope, so the mixer is a pass-through: the q slice of the qkv output feeds the o
+projection.  Everything else (shapes, formats, fusion of q|k|v and gate|up into one matrix as
+``qm_cat`` does, :380-402) is as the model runs it.
+
+Tensor parallelism (one process per GPU): q|k|v and gate|up are split by output rows, o and down by
+input columns on 256-weight super-block boundaries, and the f32 [B, hidden] partial sums of o and
+down are all-reduced (2 per layer).  K = 5120 is 20 super-blocks and n_ff = 17408 is 68, which do
+not divide by 8, so shards are uneven but aligned (3,3,3,3,2,2,2,2 and 9,9,9,9,8,8,8,8 blocks).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional
+
+import torch
+
+from . import synth
+from .ops import Context, QMatrix, GGML_Q4_K, GGML_Q6_K
+
+
+def split_blocks(total_blocks: int, world: int) -> List[int]:
+    """Blocks per rank: as even as block granularity allows, larger shards first."""
+    base, extra = divmod(total_blocks, world)
+    return [base + (1 if r < extra else 0) for r in range(world)]
+
+
+@dataclass(frozen=True)
+class TPPlan:
+    """Which slice of each layer matrix one rank owns."""
+    world: int
+    rank: int
+    hidden: int
+    n_ff: int
+    q_out: int
+    kv_out: int
+    q_row0: int
+    q_rows: int      # rows of Q this rank computes == its K slice of O
+    kv_row0: int
+    kv_rows: int     # rows of K (and of V)
+    ff_row0: int
+    ff_rows: int     # rows of gate (and of up) == its K slice of down
+
+    @staticmethod
+    def make(world: int, rank: int, hidden: int = 5120, n_ff: int = 17408, q_out: int = 5120,
+             kv_out: int = 1024) -> "TPPlan":
+        assert 0 <= rank < world
+        assert q_out % 256 == 0 and n_ff % 256 == 0 and kv_out % world == 0
+        qb = split_blocks(q_out // 256, world)
+        fb = split_blocks(n_ff // 256, world)
+        assert min(qb) > 0 and min(fb) > 0, "more ranks than 256-column blocks"
+        return TPPlan(world, rank, hidden, n_ff, q_out, kv_out,
+                      256 * sum(qb[:rank]), 256 * qb[rank],
+                      (kv_out // world) * rank, kv_out // world,
+                      256 * sum(fb[:rank]), 256 * fb[rank])
+
+    def weight_bytes_per_layer(self) -> int:
+        """Algorithmic (on-disk format) weight bytes this rank streams per layer."""
+        q4 = lambda r, c: r * c // 256 * 144
+        q6 = lambda r, c: r * c // 256 * 210
+        return (q4(self.q_rows + 2 * self.kv_rows, self.hidden) + q4(self.hidden, self.q_rows)
+                + q4(2 * self.ff_rows, self.hidden) + q6(self.hidden, self.ff_rows))
+
+
+AllReduce = Callable[[torch.Tensor], None]
+
+
+class Layer:
+    def __init__(self, wqkv: QMatrix, wo: QMatrix, wgu: QMatrix, wdown: QMatrix):
+        self.wqkv, self.wo, self.wgu, self.wdown = wqkv, wo, wgu, wdown
+
+    def close(self):
+        for w in (self.wqkv, self.wo, self.wgu, self.wdown):
+            w.close()
+
+
+class DecodeStack:
+    """``n_layers`` decoder layers' worth of packed-quant matmuls for ``batch`` tokens per step."""
+
+    def __init__(self, ctx: Context, plan: TPPlan, n_layers: int = 64, batch: int = 1, eps: float = 1e-6,
+                 all_reduce: Optional[AllReduce] = None):
+        self.ctx, self.plan, self.n_layers, self.batch, self.eps = ctx, plan, n_layers, batch, eps
+        self.all_reduce = all_reduce if plan.world > 1 else None
+        if plan.world > 1 and all_reduce is None:
+            raise ValueError("a tensor-parallel stack needs an all-reduce")
+        self.layers: List[Layer] = []
+        dev = torch.device("cuda", ctx.device)
+        p, B = plan, batch
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.h = torch.zeros((B, p.hidden), **f32)
+        self.xn = torch.empty((B, p.hidden), **f32)
+        self.qkv = torch.empty((B, p.q_rows + 2 * p.kv_rows), **f32)
+        self.o = torch.empty((B, p.hidden), **f32)
+        self.f = torch.empty((B, p.ff_rows), **f32)
+        self.d = torch.empty((B, p.hidden), **f32)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_step = 0
+
+    # -- weights ---------------------------------------------------------------------------
+    def add_layer(self, wqkv: QMatrix, wo: QMatrix, wgu: QMatrix, wdown: QMatrix) -> None:
+        p = self.plan
+        assert (wqkv.rows(), wqkv.cols()) == (p.q_rows + 2 * p.kv_rows, p.hidden)
+        assert (wo.rows(), wo.cols()) == (p.hidden, p.q_rows)
+        assert (wgu.rows(), wgu.cols()) == (2 * p.ff_rows, p.hidden)
+        assert (wdown.rows(), wdown.cols()) == (p.hidden, p.ff_rows)
+        self.layers.append(Layer(wqkv, wo, wgu, wdown))
+
+    def build_synthetic(self, seed: int = 4) -> None:
+        """Random-init weights of the named shapes and block distributions, generated on the device.
+
+        Layer l, matrix k, rank r draw from an independent stream; a rank's matrices have its shard's
+        shape (the values are synthetic, so nothing is gained by generating the whole tensor first)."""
+        p, dev = self.plan, torch.device("cuda", self.ctx.device)
+        for l in range(self.n_layers):
+            s = (seed * 1_000_003 + l) * 64 + p.rank * 4
+
+            def mk(ty, rows, cols, k):
+                raw = synth.matrix_on_device(ty, rows, cols, s + k, dev)
+                return QMatrix.from_device_bytes(self.ctx, raw, ty, rows, cols)
+
+            self.add_layer(mk(GGML_Q4_K, p.q_rows + 2 * p.kv_rows, p.hidden, 0), mk(GGML_Q4_K, p.hidden, p.q_rows, 1),
+                           mk(GGML_Q4_K, 2 * p.ff_rows, p.hidden, 2), mk(GGML_Q6_K, p.hidden, p.ff_rows, 3))
+        self.reserve()
+
+    def reserve(self) -> None:
+        need = 0
+        for L in self.layers[:1]:
+            need = max(w.scratch_bytes(self.batch) for w in (L.wqkv, L.wo, L.wgu, L.wdown))
+        self.ctx.reserve_scratch(need)
+
+    def weight_bytes_per_step(self) -> int:
+        return sum(w.nbytes() for L in self.layers for w in (L.wqkv, L.wo, L.wgu, L.wdown))
+
+    # -- one token step --------------------------------------------------------------------
+    def step(self) -> torch.Tensor:
+        """h <- stack(h) on the device, in place; returns h."""
+        c, p = self.ctx, self.plan
+        before = c.launches()
+        c.add_rmsnorm(self.h, None, None, self.eps, None, self.xn)
+        for L in self.layers:
+            L.wqkv.matmul(self.xn, out=self.qkv)
+            L.wo.matmul(self.qkv[:, :p.q_rows], out=self.o)          # mixer pass-through: q feeds o
+            if self.all_reduce:
+                self.all_reduce(self.o)
+            c.add_rmsnorm(self.h, self.o, None, self.eps, self.h, self.xn)
+            if L.wgu.try_matmul_swiglu(self.xn, out=self.f) is None:
+                raise RuntimeError("gate|up matrix is not fusable")
+            L.wdown.matmul(self.f, out=self.d)
+            if self.all_reduce:
+                self.all_reduce(self.d)
+            c.add_rmsnorm(self.h, self.d, None, self.eps, self.h, self.xn)
+        self.launches_per_step = c.launches() - before
+        return self.h
+
+    def capture(self, warmup: int = 2) -> None:
+        """Record one step into a CUDA graph (launch-bound loop: ~10 kernels per layer)."""
+        side = torch.cuda.Stream(device=self.ctx.device)
+        side.wait_stream(torch.cuda.current_stream(self.ctx.device))
+        with torch.cuda.stream(side):
+            self.ctx.use_torch_stream()
+            for _ in range(warmup):
+                self.step()
+        torch.cuda.current_stream(self.ctx.device).wait_stream(side)
+        torch.cuda.synchronize(self.ctx.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.ctx.use_torch_stream()
+            self.step()
+        self.ctx.use_torch_stream()
+        self.graph = g
+
+    def run(self) -> torch.Tensor:
+        if self.graph is not None:
+            self.graph.replay()
+            return self.h
+        return self.step()
+
+    def step_host(self, x_host: torch.Tensor, y_host: torch.Tensor) -> None:
+        """One step with HOST (pinned) input and result buffers: copy in, run, copy out, wait."""
+        self.h.copy_(x_host, non_blocking=True)
+        self.run()
+        y_host.copy_(self.h, non_blocking=True)
+        torch.cuda.current_stream(self.ctx.device).synchronize()
+
+    def close(self) -> None:
+        for L in self.layers:
+            L.close()
+        self.layers = []

@@ -1,0 +1,202 @@
+/*
+ * ferric_cuda.h -- C ABI of libferric_cuda: the sm_100a backend for Ferric's packed-quant
+ * (GGUF Q4_K / Q6_K / Q8_0) weight x activation product.
+ *
+ * Each entry point names the reference interface it stands in for (paths relative to the
+ * dcharlot-physicalai-bmi/ferric source tree).  Conventions follow the reference's own C ABI
+ * (crates/ferric-ffi/src/lib.rs:99-132, libferric.h): opaque handles, explicit *_free, nothing
+ * unwinds or aborts across the boundary.  Where the Rust side returns Result<_, String> or
+ * panics on a shape error, these functions return a status code and leave the message in
+ * ferric_cuda_last_error() (thread-local).
+ *
+ * Threading: one context per device per thread of control; calls on a context are ordered by
+ * its CUDA stream and are asynchronous like the reference's dispatch queue
+ * (crates/ferric-tensor/src/lib.rs:1712-1770) -- results are visible after ferric_cuda_ctx_sync
+ * or after the caller synchronises the stream.  A ferric_qmatrix is immutable once built and
+ * may be used by any context on the same device.
+ *
+ * There is no CPU fallback behind any of these functions: without a CUDA device they fail with
+ * FERRIC_ERR_CUDA.
+ */
+#ifndef FERRIC_CUDA_H
+#define FERRIC_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status ---------------------------------------------------------------------------- */
+#define FERRIC_OK 0
+#define FERRIC_ERR_INVALID_ARG 1      /* NULL handle / pointer, misaligned activation buffer */
+#define FERRIC_ERR_UNSUPPORTED_TYPE 2 /* Err("unsupported ggml type ..") / Err("QMatrix: no native matmul ..") */
+#define FERRIC_ERR_SHAPE 3            /* the reference's assert!s: cols % block, byte length, inner dim */
+#define FERRIC_ERR_CUDA 4
+#define FERRIC_ERR_OOM 5
+#define FERRIC_UNSUPPORTED 6          /* try_matmul_swiglu returning None */
+#define FERRIC_ERR_TIMEOUT 7          /* a bounded device-side wait ran out */
+
+/* ggml type ids carried by this path (crates/ferric-gguf/src/lib.rs:18-34). */
+#define FERRIC_GGML_F32 0u
+#define FERRIC_GGML_F16 1u
+#define FERRIC_GGML_Q8_0 8u
+#define FERRIC_GGML_Q4_K 12u
+#define FERRIC_GGML_Q6_K 14u
+#define FERRIC_GGML_BF16 30u
+
+typedef struct ferric_cuda_ctx ferric_cuda_ctx;
+typedef struct ferric_qmatrix ferric_qmatrix;
+
+/* Message of the last failing call on this thread ("" if none). */
+const char *ferric_cuda_last_error(void);
+
+/* ---- ferric-gguf: sizes and decoders ---------------------------------------------------- */
+
+/* type_size(ty, n) -> Result<usize, String>   crates/ferric-gguf/src/lib.rs:471-494
+ * (types 0, 1, 8, 12, 14, 30; any other id is FERRIC_ERR_UNSUPPORTED_TYPE). */
+int32_t ferric_gguf_type_size(uint32_t ggml_type, size_t n, size_t *out_bytes);
+
+/* deq_raw(raw, n, ty) -> Result<Vec<f32>, String>   crates/ferric-gguf/src/lib.rs:497-520
+ * raw and out are HOST buffers; the decode itself runs on the context's device (bit-exact
+ * with the reference's CPU decoders).  Types 8, 12, 14. */
+int32_t ferric_gguf_deq_raw(ferric_cuda_ctx *ctx, const uint8_t *raw, size_t raw_len, size_t n,
+                            uint32_t ggml_type, float *out);
+
+/* ---- ferric-core: the device context ---------------------------------------------------- */
+
+/* Context::new()   crates/ferric-core/src/lib.rs:109-151.  Owns a non-blocking stream. */
+int32_t ferric_cuda_ctx_create(int device, ferric_cuda_ctx **out);
+/* Same, but launches go to a caller-owned stream (cudaStream_t passed as void*; NULL = the
+ * legacy default stream), e.g. the stream of the framework hosting the activations. */
+int32_t ferric_cuda_ctx_create_on_stream(int device, void *cuda_stream, ferric_cuda_ctx **out);
+/* Redirect later launches to another stream of the same device. */
+int32_t ferric_cuda_ctx_set_stream(ferric_cuda_ctx *ctx, void *cuda_stream);
+void *ferric_cuda_ctx_stream(const ferric_cuda_ctx *ctx);
+/* Block until everything queued on the context's stream is done (the reference's
+ * flush + readback point, crates/ferric-tensor/src/lib.rs:1816-1836). */
+int32_t ferric_cuda_ctx_sync(ferric_cuda_ctx *ctx);
+void ferric_cuda_ctx_free(ferric_cuda_ctx *ctx);
+
+/* Capability record, the counterpart of Context's fields (crates/ferric-core/src/lib.rs:19-43). */
+typedef struct ferric_cuda_caps {
+    int32_t device;
+    int32_t sm_count;
+    int32_t cc_major, cc_minor;
+    uint64_t l2_bytes;
+    uint64_t total_mem_bytes;
+    uint64_t max_smem_per_block;
+} ferric_cuda_caps;
+int32_t ferric_cuda_ctx_caps(const ferric_cuda_ctx *ctx, ferric_cuda_caps *out);
+
+/* Grow the context's activation-fragment scratch to at least `bytes` now, so later calls do not
+ * allocate (needed before capturing calls into a CUDA graph). */
+int32_t ferric_cuda_ctx_reserve_scratch(ferric_cuda_ctx *ctx, size_t bytes);
+/* Launch counters since creation: kernels this library launched on the context. */
+uint64_t ferric_cuda_ctx_launches(const ferric_cuda_ctx *ctx);
+
+/* ---- ferric-tensor: QMatrix ------------------------------------------------------------- */
+
+/* QMatrix::block_bytes(ty) -> Option<(values, bytes)>   crates/ferric-tensor/src/dtype.rs:873-889
+ * rows 8 / 12 / 14.  FERRIC_UNSUPPORTED stands for None. */
+int32_t ferric_cuda_qmatrix_block_bytes(uint32_t ggml_type, size_t *values_per_block, size_t *bytes_per_block);
+
+/* QMatrix::from_bytes(ctx, bytes, ggml_type, rows, cols) -> Result<QMatrix, String>
+ * crates/ferric-tensor/src/dtype.rs:893-908 -> QShard::build :839-857 -> Q4_KWeights / Q6_KWeights /
+ * Q8_0Weights::from_bytes :1388-1420 / :1147-1166 / :1270-1286.
+ * `bytes` (HOST) are raw GGUF block bytes, row-major [rows = out, cols = in]; they are copied and
+ * re-packed into the device layout, the pointer is not kept.  Errors: cols not a multiple of the
+ * block size or len != rows * cols / block_values * block_bytes -> FERRIC_ERR_SHAPE; a type with
+ * no packed kernel -> FERRIC_ERR_UNSUPPORTED_TYPE. */
+int32_t ferric_cuda_qmatrix_from_bytes(ferric_cuda_ctx *ctx, const uint8_t *bytes, size_t len, uint32_t ggml_type,
+                                       size_t rows, size_t cols, ferric_qmatrix **out);
+
+/* The same constructor restricted to the sub-matrix rows [row0, row0 + nrows) x columns
+ * [col0, col0 + ncols) of the full tensor: a tensor-parallel shard (a row range for
+ * column-parallel Q/K/V/gate/up, a K range for row-parallel O/down) built straight from the
+ * whole tensor's bytes.  col0 and ncols must be block multiples.  Generalises the row sharding
+ * of QMatrix::from_bytes (crates/ferric-tensor/src/dtype.rs:899-905). */
+int32_t ferric_cuda_qmatrix_from_bytes_view(ferric_cuda_ctx *ctx, const uint8_t *bytes, size_t len,
+                                            uint32_t ggml_type, size_t rows, size_t cols, size_t row0, size_t nrows,
+                                            size_t col0, size_t ncols, ferric_qmatrix **out);
+
+/* As from_bytes, but `bytes_dev` already live in this device's memory (weights produced or
+ * staged on the device); they are read during the call's stream work and not kept. */
+int32_t ferric_cuda_qmatrix_from_device_bytes(ferric_cuda_ctx *ctx, const uint8_t *bytes_dev, size_t len,
+                                              uint32_t ggml_type, size_t rows, size_t cols, ferric_qmatrix **out);
+
+/* QMatrix::rows / cols / nbytes / n_shards   crates/ferric-tensor/src/dtype.rs:927-930.
+ * nbytes is the on-disk format size (rows * cols / 256 * 144 for Q4_K, :1421). */
+size_t ferric_cuda_qmatrix_rows(const ferric_qmatrix *qm);
+size_t ferric_cuda_qmatrix_cols(const ferric_qmatrix *qm);
+size_t ferric_cuda_qmatrix_nbytes(const ferric_qmatrix *qm);
+size_t ferric_cuda_qmatrix_n_shards(const ferric_qmatrix *qm);
+uint32_t ferric_cuda_qmatrix_ggml_type(const ferric_qmatrix *qm);
+void ferric_cuda_qmatrix_free(ferric_qmatrix *qm);
+
+/* Bytes of context scratch one matmul_q with m activation rows needs for this matrix. */
+size_t ferric_cuda_qmatrix_scratch_bytes(const ferric_qmatrix *qm, size_t m);
+
+/* Tensor::matmul_q(&QMatrix)   crates/ferric-tensor/src/dtype.rs:935-944 -> matmul_q4_k :1426-1473,
+ * matmul_q6_k :1172-1194, matmul_q8_0 :1292-1313.
+ * y[m, rows] = x[m, cols] . W^T, f32 in, f32 out, both DEVICE buffers, contiguous row-major,
+ * 16-byte aligned.  m >= 0.  `x_cols` is the activation's inner dimension; a mismatch with the
+ * matrix is the reference's "inner dim mismatch" panic -> FERRIC_ERR_SHAPE. */
+int32_t ferric_cuda_matmul_q(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t m,
+                             size_t x_cols, float *y_dev);
+
+/* The same product with explicit row strides (in floats) for x and y, so a column slice of a
+ * wider activation tensor feeds the matmul without a copy (the reference makes such inputs
+ * contiguous first, crates/ferric-tensor/src/dtype.rs:1427).  ldx must be a multiple of 4;
+ * 0 means "contiguous". */
+int32_t ferric_cuda_matmul_q_ld(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t m,
+                                size_t x_cols, size_t ldx, float *y_dev, size_t ldy);
+
+/* The two halves of matmul_q, for callers that feed one activation tensor to several matrices
+ * of the same format and inner dimension (fused q|k|v is one matrix in the reference,
+ * crates/ferric-llama/src/qwen35.rs:380-402; split projections are not, qwen3.rs:192-228):
+ * prepare_x converts x[m, x_cols] into the context's activation scratch once;
+ * matmul_q_prepared multiplies any such matrix with what is in the scratch (swiglu != 0 selects
+ * the fused gate/up epilogue, FERRIC_UNSUPPORTED as for matmul_q_swiglu).  Q8_0 has no prepared
+ * form (FERRIC_UNSUPPORTED). */
+int32_t ferric_cuda_prepare_x(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t m,
+                              size_t x_cols, size_t ldx);
+int32_t ferric_cuda_matmul_q_prepared(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, size_t m, float *y_dev,
+                                      size_t ldy, int32_t swiglu);
+
+/* Tensor::add_rmsnorm(other, weight, eps) -> (sum, norm)   crates/ferric-tensor/src/lib.rs:372-384
+ * (kernel :2057-2075), and Tensor::rmsnorm :346-353 when b_dev is NULL.  sum = a + b,
+ * norm = sum / sqrt(mean(sum^2) + eps) * weight; weight_dev NULL means all ones
+ * (rmsnorm_weightless, :340-344); sum_dev may be NULL or alias a_dev. */
+int32_t ferric_cuda_add_rmsnorm(ferric_cuda_ctx *ctx, const float *a_dev, const float *b_dev, const float *weight_dev,
+                                float eps, size_t rows, size_t d, float *sum_dev, float *norm_dev);
+
+/* The same product with HOST activation and result buffers: copies x in, runs, copies y out and
+ * returns when y is complete. */
+int32_t ferric_cuda_matmul_q_host(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_host, size_t m,
+                                  size_t x_cols, float *y_host);
+
+/* Tensor::try_matmul_swiglu(&QMatrix) -> Option<Tensor>   crates/ferric-tensor/src/dtype.rs:949-959
+ * (-> matmul_q4_k_swiglu :1551-1574, matmul_q6_k_swiglu :1802-1817).  The matrix is [gate rows |
+ * up rows] = [2*n_ff, cols]; y[m, n_ff] = silu(gate . x) * (up . x).  FERRIC_UNSUPPORTED (the
+ * reference's None) for Q8_0 or when n_ff is not a multiple of 16; the caller then runs
+ * matmul_q followed by ferric_cuda_swiglu, as Proj::gate_up_swiglu does
+ * (crates/ferric-llama/src/qwen3.rs:219-227). */
+int32_t ferric_cuda_matmul_q_swiglu(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t m,
+                                    size_t x_cols, float *y_dev);
+
+/* Tensor::swiglu(d)   crates/ferric-tensor/src/lib.rs:726-737: gu[t, 2d] -> out[t, d]. */
+int32_t ferric_cuda_swiglu(ferric_cuda_ctx *ctx, const float *gu_dev, size_t t, size_t d, float *out_dev);
+
+/* Device-side deq_raw of a loaded matrix: out[rows * cols] f32, bit-exact with
+ * crates/ferric-gguf/src/lib.rs:497-520 applied to the bytes the matrix was built from. */
+int32_t ferric_cuda_dequant_f32(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, float *out_dev);
+/* The same values rounded to bf16 with the reference's rule
+ * (crates/ferric-tensor/src/dtype.rs:4159-4163): out[rows * cols] uint16 bf16 bits. */
+int32_t ferric_cuda_dequant_bf16(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, uint16_t *out_dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FERRIC_CUDA_H */
