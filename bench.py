@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch kernels directly instead of replaying a CUDA graph")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-matrix table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     return ap.parse_args()
 
 
@@ -289,7 +290,7 @@ def run_ours(args):
         extras = per_matrix_table(torch, ctx, stack, QMatrix, B, peak)
 
     cpu = None
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.no_cpu:
         layer = CpuLayer(B)
         cores = layer.cores
         t_layer = min(layer.seconds() for _ in range(3))

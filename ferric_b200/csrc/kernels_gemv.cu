@@ -164,6 +164,28 @@ int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
 }
 
 // ------------------------------------------------------------------------------------------
+// Weight streaming: every warp owns a ring of kStages unit-sized slots in shared memory and keeps
+// kStages-1 units in flight with 16-byte asynchronous copies (L1 bypassed), so the bytes in
+// flight per SM (16 warps x 3 units x 2.3..3.4 KB) cover the HBM latency-bandwidth product
+// without holding the prefetched data in registers.
+// ------------------------------------------------------------------------------------------
+constexpr int kStagesQ4K = 4, kStagesQ6K = 3;
+constexpr int kSmemQ4K = 8 * kStagesQ4K * kQ4KUnit, kSmemQ6K = 8 * kStagesQ6K * kQ6KUnit;
+extern __shared__ __align__(16) uint8_t gemv_smem[];
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src)
+{
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ------------------------------------------------------------------------------------------
 // Shared tail: reduce the K-split partials of a CTA in a fixed order and store.
 // acc[nt][0..1] = row g (head column, tail column), acc[nt][2..3] = row g+8.
 // ------------------------------------------------------------------------------------------
@@ -234,14 +256,23 @@ __device__ __forceinline__ void pick_tile(int wk, int row_tiles, int ff_tiles, i
 struct Q4KUnit {
     uint4 hg, hh, q[4];
 };
-__device__ __forceinline__ void q4k_load(Q4KUnit& u, const uint8_t* units, size_t unit, int lane)
+// Stage copy: the unit is mirrored byte for byte into the warp's ring slot.  Every lane copies its
+// own four 16-byte quant chunks; lanes 0..15 also copy one header row each.
+__device__ __forceinline__ void q4k_issue(uint8_t* slot, const uint8_t* units, size_t unit, int lane)
 {
-    const uint4* p = reinterpret_cast<const uint4*>(units + unit * kQ4KUnit);
-    const int g = lane >> 2;
-    u.hg = ld_stream_u4(p + g);
-    u.hh = ld_stream_u4(p + 8 + g);
+    const uint8_t* src = units + unit * kQ4KUnit;
+    if (lane < 16) cp_async_16(slot + 16 * lane, src + 16 * lane);
 #pragma unroll
-    for (int s = 0; s < 4; s++) u.q[s] = ld_stream_u4(p + 16 + 32 * s + lane);
+    for (int s = 0; s < 4; s++) cp_async_16(slot + 256 + 512 * s + 16 * lane, src + 256 + 512 * s + 16 * lane);
+}
+__device__ __forceinline__ void q4k_read(Q4KUnit& u, const uint8_t* slot, int lane)
+{
+    const uint4* p = reinterpret_cast<const uint4*>(slot);
+    const int g = lane >> 2;
+    u.hg = p[g];
+    u.hh = p[8 + g];
+#pragma unroll
+    for (int s = 0; s < 4; s++) u.q[s] = p[16 + 32 * s + lane];
 }
 
 struct Q4KRow {
@@ -300,10 +331,22 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
         for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
 
     if (active && b0 < b1) {
-        Q4KUnit cur, nxt;
-        q4k_load(cur, units, (size_t)rt * nblk + b0, lane);
+        uint8_t* ring = gemv_smem + (size_t)warp * (kStagesQ4K * kQ4KUnit);
+        const size_t unit0 = (size_t)rt * nblk;
+#pragma unroll
+        for (int i = 0; i < kStagesQ4K - 1; i++) {
+            if (b0 + i < b1) q4k_issue(ring + i * kQ4KUnit, units, unit0 + b0 + i, lane);
+            cp_async_commit();
+        }
         for (int b = b0; b < b1; b++) {
-            if (b + 1 < b1) q4k_load(nxt, units, (size_t)rt * nblk + b + 1, lane);
+            const int pre = b + kStagesQ4K - 1;
+            if (pre < b1) q4k_issue(ring + ((pre - b0) % kStagesQ4K) * kQ4KUnit, units, unit0 + pre, lane);
+            cp_async_commit();
+            cp_async_wait<kStagesQ4K - 1>();
+            __syncwarp();
+            Q4KUnit cur;
+            q4k_read(cur, ring + ((b - b0) % kStagesQ4K) * kQ4KUnit, lane);
+            __syncwarp();  // every lane has its copy before a later stage copy may overwrite the slot
             Q4KRow rg, rh;
             q4k_row(cur.hg, t, rg);
             q4k_row(cur.hh, t, rh);
@@ -352,7 +395,6 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
                 acc[nt][2] = fmaf(fmh, cm[nt][2], fmaf(fh, cw[nt][2], acc[nt][2]));
                 acc[nt][3] = fmaf(fmh, cm[nt][3], fmaf(fh, cw[nt][3], acc[nt][3]));
             }
-            cur = nxt;
         }
     }
     reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active);
@@ -365,16 +407,28 @@ struct Q6KUnit {
     uint32_t dpair, scg, sch;
     uint4 ql[4], qh[2];
 };
-__device__ __forceinline__ void q6k_load(Q6KUnit& u, const uint8_t* units, size_t unit, int lane)
+// Stage copy of one 3360-byte unit: lanes copy their own six quant chunks; lanes 0..17 also copy
+// the 288 bytes of d pairs and scales.
+__device__ __forceinline__ void q6k_issue(uint8_t* slot, const uint8_t* units, size_t unit, int lane)
 {
-    const uint8_t* p = units + unit * kQ6KUnit;
-    u.dpair = ld_stream_u32(p + 4 * (lane >> 2));
-    u.scg = ld_stream_u32(p + kQ6KOffSc + 4 * lane);
-    u.sch = ld_stream_u32(p + kQ6KOffSc + 128 + 4 * lane);
+    const uint8_t* src = units + unit * kQ6KUnit;
+    if (lane < 18) cp_async_16(slot + 16 * lane, src + 16 * lane);
 #pragma unroll
-    for (int s = 0; s < 4; s++) u.ql[s] = ld_stream_u4(p + kQ6KOffQl + 512 * s + 16 * lane);
+    for (int s = 0; s < 4; s++)
+        cp_async_16(slot + kQ6KOffQl + 512 * s + 16 * lane, src + kQ6KOffQl + 512 * s + 16 * lane);
 #pragma unroll
-    for (int s = 0; s < 2; s++) u.qh[s] = ld_stream_u4(p + kQ6KOffQh + 512 * s + 16 * lane);
+    for (int s = 0; s < 2; s++)
+        cp_async_16(slot + kQ6KOffQh + 512 * s + 16 * lane, src + kQ6KOffQh + 512 * s + 16 * lane);
+}
+__device__ __forceinline__ void q6k_read(Q6KUnit& u, const uint8_t* p, int lane)
+{
+    u.dpair = *reinterpret_cast<const uint32_t*>(p + 4 * (lane >> 2));
+    u.scg = *reinterpret_cast<const uint32_t*>(p + kQ6KOffSc + 4 * lane);
+    u.sch = *reinterpret_cast<const uint32_t*>(p + kQ6KOffSc + 128 + 4 * lane);
+#pragma unroll
+    for (int s = 0; s < 4; s++) u.ql[s] = *reinterpret_cast<const uint4*>(p + kQ6KOffQl + 512 * s + 16 * lane);
+#pragma unroll
+    for (int s = 0; s < 2; s++) u.qh[s] = *reinterpret_cast<const uint4*>(p + kQ6KOffQh + 512 * s + 16 * lane);
 }
 
 struct Q6KRow {
@@ -420,10 +474,22 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
         for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
 
     if (active && b0 < b1) {
-        Q6KUnit cur, nxt;
-        q6k_load(cur, units, (size_t)rt * nblk + b0, lane);
+        uint8_t* ring = gemv_smem + (size_t)warp * (kStagesQ6K * kQ6KUnit);
+        const size_t unit0 = (size_t)rt * nblk;
+#pragma unroll
+        for (int i = 0; i < kStagesQ6K - 1; i++) {
+            if (b0 + i < b1) q6k_issue(ring + i * kQ6KUnit, units, unit0 + b0 + i, lane);
+            cp_async_commit();
+        }
         for (int b = b0; b < b1; b++) {
-            if (b + 1 < b1) q6k_load(nxt, units, (size_t)rt * nblk + b + 1, lane);
+            const int pre = b + kStagesQ6K - 1;
+            if (pre < b1) q6k_issue(ring + ((pre - b0) % kStagesQ6K) * kQ6KUnit, units, unit0 + pre, lane);
+            cp_async_commit();
+            cp_async_wait<kStagesQ6K - 1>();
+            __syncwarp();
+            Q6KUnit cur;
+            q6k_read(cur, ring + ((b - b0) % kStagesQ6K) * kQ6KUnit, lane);
+            __syncwarp();
             Q6KRow rg, rh;
             q6k_row(cur.scg, rg);
             q6k_row(cur.sch, rh);
@@ -484,7 +550,6 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
                 acc[nt][2] = fmaf(fhs, cs[nt][2], fmaf(fhw, cw[nt][2], acc[nt][2]));
                 acc[nt][3] = fmaf(fhs, cs[nt][3], fmaf(fhw, cw[nt][3], acc[nt][3]));
             }
-            cur = nxt;
         }
     }
     reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active);
@@ -515,12 +580,25 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
     const int ff_tiles = (int)(w.rows / 2 / 16);
     unsigned gx = EPI == kEpiStore ? (unsigned)((row_tiles + wr - 1) / wr) : (unsigned)((ff_tiles + wr / 2 - 1) / (wr / 2));
     dim3 grid(gx, passes);
-    if (ty == kGgmlQ4K)
-        gemv_q4k_kernel<NT, EPI><<<grid, 256, 0, st>>>(w.units, frag, y, (int)w.rows, (int)w.nblk, (int)m, ldy,
-                                                      row_tiles, wk, ff_tiles);
-    else
-        gemv_q6k_kernel<NT, EPI><<<grid, 256, 0, st>>>(w.units, frag, y, (int)w.rows, (int)w.nblk, (int)m, ldy,
-                                                      row_tiles, wk, ff_tiles);
+    // opt in to > 48 KB of dynamic shared memory once per kernel instantiation and device
+    static thread_local int attr_dev_q4 = -1, attr_dev_q6 = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (ty == kGgmlQ4K) {
+        if (attr_dev_q4 != dev) {
+            cudaFuncSetAttribute(gemv_q4k_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ4K);
+            attr_dev_q4 = dev;
+        }
+        gemv_q4k_kernel<NT, EPI><<<grid, 256, kSmemQ4K, st>>>(w.units, frag, y, (int)w.rows, (int)w.nblk, (int)m, ldy,
+                                                             row_tiles, wk, ff_tiles);
+    } else {
+        if (attr_dev_q6 != dev) {
+            cudaFuncSetAttribute(gemv_q6k_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ6K);
+            attr_dev_q6 = dev;
+        }
+        gemv_q6k_kernel<NT, EPI><<<grid, 256, kSmemQ6K, st>>>(w.units, frag, y, (int)w.rows, (int)w.nblk, (int)m, ldy,
+                                                             row_tiles, wk, ff_tiles);
+    }
 }
 
 int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const void* frag, size_t m, float* y,
