@@ -5,140 +5,159 @@
 // :1292-1313 + :3473-3529) and the fused gate/up + SwiGLU kernel (:949-959, :2372-2410).
 //
 // Shape of the computation (Q4_K; Q6_K is analogous):
-//   y[r] = sum_blk d[r,blk] * ( sum_k (sc*q)[r,k] * x[k] )  -  dmin[r,blk] * ( sum_sb m[r,sb] * Sx[sb] )
-// The inner sums are integer-valued weights (sc*q <= 945, exact in f16) times activations, and run
-// on the tensor cores as m16n8k16 f16 MMAs with f32 accumulation: 16 weight rows per warp, the 8
-// MMA columns carrying up to four activation rows, each split into an f16 head and a scaled f16
-// tail so that the product keeps f32-level accuracy.  The f32 factors d, dmin and the per-block
-// activation exponent are applied to the accumulators once per super-block.  Weights stream from
-// HBM exactly once, as fully coalesced 128-bit loads of the re-packed layout (layout.h).
+//   y[r] = sum_blk d[r,blk] * ( sum_sb sc[r,sb] * sum_{k in sb} q[r,k] x[k] )
+//                 - dmin[r,blk] * ( sum_sb m[r,sb] * sum_{k in sb} x[k] )
+// The innermost sums are integer weights times activations and run on the tensor cores as int8
+// MMAs (mma.sync m16n8k32 / m16n8k16, s32 accumulate): 16 weight rows per warp, the 8 MMA columns
+// carrying two activation rows as four signed 7-bit limbs each (layout.h), so the integer dot
+// products are exact and the result keeps f32-level accuracy.  Nibble extraction is one AND per
+// four weights; the 6-bit sub-block scales are applied to the s32 sub-block sums, and the f32
+// factors d, dmin and the activation exponent once per super-block.  Weights stream from HBM
+// exactly once, as fully coalesced 16-byte asynchronous copies of the re-packed layout.
 #include "common.cuh"
 #include "kernels.h"
 
 namespace ferric {
 
-__device__ __forceinline__ uint32_t hfma2_bits(uint32_t a, uint32_t b, uint32_t c)
+// D(16x8, s32) = A(16x32, u8, row) * B(32x8, s8, col) + C
+__device__ __forceinline__ void imma_16832_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint32_t b0, uint32_t b1, const int (&c)[4])
 {
-    uint32_t d;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
-__device__ __forceinline__ uint32_t hsub2_bits(uint32_t a, uint32_t b)
+// D(16x8, s32) = A(16x16, u8) * B(16x8, s8) + C
+__device__ __forceinline__ void imma_16816_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&c)[4])
 {
-    uint32_t d;
-    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+// D(16x8, s32) = A(16x16, s8) * B(16x8, s8) + C
+__device__ __forceinline__ void imma_16816_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&c)[4])
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 
-// Packed f16 constants (both halves equal).
-constexpr uint32_t kH2_1024 = 0x64006400u;   // 1024
-constexpr uint32_t kH2_1152 = 0x64806480u;   // 1152 = 1024 + 128
-constexpr uint32_t kH2_n1024 = 0xE400E400u;  // -1024
-constexpr uint32_t kH2_n64 = 0xD400D400u;    // -64
-constexpr uint32_t kH2_1_16 = 0x2C002C00u;   // 1/16
-constexpr uint32_t kH2_n72 = 0xD480D480u;    // -72
-constexpr uint32_t kH2_16 = 0x4C004C00u;     // 16
-constexpr uint32_t kH2_n18432 = 0xF480F480u; // -18432
-constexpr uint32_t kH2_4 = 0x44004400u;      // 4
-constexpr uint32_t kH2_n4608 = 0xEC80EC80u;  // -4608
-constexpr uint32_t kH2_1_4 = 0x34003400u;    // 1/4
-constexpr uint32_t kH2_n288 = 0xDC80DC80u;   // -288
-
 // ------------------------------------------------------------------------------------------
-// Activation preparation: x (f32) -> B fragments (layout.h, "activation fragments").
-// One warp per (batch tile of 4 rows, super-block).
+// Activation preparation: x (f32) -> int8 limb fragments (layout.h, "activation fragments").
+// One warp per (tile of 2 activation rows, super-block); 4 warps per CTA.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t split_f16(float v, bool tail)
-{
-    __half h = __float2half_rn(v);
-    if (tail) h = __float2half_rn((v - __half2float(h)) * kTailScale);
-    return (uint32_t)__half_as_ushort(h);
-}
+constexpr int kPrepWarps = 4;
 
 template <int TY>
-__global__ void __launch_bounds__(128) prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk,
-                                                   size_t ntiles, uint2* __restrict__ frag)
+__global__ void __launch_bounds__(32 * kPrepWarps)
+prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk, size_t ntiles, uint2* __restrict__ frag)
 {
-    constexpr int STEPS = TY == (int)kGgmlQ4K ? kQ4KSteps : kQ6KSteps;
-    const size_t wid = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
-    if (wid >= ntiles * nblk) return;
-    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, q = lane & 7;
-    const size_t tile = wid / nblk, blk = wid % nblk;
-    const size_t batch = tile * 4 + (size_t)(g >> 1);
-    const bool valid = batch < m, tail = (g & 1) != 0;
-    const float* xb = x + (valid ? batch : 0) * ldx + blk * 256;
+    // per warp: limb bytes [row 0..1][limb 0..3][256], 16-weight limb sums [row][limb][16], 2^(e-6) [row]
+    __shared__ __align__(16) int8_t s_limb[kPrepWarps][2][kLimbs][256];
+    __shared__ int s_sum[kPrepWarps][2][kLimbs][16];
+    __shared__ float s_up[kPrepWarps][2];
 
-    // pass 1: the 8 lanes that share a batch row scan 32 activations each
-    float amax = 0.0f, s0 = 0.0f, s1 = 0.0f;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t wid = blockIdx.x * (size_t)kPrepWarps + warp;
+    if (wid >= ntiles * nblk) return;
+    const size_t tile = wid / nblk, blk = wid % nblk;
+
+    // pass 1: lanes 0..15 scan activation row 2*tile, lanes 16..31 row 2*tile+1, 16 values each
+    const int prow = lane >> 4, q = lane & 15;
+    const size_t batch = tile * kRowsPerTile + (size_t)prow;
+    const bool valid = batch < m;
+    float v[16];
+    float amax = 0.0f;
     if (valid) {
-        const float4* p = reinterpret_cast<const float4*>(xb + 32 * q);
+        const float4* p = reinterpret_cast<const float4*>(x + batch * ldx + blk * 256 + 16 * q);
 #pragma unroll
-        for (int v = 0; v < 8; v++) {
-            float4 f = __ldg(p + v);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
-            float s = (f.x + f.y) + (f.z + f.w);
-            if (v < 4) s0 += s; else s1 += s;
+        for (int i = 0; i < 4; i++) {
+            float4 f = __ldg(p + i);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
         }
+#pragma unroll
+        for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(v[i]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = 0.0f;
     }
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     int e = 0;
     if (amax > 0.0f && amax < INFINITY) {
-        (void)frexpf(amax, &e);  // amax = f * 2^e with f in [0.5, 1)
-        if (e < -100) e = -100;
+        (void)frexpf(amax, &e);  // amax = f * 2^e, f in [0.5, 1)
+        e += 1;                  // 2^e >= 2 max|x|, so |x| 2^-e <= 1/2
+        if (e < -80) e = -80;
+        if (e > 120) e = 120;
     }
-    const float down = ldexpf(1.0f, -e), up = ldexpf(1.0f, e);
-    s0 *= down;
-    s1 *= down;
-    const int grp = lane & ~7;
-    const float up_t = __shfl_sync(0xffffffffu, up, 8 * t);  // the batch row this lane's accumulators hold
+    const float to_int = ldexpf(1.0f, 27 - e);  // X = rint(x * 2^(27-e)), |X| <= 2^27
+    int sum[kLimbs] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        int X = __float2int_rn(v[i] * to_int);
+        int a3 = ((X + 64) & 127) - 64; X = (X - a3) >> 7;
+        int a2 = ((X + 64) & 127) - 64; X = (X - a2) >> 7;
+        int a1 = ((X + 64) & 127) - 64; X = (X - a1) >> 7;
+        int a0 = X;
+        s_limb[warp][prow][0][16 * q + i] = (int8_t)a0;
+        s_limb[warp][prow][1][16 * q + i] = (int8_t)a1;
+        s_limb[warp][prow][2][16 * q + i] = (int8_t)a2;
+        s_limb[warp][prow][3][16 * q + i] = (int8_t)a3;
+        sum[0] += a0; sum[1] += a1; sum[2] += a2; sum[3] += a3;
+    }
+#pragma unroll
+    for (int j = 0; j < kLimbs; j++) s_sum[warp][prow][j][q] = sum[j];
+    if (q == 0) s_up[warp][prow] = ldexpf(1.0f, e - 6);
+    __syncwarp();
 
-    // pass 2: 16 weight steps
+    // pass 2: fragments.  B layout: lane = 4*g + t, column g = 4*(row in tile) + limb.
+    const int g = lane >> 2, t = lane & 3, brow = g >> 2, limb = g & 3;
+    const int8_t* lb = s_limb[warp][brow][limb];
+    const int* sm = s_sum[warp][brow][limb];
+    constexpr int STEPS = TY == (int)kGgmlQ4K ? kQ4KSteps : kQ6KSteps;
+    uint2* out = frag + frag_index(tile, nblk, blk, STEPS, 0, lane);
 #pragma unroll
-    for (int s = 0; s < 16; s++) {
-        const int base = TY == (int)kGgmlQ4K ? q4k_frag_weight(s, t, 0) : q6k_frag_weight(s, t, 0);
-        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (valid) f = __ldg(reinterpret_cast<const float4*>(xb + base));
+    for (int s = 0; s < 8; s++) {
         uint2 o;
-        o.x = split_f16(f.x * down, tail) | (split_f16(f.z * down, tail) << 16);
-        o.y = split_f16(f.y * down, tail) | (split_f16(f.w * down, tail) << 16);
-        frag[frag_index(tile, nblk, blk, STEPS, s, lane)] = o;
-    }
-    if (TY == (int)kGgmlQ4K) {
-        // sums over the 32-weight sub-blocks 2t, 2t+1 (lane q of the group holds sub-block q)
-        const float s32 = s0 + s1;
-        float a = __shfl_sync(0xffffffffu, s32, grp + 2 * t);
-        float b = __shfl_sync(0xffffffffu, s32, grp + 2 * t + 1);
-        uint2 o;
-        o.x = split_f16(a, tail) | (split_f16(b, tail) << 16);
-        o.y = __float_as_uint(up_t);
-        frag[frag_index(tile, nblk, blk, STEPS, 16, lane)] = o;
-    } else {
-        // sums over the 16-weight sub-blocks sb(t,k): lane q holds sub-blocks 2q (s0) and 2q+1 (s1)
-        float v[4];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const int src = grp + 4 * (t >> 1) + k;
-            float a = __shfl_sync(0xffffffffu, s0, src), b = __shfl_sync(0xffffffffu, s1, src);
-            v[k] = (t & 1) ? b : a;
+        if (TY == (int)kGgmlQ4K) {  // sub-block s: weights 32s + 8t + 0..7
+            o = *reinterpret_cast<const uint2*>(lb + 32 * s + 8 * t);
+        } else {                    // sub-blocks 2s, 2s+1: weights 16sb + 4t + 0..3
+            o.x = *reinterpret_cast<const uint32_t*>(lb + 32 * s + 4 * t);
+            o.y = *reinterpret_cast<const uint32_t*>(lb + 32 * s + 16 + 4 * t);
         }
-        uint2 o;
-        o.x = split_f16(v[0], tail) | (split_f16(v[1], tail) << 16);
-        o.y = split_f16(v[2], tail) | (split_f16(v[3], tail) << 16);
-        frag[frag_index(tile, nblk, blk, STEPS, 16, lane)] = o;
-        frag[frag_index(tile, nblk, blk, STEPS, 17, lane)] = make_uint2(__float_as_uint(up_t), 0u);
+        out[s * 32] = o;
     }
+    // limb sums per sub-block, S = 128*s1 + s0 with |s0| <= 64: k slot 4t + i <-> sub-block 4t + i
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int S;
+        if (TY == (int)kGgmlQ4K) {
+            const int sb = 4 * t + i;  // 8 sub-blocks of 32 weights; k slots 8..15 stay zero
+            S = sb < 8 ? sm[2 * sb] + sm[2 * sb + 1] : 0;
+        } else {
+            S = sm[4 * t + i];
+        }
+        const int s0 = ((S + 64) & 127) - 64, s1 = (S - s0) >> 7;
+        lo |= (uint32_t)(s0 & 0xff) << (8 * i);
+        hi |= (uint32_t)(s1 & 0xff) << (8 * i);
+    }
+    out[8 * 32] = make_uint2(lo, hi);
+    // the C layout gives this lane columns 2t, 2t+1 = activation row t>>1 of the tile
+    out[9 * 32] = make_uint2(__float_as_uint(s_up[warp][t >> 1]), 0u);
 }
 
 static int tiles_per_pass(size_t m)
 {
-    size_t ntiles = (m + 3) / 4;
+    size_t ntiles = (m + kRowsPerTile - 1) / kRowsPerTile;
     return ntiles >= 3 ? 4 : ntiles == 2 ? 2 : 1;
 }
 static size_t padded_tiles(size_t m)
 {
-    size_t nt = (size_t)tiles_per_pass(m), ntiles = (m + 3) / 4;
+    size_t nt = (size_t)tiles_per_pass(m), ntiles = (m + kRowsPerTile - 1) / kRowsPerTile;
     return (ntiles + nt - 1) / nt * nt;
 }
 
@@ -154,11 +173,11 @@ int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
 {
     size_t ntiles = padded_tiles(m), warps = ntiles * w.nblk;
     if (warps == 0) return kOk;
-    unsigned grid = (unsigned)((warps + 3) / 4);
+    unsigned grid = (unsigned)((warps + kPrepWarps - 1) / kPrepWarps);
     if (ty == kGgmlQ4K)
-        prep_kernel<(int)kGgmlQ4K><<<grid, 128, 0, st>>>(x, m, ldx, w.nblk, ntiles, reinterpret_cast<uint2*>(frag));
+        prep_kernel<(int)kGgmlQ4K><<<grid, 32 * kPrepWarps, 0, st>>>(x, m, ldx, w.nblk, ntiles, reinterpret_cast<uint2*>(frag));
     else
-        prep_kernel<(int)kGgmlQ6K><<<grid, 128, 0, st>>>(x, m, ldx, w.nblk, ntiles, reinterpret_cast<uint2*>(frag));
+        prep_kernel<(int)kGgmlQ6K><<<grid, 32 * kPrepWarps, 0, st>>>(x, m, ldx, w.nblk, ntiles, reinterpret_cast<uint2*>(frag));
     FERRIC_CUDA_TRY(cudaGetLastError());
     return kOk;
 }
@@ -166,8 +185,8 @@ int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
 // ------------------------------------------------------------------------------------------
 // Weight streaming: every warp owns a ring of kStages unit-sized slots in shared memory and keeps
 // kStages-1 units in flight with 16-byte asynchronous copies (L1 bypassed), so the bytes in
-// flight per SM (16 warps x 3 units x 2.3..3.4 KB) cover the HBM latency-bandwidth product
-// without holding the prefetched data in registers.
+// flight per SM cover the HBM latency-bandwidth product without holding prefetched data in
+// registers.
 // ------------------------------------------------------------------------------------------
 constexpr int kStagesQ4K = 4, kStagesQ6K = 3;
 constexpr int kSmemQ4K = 8 * kStagesQ4K * kQ4KUnit, kSmemQ6K = 8 * kStagesQ6K * kQ6KUnit;
@@ -186,12 +205,13 @@ __device__ __forceinline__ void cp_async_wait()
 }
 
 // ------------------------------------------------------------------------------------------
-// Shared tail: reduce the K-split partials of a CTA in a fixed order and store.
-// acc[nt][0..1] = row g (head column, tail column), acc[nt][2..3] = row g+8.
+// Shared tail: reduce the K-split partials of a CTA in a fixed order, recombine the limbs, store.
+// acc[nt][0..1] = row g, columns 2t, 2t+1 (activation row t>>1, limbs 2(t&1), 2(t&1)+1);
+// acc[nt][2..3] = row g+8.
 // ------------------------------------------------------------------------------------------
 template <int NT, int EPI>
 __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*red)[NT * 4][32], float* __restrict__ y,
-                                                 size_t ldy, int rows, int m, int tile0, int wk, int rt_or_pair,
+                                                 size_t ldy, int rows, int m, int tile0, int wk, int out_tile,
                                                  bool active)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -203,6 +223,9 @@ __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*re
     __syncthreads();
     if (kpart != 0 || !active) return;
     if (EPI == kEpiSwiglu && (wr & 1)) return;
+    // limb weights of this lane's two columns: 2^(-7*limb)
+    const float w0 = (t & 1) ? 6.103515625e-05f : 1.0f;          // 2^-14 : 2^0
+    const float w1 = (t & 1) ? 4.76837158203125e-07f : 0.0078125f; // 2^-21 : 2^-7
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         float v[4], u[4];
@@ -217,17 +240,22 @@ __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*re
                 u[i] = s2;
             }
         }
-        const int batch = (tile0 + nt) * 4 + t;
-        if (batch >= m) continue;
-        float lo = v[0] + v[1] * kTailUnscale, hi = v[2] + v[3] * kTailUnscale;
-        const int r0 = rt_or_pair * 16 + g;
+        float lo = v[0] * w0 + v[1] * w1, hi = v[2] * w0 + v[3] * w1;
+        lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+        hi += __shfl_xor_sync(0xffffffffu, hi, 1);
         if (EPI == kEpiSwiglu) {
-            float ulo = u[0] + u[1] * kTailUnscale, uhi = u[2] + u[3] * kTailUnscale;
+            float ulo = u[0] * w0 + u[1] * w1, uhi = u[2] * w0 + u[3] * w1;
+            ulo += __shfl_xor_sync(0xffffffffu, ulo, 1);
+            uhi += __shfl_xor_sync(0xffffffffu, uhi, 1);
             lo = silu_mul(lo, ulo);
             hi = silu_mul(hi, uhi);
         }
-        if (r0 < rows) y[(size_t)batch * ldy + r0] = lo;
-        if (r0 + 8 < rows) y[(size_t)batch * ldy + r0 + 8] = hi;
+        const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
+        const int r0 = out_tile * 16 + g;
+        if ((t & 1) == 0 && batch < m) {
+            if (r0 < rows) y[(size_t)batch * ldy + r0] = lo;
+            if (r0 + 8 < rows) y[(size_t)batch * ldy + r0 + 8] = hi;
+        }
     }
 }
 
@@ -275,43 +303,24 @@ __device__ __forceinline__ void q4k_read(Q4KUnit& u, const uint8_t* slot, int la
     for (int s = 0; s < 4; s++) u.q[s] = p[16 + 32 * s + lane];
 }
 
+// 6-bit scales / mins of one row's super-block as clean bytes: sc[0..3], sc[4..7], m[0..3], m[4..7]
+// (unpack rule: crates/ferric-gguf/src/lib.rs:795-804).
 struct Q4KRow {
-    uint32_t mult[2][2], nbias[2][2], mins;
+    uint32_t sc_lo, sc_hi, m_lo, m_hi;
     float d, dmin;
 };
-// 6-bit scales/mins of one row's super-block -> the f16 multipliers this lane needs
-// (unpack rule: crates/ferric-gguf/src/lib.rs:795-804).
-__device__ __forceinline__ void q4k_row(const uint4& h, int t, Q4KRow& r)
+__device__ __forceinline__ void q4k_row(const uint4& h, Q4KRow& r)
 {
     r.d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
     r.dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-    const uint32_t sc_lo = h.y & 0x3f3f3f3fu, m_lo = h.z & 0x3f3f3f3fu;
-    const uint32_t sc_hi = (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u);
-    const uint32_t m_hi = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
-    const int p = t >> 1;
-#pragma unroll
-    for (int X = 0; X < 2; X++) {
-        const uint32_t word = X ? sc_hi : sc_lo;
-#pragma unroll
-        for (int n = 0; n < 2; n++) {
-            const uint32_t byte = (uint32_t)(2 * p + n);
-            const uint32_t sc2 = bytes_to_h2(word, 0x4040u | (byte * 0x0101u));  // (sc, sc)
-            if (n == 0) {
-                r.mult[X][n] = sc2;                               // low nibble: (1024+q)*sc - 1024*sc
-                r.nbias[X][n] = hmul2_bits(sc2, kH2_n1024);
-            } else {
-                r.mult[X][n] = hmul2_bits(sc2, kH2_1_16);         // high nibble: (1024+16q)*sc/16 - 64*sc
-                r.nbias[X][n] = hmul2_bits(sc2, kH2_n64);
-            }
-        }
-    }
-    const uint32_t mword = (t < 2) ? m_lo : m_hi;
-    const uint32_t mb = (uint32_t)(2 * (t & 1));
-    r.mins = bytes_to_h2(mword, 0x4040u | mb | ((mb + 1) << 8));  // (m[2t], m[2t+1])
+    r.sc_lo = h.y & 0x3f3f3f3fu;
+    r.m_lo = h.z & 0x3f3f3f3fu;
+    r.sc_hi = (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u);
+    r.m_hi = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
 }
 
 template <int NT, int EPI>
-__global__ void __launch_bounds__(256, (NT <= 2) ? 2 : 1)
+__global__ void __launch_bounds__(256, 2)
 gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
                 int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles)
 {
@@ -323,6 +332,7 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
     const int kpart = warp % wk, per = (nblk + wk - 1) / wk;
     const int b0 = kpart * per, b1 = min(nblk, b0 + per);
     const int tile0 = blockIdx.y * NT;
+    const int zero[4] = {0, 0, 0, 0};
 
     float acc[NT][4];
 #pragma unroll
@@ -348,52 +358,58 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             q4k_read(cur, ring + ((b - b0) % kStagesQ4K) * kQ4KUnit, lane);
             __syncwarp();  // every lane has its copy before a later stage copy may overwrite the slot
             Q4KRow rg, rh;
-            q4k_row(cur.hg, t, rg);
-            q4k_row(cur.hh, t, rh);
+            q4k_row(cur.hg, rg);
+            q4k_row(cur.hh, rh);
             const uint2* fb[NT];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
                 fb[nt] = frag + ((size_t)(tile0 + nt) * nblk + b) * (kQ4KSteps * 32) + lane;
 
-            float cw[NT][4], cm[NT][4];
+            int ai[NT][4];  // sum_sb sc * (q . limb), per column
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) cw[nt][i] = cm[nt][i] = 0.0f;
+                for (int i = 0; i < 4; i++) ai[nt][i] = 0;
 
 #pragma unroll
-            for (int X = 0; X < 2; X++) {
-                const uint32_t wg[4] = {cur.q[X].x, cur.q[X].y, cur.q[X].z, cur.q[X].w};
-                const uint32_t wh[4] = {cur.q[2 + X].x, cur.q[2 + X].y, cur.q[2 + X].z, cur.q[2 + X].w};
+            for (int p = 0; p < 4; p++) {  // 32-byte group p: sub-blocks 2p (low nibbles), 2p+1 (high)
+                const uint4 qg = cur.q[p >> 1], qh = cur.q[2 + (p >> 1)];
+                const uint32_t w0 = (p & 1) ? qg.z : qg.x, w1 = (p & 1) ? qg.w : qg.y;
+                const uint32_t v0 = (p & 1) ? qh.z : qh.x, v1 = (p & 1) ? qh.w : qh.y;
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t a = wg[i], a8 = a >> 8, c = wh[i], c8 = c >> 8;
+                for (int n = 0; n < 2; n++) {
+                    const int s = 2 * p + n;
+                    const uint32_t a0 = (n ? (w0 >> 4) : w0) & 0x0f0f0f0fu, a2 = (n ? (w1 >> 4) : w1) & 0x0f0f0f0fu;
+                    const uint32_t a1 = (n ? (v0 >> 4) : v0) & 0x0f0f0f0fu, a3 = (n ? (v1 >> 4) : v1) & 0x0f0f0f0fu;
+                    const int scg = (int)__byte_perm(s < 4 ? rg.sc_lo : rg.sc_hi, 0u, 0x4440u | (uint32_t)(s & 3));
+                    const int sch = (int)__byte_perm(s < 4 ? rh.sc_lo : rh.sc_hi, 0u, 0x4440u | (uint32_t)(s & 3));
 #pragma unroll
-                    for (int n = 0; n < 2; n++) {
-                        const uint32_t mask = n ? 0x00f000f0u : 0x000f000fu;
-                        const uint32_t A0 = hfma2_bits((a & mask) | kH2_1024, rg.mult[X][n], rg.nbias[X][n]);
-                        const uint32_t A2 = hfma2_bits((a8 & mask) | kH2_1024, rg.mult[X][n], rg.nbias[X][n]);
-                        const uint32_t A1 = hfma2_bits((c & mask) | kH2_1024, rh.mult[X][n], rh.nbias[X][n]);
-                        const uint32_t A3 = hfma2_bits((c8 & mask) | kH2_1024, rh.mult[X][n], rh.nbias[X][n]);
-                        const int s = 8 * X + 2 * i + n;
-#pragma unroll
-                        for (int nt = 0; nt < NT; nt++) {
-                            const uint2 bf = __ldg(fb[nt] + s * 32);
-                            mma_16816(cw[nt], A0, A1, A2, A3, bf.x, bf.y);
-                        }
+                    for (int nt = 0; nt < NT; nt++) {
+                        const uint2 bf = __ldg(fb[nt] + s * 32);
+                        int c[4];
+                        imma_16832_u8s8(c, a0, a1, a2, a3, bf.x, bf.y, zero);
+                        ai[nt][0] += scg * c[0];
+                        ai[nt][1] += scg * c[1];
+                        ai[nt][2] += sch * c[2];
+                        ai[nt][3] += sch * c[3];
                     }
                 }
             }
+            // mins: sum_sb m[sb] * (limb sum of sub-block sb); k slot 4t+i <-> sub-block 4t+i (0..7)
+            const uint32_t mg = t == 0 ? rg.m_lo : t == 1 ? rg.m_hi : 0u;
+            const uint32_t mh = t == 0 ? rh.m_lo : t == 1 ? rh.m_hi : 0u;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const uint2 bf = __ldg(fb[nt] + 16 * 32);
-                mma_16816(cm[nt], rg.mins, rh.mins, 0u, 0u, bf.x, 0u);
-                const float up = __uint_as_float(bf.y);
+                const uint2 bs = __ldg(fb[nt] + 8 * 32);
+                int c0[4], c1[4];
+                imma_16816_u8s8(c0, mg, mh, bs.x, zero);
+                imma_16816_u8s8(c1, mg, mh, bs.y, zero);
+                const float up = __uint_as_float(__ldg(fb[nt] + 9 * 32).x);
                 const float fg = rg.d * up, fmg = -rg.dmin * up, fh = rh.d * up, fmh = -rh.dmin * up;
-                acc[nt][0] = fmaf(fmg, cm[nt][0], fmaf(fg, cw[nt][0], acc[nt][0]));
-                acc[nt][1] = fmaf(fmg, cm[nt][1], fmaf(fg, cw[nt][1], acc[nt][1]));
-                acc[nt][2] = fmaf(fmh, cm[nt][2], fmaf(fh, cw[nt][2], acc[nt][2]));
-                acc[nt][3] = fmaf(fmh, cm[nt][3], fmaf(fh, cw[nt][3], acc[nt][3]));
+                acc[nt][0] = fmaf(fmg, (float)(c0[0] + 128 * c1[0]), fmaf(fg, (float)ai[nt][0], acc[nt][0]));
+                acc[nt][1] = fmaf(fmg, (float)(c0[1] + 128 * c1[1]), fmaf(fg, (float)ai[nt][1], acc[nt][1]));
+                acc[nt][2] = fmaf(fmh, (float)(c0[2] + 128 * c1[2]), fmaf(fh, (float)ai[nt][2], acc[nt][2]));
+                acc[nt][3] = fmaf(fmh, (float)(c0[3] + 128 * c1[3]), fmaf(fh, (float)ai[nt][3], acc[nt][3]));
             }
         }
     }
@@ -404,8 +420,8 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 // Q6_K
 // ------------------------------------------------------------------------------------------
 struct Q6KUnit {
-    uint32_t dpair, scg, sch;
-    uint4 ql[4], qh[2];
+    uint32_t dpair;
+    uint4 scg, sch, ql[4], qh[2];
 };
 // Stage copy of one 3360-byte unit: lanes copy their own six quant chunks; lanes 0..17 also copy
 // the 288 bytes of d pairs and scales.
@@ -422,50 +438,37 @@ __device__ __forceinline__ void q6k_issue(uint8_t* slot, const uint8_t* units, s
 }
 __device__ __forceinline__ void q6k_read(Q6KUnit& u, const uint8_t* p, int lane)
 {
-    u.dpair = *reinterpret_cast<const uint32_t*>(p + 4 * (lane >> 2));
-    u.scg = *reinterpret_cast<const uint32_t*>(p + kQ6KOffSc + 4 * lane);
-    u.sch = *reinterpret_cast<const uint32_t*>(p + kQ6KOffSc + 128 + 4 * lane);
+    const int g = lane >> 2;
+    u.dpair = *reinterpret_cast<const uint32_t*>(p + 4 * g);
+    u.scg = *reinterpret_cast<const uint4*>(p + kQ6KOffSc + 16 * g);
+    u.sch = *reinterpret_cast<const uint4*>(p + kQ6KOffSc + 16 * (g + 8));
 #pragma unroll
     for (int s = 0; s < 4; s++) u.ql[s] = *reinterpret_cast<const uint4*>(p + kQ6KOffQl + 512 * s + 16 * lane);
 #pragma unroll
     for (int s = 0; s < 2; s++) u.qh[s] = *reinterpret_cast<const uint4*>(p + kQ6KOffQh + 512 * s + 16 * lane);
 }
-
-struct Q6KRow {
-    uint32_t lo[4], hi[4], s01, s23;
-};
-// The lane's four int8 sub-block scales -> f16 multipliers.  Low-nibble weights arrive as
-// q*2^-24 (k = 0,1) or 16q*2^-24 (k = 2,3); high-bit pairs as h*4^k*2^-24, and must end up as
-// 16*h*sc*2^-24 to line up with the low part.  All products are exact in f16.
-__device__ __forceinline__ void q6k_row(uint32_t scw, Q6KRow& r)
+__device__ __forceinline__ uint32_t u4_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+// sign-extended byte `i` (0..15) of a 16-byte scale row
+__device__ __forceinline__ int sc_byte(const uint4& v, int i)
 {
-    const uint32_t u = scw ^ 0x80808080u;  // bytes = sc + 128
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-        const uint32_t v = __byte_perm(u, 0x64646464u, 0x4040u | ((uint32_t)k * 0x0101u));  // 1152 + sc, twice
-        const uint32_t sc2 = hsub2_bits(v, kH2_1152);
-        r.lo[k] = (k < 2) ? sc2 : hfma2_bits(v, kH2_1_16, kH2_n72);
-        r.hi[k] = k == 0 ? hfma2_bits(v, kH2_16, kH2_n18432)
-                : k == 1 ? hfma2_bits(v, kH2_4, kH2_n4608)
-                : k == 2 ? sc2 : hfma2_bits(v, kH2_1_4, kH2_n288);
-    }
-    r.s01 = hsub2_bits(__byte_perm(u, 0x64646464u, 0x4140u), kH2_1152);
-    r.s23 = hsub2_bits(__byte_perm(u, 0x64646464u, 0x4342u), kH2_1152);
+    const uint32_t b = (uint32_t)(i & 3);
+    return (int)__byte_perm(u4_word(v, i >> 2), 0u, b | ((8u + b) << 4) | ((8u + b) << 8) | ((8u + b) << 12));
 }
 
 template <int NT, int EPI>
-__global__ void __launch_bounds__(256, (NT <= 2) ? 2 : 1)
+__global__ void __launch_bounds__(256, 2)
 gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
                 int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles)
 {
     __shared__ float red[8][NT * 4][32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, t = lane & 3;
     int rt, out_tile;
     bool active;
     pick_tile<EPI>(wk, row_tiles, ff_tiles, rt, out_tile, active);
     const int kpart = warp % wk, per = (nblk + wk - 1) / wk;
     const int b0 = kpart * per, b1 = min(nblk, b0 + per);
     const int tile0 = blockIdx.y * NT;
+    const int zero[4] = {0, 0, 0, 0};
 
     float acc[NT][4];
 #pragma unroll
@@ -490,65 +493,65 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             Q6KUnit cur;
             q6k_read(cur, ring + ((b - b0) % kStagesQ6K) * kQ6KUnit, lane);
             __syncwarp();
-            Q6KRow rg, rh;
-            q6k_row(cur.scg, rg);
-            q6k_row(cur.sch, rh);
             const uint2* fb[NT];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
                 fb[nt] = frag + ((size_t)(tile0 + nt) * nblk + b) * (kQ6KSteps * 32) + lane;
 
-            float cw[NT][4], cs[NT][4];
+            int ai[NT][4];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) cw[nt][i] = cs[nt][i] = 0.0f;
+                for (int i = 0; i < 4; i++) ai[nt][i] = 0;
 
-            const uint32_t qhg[4] = {cur.qh[0].x, cur.qh[0].y, cur.qh[0].z, cur.qh[0].w};
-            const uint32_t qhh[4] = {cur.qh[1].x, cur.qh[1].y, cur.qh[1].z, cur.qh[1].w};
 #pragma unroll
-            for (int wi = 0; wi < 4; wi++) {
-                const uint32_t hg = qhg[wi], hg8 = hg >> 8, hh = qhh[wi], hh8 = hh >> 8;
+            for (int h = 0; h < 2; h++) {
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    const uint32_t lg = c ? (wi == 0 ? cur.ql[1].x : wi == 1 ? cur.ql[1].y : wi == 2 ? cur.ql[1].z : cur.ql[1].w)
-                                          : (wi == 0 ? cur.ql[0].x : wi == 1 ? cur.ql[0].y : wi == 2 ? cur.ql[0].z : cur.ql[0].w);
-                    const uint32_t lh = c ? (wi == 0 ? cur.ql[3].x : wi == 1 ? cur.ql[3].y : wi == 2 ? cur.ql[3].z : cur.ql[3].w)
-                                          : (wi == 0 ? cur.ql[2].x : wi == 1 ? cur.ql[2].y : wi == 2 ? cur.ql[2].z : cur.ql[2].w);
-                    const uint32_t lg8 = lg >> 8, lh8 = lh >> 8;
+                for (int k = 0; k < 4; k++) {
+                    // double step 4h + k: sub-blocks sb = 8h + 2k + is, is = 0 (.x) and 1 (.y)
+                    uint2 bf[NT];
 #pragma unroll
-                    for (int n = 0; n < 2; n++) {
-                        const int k = c + 2 * n, s = 4 * wi + k;
-                        const uint32_t m4 = n ? 0x00f000f0u : 0x000f000fu;
-                        const uint32_t m2 = 0x00030003u << (2 * k);
-                        // low 4 bits
-                        const uint32_t L0 = hmul2_bits(lg & m4, rg.lo[k]), L2 = hmul2_bits(lg8 & m4, rg.lo[k]);
-                        const uint32_t L1 = hmul2_bits(lh & m4, rh.lo[k]), L3 = hmul2_bits(lh8 & m4, rh.lo[k]);
-                        // high 2 bits
-                        const uint32_t H0 = hmul2_bits(hg & m2, rg.hi[k]), H2 = hmul2_bits(hg8 & m2, rg.hi[k]);
-                        const uint32_t H1 = hmul2_bits(hh & m2, rh.hi[k]), H3 = hmul2_bits(hh8 & m2, rh.hi[k]);
+                    for (int nt = 0; nt < NT; nt++) bf[nt] = __ldg(fb[nt] + (4 * h + k) * 32);
+#pragma unroll
+                    for (int is = 0; is < 2; is++) {
+                        const int wi = 2 * h + is, sb = 8 * h + 2 * k + is;
+                        // 6-bit weights of rows g and g+8: low nibble source word, high-bit source word
+                        const uint32_t lg = u4_word(cur.ql[k & 1], wi), lh = u4_word(cur.ql[2 + (k & 1)], wi);
+                        const uint32_t hg = u4_word(cur.qh[0], wi), hh = u4_word(cur.qh[1], wi);
+                        const uint32_t lo_g = ((k & 2) ? (lg >> 4) : lg) & 0x0f0f0f0fu;
+                        const uint32_t lo_h = ((k & 2) ? (lh >> 4) : lh) & 0x0f0f0f0fu;
+                        const uint32_t hi_g = (k == 0 ? (hg << 4) : k == 1 ? (hg << 2) : k == 2 ? hg : (hg >> 2)) & 0x30303030u;
+                        const uint32_t hi_h = (k == 0 ? (hh << 4) : k == 1 ? (hh << 2) : k == 2 ? hh : (hh >> 2)) & 0x30303030u;
+                        const uint32_t a0 = lo_g | hi_g, a1 = lo_h | hi_h;
+                        const int scg = sc_byte(cur.scg, sb), sch = sc_byte(cur.sch, sb);
 #pragma unroll
                         for (int nt = 0; nt < NT; nt++) {
-                            const uint2 bf = __ldg(fb[nt] + s * 32);
-                            mma_16816(cw[nt], L0, L1, L2, L3, bf.x, bf.y);
-                            mma_16816(cw[nt], H0, H1, H2, H3, bf.x, bf.y);
+                            int c[4];
+                            imma_16816_u8s8(c, a0, a1, is ? bf[nt].y : bf[nt].x, zero);
+                            ai[nt][0] += scg * c[0];
+                            ai[nt][1] += scg * c[1];
+                            ai[nt][2] += sch * c[2];
+                            ai[nt][3] += sch * c[3];
                         }
                     }
                 }
             }
+            // the -32 offset: sum_sb sc[sb] * (limb sum of sub-block sb); k slot 4t+i <-> sub-block 4t+i
+            const uint32_t sg = u4_word(cur.scg, t), sh = u4_word(cur.sch, t);
             const float dg = __half2float(__ushort_as_half((unsigned short)(cur.dpair & 0xffffu)));
             const float dh = __half2float(__ushort_as_half((unsigned short)(cur.dpair >> 16)));
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const uint2 bs = __ldg(fb[nt] + 16 * 32);
-                mma_16816(cs[nt], rg.s01, rh.s01, rg.s23, rh.s23, bs.x, bs.y);
-                const float up = __uint_as_float(__ldg(fb[nt] + 17 * 32).x);
+                const uint2 bs = __ldg(fb[nt] + 8 * 32);
+                int c0[4], c1[4];
+                imma_16816_s8s8(c0, sg, sh, bs.x, zero);
+                imma_16816_s8s8(c1, sg, sh, bs.y, zero);
+                const float up = __uint_as_float(__ldg(fb[nt] + 9 * 32).x);
                 const float fg = dg * up, fh = dh * up;
-                const float fgw = fg * 16777216.0f, fgs = fg * -32.0f, fhw = fh * 16777216.0f, fhs = fh * -32.0f;
-                acc[nt][0] = fmaf(fgs, cs[nt][0], fmaf(fgw, cw[nt][0], acc[nt][0]));
-                acc[nt][1] = fmaf(fgs, cs[nt][1], fmaf(fgw, cw[nt][1], acc[nt][1]));
-                acc[nt][2] = fmaf(fhs, cs[nt][2], fmaf(fhw, cw[nt][2], acc[nt][2]));
-                acc[nt][3] = fmaf(fhs, cs[nt][3], fmaf(fhw, cw[nt][3], acc[nt][3]));
+                acc[nt][0] = fmaf(fg, (float)(ai[nt][0] - 32 * (c0[0] + 128 * c1[0])), acc[nt][0]);
+                acc[nt][1] = fmaf(fg, (float)(ai[nt][1] - 32 * (c0[1] + 128 * c1[1])), acc[nt][1]);
+                acc[nt][2] = fmaf(fh, (float)(ai[nt][2] - 32 * (c0[2] + 128 * c1[2])), acc[nt][2]);
+                acc[nt][3] = fmaf(fh, (float)(ai[nt][3] - 32 * (c0[3] + 128 * c1[3])), acc[nt][3]);
             }
         }
     }

@@ -17,15 +17,16 @@ namespace ferric {
 __global__ void repack_q4k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, size_t nrows,
                                   size_t nblk, size_t src_nblk, size_t row0, size_t blk0, bool aligned)
 {
-    size_t total = nrows * nblk * 9;
+    // 18 pieces of 8 bytes per block: the layout keeps every aligned 8-byte run contiguous
+    size_t total = nrows * nblk * 18;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        size_t c = i % 9, rb = i / 9, b = rb % nblk, r = rb / nblk;
-        const uint8_t* s = src + ((row0 + r) * src_nblk + blk0 + b) * kQ4KBlock + 16 * c;
-        uint8_t* d = dst + ((r >> 4) * nblk + b) * kQ4KUnit + q4k_unit_offset((int)(r & 15), (int)(16 * c));
+        size_t c = i % 18, rb = i / 18, b = rb % nblk, r = rb / nblk;
+        const uint8_t* s = src + ((row0 + r) * src_nblk + blk0 + b) * kQ4KBlock + 8 * c;
+        uint8_t* d = dst + ((r >> 4) * nblk + b) * kQ4KUnit + q4k_unit_offset((int)(r & 15), (int)(8 * c));
         if (aligned) {
-            *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(s);
+            *reinterpret_cast<uint2*>(d) = *reinterpret_cast<const uint2*>(s);
         } else {
-            for (int j = 0; j < 16; j++) d[j] = s[j];
+            for (int j = 0; j < 8; j++) d[j] = s[j];
         }
     }
 }
@@ -33,21 +34,19 @@ __global__ void repack_q4k_kernel(const uint8_t* __restrict__ src, uint8_t* __re
 __global__ void repack_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, size_t nrows,
                                   size_t nblk, size_t src_nblk, size_t row0, size_t blk0)
 {
-    size_t total = nrows * nblk * 13;
+    // 48 four-byte pieces of ql / qh (contiguous in both layouts) + one piece for scales and d
+    size_t total = nrows * nblk * 49;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        size_t p = i % 13, rb = i / 13, b = rb % nblk, r = rb / nblk;
+        size_t p = i % 49, rb = i / 49, b = rb % nblk, r = rb / nblk;
         const uint8_t* s = src + ((row0 + r) * src_nblk + blk0 + b) * kQ6KBlock;
         uint8_t* u = dst + ((r >> 4) * nblk + b) * kQ6KUnit;
         int rr = (int)(r & 15);
-        if (p < 12) {  // one 16-byte run of ql (p < 8) or qh: contiguous in both layouts
-            int byte0 = (int)(16 * p);
-            uint8_t* d = u + q6k_unit_offset(rr, byte0);
-            uint32_t w[4];
-            for (int k = 0; k < 4; k++)
-                w[k] = (uint32_t)s[byte0 + 4 * k] | ((uint32_t)s[byte0 + 4 * k + 1] << 8) |
-                       ((uint32_t)s[byte0 + 4 * k + 2] << 16) | ((uint32_t)s[byte0 + 4 * k + 3] << 24);
-            *reinterpret_cast<uint4*>(d) = make_uint4(w[0], w[1], w[2], w[3]);
-        } else {  // the 16 scales and the f16 d scatter byte by byte
+        if (p < 48) {
+            int byte0 = (int)(4 * p);
+            uint32_t w = (uint32_t)s[byte0] | ((uint32_t)s[byte0 + 1] << 8) | ((uint32_t)s[byte0 + 2] << 16) |
+                         ((uint32_t)s[byte0 + 3] << 24);
+            *reinterpret_cast<uint32_t*>(u + q6k_unit_offset(rr, byte0)) = w;
+        } else {
             for (int byte = 192; byte < 210; byte++) u[q6k_unit_offset(rr, byte)] = s[byte];
         }
     }
@@ -86,11 +85,11 @@ int32_t launch_repack(cudaStream_t st, uint32_t ty, const uint8_t* src, DeviceWe
     size_t nrows = w.rows, nblk = w.nblk;
     if (nrows == 0 || nblk == 0) return kOk;
     if (ty == kGgmlQ4K) {
-        bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
-        repack_q4k_kernel<<<grid_for(nrows * nblk * 9, 256), 256, 0, st>>>(src, w.units, nrows, nblk, src_nblk,
+        bool aligned = (reinterpret_cast<uintptr_t>(src) & 7) == 0;
+        repack_q4k_kernel<<<grid_for(nrows * nblk * 18, 256), 256, 0, st>>>(src, w.units, nrows, nblk, src_nblk,
                                                                             row0, blk0, aligned);
     } else if (ty == kGgmlQ6K) {
-        repack_q6k_kernel<<<grid_for(nrows * nblk * 13, 256), 256, 0, st>>>(src, w.units, nrows, nblk, src_nblk,
+        repack_q6k_kernel<<<grid_for(nrows * nblk * 49, 256), 256, 0, st>>>(src, w.units, nrows, nblk, src_nblk,
                                                                              row0, blk0);
     } else {
         repack_q8_0_kernel<<<grid_for(nrows * nblk, 256), 256, 0, st>>>(src, w.q8_qs, w.q8_d, nrows, nblk,

@@ -5,10 +5,10 @@
 extern "C" {
 uint32_t shim_q4k_unit_offset(int r, int byte) { return ferric::q4k_unit_offset(r, byte); }
 int shim_q4k_frag_weight(int s, int t, int j) { return ferric::q4k_frag_weight(s, t, j); }
-int shim_q4k_frag_subblock(int X, int t, int n) { return ferric::q4k_frag_subblock(X, t, n); }
+
 uint32_t shim_q6k_unit_offset(int r, int byte) { return ferric::q6k_unit_offset(r, byte); }
 int shim_q6k_frag_weight(int s, int t, int j) { return ferric::q6k_frag_weight(s, t, j); }
-int shim_q6k_frag_subblock(int t, int k) { return ferric::q6k_frag_subblock(t, k); }
+
 int shim_q4k_unit_bytes() { return ferric::kQ4KUnit; }
 int shim_q6k_unit_bytes() { return ferric::kQ6KUnit; }
 }
