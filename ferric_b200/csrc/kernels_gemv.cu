@@ -204,6 +204,14 @@ __device__ __forceinline__ void cp_async_wait()
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// Pull the activation fragments of one (tile, super-block) -- STEPS x 256 bytes -- into L1 ahead of
+// use: lanes 0..(STEPS*2-1) touch one 128-byte line each.
+template <int STEPS>
+__device__ __forceinline__ void prefetch_frags(const uint2* frag_unit, int lane)
+{
+    if (lane < STEPS * 2) asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(frag_unit) + 128 * lane));
+}
+
 // ------------------------------------------------------------------------------------------
 // Shared tail: reduce the K-split partials of a CTA in a fixed order, recombine the limbs, store.
 // acc[nt][0..1] = row g, columns 2t, 2t+1 (activation row t>>1, limbs 2(t&1), 2(t&1)+1);
@@ -345,12 +353,22 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
         const size_t unit0 = (size_t)rt * nblk;
 #pragma unroll
         for (int i = 0; i < kStagesQ4K - 1; i++) {
-            if (b0 + i < b1) q4k_issue(ring + i * kQ4KUnit, units, unit0 + b0 + i, lane);
+            if (b0 + i < b1) {
+                q4k_issue(ring + i * kQ4KUnit, units, unit0 + b0 + i, lane);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+                    prefetch_frags<kQ4KSteps>(frag + ((size_t)(tile0 + nt) * nblk + b0 + i) * (kQ4KSteps * 32), lane);
+            }
             cp_async_commit();
         }
         for (int b = b0; b < b1; b++) {
             const int pre = b + kStagesQ4K - 1;
-            if (pre < b1) q4k_issue(ring + ((pre - b0) % kStagesQ4K) * kQ4KUnit, units, unit0 + pre, lane);
+            if (pre < b1) {
+                q4k_issue(ring + ((pre - b0) % kStagesQ4K) * kQ4KUnit, units, unit0 + pre, lane);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+                    prefetch_frags<kQ4KSteps>(frag + ((size_t)(tile0 + nt) * nblk + pre) * (kQ4KSteps * 32), lane);
+            }
             cp_async_commit();
             cp_async_wait<kStagesQ4K - 1>();
             __syncwarp();
@@ -448,11 +466,15 @@ __device__ __forceinline__ void q6k_read(Q6KUnit& u, const uint8_t* p, int lane)
     for (int s = 0; s < 2; s++) u.qh[s] = *reinterpret_cast<const uint4*>(p + kQ6KOffQh + 512 * s + 16 * lane);
 }
 __device__ __forceinline__ uint32_t u4_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
-// sign-extended byte `i` (0..15) of a 16-byte scale row
+// sign-extended byte `i` (0..15) of a 16-byte scale row: PRMT copies the byte and replicates its
+// sign bit into the three upper bytes (selector nibble 8|b)
 __device__ __forceinline__ int sc_byte(const uint4& v, int i)
 {
     const uint32_t b = (uint32_t)(i & 3);
-    return (int)__byte_perm(u4_word(v, i >> 2), 0u, b | ((8u + b) << 4) | ((8u + b) << 8) | ((8u + b) << 12));
+    const uint32_t sel = b | ((8u | b) << 4) | ((8u | b) << 8) | ((8u | b) << 12);
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(u4_word(v, i >> 2)), "r"(0u), "r"(sel));
+    return (int)d;
 }
 
 template <int NT, int EPI>
@@ -481,12 +503,22 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
         const size_t unit0 = (size_t)rt * nblk;
 #pragma unroll
         for (int i = 0; i < kStagesQ6K - 1; i++) {
-            if (b0 + i < b1) q6k_issue(ring + i * kQ6KUnit, units, unit0 + b0 + i, lane);
+            if (b0 + i < b1) {
+                q6k_issue(ring + i * kQ6KUnit, units, unit0 + b0 + i, lane);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+                    prefetch_frags<kQ6KSteps>(frag + ((size_t)(tile0 + nt) * nblk + b0 + i) * (kQ6KSteps * 32), lane);
+            }
             cp_async_commit();
         }
         for (int b = b0; b < b1; b++) {
             const int pre = b + kStagesQ6K - 1;
-            if (pre < b1) q6k_issue(ring + ((pre - b0) % kStagesQ6K) * kQ6KUnit, units, unit0 + pre, lane);
+            if (pre < b1) {
+                q6k_issue(ring + ((pre - b0) % kStagesQ6K) * kQ6KUnit, units, unit0 + pre, lane);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+                    prefetch_frags<kQ6KSteps>(frag + ((size_t)(tile0 + nt) * nblk + pre) * (kQ6KSteps * 32), lane);
+            }
             cp_async_commit();
             cp_async_wait<kStagesQ6K - 1>();
             __syncwarp();
