@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libferric_cuda.so")
+# FERRIC_CUDA_LIB points the loader at another build of the same library (kernel A/B comparisons)
+LIB_PATH = os.environ.get("FERRIC_CUDA_LIB") or os.path.join(_HERE, "libferric_cuda.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED_TYPE, ERR_SHAPE, ERR_CUDA, ERR_OOM, UNSUPPORTED, ERR_TIMEOUT = range(8)
 STATUS_NAMES = ["OK", "ERR_INVALID_ARG", "ERR_UNSUPPORTED_TYPE", "ERR_SHAPE", "ERR_CUDA", "ERR_OOM", "UNSUPPORTED",

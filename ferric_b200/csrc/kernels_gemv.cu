@@ -328,7 +328,7 @@ __device__ __forceinline__ void q4k_row(const uint4& h, Q4KRow& r)
 }
 
 template <int NT, int EPI>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
                 int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles)
 {
@@ -350,38 +350,67 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 
     if (active && b0 < b1) {
         uint8_t* ring = gemv_smem + (size_t)warp * (kStagesQ4K * kQ4KUnit);
-        const size_t unit0 = (size_t)rt * nblk;
+        const uint8_t* wsrc = units + ((size_t)rt * nblk + b0) * kQ4KUnit;   // next unit to copy
+        const uint2* fsrc[NT];                                                 // fragments of the next unit to use
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) fsrc[nt] = frag + ((size_t)(tile0 + nt) * nblk + b0) * (kQ4KSteps * 32) + lane;
+        int issued = b0, wstage = 0, rstage = 0;
 #pragma unroll
         for (int i = 0; i < kStagesQ4K - 1; i++) {
-            if (b0 + i < b1) {
-                q4k_issue(ring + i * kQ4KUnit, units, unit0 + b0 + i, lane);
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++)
-                    prefetch_frags<kQ4KSteps>(frag + ((size_t)(tile0 + nt) * nblk + b0 + i) * (kQ4KSteps * 32), lane);
+            if (issued < b1) {
+                q4k_issue(ring + wstage * kQ4KUnit, wsrc, 0, lane);
+                wsrc += kQ4KUnit;
+                issued++;
+                wstage = wstage + 1 == kStagesQ4K ? 0 : wstage + 1;
             }
             cp_async_commit();
         }
-        for (int b = b0; b < b1; b++) {
-            const int pre = b + kStagesQ4K - 1;
-            if (pre < b1) {
-                q4k_issue(ring + ((pre - b0) % kStagesQ4K) * kQ4KUnit, units, unit0 + pre, lane);
+        // activation fragments are double-buffered in registers one super-block ahead, so the
+        // (L1 / L2 resident) loads never sit between an MMA and its operands
+        constexpr bool kAhead = NT == 1;  // with more column tiles the second buffer would spill
+        uint2 bf[NT][kQ4KSteps];
+        if (kAhead) {
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++)
-                    prefetch_frags<kQ4KSteps>(frag + ((size_t)(tile0 + nt) * nblk + pre) * (kQ4KSteps * 32), lane);
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int s = 0; s < kQ4KSteps; s++) bf[nt][s] = __ldg(fsrc[nt] + s * 32);
+        }
+
+        for (int b = b0; b < b1; b++) {
+            if (issued < b1) {
+                q4k_issue(ring + wstage * kQ4KUnit, wsrc, 0, lane);
+                wsrc += kQ4KUnit;
+                issued++;
+                wstage = wstage + 1 == kStagesQ4K ? 0 : wstage + 1;
             }
             cp_async_commit();
+            uint2 bn[kAhead ? NT : 1][kQ4KSteps];
+            if (kAhead) {
+                if (b + 1 < b1) {
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        fsrc[nt] += kQ4KSteps * 32;
+#pragma unroll
+                        for (int s = 0; s < kQ4KSteps; s++) bn[nt][s] = __ldg(fsrc[nt] + s * 32);
+                    }
+                }
+            } else {  // issue this super-block's fragment loads before waiting for its weights
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+                    for (int s = 0; s < kQ4KSteps; s++) bf[nt][s] = __ldg(fsrc[nt] + s * 32);
+                    fsrc[nt] += kQ4KSteps * 32;
+                }
+            }
             cp_async_wait<kStagesQ4K - 1>();
             __syncwarp();
             Q4KUnit cur;
-            q4k_read(cur, ring + ((b - b0) % kStagesQ4K) * kQ4KUnit, lane);
+            q4k_read(cur, ring + rstage * kQ4KUnit, lane);
+            rstage = rstage + 1 == kStagesQ4K ? 0 : rstage + 1;
             __syncwarp();  // every lane has its copy before a later stage copy may overwrite the slot
             Q4KRow rg, rh;
             q4k_row(cur.hg, rg);
             q4k_row(cur.hh, rh);
-            const uint2* fb[NT];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-                fb[nt] = frag + ((size_t)(tile0 + nt) * nblk + b) * (kQ4KSteps * 32) + lane;
 
             int ai[NT][4];  // sum_sb sc * (q . limb), per column
 #pragma unroll
@@ -403,9 +432,8 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
                     const int sch = (int)__byte_perm(s < 4 ? rh.sc_lo : rh.sc_hi, 0u, 0x4440u | (uint32_t)(s & 3));
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
-                        const uint2 bf = __ldg(fb[nt] + s * 32);
                         int c[4];
-                        imma_16832_u8s8(c, a0, a1, a2, a3, bf.x, bf.y, zero);
+                        imma_16832_u8s8(c, a0, a1, a2, a3, bf[nt][s].x, bf[nt][s].y, zero);
                         ai[nt][0] += scg * c[0];
                         ai[nt][1] += scg * c[1];
                         ai[nt][2] += sch * c[2];
@@ -418,16 +446,21 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             const uint32_t mh = t == 0 ? rh.m_lo : t == 1 ? rh.m_hi : 0u;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const uint2 bs = __ldg(fb[nt] + 8 * 32);
                 int c0[4], c1[4];
-                imma_16816_u8s8(c0, mg, mh, bs.x, zero);
-                imma_16816_u8s8(c1, mg, mh, bs.y, zero);
-                const float up = __uint_as_float(__ldg(fb[nt] + 9 * 32).x);
+                imma_16816_u8s8(c0, mg, mh, bf[nt][8].x, zero);
+                imma_16816_u8s8(c1, mg, mh, bf[nt][8].y, zero);
+                const float up = __uint_as_float(bf[nt][9].x);
                 const float fg = rg.d * up, fmg = -rg.dmin * up, fh = rh.d * up, fmh = -rh.dmin * up;
                 acc[nt][0] = fmaf(fmg, (float)(c0[0] + 128 * c1[0]), fmaf(fg, (float)ai[nt][0], acc[nt][0]));
                 acc[nt][1] = fmaf(fmg, (float)(c0[1] + 128 * c1[1]), fmaf(fg, (float)ai[nt][1], acc[nt][1]));
                 acc[nt][2] = fmaf(fmh, (float)(c0[2] + 128 * c1[2]), fmaf(fh, (float)ai[nt][2], acc[nt][2]));
                 acc[nt][3] = fmaf(fmh, (float)(c0[3] + 128 * c1[3]), fmaf(fh, (float)ai[nt][3], acc[nt][3]));
+            }
+            if (kAhead) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                    for (int s = 0; s < kQ4KSteps; s++) bf[nt][s] = bn[nt][s];
             }
         }
     }
@@ -478,7 +511,7 @@ __device__ __forceinline__ int sc_byte(const uint4& v, int i)
 }
 
 template <int NT, int EPI>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
                 int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles)
 {
