@@ -626,18 +626,31 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 // ------------------------------------------------------------------------------------------
 // launch
 // ------------------------------------------------------------------------------------------
-static int choose_wk(const DeviceWeights& w, Epilogue epi, const GemvTuning& tune)
+// How many of a CTA's 8 warps split K (the rest take different row tiles).  The grid should fit
+// in as few waves of resident CTAs as possible -- every wave pays its own pipeline fill and
+// drain -- and within that, K-splitting shortens each warp's serial walk.  Cost model: waves x
+// (super-blocks per warp + a fixed fill/drain term), measured in super-block times.
+static int choose_wk(const DeviceWeights& w, Epilogue epi, int nt, const GemvTuning& tune)
 {
-    int wk = tune.wk;
-    if (wk != 1 && wk != 2 && wk != 4 && wk != 8) {
-        // enough warps to keep ~24 per SM busy, but at least two super-blocks per warp
-        size_t tiles = w.row_tiles();
-        wk = 1;
-        while (wk < 8 && tiles * (size_t)wk < (size_t)tune.sm_count * 24 && w.nblk >= (size_t)(4 * wk)) wk *= 2;
+    int forced = tune.wk;
+    const int ctas_per_sm = nt <= 2 ? 2 : 1;
+    const size_t slots = (size_t)tune.sm_count * ctas_per_sm;
+    const size_t tiles = epi == kEpiSwiglu ? w.rows / 2 / 16 * 2 : w.row_tiles();
+    int best = 1;
+    double best_cost = 1e30;
+    for (int wk = 1; wk <= 8; wk *= 2) {
+        if ((size_t)wk > w.nblk && wk > 1) break;
+        if (epi == kEpiSwiglu && wk > 4) break;
+        if (forced == wk) return wk;
+        const size_t ctas = (tiles + (size_t)(8 / wk) - 1) / (size_t)(8 / wk);
+        const size_t waves = (ctas + slots - 1) / slots;
+        const double cost = (double)waves * ((double)((w.nblk + wk - 1) / wk) + 4.0);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = wk;
+        }
     }
-    if (epi == kEpiSwiglu && wk > 4) wk = 4;
-    while (wk > 1 && (size_t)wk > w.nblk) wk /= 2;
-    return wk;
+    return best;
 }
 
 template <int NT, int EPI>
@@ -673,7 +686,7 @@ int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
                     size_t ldy, Epilogue epi, const GemvTuning& tune)
 {
     if (m == 0 || w.rows == 0) return kOk;
-    const int nt = tiles_per_pass(m), wk = choose_wk(w, epi, tune);
+    const int nt = tiles_per_pass(m), wk = choose_wk(w, epi, nt, tune);
     const unsigned passes = (unsigned)(padded_tiles(m) / (size_t)nt);
     const uint2* f = reinterpret_cast<const uint2*>(frag);
 #define FERRIC_GEMV_CASE(NT_)                                                                             \
