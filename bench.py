@@ -252,22 +252,18 @@ def run_ours(args):
            "d2h_bytes_per_step": yh.numel() * 4, "ms_per_step": e2e_s * 1e3 / K}
 
     # ---- roofline of the dominant kernel: the Q4_K gate|up GEMV with the SwiGLU epilogue ----
+    # 64 distinct 100 MB matrices in turn (always cold in L2), launched from a CUDA graph so the host
+    # is out of the loop; CUDA events on the launching stream bracket 3 replays.
     peak, peak_kind = measured_peak()
     L0 = stack.layers[0]
-    m = L0.wgu.prepare(stack.xn)
-    reps = 3
-    for L in stack.layers:                                   # warm-up pass over every matrix
-        L.wgu.matmul_prepared(m, out=stack.f, swiglu=True)
-    torch.cuda.synchronize(dev)
-    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    r0.record()
-    for _ in range(reps):
-        for L in stack.layers:                               # 64 distinct 100 MB matrices: always cold in L2
+    xr = torch.randn((B, HIDDEN), device=dev, generator=g)
+    m = L0.wgu.prepare(xr)
+
+    def gate_up_pass():
+        for L in stack.layers:
             L.wgu.matmul_prepared(m, out=stack.f, swiglu=True)
-    r1.record()
-    torch.cuda.synchronize(dev)
-    n_launch = reps * len(stack.layers)
-    us_per_launch = r0.elapsed_time(r1) * 1e3 / n_launch
+
+    us_per_launch = graph_time_us(torch, ctx, gate_up_pass, reps=3) / len(stack.layers)
     algo_bytes = L0.wgu.nbytes() + B * HIDDEN * 4 + B * plan.ff_rows * 4
     achieved = algo_bytes / (us_per_launch * 1e-6) / 1e9
     traffic = None
@@ -320,12 +316,40 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def graph_time_us(torch, ctx, fn, reps=3):
+    """Microseconds for one call of `fn` (a sequence of launches on the context), replayed from a CUDA graph."""
+    dev = ctx.device
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        ctx.use_torch_stream()
+        fn()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        ctx.use_torch_stream()
+        fn()
+    ctx.use_torch_stream()
+    gr.replay()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        gr.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
 def per_matrix_table(torch, ctx, stack, QMatrix, B, peak):
-    """GB/s of each product of the layer (prepare + GEMV, cold: cycling over all layers' copies)."""
+    """GB/s of each product of the layer (prepare + GEMV), cold: cycling over all layers' copies."""
     out = {}
     p = stack.plan
-    cases = [("qkv_q4k_7168x5120", "wqkv", stack.xn, stack.qkv), ("o_q4k_5120x5120", "wo", stack.qkv[:, :p.q_rows], stack.o),
-             ("gate_up_swiglu_q4k_34816x5120", "wgu", stack.xn, stack.f), ("down_q6k_5120x17408", "wdown", stack.f, stack.d)]
+    xh = torch.randn((B, p.hidden), device=stack.h.device)
+    xf = torch.randn((B, p.ff_rows), device=stack.h.device)
+    cases = [("qkv_q4k_7168x5120", "wqkv", xh, stack.qkv), ("o_q4k_5120x5120", "wo", stack.qkv[:, :p.q_rows], stack.o),
+             ("gate_up_swiglu_q4k_34816x5120", "wgu", xh, stack.f), ("down_q6k_5120x17408", "wdown", xf, stack.d)]
     for name, attr, x, y in cases:
         def once():
             for L in stack.layers:
@@ -334,15 +358,7 @@ def per_matrix_table(torch, ctx, stack, QMatrix, B, peak):
                     w.try_matmul_swiglu(x, out=y)
                 else:
                     w.matmul(x, out=y)
-        once()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        once()
-        once()
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (2 * len(stack.layers))
+        us = graph_time_us(torch, ctx, once, reps=2) / len(stack.layers)
         w = getattr(stack.layers[0], attr)
         nbytes = w.nbytes() + x.shape[0] * x.shape[1] * 4 + y.numel() * 4
         out[name] = {"us": us, "GB/s": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak, "launches": 2}

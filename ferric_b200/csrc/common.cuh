@@ -76,6 +76,47 @@ __device__ __forceinline__ uint32_t bytes_to_h2(uint32_t w, uint32_t sel)
     return h2_as_u32(__hsub2(u32_as_h2(biased), u32_as_h2(0x64006400u)));
 }
 
+// Programmatic dependent launch.  Every hot-path kernel lets its successor in the stream start
+// launching at once (launch_dependents) and blocks (wait) before it touches anything an earlier
+// kernel produces or still reads.  A successor therefore overlaps its launch latency and its
+// weight prefetch -- weights are immutable -- with the tail of its predecessor.  Every kernel
+// executes the wait, so completion order stays transitive along the stream.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Loads of activations and activation fragments: data another kernel wrote, possibly while this
+// kernel was already resident (it only *used* them after pdl_wait).  They must take the coherent
+// path -- never ld.global.nc, whose lines may predate the producer's writes.
+__device__ __forceinline__ uint2 ld_act(const uint2* p)
+{
+    uint2 v;
+    asm volatile("ld.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_act(const float4* p)
+{
+    float4 v;
+    asm volatile("ld.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                                 Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
 
 }  // namespace ferric

@@ -244,7 +244,7 @@ int32_t run_matmul(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* 
     int32_t rc = kOk;
     if (phases & 1) {
         if ((rc = ensure_scratch(ctx, need)) != kOk) return rc;
-        if ((rc = launch_prep(ctx->stream, qm->ty, qm->w, x, m, ldx, ctx->scratch)) != kOk) return rc;
+        if ((rc = launch_prep(ctx->stream, qm->ty, qm->w, x, m, ldx, ctx->scratch, ctx->tune)) != kOk) return rc;
         ctx->launches++;
     }
     if (phases & 2) {
@@ -329,6 +329,7 @@ int32_t ferric_cuda_ctx_create_on_stream(int device, void* cuda_stream, ferric_c
     }
     ctx->tune.sm_count = ctx->prop.multiProcessorCount;
     if (const char* s = getenv("FERRIC_CUDA_GEMV_WK")) ctx->tune.wk = atoi(s);
+    if (const char* s = getenv("FERRIC_CUDA_PDL")) ctx->tune.pdl = atoi(s) != 0;
     *out = ctx;
     return kOk;
 }
@@ -522,7 +523,33 @@ int32_t ferric_cuda_add_rmsnorm(ferric_cuda_ctx* ctx, const float* a_dev, const 
     }
     DeviceGuard guard(ctx->device);
     ctx->launches++;
-    return launch_add_rmsnorm(ctx->stream, a_dev, b_dev, weight_dev, eps, rows, d, sum_dev, norm_dev);
+    return launch_add_rmsnorm(ctx->stream, a_dev, b_dev, weight_dev, eps, rows, d, sum_dev, norm_dev, ctx->tune);
+}
+
+int32_t ferric_cuda_add_rmsnorm_prepare(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* a_dev,
+                                        const float* b_dev, const float* weight_dev, float eps, size_t m, float* sum_dev,
+                                        float* norm_dev)
+{
+    if (!ctx || !qm || (m > 0 && !a_dev)) {
+        set_last_error("NULL context, matrix or buffer");
+        return kErrInvalidArg;
+    }
+    if (qm->ty == kGgmlQ8_0) {
+        set_last_error("Q8_0 has no prepared form");
+        return kUnsupported;
+    }
+    if ((reinterpret_cast<uintptr_t>(a_dev) | reinterpret_cast<uintptr_t>(b_dev) | reinterpret_cast<uintptr_t>(sum_dev) |
+         reinterpret_cast<uintptr_t>(norm_dev) | reinterpret_cast<uintptr_t>(weight_dev)) & 15) {
+        set_last_error("buffers must be 16-byte aligned");
+        return kErrInvalidArg;
+    }
+    if (m == 0 || qm->w.nblk == 0) return kOk;
+    DeviceGuard guard(ctx->device);
+    int32_t rc = ensure_scratch(ctx, frag_bytes(qm->ty, qm->w, m));
+    if (rc != kOk) return rc;
+    ctx->launches++;
+    return launch_norm_prep(ctx->stream, qm->ty, qm->w, a_dev, b_dev, weight_dev, eps, m, sum_dev, norm_dev, ctx->scratch,
+                            ctx->tune);
 }
 
 int32_t ferric_cuda_matmul_q_host(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_host, size_t m,
@@ -569,7 +596,7 @@ int32_t ferric_cuda_swiglu(ferric_cuda_ctx* ctx, const float* gu_dev, size_t t, 
     }
     DeviceGuard guard(ctx->device);
     ctx->launches++;
-    return launch_swiglu(ctx->stream, gu_dev, t, d, out_dev);
+    return launch_swiglu(ctx->stream, gu_dev, t, d, out_dev, ctx->tune);
 }
 
 int32_t ferric_cuda_dequant_f32(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, float* out_dev)

@@ -25,6 +25,7 @@ enum Epilogue : int { kEpiStore = 0, kEpiSwiglu = 1 };
 struct GemvTuning {
     int wk = 0;        // warps of a CTA that split K (0 = choose from the shape)
     int sm_count = 148;
+    bool pdl = true;   // programmatic dependent launch between consecutive kernels (FERRIC_CUDA_PDL=0 disables)
 };
 
 int32_t launch_repack(cudaStream_t st, uint32_t ty, const uint8_t* src, DeviceWeights& w, size_t src_nblk,
@@ -36,7 +37,12 @@ int32_t launch_dequant_raw(cudaStream_t st, uint32_t ty, const uint8_t* raw, siz
 size_t frag_bytes(uint32_t ty, const DeviceWeights& w, size_t m);
 // x[m, cols] (f32, row stride ldx) -> tensor-core B fragments in `frag`.
 int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* x, size_t m, size_t ldx,
-                    void* frag);
+                    void* frag, const GemvTuning& tune);
+// Fused (sum, norm) = add_rmsnorm(a, b, weight) and activation preparation of `norm` (row length
+// w.cols) in one kernel; sum / norm may be null when the caller does not need them in memory.
+int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* a, const float* b,
+                         const float* weight, float eps, size_t m, float* sum, float* norm, void* frag,
+                         const GemvTuning& tune);
 // y[m, rows] (row stride ldy) = x . W^T from prepared fragments.  With kEpiSwiglu the matrix is
 // [gate rows | up rows] and y is [m, rows/2] = silu(gate) * up.
 int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const void* frag, size_t m, float* y,
@@ -45,11 +51,11 @@ int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
 int32_t launch_gemv_q8_0(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y,
                          size_t ldy, const GemvTuning& tune);
 // out[t, d] = silu(gu[t, d]) * gu[t, d + ..] on a [t, 2d] tensor (the unfused twin).
-int32_t launch_swiglu(cudaStream_t st, const float* gu, size_t t, size_t d, float* out);
+int32_t launch_swiglu(cudaStream_t st, const float* gu, size_t t, size_t d, float* out, const GemvTuning& tune);
 
 // (sum, norm) = (a + b, rmsnorm(a + b) * weight); b and weight may be null (no add / unit weight),
 // sum may be null.
 int32_t launch_add_rmsnorm(cudaStream_t st, const float* a, const float* b, const float* weight, float eps,
-                           size_t rows, size_t d, float* sum, float* norm);
+                           size_t rows, size_t d, float* sum, float* norm, const GemvTuning& tune);
 
 }  // namespace ferric

@@ -50,40 +50,25 @@ __device__ __forceinline__ void imma_16816_s8s8(int (&d)[4], uint32_t a0, uint32
 // One warp per (tile of 2 activation rows, super-block); 4 warps per CTA.
 // ------------------------------------------------------------------------------------------
 constexpr int kPrepWarps = 4;
+constexpr int kNormPrepMaxWarps = 32;
 
-template <int TY>
-__global__ void __launch_bounds__(32 * kPrepWarps)
-prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk, size_t ntiles, uint2* __restrict__ frag)
-{
+struct PrepSmem {
     // per warp: limb bytes [row 0..1][limb 0..3][256], 16-weight limb sums [row][limb][16], 2^(e-6) [row]
-    __shared__ __align__(16) int8_t s_limb[kPrepWarps][2][kLimbs][256];
-    __shared__ int s_sum[kPrepWarps][2][kLimbs][16];
-    __shared__ float s_up[kPrepWarps][2];
+    int8_t limb[2][kLimbs][256];
+    int sum[2][kLimbs][16];
+    float up[2];
+};
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const size_t wid = blockIdx.x * (size_t)kPrepWarps + warp;
-    if (wid >= ntiles * nblk) return;
-    const size_t tile = wid / nblk, blk = wid % nblk;
-
-    // pass 1: lanes 0..15 scan activation row 2*tile, lanes 16..31 row 2*tile+1, 16 values each
-    const int prow = lane >> 4, q = lane & 15;
-    const size_t batch = tile * kRowsPerTile + (size_t)prow;
-    const bool valid = batch < m;
-    float v[16];
+// One warp turns 2 x 256 activations (lanes 0..15: row 0, lanes 16..31: row 1; 16 values each, in
+// v[]) into the fragments of (tile, blk).
+template <int TY>
+__device__ __forceinline__ void prep_block(const float (&v)[16], PrepSmem& sm, size_t tile, size_t nblk, size_t blk,
+                                           uint2* __restrict__ frag)
+{
+    const int lane = threadIdx.x & 31, prow = lane >> 4, q = lane & 15;
     float amax = 0.0f;
-    if (valid) {
-        const float4* p = reinterpret_cast<const float4*>(x + batch * ldx + blk * 256 + 16 * q);
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float4 f = __ldg(p + i);
-            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(v[i]));
-    } else {
-#pragma unroll
-        for (int i = 0; i < 16; i++) v[i] = 0.0f;
-    }
+    for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(v[i]));
 #pragma unroll
     for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     int e = 0;
@@ -95,6 +80,7 @@ prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk, size
     }
     const float to_int = ldexpf(1.0f, 27 - e);  // X = rint(x * 2^(27-e)), |X| <= 2^27
     int sum[kLimbs] = {0, 0, 0, 0};
+    uint32_t packed[kLimbs][4];
 #pragma unroll
     for (int i = 0; i < 16; i++) {
         int X = __float2int_rn(v[i] * to_int);
@@ -102,21 +88,26 @@ prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk, size
         int a2 = ((X + 64) & 127) - 64; X = (X - a2) >> 7;
         int a1 = ((X + 64) & 127) - 64; X = (X - a1) >> 7;
         int a0 = X;
-        s_limb[warp][prow][0][16 * q + i] = (int8_t)a0;
-        s_limb[warp][prow][1][16 * q + i] = (int8_t)a1;
-        s_limb[warp][prow][2][16 * q + i] = (int8_t)a2;
-        s_limb[warp][prow][3][16 * q + i] = (int8_t)a3;
+        const int w = i >> 2, sh = 8 * (i & 3);
+        if ((i & 3) == 0) packed[0][w] = packed[1][w] = packed[2][w] = packed[3][w] = 0u;
+        packed[0][w] |= (uint32_t)(a0 & 0xff) << sh;
+        packed[1][w] |= (uint32_t)(a1 & 0xff) << sh;
+        packed[2][w] |= (uint32_t)(a2 & 0xff) << sh;
+        packed[3][w] |= (uint32_t)(a3 & 0xff) << sh;
         sum[0] += a0; sum[1] += a1; sum[2] += a2; sum[3] += a3;
     }
 #pragma unroll
-    for (int j = 0; j < kLimbs; j++) s_sum[warp][prow][j][q] = sum[j];
-    if (q == 0) s_up[warp][prow] = ldexpf(1.0f, e - 6);
+    for (int j = 0; j < kLimbs; j++) {
+        *reinterpret_cast<uint4*>(&sm.limb[prow][j][16 * q]) = make_uint4(packed[j][0], packed[j][1], packed[j][2], packed[j][3]);
+        sm.sum[prow][j][q] = sum[j];
+    }
+    if (q == 0) sm.up[prow] = ldexpf(1.0f, e - 6);
     __syncwarp();
 
-    // pass 2: fragments.  B layout: lane = 4*g + t, column g = 4*(row in tile) + limb.
+    // fragments.  B layout: lane = 4*g + t, column g = 4*(row in tile) + limb.
     const int g = lane >> 2, t = lane & 3, brow = g >> 2, limb = g & 3;
-    const int8_t* lb = s_limb[warp][brow][limb];
-    const int* sm = s_sum[warp][brow][limb];
+    const int8_t* lb = sm.limb[brow][limb];
+    const int* ss = sm.sum[brow][limb];
     constexpr int STEPS = TY == (int)kGgmlQ4K ? kQ4KSteps : kQ6KSteps;
     uint2* out = frag + frag_index(tile, nblk, blk, STEPS, 0, lane);
 #pragma unroll
@@ -137,9 +128,9 @@ prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk, size
         int S;
         if (TY == (int)kGgmlQ4K) {
             const int sb = 4 * t + i;  // 8 sub-blocks of 32 weights; k slots 8..15 stay zero
-            S = sb < 8 ? sm[2 * sb] + sm[2 * sb + 1] : 0;
+            S = sb < 8 ? ss[2 * sb] + ss[2 * sb + 1] : 0;
         } else {
-            S = sm[4 * t + i];
+            S = ss[4 * t + i];
         }
         const int s0 = ((S + 64) & 127) - 64, s1 = (S - s0) >> 7;
         lo |= (uint32_t)(s0 & 0xff) << (8 * i);
@@ -147,7 +138,108 @@ prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk, size
     }
     out[8 * 32] = make_uint2(lo, hi);
     // the C layout gives this lane columns 2t, 2t+1 = activation row t>>1 of the tile
-    out[9 * 32] = make_uint2(__float_as_uint(s_up[warp][t >> 1]), 0u);
+    out[9 * 32] = make_uint2(__float_as_uint(sm.up[t >> 1]), 0u);
+    __syncwarp();
+}
+
+template <int TY>
+__global__ void __launch_bounds__(32 * kPrepWarps)
+prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk, size_t ntiles, uint2* __restrict__ frag)
+{
+    __shared__ __align__(16) PrepSmem sm[kPrepWarps];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t wid = blockIdx.x * (size_t)kPrepWarps + warp;
+    if (wid >= ntiles * nblk) return;
+    const size_t tile = wid / nblk, blk = wid % nblk;
+    const size_t batch = tile * kRowsPerTile + (size_t)(lane >> 4);
+    float v[16];
+    if (batch < m) {
+        const float4* p = reinterpret_cast<const float4*>(x + batch * ldx + blk * 256 + 16 * (lane & 15));
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float4 f = ld_act(p + i);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = 0.0f;
+    }
+    prep_block<TY>(v, sm[warp], tile, nblk, blk, frag);
+}
+
+// Fused residual add + RMSNorm + activation preparation (crates/ferric-tensor/src/lib.rs:372-384
+// followed by the matmul's own input conversion).  One CTA per tile of 2 activation rows; warp w
+// handles super-blocks w, w + nwarps, ...
+template <int TY>
+__global__ void __launch_bounds__(32 * kNormPrepMaxWarps)
+norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wgt, float eps,
+                 size_t m, size_t d, size_t nblk, float* __restrict__ sum, float* __restrict__ norm,
+                 uint2* __restrict__ frag)
+{
+    extern __shared__ __align__(16) uint8_t np_smem[];
+    PrepSmem* sm = reinterpret_cast<PrepSmem*>(np_smem);
+    __shared__ float part[2][kNormPrepMaxWarps];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int prow = lane >> 4, q = lane & 15;
+    const size_t tile = blockIdx.x, batch = tile * kRowsPerTile + (size_t)prow;
+    const bool valid = batch < m;
+    // pass 1: s = a + b, sum of squares per row
+    float ms = 0.0f;
+    for (size_t blk = warp; blk < nblk; blk += nwarps) {
+        if (valid) {
+            const size_t off = batch * d + blk * 256 + 16 * q;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float4 f = ld_act(reinterpret_cast<const float4*>(a + off) + i);
+                if (b) {
+                    const float4 g = ld_act(reinterpret_cast<const float4*>(b + off) + i);
+                    f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
+                }
+                if (sum) reinterpret_cast<float4*>(sum + off)[i] = f;
+                ms = fmaf(f.x, f.x, ms); ms = fmaf(f.y, f.y, ms); ms = fmaf(f.z, f.z, ms); ms = fmaf(f.w, f.w, ms);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) ms += __shfl_xor_sync(0xffffffffu, ms, o);
+    if (q == 0) part[prow][warp] = ms;
+    __syncthreads();
+    float tot = 0.0f;
+    for (int i = 0; i < nwarps; i++) tot += part[prow][i];
+    const float inv = 1.0f / sqrtf(tot / (float)d + eps);
+    // pass 2: normalise and convert
+    for (size_t blk = warp; blk < nblk; blk += nwarps) {
+        float v[16];
+        if (valid) {
+            const size_t off = batch * d + blk * 256 + 16 * q;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float4 f;
+                if (sum) {
+                    f = reinterpret_cast<const float4*>(sum + off)[i];
+                } else {
+                    f = ld_act(reinterpret_cast<const float4*>(a + off) + i);
+                    if (b) {
+                        const float4 g = ld_act(reinterpret_cast<const float4*>(b + off) + i);
+                        f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
+                    }
+                }
+                float4 w4 = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (wgt) w4 = __ldg(reinterpret_cast<const float4*>(wgt + blk * 256 + 16 * q) + i);
+                f.x = f.x * inv * w4.x; f.y = f.y * inv * w4.y; f.z = f.z * inv * w4.z; f.w = f.w * inv * w4.w;
+                if (norm) reinterpret_cast<float4*>(norm + off)[i] = f;
+                v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[i] = 0.0f;
+        }
+        prep_block<TY>(v, sm[warp], tile, nblk, blk, frag);
+    }
 }
 
 static int tiles_per_pass(size_t m)
@@ -169,16 +261,45 @@ size_t frag_bytes(uint32_t ty, const DeviceWeights& w, size_t m)
 }
 
 int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* x, size_t m, size_t ldx,
-                    void* frag)
+                    void* frag, const GemvTuning& tune)
 {
     size_t ntiles = padded_tiles(m), warps = ntiles * w.nblk;
     if (warps == 0) return kOk;
-    unsigned grid = (unsigned)((warps + kPrepWarps - 1) / kPrepWarps);
+    dim3 grid((unsigned)((warps + kPrepWarps - 1) / kPrepWarps)), block(32 * kPrepWarps);
+    uint2* f = reinterpret_cast<uint2*>(frag);
     if (ty == kGgmlQ4K)
-        prep_kernel<(int)kGgmlQ4K><<<grid, 32 * kPrepWarps, 0, st>>>(x, m, ldx, w.nblk, ntiles, reinterpret_cast<uint2*>(frag));
+        FERRIC_CUDA_TRY(launch_kernel(prep_kernel<(int)kGgmlQ4K>, grid, block, 0, st, tune.pdl, x, m, ldx, w.nblk, ntiles, f));
     else
-        prep_kernel<(int)kGgmlQ6K><<<grid, 32 * kPrepWarps, 0, st>>>(x, m, ldx, w.nblk, ntiles, reinterpret_cast<uint2*>(frag));
-    FERRIC_CUDA_TRY(cudaGetLastError());
+        FERRIC_CUDA_TRY(launch_kernel(prep_kernel<(int)kGgmlQ6K>, grid, block, 0, st, tune.pdl, x, m, ldx, w.nblk, ntiles, f));
+    return kOk;
+}
+
+int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* a, const float* b,
+                         const float* weight, float eps, size_t m, float* sum, float* norm, void* frag,
+                         const GemvTuning& tune)
+{
+    size_t ntiles = padded_tiles(m);
+    if (ntiles == 0 || w.nblk == 0) return kOk;
+    int nwarps = (int)(w.nblk < (size_t)kNormPrepMaxWarps ? w.nblk : (size_t)kNormPrepMaxWarps);
+    dim3 grid((unsigned)ntiles), block(32 * nwarps);
+    size_t smem = (size_t)nwarps * sizeof(PrepSmem);
+    uint2* f = reinterpret_cast<uint2*>(frag);
+    static thread_local int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ4K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(kNormPrepMaxWarps * sizeof(PrepSmem)));
+        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ6K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(kNormPrepMaxWarps * sizeof(PrepSmem)));
+        attr_dev = dev;
+    }
+    if (ty == kGgmlQ4K)
+        FERRIC_CUDA_TRY(launch_kernel(norm_prep_kernel<(int)kGgmlQ4K>, grid, block, smem, st, tune.pdl, a, b, weight, eps, m,
+                                      w.cols, w.nblk, sum, norm, f));
+    else
+        FERRIC_CUDA_TRY(launch_kernel(norm_prep_kernel<(int)kGgmlQ6K>, grid, block, smem, st, tune.pdl, a, b, weight, eps, m,
+                                      w.cols, w.nblk, sum, norm, f));
     return kOk;
 }
 
@@ -202,14 +323,6 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait()
 {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-// Pull the activation fragments of one (tile, super-block) -- STEPS x 256 bytes -- into L1 ahead of
-// use: lanes 0..(STEPS*2-1) touch one 128-byte line each.
-template <int STEPS>
-__device__ __forceinline__ void prefetch_frags(const uint2* frag_unit, int lane)
-{
-    if (lane < STEPS * 2) asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(frag_unit) + 128 * lane));
 }
 
 // ------------------------------------------------------------------------------------------
@@ -333,6 +446,7 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
                 int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles)
 {
     __shared__ float red[8][NT * 4][32];
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, t = lane & 3;
     int rt, out_tile;
     bool active;
@@ -348,13 +462,13 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 #pragma unroll
         for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
 
-    if (active && b0 < b1) {
-        uint8_t* ring = gemv_smem + (size_t)warp * (kStagesQ4K * kQ4KUnit);
-        const uint8_t* wsrc = units + ((size_t)rt * nblk + b0) * kQ4KUnit;   // next unit to copy
-        const uint2* fsrc[NT];                                                 // fragments of the next unit to use
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) fsrc[nt] = frag + ((size_t)(tile0 + nt) * nblk + b0) * (kQ4KSteps * 32) + lane;
-        int issued = b0, wstage = 0, rstage = 0;
+    // weights never change, so their first pipeline stages are requested before the wait on the
+    // preceding kernel; everything that depends on the activations comes after it
+    const bool work = active && b0 < b1;
+    uint8_t* ring = gemv_smem + (size_t)warp * (kStagesQ4K * kQ4KUnit);
+    const uint8_t* wsrc = units + ((size_t)(work ? rt : 0) * nblk + (work ? b0 : 0)) * kQ4KUnit;   // next unit to copy
+    int issued = b0, wstage = 0, rstage = 0;
+    if (work) {
 #pragma unroll
         for (int i = 0; i < kStagesQ4K - 1; i++) {
             if (issued < b1) {
@@ -365,15 +479,19 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             }
             cp_async_commit();
         }
-        // activation fragments are double-buffered in registers one super-block ahead, so the
-        // (L1 / L2 resident) loads never sit between an MMA and its operands
+    }
+    pdl_wait();
+    if (work) {
+        const uint2* fsrc[NT];                                                 // fragments of the next unit to use
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) fsrc[nt] = frag + ((size_t)(tile0 + nt) * nblk + b0) * (kQ4KSteps * 32) + lane;
         constexpr bool kAhead = NT == 1;  // with more column tiles the second buffer would spill
         uint2 bf[NT][kQ4KSteps];
         if (kAhead) {
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-                for (int s = 0; s < kQ4KSteps; s++) bf[nt][s] = __ldg(fsrc[nt] + s * 32);
+                for (int s = 0; s < kQ4KSteps; s++) bf[nt][s] = ld_act(fsrc[nt] + s * 32);
         }
 
         for (int b = b0; b < b1; b++) {
@@ -391,14 +509,14 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
                     for (int nt = 0; nt < NT; nt++) {
                         fsrc[nt] += kQ4KSteps * 32;
 #pragma unroll
-                        for (int s = 0; s < kQ4KSteps; s++) bn[nt][s] = __ldg(fsrc[nt] + s * 32);
+                        for (int s = 0; s < kQ4KSteps; s++) bn[nt][s] = ld_act(fsrc[nt] + s * 32);
                     }
                 }
             } else {  // issue this super-block's fragment loads before waiting for its weights
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
 #pragma unroll
-                    for (int s = 0; s < kQ4KSteps; s++) bf[nt][s] = __ldg(fsrc[nt] + s * 32);
+                    for (int s = 0; s < kQ4KSteps; s++) bf[nt][s] = ld_act(fsrc[nt] + s * 32);
                     fsrc[nt] += kQ4KSteps * 32;
                 }
             }
@@ -516,6 +634,7 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
                 int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles)
 {
     __shared__ float red[8][NT * 4][32];
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, t = lane & 3;
     int rt, out_tile;
     bool active;
@@ -531,37 +650,69 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 #pragma unroll
         for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
 
-    if (active && b0 < b1) {
-        uint8_t* ring = gemv_smem + (size_t)warp * (kStagesQ6K * kQ6KUnit);
-        const size_t unit0 = (size_t)rt * nblk;
+    // weights never change, so their first pipeline stages are requested before the wait on the
+    // preceding kernel; everything that depends on the activations comes after it
+    const bool work = active && b0 < b1;
+    uint8_t* ring = gemv_smem + (size_t)warp * (kStagesQ6K * kQ6KUnit);
+    const uint8_t* wsrc = units + ((size_t)(work ? rt : 0) * nblk + (work ? b0 : 0)) * kQ6KUnit;   // next unit to copy
+    int issued = b0, wstage = 0, rstage = 0;
+    if (work) {
 #pragma unroll
         for (int i = 0; i < kStagesQ6K - 1; i++) {
-            if (b0 + i < b1) {
-                q6k_issue(ring + i * kQ6KUnit, units, unit0 + b0 + i, lane);
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++)
-                    prefetch_frags<kQ6KSteps>(frag + ((size_t)(tile0 + nt) * nblk + b0 + i) * (kQ6KSteps * 32), lane);
+            if (issued < b1) {
+                q6k_issue(ring + wstage * kQ6KUnit, wsrc, 0, lane);
+                wsrc += kQ6KUnit;
+                issued++;
+                wstage = wstage + 1 == kStagesQ6K ? 0 : wstage + 1;
             }
             cp_async_commit();
         }
-        for (int b = b0; b < b1; b++) {
-            const int pre = b + kStagesQ6K - 1;
-            if (pre < b1) {
-                q6k_issue(ring + ((pre - b0) % kStagesQ6K) * kQ6KUnit, units, unit0 + pre, lane);
+    }
+    pdl_wait();
+    if (work) {
+        const uint2* fsrc[NT];                                                 // fragments of the next unit to use
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++)
-                    prefetch_frags<kQ6KSteps>(frag + ((size_t)(tile0 + nt) * nblk + pre) * (kQ6KSteps * 32), lane);
+        for (int nt = 0; nt < NT; nt++) fsrc[nt] = frag + ((size_t)(tile0 + nt) * nblk + b0) * (kQ6KSteps * 32) + lane;
+        constexpr bool kAhead = NT == 1;
+        uint2 bf[NT][kQ6KSteps];
+        if (kAhead) {
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int s = 0; s < kQ6KSteps; s++) bf[nt][s] = ld_act(fsrc[nt] + s * 32);
+        }
+        for (int b = b0; b < b1; b++) {
+            if (issued < b1) {
+                q6k_issue(ring + wstage * kQ6KUnit, wsrc, 0, lane);
+                wsrc += kQ6KUnit;
+                issued++;
+                wstage = wstage + 1 == kStagesQ6K ? 0 : wstage + 1;
             }
             cp_async_commit();
+            uint2 bn[kAhead ? NT : 1][kQ6KSteps];
+            if (kAhead) {
+                if (b + 1 < b1) {
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        fsrc[nt] += kQ6KSteps * 32;
+#pragma unroll
+                        for (int s = 0; s < kQ6KSteps; s++) bn[nt][s] = ld_act(fsrc[nt] + s * 32);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+                    for (int s = 0; s < kQ6KSteps; s++) bf[nt][s] = ld_act(fsrc[nt] + s * 32);
+                    fsrc[nt] += kQ6KSteps * 32;
+                }
+            }
             cp_async_wait<kStagesQ6K - 1>();
             __syncwarp();
             Q6KUnit cur;
-            q6k_read(cur, ring + ((b - b0) % kStagesQ6K) * kQ6KUnit, lane);
+            q6k_read(cur, ring + rstage * kQ6KUnit, lane);
+            rstage = rstage + 1 == kStagesQ6K ? 0 : rstage + 1;
             __syncwarp();
-            const uint2* fb[NT];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-                fb[nt] = frag + ((size_t)(tile0 + nt) * nblk + b) * (kQ6KSteps * 32) + lane;
 
             int ai[NT][4];
 #pragma unroll
@@ -574,9 +725,6 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
                     // double step 4h + k: sub-blocks sb = 8h + 2k + is, is = 0 (.x) and 1 (.y)
-                    uint2 bf[NT];
-#pragma unroll
-                    for (int nt = 0; nt < NT; nt++) bf[nt] = __ldg(fb[nt] + (4 * h + k) * 32);
 #pragma unroll
                     for (int is = 0; is < 2; is++) {
                         const int wi = 2 * h + is, sb = 8 * h + 2 * k + is;
@@ -592,7 +740,7 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 #pragma unroll
                         for (int nt = 0; nt < NT; nt++) {
                             int c[4];
-                            imma_16816_u8s8(c, a0, a1, is ? bf[nt].y : bf[nt].x, zero);
+                            imma_16816_u8s8(c, a0, a1, is ? bf[nt][4 * h + k].y : bf[nt][4 * h + k].x, zero);
                             ai[nt][0] += scg * c[0];
                             ai[nt][1] += scg * c[1];
                             ai[nt][2] += sch * c[2];
@@ -607,16 +755,21 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             const float dh = __half2float(__ushort_as_half((unsigned short)(cur.dpair >> 16)));
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const uint2 bs = __ldg(fb[nt] + 8 * 32);
                 int c0[4], c1[4];
-                imma_16816_s8s8(c0, sg, sh, bs.x, zero);
-                imma_16816_s8s8(c1, sg, sh, bs.y, zero);
-                const float up = __uint_as_float(__ldg(fb[nt] + 9 * 32).x);
+                imma_16816_s8s8(c0, sg, sh, bf[nt][8].x, zero);
+                imma_16816_s8s8(c1, sg, sh, bf[nt][8].y, zero);
+                const float up = __uint_as_float(bf[nt][9].x);
                 const float fg = dg * up, fh = dh * up;
                 acc[nt][0] = fmaf(fg, (float)(ai[nt][0] - 32 * (c0[0] + 128 * c1[0])), acc[nt][0]);
                 acc[nt][1] = fmaf(fg, (float)(ai[nt][1] - 32 * (c0[1] + 128 * c1[1])), acc[nt][1]);
                 acc[nt][2] = fmaf(fh, (float)(ai[nt][2] - 32 * (c0[2] + 128 * c1[2])), acc[nt][2]);
                 acc[nt][3] = fmaf(fh, (float)(ai[nt][3] - 32 * (c0[3] + 128 * c1[3])), acc[nt][3]);
+            }
+            if (kAhead) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                    for (int s = 0; s < kQ6KSteps; s++) bf[nt][s] = bn[nt][s];
             }
         }
     }
@@ -655,7 +808,7 @@ static int choose_wk(const DeviceWeights& w, Epilogue epi, int nt, const GemvTun
 
 template <int NT, int EPI>
 static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint2* frag, size_t m, float* y,
-                          size_t ldy, int wk, unsigned passes)
+                          size_t ldy, int wk, unsigned passes, bool pdl)
 {
     const int row_tiles = (int)w.row_tiles(), wr = 8 / wk;
     const int ff_tiles = (int)(w.rows / 2 / 16);
@@ -670,15 +823,15 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
             cudaFuncSetAttribute(gemv_q4k_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ4K);
             attr_dev_q4 = dev;
         }
-        gemv_q4k_kernel<NT, EPI><<<grid, 256, kSmemQ4K, st>>>(w.units, frag, y, (int)w.rows, (int)w.nblk, (int)m, ldy,
-                                                             row_tiles, wk, ff_tiles);
+        launch_kernel(gemv_q4k_kernel<NT, EPI>, grid, dim3(256), kSmemQ4K, st, pdl, w.units, frag, y, (int)w.rows,
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles);
     } else {
         if (attr_dev_q6 != dev) {
             cudaFuncSetAttribute(gemv_q6k_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ6K);
             attr_dev_q6 = dev;
         }
-        gemv_q6k_kernel<NT, EPI><<<grid, 256, kSmemQ6K, st>>>(w.units, frag, y, (int)w.rows, (int)w.nblk, (int)m, ldy,
-                                                             row_tiles, wk, ff_tiles);
+        launch_kernel(gemv_q6k_kernel<NT, EPI>, grid, dim3(256), kSmemQ6K, st, pdl, w.units, frag, y, (int)w.rows,
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles);
     }
 }
 
@@ -690,8 +843,8 @@ int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
     const unsigned passes = (unsigned)(padded_tiles(m) / (size_t)nt);
     const uint2* f = reinterpret_cast<const uint2*>(frag);
 #define FERRIC_GEMV_CASE(NT_)                                                                             \
-    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, passes);             \
-    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, passes)
+    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl);             \
+    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl)
     if (nt == 1) { FERRIC_GEMV_CASE(1); }
     else if (nt == 2) { FERRIC_GEMV_CASE(2); }
     else { FERRIC_GEMV_CASE(4); }
@@ -710,6 +863,8 @@ __global__ void __launch_bounds__(256) gemv_q8_0_kernel(const int8_t* __restrict
                                                         const float* __restrict__ x, int m, size_t ldx,
                                                         float* __restrict__ y, size_t ldy, int rows, int cols)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row = blockIdx.x * 8 + warp;
     if (row >= rows) return;
@@ -734,7 +889,7 @@ __global__ void __launch_bounds__(256) gemv_q8_0_kernel(const int8_t* __restrict
             float part = 0.0f;
 #pragma unroll
             for (int k = 0; k < 4; k++) {
-                const float4 xv = __ldg(xp + k);
+                const float4 xv = ld_act(xp + k);
                 part = fmaf(xv.x, wf[4 * k], part);
                 part = fmaf(xv.y, wf[4 * k + 1], part);
                 part = fmaf(xv.z, wf[4 * k + 2], part);
@@ -753,18 +908,20 @@ __global__ void __launch_bounds__(256) gemv_q8_0_kernel(const int8_t* __restrict
 }
 
 int32_t launch_gemv_q8_0(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y,
-                         size_t ldy, const GemvTuning&)
+                         size_t ldy, const GemvTuning& tune)
 {
     if (m == 0 || w.rows == 0) return kOk;
     dim3 grid((unsigned)((w.rows + 7) / 8), (unsigned)((m + 3) / 4));
-    gemv_q8_0_kernel<4><<<grid, 256, 0, st>>>(w.q8_qs, w.q8_d, x, (int)m, ldx, y, ldy, (int)w.rows, (int)w.cols);
-    FERRIC_CUDA_TRY(cudaGetLastError());
+    FERRIC_CUDA_TRY(launch_kernel(gemv_q8_0_kernel<4>, grid, dim3(256), 0, st, tune.pdl, w.q8_qs, w.q8_d, x, (int)m, ldx, y,
+                                  ldy, (int)w.rows, (int)w.cols));
     return kOk;
 }
 
 // out[r, c] = silu(gu[r, c]) * gu[r, d + c]   (crates/ferric-tensor/src/lib.rs:2603-2618)
 __global__ void swiglu_kernel(const float* __restrict__ gu, size_t t, size_t d, float* __restrict__ out)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t total = t * d;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t r = i / d, c = i % d;
@@ -772,14 +929,13 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, size_t t, size_t d, 
     }
 }
 
-int32_t launch_swiglu(cudaStream_t st, const float* gu, size_t t, size_t d, float* out)
+int32_t launch_swiglu(cudaStream_t st, const float* gu, size_t t, size_t d, float* out, const GemvTuning& tune)
 {
     size_t total = t * d;
     if (total == 0) return kOk;
     size_t g = (total + 255) / 256;
     if (g > 148 * 32) g = 148 * 32;
-    swiglu_kernel<<<(unsigned)g, 256, 0, st>>>(gu, t, d, out);
-    FERRIC_CUDA_TRY(cudaGetLastError());
+    FERRIC_CUDA_TRY(launch_kernel(swiglu_kernel, dim3((unsigned)g), dim3(256), 0, st, tune.pdl, gu, t, d, out));
     return kOk;
 }
 

@@ -10,6 +10,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const float* __restric
                                                           float* __restrict__ sum, float* __restrict__ norm)
 {
     __shared__ float part[8];
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t base = blockIdx.x * d;
     float ms = 0.0f;
     for (size_t j = threadIdx.x; j < d; j += blockDim.x) {
@@ -33,11 +35,11 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const float* __restric
 }
 
 int32_t launch_add_rmsnorm(cudaStream_t st, const float* a, const float* b, const float* weight, float eps,
-                           size_t rows, size_t d, float* sum, float* norm)
+                           size_t rows, size_t d, float* sum, float* norm, const GemvTuning& tune)
 {
     if (rows == 0 || d == 0) return kOk;
-    add_rmsnorm_kernel<<<(unsigned)rows, 256, 0, st>>>(a, b, weight, eps, d, sum, norm);
-    FERRIC_CUDA_TRY(cudaGetLastError());
+    FERRIC_CUDA_TRY(launch_kernel(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(256), 0, st, tune.pdl, a, b, weight, eps, d,
+                                  sum, norm));
     return kOk;
 }
 

@@ -239,6 +239,18 @@ class QMatrix:
                                                x.stride(0) if m > 1 else 0), "prepare_x")
         return m
 
+    def add_rmsnorm_prepare(self, a: torch.Tensor, b: Optional[torch.Tensor] = None,
+                            weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                            sum_out: Optional[torch.Tensor] = None, norm_out: Optional[torch.Tensor] = None) -> int:
+        """``(sum, norm) = a.add_rmsnorm(b, weight, eps)`` fused with ``prepare(norm)``; returns m."""
+        m = a.numel() // a.shape[-1]
+        assert a.shape[-1] == self.cols() and a.is_contiguous()
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        _check(self._lib.ferric_cuda_add_rmsnorm_prepare(self.ctx._h, self._h, a.data_ptr(), ptr(b), ptr(weight),
+                                                         float(eps), m, ptr(sum_out), ptr(norm_out)),
+               "add_rmsnorm_prepare")
+        return m
+
     def matmul_prepared(self, m: int, out: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
         """Second half of ``matmul`` / ``try_matmul_swiglu`` on the activations last prepared on the context."""
         n = self.rows() // 2 if swiglu else self.rows()

@@ -137,22 +137,29 @@ class DecodeStack:
 
     # -- one token step --------------------------------------------------------------------
     def step(self) -> torch.Tensor:
-        """h <- stack(h) on the device, in place; returns h."""
+        """h <- stack(h) on the device, in place; returns h.
+
+        Per layer: [norm + prepare] -> q|k|v -> o (+ all-reduce) -> [add + norm + prepare] ->
+        gate|up+SwiGLU -> down (+ all-reduce); the residual add after down is fused into the next
+        layer's first kernel."""
         c, p = self.ctx, self.plan
         before = c.launches()
-        c.add_rmsnorm(self.h, None, None, self.eps, None, self.xn)
-        for L in self.layers:
-            L.wqkv.matmul(self.xn, out=self.qkv)
+        n = len(self.layers)
+        m = self.layers[0].wqkv.add_rmsnorm_prepare(self.h, None, None, self.eps)
+        for i, L in enumerate(self.layers):
+            L.wqkv.matmul_prepared(m, out=self.qkv)
             L.wo.matmul(self.qkv[:, :p.q_rows], out=self.o)          # mixer pass-through: q feeds o
             if self.all_reduce:
                 self.all_reduce(self.o)
-            c.add_rmsnorm(self.h, self.o, None, self.eps, self.h, self.xn)
-            if L.wgu.try_matmul_swiglu(self.xn, out=self.f) is None:
-                raise RuntimeError("gate|up matrix is not fusable")
+            L.wgu.add_rmsnorm_prepare(self.h, self.o, None, self.eps, sum_out=self.h)
+            L.wgu.matmul_prepared(m, out=self.f, swiglu=True)
             L.wdown.matmul(self.f, out=self.d)
             if self.all_reduce:
                 self.all_reduce(self.d)
-            c.add_rmsnorm(self.h, self.d, None, self.eps, self.h, self.xn)
+            if i + 1 < n:
+                self.layers[i + 1].wqkv.add_rmsnorm_prepare(self.h, self.d, None, self.eps, sum_out=self.h)
+            else:
+                c.add_rmsnorm(self.h, self.d, None, self.eps, self.h, self.xn)
         self.launches_per_step = c.launches() - before
         return self.h
 

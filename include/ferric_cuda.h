@@ -172,6 +172,15 @@ int32_t ferric_cuda_matmul_q_prepared(ferric_cuda_ctx *ctx, const ferric_qmatrix
 int32_t ferric_cuda_add_rmsnorm(ferric_cuda_ctx *ctx, const float *a_dev, const float *b_dev, const float *weight_dev,
                                 float eps, size_t rows, size_t d, float *sum_dev, float *norm_dev);
 
+/* add_rmsnorm fused with prepare_x: norm = rmsnorm(a + b) * weight (row length = the matrix's
+ * inner dimension) is converted straight into the context's activation scratch, ready for
+ * matmul_q_prepared on `qm` or any matrix of the same format and inner dimension -- the
+ * `x.add_rmsnorm(..)` -> `matmul_q` pair of a decoder layer (crates/ferric-llama/src/qwen35.rs:986-996)
+ * in one launch.  b_dev, weight_dev, sum_dev (may alias a_dev) and norm_dev may each be NULL. */
+int32_t ferric_cuda_add_rmsnorm_prepare(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *a_dev,
+                                        const float *b_dev, const float *weight_dev, float eps, size_t m,
+                                        float *sum_dev, float *norm_dev);
+
 /* The same product with HOST activation and result buffers: copies x in, runs, copies y out and
  * returns when y is complete. */
 int32_t ferric_cuda_matmul_q_host(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_host, size_t m,

@@ -566,6 +566,28 @@ void fo_swiglu(const float *gu, size_t t, size_t d, float *out)
         }
 }
 
+/* (sum, norm) = (a + b, rmsnorm(a + b) * weight): one sequential f32 pass per row for the mean of
+ * squares, inv = 1 / sqrt(ms / d + eps), norm = s * inv * w.  b NULL = plain rmsnorm, w NULL = ones.
+ * crates/ferric-tensor/src/lib.rs:2057-2075 (ADD_RMSNORM_WGSL), :2018-2032 (RMSNORM_WGSL). */
+void fo_add_rmsnorm(const float *a, const float *b, const float *w, float eps, size_t rows, size_t d,
+                    float *sum, float *norm)
+{
+    for (size_t r = 0; r < rows; r++) {
+        size_t base = r * d;
+        float ms = 0.0f;
+        for (size_t j = 0; j < d; j++) {
+            float s = b ? a[base + j] + b[base + j] : a[base + j];
+            if (sum) sum[base + j] = s;
+            ms = ms + s * s;
+        }
+        float inv = 1.0f / sqrtf(ms / (float)d + eps);
+        for (size_t j = 0; j < d; j++) {
+            float s = b ? a[base + j] + b[base + j] : a[base + j];
+            norm[base + j] = s * inv * (w ? w[j] : 1.0f);
+        }
+    }
+}
+
 /* ---- fixture generators used by the reference's own kernel tests --------------------------- */
 
 /* crates/ferric-gguf/src/lib.rs:985-997 (`quant_q8_0`); out holds ceil(n/32)*34 bytes. */

@@ -62,6 +62,8 @@ def lib() -> C.CDLL:
                                      C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_int, C.c_int]
         L.fo_swiglu.restype = None
         L.fo_swiglu.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]
+        L.fo_add_rmsnorm.restype = None
+        L.fo_add_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]
         L.fo_quant_q8_0.restype = None
         L.fo_quant_q8_0.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
         L.fo_q4k_block.restype = None
@@ -174,6 +176,19 @@ def swiglu(gu: np.ndarray, d: int) -> np.ndarray:
     out = np.empty((t, d), dtype=np.float32)
     lib().fo_swiglu(_p(gu), t, d, _p(out))
     return out
+
+
+def add_rmsnorm(a: np.ndarray, b=None, w=None, eps: float = 1e-6):
+    """(sum, norm) as the reference's add_rmsnorm kernel computes them; b=None is plain rmsnorm."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    d = a.shape[-1]
+    rows = a.size // d
+    b = None if b is None else np.ascontiguousarray(b, dtype=np.float32)
+    w = None if w is None else np.ascontiguousarray(w, dtype=np.float32)
+    s, n = np.empty_like(a), np.empty_like(a)
+    lib().fo_add_rmsnorm(_p(a), _p(b) if b is not None else None, _p(w) if w is not None else None, eps, rows, d,
+                         _p(s), _p(n))
+    return s, n
 
 
 def quant_q8_0(x: np.ndarray) -> np.ndarray:

@@ -320,6 +320,83 @@ def test_swiglu_declines_what_the_reference_declines(F, ctx):
     qm.close()
 
 
+# ------------------------------------------------------------------------------ norms around the matmuls
+@pytest.mark.parametrize("rows,d", [(1, 5120), (3, 1024), (8, 256)])
+def test_add_rmsnorm_matches_reference_kernel(F, ctx, rows, d):
+    rng = np.random.default_rng(rows + d)
+    a = rng.standard_normal((rows, d)).astype(np.float32) * np.float32(3)
+    b = rng.standard_normal((rows, d)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, d).astype(np.float32)
+    ta, tb, tw = (torch.from_numpy(v).cuda() for v in (a, b, w))
+    s_ref, n_ref = O.add_rmsnorm(a, b, w, 1e-6)
+    s, n = ctx.add_rmsnorm(ta, tb, tw, 1e-6)
+    assert (s.cpu().numpy().view(np.uint32) == s_ref.view(np.uint32)).all()          # the sum is one f32 add
+    assert np.abs(n.cpu().numpy() - n_ref).max() <= 1e-5 * np.abs(n_ref).max()    # the mean of squares reassociates
+    _, n2 = ctx.add_rmsnorm(ta, None, None, 1e-6)                                   # plain, weightless rmsnorm
+    assert np.abs(n2.cpu().numpy() - O.add_rmsnorm(a, None, None, 1e-6)[1]).max() <= 1e-5 * np.abs(n_ref).max()
+
+
+@pytest.mark.parametrize("ty", [12, 14])
+@pytest.mark.parametrize("m", [1, 2, 5])
+def test_fused_add_rmsnorm_prepare(F, ctx, ty, m):
+    rows, d = 96, 1536
+    raw = synth.matrix(ty, rows, d, seed=21)
+    rng = np.random.default_rng(m)
+    a = rng.standard_normal((m, d)).astype(np.float32) * np.float32(2)
+    b = rng.standard_normal((m, d)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, d).astype(np.float32)
+    qm = F.QMatrix.from_bytes(ctx, raw, ty, rows, d)
+    ta, tb, tw = (torch.from_numpy(v).cuda() for v in (a, b, w))
+    s_out, n_out = torch.empty_like(ta), torch.empty_like(ta)
+    mm = qm.add_rmsnorm_prepare(ta, tb, tw, 1e-6, sum_out=s_out, norm_out=n_out)
+    y = qm.matmul_prepared(mm).cpu().numpy()
+    s_ref, n_ref = O.add_rmsnorm(a, b, w, 1e-6)
+    assert (s_out.cpu().numpy().view(np.uint32) == s_ref.view(np.uint32)).all()
+    assert np.abs(n_out.cpu().numpy() - n_ref).max() <= 1e-5 * np.abs(n_ref).max()
+    # the product must be the unfused pair's: matmul_q of the norm this kernel produced
+    y2 = qm.matmul(n_out).cpu().numpy()
+    assert np.abs(y - y2).max() <= 1e-6 * max(np.abs(y2).max(), 1e-3)
+    assert_close(y, O.matmul_q(raw, ty, rows, d, n_ref), "fused norm + prepare", exact_product(raw, ty, rows, d, n_ref))
+    # in place on the residual stream, no norm written
+    qm.add_rmsnorm_prepare(ta, tb, tw, 1e-6, sum_out=ta)
+    y3 = qm.matmul_prepared(mm).cpu().numpy()
+    assert (ta.cpu().numpy().view(np.uint32) == s_ref.view(np.uint32)).all() and np.array_equal(y3, y)
+    qm.close()
+
+
+def test_decode_stack_step_matches_layerwise_oracle(F, ctx):
+    """Two small layers of the decode stack against the oracle, kernel by kernel semantics."""
+    from ferric_b200.stack import DecodeStack, TPPlan
+    plan = TPPlan.make(1, 0, hidden=512, n_ff=768, q_out=512, kv_out=256)
+    st = DecodeStack(ctx, plan, n_layers=2, batch=2)
+    rng = np.random.default_rng(8)
+    raws = []
+    for l in range(2):
+        mats = [(12, plan.q_rows + 2 * plan.kv_rows, 512), (12, 512, plan.q_rows), (12, 2 * plan.ff_rows, 512), (14, 512, plan.ff_rows)]
+        raw = [synth.matrix(ty, r, c, seed=100 + 10 * l + i) for i, (ty, r, c) in enumerate(mats)]
+        raws.append(list(zip(mats, raw)))
+        st.add_layer(*[F.QMatrix.from_bytes(ctx, rw, ty, r, c) for (ty, r, c), rw in zip(mats, raw)])
+    st.reserve()
+    h0 = rng.standard_normal((2, 512)).astype(np.float32)
+    st.h.copy_(torch.from_numpy(h0).cuda())
+    got = st.step().cpu().numpy()
+    h = h0.copy()
+    xn = O.add_rmsnorm(h, None, None, 1e-6)[1]
+    for (q, o, gu, dn) in raws:
+        qkv = O.matmul_q(q[1], *q[0], xn)
+        oo = O.matmul_q(o[1], *o[0], np.ascontiguousarray(qkv[:, :plan.q_rows]))
+        h, xn = O.add_rmsnorm(h, oo, None, 1e-6)
+        f = O.swiglu(O.matmul_q(gu[1], *gu[0], xn), plan.ff_rows)
+        dd = O.matmul_q(dn[1], *dn[0], f)
+        h, xn = O.add_rmsnorm(h, dd, None, 1e-6)
+    assert np.abs(got - h).max() <= 1e-4 + 1e-3 * np.abs(h).max()
+    st.capture()
+    st.h.copy_(torch.from_numpy(h0).cuda())
+    got2 = st.run().cpu().numpy()
+    assert np.array_equal(got, got2)           # graph replay == eager launches, bit for bit
+    st.close()
+
+
 # ------------------------------------------------------------------------------ shards
 @pytest.mark.parametrize("ty", [12, 14, 8])
 def test_row_and_k_shards_compose(F, ctx, ty):
