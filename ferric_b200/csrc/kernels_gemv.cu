@@ -52,12 +52,14 @@ __device__ __forceinline__ void imma_16816_s8s8(int (&d)[4], uint32_t a0, uint32
 constexpr int kPrepWarps = 4;
 constexpr int kNormPrepMaxWarps = 32;
 
-struct PrepSmem {
-    // per warp: limb bytes [row 0..1][limb 0..3][256], 16-weight limb sums [row][limb][16], 2^(e-6) [row]
-    int8_t limb[2][kLimbs][256];
-    int sum[2][kLimbs][16];
-    float up[2];
+// Per-warp staging.  16-byte aligned (and so padded to a multiple of 16 bytes): the limb rows are
+// written with 128-bit stores, and the struct is used in arrays indexed by warp.
+struct __align__(16) PrepSmem {
+    int8_t limb[2][kLimbs][256];  // limb bytes [row 0..1][limb 0..3][256]
+    int sum[2][kLimbs][16];       // 16-weight limb sums
+    float up[2];                  // 2^(e-6) per row
 };
+static_assert(sizeof(PrepSmem) % 16 == 0, "PrepSmem must keep 16-byte alignment inside arrays");
 
 // One warp turns 2 x 256 activations (lanes 0..15: row 0, lanes 16..31: row 1; 16 values each, in
 // v[]) into the fragments of (tile, blk).
