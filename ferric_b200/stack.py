@@ -197,3 +197,36 @@ class DecodeStack:
         for L in self.layers:
             L.close()
         self.layers = []
+
+
+def shard_bytes(raw, ggml_type: int, rows: int, cols: int, row0: int, nrows: int, col0: int, ncols: int):
+    """Host-side twin of ``QMatrix.from_bytes_view``: the raw GGUF block bytes of a row range x K range.
+
+    Row ranges are contiguous byte ranges; K ranges gather each row's blocks (256-column aligned)."""
+    import numpy as np
+
+    vals, bb = synth.BLOCK[ggml_type]
+    assert cols % vals == 0 and col0 % vals == 0 and ncols % vals == 0
+    a = np.frombuffer(raw, dtype=np.uint8) if not isinstance(raw, np.ndarray) else raw
+    blocks = a.reshape(rows, cols // vals, bb)
+    return np.ascontiguousarray(blocks[row0:row0 + nrows, col0 // vals:(col0 + ncols) // vals, :]).reshape(-1)
+
+
+def layer_shards(plan: TPPlan, full: dict) -> dict:
+    """Slice one layer's full matrices {"q","k","v","o","gate","up","down"} (raw bytes, GGUF [out, in]) into this
+    rank's fused shards {"qkv","o","gate_up","down"}: q|k|v and gate|up stacked along rows as ``qm_cat`` does
+    (crates/ferric-llama/src/qwen35.rs:380-402), o and down cut along K."""
+    import numpy as np
+
+    p = plan
+    q = shard_bytes(full["q"], GGML_Q4_K, p.q_out, p.hidden, p.q_row0, p.q_rows, 0, p.hidden)
+    k = shard_bytes(full["k"], GGML_Q4_K, p.kv_out, p.hidden, p.kv_row0, p.kv_rows, 0, p.hidden)
+    v = shard_bytes(full["v"], GGML_Q4_K, p.kv_out, p.hidden, p.kv_row0, p.kv_rows, 0, p.hidden)
+    g = shard_bytes(full["gate"], GGML_Q4_K, p.n_ff, p.hidden, p.ff_row0, p.ff_rows, 0, p.hidden)
+    u = shard_bytes(full["up"], GGML_Q4_K, p.n_ff, p.hidden, p.ff_row0, p.ff_rows, 0, p.hidden)
+    return {
+        "qkv": np.concatenate([q, k, v]),
+        "o": shard_bytes(full["o"], GGML_Q4_K, p.hidden, p.q_out, 0, p.hidden, p.q_row0, p.q_rows),
+        "gate_up": np.concatenate([g, u]),
+        "down": shard_bytes(full["down"], GGML_Q6_K, p.hidden, p.n_ff, 0, p.hidden, p.ff_row0, p.ff_rows),
+    }
