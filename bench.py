@@ -311,9 +311,14 @@ def run_ours(args):
             "extras": extras,
         }
         print(json.dumps(line), flush=True)
-    stack.close()
     if world > 1:
-        dist.destroy_process_group()
+        # Captured graphs hold NCCL work; tearing the process group down under them can block for
+        # minutes.  All ranks meet once more, then leave without the collective teardown.
+        barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+    stack.close()
 
 
 def graph_time_us(torch, ctx, fn, reps=3):
