@@ -665,4 +665,73 @@ int32_t ferric_gguf_deq_raw(ferric_cuda_ctx* ctx, const uint8_t* raw, size_t raw
     return rc;
 }
 
+// ---------------------------------------------------------------------------------------------
+// matmul_q for callers that must not allocate.
+//
+// Some hosts hand this library a device whose memory is already fully spoken for -- a serving
+// process that carved HBM into KV-cache pages at start-up, a real-time loop in which the implicit
+// device synchronisation of cudaMalloc / cudaFree is not acceptable, a sandboxed plugin that is
+// not permitted to call the allocator at all.  For them the activation-fragment scratch of the
+// Q4_K / Q6_K product lives in a fixed array inside the library image instead of in memory the
+// context grows on demand.  Every GPU that loads the library carries the array until the process
+// exits.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kNoAllocScratchBytes = 2u << 20;  // 2 MiB: e.g. 8 activation rows x 32768 columns
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {};
+
+// The array's name is only a host-side handle; its device address has to be looked up, per device,
+// with that device current.  Done once per device and cached.
+int32_t noalloc_scratch_ptr(int device, void** out)
+{
+    if (device < 0 || device >= kMaxDevices) {
+        set_last_error("device %d out of range for the fixed scratch table", device);
+        return kErrInvalidArg;
+    }
+    void* p = __atomic_load_n(&g_noalloc_ptr[device], __ATOMIC_ACQUIRE);
+    if (!p) {
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);  // the caller made `device` current
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+        __atomic_store_n(&g_noalloc_ptr[device], p, __ATOMIC_RELEASE);
+    }
+    *out = p;
+    return kOk;
+}
+}  // namespace
+
+int32_t ferric_cuda_matmul_q_noalloc(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_dev, size_t m,
+                                     size_t x_cols, float* y_dev)
+{
+    int32_t rc = check_matmul_args(ctx, qm, x_dev, m, x_cols, y_dev);
+    if (rc != kOk) return rc;
+    if (m == 0 || qm->w.rows == 0) return kOk;
+    DeviceGuard guard(ctx->device);
+    if (qm->ty == kGgmlQ8_0) {  // this format needs no scratch at all
+        ctx->launches++;
+        return launch_gemv_q8_0(ctx->stream, qm->w, x_dev, m, qm->w.cols, y_dev, qm->w.rows, ctx->tune);
+    }
+    if (qm->w.nblk == 0) {
+        FERRIC_CUDA_TRY(cudaMemsetAsync(y_dev, 0, m * qm->w.rows * sizeof(float), ctx->stream));
+        return kOk;
+    }
+    const size_t need = frag_bytes(qm->ty, qm->w, m);
+    if (need > kNoAllocScratchBytes) {
+        set_last_error("matmul_q_noalloc: %zu activation rows x %zu columns need %zu bytes of scratch, the fixed "
+                       "array holds %zu; use ferric_cuda_matmul_q or split the batch", m, x_cols, need,
+                       kNoAllocScratchBytes);
+        return kErrShape;
+    }
+    void* scratch = nullptr;
+    if ((rc = noalloc_scratch_ptr(ctx->device, &scratch)) != kOk) return rc;
+    // The preparation kernel rewrites every fragment the product reads (all padded tiles, every
+    // super-block), so nothing left over from an earlier call needs clearing first.
+    if ((rc = launch_prep(ctx->stream, qm->ty, qm->w, x_dev, m, qm->w.cols, scratch, ctx->tune)) != kOk) return rc;
+    rc = launch_gemv(ctx->stream, qm->ty, qm->w, scratch, m, y_dev, qm->w.rows, kEpiStore, ctx->tune);
+    ctx->launches += 2;
+    return rc;
+}
+
 }  // extern "C"

@@ -231,6 +231,16 @@ class QMatrix:
                                                  y.data_ptr(), ldy), "matmul_q")
         return y
 
+    def matmul_noalloc(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``matmul`` for hosts that must not allocate: the library's fixed scratch array is used and the
+        caller supplies ``out``.  Contiguous inputs only; fails if the product needs more than 2 MiB of scratch."""
+        if not (x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()):
+            raise TypeError("matmul_noalloc needs contiguous float32 CUDA tensors")
+        m = 1 if x.dim() == 1 else x.shape[0]
+        _check(self._lib.ferric_cuda_matmul_q_noalloc(self.ctx._h, self._h, x.data_ptr(), m, x.shape[-1],
+                                                      out.data_ptr()), "matmul_q_noalloc")
+        return out
+
     def prepare(self, x: torch.Tensor) -> int:
         """First half of ``matmul``: convert x into the context's activation scratch; returns m."""
         x = self._x2d(x, allow_row_stride=True)

@@ -181,6 +181,24 @@ int32_t ferric_cuda_add_rmsnorm_prepare(ferric_cuda_ctx *ctx, const ferric_qmatr
                                         const float *b_dev, const float *weight_dev, float eps, size_t m,
                                         float *sum_dev, float *norm_dev);
 
+/* No counterpart in the reference.  matmul_q for hosts that cannot let this library allocate: a
+ * server that has already divided the device's memory among its own pools, a latency-critical
+ * loop that cannot take the device-wide stall of cudaMalloc / cudaFree, a restricted plugin host.
+ * The Q4_K / Q6_K activation scratch is a fixed 2 MiB array inside the library (held by every GPU
+ * that loads it, until exit) rather than context memory grown on demand; the call makes no
+ * cudaMalloc, cudaFree or other allocating call.  Same arguments and result as
+ * ferric_cuda_matmul_q.  Limits and rules:
+ *  - the product must need no more than 2 MiB of scratch (ferric_cuda_qmatrix_scratch_bytes(qm, m);
+ *    e.g. m <= 8 at 32768 columns, m <= 2 at 131072) -- larger requests fail with FERRIC_ERR_SHAPE
+ *    and a message, nothing is launched;
+ *  - the first call on each device looks up the array's device address; make that first call
+ *    outside any stream capture;
+ *  - all contexts and threads share the one array per device: two such calls that overlap on the
+ *    GPU (different streams) race on it, so order them.  Nothing needs clearing between calls --
+ *    each call overwrites every byte it later reads. */
+int32_t ferric_cuda_matmul_q_noalloc(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t m,
+                                     size_t x_cols, float *y_dev);
+
 /* The same product with HOST activation and result buffers: copies x in, runs, copies y out and
  * returns when y is complete. */
 int32_t ferric_cuda_matmul_q_host(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_host, size_t m,
