@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch kernels directly instead of replaying a CUDA graph")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-matrix table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: the library's own peer-memory exchange (default) or NCCL through torch.distributed")
     return ap.parse_args()
 
 
@@ -175,7 +177,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    from ferric_b200 import Context, QMatrix
+    from ferric_b200 import Context, QMatrix, TPGroup
     from ferric_b200.stack import DecodeStack, TPPlan
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -204,8 +206,13 @@ def run_ours(args):
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
     ctx = Context(local)
     plan = TPPlan.make(world, rank, HIDDEN, N_FF, Q_OUT, KV_OUT)
-    allreduce = (lambda t: dist.all_reduce(t)) if world > 1 else None
-    stack = DecodeStack(ctx, plan, n_layers=args.layers, batch=B, all_reduce=allreduce)
+    allreduce, group = None, None
+    if world > 1 and args.allreduce == "nccl":
+        allreduce = lambda t: dist.all_reduce(t)
+    elif world > 1:
+        group = TPGroup(ctx, rank, world, B, HIDDEN)
+        group.connect_with_torch_distributed()
+    stack = DecodeStack(ctx, plan, n_layers=args.layers, batch=B, all_reduce=allreduce, group=group)
     stack.build_synthetic(seed=4)
     g = torch.Generator(device=dev).manual_seed(4)
     x0 = torch.randn((B, HIDDEN), device=dev, generator=g)
@@ -233,6 +240,8 @@ def run_ours(args):
     barrier()
     elapsed_ms = max_over_ranks(ev0.elapsed_time(ev1))
     finite = bool(torch.isfinite(stack.h).all().item())
+    if group is not None:
+        group.check()      # raises if any bounded wait on a peer ran out
     ms_per_step = elapsed_ms / K
     value = B * 1e3 / ms_per_step
 
@@ -304,7 +313,7 @@ def run_ours(args):
             "config": {"workload": WORKLOAD.format(b=B), "batch": B, "layers": args.layers,
                        "parallelism": f"tp{world}", "cuda_graph": not args.no_graph,
                        "l2": f"{stack.weight_bytes_per_step() / 1e9:.2f} GB of weights per GPU per step, larger than L2",
-                       "all_reduce": "nccl" if world > 1 else "none"},
+                       "all_reduce": (args.allreduce if world > 1 else "none")},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches_per_step * K), "launches_per_step": int(launches_per_step),
             "clocks": clocks.summary(), "step_weight_gbs_per_gpu": step_gbs, "output_finite": finite,

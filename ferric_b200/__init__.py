@@ -14,4 +14,4 @@ reference (dcharlot-physicalai-bmi/ferric)              here
 
 PyTorch is used only for device memory and streams; all arithmetic runs in ``libferric_cuda.so``.
 """
-from .ops import (Context, FerricError, QMatrix, GGML_Q4_K, GGML_Q6_K, GGML_Q8_0, type_size)  # noqa: F401
+from .ops import (Context, FerricError, QMatrix, TPGroup, GGML_Q4_K, GGML_Q6_K, GGML_Q8_0, type_size)  # noqa: F401

@@ -59,6 +59,14 @@ SIGNATURES = {
     "ferric_cuda_matmul_q_host": (_I32, [_P, _P, _P, _SZ, _SZ, _P]),
     "ferric_cuda_matmul_q_swiglu": (_I32, [_P, _P, _P, _SZ, _SZ, _P]),
     "ferric_cuda_swiglu": (_I32, [_P, _P, _SZ, _SZ, _P]),
+    "ferric_cuda_tp_create": (_I32, [_P, _I32, _I32, _SZ, C.POINTER(_P)]),
+    "ferric_cuda_tp_export": (_I32, [_P, _P]),
+    "ferric_cuda_tp_connect": (_I32, [_P, _P]),
+    "ferric_cuda_tp_partial": (_P, [_P, _I32]),
+    "ferric_cuda_tp_signal": (_I32, [_P, _P, _I32]),
+    "ferric_cuda_tp_add_rmsnorm_prepare": (_I32, [_P, _P, _I32, _P, _P, _P, C.c_float, _SZ, _P, _P]),
+    "ferric_cuda_tp_status": (_I32, [_P, _P, C.POINTER(_I32)]),
+    "ferric_cuda_tp_free": (None, [_P]),
     "ferric_cuda_dequant_f32": (_I32, [_P, _P, _P]),
     "ferric_cuda_dequant_bf16": (_I32, [_P, _P, _P]),
 }

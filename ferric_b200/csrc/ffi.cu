@@ -9,6 +9,7 @@
 #include "../../include/ferric_cuda.h"
 #include "common.cuh"
 #include "kernels.h"
+#include "handles.h"
 
 namespace ferric {
 
@@ -32,51 +33,7 @@ int32_t cuda_fail(cudaError_t e, const char* what)
 
 using namespace ferric;
 
-struct ferric_cuda_ctx {
-    int device = 0;
-    cudaStream_t stream = nullptr;
-    bool owns_stream = false;
-    void* scratch = nullptr;
-    size_t scratch_bytes = 0;
-    uint64_t launches = 0;
-    GemvTuning tune;
-    cudaDeviceProp prop;
-};
-
-struct ferric_qmatrix {
-    uint32_t ty = 0;
-    int device = 0;
-    DeviceWeights w;
-    void* storage = nullptr;
-    size_t storage_bytes = 0;
-};
-
-namespace {
-
-struct DeviceGuard {
-    int prev = -1;
-    bool ok = false;
-    explicit DeviceGuard(int dev)
-    {
-        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        ok = cudaSetDevice(dev) == cudaSuccess;
-    }
-    ~DeviceGuard()
-    {
-        if (prev >= 0) cudaSetDevice(prev);
-    }
-};
-
-bool block_info(uint32_t ty, size_t* vals, size_t* bytes)
-{
-    switch (ty) {
-    case kGgmlQ8_0: *vals = 32; *bytes = 34; return true;
-    case kGgmlQ4K: *vals = 256; *bytes = 144; return true;
-    case kGgmlQ6K: *vals = 256; *bytes = 210; return true;
-    default: return false;
-    }
-}
-
+namespace ferric {
 int32_t ensure_scratch(ferric_cuda_ctx* ctx, size_t bytes)
 {
     if (bytes <= ctx->scratch_bytes) return kOk;
@@ -88,6 +45,20 @@ int32_t ensure_scratch(ferric_cuda_ctx* ctx, size_t bytes)
     FERRIC_CUDA_TRY(cudaMallocAsync(&ctx->scratch, want, ctx->stream));
     ctx->scratch_bytes = want;
     return kOk;
+}
+
+}  // namespace ferric
+
+namespace {
+
+bool block_info(uint32_t ty, size_t* vals, size_t* bytes)
+{
+    switch (ty) {
+    case kGgmlQ8_0: *vals = 32; *bytes = 34; return true;
+    case kGgmlQ4K: *vals = 256; *bytes = 144; return true;
+    case kGgmlQ6K: *vals = 256; *bytes = 210; return true;
+    default: return false;
+    }
 }
 
 int32_t check_matmul_args(const ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const void* x, size_t m,

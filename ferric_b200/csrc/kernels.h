@@ -18,6 +18,18 @@ struct DeviceWeights {
     size_t row_tiles() const { return (rows + 15) / 16; }
 };
 
+// Tensor-parallel exchange seen from one rank: the f32 partial sums of every rank (its own
+// included) in peer-mapped memory, the arrival flags peers write into this rank's memory, this
+// rank's own count of exchanges so far, and a status word for waits that give up.
+constexpr int kMaxRanks = 8;
+struct PeerSum {
+    const float* part[kMaxRanks] = {};
+    const unsigned* flags = nullptr;   // [world], local memory, written by peers
+    const unsigned* epoch = nullptr;   // local: how many exchanges of this kind this rank has signalled
+    int* status = nullptr;             // set to 1 if a wait ran out
+    int world = 0;                     // 0 = no exchange
+};
+
 enum Epilogue : int { kEpiStore = 0, kEpiSwiglu = 1 };
 
 // Tunables read once from the environment (FERRIC_CUDA_*), the counterpart of the reference's
@@ -42,6 +54,9 @@ int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
 // w.cols) in one kernel; sum / norm may be null when the caller does not need them in memory.
 int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* a, const float* b,
                          const float* weight, float eps, size_t m, float* sum, float* norm, void* frag,
+                         const GemvTuning& tune, const PeerSum& peers = PeerSum());
+// One CTA: bump this rank's exchange count and publish it to every peer's flag slot for this rank.
+int32_t launch_tp_signal(cudaStream_t st, unsigned* epoch, unsigned* const* peer_flag_slots, int world,
                          const GemvTuning& tune);
 // y[m, rows] (row stride ldy) = x . W^T from prepared fragments.  With kEpiSwiglu the matrix is
 // [gate rows | up rows] and y is [m, rows/2] = silu(gate) * up.

@@ -171,6 +171,47 @@ prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk, size
     prep_block<TY>(v, sm[warp], tile, nblk, blk, frag);
 }
 
+// A bounded wait on a peer: ~1 s of polling, then the kernel records the failure and carries on.
+constexpr int kPeerWaitSpins = 4000000;
+
+// Sum of all ranks' partials at float offset `off`, in rank order (the same order on every rank,
+// so every rank forms bit-identical sums).  Peer memory is read uncached: it changes between
+// exchanges while this SM may still hold lines of the previous one.
+__device__ __forceinline__ float4 peer_sum4(const PeerSum& p, size_t off)
+{
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < p.world; r++) {
+        float4 v;
+        asm volatile("ld.global.cv.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p.part[r] + off) : "memory");
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    return s;
+}
+
+// Publish this rank's next exchange count to every peer (one thread per peer).
+__global__ void tp_signal_kernel(unsigned* epoch, unsigned* const* peer_flag_slots, int world)
+{
+    __shared__ unsigned e;
+    pdl_launch_dependents();
+    pdl_wait();  // the product whose result is being announced is complete and visible
+    if (threadIdx.x == 0) {
+        e = *epoch + 1;
+        *epoch = e;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag_slots[threadIdx.x]), "r"(e) : "memory");
+    }
+}
+
+int32_t launch_tp_signal(cudaStream_t st, unsigned* epoch, unsigned* const* peer_flag_slots, int world,
+                         const GemvTuning& tune)
+{
+    FERRIC_CUDA_TRY(launch_kernel(tp_signal_kernel, dim3(1), dim3(32), 0, st, tune.pdl, epoch, peer_flag_slots, world));
+    return kOk;
+}
+
 // Fused residual add + RMSNorm + activation preparation (crates/ferric-tensor/src/lib.rs:372-384
 // followed by the matmul's own input conversion).  One CTA per tile of 2 activation rows; warp w
 // handles super-blocks w, w + nwarps, ...
@@ -178,13 +219,31 @@ template <int TY>
 __global__ void __launch_bounds__(32 * kNormPrepMaxWarps)
 norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wgt, float eps,
                  size_t m, size_t d, size_t nblk, float* __restrict__ sum, float* __restrict__ norm,
-                 uint2* __restrict__ frag)
+                 uint2* __restrict__ frag, PeerSum peers)
 {
     extern __shared__ __align__(16) uint8_t np_smem[];
     PrepSmem* sm = reinterpret_cast<PrepSmem*>(np_smem);
     __shared__ float part[2][kNormPrepMaxWarps];
     pdl_launch_dependents();
     pdl_wait();
+    if (peers.world > 0) {
+        // every rank's partial must have arrived: peers publish their exchange count into this
+        // rank's flag slots; wait (bounded) until each has reached this rank's own count
+        if (threadIdx.x < peers.world) {
+            const unsigned want = *peers.epoch;
+            unsigned seen = 0;
+            int spins = 0;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(peers.flags + threadIdx.x) : "memory");
+                if ((int)(seen - want) >= 0) break;
+                if (++spins > kPeerWaitSpins) {
+                    *peers.status = 1;
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int prow = lane >> 4, q = lane & 15;
     const size_t tile = blockIdx.x, batch = tile * kRowsPerTile + (size_t)prow;
@@ -199,6 +258,10 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
                 float4 f = ld_act(reinterpret_cast<const float4*>(a + off) + i);
                 if (b) {
                     const float4 g = ld_act(reinterpret_cast<const float4*>(b + off) + i);
+                    f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
+                }
+                if (peers.world > 0) {
+                    const float4 g = peer_sum4(peers, off + 4 * i);
                     f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                 }
                 if (sum) reinterpret_cast<float4*>(sum + off)[i] = f;
@@ -227,6 +290,10 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
                     f = ld_act(reinterpret_cast<const float4*>(a + off) + i);
                     if (b) {
                         const float4 g = ld_act(reinterpret_cast<const float4*>(b + off) + i);
+                        f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
+                    }
+                    if (peers.world > 0) {
+                        const float4 g = peer_sum4(peers, off + 4 * i);
                         f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                     }
                 }
@@ -278,7 +345,7 @@ int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
 
 int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* a, const float* b,
                          const float* weight, float eps, size_t m, float* sum, float* norm, void* frag,
-                         const GemvTuning& tune)
+                         const GemvTuning& tune, const PeerSum& peers)
 {
     size_t ntiles = padded_tiles(m);
     if (ntiles == 0 || w.nblk == 0) return kOk;
@@ -298,10 +365,10 @@ int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
     }
     if (ty == kGgmlQ4K)
         FERRIC_CUDA_TRY(launch_kernel(norm_prep_kernel<(int)kGgmlQ4K>, grid, block, smem, st, tune.pdl, a, b, weight, eps, m,
-                                      w.cols, w.nblk, sum, norm, f));
+                                      w.cols, w.nblk, sum, norm, f, peers));
     else
         FERRIC_CUDA_TRY(launch_kernel(norm_prep_kernel<(int)kGgmlQ6K>, grid, block, smem, st, tune.pdl, a, b, weight, eps, m,
-                                      w.cols, w.nblk, sum, norm, f));
+                                      w.cols, w.nblk, sum, norm, f, peers));
     return kOk;
 }
 

@@ -1,0 +1,204 @@
+// Tensor-parallel exchange group: the all-reduce of the row-parallel products' f32 partial sums,
+// done by this library's own kernels over peer-mapped memory (NVLink), one process per GPU.
+//
+// The reference has no collective at all (its multi-device story is host-buffer hops,
+// crates/ferric-tensor/src/sched.rs:209-265); the exchange exists because the layer matrices are
+// sharded across GPUs.  Shape of one exchange, for kind k (0: after o, 1: after down):
+//   1. the row-parallel GEMV writes its [m, hidden] partial straight into this rank's exchange
+//      buffer k (plain device memory, exported to the peers with CUDA IPC);
+//   2. a one-CTA signal kernel bumps this rank's count for k and stores it, release / system
+//      scope, into every peer's flag slot for this rank;
+//   3. the consumer (the fused add + rmsnorm + prepare kernel) waits, bounded, until all flag
+//      slots have reached its own count, then reads every rank's partial with plain peer loads
+//      and sums them in rank order -- bit-identical on every rank.
+// Buffers never need a second copy: a rank can only signal exchange n+1 of a kind after its own
+// consumer of exchange n ran, and that consumer ran only after every peer had signalled n, i.e.
+// had finished the step that read exchange n-1.  No multicast, no multimem: peer loads/stores only.
+#include <string.h>
+
+#include <new>
+
+#include "../../include/ferric_cuda.h"
+#include "common.cuh"
+#include "handles.h"
+#include "kernels.h"
+
+using namespace ferric;
+
+struct ferric_tp_group {
+    int device = 0, rank = 0, world = 1;
+    size_t elems = 0;                 // floats per exchange buffer
+    // one local allocation: [2 buffers of elems floats][flags 2 x kMaxRanks][epoch 2][status 1][slot tables]
+    void* local = nullptr;
+    size_t local_bytes = 0;
+    float* part[2] = {};
+    unsigned* flags[2] = {};          // [kind][world] written by peers
+    unsigned* epoch = nullptr;        // [2]
+    int* status = nullptr;
+    unsigned** slot_table[2] = {};    // device arrays [world] of peers' flag-slot addresses for this rank
+    void* peer_base[kMaxRanks] = {};  // IPC mappings of the peers' `local`
+    bool connected = false;
+};
+
+namespace {
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+size_t off_flags(size_t elems) { return align_up(2 * elems * sizeof(float), 256); }
+size_t off_epoch(size_t elems) { return off_flags(elems) + 2 * kMaxRanks * sizeof(unsigned); }
+size_t off_status(size_t elems) { return off_epoch(elems) + 2 * sizeof(unsigned); }
+size_t off_slots(size_t elems) { return align_up(off_status(elems) + sizeof(int), 256); }
+size_t total_bytes(size_t elems) { return off_slots(elems) + 2 * kMaxRanks * sizeof(void*); }
+}  // namespace
+
+extern "C" {
+
+int32_t ferric_cuda_tp_create(ferric_cuda_ctx* ctx, int32_t rank, int32_t world, size_t elems, ferric_tp_group** out)
+{
+    if (!ctx || !out || world < 1 || world > kMaxRanks || rank < 0 || rank >= world || elems == 0 || (elems & 3)) {
+        set_last_error("tp_create: bad arguments (world 1..%d, 0 <= rank < world, elems a positive multiple of 4)", kMaxRanks);
+        return kErrInvalidArg;
+    }
+    *out = nullptr;
+    DeviceGuard guard(ctx->device);
+    ferric_tp_group* g = new (std::nothrow) ferric_tp_group;
+    if (!g) return kErrOom;
+    g->device = ctx->device;
+    g->rank = rank;
+    g->world = world;
+    g->elems = elems;
+    g->local_bytes = total_bytes(elems);
+    cudaError_t e = cudaMalloc(&g->local, g->local_bytes);
+    if (e != cudaSuccess) {
+        delete g;
+        return cuda_fail(e, "cudaMalloc(exchange buffers)");
+    }
+    e = cudaMemset(g->local, 0, g->local_bytes);
+    if (e != cudaSuccess) {
+        cudaFree(g->local);
+        delete g;
+        return cuda_fail(e, "cudaMemset(exchange buffers)");
+    }
+    uint8_t* base = reinterpret_cast<uint8_t*>(g->local);
+    g->part[0] = reinterpret_cast<float*>(base);
+    g->part[1] = g->part[0] + elems;
+    g->flags[0] = reinterpret_cast<unsigned*>(base + off_flags(elems));
+    g->flags[1] = g->flags[0] + kMaxRanks;
+    g->epoch = reinterpret_cast<unsigned*>(base + off_epoch(elems));
+    g->status = reinterpret_cast<int*>(base + off_status(elems));
+    g->slot_table[0] = reinterpret_cast<unsigned**>(base + off_slots(elems));
+    g->slot_table[1] = g->slot_table[0] + kMaxRanks;
+    g->peer_base[rank] = g->local;
+    *out = g;
+    return kOk;
+}
+
+int32_t ferric_cuda_tp_export(ferric_tp_group* g, uint8_t* handle64)
+{
+    if (!g || !handle64) {
+        set_last_error("NULL group or handle buffer");
+        return kErrInvalidArg;
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    DeviceGuard guard(g->device);
+    cudaIpcMemHandle_t h;
+    FERRIC_CUDA_TRY(cudaIpcGetMemHandle(&h, g->local));
+    memcpy(handle64, &h, 64);
+    return kOk;
+}
+
+int32_t ferric_cuda_tp_connect(ferric_tp_group* g, const uint8_t* handles)
+{
+    if (!g || !handles) {
+        set_last_error("NULL group or handles");
+        return kErrInvalidArg;
+    }
+    if (g->connected) return kOk;
+    DeviceGuard guard(g->device);
+    for (int r = 0; r < g->world; r++) {
+        if (r == g->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + 64 * r, 64);
+        FERRIC_CUDA_TRY(cudaIpcOpenMemHandle(&g->peer_base[r], h, cudaIpcMemLazyEnablePeerAccess));
+    }
+    // where this rank announces itself: slot [kind][rank] of every rank's flag array
+    unsigned* slots[2][kMaxRanks] = {};
+    for (int k = 0; k < 2; k++)
+        for (int r = 0; r < g->world; r++)
+            slots[k][r] = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(g->peer_base[r]) + off_flags(g->elems)) +
+                          k * kMaxRanks + g->rank;
+    FERRIC_CUDA_TRY(cudaMemcpy(g->slot_table[0], slots, sizeof(slots), cudaMemcpyHostToDevice));
+    g->connected = true;
+    return kOk;
+}
+
+void* ferric_cuda_tp_partial(ferric_tp_group* g, int32_t kind) { return (g && kind >= 0 && kind < 2) ? g->part[kind] : nullptr; }
+
+int32_t ferric_cuda_tp_signal(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t kind)
+{
+    if (!ctx || !g || kind < 0 || kind > 1 || !g->connected) {
+        set_last_error("tp_signal: NULL / unconnected group or bad kind");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    ctx->launches++;
+    return launch_tp_signal(ctx->stream, g->epoch + kind, g->slot_table[kind], g->world, ctx->tune);
+}
+
+int32_t ferric_cuda_tp_add_rmsnorm_prepare(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t kind,
+                                           const ferric_qmatrix* qm, const float* a_dev, const float* weight_dev,
+                                           float eps, size_t m, float* sum_dev, float* norm_dev)
+{
+    if (!ctx || !g || !qm || kind < 0 || kind > 1 || !g->connected || (m > 0 && !a_dev)) {
+        set_last_error("tp_add_rmsnorm_prepare: NULL / unconnected argument or bad kind");
+        return kErrInvalidArg;
+    }
+    if (qm->ty == kGgmlQ8_0) return kUnsupported;
+    if (m * qm->w.cols > g->elems) {
+        set_last_error("exchange buffers hold %zu floats, %zu x %zu requested", g->elems, m, qm->w.cols);
+        return kErrShape;
+    }
+    if (m == 0 || qm->w.nblk == 0) return kOk;
+    DeviceGuard guard(ctx->device);
+    int32_t rc = ensure_scratch(ctx, frag_bytes(qm->ty, qm->w, m));
+    if (rc != kOk) return rc;
+    PeerSum p;
+    p.world = g->world;
+    for (int r = 0; r < g->world; r++)
+        p.part[r] = reinterpret_cast<const float*>(g->peer_base[r]) + (size_t)kind * g->elems;
+    p.flags = g->flags[kind];
+    p.epoch = g->epoch + kind;
+    p.status = g->status;
+    ctx->launches++;
+    return launch_norm_prep(ctx->stream, qm->ty, qm->w, a_dev, nullptr, weight_dev, eps, m, sum_dev, norm_dev, ctx->scratch,
+                            ctx->tune, p);
+}
+
+int32_t ferric_cuda_tp_status(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t* timed_out)
+{
+    if (!ctx || !g || !timed_out) {
+        set_last_error("NULL argument");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    FERRIC_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    int s = 0;
+    FERRIC_CUDA_TRY(cudaMemcpy(&s, g->status, sizeof(int), cudaMemcpyDeviceToHost));
+    *timed_out = s;
+    if (s) {
+        set_last_error("a peer did not announce its partial within the wait bound");
+        return kErrTimeout;
+    }
+    return kOk;
+}
+
+void ferric_cuda_tp_free(ferric_tp_group* g)
+{
+    if (!g) return;
+    DeviceGuard guard(g->device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < g->world; r++)
+        if (r != g->rank && g->peer_base[r]) cudaIpcCloseMemHandle(g->peer_base[r]);
+    cudaFree(g->local);
+    delete g;
+}
+
+}  // extern "C"

@@ -309,3 +309,75 @@ class QMatrix:
             out = torch.empty((self.rows(), self.cols()), dtype=torch.float32, device=dev)
             _check(self._lib.ferric_cuda_dequant_f32(self.ctx._h, self._h, out.data_ptr()), "dequant_f32")
         return out
+
+
+class _DevView:
+    """A raw device pointer dressed as a CUDA array, so torch can wrap it without copying."""
+
+    def __init__(self, ptr: int, shape, typestr: str = "<f4"):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
+                                         "version": 3, "strides": None}
+
+
+class TPGroup:
+    """One rank's end of the tensor-parallel exchange (``ferric_cuda_tp_*``): the all-reduce of the o / down
+    partial sums over CUDA-IPC peer memory.  ``exchange`` hands the 64-byte IPC handles round the ranks; any
+    all-gather of bytes will do (``torch.distributed.all_gather_object`` here)."""
+
+    def __init__(self, ctx: Context, rank: int, world: int, rows: int, cols: int):
+        self.ctx, self.rank, self.world, self.rows, self.cols = ctx, rank, world, rows, cols
+        self._lib = ctx._lib
+        h = C.c_void_p()
+        _check(self._lib.ferric_cuda_tp_create(ctx._h, rank, world, rows * cols, C.byref(h)), "tp_create")
+        self._h = h
+        self._views = {}
+
+    def export(self) -> bytes:
+        buf = (C.c_uint8 * 64)()
+        _check(self._lib.ferric_cuda_tp_export(self._h, buf), "tp_export")
+        return bytes(buf)
+
+    def connect(self, handles) -> None:
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.world
+        _check(self._lib.ferric_cuda_tp_connect(self._h, blob), "tp_connect")
+
+    def connect_with_torch_distributed(self) -> None:
+        import torch.distributed as dist
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.export())
+        self.connect(handles)
+        dist.barrier()
+
+    def partial(self, kind: int) -> torch.Tensor:
+        """This rank's exchange buffer `kind` as a [rows, cols] f32 tensor: the ``out`` of the row-parallel matmul."""
+        if kind not in self._views:
+            ptr = self._lib.ferric_cuda_tp_partial(self._h, kind)
+            self._views[kind] = torch.as_tensor(_DevView(ptr, (self.rows, self.cols)),
+                                                device=torch.device("cuda", self.ctx.device))
+        return self._views[kind]
+
+    def signal(self, kind: int) -> None:
+        _check(self._lib.ferric_cuda_tp_signal(self.ctx._h, self._h, kind), "tp_signal")
+
+    def add_rmsnorm_prepare(self, kind: int, qm: "QMatrix", a: torch.Tensor, weight: Optional[torch.Tensor] = None,
+                            eps: float = 1e-6, sum_out: Optional[torch.Tensor] = None,
+                            norm_out: Optional[torch.Tensor] = None) -> int:
+        """``qm.add_rmsnorm_prepare(a, b, ..)`` with b = the all-reduced exchange buffer `kind`."""
+        m = a.numel() // a.shape[-1]
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        _check(self._lib.ferric_cuda_tp_add_rmsnorm_prepare(self.ctx._h, self._h, kind, qm._h, a.data_ptr(), ptr(weight),
+                                                            float(eps), m, ptr(sum_out), ptr(norm_out)),
+               "tp_add_rmsnorm_prepare")
+        return m
+
+    def check(self) -> None:
+        """Synchronise and raise if a wait on a peer ran out."""
+        t = C.c_int32(0)
+        _check(self._lib.ferric_cuda_tp_status(self.ctx._h, self._h, C.byref(t)), "tp_status")
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._views = {}
+            self._lib.ferric_cuda_tp_free(self._h)
+            self._h = None

@@ -20,7 +20,7 @@ from typing import Callable, List, Optional
 import torch
 
 from . import synth
-from .ops import Context, QMatrix, GGML_Q4_K, GGML_Q6_K
+from .ops import Context, QMatrix, TPGroup, GGML_Q4_K, GGML_Q6_K
 
 
 def split_blocks(total_blocks: int, world: int) -> List[int]:
@@ -82,11 +82,14 @@ class DecodeStack:
     """``n_layers`` decoder layers' worth of packed-quant matmuls for ``batch`` tokens per step."""
 
     def __init__(self, ctx: Context, plan: TPPlan, n_layers: int = 64, batch: int = 1, eps: float = 1e-6,
-                 all_reduce: Optional[AllReduce] = None):
+                 all_reduce: Optional[AllReduce] = None, group: Optional[TPGroup] = None):
+        """`all_reduce`: a callable summing a tensor over ranks in place (e.g. NCCL through torch.distributed).
+        `group`: a connected TPGroup -- then the exchange is done by this library's own kernels instead."""
         self.ctx, self.plan, self.n_layers, self.batch, self.eps = ctx, plan, n_layers, batch, eps
-        self.all_reduce = all_reduce if plan.world > 1 else None
-        if plan.world > 1 and all_reduce is None:
-            raise ValueError("a tensor-parallel stack needs an all-reduce")
+        self.all_reduce = all_reduce if (plan.world > 1 and group is None) else None
+        self.group = group if plan.world > 1 else None
+        if plan.world > 1 and all_reduce is None and group is None:
+            raise ValueError("a tensor-parallel stack needs an all-reduce or an exchange group")
         self.layers: List[Layer] = []
         dev = torch.device("cuda", ctx.device)
         p, B = plan, batch
@@ -94,9 +97,12 @@ class DecodeStack:
         self.h = torch.zeros((B, p.hidden), **f32)
         self.xn = torch.empty((B, p.hidden), **f32)
         self.qkv = torch.empty((B, p.q_rows + 2 * p.kv_rows), **f32)
-        self.o = torch.empty((B, p.hidden), **f32)
         self.f = torch.empty((B, p.ff_rows), **f32)
-        self.d = torch.empty((B, p.hidden), **f32)
+        if self.group is not None:      # the row-parallel products write straight into the exchange buffers
+            self.o, self.d = self.group.partial(0), self.group.partial(1)
+        else:
+            self.o = torch.empty((B, p.hidden), **f32)
+            self.d = torch.empty((B, p.hidden), **f32)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_step = 0
 
@@ -146,20 +152,28 @@ class DecodeStack:
         before = c.launches()
         n = len(self.layers)
         m = self.layers[0].wqkv.add_rmsnorm_prepare(self.h, None, None, self.eps)
+        G = self.group
         for i, L in enumerate(self.layers):
             L.wqkv.matmul_prepared(m, out=self.qkv)
             L.wo.matmul(self.qkv[:, :p.q_rows], out=self.o)          # mixer pass-through: q feeds o
-            if self.all_reduce:
-                self.all_reduce(self.o)
-            L.wgu.add_rmsnorm_prepare(self.h, self.o, None, self.eps, sum_out=self.h)
+            if G is not None:
+                G.signal(0)
+                G.add_rmsnorm_prepare(0, L.wgu, self.h, None, self.eps, sum_out=self.h)
+            else:
+                if self.all_reduce:
+                    self.all_reduce(self.o)
+                L.wgu.add_rmsnorm_prepare(self.h, self.o, None, self.eps, sum_out=self.h)
             L.wgu.matmul_prepared(m, out=self.f, swiglu=True)
             L.wdown.matmul(self.f, out=self.d)
-            if self.all_reduce:
-                self.all_reduce(self.d)
-            if i + 1 < n:
-                self.layers[i + 1].wqkv.add_rmsnorm_prepare(self.h, self.d, None, self.eps, sum_out=self.h)
+            nxt = self.layers[i + 1].wqkv if i + 1 < n else self.layers[0].wqkv
+            last_norm = self.xn if i + 1 == n else None      # after the last layer the norm itself is the result
+            if G is not None:
+                G.signal(1)
+                G.add_rmsnorm_prepare(1, nxt, self.h, None, self.eps, sum_out=self.h, norm_out=last_norm)
             else:
-                c.add_rmsnorm(self.h, self.d, None, self.eps, self.h, self.xn)
+                if self.all_reduce:
+                    self.all_reduce(self.d)
+                nxt.add_rmsnorm_prepare(self.h, self.d, None, self.eps, sum_out=self.h, norm_out=last_norm)
         self.launches_per_step = c.launches() - before
         return self.h
 

@@ -223,6 +223,33 @@ int32_t ferric_cuda_dequant_f32(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, 
  * (crates/ferric-tensor/src/dtype.rs:4159-4163): out[rows * cols] uint16 bf16 bits. */
 int32_t ferric_cuda_dequant_bf16(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, uint16_t *out_dev);
 
+/* ---- tensor-parallel exchange (one process per GPU) ------------------------------------- */
+/* The reference shards a QMatrix by rows and concatenates (crates/ferric-tensor/src/dtype.rs:893-908,
+ * :935-944) and moves activations between devices through host buffers
+ * (crates/ferric-tensor/src/sched.rs:209-265); it has no reduction across devices.  Sharding the
+ * o / down projections along K needs one: the f32 [m, hidden] partial sums of all ranks are added.
+ * These entry points do that with the library's own kernels over CUDA-IPC peer memory. */
+typedef struct ferric_tp_group ferric_tp_group;
+
+/* Allocate this rank's two exchange buffers of `elems` floats (kind 0 and 1) plus flags. */
+int32_t ferric_cuda_tp_create(ferric_cuda_ctx *ctx, int32_t rank, int32_t world, size_t elems, ferric_tp_group **out);
+/* 64-byte CUDA IPC handle of this rank's exchange memory, to be sent to every peer by the host. */
+int32_t ferric_cuda_tp_export(ferric_tp_group *g, uint8_t *handle64);
+/* Map the peers' exchange memory: `handles` holds world x 64 bytes in rank order. */
+int32_t ferric_cuda_tp_connect(ferric_tp_group *g, const uint8_t *handles);
+/* Device address of this rank's exchange buffer `kind`: pass it as y_dev of the row-parallel matmul. */
+void *ferric_cuda_tp_partial(ferric_tp_group *g, int32_t kind);
+/* Announce to all peers that exchange buffer `kind` holds this rank's next partial (stream-ordered). */
+int32_t ferric_cuda_tp_signal(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t kind);
+/* ferric_cuda_add_rmsnorm_prepare with b = the sum over all ranks of exchange buffer `kind`
+ * (waits, bounded, for every rank's announcement; sums in rank order, identically on every rank). */
+int32_t ferric_cuda_tp_add_rmsnorm_prepare(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t kind,
+                                           const ferric_qmatrix *qm, const float *a_dev, const float *weight_dev,
+                                           float eps, size_t m, float *sum_dev, float *norm_dev);
+/* Synchronise the context and report whether any wait on a peer ran out (FERRIC_ERR_TIMEOUT). */
+int32_t ferric_cuda_tp_status(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t *timed_out);
+void ferric_cuda_tp_free(ferric_tp_group *g);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,64 @@
+"""Worker for the 2-GPU tensor-parallel test: one process per GPU, launched by test_gpu_tp.py."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+HID, NFF, QOUT, KV, LAYERS, B = 1024, 1536, 1024, 512, 3, 2
+
+
+def main(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import ferric_b200 as F
+    from ferric_b200.stack import DecodeStack, TPPlan, layer_shards
+    from test_tp_gloo import full_layer  # same synthetic layers as the CPU test (sizes overridden below)
+    import test_tp_gloo as T
+    T.HID, T.NFF, T.QOUT, T.KV = HID, NFF, QOUT, KV
+
+    ctx = F.Context(rank)
+    plan = TPPlan.make(world, rank, HID, NFF, QOUT, KV)
+    results = {}
+    for mode in ("nccl", "fused"):
+        group = None
+        if mode == "fused":
+            group = F.TPGroup(ctx, rank, world, B, HID)
+            group.connect_with_torch_distributed()
+        st = DecodeStack(ctx, plan, n_layers=LAYERS, batch=B,
+                         all_reduce=(lambda t: dist.all_reduce(t)) if mode == "nccl" else None, group=group)
+        for l in range(LAYERS):
+            sh = layer_shards(plan, full_layer(100 + 10 * l))
+            st.add_layer(F.QMatrix.from_bytes(ctx, sh["qkv"], 12, plan.q_rows + 2 * plan.kv_rows, HID),
+                         F.QMatrix.from_bytes(ctx, sh["o"], 12, HID, plan.q_rows),
+                         F.QMatrix.from_bytes(ctx, sh["gate_up"], 12, 2 * plan.ff_rows, HID),
+                         F.QMatrix.from_bytes(ctx, sh["down"], 14, HID, plan.ff_rows))
+        st.reserve()
+        from ferric_b200 import synth
+        h0 = torch.from_numpy(synth.activations(B, HID, seed=5)).cuda()
+        st.h.copy_(h0)
+        eager = st.step().clone()
+        st.capture()
+        st.h.copy_(h0)
+        replay = st.run().clone()
+        torch.cuda.synchronize()
+        if group is not None:
+            group.check()
+        results[mode] = (eager.cpu().numpy(), replay.cpu().numpy())
+        st.close()
+        dist.barrier()
+    if rank == 0:
+        np.savez(out, nccl=results["nccl"][0], nccl_replay=results["nccl"][1], fused=results["fused"][0],
+                 fused_replay=results["fused"][1])
+    dist.barrier()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main(int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), sys.argv[4])
