@@ -56,6 +56,8 @@ SIGNATURES = {
     "ferric_cuda_add_rmsnorm": (_I32, [_P, _P, _P, _P, C.c_float, _SZ, _SZ, _P, _P]),
     "ferric_cuda_add_rmsnorm_prepare": (_I32, [_P, _P, _P, _P, _P, C.c_float, _SZ, _P, _P]),
     "ferric_cuda_matmul_q_noalloc": (_I32, [_P, _P, _P, _SZ, _SZ, _P]),
+    "ferric_cuda_matmul_q_bf16": (_I32, [_P, _P, _P, _SZ, _SZ, _P]),
+    "ferric_cuda_gemm_status": (_I32, [_P, C.POINTER(_I32)]),
     "ferric_cuda_matmul_q_host": (_I32, [_P, _P, _P, _SZ, _SZ, _P]),
     "ferric_cuda_matmul_q_swiglu": (_I32, [_P, _P, _P, _SZ, _SZ, _P]),
     "ferric_cuda_swiglu": (_I32, [_P, _P, _SZ, _SZ, _P]),

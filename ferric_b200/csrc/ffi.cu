@@ -440,6 +440,42 @@ int32_t ferric_cuda_matmul_q(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, con
     return run_matmul(ctx, qm, x_dev, m, 0, y_dev, 0, kEpiStore);
 }
 
+int32_t ferric_cuda_matmul_q_bf16(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const uint16_t* x_bf16_dev, size_t m,
+                                  size_t x_cols, float* y_dev)
+{
+    int32_t rc = check_matmul_args(ctx, qm, x_bf16_dev, m, x_cols, y_dev);
+    if (rc != kOk) return rc;
+    if (qm->ty != kGgmlQ4K) {
+        set_last_error("the bf16 tensor-core product is built for Q4_K (ggml type 12) only, matrix is type %u", qm->ty);
+        return kUnsupported;
+    }
+    if (m > (size_t)INT32_MAX || qm->w.rows > (size_t)INT32_MAX) {
+        set_last_error("matrix or batch too large");
+        return kErrShape;
+    }
+    DeviceGuard guard(ctx->device);
+    ctx->launches++;
+    return launch_gemm_q4k_bf16(ctx->stream, qm->w, x_bf16_dev, m, qm->w.cols, y_dev, qm->w.rows);
+}
+
+int32_t ferric_cuda_gemm_status(ferric_cuda_ctx* ctx, int32_t* code)
+{
+    if (!ctx || !code) {
+        set_last_error("NULL argument");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    int v = 0;
+    int32_t rc = gemm_status(ctx->stream, &v);
+    if (rc != kOk) return rc;
+    *code = v;
+    if (v) {
+        set_last_error("a tensor-core GEMM block gave up waiting (role code %d)", v);
+        return kErrTimeout;
+    }
+    return kOk;
+}
+
 int32_t ferric_cuda_matmul_q_swiglu(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_dev, size_t m,
                                     size_t x_cols, float* y_dev)
 {

@@ -1,0 +1,435 @@
+// Prefill (M >= 128) Q4_K x bf16 GEMM on the 5th-generation tensor cores: tcgen05.mma with the
+// accumulator in tensor memory.
+//
+// Replaces Tensor::matmul_q4_k_coop (crates/ferric-tensor/src/dtype.rs:1818-1834, kernel :2059-2096):
+// there a workgroup dequantises an 8x8 weight tile into shared memory and feeds 8x8x8 f32
+// cooperative-matrix ops (Metal only; "exactly 1.0x" on NVIDIA, crates/ferric-core/src/lib.rs:90-100).
+// Here a CTA owns 128 weight rows x up to 256 activation rows:
+//   * warp 0 (one lane)  producer: bulk-copies the raw quant units of the next super-block and TMA-loads
+//                        the activation tile (bf16 [N, 64] boxes, 128-byte swizzle) for each 64-wide K chunk;
+//   * warps 2..9         dequantise: each warp owns one 16-row unit, each thread 32 weights per K chunk, into bf16
+//                        with the reference decoder's exact arithmetic (d*sc, dmin*m, d1*q - mm, round to
+//                        nearest even) and stores it into the K-major, 128-byte-swizzled A tile;
+//   * warp 1 (one lane)  issues tcgen05.mma (M 128, N = tile, K 16, bf16 -> f32 in TMEM), four per chunk,
+//                        and commits to mbarriers that free the A / B stages;
+//   * warps 2..5         epilogue: tcgen05.ld the accumulator (lane = weight row, column = activation row)
+//                        and store y[activation row][weight row], coalesced along weight rows.
+// Every wait on an mbarrier is bounded: on expiry the thread records an error code and the CTA drains.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ferric {
+
+constexpr int kGemmRows = 128;        // weight rows per CTA (UMMA M)
+constexpr int kGemmChunkK = 64;       // K per pipeline stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kGemmStages = 3;        // A / B stages in flight
+constexpr int kGemmRawStages = 2;     // raw quant super-blocks in flight
+constexpr int kGemmThreads = 320;     // producer warp, MMA warp, 8 dequant warps
+constexpr int kGemmRawBytes = 8 * kQ4KUnit;                   // 18432: 8 row tiles x one super-block
+constexpr int kGemmABytes = kGemmRows * 128;                  // 16384 per stage
+constexpr unsigned long long kGemmWaitNs = 1000000000ull;     // every mbarrier wait gives up after one second
+
+__host__ __device__ constexpr int gemm_b_bytes(int n_tile) { return n_tile * 128; }
+__host__ __device__ constexpr int gemm_smem_bytes(int n_tile)
+{
+    return 1024 /*align*/ + kGemmStages * (kGemmABytes + gemm_b_bytes(n_tile)) + kGemmRawStages * kGemmRawBytes + 256 /*barriers*/;
+}
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false if it did not complete within kGemmWaitNs.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+{
+    const uint32_t a = smem_u32(bar);
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((i & 255u) == 255u) {
+            uint64_t now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kGemmWaitNs) return false;
+        }
+    }
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                           // leading-dimension offset: unused with a swizzle, kept at 1
+    d |= (uint64_t)(1024 >> 4) << 32;                 // stride between 8-row groups
+    d |= (uint64_t)1 << 46;                           // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                           // SWIZZLE_128B
+    return d;
+}
+// kind::f16, bf16 x bf16 -> f32, both operands K-major.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n)
+{
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// ---------------------------------------------------------------- the kernel
+struct GemmBarriers {
+    uint64_t raw_full[kGemmRawStages], raw_empty[kGemmRawStages];
+    uint64_t a_full[kGemmStages], b_full[kGemmStages], stage_empty[kGemmStages];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    int abort;
+};
+
+// 6-bit (scale, min) of sub-block j from the 12 packed bytes (crates/ferric-gguf/src/lib.rs:795-804); the raw
+// block's first 16 bytes sit in `hdr` (x = d | dmin << 16, y..w = the 12 bytes).
+__device__ __forceinline__ uint32_t q4k_hdr_byte(const uint4& hdr, int i)
+{
+    const uint32_t w = i < 4 ? hdr.y : (i < 8 ? hdr.z : hdr.w);
+    return (w >> (8 * (i & 3))) & 0xffu;
+}
+__device__ __forceinline__ void q4k_scale_min(const uint4& hdr, int j, uint32_t& sc, uint32_t& mn)
+{
+    if (j < 4) {
+        sc = q4k_hdr_byte(hdr, j) & 63u;
+        mn = q4k_hdr_byte(hdr, j + 4) & 63u;
+    } else {
+        sc = (q4k_hdr_byte(hdr, j + 4) & 0x0Fu) | ((q4k_hdr_byte(hdr, j - 4) >> 6) << 4);
+        mn = (q4k_hdr_byte(hdr, j + 4) >> 4) | ((q4k_hdr_byte(hdr, j) >> 6) << 4);
+    }
+}
+// Eight weights (nibbles at bit `shift` of the eight bytes in w0, w1) -> bf16, exactly as the reference decoder
+// computes them in f32 (d1 * q - mm, lib.rs:813-822) and then rounds to nearest even.  d1 * q is exact in f32
+// (<= 21 significant bits), so the fused multiply-add rounds once, like the separate multiply and subtract.
+__device__ __forceinline__ uint4 deq8(uint32_t w0, uint32_t w1, int shift, float d1, float mm)
+{
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        // 0x4B000000 | q is the float 2^23 + q; subtracting 2^23 is exact
+        const float q0 = __uint_as_float(0x4B000000u | ((w0 >> (8 * e + shift)) & 0xFu)) - 8388608.f;
+        const float q1 = __uint_as_float(0x4B000000u | ((w1 >> (8 * e + shift)) & 0xFu)) - 8388608.f;
+        v[e] = __fmaf_rn(d1, q0, -mm);
+        v[4 + e] = __fmaf_rn(d1, q1, -mm);
+    }
+    const __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+    const __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+    uint4 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&p0);
+    o.y = *reinterpret_cast<const uint32_t*>(&p1);
+    o.z = *reinterpret_cast<const uint32_t*>(&p2);
+    o.w = *reinterpret_cast<const uint32_t*>(&p3);
+    return o;
+}
+
+template <int N_TILE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap, float* __restrict__ y,
+                     int rows, int nblk, int m, size_t ldy, int row_tiles16, int* __restrict__ err)
+{
+    extern __shared__ uint8_t gemm_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* a_stage = smem;                                               // [S][16384]
+    uint8_t* b_stage = a_stage + kGemmStages * kGemmABytes;                // [S][N_TILE * 128]
+    uint8_t* raw_stage = b_stage + kGemmStages * gemm_b_bytes(N_TILE);     // [2][18432]
+    GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(raw_stage + kGemmRawStages * kGemmRawBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.x * kGemmRows, n0 = blockIdx.y * N_TILE;
+    const int rt0 = blockIdx.x * 8;                                        // first 16-row tile of this CTA
+    const int tiles_here = min(8, row_tiles16 - rt0);
+    const int nchunks = nblk * 4;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kGemmRawStages; i++) {
+            mbar_init(&bar->raw_full[i], 1);
+            mbar_init(&bar->raw_empty[i], 8);
+        }
+        for (int i = 0; i < kGemmStages; i++) {
+            mbar_init(&bar->a_full[i], 8);
+            mbar_init(&bar->b_full[i], 1);
+            mbar_init(&bar->stage_empty[i], 1);
+        }
+        mbar_init(&bar->acc_full, 1);
+        bar->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // tensor memory for the 128 x N_TILE f32 accumulator
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)), "n"(N_TILE)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = bar->tmem_base;
+    int fail = 0;
+
+    if (warp == 0) {
+        // ---------------- producer
+        if (lane == 0) {
+            auto load_raw = [&](int b) -> bool {
+                const int rs = b % kGemmRawStages;
+                if (!mbar_wait(&bar->raw_empty[rs], (((uint32_t)b / kGemmRawStages) & 1u) ^ 1u)) return false;
+                mbar_expect_tx(&bar->raw_full[rs], (uint32_t)(tiles_here * kQ4KUnit));
+                for (int t = 0; t < tiles_here; t++)
+                    bulk_g2s(raw_stage + rs * kGemmRawBytes + t * kQ4KUnit, units + ((size_t)(rt0 + t) * nblk + b) * kQ4KUnit,
+                             kQ4KUnit, &bar->raw_full[rs]);
+                return true;
+            };
+            if (!load_raw(0)) fail = 1;
+            for (int b = 0; b < nblk && !fail; b++) {
+                if (b + 1 < nblk && !load_raw(b + 1)) { fail = 1; break; }
+                for (int j = 0; j < 4; j++) {
+                    const int c = 4 * b + j, s = c % kGemmStages;
+                    if (!mbar_wait(&bar->stage_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 2; break; }
+                    mbar_expect_tx(&bar->b_full[s], (uint32_t)gemm_b_bytes(N_TILE));
+                    tma_load_2d(b_stage + s * gemm_b_bytes(N_TILE), &xmap, c * kGemmChunkK, n0, &bar->b_full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(kGemmRows, N_TILE);
+            for (int c = 0; c < nchunks; c++) {
+                const int s = c % kGemmStages;
+                const uint32_t ph = ((uint32_t)c / kGemmStages) & 1u;
+                if (!mbar_wait(&bar->a_full[s], ph) || !mbar_wait(&bar->b_full[s], ph)) { fail = 3; break; }
+                tc_fence_after();
+                const uint32_t a0 = smem_u32(a_stage + s * kGemmABytes), b0 = smem_u32(b_stage + s * gemm_b_bytes(N_TILE));
+#pragma unroll
+                for (int k4 = 0; k4 < 4; k4++)
+                    umma_bf16(tmem_acc, umma_desc_sw128(a0 + 32 * k4), umma_desc_sw128(b0 + 32 * k4), idesc, (c | k4) ? 1u : 0u);
+                umma_commit(&bar->stage_empty[s]);   // frees this A / B stage once the MMAs above have read it
+            }
+            if (!fail) umma_commit(&bar->acc_full);
+        }
+    } else {
+        // ---------------- dequantise: warp = one 16-row unit, lane = (row g / g+8, 8-byte piece t)
+        // The lane -> (g, t) map keeps both the 16-byte loads of the raw unit and the 16-byte stores into the
+        // swizzled A tile free of bank conflicts: the two rows of a quarter-warp differ in bits 0 and 2.
+        const int wd = warp - 2, t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
+        const bool unit_ok = wd < tiles_here;
+        for (int b = 0; b < nblk && !fail; b++) {
+            const int rs = b % kGemmRawStages;
+            if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)b / kGemmRawStages) & 1u)) { fail = 4; break; }
+            const uint8_t* u = raw_stage + rs * kGemmRawBytes + wd * kQ4KUnit;
+            uint4 hdr[2], qs[2][2];
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                hdr[hi] = make_uint4(0, 0, 0, 0);
+                qs[hi][0] = qs[hi][1] = make_uint4(0, 0, 0, 0);
+                if (unit_ok) {
+                    hdr[hi] = *reinterpret_cast<const uint4*>(u + 16 * (g + 8 * hi));
+                    qs[hi][0] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi) + 16 * (4 * g + t));
+                    qs[hi][1] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi + 1) + 16 * (4 * g + t));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar->raw_empty[rs]);   // the block now lives in registers
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int c = 4 * b + j, s = c % kGemmStages;
+                if (!mbar_wait(&bar->stage_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
+#pragma unroll
+                for (int hi = 0; hi < 2; hi++) {
+                    const float d = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x & 0xffffu)));
+                    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x >> 16)));
+                    uint32_t sc0, mn0, sc1, mn1;
+                    q4k_scale_min(hdr[hi], 2 * j, sc0, mn0);
+                    q4k_scale_min(hdr[hi], 2 * j + 1, sc1, mn1);
+                    const float d1a = __fmul_rn(d, (float)sc0), mma = __fmul_rn(dmin, (float)mn0);
+                    const float d1b = __fmul_rn(d, (float)sc1), mmb = __fmul_rn(dmin, (float)mn1);
+                    const uint4 q4 = qs[hi][j >> 1];
+                    const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
+                    const int r = 16 * wd + 8 * hi + g;
+                    uint8_t* arow = a_stage + s * kGemmABytes + (r >> 3) * 1024 + (r & 7) * 128;
+                    *reinterpret_cast<uint4*>(arow + ((t ^ (r & 7)) << 4)) = deq8(w0, w1, 0, d1a, mma);
+                    *reinterpret_cast<uint4*>(arow + (((4 + t) ^ (r & 7)) << 4)) = deq8(w0, w1, 4, d1b, mmb);
+                }
+                fence_proxy_async();     // generic-proxy stores -> visible to the tensor core's async reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar->a_full[s]);
+            }
+        }
+        // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +32
+        if (warp < 6 && !fail) {
+            if (!mbar_wait(&bar->acc_full, 0)) {
+                fail = 6;
+            } else {
+                tc_fence_after();
+                const int q = warp & 3, wrow = row0 + 32 * q + lane;
+#pragma unroll 1
+                for (int c0 = 0; c0 < N_TILE; c0 += 32) {
+                    uint32_t v[32];
+                    const uint32_t taddr = tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)c0;
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (wrow < rows) {
+#pragma unroll
+                        for (int jj = 0; jj < 32; jj++) {
+                            const int batch = n0 + c0 + jj;
+                            if (batch < m) y[(size_t)batch * ldy + wrow] = __uint_as_float(v[jj]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (fail) {
+        atomicExch(&bar->abort, fail);
+        if (err) atomicExch(err, fail);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (bar->abort) {
+        // something never arrived: give copies still in flight time to land before the CTA's memory goes away
+        for (int i = 0; i < 200; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "n"(N_TILE) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+// Set by a CTA whose bounded wait ran out (the code says which role gave up); read by gemm_status().
+static __device__ int g_gemm_status = 0;
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+template <int N_TILE>
+int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, size_t m, float* y, size_t ldy)
+{
+    static bool attr_done[64] = {};
+    int dev = 0;
+    FERRIC_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_done[dev]) {
+        FERRIC_CUDA_TRY(cudaFuncSetAttribute(gemm_q4k_bf16_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             gemm_smem_bytes(N_TILE)));
+        attr_done[dev] = true;
+    }
+    int* err = nullptr;
+    FERRIC_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_gemm_status));
+    dim3 grid((unsigned)((w.rows + kGemmRows - 1) / kGemmRows), (unsigned)((m + N_TILE - 1) / N_TILE));
+    gemm_q4k_bf16_kernel<N_TILE><<<grid, kGemmThreads, gemm_smem_bytes(N_TILE), st>>>(
+        w.units, map, y, (int)w.rows, (int)w.nblk, (int)m, ldy, (int)w.row_tiles(), err);
+    FERRIC_CUDA_TRY(cudaGetLastError());
+    return kOk;
+}
+}  // namespace
+
+int32_t launch_gemm_q4k_bf16(cudaStream_t st, const DeviceWeights& w, const uint16_t* x_bf16, size_t m, size_t ldx, float* y,
+                             size_t ldy)
+{
+    if (m == 0 || w.rows == 0 || w.nblk == 0) return kOk;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (ldx * 2) % 16 != 0) {
+        set_last_error("bf16 activations must be 16-byte aligned with a row stride that is a multiple of 8 elements");
+        return kErrInvalidArg;
+    }
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) {
+        set_last_error("the CUDA driver does not export cuTensorMapEncodeTiled");
+        return kErrCuda;
+    }
+    const int n_tile = m <= 128 ? 128 : 256;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)w.cols, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kGemmChunkK, (cuuint32_t)n_tile};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(x_bf16), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled failed with code %d", (int)r);
+        return kErrCuda;
+    }
+    return n_tile == 128 ? launch_gemm_tile<128>(st, w, map, m, y, ldy) : launch_gemm_tile<256>(st, w, map, m, y, ldy);
+}
+
+// Synchronises the stream, returns the code of the first bounded wait that ran out (0 = none) and clears it.
+int32_t gemm_status(cudaStream_t st, int* code)
+{
+    FERRIC_CUDA_TRY(cudaStreamSynchronize(st));
+    int v = 0, zero = 0;
+    FERRIC_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)));
+    if (v) FERRIC_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)));
+    *code = v;
+    return kOk;
+}
+
+}  // namespace ferric

@@ -241,6 +241,24 @@ class QMatrix:
                                                       out.data_ptr()), "matmul_q_noalloc")
         return out
 
+    def matmul_bf16(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Prefill product on the tensor cores: ``x`` [m, cols] bfloat16, result [m, rows] float32 with the
+        weights rounded to bf16 (``Tensor::matmul_q4_k_coop``, ferric-tensor/src/dtype.rs:1818-1834).  Q4_K only."""
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()):
+            raise TypeError("matmul_bf16 needs a contiguous 2-D bfloat16 CUDA tensor")
+        m = x.shape[0]
+        if out is None:
+            out = torch.empty((m, self.rows()), dtype=torch.float32, device=x.device)
+        _check(self._lib.ferric_cuda_matmul_q_bf16(self.ctx._h, self._h, x.data_ptr(), m, x.shape[1], out.data_ptr()),
+               "matmul_q_bf16")
+        return out
+
+    def gemm_status(self) -> int:
+        """Synchronise and return the tensor-core kernel's give-up code (0 = every wait completed); raises on non-zero."""
+        code = C.c_int32(0)
+        _check(self._lib.ferric_cuda_gemm_status(self.ctx._h, C.byref(code)), "gemm_status")
+        return code.value
+
     def prepare(self, x: torch.Tensor) -> int:
         """First half of ``matmul``: convert x into the context's activation scratch; returns m."""
         x = self._x2d(x, allow_row_stride=True)

@@ -199,6 +199,22 @@ int32_t ferric_cuda_add_rmsnorm_prepare(ferric_cuda_ctx *ctx, const ferric_qmatr
 int32_t ferric_cuda_matmul_q_noalloc(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t m,
                                      size_t x_cols, float *y_dev);
 
+/* Prefill product on the tensor cores: y[m, rows] (f32) = x . W^T with bf16 activations x[m, cols]
+ * (raw bf16 bits, 16-byte aligned) and the weights dequantised to bf16, round to nearest even.
+ * Replaces the reference's cooperative-matrix prefill kernel Tensor::matmul_q4_k_coop
+ * (crates/ferric-tensor/src/dtype.rs:1818-1834, WGSL :2059-2096), which dequantises weight tiles
+ * into workgroup memory and multiplies them with 8x8x8 subgroup-matrix ops; here the tile is
+ * 128 weight rows x 256 activation rows x 64 and the multiply is tcgen05.mma with the f32
+ * accumulator in tensor memory.  Q4_K only (other types return FERRIC_UNSUPPORTED); any m >= 1
+ * works but the kernel is meant for m >= 128.  Asynchronous on the context's stream. */
+int32_t ferric_cuda_matmul_q_bf16(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const uint16_t *x_bf16_dev, size_t m,
+                                  size_t x_cols, float *y_dev);
+
+/* Every wait inside the tensor-core kernel is bounded.  This call synchronises the stream and
+ * reports (and clears) the code a block left if one of its waits ran out: *code 0 and FERRIC_OK
+ * when none did, FERRIC_ERR_TIMEOUT otherwise.  No counterpart in the reference. */
+int32_t ferric_cuda_gemm_status(ferric_cuda_ctx *ctx, int32_t *code);
+
 /* The same product with HOST activation and result buffers: copies x in, runs, copies y out and
  * returns when y is complete. */
 int32_t ferric_cuda_matmul_q_host(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_host, size_t m,

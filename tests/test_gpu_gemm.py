@@ -1,0 +1,113 @@
+"""GPU parity of the tensor-core prefill product (Q4_K weights x bf16 activations).
+
+The reference product for this configuration is: weights dequantised with the reference decoder and
+rounded to bf16 (nearest even), activations bf16, f32 accumulation.  The tensor core sums in a
+different order, so the comparison is done twice: against the oracle's sequential f32 sum
+(1e-3 relative + 1e-4 absolute, widened by that sum's own distance from the exact value) and
+against the exact float64 product of the same bf16 operands.
+"""
+import numpy as np
+import pytest
+import torch
+
+from ferric_b200 import synth
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-3, 1e-4
+
+
+@pytest.fixture(scope="module")
+def F():
+    import ferric_b200
+    return ferric_b200
+
+
+@pytest.fixture(scope="module")
+def ctx(F):
+    c = F.Context(0)
+    yield c
+    c.close()
+
+
+def bf16_to_f64(bits):
+    return (np.asarray(bits, dtype=np.uint32) << 16).view(np.float32).astype(np.float64)
+
+
+def make_case(rows, cols, m, seed):
+    rng = np.random.default_rng(seed)
+    raw = synth.q4k_blocks(rng, rows * cols // 256)
+    x = torch.from_numpy(rng.standard_normal((m, cols), dtype=np.float32)).to(torch.bfloat16)
+    xbits = x.view(torch.int16).numpy().view(np.uint16)
+    return raw, x, xbits
+
+
+def exact_bf16_product(raw, rows, cols, xbits):
+    w = bf16_to_f64(O.deq_raw_bf16(raw, rows * cols, 12)).reshape(rows, cols)
+    return bf16_to_f64(xbits) @ w.T
+
+
+def check(F, ctx, rows, cols, m, seed, oracle_rows=None):
+    raw, x, xbits = make_case(rows, cols, m, seed)
+    qm = F.QMatrix.from_bytes(ctx, raw, 12, rows, cols)
+    y = qm.matmul_bf16(x.cuda())
+    assert qm.gemm_status() == 0
+    got = y.cpu().numpy().astype(np.float64)
+    exact = exact_bf16_product(raw, rows, cols, xbits)
+    e = np.abs(got - exact)
+    tol = ATOL + RTOL * np.abs(exact)
+    w = int(np.argmax(e / tol))
+    assert (e <= tol).all(), f"vs exact: worst |d|={e.flat[w]:.3e} at {np.unravel_index(w, e.shape)} (exact {exact.flat[w]:.6g})"
+    # the oracle's own sequential f32 sum on a slice of the batch (it is a scalar loop)
+    mo = min(m, oracle_rows or m)
+    ref = O.matmul_q(raw, 12, rows, cols, xbits[:mo], threads=8, mode=O.MODE_BF16).astype(np.float64)
+    e = np.abs(got[:mo] - ref)
+    tol = ATOL + RTOL * np.abs(ref) + np.abs(ref - exact[:mo])
+    assert (e <= tol).all(), f"vs oracle: worst ratio {(e / tol).max():.3f}"
+    qm.close()
+    return float(np.abs(got - exact).max() / np.abs(exact).max())
+
+
+@pytest.mark.parametrize("rows,cols,m", [
+    (128, 256, 128),      # one CTA, one super-block
+    (128, 1024, 128),     # pipeline wraps around its stages
+    (256, 512, 256),      # N tile 256
+    (144, 768, 40),       # ragged: rows not a multiple of 128, batch below one tile
+    (16, 256, 1),         # smallest legal matrix
+    (1000, 2048, 300),    # ragged rows and two N tiles with a partial one
+])
+def test_small_shapes(F, ctx, rows, cols, m):
+    rel = check(F, ctx, rows, cols, m, seed=rows + cols + m)
+    assert rel < 1e-5, rel   # the reference's kernel-test bar, max|d| / max|ref| (examples/q4_k.rs:52-55)
+
+
+@pytest.mark.parametrize("m", [128, 512, 2048])
+def test_prefill_config(F, ctx, m):
+    """Prefill configuration: hidden 5120 -> 4096 rows (a q-projection slice), batch 128 / 512 / 2048."""
+    check(F, ctx, 4096, 5120, m, seed=m, oracle_rows=32)
+
+
+def test_dequant_stage_is_bit_exact(F, ctx):
+    """x = identity columns: y[i, r] is then exactly the bf16 weight W[r, i] -- the dequant-to-bf16 stage
+    inside the kernel must match the oracle's bf16 dequantisation bit for bit."""
+    rows, cols = 256, 256
+    rng = np.random.default_rng(7)
+    raw = synth.q4k_blocks(rng, rows * cols // 256)
+    qm = F.QMatrix.from_bytes(ctx, raw, 12, rows, cols)
+    x = torch.eye(cols, dtype=torch.bfloat16, device="cuda")
+    y = qm.matmul_bf16(x)
+    assert qm.gemm_status() == 0
+    got = y.cpu().numpy()                                  # [cols, rows]
+    want = (O.deq_raw_bf16(raw, rows * cols, 12).astype(np.uint32) << 16).view(np.float32).reshape(rows, cols)
+    assert np.array_equal(np.ascontiguousarray(got.T).view(np.uint32), want.view(np.uint32))
+    qm.close()
+
+
+def test_rejects_other_types(F, ctx):
+    rng = np.random.default_rng(1)
+    raw = synth.q6k_blocks(rng, 16)
+    qm = F.QMatrix.from_bytes(ctx, raw, 14, 16, 256)
+    with pytest.raises(F.FerricError):
+        qm.matmul_bf16(torch.zeros(4, 256, dtype=torch.bfloat16, device="cuda"))
+    qm.close()
