@@ -2,9 +2,17 @@
 
 The reference product for this configuration is: weights dequantised with the reference decoder and
 rounded to bf16 (nearest even), activations bf16, f32 accumulation.  The tensor core sums in a
-different order, so the comparison is done twice: against the oracle's sequential f32 sum
-(1e-3 relative + 1e-4 absolute, widened by that sum's own distance from the exact value) and
-against the exact float64 product of the same bf16 operands.
+different order, so the comparison is done twice: against the exact float64 product of the same bf16
+operands and against the oracle's sequential f32 sum (widened by that sum's own distance from the
+exact value).
+
+Tolerance: 1e-3 relative + 1e-4 absolute, plus the forward-error term of a dot product,
+u * sum_k |x_k w_k| with u = 2^-21.  The tensor core adds each 16-term group into the f32 accumulator
+with truncation, so a sum of K terms drifts by up to (K / 16) * 2^-23 of the running sum's magnitude;
+on elements where thousands of O(1) terms cancel to ~1e-2 that drift (measured 1.2e-4 at K = 2048) is
+above the bare absolute bar although it is 2e-6 of the row's scale.  u = 2^-21 is 8x tighter than the
+worst case at K = 2048.  The reference's own kernel tests use max|d| / max|ref| < 1e-5
+(crates/ferric-tensor/examples/q4_k.rs:52-55); that bar is asserted as well.
 """
 import numpy as np
 import pytest
@@ -15,7 +23,7 @@ from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
-RTOL, ATOL = 1e-3, 1e-4
+RTOL, ATOL, U_ACC = 1e-3, 1e-4, 2.0 ** -21
 
 
 @pytest.fixture(scope="module")
@@ -44,8 +52,10 @@ def make_case(rows, cols, m, seed):
 
 
 def exact_bf16_product(raw, rows, cols, xbits):
+    """(x . W^T, |x| . |W|^T) in float64 on the bf16 operands."""
     w = bf16_to_f64(O.deq_raw_bf16(raw, rows * cols, 12)).reshape(rows, cols)
-    return bf16_to_f64(xbits) @ w.T
+    x = bf16_to_f64(xbits)
+    return x @ w.T, np.abs(x) @ np.abs(w).T
 
 
 def check(F, ctx, rows, cols, m, seed, oracle_rows=None):
@@ -54,16 +64,16 @@ def check(F, ctx, rows, cols, m, seed, oracle_rows=None):
     y = qm.matmul_bf16(x.cuda())
     assert qm.gemm_status() == 0
     got = y.cpu().numpy().astype(np.float64)
-    exact = exact_bf16_product(raw, rows, cols, xbits)
+    exact, mag = exact_bf16_product(raw, rows, cols, xbits)
     e = np.abs(got - exact)
-    tol = ATOL + RTOL * np.abs(exact)
+    tol = ATOL + RTOL * np.abs(exact) + U_ACC * mag
     w = int(np.argmax(e / tol))
     assert (e <= tol).all(), f"vs exact: worst |d|={e.flat[w]:.3e} at {np.unravel_index(w, e.shape)} (exact {exact.flat[w]:.6g})"
     # the oracle's own sequential f32 sum on a slice of the batch (it is a scalar loop)
     mo = min(m, oracle_rows or m)
     ref = O.matmul_q(raw, 12, rows, cols, xbits[:mo], threads=8, mode=O.MODE_BF16).astype(np.float64)
     e = np.abs(got[:mo] - ref)
-    tol = ATOL + RTOL * np.abs(ref) + np.abs(ref - exact[:mo])
+    tol = ATOL + RTOL * np.abs(ref) + U_ACC * mag[:mo] + np.abs(ref - exact[:mo])
     assert (e <= tol).all(), f"vs oracle: worst ratio {(e / tol).max():.3f}"
     qm.close()
     return float(np.abs(got - exact).max() / np.abs(exact).max())
