@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch kernels directly instead of replaying a CUDA graph")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-matrix table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--prefill", type=int, default=0, metavar="M",
+                    help="time only the tensor-core prefill product (Q4_K x bf16, M activation rows) and print its line")
+    ap.add_argument("--prefill-rows", type=int, default=34816, help="weight rows of the --prefill matrix (x 5120 columns)")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="N > 1: the library's own peer-memory exchange (default) or NCCL through torch.distributed")
     return ap.parse_args()
@@ -293,6 +296,8 @@ def run_ours(args):
     extras = None
     if rank == 0 and world == 1 and not args.no_extras:
         extras = per_matrix_table(torch, ctx, stack, QMatrix, B, peak)
+        extras["prefill_q4k_bf16_34816x5120"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, stack.layers[0].wgu, m, 5)
+                                                 for m in (128, 512, 2048)}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -379,9 +384,63 @@ def per_matrix_table(torch, ctx, stack, QMatrix, B, peak):
     return out
 
 
+def bf16_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 1590.0, 1400.0, "fallback"
+
+
+def prefill_case(torch, ctx, QMatrix, w, m, reps):
+    """TFLOP/s of y[m, rows] = x[m, cols] . W^T on the tensor cores (weights dequantised to bf16 in the kernel).
+    x (bf16) and y (f32) are resident; the weights of one matrix (100 MB at full size) are re-read from L2/HBM."""
+    dev = torch.device("cuda", ctx.device)
+    x = torch.randn((m, w.cols()), device=dev).to(torch.bfloat16)
+    y = torch.empty((m, w.rows()), device=dev, dtype=torch.float32)
+    for _ in range(3):
+        w.matmul_bf16(x, out=y)
+    assert w.gemm_status() == 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        w.matmul_bf16(x, out=y)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    tf = 2.0 * m * w.rows() * w.cols() / us / 1e6
+    burst, sustained, kind = bf16_peaks()
+    return {"us": us, "TFLOP/s": tf, "frac_of_bf16_peak": tf / burst, "frac_of_sustained_bf16_peak": tf / sustained,
+            "peak_source": kind, "finite": bool(torch.isfinite(y).all().item())}
+
+
+def run_prefill(args):
+    """One line for the prefill configuration alone (also the command the tensor-pipe profile is taken with)."""
+    import torch
+    from ferric_b200 import Context, QMatrix, synth
+    torch.cuda.set_device(0)
+    ctx = Context(0)
+    rows, cols, m = args.prefill_rows, 5120, args.prefill
+    raw = synth.matrix_on_device(12, rows, cols, 1, torch.device("cuda:0"))
+    w = QMatrix.from_device_bytes(ctx, raw, 12, rows, cols)
+    with ClockSampler(0) as clocks:
+        r = prefill_case(torch, ctx, QMatrix, w, m, max(args.steps, 1))
+    burst, _, kind = bf16_peaks()
+    print(json.dumps({
+        "metric": "prefill_tflops", "value": r["TFLOP/s"], "unit": "TFLOP/s", "n_gpus": 1, "steps": max(args.steps, 1),
+        "warmup": 3, "ms_per_step": r["us"] / 1e3, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"Q4_K [{rows}x{cols}] x bf16 [{m}x{cols}] -> f32, weights dequantised in-kernel"},
+        "roofline": {"kernel": "gemm_q4k_bf16_kernel", "bound": "tensor", "achieved": r["TFLOP/s"], "peak": burst,
+                     "unit": "TFLOP/s", "frac": r["TFLOP/s"] / burst, "peak_source": kind, "traffic": None},
+        "gpu_launches": max(args.steps, 1), "clocks": clocks.summary(), "output_finite": r["finite"]}), flush=True)
+
+
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.prefill:
+        run_prefill(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

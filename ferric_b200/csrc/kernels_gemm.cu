@@ -4,15 +4,16 @@
 // Replaces Tensor::matmul_q4_k_coop (crates/ferric-tensor/src/dtype.rs:1818-1834, kernel :2059-2096):
 // there a workgroup dequantises an 8x8 weight tile into shared memory and feeds 8x8x8 f32
 // cooperative-matrix ops (Metal only; "exactly 1.0x" on NVIDIA, crates/ferric-core/src/lib.rs:90-100).
-// Here a CTA owns 128 weight rows x up to 256 activation rows:
-//   * warp 0 (one lane)  producer: bulk-copies the raw quant units of the next super-block and TMA-loads
-//                        the activation tile (bf16 [N, 64] boxes, 128-byte swizzle) for each 64-wide K chunk;
-//   * warps 2..9         dequantise: each warp owns one 16-row unit, each thread 32 weights per K chunk, into bf16
+// Here a CTA owns 128 weight rows x 128, 256 or 512 activation rows (512 = all of tensor memory):
+//   * warp 0 (one lane)  weight producer: bulk-copies the raw quant units of the next super-blocks;
+//   * warp 2 (one lane)  activation producer: TMA-loads the activation tile (bf16 [N, 64] boxes, 128-byte
+//                        swizzle) of each 64-wide K chunk, as many chunks ahead as shared memory holds;
+//   * warps 3..10        dequantise: each warp owns one 16-row unit, each thread 32 weights per K chunk, into bf16
 //                        with the reference decoder's exact arithmetic (d*sc, dmin*m, d1*q - mm, round to
 //                        nearest even) and stores it into the K-major, 128-byte-swizzled A tile;
-//   * warp 1 (one lane)  issues tcgen05.mma (M 128, N = tile, K 16, bf16 -> f32 in TMEM), four per chunk,
+//   * warp 1 (one lane)  issues tcgen05.mma (M 128, N <= 256, K 16, bf16 -> f32 in TMEM), four or eight per chunk,
 //                        and commits to mbarriers that free the A / B stages;
-//   * warps 2..5         epilogue: tcgen05.ld the accumulator (lane = weight row, column = activation row)
+//   * warps 3..6         epilogue: tcgen05.ld the accumulator (lane = weight row, column = activation row)
 //                        and store y[activation row][weight row], coalesced along weight rows.
 // Every wait on an mbarrier is bounded: on expiry the thread records an error code and the CTA drains.
 #include <cuda.h>
@@ -25,18 +26,38 @@ namespace ferric {
 
 constexpr int kGemmRows = 128;        // weight rows per CTA (UMMA M)
 constexpr int kGemmChunkK = 64;       // K per pipeline stage: 64 bf16 = one 128-byte swizzle row
-constexpr int kGemmStages = 3;        // A / B stages in flight
+constexpr int kGemmStages = 3;        // dequantised A stages in flight
 constexpr int kGemmRawStages = 2;     // raw quant super-blocks in flight
-constexpr int kGemmThreads = 320;     // producer warp, MMA warp, 8 dequant warps
+#ifndef FERRIC_GEMM_EXP
+#define FERRIC_GEMM_EXP 0
+#endif
+#ifndef FERRIC_GEMM_DEQ_WARPS
+#define FERRIC_GEMM_DEQ_WARPS 8
+#endif
+constexpr int kGemmDeqWarps = FERRIC_GEMM_DEQ_WARPS;   // 8: one per 16-row unit; 16: two per unit
+constexpr int kGemmHalves = 16 / kGemmDeqWarps;        // 8-row halves of a unit each dequant warp converts
+static_assert(kGemmDeqWarps == 8 || kGemmDeqWarps == 16, "one or two dequant warps per 16-row unit");
+constexpr int kGemmFirstDeqWarp = 3;                   // warp 0 weight producer, 1 MMA issuer, 2 activation producer
+constexpr int kGemmThreads = 32 * (kGemmFirstDeqWarp + kGemmDeqWarps);
 constexpr int kGemmRawBytes = 8 * kQ4KUnit;                   // 18432: 8 row tiles x one super-block
 constexpr int kGemmABytes = kGemmRows * 128;                  // 16384 per stage
 constexpr unsigned long long kGemmWaitNs = 1000000000ull;     // every mbarrier wait gives up after one second
 
 __host__ __device__ constexpr int gemm_b_bytes(int n_tile) { return n_tile * 128; }
-__host__ __device__ constexpr int gemm_smem_bytes(int n_tile)
+// Activation stages: as many as the shared memory left by the A ring and the raw ring holds, at most 8.  What
+// bounds the kernel at small N is bytes in flight (a stage's round trip through TMA and L2 is over a microsecond),
+// so the ring is as deep as it can be: 8 stages at N 128, 4 at 256, 2 at 512.
+constexpr int kGemmSmemMax = 232448;  // 227 KB per CTA
+constexpr int kGemmFixedBytes = 1024 /*align*/ + 256 /*barriers*/ + kGemmStages * kGemmABytes + kGemmRawStages * kGemmRawBytes;
+constexpr int kGemmMaxBStages = 8;
+__host__ __device__ constexpr int gemm_b_stages(int n_tile)
 {
-    return 1024 /*align*/ + kGemmStages * (kGemmABytes + gemm_b_bytes(n_tile)) + kGemmRawStages * kGemmRawBytes + 256 /*barriers*/;
+    return (kGemmSmemMax - kGemmFixedBytes) / gemm_b_bytes(n_tile) > kGemmMaxBStages
+               ? kGemmMaxBStages
+               : (kGemmSmemMax - kGemmFixedBytes) / gemm_b_bytes(n_tile);
 }
+__host__ __device__ constexpr int gemm_smem_bytes(int n_tile) { return kGemmFixedBytes + gemm_b_stages(n_tile) * gemm_b_bytes(n_tile); }
+static_assert(gemm_b_stages(128) == 8 && gemm_b_stages(256) == 4 && gemm_b_stages(512) == 2, "stage counts");
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -119,10 +140,25 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+#if FERRIC_GEMM_EXP == 9
+__device__ unsigned long long g_gemm_trace[128];
+__device__ __forceinline__ void trace(int slot)
+{
+    if (blockIdx.x == 0 && blockIdx.y == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        g_gemm_trace[slot] = now;
+    }
+}
+#define GEMM_TRACE(slot) trace(slot)
+#else
+#define GEMM_TRACE(slot)
+#endif
+
 // ---------------------------------------------------------------- the kernel
 struct GemmBarriers {
     uint64_t raw_full[kGemmRawStages], raw_empty[kGemmRawStages];
-    uint64_t a_full[kGemmStages], b_full[kGemmStages], stage_empty[kGemmStages];
+    uint64_t a_full[kGemmStages], a_empty[kGemmStages], b_full[kGemmMaxBStages], b_empty[kGemmMaxBStages];
     uint64_t acc_full;
     uint32_t tmem_base;
     int abort;
@@ -145,27 +181,60 @@ __device__ __forceinline__ void q4k_scale_min(const uint4& hdr, int j, uint32_t&
         mn = (q4k_hdr_byte(hdr, j + 4) >> 4) | ((q4k_hdr_byte(hdr, j) >> 6) << 4);
     }
 }
-// Eight weights (nibbles at bit `shift` of the eight bytes in w0, w1) -> bf16, exactly as the reference decoder
-// computes them in f32 (d1 * q - mm, lib.rs:813-822) and then rounds to nearest even.  d1 * q is exact in f32
-// (<= 21 significant bits), so the fused multiply-add rounds once, like the separate multiply and subtract.
-__device__ __forceinline__ uint4 deq8(uint32_t w0, uint32_t w1, int shift, float d1, float mm)
+// The same for a sub-block index known only at run time: the 12 bytes as three words, byte i by funnel shift.
+__device__ __forceinline__ uint32_t q4k_hdr_byte_dyn(const uint4& hdr, int i)
 {
-    float v[8];
-#pragma unroll
-    for (int e = 0; e < 4; e++) {
-        // 0x4B000000 | q is the float 2^23 + q; subtracting 2^23 is exact
-        const float q0 = __uint_as_float(0x4B000000u | ((w0 >> (8 * e + shift)) & 0xFu)) - 8388608.f;
-        const float q1 = __uint_as_float(0x4B000000u | ((w1 >> (8 * e + shift)) & 0xFu)) - 8388608.f;
-        v[e] = __fmaf_rn(d1, q0, -mm);
-        v[4 + e] = __fmaf_rn(d1, q1, -mm);
+    const uint32_t w = i < 4 ? hdr.y : (i < 8 ? hdr.z : hdr.w);
+    return (w >> (8 * (i & 3))) & 0xffu;
+}
+__device__ __forceinline__ void q4k_scale_min_dyn(const uint4& hdr, int j, uint32_t& sc, uint32_t& mn)
+{
+    const uint32_t lo_sc = q4k_hdr_byte_dyn(hdr, j & 3), lo_mn = q4k_hdr_byte_dyn(hdr, (j & 3) + 4), hi_b = q4k_hdr_byte_dyn(hdr, (j & 3) + 8);
+    if (j < 4) {
+        sc = lo_sc & 63u;
+        mn = lo_mn & 63u;
+    } else {
+        sc = (hi_b & 0x0Fu) | ((lo_sc >> 6) << 4);
+        mn = (hi_b >> 4) | ((lo_mn >> 6) << 4);
     }
-    const __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
-    const __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+}
+// Exact float of an integer below 2^23 without the conversion unit: 0x4B000000 | v is 2^23 + v.
+__device__ __forceinline__ float small_u32_to_float(uint32_t v) { return __uint_as_float(0x4B000000u | v) - 8388608.f; }
+// Two f32 lanes in one 64-bit register, for the packed f32x2 arithmetic of sm_100 (IEEE per lane).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+// One 32-bit word of two bf16 = round-to-nearest-even of fma(d1, q, c) per lane, q = f - 2^23.
+__device__ __forceinline__ uint32_t deq2(uint64_t f, uint64_t minus_magic, uint64_t d1, uint64_t c)
+{
+    uint64_t q, v;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(q) : "l"(f), "l"(minus_magic));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(v) : "l"(d1), "l"(q), "l"(c));
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// Eight weights (one 4-bit value in each byte of w0, w1) -> bf16, exactly as the reference decoder computes them
+// in f32 (d1 * q - mm, crates/ferric-gguf/src/lib.rs:813-822) and then rounds to nearest even.  d1 * q is exact
+// in f32 (<= 21 significant bits), so the fused multiply-add rounds once, like the separate multiply and subtract.
+// A byte permute drops each value into the mantissa of 2^23 (0x4B000000 | q = 2^23 + q); subtracting 2^23 is exact.
+__device__ __forceinline__ uint4 deq8(uint32_t w0, uint32_t w1, float d1, float mm)
+{
+    const uint64_t dd = pack_f32x2(d1, d1), cc = pack_f32x2(-mm, -mm), mg = pack_f32x2(-8388608.f, -8388608.f);
+    auto word = [&](uint32_t w, int e) {
+        return pack_f32x2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650 + e)),
+                          __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7651 + e)));
+    };
     uint4 o;
-    o.x = *reinterpret_cast<const uint32_t*>(&p0);
-    o.y = *reinterpret_cast<const uint32_t*>(&p1);
-    o.z = *reinterpret_cast<const uint32_t*>(&p2);
-    o.w = *reinterpret_cast<const uint32_t*>(&p3);
+    o.x = deq2(word(w0, 0), mg, dd, cc);
+    o.y = deq2(word(w0, 2), mg, dd, cc);
+    o.z = deq2(word(w1, 0), mg, dd, cc);
+    o.w = deq2(word(w1, 2), mg, dd, cc);
     return o;
 }
 
@@ -177,8 +246,10 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
     extern __shared__ uint8_t gemm_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* a_stage = smem;                                               // [S][16384]
-    uint8_t* b_stage = a_stage + kGemmStages * kGemmABytes;                // [S][N_TILE * 128]
-    uint8_t* raw_stage = b_stage + kGemmStages * gemm_b_bytes(N_TILE);     // [2][18432]
+    constexpr int kBStages = gemm_b_stages(N_TILE), kBBytes = gemm_b_bytes(N_TILE);
+    constexpr int kNMma = N_TILE > 256 ? 256 : N_TILE;                     // activation rows per tcgen05.mma
+    uint8_t* b_stage = a_stage + kGemmStages * kGemmABytes;                // [kBStages][N_TILE * 128]
+    uint8_t* raw_stage = b_stage + kBStages * kBBytes;                     // [2][18432]
     GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(raw_stage + kGemmRawStages * kGemmRawBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -187,15 +258,19 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
     const int tiles_here = min(8, row_tiles16 - rt0);
     const int nchunks = nblk * 4;
 
+    if (threadIdx.x == 0) GEMM_TRACE(0);
     if (threadIdx.x == 0) {
         for (int i = 0; i < kGemmRawStages; i++) {
             mbar_init(&bar->raw_full[i], 1);
-            mbar_init(&bar->raw_empty[i], 8);
+            mbar_init(&bar->raw_empty[i], kGemmDeqWarps);
         }
         for (int i = 0; i < kGemmStages; i++) {
-            mbar_init(&bar->a_full[i], 8);
+            mbar_init(&bar->a_full[i], kGemmDeqWarps);
+            mbar_init(&bar->a_empty[i], 1);
+        }
+        for (int i = 0; i < kBStages; i++) {
             mbar_init(&bar->b_full[i], 1);
-            mbar_init(&bar->stage_empty[i], 1);
+            mbar_init(&bar->b_empty[i], 1);
         }
         mbar_init(&bar->acc_full, 1);
         bar->abort = 0;
@@ -211,101 +286,136 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_acc = bar->tmem_base;
     int fail = 0;
+    if (threadIdx.x == 0) GEMM_TRACE(1);
 
     if (warp == 0) {
-        // ---------------- producer
+        // ---------------- weight producer: raw quant units of one super-block per stage
         if (lane == 0) {
-            auto load_raw = [&](int b) -> bool {
+            for (int b = 0; b < nblk; b++) {
                 const int rs = b % kGemmRawStages;
-                if (!mbar_wait(&bar->raw_empty[rs], (((uint32_t)b / kGemmRawStages) & 1u) ^ 1u)) return false;
+                if (!mbar_wait(&bar->raw_empty[rs], (((uint32_t)b / kGemmRawStages) & 1u) ^ 1u)) { fail = 1; break; }
                 mbar_expect_tx(&bar->raw_full[rs], (uint32_t)(tiles_here * kQ4KUnit));
                 for (int t = 0; t < tiles_here; t++)
                     bulk_g2s(raw_stage + rs * kGemmRawBytes + t * kQ4KUnit, units + ((size_t)(rt0 + t) * nblk + b) * kQ4KUnit,
                              kQ4KUnit, &bar->raw_full[rs]);
-                return true;
-            };
-            if (!load_raw(0)) fail = 1;
-            for (int b = 0; b < nblk && !fail; b++) {
-                if (b + 1 < nblk && !load_raw(b + 1)) { fail = 1; break; }
-                for (int j = 0; j < 4; j++) {
-                    const int c = 4 * b + j, s = c % kGemmStages;
-                    if (!mbar_wait(&bar->stage_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 2; break; }
-                    mbar_expect_tx(&bar->b_full[s], (uint32_t)gemm_b_bytes(N_TILE));
-                    tma_load_2d(b_stage + s * gemm_b_bytes(N_TILE), &xmap, c * kGemmChunkK, n0, &bar->b_full[s]);
-                }
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------- activation producer: one [64 k x N_TILE rows] bf16 tile per stage
+        if (lane == 0) {
+            for (int c = 0; c < nchunks; c++) {
+                const int s = c % kBStages;
+                if (!mbar_wait(&bar->b_empty[s], (((uint32_t)c / kBStages) & 1u) ^ 1u)) { fail = 2; break; }
+                mbar_expect_tx(&bar->b_full[s], (uint32_t)kBBytes);
+#pragma unroll
+                for (int h = 0; h < N_TILE / kNMma; h++)   // one box of at most 256 activation rows each
+                    tma_load_2d(b_stage + s * kBBytes + h * kNMma * 128, &xmap, c * kGemmChunkK, n0 + h * kNMma, &bar->b_full[s]);
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(kGemmRows, N_TILE);
+            constexpr uint32_t idesc = umma_idesc_bf16(kGemmRows, kNMma);
             for (int c = 0; c < nchunks; c++) {
-                const int s = c % kGemmStages;
-                const uint32_t ph = ((uint32_t)c / kGemmStages) & 1u;
-                if (!mbar_wait(&bar->a_full[s], ph) || !mbar_wait(&bar->b_full[s], ph)) { fail = 3; break; }
+                const int sa = c % kGemmStages, sb = c % kBStages;
+                if (!mbar_wait(&bar->a_full[sa], ((uint32_t)c / kGemmStages) & 1u) ||
+                    !mbar_wait(&bar->b_full[sb], ((uint32_t)c / kBStages) & 1u)) { fail = 3; break; }
                 tc_fence_after();
-                const uint32_t a0 = smem_u32(a_stage + s * kGemmABytes), b0 = smem_u32(b_stage + s * gemm_b_bytes(N_TILE));
+                if (c < 100) GEMM_TRACE(8 + c);
+                const uint32_t a0 = smem_u32(a_stage + sa * kGemmABytes), b0 = smem_u32(b_stage + sb * kBBytes);
 #pragma unroll
-                for (int k4 = 0; k4 < 4; k4++)
-                    umma_bf16(tmem_acc, umma_desc_sw128(a0 + 32 * k4), umma_desc_sw128(b0 + 32 * k4), idesc, (c | k4) ? 1u : 0u);
-                umma_commit(&bar->stage_empty[s]);   // frees this A / B stage once the MMAs above have read it
+                for (int k4 = 0; k4 < (FERRIC_GEMM_EXP == 3 ? 0 : 4); k4++)
+#pragma unroll
+                    for (int h = 0; h < N_TILE / kNMma; h++)
+                        umma_bf16(tmem_acc + h * kNMma, umma_desc_sw128(a0 + 32 * k4),
+                                  umma_desc_sw128(b0 + h * kNMma * 128 + 32 * k4), idesc, (c | k4) ? 1u : 0u);
+                umma_commit(&bar->a_empty[sa]);   // each frees its stage once the MMAs above have read it
+                umma_commit(&bar->b_empty[sb]);
             }
             if (!fail) umma_commit(&bar->acc_full);
         }
     } else {
-        // ---------------- dequantise: warp = one 16-row unit, lane = (row g / g+8, 8-byte piece t)
+        // ---------------- dequantise: warp = one 16-row unit (or eight rows of it), lane = (row g, 8-byte piece t)
         // The lane -> (g, t) map keeps both the 16-byte loads of the raw unit and the 16-byte stores into the
         // swizzled A tile free of bank conflicts: the two rows of a quarter-warp differ in bits 0 and 2.
-        const int wd = warp - 2, t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
+        const int wq = warp - kGemmFirstDeqWarp, wd = kGemmHalves == 2 ? wq : (wq >> 1), hi0 = kGemmHalves == 2 ? 0 : (wq & 1);
+        const int t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
         const bool unit_ok = wd < tiles_here;
+        const uint32_t arow_off = (uint32_t)((2 * wd + hi0) * 1024 + g * 128);
+        const uint32_t col_lo = (uint32_t)((t ^ g) << 4), col_hi = (uint32_t)(((4 + t) ^ g) << 4);
         for (int b = 0; b < nblk && !fail; b++) {
             const int rs = b % kGemmRawStages;
             if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)b / kGemmRawStages) & 1u)) { fail = 4; break; }
             const uint8_t* u = raw_stage + rs * kGemmRawBytes + wd * kQ4KUnit;
-            uint4 hdr[2], qs[2][2];
+            uint4 hdr[kGemmHalves], qs[kGemmHalves][2];
+            float d[kGemmHalves], dmin[kGemmHalves];
 #pragma unroll
-            for (int hi = 0; hi < 2; hi++) {
-                hdr[hi] = make_uint4(0, 0, 0, 0);
-                qs[hi][0] = qs[hi][1] = make_uint4(0, 0, 0, 0);
+            for (int hh = 0; hh < kGemmHalves; hh++) {
+                const int hi = hi0 + hh;
+                hdr[hh] = qs[hh][0] = qs[hh][1] = make_uint4(0, 0, 0, 0);
                 if (unit_ok) {
-                    hdr[hi] = *reinterpret_cast<const uint4*>(u + 16 * (g + 8 * hi));
-                    qs[hi][0] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi) + 16 * (4 * g + t));
-                    qs[hi][1] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi + 1) + 16 * (4 * g + t));
+                    hdr[hh] = *reinterpret_cast<const uint4*>(u + 16 * (g + 8 * hi));
+                    qs[hh][0] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi) + 16 * (4 * g + t));
+                    qs[hh][1] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi + 1) + 16 * (4 * g + t));
                 }
+                d[hh] = __half2float(__ushort_as_half((unsigned short)(hdr[hh].x & 0xffffu)));
+                dmin[hh] = __half2float(__ushort_as_half((unsigned short)(hdr[hh].x >> 16)));
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar->raw_empty[rs]);   // the block now lives in registers
+            // The four lanes of a row share its header: lane t works out (d*sc, dmin*m) of the two sub-blocks of
+            // chunk t once, and every chunk fetches its pair from the lane that holds it.
+            float my_d1a[kGemmHalves], my_mma[kGemmHalves], my_d1b[kGemmHalves], my_mmb[kGemmHalves];
+#pragma unroll
+            for (int hh = 0; hh < kGemmHalves; hh++) {
+                uint32_t sc0, mn0, sc1, mn1;
+                q4k_scale_min_dyn(hdr[hh], 2 * t, sc0, mn0);
+                q4k_scale_min_dyn(hdr[hh], 2 * t + 1, sc1, mn1);
+                my_d1a[hh] = __fmul_rn(d[hh], small_u32_to_float(sc0));
+                my_mma[hh] = __fmul_rn(dmin[hh], small_u32_to_float(mn0));
+                my_d1b[hh] = __fmul_rn(d[hh], small_u32_to_float(sc1));
+                my_mmb[hh] = __fmul_rn(dmin[hh], small_u32_to_float(mn1));
+            }
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const int c = 4 * b + j, s = c % kGemmStages;
-                if (!mbar_wait(&bar->stage_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
+                uint4 lo[kGemmHalves], up[kGemmHalves];
+                const int src = (lane & ~3) | j;
 #pragma unroll
-                for (int hi = 0; hi < 2; hi++) {
-                    const float d = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x & 0xffffu)));
-                    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x >> 16)));
-                    uint32_t sc0, mn0, sc1, mn1;
-                    q4k_scale_min(hdr[hi], 2 * j, sc0, mn0);
-                    q4k_scale_min(hdr[hi], 2 * j + 1, sc1, mn1);
-                    const float d1a = __fmul_rn(d, (float)sc0), mma = __fmul_rn(dmin, (float)mn0);
-                    const float d1b = __fmul_rn(d, (float)sc1), mmb = __fmul_rn(dmin, (float)mn1);
-                    const uint4 q4 = qs[hi][j >> 1];
+                for (int hh = 0; hh < kGemmHalves; hh++) {
+                    const float d1a = __shfl_sync(0xffffffffu, my_d1a[hh], src), mma = __shfl_sync(0xffffffffu, my_mma[hh], src);
+                    const float d1b = __shfl_sync(0xffffffffu, my_d1b[hh], src), mmb = __shfl_sync(0xffffffffu, my_mmb[hh], src);
+                    const uint4 q4 = qs[hh][j >> 1];
                     const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
-                    const int r = 16 * wd + 8 * hi + g;
-                    uint8_t* arow = a_stage + s * kGemmABytes + (r >> 3) * 1024 + (r & 7) * 128;
-                    *reinterpret_cast<uint4*>(arow + ((t ^ (r & 7)) << 4)) = deq8(w0, w1, 0, d1a, mma);
-                    *reinterpret_cast<uint4*>(arow + (((4 + t) ^ (r & 7)) << 4)) = deq8(w0, w1, 4, d1b, mmb);
+#if FERRIC_GEMM_EXP == 1
+                    lo[hh] = make_uint4(w0, w1, __float_as_uint(d1a), __float_as_uint(mma));
+                    up[hh] = make_uint4(w0, w1, __float_as_uint(d1b), __float_as_uint(mmb));
+#else
+                    lo[hh] = deq8(w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, d1a, mma);
+                    up[hh] = deq8((w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, d1b, mmb);
+#endif
                 }
+                const int c = 4 * b + j, s = c % kGemmStages;
+                if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
+                uint8_t* arow = a_stage + s * kGemmABytes + arow_off;
+#pragma unroll
+                for (int hh = 0; hh < kGemmHalves; hh++) {
+                    *reinterpret_cast<uint4*>(arow + hh * 1024 + col_lo) = lo[hh];
+                    *reinterpret_cast<uint4*>(arow + hh * 1024 + col_hi) = up[hh];
+                }
+#if FERRIC_GEMM_EXP != 2
                 fence_proxy_async();     // generic-proxy stores -> visible to the tensor core's async reads
+#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar->a_full[s]);
             }
         }
-        // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +32
-        if (warp < 6 && !fail) {
+        // ---------------- epilogue: the first four dequant warps; a warp may read TMEM lanes 32*(warp%4) .. +32
+        if (wq < 4 && !fail) {
             if (!mbar_wait(&bar->acc_full, 0)) {
                 fail = 6;
             } else {
                 tc_fence_after();
+                if (threadIdx.x == 32 * kGemmFirstDeqWarp) GEMM_TRACE(2);
                 const int q = warp & 3, wrow = row0 + 32 * q + lane;
 #pragma unroll 1
                 for (int c0 = 0; c0 < N_TILE; c0 += 32) {
@@ -332,6 +442,7 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
             }
         }
     }
+    if (threadIdx.x == 32 * kGemmFirstDeqWarp) GEMM_TRACE(3);
     if (fail) {
         atomicExch(&bar->abort, fail);
         if (err) atomicExch(err, fail);
@@ -405,11 +516,11 @@ int32_t launch_gemm_q4k_bf16(cudaStream_t st, const DeviceWeights& w, const uint
         set_last_error("the CUDA driver does not export cuTensorMapEncodeTiled");
         return kErrCuda;
     }
-    const int n_tile = m <= 128 ? 128 : 256;
+    const int n_tile = m <= 128 ? 128 : (m <= 256 ? 256 : 512);
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)w.cols, (cuuint64_t)m};
     const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kGemmChunkK, (cuuint32_t)n_tile};
+    const cuuint32_t box[2] = {(cuuint32_t)kGemmChunkK, (cuuint32_t)(n_tile > 256 ? 256 : n_tile)};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(x_bf16), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -418,7 +529,9 @@ int32_t launch_gemm_q4k_bf16(cudaStream_t st, const DeviceWeights& w, const uint
         set_last_error("cuTensorMapEncodeTiled failed with code %d", (int)r);
         return kErrCuda;
     }
-    return n_tile == 128 ? launch_gemm_tile<128>(st, w, map, m, y, ldy) : launch_gemm_tile<256>(st, w, map, m, y, ldy);
+    if (n_tile == 128) return launch_gemm_tile<128>(st, w, map, m, y, ldy);
+    if (n_tile == 256) return launch_gemm_tile<256>(st, w, map, m, y, ldy);
+    return launch_gemm_tile<512>(st, w, map, m, y, ldy);
 }
 
 // Synchronises the stream, returns the code of the first bounded wait that ran out (0 = none) and clears it.
@@ -433,3 +546,10 @@ int32_t gemm_status(cudaStream_t st, int* code)
 }
 
 }  // namespace ferric
+
+#if FERRIC_GEMM_EXP == 9
+extern "C" int ferric_debug_gemm_trace(unsigned long long* out128)
+{
+    return (int)cudaMemcpyFromSymbol(out128, ferric::g_gemm_trace, sizeof(unsigned long long) * 128);
+}
+#endif
