@@ -18,6 +18,7 @@
 // Every wait on an mbarrier is bounded: on expiry the thread records an error code and the CTA drains.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -41,6 +42,7 @@ constexpr int kGemmFirstDeqWarp = 3;                   // warp 0 weight producer
 constexpr int kGemmThreads = 32 * (kGemmFirstDeqWarp + kGemmDeqWarps);
 constexpr int kGemmRawBytes = 8 * kQ4KUnit;                   // 18432: 8 row tiles x one super-block
 constexpr int kGemmABytes = kGemmRows * 128;                  // 16384 per stage
+constexpr int kGemmStoreBytes = 32 * kGemmRows * 4;            // one [32 activation rows][128 weight rows] f32 store tile
 constexpr unsigned long long kGemmWaitNs = 1000000000ull;     // every mbarrier wait gives up after one second
 
 __host__ __device__ constexpr int gemm_b_bytes(int n_tile) { return n_tile * 128; }
@@ -155,6 +157,25 @@ __device__ __forceinline__ void trace(int slot)
 #define GEMM_TRACE(slot)
 #endif
 
+__device__ __forceinline__ void named_bar_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// 32 consecutive accumulator columns of this warp's 32 TMEM lanes: v[j] = D[lane][column + j].
+__device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- the kernel
 struct GemmBarriers {
     uint64_t raw_full[kGemmRawStages], raw_empty[kGemmRawStages];
@@ -240,8 +261,9 @@ __device__ __forceinline__ uint4 deq8(uint32_t w0, uint32_t w1, float d1, float 
 
 template <int N_TILE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap, float* __restrict__ y,
-                     int rows, int nblk, int m, size_t ldy, int row_tiles16, int* __restrict__ err)
+gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap,
+                     const __grid_constant__ CUtensorMap ymap, int tma_store, float* __restrict__ y, int rows, int nblk, int m,
+                     size_t ldy, int row_tiles16, int* __restrict__ err)
 {
     extern __shared__ uint8_t gemm_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -409,28 +431,52 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
                 if (lane == 0) mbar_arrive(&bar->a_full[s]);
             }
         }
-        // ---------------- epilogue: the first four dequant warps; a warp may read TMEM lanes 32*(warp%4) .. +32
-        if (wq < 4 && !fail) {
-            if (!mbar_wait(&bar->acc_full, 0)) {
-                fail = 6;
-            } else {
-                tc_fence_after();
-                if (threadIdx.x == 32 * kGemmFirstDeqWarp) GEMM_TRACE(2);
-                const int q = warp & 3, wrow = row0 + 32 * q + lane;
+        // ---------------- epilogue.  All dequant warps first agree that nobody gave up (the staged path below
+        // synchronises them with named barriers, which must not be entered by only some of them).
+        if (fail) atomicExch(&bar->abort, fail);
+        named_bar_sync(1, 32 * kGemmDeqWarps);
+        if (*reinterpret_cast<volatile int*>(&bar->abort) == 0 && wq < 8 && !mbar_wait(&bar->acc_full, 0)) {
+            fail = 6;
+            atomicExch(&bar->abort, fail);
+        }
+        named_bar_sync(1, 32 * kGemmDeqWarps);
+        if (*reinterpret_cast<volatile int*>(&bar->abort) == 0 && wq < 8) {
+            tc_fence_after();
+            if (threadIdx.x == 32 * kGemmFirstDeqWarp) GEMM_TRACE(2);
+            // A warp may read TMEM lanes 32*(warp%4) .. +32; lane = weight row, column = activation row.
+            const int q = warp & 3, grp = wq >> 2, wrow = row0 + 32 * q + lane;
+            if (tma_store) {
+                // Two groups of four warps take alternate 32-column slabs: TMEM -> registers -> a [32][128] f32
+                // staging tile (two per group, in the idle activation ring) -> one TMA store per slab, which
+                // clips rows past `rows` and activation rows past `m`.
+                float* stage0 = reinterpret_cast<float*>(b_stage + grp * 2 * kGemmStoreBytes);
+                const bool elected = (wq & 3) == 0 && lane == 0;
+                int it = 0;
+#pragma unroll 1
+                for (int c0 = 32 * grp; c0 < N_TILE; c0 += 64, it++) {
+                    if (n0 + c0 >= m) break;                       // uniform over the group
+                    float* stg = stage0 + (it & 1) * (kGemmStoreBytes / 4);
+                    if (elected) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // tile (it - 2) has been read
+                    named_bar_sync(2 + grp, 128);
+                    uint32_t v[32];
+                    tmem_ld_32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+#pragma unroll
+                    for (int jj = 0; jj < 32; jj++) stg[jj * 128 + 32 * q + lane] = __uint_as_float(v[jj]);
+                    fence_proxy_async();
+                    named_bar_sync(2 + grp, 128);
+                    if (elected) {
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&ymap),
+                                     "r"(row0), "r"(n0 + c0), "r"(smem_u32(stg))
+                                     : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
+                if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            } else if (wq < 4) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < N_TILE; c0 += 32) {
                     uint32_t v[32];
-                    const uint32_t taddr = tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)c0;
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-                          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                        : "r"(taddr)
-                        : "memory");
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tmem_ld_32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
                     if (wrow < rows) {
 #pragma unroll
                         for (int jj = 0; jj < 32; jj++) {
@@ -483,7 +529,8 @@ EncodeTiledFn encode_tiled_fn()
 }
 
 template <int N_TILE>
-int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, size_t m, float* y, size_t ldy)
+int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& ymap, int tma_store,
+                         size_t m, float* y, size_t ldy)
 {
     static bool attr_done[64] = {};
     int dev = 0;
@@ -497,7 +544,7 @@ int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensor
     FERRIC_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_gemm_status));
     dim3 grid((unsigned)((w.rows + kGemmRows - 1) / kGemmRows), (unsigned)((m + N_TILE - 1) / N_TILE));
     gemm_q4k_bf16_kernel<N_TILE><<<grid, kGemmThreads, gemm_smem_bytes(N_TILE), st>>>(
-        w.units, map, y, (int)w.rows, (int)w.nblk, (int)m, ldy, (int)w.row_tiles(), err);
+        w.units, map, ymap, tma_store, y, (int)w.rows, (int)w.nblk, (int)m, ldy, (int)w.row_tiles(), err);
     FERRIC_CUDA_TRY(cudaGetLastError());
     return kOk;
 }
@@ -529,9 +576,26 @@ int32_t launch_gemm_q4k_bf16(cudaStream_t st, const DeviceWeights& w, const uint
         set_last_error("cuTensorMapEncodeTiled failed with code %d", (int)r);
         return kErrCuda;
     }
-    if (n_tile == 128) return launch_gemm_tile<128>(st, w, map, m, y, ldy);
-    if (n_tile == 256) return launch_gemm_tile<256>(st, w, map, m, y, ldy);
-    return launch_gemm_tile<512>(st, w, map, m, y, ldy);
+    // The result leaves through TMA stores of [32 activation rows][128 weight rows] f32 tiles when y allows it
+    // (16-byte aligned base and row pitch); otherwise the epilogue stores element-wise.
+    CUtensorMap ymap;
+    memset(&ymap, 0, sizeof(ymap));
+    int tma_store = 0;
+    if ((reinterpret_cast<uintptr_t>(y) & 15) == 0 && (ldy * 4) % 16 == 0) {
+        const cuuint64_t ydims[2] = {(cuuint64_t)w.rows, (cuuint64_t)m};
+        const cuuint64_t ystrides[1] = {(cuuint64_t)ldy * 4};
+        const cuuint32_t ybox[2] = {(cuuint32_t)kGemmRows, 32};
+        r = enc(&ymap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, y, ydims, ystrides, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            set_last_error("cuTensorMapEncodeTiled (result) failed with code %d", (int)r);
+            return kErrCuda;
+        }
+        tma_store = 1;
+    }
+    if (n_tile == 128) return launch_gemm_tile<128>(st, w, map, ymap, tma_store, m, y, ldy);
+    if (n_tile == 256) return launch_gemm_tile<256>(st, w, map, ymap, tma_store, m, y, ldy);
+    return launch_gemm_tile<512>(st, w, map, ymap, tma_store, m, y, ldy);
 }
 
 // Synchronises the stream, returns the code of the first bounded wait that ran out (0 = none) and clears it.

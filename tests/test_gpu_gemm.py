@@ -85,6 +85,7 @@ def check(F, ctx, rows, cols, m, seed, oracle_rows=None):
     (256, 512, 256),      # N tile 256
     (144, 768, 40),       # ragged: rows not a multiple of 128, batch below one tile
     (16, 256, 1),         # smallest legal matrix
+    (50, 512, 40),        # result pitch not a multiple of 16 bytes: element-wise epilogue instead of TMA stores
     (1000, 2048, 300),    # ragged rows and two N tiles with a partial one
 ])
 def test_small_shapes(F, ctx, rows, cols, m):
