@@ -4,20 +4,27 @@
 // Replaces Tensor::matmul_q4_k_coop (crates/ferric-tensor/src/dtype.rs:1818-1834, kernel :2059-2096):
 // there a workgroup dequantises an 8x8 weight tile into shared memory and feeds 8x8x8 f32
 // cooperative-matrix ops (Metal only; "exactly 1.0x" on NVIDIA, crates/ferric-core/src/lib.rs:90-100).
-// Here a CTA owns 128 weight rows x 128, 256 or 512 activation rows (512 = all of tensor memory):
+// Here a CTA owns 128 weight rows x 128, 256 or 512 activation rows (512 = all of tensor memory); above 256
+// activation rows two CTAs on neighbouring SMs form a pair (cta_group::2) that works on a 256 x 512 tile: each
+// dequantises its own 128 weight rows, each loads half of the activation tile, one thread of the leader issues
+// M = 256 MMAs that read both CTAs' shared memory and write both CTAs' tensor memory.  That halves the
+// activation bytes a CTA pulls from L2 per flop, which is what bounds the single-CTA form.
 //   * warp 0 (one lane)  weight producer: bulk-copies the raw quant units of the next super-blocks;
-//   * warp 2 (one lane)  activation producer: TMA-loads the activation tile (bf16 [N, 64] boxes, 128-byte
+//   * warp 2 (one lane)  activation producer: TMA-loads the activation tile (bf16 [rows, 64] boxes, 128-byte
 //                        swizzle) of each 64-wide K chunk, as many chunks ahead as shared memory holds;
-//   * warps 3..10        dequantise: each warp owns one 16-row unit, each thread 32 weights per K chunk, into bf16
-//                        with the reference decoder's exact arithmetic (d*sc, dmin*m, d1*q - mm, round to
-//                        nearest even) and stores it into the K-major, 128-byte-swizzled A tile;
-//   * warp 1 (one lane)  issues tcgen05.mma (M 128, N <= 256, K 16, bf16 -> f32 in TMEM), four or eight per chunk,
-//                        and commits to mbarriers that free the A / B stages;
-//   * warps 3..6         epilogue: tcgen05.ld the accumulator (lane = weight row, column = activation row)
-//                        and store y[activation row][weight row], coalesced along weight rows.
+//   * warps 3..10        dequantise: each warp owns one 16-row unit, each thread 32 weights per K chunk, into
+//                        bf16 with the reference decoder's exact arithmetic (d*sc, dmin*m, d1*q - mm, round to
+//                        nearest even), stored into the K-major, 128-byte-swizzled A tile;
+//   * warp 1 (one lane)  issues tcgen05.mma (N <= 256, K 16, bf16 -> f32 in TMEM), four or eight per chunk, and
+//                        commits to the mbarriers that free the A / B stages (in both CTAs of a pair);
+//   * warps 3..10        epilogue: tcgen05.ld the accumulator (lane = weight row, column = activation row),
+//                        stage it in shared memory and TMA-store y[activation row][weight row].
 // Every wait on an mbarrier is bounded: on expiry the thread records an error code and the CTA drains.
+// No load in this file uses cluster multicast; the only multicast is tcgen05.commit's arrival on both CTAs'
+// barriers.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -29,15 +36,8 @@ constexpr int kGemmRows = 128;        // weight rows per CTA (UMMA M)
 constexpr int kGemmChunkK = 64;       // K per pipeline stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kGemmStages = 3;        // dequantised A stages in flight
 constexpr int kGemmRawStages = 2;     // raw quant super-blocks in flight
-#ifndef FERRIC_GEMM_EXP
-#define FERRIC_GEMM_EXP 0
-#endif
-#ifndef FERRIC_GEMM_DEQ_WARPS
-#define FERRIC_GEMM_DEQ_WARPS 8
-#endif
-constexpr int kGemmDeqWarps = FERRIC_GEMM_DEQ_WARPS;   // 8: one per 16-row unit; 16: two per unit
-constexpr int kGemmHalves = 16 / kGemmDeqWarps;        // 8-row halves of a unit each dequant warp converts
-static_assert(kGemmDeqWarps == 8 || kGemmDeqWarps == 16, "one or two dequant warps per 16-row unit");
+constexpr int kGemmDeqWarps = 8;      // one per 16-row unit of the 128-row tile
+constexpr int kGemmHalves = 2;        // the two 8-row halves of its unit a dequant warp converts
 constexpr int kGemmFirstDeqWarp = 3;                   // warp 0 weight producer, 1 MMA issuer, 2 activation producer
 constexpr int kGemmThreads = 32 * (kGemmFirstDeqWarp + kGemmDeqWarps);
 constexpr int kGemmRawBytes = 8 * kQ4KUnit;                   // 18432: 8 row tiles x one super-block
@@ -45,21 +45,27 @@ constexpr int kGemmABytes = kGemmRows * 128;                  // 16384 per stage
 constexpr int kGemmStoreBytes = 32 * kGemmRows * 4;            // one [32 activation rows][128 weight rows] f32 store tile
 constexpr unsigned long long kGemmWaitNs = 1000000000ull;     // every mbarrier wait gives up after one second
 
-__host__ __device__ constexpr int gemm_b_bytes(int n_tile) { return n_tile * 128; }
+// Activation bytes of one K chunk held by one CTA: the whole [n_tile x 64] bf16 tile, or half of it when two
+// CTAs form a pair and each supplies half of the tensor core's B operand.
+__host__ __device__ constexpr int gemm_b_bytes(int n_tile, bool pair = false) { return n_tile * 128 / (pair ? 2 : 1); }
 // Activation stages: as many as the shared memory left by the A ring and the raw ring holds, at most 8.  What
 // bounds the kernel at small N is bytes in flight (a stage's round trip through TMA and L2 is over a microsecond),
 // so the ring is as deep as it can be: 8 stages at N 128, 4 at 256, 2 at 512.
 constexpr int kGemmSmemMax = 232448;  // 227 KB per CTA
 constexpr int kGemmFixedBytes = 1024 /*align*/ + 256 /*barriers*/ + kGemmStages * kGemmABytes + kGemmRawStages * kGemmRawBytes;
 constexpr int kGemmMaxBStages = 8;
-__host__ __device__ constexpr int gemm_b_stages(int n_tile)
+__host__ __device__ constexpr int gemm_b_stages(int n_tile, bool pair = false)
 {
-    return (kGemmSmemMax - kGemmFixedBytes) / gemm_b_bytes(n_tile) > kGemmMaxBStages
+    return (kGemmSmemMax - kGemmFixedBytes) / gemm_b_bytes(n_tile, pair) > kGemmMaxBStages
                ? kGemmMaxBStages
-               : (kGemmSmemMax - kGemmFixedBytes) / gemm_b_bytes(n_tile);
+               : (kGemmSmemMax - kGemmFixedBytes) / gemm_b_bytes(n_tile, pair);
 }
-__host__ __device__ constexpr int gemm_smem_bytes(int n_tile) { return kGemmFixedBytes + gemm_b_stages(n_tile) * gemm_b_bytes(n_tile); }
-static_assert(gemm_b_stages(128) == 8 && gemm_b_stages(256) == 4 && gemm_b_stages(512) == 2, "stage counts");
+__host__ __device__ constexpr int gemm_smem_bytes(int n_tile, bool pair = false)
+{
+    return kGemmFixedBytes + gemm_b_stages(n_tile, pair) * gemm_b_bytes(n_tile, pair);
+}
+static_assert(gemm_b_stages(128) == 8 && gemm_b_stages(256) == 4 && gemm_b_stages(512) == 2 && gemm_b_stages(512, true) == 4,
+              "stage counts");
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -110,6 +116,42 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
                  "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
                  : "memory");
 }
+// Cluster-wide address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
+{
+    // CTA-scope release as for a local arrive: what the leader's tensor core reads from this CTA's shared memory was
+    // already handed to the async proxy by fence.proxy.async; a cluster-scope release here costs most of a microsecond.
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
+// TMA load inside a CTA pair: the data lands in this CTA's shared memory, the completion bytes are counted on
+// a barrier that may live in the pair's leader.  No multicast: every CTA fetches its own half.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(cluster_bar)
+                 : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -141,21 +183,23 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-
-#if FERRIC_GEMM_EXP == 9
-__device__ unsigned long long g_gemm_trace[128];
-__device__ __forceinline__ void trace(int slot)
+// The pair's forms: one thread of the leader issues an MMA that spans both CTAs (M 256: 128 rows of A and of the
+// accumulator in each CTA, half of B from each), and its commit arrives on the same barrier in both CTAs.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
-    if (blockIdx.x == 0 && blockIdx.y == 0) {
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        g_gemm_trace[slot] = now;
-    }
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
-#define GEMM_TRACE(slot) trace(slot)
-#else
-#define GEMM_TRACE(slot)
-#endif
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     smem_u32(bar)),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads)
 {
@@ -259,7 +303,7 @@ __device__ __forceinline__ uint4 deq8(uint32_t w0, uint32_t w1, float d1, float 
     return o;
 }
 
-template <int N_TILE>
+template <int N_TILE, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap,
                      const __grid_constant__ CUtensorMap ymap, int tma_store, float* __restrict__ y, int rows, int nblk, int m,
@@ -268,47 +312,57 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
     extern __shared__ uint8_t gemm_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* a_stage = smem;                                               // [S][16384]
-    constexpr int kBStages = gemm_b_stages(N_TILE), kBBytes = gemm_b_bytes(N_TILE);
+    constexpr int kBStages = gemm_b_stages(N_TILE, PAIR), kBBytes = gemm_b_bytes(N_TILE, PAIR);
     constexpr int kNMma = N_TILE > 256 ? 256 : N_TILE;                     // activation rows per tcgen05.mma
-    uint8_t* b_stage = a_stage + kGemmStages * kGemmABytes;                // [kBStages][N_TILE * 128]
+    constexpr int kBoxRows = PAIR ? kNMma / 2 : kNMma;                     // of them, rows this CTA holds
+    constexpr int kPeers = PAIR ? 2 : 1;
+    uint8_t* b_stage = a_stage + kGemmStages * kGemmABytes;                // [kBStages][kBBytes]
     uint8_t* raw_stage = b_stage + kBStages * kBBytes;                     // [2][18432]
     GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(raw_stage + kGemmRawStages * kGemmRawBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * kGemmRows, n0 = blockIdx.y * N_TILE;
     const int rt0 = blockIdx.x * 8;                                        // first 16-row tile of this CTA
-    const int tiles_here = min(8, row_tiles16 - rt0);
+    const int tiles_here = max(0, min(8, row_tiles16 - rt0));              // 0: padding CTA of an odd pair
     const int nchunks = nblk * 4;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;                   // rank 0 leads the pair
 
-    if (threadIdx.x == 0) GEMM_TRACE(0);
     if (threadIdx.x == 0) {
         for (int i = 0; i < kGemmRawStages; i++) {
             mbar_init(&bar->raw_full[i], 1);
             mbar_init(&bar->raw_empty[i], kGemmDeqWarps);
         }
         for (int i = 0; i < kGemmStages; i++) {
-            mbar_init(&bar->a_full[i], kGemmDeqWarps);
+            mbar_init(&bar->a_full[i], kGemmDeqWarps * kPeers);   // in a pair only the leader's is used
             mbar_init(&bar->a_empty[i], 1);
         }
         for (int i = 0; i < kBStages; i++) {
-            mbar_init(&bar->b_full[i], 1);
+            mbar_init(&bar->b_full[i], kPeers);
             mbar_init(&bar->b_empty[i], 1);
         }
         mbar_init(&bar->acc_full, 1);
         bar->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // tensor memory for the 128 x N_TILE f32 accumulator
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)), "n"(N_TILE)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == 1) {  // tensor memory for the 128 x N_TILE f32 accumulator (in a pair: one warp of each CTA)
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
+                         "n"(N_TILE)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
+                         "n"(N_TILE)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_acc = bar->tmem_base;
     int fail = 0;
-    if (threadIdx.x == 0) GEMM_TRACE(1);
 
     if (warp == 0) {
         // ---------------- weight producer: raw quant units of one super-block per stage
@@ -328,42 +382,62 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
             for (int c = 0; c < nchunks; c++) {
                 const int s = c % kBStages;
                 if (!mbar_wait(&bar->b_empty[s], (((uint32_t)c / kBStages) & 1u) ^ 1u)) { fail = 2; break; }
-                mbar_expect_tx(&bar->b_full[s], (uint32_t)kBBytes);
+                if (PAIR) {
+                    // each CTA fetches its half of every 256-row operand; the bytes of both are counted by the leader
+                    const uint32_t full = cluster_addr(&bar->b_full[s], 0);
+                    mbar_expect_tx_cluster(full, (uint32_t)kBBytes);
 #pragma unroll
-                for (int h = 0; h < N_TILE / kNMma; h++)   // one box of at most 256 activation rows each
-                    tma_load_2d(b_stage + s * kBBytes + h * kNMma * 128, &xmap, c * kGemmChunkK, n0 + h * kNMma, &bar->b_full[s]);
+                    for (int h = 0; h < N_TILE / kNMma; h++)
+                        tma_load_2d_pair(b_stage + s * kBBytes + h * kBoxRows * 128, &xmap, c * kGemmChunkK,
+                                         n0 + h * kNMma + (int)rank * kBoxRows, full);
+                } else {
+                    mbar_expect_tx(&bar->b_full[s], (uint32_t)kBBytes);
+#pragma unroll
+                    for (int h = 0; h < N_TILE / kNMma; h++)   // one box of at most 256 activation rows each
+                        tma_load_2d(b_stage + s * kBBytes + h * kNMma * 128, &xmap, c * kGemmChunkK, n0 + h * kNMma, &bar->b_full[s]);
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(kGemmRows, kNMma);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(kGemmRows * kPeers, kNMma);
             for (int c = 0; c < nchunks; c++) {
                 const int sa = c % kGemmStages, sb = c % kBStages;
                 if (!mbar_wait(&bar->a_full[sa], ((uint32_t)c / kGemmStages) & 1u) ||
                     !mbar_wait(&bar->b_full[sb], ((uint32_t)c / kBStages) & 1u)) { fail = 3; break; }
                 tc_fence_after();
-                if (c < 100) GEMM_TRACE(8 + c);
                 const uint32_t a0 = smem_u32(a_stage + sa * kGemmABytes), b0 = smem_u32(b_stage + sb * kBBytes);
 #pragma unroll
-                for (int k4 = 0; k4 < (FERRIC_GEMM_EXP == 3 ? 0 : 4); k4++)
+                for (int k4 = 0; k4 < 4; k4++)
 #pragma unroll
-                    for (int h = 0; h < N_TILE / kNMma; h++)
-                        umma_bf16(tmem_acc + h * kNMma, umma_desc_sw128(a0 + 32 * k4),
-                                  umma_desc_sw128(b0 + h * kNMma * 128 + 32 * k4), idesc, (c | k4) ? 1u : 0u);
-                umma_commit(&bar->a_empty[sa]);   // each frees its stage once the MMAs above have read it
-                umma_commit(&bar->b_empty[sb]);
+                    for (int h = 0; h < N_TILE / kNMma; h++) {
+                        const uint64_t ad = umma_desc_sw128(a0 + 32 * k4), bd = umma_desc_sw128(b0 + h * kBoxRows * 128 + 32 * k4);
+                        if (PAIR) umma_bf16_pair(tmem_acc + h * kNMma, ad, bd, idesc, (c | k4) ? 1u : 0u);
+                        else umma_bf16(tmem_acc + h * kNMma, ad, bd, idesc, (c | k4) ? 1u : 0u);
+                    }
+                // each commit frees its stage (in both CTAs of a pair) once the MMAs above have read it
+                if (PAIR) {
+                    umma_commit_pair(&bar->a_empty[sa]);
+                    umma_commit_pair(&bar->b_empty[sb]);
+                } else {
+                    umma_commit(&bar->a_empty[sa]);
+                    umma_commit(&bar->b_empty[sb]);
+                }
             }
-            if (!fail) umma_commit(&bar->acc_full);
+            if (!fail) {
+                if (PAIR) umma_commit_pair(&bar->acc_full);
+                else umma_commit(&bar->acc_full);
+            }
         }
     } else {
         // ---------------- dequantise: warp = one 16-row unit (or eight rows of it), lane = (row g, 8-byte piece t)
         // The lane -> (g, t) map keeps both the 16-byte loads of the raw unit and the 16-byte stores into the
         // swizzled A tile free of bank conflicts: the two rows of a quarter-warp differ in bits 0 and 2.
-        const int wq = warp - kGemmFirstDeqWarp, wd = kGemmHalves == 2 ? wq : (wq >> 1), hi0 = kGemmHalves == 2 ? 0 : (wq & 1);
+        const int wq = warp - kGemmFirstDeqWarp, wd = wq;
         const int t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
         const bool unit_ok = wd < tiles_here;
-        const uint32_t arow_off = (uint32_t)((2 * wd + hi0) * 1024 + g * 128);
+        const uint32_t arow_off = (uint32_t)(2 * wd * 1024 + g * 128);
         const uint32_t col_lo = (uint32_t)((t ^ g) << 4), col_hi = (uint32_t)(((4 + t) ^ g) << 4);
         for (int b = 0; b < nblk && !fail; b++) {
             const int rs = b % kGemmRawStages;
@@ -373,7 +447,7 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
             float d[kGemmHalves], dmin[kGemmHalves];
 #pragma unroll
             for (int hh = 0; hh < kGemmHalves; hh++) {
-                const int hi = hi0 + hh;
+                const int hi = hh;
                 hdr[hh] = qs[hh][0] = qs[hh][1] = make_uint4(0, 0, 0, 0);
                 if (unit_ok) {
                     hdr[hh] = *reinterpret_cast<const uint4*>(u + 16 * (g + 8 * hi));
@@ -408,13 +482,8 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
                     const float d1b = __shfl_sync(0xffffffffu, my_d1b[hh], src), mmb = __shfl_sync(0xffffffffu, my_mmb[hh], src);
                     const uint4 q4 = qs[hh][j >> 1];
                     const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
-#if FERRIC_GEMM_EXP == 1
-                    lo[hh] = make_uint4(w0, w1, __float_as_uint(d1a), __float_as_uint(mma));
-                    up[hh] = make_uint4(w0, w1, __float_as_uint(d1b), __float_as_uint(mmb));
-#else
                     lo[hh] = deq8(w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, d1a, mma);
                     up[hh] = deq8((w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, d1b, mmb);
-#endif
                 }
                 const int c = 4 * b + j, s = c % kGemmStages;
                 if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
@@ -424,11 +493,12 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
                     *reinterpret_cast<uint4*>(arow + hh * 1024 + col_lo) = lo[hh];
                     *reinterpret_cast<uint4*>(arow + hh * 1024 + col_hi) = up[hh];
                 }
-#if FERRIC_GEMM_EXP != 2
                 fence_proxy_async();     // generic-proxy stores -> visible to the tensor core's async reads
-#endif
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bar->a_full[s]);
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
+                    else mbar_arrive(&bar->a_full[s]);
+                }
             }
         }
         // ---------------- epilogue.  All dequant warps first agree that nobody gave up (the staged path below
@@ -442,7 +512,6 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
         named_bar_sync(1, 32 * kGemmDeqWarps);
         if (*reinterpret_cast<volatile int*>(&bar->abort) == 0 && wq < 8) {
             tc_fence_after();
-            if (threadIdx.x == 32 * kGemmFirstDeqWarp) GEMM_TRACE(2);
             // A warp may read TMEM lanes 32*(warp%4) .. +32; lane = weight row, column = activation row.
             const int q = warp & 3, grp = wq >> 2, wrow = row0 + 32 * q + lane;
             if (tma_store) {
@@ -464,7 +533,7 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
                     for (int jj = 0; jj < 32; jj++) stg[jj * 128 + 32 * q + lane] = __uint_as_float(v[jj]);
                     fence_proxy_async();
                     named_bar_sync(2 + grp, 128);
-                    if (elected) {
+                    if (elected && row0 < rows) {
                         asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&ymap),
                                      "r"(row0), "r"(n0 + c0), "r"(smem_u32(stg))
                                      : "memory");
@@ -488,7 +557,6 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
             }
         }
     }
-    if (threadIdx.x == 32 * kGemmFirstDeqWarp) GEMM_TRACE(3);
     if (fail) {
         atomicExch(&bar->abort, fail);
         if (err) atomicExch(err, fail);
@@ -500,9 +568,13 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
         for (int i = 0; i < 200; i++) __nanosleep(1000);
         __syncthreads();
     }
+    // In a pair neither CTA may leave, or give its tensor memory back, while the other can still signal its barriers
+    // or the leader's MMAs can still touch its shared and tensor memory.
+    if (PAIR) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "n"(N_TILE) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "n"(N_TILE) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "n"(N_TILE) : "memory");
     }
 }
 
@@ -528,25 +600,47 @@ EncodeTiledFn encode_tiled_fn()
     return fn;
 }
 
-template <int N_TILE>
+template <int N_TILE, bool PAIR>
 int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& ymap, int tma_store,
                          size_t m, float* y, size_t ldy)
 {
     static bool attr_done[64] = {};
     int dev = 0;
     FERRIC_CUDA_TRY(cudaGetDevice(&dev));
+    constexpr int smem = gemm_smem_bytes(N_TILE, PAIR);
     if (dev < 64 && !attr_done[dev]) {
-        FERRIC_CUDA_TRY(cudaFuncSetAttribute(gemm_q4k_bf16_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             gemm_smem_bytes(N_TILE)));
+        FERRIC_CUDA_TRY(cudaFuncSetAttribute(gemm_q4k_bf16_kernel<N_TILE, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_done[dev] = true;
     }
     int* err = nullptr;
     FERRIC_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_gemm_status));
-    dim3 grid((unsigned)((w.rows + kGemmRows - 1) / kGemmRows), (unsigned)((m + N_TILE - 1) / N_TILE));
-    gemm_q4k_bf16_kernel<N_TILE><<<grid, kGemmThreads, gemm_smem_bytes(N_TILE), st>>>(
-        w.units, map, ymap, tma_store, y, (int)w.rows, (int)w.nblk, (int)m, ldy, (int)w.row_tiles(), err);
-    FERRIC_CUDA_TRY(cudaGetLastError());
+    unsigned gx = (unsigned)((w.rows + kGemmRows - 1) / kGemmRows);
+    if (PAIR) gx = (gx + 1) & ~1u;   // whole pairs; a padding CTA multiplies zeros and stores nothing
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(gx, (unsigned)((m + N_TILE - 1) / N_TILE));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FERRIC_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_q4k_bf16_kernel<N_TILE, PAIR>, (const uint8_t*)w.units, map, ymap, tma_store, y,
+                                       (int)w.rows, (int)w.nblk, (int)m, ldy, (int)w.row_tiles(), err));
     return kOk;
+}
+
+// FERRIC_CUDA_GEMM_PAIR=0 keeps every tile on a single CTA (for comparison runs).
+bool gemm_pair_enabled()
+{
+    static const bool on = [] {
+        const char* e = getenv("FERRIC_CUDA_GEMM_PAIR");
+        return !(e && e[0] == '0');
+    }();
+    return on;
 }
 }  // namespace
 
@@ -564,10 +658,11 @@ int32_t launch_gemm_q4k_bf16(cudaStream_t st, const DeviceWeights& w, const uint
         return kErrCuda;
     }
     const int n_tile = m <= 128 ? 128 : (m <= 256 ? 256 : 512);
+    const bool pair = n_tile == 512 && gemm_pair_enabled();   // two CTAs share each activation tile
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)w.cols, (cuuint64_t)m};
     const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kGemmChunkK, (cuuint32_t)(n_tile > 256 ? 256 : n_tile)};
+    const cuuint32_t box[2] = {(cuuint32_t)kGemmChunkK, (cuuint32_t)(pair ? 128 : (n_tile > 256 ? 256 : n_tile))};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(x_bf16), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -593,9 +688,10 @@ int32_t launch_gemm_q4k_bf16(cudaStream_t st, const DeviceWeights& w, const uint
         }
         tma_store = 1;
     }
-    if (n_tile == 128) return launch_gemm_tile<128>(st, w, map, ymap, tma_store, m, y, ldy);
-    if (n_tile == 256) return launch_gemm_tile<256>(st, w, map, ymap, tma_store, m, y, ldy);
-    return launch_gemm_tile<512>(st, w, map, ymap, tma_store, m, y, ldy);
+    if (n_tile == 128) return launch_gemm_tile<128, false>(st, w, map, ymap, tma_store, m, y, ldy);
+    if (n_tile == 256) return launch_gemm_tile<256, false>(st, w, map, ymap, tma_store, m, y, ldy);
+    if (!pair) return launch_gemm_tile<512, false>(st, w, map, ymap, tma_store, m, y, ldy);
+    return launch_gemm_tile<512, true>(st, w, map, ymap, tma_store, m, y, ldy);
 }
 
 // Synchronises the stream, returns the code of the first bounded wait that ran out (0 = none) and clears it.
@@ -610,10 +706,3 @@ int32_t gemm_status(cudaStream_t st, int* code)
 }
 
 }  // namespace ferric
-
-#if FERRIC_GEMM_EXP == 9
-extern "C" int ferric_debug_gemm_trace(unsigned long long* out128)
-{
-    return (int)cudaMemcpyFromSymbol(out128, ferric::g_gemm_trace, sizeof(unsigned long long) * 128);
-}
-#endif

@@ -86,7 +86,9 @@ def check(F, ctx, rows, cols, m, seed, oracle_rows=None):
     (144, 768, 40),       # ragged: rows not a multiple of 128, batch below one tile
     (16, 256, 1),         # smallest legal matrix
     (50, 512, 40),        # result pitch not a multiple of 16 bytes: element-wise epilogue instead of TMA stores
-    (1000, 2048, 300),    # ragged rows and two N tiles with a partial one
+    (1000, 2048, 300),    # ragged rows; above 256 activation rows two CTAs pair up on a 256 x 512 tile
+    (384, 512, 260),      # an odd number of 128-row tiles: the last pair has a padding CTA
+    (128, 256, 700),      # one real CTA, its pair partner all padding, two N tiles
 ])
 def test_small_shapes(F, ctx, rows, cols, m):
     rel = check(F, ctx, rows, cols, m, seed=rows + cols + m)
