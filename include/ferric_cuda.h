@@ -203,10 +203,12 @@ int32_t ferric_cuda_matmul_q_noalloc(ferric_cuda_ctx *ctx, const ferric_qmatrix 
  * (raw bf16 bits, 16-byte aligned) and the weights dequantised to bf16, round to nearest even.
  * Replaces the reference's cooperative-matrix prefill kernel Tensor::matmul_q4_k_coop
  * (crates/ferric-tensor/src/dtype.rs:1818-1834, WGSL :2059-2096), which dequantises weight tiles
- * into workgroup memory and multiplies them with 8x8x8 subgroup-matrix ops; here the tile is
- * 128 weight rows x 256 activation rows x 64 and the multiply is tcgen05.mma with the f32
- * accumulator in tensor memory.  Q4_K only (other types return FERRIC_UNSUPPORTED); any m >= 1
- * works but the kernel is meant for m >= 128.  Asynchronous on the context's stream. */
+ * into workgroup memory and multiplies them with 8x8x8 subgroup-matrix ops; here a CTA (above
+ * 256 activation rows: a pair of CTAs) owns 128 (256) weight rows x up to 512 activation rows,
+ * K advances in chunks of 64, and the multiply is tcgen05.mma with the f32 accumulator in tensor
+ * memory.  Q4_K only (other types return FERRIC_UNSUPPORTED); any m >= 1 works but the kernel is
+ * meant for m >= 128.  Asynchronous on the context's stream.  FERRIC_CUDA_GEMM_PAIR=0 in the
+ * environment keeps every tile on a single CTA. */
 int32_t ferric_cuda_matmul_q_bf16(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const uint16_t *x_bf16_dev, size_t m,
                                   size_t x_cols, float *y_dev);
 
