@@ -48,7 +48,9 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--prefill", type=int, default=0, metavar="M",
                     help="time only the tensor-core prefill product (Q4_K x bf16, M activation rows) and print its line")
-    ap.add_argument("--prefill-rows", type=int, default=34816, help="weight rows of the --prefill matrix (x 5120 columns)")
+    ap.add_argument("--prefill-rows", type=int, default=34816, help="weight rows of the --prefill matrix")
+    ap.add_argument("--prefill-cols", type=int, default=5120, help="columns (K) of the --prefill matrix")
+    ap.add_argument("--prefill-type", type=int, default=12, choices=[12, 14], help="ggml type of the --prefill matrix")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="N > 1: the library's own peer-memory exchange (default) or NCCL through torch.distributed")
     return ap.parse_args()
@@ -298,6 +300,8 @@ def run_ours(args):
         extras = per_matrix_table(torch, ctx, stack, QMatrix, B, peak)
         extras["prefill_q4k_bf16_34816x5120"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, stack.layers[0].wgu, m, 5)
                                                  for m in (128, 512, 2048)}
+        extras["prefill_q6k_bf16_5120x17408"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, stack.layers[0].wdown, m, 5)
+                                                 for m in (512, 2048)}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -421,17 +425,17 @@ def run_prefill(args):
     from ferric_b200 import Context, QMatrix, synth
     torch.cuda.set_device(0)
     ctx = Context(0)
-    rows, cols, m = args.prefill_rows, 5120, args.prefill
-    raw = synth.matrix_on_device(12, rows, cols, 1, torch.device("cuda:0"))
-    w = QMatrix.from_device_bytes(ctx, raw, 12, rows, cols)
+    rows, cols, m, ty = args.prefill_rows, args.prefill_cols, args.prefill, args.prefill_type
+    raw = synth.matrix_on_device(ty, rows, cols, 1, torch.device("cuda:0"))
+    w = QMatrix.from_device_bytes(ctx, raw, ty, rows, cols)
     with ClockSampler(0) as clocks:
         r = prefill_case(torch, ctx, QMatrix, w, m, max(args.steps, 1))
     burst, _, kind = bf16_peaks()
     print(json.dumps({
         "metric": "prefill_tflops", "value": r["TFLOP/s"], "unit": "TFLOP/s", "n_gpus": 1, "steps": max(args.steps, 1),
         "warmup": 3, "ms_per_step": r["us"] / 1e3, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"Q4_K [{rows}x{cols}] x bf16 [{m}x{cols}] -> f32, weights dequantised in-kernel"},
-        "roofline": {"kernel": "gemm_q4k_bf16_kernel", "bound": "tensor", "achieved": r["TFLOP/s"], "peak": burst,
+        "config": {"workload": f"{'Q4_K' if ty == 12 else 'Q6_K'} [{rows}x{cols}] x bf16 [{m}x{cols}] -> f32, weights dequantised in-kernel"},
+        "roofline": {"kernel": "gemm_q_bf16_kernel", "bound": "tensor", "achieved": r["TFLOP/s"], "peak": burst,
                      "unit": "TFLOP/s", "frac": r["TFLOP/s"] / burst, "peak_source": kind, "traffic": None},
         "gpu_launches": max(args.steps, 1), "clocks": clocks.summary(), "output_finite": r["finite"]}), flush=True)
 

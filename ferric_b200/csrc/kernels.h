@@ -73,10 +73,10 @@ int32_t launch_swiglu(cudaStream_t st, const float* gu, size_t t, size_t d, floa
 int32_t launch_add_rmsnorm(cudaStream_t st, const float* a, const float* b, const float* weight, float eps,
                            size_t rows, size_t d, float* sum, float* norm, const GemvTuning& tune);
 
-// Prefill product on the tcgen05 tensor cores: y[m, rows] (f32, row stride ldy) = x . W^T with Q4_K weights
+// Prefill product on the tcgen05 tensor cores: y[m, rows] (f32, row stride ldy) = x . W^T with Q4_K or Q6_K weights
 // dequantised to bf16 (round to nearest even) and bf16 activations x[m, cols] (row stride ldx elements).
-int32_t launch_gemm_q4k_bf16(cudaStream_t st, const DeviceWeights& w, const uint16_t* x_bf16, size_t m, size_t ldx,
-                             float* y, size_t ldy);
+int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint16_t* x_bf16, size_t m, size_t ldx,
+                         float* y, size_t ldy);
 // Synchronise the stream and fetch-and-clear the code a GEMM CTA left when one of its bounded waits ran out.
 int32_t gemm_status(cudaStream_t st, int* code);
 

@@ -40,7 +40,9 @@ constexpr int kGemmDeqWarps = 8;      // one per 16-row unit of the 128-row tile
 constexpr int kGemmHalves = 2;        // the two 8-row halves of its unit a dequant warp converts
 constexpr int kGemmFirstDeqWarp = 3;                   // warp 0 weight producer, 1 MMA issuer, 2 activation producer
 constexpr int kGemmThreads = 32 * (kGemmFirstDeqWarp + kGemmDeqWarps);
-constexpr int kGemmRawBytes = 8 * kQ4KUnit;                   // 18432: 8 row tiles x one super-block
+// raw quant bytes of one stage: 8 row tiles x one super-block (18432 for Q4_K, 26880 for Q6_K)
+__host__ __device__ constexpr int gemm_unit_bytes(uint32_t ty) { return ty == kGgmlQ4K ? kQ4KUnit : kQ6KUnit; }
+__host__ __device__ constexpr int gemm_raw_bytes(uint32_t ty) { return 8 * gemm_unit_bytes(ty); }
 constexpr int kGemmABytes = kGemmRows * 128;                  // 16384 per stage
 constexpr int kGemmStoreBytes = 32 * kGemmRows * 4;            // one [32 activation rows][128 weight rows] f32 store tile
 constexpr unsigned long long kGemmWaitNs = 1000000000ull;     // every mbarrier wait gives up after one second
@@ -52,20 +54,29 @@ __host__ __device__ constexpr int gemm_b_bytes(int n_tile, bool pair = false) { 
 // bounds the kernel at small N is bytes in flight (a stage's round trip through TMA and L2 is over a microsecond),
 // so the ring is as deep as it can be: 8 stages at N 128, 4 at 256, 2 at 512.
 constexpr int kGemmSmemMax = 232448;  // 227 KB per CTA
-constexpr int kGemmFixedBytes = 1024 /*align*/ + 256 /*barriers*/ + kGemmStages * kGemmABytes + kGemmRawStages * kGemmRawBytes;
 constexpr int kGemmMaxBStages = 8;
-__host__ __device__ constexpr int gemm_b_stages(int n_tile, bool pair = false)
+__host__ __device__ constexpr int gemm_fixed_bytes(uint32_t ty)
 {
-    return (kGemmSmemMax - kGemmFixedBytes) / gemm_b_bytes(n_tile, pair) > kGemmMaxBStages
+    return 1024 /*align*/ + 256 /*barriers*/ + kGemmStages * kGemmABytes + kGemmRawStages * gemm_raw_bytes(ty);
+}
+__host__ __device__ constexpr int gemm_b_stages(uint32_t ty, int n_tile, bool pair)
+{
+    return (kGemmSmemMax - gemm_fixed_bytes(ty)) / gemm_b_bytes(n_tile, pair) > kGemmMaxBStages
                ? kGemmMaxBStages
-               : (kGemmSmemMax - kGemmFixedBytes) / gemm_b_bytes(n_tile, pair);
+               : (kGemmSmemMax - gemm_fixed_bytes(ty)) / gemm_b_bytes(n_tile, pair);
 }
-__host__ __device__ constexpr int gemm_smem_bytes(int n_tile, bool pair = false)
+__host__ __device__ constexpr int gemm_smem_bytes(uint32_t ty, int n_tile, bool pair)
 {
-    return kGemmFixedBytes + gemm_b_stages(n_tile, pair) * gemm_b_bytes(n_tile, pair);
+    return gemm_fixed_bytes(ty) + gemm_b_stages(ty, n_tile, pair) * gemm_b_bytes(n_tile, pair);
 }
-static_assert(gemm_b_stages(128) == 8 && gemm_b_stages(256) == 4 && gemm_b_stages(512) == 2 && gemm_b_stages(512, true) == 4,
-              "stage counts");
+static_assert(gemm_b_stages(kGgmlQ4K, 128, false) == 8 && gemm_b_stages(kGgmlQ4K, 256, false) == 4 &&
+                  gemm_b_stages(kGgmlQ4K, 512, false) == 2 && gemm_b_stages(kGgmlQ4K, 512, true) == 4,
+              "Q4_K stage counts");
+static_assert(gemm_b_stages(kGgmlQ6K, 128, false) == 7 && gemm_b_stages(kGgmlQ6K, 256, false) == 3 &&
+                  gemm_b_stages(kGgmlQ6K, 512, true) == 3,
+              "Q6_K stage counts");
+// The epilogue stages its stores in the activation ring: two groups x two [32][128] f32 tiles.
+static_assert(gemm_b_stages(kGgmlQ6K, 256, false) * gemm_b_bytes(256) >= 4 * 32 * 128 * 4, "store staging fits");
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -303,22 +314,206 @@ __device__ __forceinline__ uint4 deq8(uint32_t w0, uint32_t w1, float d1, float 
     return o;
 }
 
-template <int N_TILE, bool PAIR>
+// ---------------------------------------------------------------- dequant stages
+// One call per dequant warp: for every super-block, wait for its raw units, pull this warp's 16-row unit into
+// registers, and for each of its four K chunks convert 16 rows x 64 weights to bf16, wait for a free A stage,
+// store, and announce it.  Returns 0, or the code of the wait that ran out.
+template <bool PAIR>
+__device__ __forceinline__ int dequant_loop_q4k(GemmBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, int nblk,
+                                                int tiles_here, int wq, int lane)
+{
+    // ---------------- dequantise: warp = one 16-row unit (or eight rows of it), lane = (row g, 8-byte piece t)
+    // The lane -> (g, t) map keeps both the 16-byte loads of the raw unit and the 16-byte stores into the
+    // swizzled A tile free of bank conflicts: the two rows of a quarter-warp differ in bits 0 and 2.
+    const int wd = wq;
+    int fail = 0;
+    const int t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
+    const bool unit_ok = wd < tiles_here;
+    const uint32_t arow_off = (uint32_t)(2 * wd * 1024 + g * 128);
+    const uint32_t col_lo = (uint32_t)((t ^ g) << 4), col_hi = (uint32_t)(((4 + t) ^ g) << 4);
+    for (int b = 0; b < nblk && !fail; b++) {
+        const int rs = b % kGemmRawStages;
+        if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)b / kGemmRawStages) & 1u)) { fail = 4; break; }
+        const uint8_t* u = raw_stage + rs * (8 * kQ4KUnit) + wd * kQ4KUnit;
+        uint4 hdr[kGemmHalves], qs[kGemmHalves][2];
+        float d[kGemmHalves], dmin[kGemmHalves];
+#pragma unroll
+        for (int hh = 0; hh < kGemmHalves; hh++) {
+            const int hi = hh;
+            hdr[hh] = qs[hh][0] = qs[hh][1] = make_uint4(0, 0, 0, 0);
+            if (unit_ok) {
+                hdr[hh] = *reinterpret_cast<const uint4*>(u + 16 * (g + 8 * hi));
+                qs[hh][0] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi) + 16 * (4 * g + t));
+                qs[hh][1] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi + 1) + 16 * (4 * g + t));
+            }
+            d[hh] = __half2float(__ushort_as_half((unsigned short)(hdr[hh].x & 0xffffu)));
+            dmin[hh] = __half2float(__ushort_as_half((unsigned short)(hdr[hh].x >> 16)));
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar->raw_empty[rs]);   // the block now lives in registers
+        // The four lanes of a row share its header: lane t works out (d*sc, dmin*m) of the two sub-blocks of
+        // chunk t once, and every chunk fetches its pair from the lane that holds it.
+        float my_d1a[kGemmHalves], my_mma[kGemmHalves], my_d1b[kGemmHalves], my_mmb[kGemmHalves];
+#pragma unroll
+        for (int hh = 0; hh < kGemmHalves; hh++) {
+            uint32_t sc0, mn0, sc1, mn1;
+            q4k_scale_min_dyn(hdr[hh], 2 * t, sc0, mn0);
+            q4k_scale_min_dyn(hdr[hh], 2 * t + 1, sc1, mn1);
+            my_d1a[hh] = __fmul_rn(d[hh], small_u32_to_float(sc0));
+            my_mma[hh] = __fmul_rn(dmin[hh], small_u32_to_float(mn0));
+            my_d1b[hh] = __fmul_rn(d[hh], small_u32_to_float(sc1));
+            my_mmb[hh] = __fmul_rn(dmin[hh], small_u32_to_float(mn1));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint4 lo[kGemmHalves], up[kGemmHalves];
+            const int src = (lane & ~3) | j;
+#pragma unroll
+            for (int hh = 0; hh < kGemmHalves; hh++) {
+                const float d1a = __shfl_sync(0xffffffffu, my_d1a[hh], src), mma = __shfl_sync(0xffffffffu, my_mma[hh], src);
+                const float d1b = __shfl_sync(0xffffffffu, my_d1b[hh], src), mmb = __shfl_sync(0xffffffffu, my_mmb[hh], src);
+                const uint4 q4 = qs[hh][j >> 1];
+                const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
+                lo[hh] = deq8(w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, d1a, mma);
+                up[hh] = deq8((w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, d1b, mmb);
+            }
+            const int c = 4 * b + j, s = c % kGemmStages;
+            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
+            uint8_t* arow = a_stage + s * kGemmABytes + arow_off;
+#pragma unroll
+            for (int hh = 0; hh < kGemmHalves; hh++) {
+                *reinterpret_cast<uint4*>(arow + hh * 1024 + col_lo) = lo[hh];
+                *reinterpret_cast<uint4*>(arow + hh * 1024 + col_hi) = up[hh];
+            }
+            fence_proxy_async();     // generic-proxy stores -> visible to the tensor core's async reads
+            __syncwarp();
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
+                else mbar_arrive(&bar->a_full[s]);
+            }
+        }
+    }
+    return fail;
+}
+
+// Four Q6_K weights (one 6-bit value in each byte of q) -> bf16 of t * (q - 32), t = d * scale, in the reference
+// decoder's order (crates/ferric-gguf/src/lib.rs:721-746: (d * sc) * (q - 32)): q - 32 first (exact; +0 at q = 32),
+// then the product (exact in f32: 18 x 6 bits, and with the decoder's sign of zero), then the rounding to bf16.
+__device__ __forceinline__ uint2 deq4_q6(uint32_t q, float t)
+{
+    const uint64_t tt = pack_f32x2(t, t), mg = pack_f32x2(-8388640.f, -8388640.f);   // -(2^23 + 32)
+    auto two = [&](int e) {
+        const uint64_t f = pack_f32x2(__uint_as_float(__byte_perm(q, 0x4B000000u, 0x7650 + e)),
+                                      __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7651 + e)));
+        uint64_t qm, v;
+        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(qm) : "l"(f), "l"(mg));
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(tt), "l"(qm));
+        float lo, hi;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+        uint32_t r;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+        return r;
+    };
+    return make_uint2(two(0), two(2));
+}
+
+// Q6_K unit (layout.h): d pairs | int8 scales [16 rows][16] | ql: 4 segments (2 * half + c) | qh: 2 segments.
+// Lane (g, t) holds, per row, ql words (c, h, is) = raw ql bytes [64h + 32c + 16is + 4t, +4) and qh words
+// (h, is) = raw qh bytes [32h + 16is + 4t, +4).  K chunk j = (h, kp) = (j >> 1, j & 1) takes sub-blocks
+// k = 2kp + c: nibble kp of the ql word, bits 2k..2k+1 of the qh word, chunk-local position 32c + 16is + 4t.
+template <bool PAIR>
+__device__ __forceinline__ int dequant_loop_q6k(GemmBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, int nblk,
+                                                int tiles_here, int wq, int lane)
+{
+    const int wd = wq;
+    int fail = 0;
+    const int t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
+    const bool unit_ok = wd < tiles_here;
+    const uint32_t arow_off = (uint32_t)(2 * wd * 1024 + g * 128);
+    for (int b = 0; b < nblk && !fail; b++) {
+        const int rs = b % kGemmRawStages;
+        if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)b / kGemmRawStages) & 1u)) { fail = 4; break; }
+        const uint8_t* u = raw_stage + rs * (8 * kQ6KUnit) + wd * kQ6KUnit;
+        uint4 ql[2][2], qh[2], sc[2];
+        uint32_t dpair = 0;
+#pragma unroll
+        for (int hi = 0; hi < 2; hi++) {
+            ql[hi][0] = ql[hi][1] = qh[hi] = sc[hi] = make_uint4(0, 0, 0, 0);
+            if (unit_ok) {
+                ql[hi][0] = *reinterpret_cast<const uint4*>(u + kQ6KOffQl + 512 * (2 * hi) + 16 * (4 * g + t));
+                ql[hi][1] = *reinterpret_cast<const uint4*>(u + kQ6KOffQl + 512 * (2 * hi + 1) + 16 * (4 * g + t));
+                qh[hi] = *reinterpret_cast<const uint4*>(u + kQ6KOffQh + 512 * hi + 16 * (4 * g + t));
+                sc[hi] = *reinterpret_cast<const uint4*>(u + kQ6KOffSc + 16 * (g + 8 * hi));
+            }
+        }
+        if (unit_ok) dpair = *reinterpret_cast<const uint32_t*>(u + 4 * g);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar->raw_empty[rs]);   // the block now lives in registers
+        // Lane t works out d * scale for the four sub-blocks of chunk t (scale bytes 4t .. 4t+3 = word t of the
+        // row's 16, byte 2c + is); every chunk fetches its four from the lane that holds them.
+        float my_t[2][4];
+#pragma unroll
+        for (int hi = 0; hi < 2; hi++) {
+            const float d = __half2float(__ushort_as_half((unsigned short)(hi ? (dpair >> 16) : (dpair & 0xffffu))));
+            const uint32_t w = t == 0 ? sc[hi].x : (t == 1 ? sc[hi].y : (t == 2 ? sc[hi].z : sc[hi].w));
+#pragma unroll
+            for (int i = 0; i < 4; i++) my_t[hi][i] = __fmul_rn(d, (float)(int)(int8_t)(w >> (8 * i)));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int h = j >> 1, kp = j & 1, src = (lane & ~3) | j;
+            uint2 out[2][4];
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+#pragma unroll
+                    for (int is = 0; is < 2; is++) {
+                        const float tv = __shfl_sync(0xffffffffu, my_t[hi][2 * c + is], src);
+                        const uint4 qlv = ql[hi][c];
+                        const uint32_t lw = (2 * h + is) == 0 ? qlv.x : ((2 * h + is) == 1 ? qlv.y : ((2 * h + is) == 2 ? qlv.z : qlv.w));
+                        const uint32_t hw = (2 * h + is) == 0 ? qh[hi].x : ((2 * h + is) == 1 ? qh[hi].y : ((2 * h + is) == 2 ? qh[hi].z : qh[hi].w));
+                        const uint32_t q = ((lw >> (4 * kp)) & 0x0F0F0F0Fu) | (((hw >> (2 * (2 * kp + c))) & 0x03030303u) << 4);
+                        out[hi][2 * c + is] = deq4_q6(q, tv);
+                    }
+                }
+            }
+            const int c4 = 4 * b + j, s = c4 % kGemmStages;
+            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c4 / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
+            uint8_t* arow = a_stage + s * kGemmABytes + arow_off;
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++)
+#pragma unroll
+                for (int i = 0; i < 4; i++)   // i = 2c + is: 16-byte column 2i + (t >> 1), half t & 1
+                    *reinterpret_cast<uint2*>(arow + hi * 1024 + (((2 * i + (t >> 1)) ^ g) << 4) + 8 * (t & 1)) = out[hi][i];
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
+                else mbar_arrive(&bar->a_full[s]);
+            }
+        }
+    }
+    return fail;
+}
+
+template <uint32_t TY, int N_TILE, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap,
+gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap,
                      const __grid_constant__ CUtensorMap ymap, int tma_store, float* __restrict__ y, int rows, int nblk, int m,
                      size_t ldy, int row_tiles16, int* __restrict__ err)
 {
     extern __shared__ uint8_t gemm_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* a_stage = smem;                                               // [S][16384]
-    constexpr int kBStages = gemm_b_stages(N_TILE, PAIR), kBBytes = gemm_b_bytes(N_TILE, PAIR);
+    constexpr int kBStages = gemm_b_stages(TY, N_TILE, PAIR), kBBytes = gemm_b_bytes(N_TILE, PAIR);
+    constexpr int kUnit = gemm_unit_bytes(TY), kRawBytes = gemm_raw_bytes(TY);
     constexpr int kNMma = N_TILE > 256 ? 256 : N_TILE;                     // activation rows per tcgen05.mma
     constexpr int kBoxRows = PAIR ? kNMma / 2 : kNMma;                     // of them, rows this CTA holds
     constexpr int kPeers = PAIR ? 2 : 1;
     uint8_t* b_stage = a_stage + kGemmStages * kGemmABytes;                // [kBStages][kBBytes]
     uint8_t* raw_stage = b_stage + kBStages * kBBytes;                     // [2][18432]
-    GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(raw_stage + kGemmRawStages * kGemmRawBytes);
+    GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(raw_stage + kGemmRawStages * kRawBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * kGemmRows, n0 = blockIdx.y * N_TILE;
@@ -370,10 +565,10 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
             for (int b = 0; b < nblk; b++) {
                 const int rs = b % kGemmRawStages;
                 if (!mbar_wait(&bar->raw_empty[rs], (((uint32_t)b / kGemmRawStages) & 1u) ^ 1u)) { fail = 1; break; }
-                mbar_expect_tx(&bar->raw_full[rs], (uint32_t)(tiles_here * kQ4KUnit));
+                mbar_expect_tx(&bar->raw_full[rs], (uint32_t)(tiles_here * kUnit));
                 for (int t = 0; t < tiles_here; t++)
-                    bulk_g2s(raw_stage + rs * kGemmRawBytes + t * kQ4KUnit, units + ((size_t)(rt0 + t) * nblk + b) * kQ4KUnit,
-                             kQ4KUnit, &bar->raw_full[rs]);
+                    bulk_g2s(raw_stage + rs * kRawBytes + t * kUnit, units + ((size_t)(rt0 + t) * nblk + b) * kUnit, kUnit,
+                             &bar->raw_full[rs]);
             }
         }
     } else if (warp == 2) {
@@ -431,76 +626,10 @@ gemm_q4k_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ 
             }
         }
     } else {
-        // ---------------- dequantise: warp = one 16-row unit (or eight rows of it), lane = (row g, 8-byte piece t)
-        // The lane -> (g, t) map keeps both the 16-byte loads of the raw unit and the 16-byte stores into the
-        // swizzled A tile free of bank conflicts: the two rows of a quarter-warp differ in bits 0 and 2.
-        const int wq = warp - kGemmFirstDeqWarp, wd = wq;
-        const int t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
-        const bool unit_ok = wd < tiles_here;
-        const uint32_t arow_off = (uint32_t)(2 * wd * 1024 + g * 128);
-        const uint32_t col_lo = (uint32_t)((t ^ g) << 4), col_hi = (uint32_t)(((4 + t) ^ g) << 4);
-        for (int b = 0; b < nblk && !fail; b++) {
-            const int rs = b % kGemmRawStages;
-            if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)b / kGemmRawStages) & 1u)) { fail = 4; break; }
-            const uint8_t* u = raw_stage + rs * kGemmRawBytes + wd * kQ4KUnit;
-            uint4 hdr[kGemmHalves], qs[kGemmHalves][2];
-            float d[kGemmHalves], dmin[kGemmHalves];
-#pragma unroll
-            for (int hh = 0; hh < kGemmHalves; hh++) {
-                const int hi = hh;
-                hdr[hh] = qs[hh][0] = qs[hh][1] = make_uint4(0, 0, 0, 0);
-                if (unit_ok) {
-                    hdr[hh] = *reinterpret_cast<const uint4*>(u + 16 * (g + 8 * hi));
-                    qs[hh][0] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi) + 16 * (4 * g + t));
-                    qs[hh][1] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi + 1) + 16 * (4 * g + t));
-                }
-                d[hh] = __half2float(__ushort_as_half((unsigned short)(hdr[hh].x & 0xffffu)));
-                dmin[hh] = __half2float(__ushort_as_half((unsigned short)(hdr[hh].x >> 16)));
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar->raw_empty[rs]);   // the block now lives in registers
-            // The four lanes of a row share its header: lane t works out (d*sc, dmin*m) of the two sub-blocks of
-            // chunk t once, and every chunk fetches its pair from the lane that holds it.
-            float my_d1a[kGemmHalves], my_mma[kGemmHalves], my_d1b[kGemmHalves], my_mmb[kGemmHalves];
-#pragma unroll
-            for (int hh = 0; hh < kGemmHalves; hh++) {
-                uint32_t sc0, mn0, sc1, mn1;
-                q4k_scale_min_dyn(hdr[hh], 2 * t, sc0, mn0);
-                q4k_scale_min_dyn(hdr[hh], 2 * t + 1, sc1, mn1);
-                my_d1a[hh] = __fmul_rn(d[hh], small_u32_to_float(sc0));
-                my_mma[hh] = __fmul_rn(dmin[hh], small_u32_to_float(mn0));
-                my_d1b[hh] = __fmul_rn(d[hh], small_u32_to_float(sc1));
-                my_mmb[hh] = __fmul_rn(dmin[hh], small_u32_to_float(mn1));
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                uint4 lo[kGemmHalves], up[kGemmHalves];
-                const int src = (lane & ~3) | j;
-#pragma unroll
-                for (int hh = 0; hh < kGemmHalves; hh++) {
-                    const float d1a = __shfl_sync(0xffffffffu, my_d1a[hh], src), mma = __shfl_sync(0xffffffffu, my_mma[hh], src);
-                    const float d1b = __shfl_sync(0xffffffffu, my_d1b[hh], src), mmb = __shfl_sync(0xffffffffu, my_mmb[hh], src);
-                    const uint4 q4 = qs[hh][j >> 1];
-                    const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
-                    lo[hh] = deq8(w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, d1a, mma);
-                    up[hh] = deq8((w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, d1b, mmb);
-                }
-                const int c = 4 * b + j, s = c % kGemmStages;
-                if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
-                uint8_t* arow = a_stage + s * kGemmABytes + arow_off;
-#pragma unroll
-                for (int hh = 0; hh < kGemmHalves; hh++) {
-                    *reinterpret_cast<uint4*>(arow + hh * 1024 + col_lo) = lo[hh];
-                    *reinterpret_cast<uint4*>(arow + hh * 1024 + col_hi) = up[hh];
-                }
-                fence_proxy_async();     // generic-proxy stores -> visible to the tensor core's async reads
-                __syncwarp();
-                if (lane == 0) {
-                    if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
-                    else mbar_arrive(&bar->a_full[s]);
-                }
-            }
-        }
+        // ---------------- dequantise (per quant type, above), then the epilogue
+        const int wq = warp - kGemmFirstDeqWarp;
+        if (TY == kGgmlQ4K) fail = dequant_loop_q4k<PAIR>(bar, a_stage, raw_stage, nblk, tiles_here, wq, lane);
+        else fail = dequant_loop_q6k<PAIR>(bar, a_stage, raw_stage, nblk, tiles_here, wq, lane);
         // ---------------- epilogue.  All dequant warps first agree that nobody gave up (the staged path below
         // synchronises them with named barriers, which must not be entered by only some of them).
         if (fail) atomicExch(&bar->abort, fail);
@@ -600,16 +729,16 @@ EncodeTiledFn encode_tiled_fn()
     return fn;
 }
 
-template <int N_TILE, bool PAIR>
+template <uint32_t TY, int N_TILE, bool PAIR>
 int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& ymap, int tma_store,
                          size_t m, float* y, size_t ldy)
 {
     static bool attr_done[64] = {};
     int dev = 0;
     FERRIC_CUDA_TRY(cudaGetDevice(&dev));
-    constexpr int smem = gemm_smem_bytes(N_TILE, PAIR);
+    constexpr int smem = gemm_smem_bytes(TY, N_TILE, PAIR);
     if (dev < 64 && !attr_done[dev]) {
-        FERRIC_CUDA_TRY(cudaFuncSetAttribute(gemm_q4k_bf16_kernel<N_TILE, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        FERRIC_CUDA_TRY(cudaFuncSetAttribute(gemm_q_bf16_kernel<TY, N_TILE, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_done[dev] = true;
     }
     int* err = nullptr;
@@ -628,7 +757,7 @@ int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensor
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    FERRIC_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_q4k_bf16_kernel<N_TILE, PAIR>, (const uint8_t*)w.units, map, ymap, tma_store, y,
+    FERRIC_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_q_bf16_kernel<TY, N_TILE, PAIR>, (const uint8_t*)w.units, map, ymap, tma_store, y,
                                        (int)w.rows, (int)w.nblk, (int)m, ldy, (int)w.row_tiles(), err));
     return kOk;
 }
@@ -644,9 +773,20 @@ bool gemm_pair_enabled()
 }
 }  // namespace
 
-int32_t launch_gemm_q4k_bf16(cudaStream_t st, const DeviceWeights& w, const uint16_t* x_bf16, size_t m, size_t ldx, float* y,
-                             size_t ldy)
+template <uint32_t TY>
+static int32_t launch_gemm_ty(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& ymap, int tma_store,
+                              size_t m, float* y, size_t ldy, int n_tile, bool pair)
 {
+    if (n_tile == 128) return launch_gemm_tile<TY, 128, false>(st, w, map, ymap, tma_store, m, y, ldy);
+    if (n_tile == 256) return launch_gemm_tile<TY, 256, false>(st, w, map, ymap, tma_store, m, y, ldy);
+    if (!pair) return launch_gemm_tile<TY, 512, false>(st, w, map, ymap, tma_store, m, y, ldy);
+    return launch_gemm_tile<TY, 512, true>(st, w, map, ymap, tma_store, m, y, ldy);
+}
+
+int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint16_t* x_bf16, size_t m, size_t ldx,
+                         float* y, size_t ldy)
+{
+    if (ty != kGgmlQ4K && ty != kGgmlQ6K) return kUnsupported;
     if (m == 0 || w.rows == 0 || w.nblk == 0) return kOk;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (ldx * 2) % 16 != 0) {
         set_last_error("bf16 activations must be 16-byte aligned with a row stride that is a multiple of 8 elements");
@@ -688,10 +828,8 @@ int32_t launch_gemm_q4k_bf16(cudaStream_t st, const DeviceWeights& w, const uint
         }
         tma_store = 1;
     }
-    if (n_tile == 128) return launch_gemm_tile<128, false>(st, w, map, ymap, tma_store, m, y, ldy);
-    if (n_tile == 256) return launch_gemm_tile<256, false>(st, w, map, ymap, tma_store, m, y, ldy);
-    if (!pair) return launch_gemm_tile<512, false>(st, w, map, ymap, tma_store, m, y, ldy);
-    return launch_gemm_tile<512, true>(st, w, map, ymap, tma_store, m, y, ldy);
+    return ty == kGgmlQ4K ? launch_gemm_ty<kGgmlQ4K>(st, w, map, ymap, tma_store, m, y, ldy, n_tile, pair)
+                          : launch_gemm_ty<kGgmlQ6K>(st, w, map, ymap, tma_store, m, y, ldy, n_tile, pair);
 }
 
 // Synchronises the stream, returns the code of the first bounded wait that ran out (0 = none) and clears it.

@@ -1,4 +1,4 @@
-"""GPU parity of the tensor-core prefill product (Q4_K weights x bf16 activations).
+"""GPU parity of the tensor-core prefill product (Q4_K / Q6_K weights x bf16 activations).
 
 The reference product for this configuration is: weights dequantised with the reference decoder and
 rounded to bf16 (nearest even), activations bf16, f32 accumulation.  The tensor core sums in a
@@ -43,35 +43,35 @@ def bf16_to_f64(bits):
     return (np.asarray(bits, dtype=np.uint32) << 16).view(np.float32).astype(np.float64)
 
 
-def make_case(rows, cols, m, seed):
+def make_case(rows, cols, m, seed, ty=12):
     rng = np.random.default_rng(seed)
-    raw = synth.q4k_blocks(rng, rows * cols // 256)
+    raw = (synth.q4k_blocks if ty == 12 else synth.q6k_blocks)(rng, rows * cols // 256)
     x = torch.from_numpy(rng.standard_normal((m, cols), dtype=np.float32)).to(torch.bfloat16)
     xbits = x.view(torch.int16).numpy().view(np.uint16)
     return raw, x, xbits
 
 
-def exact_bf16_product(raw, rows, cols, xbits):
+def exact_bf16_product(raw, rows, cols, xbits, ty=12):
     """(x . W^T, |x| . |W|^T) in float64 on the bf16 operands."""
-    w = bf16_to_f64(O.deq_raw_bf16(raw, rows * cols, 12)).reshape(rows, cols)
+    w = bf16_to_f64(O.deq_raw_bf16(raw, rows * cols, ty)).reshape(rows, cols)
     x = bf16_to_f64(xbits)
     return x @ w.T, np.abs(x) @ np.abs(w).T
 
 
-def check(F, ctx, rows, cols, m, seed, oracle_rows=None):
-    raw, x, xbits = make_case(rows, cols, m, seed)
-    qm = F.QMatrix.from_bytes(ctx, raw, 12, rows, cols)
+def check(F, ctx, rows, cols, m, seed, oracle_rows=None, ty=12):
+    raw, x, xbits = make_case(rows, cols, m, seed, ty)
+    qm = F.QMatrix.from_bytes(ctx, raw, ty, rows, cols)
     y = qm.matmul_bf16(x.cuda())
     assert qm.gemm_status() == 0
     got = y.cpu().numpy().astype(np.float64)
-    exact, mag = exact_bf16_product(raw, rows, cols, xbits)
+    exact, mag = exact_bf16_product(raw, rows, cols, xbits, ty)
     e = np.abs(got - exact)
     tol = ATOL + RTOL * np.abs(exact) + U_ACC * mag
     w = int(np.argmax(e / tol))
     assert (e <= tol).all(), f"vs exact: worst |d|={e.flat[w]:.3e} at {np.unravel_index(w, e.shape)} (exact {exact.flat[w]:.6g})"
     # the oracle's own sequential f32 sum on a slice of the batch (it is a scalar loop)
     mo = min(m, oracle_rows or m)
-    ref = O.matmul_q(raw, 12, rows, cols, xbits[:mo], threads=8, mode=O.MODE_BF16).astype(np.float64)
+    ref = O.matmul_q(raw, ty, rows, cols, xbits[:mo], threads=8, mode=O.MODE_BF16).astype(np.float64)
     e = np.abs(got[:mo] - ref)
     tol = ATOL + RTOL * np.abs(ref) + U_ACC * mag[:mo] + np.abs(ref - exact[:mo])
     assert (e <= tol).all(), f"vs oracle: worst ratio {(e / tol).max():.3f}"
@@ -79,7 +79,7 @@ def check(F, ctx, rows, cols, m, seed, oracle_rows=None):
     return float(np.abs(got - exact).max() / np.abs(exact).max())
 
 
-@pytest.mark.parametrize("rows,cols,m", [
+SHAPES = [
     (128, 256, 128),      # one CTA, one super-block
     (128, 1024, 128),     # pipeline wraps around its stages
     (256, 512, 256),      # N tile 256
@@ -89,9 +89,13 @@ def check(F, ctx, rows, cols, m, seed, oracle_rows=None):
     (1000, 2048, 300),    # ragged rows; above 256 activation rows two CTAs pair up on a 256 x 512 tile
     (384, 512, 260),      # an odd number of 128-row tiles: the last pair has a padding CTA
     (128, 256, 700),      # one real CTA, its pair partner all padding, two N tiles
-])
-def test_small_shapes(F, ctx, rows, cols, m):
-    rel = check(F, ctx, rows, cols, m, seed=rows + cols + m)
+]
+
+
+@pytest.mark.parametrize("ty", [12, 14])
+@pytest.mark.parametrize("rows,cols,m", SHAPES)
+def test_small_shapes(F, ctx, rows, cols, m, ty):
+    rel = check(F, ctx, rows, cols, m, seed=rows + cols + m + ty, ty=ty)
     assert rel < 1e-5, rel   # the reference's kernel-test bar, max|d| / max|ref| (examples/q4_k.rs:52-55)
 
 
@@ -101,26 +105,35 @@ def test_prefill_config(F, ctx, m):
     check(F, ctx, 4096, 5120, m, seed=m, oracle_rows=32)
 
 
-def test_dequant_stage_is_bit_exact(F, ctx):
+def test_prefill_down_q6k(F, ctx):
+    """The Q6_K down projection of the same layer (K = 17408), a 1024-row slice, batch 512."""
+    check(F, ctx, 1024, 17408, 512, seed=5, oracle_rows=16, ty=14)
+
+
+@pytest.mark.parametrize("ty", [12, 14])
+def test_dequant_stage_is_bit_exact(F, ctx, ty):
     """x = identity columns: y[i, r] is then exactly the bf16 weight W[r, i] -- the dequant-to-bf16 stage
     inside the kernel must match the oracle's bf16 dequantisation bit for bit."""
     rows, cols = 256, 256
     rng = np.random.default_rng(7)
-    raw = synth.q4k_blocks(rng, rows * cols // 256)
-    qm = F.QMatrix.from_bytes(ctx, raw, 12, rows, cols)
+    raw = (synth.q4k_blocks if ty == 12 else synth.q6k_blocks)(rng, rows * cols // 256)
+    qm = F.QMatrix.from_bytes(ctx, raw, ty, rows, cols)
     x = torch.eye(cols, dtype=torch.bfloat16, device="cuda")
     y = qm.matmul_bf16(x)
     assert qm.gemm_status() == 0
     got = y.cpu().numpy()                                  # [cols, rows]
-    want = (O.deq_raw_bf16(raw, rows * cols, 12).astype(np.uint32) << 16).view(np.float32).reshape(rows, cols)
+    want = (O.deq_raw_bf16(raw, rows * cols, ty).astype(np.uint32) << 16).view(np.float32).reshape(rows, cols)
+    # a weight of -0.0 (Q6_K: q = 32 under a negative scale) reaches y as +0.0: it is summed with the +0.0 products
+    # of the other columns.  Every other value must match bit for bit.
+    want = want + np.float32(0.0)
     assert np.array_equal(np.ascontiguousarray(got.T).view(np.uint32), want.view(np.uint32))
     qm.close()
 
 
 def test_rejects_other_types(F, ctx):
     rng = np.random.default_rng(1)
-    raw = synth.q6k_blocks(rng, 16)
-    qm = F.QMatrix.from_bytes(ctx, raw, 14, 16, 256)
+    raw = synth.q8_0_blocks(rng, 16 * 256 // 32)
+    qm = F.QMatrix.from_bytes(ctx, raw, 8, 16, 256)
     with pytest.raises(F.FerricError):
         qm.matmul_bf16(torch.zeros(4, 256, dtype=torch.bfloat16, device="cuda"))
     qm.close()
