@@ -48,7 +48,7 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--prefill", type=int, default=0, metavar="M",
                     help="time only the tensor-core prefill product (Q4_K x bf16, M activation rows) and print its line")
-    ap.add_argument("--prefill-rows", type=int, default=34816, help="weight rows of the --prefill matrix")
+    ap.add_argument("--prefill-rows", type=int, default=17408, help="weight rows of the --prefill matrix")
     ap.add_argument("--prefill-cols", type=int, default=5120, help="columns (K) of the --prefill matrix")
     ap.add_argument("--prefill-type", type=int, default=12, choices=[12, 14], help="ggml type of the --prefill matrix")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
@@ -298,6 +298,7 @@ def run_ours(args):
     extras = None
     if rank == 0 and world == 1 and not args.no_extras:
         extras = per_matrix_table(torch, ctx, stack, QMatrix, B, peak)
+        extras.update(other_configs(torch, ctx, QMatrix, peak))
         extras["prefill_q4k_bf16_34816x5120"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, stack.layers[0].wgu, m, 5)
                                                  for m in (128, 512, 2048)}
         extras["prefill_q6k_bf16_5120x17408"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, stack.layers[0].wdown, m, 5)
@@ -385,6 +386,47 @@ def per_matrix_table(torch, ctx, stack, QMatrix, B, peak):
         w = getattr(stack.layers[0], attr)
         nbytes = w.nbytes() + x.shape[0] * x.shape[1] * 4 + y.numel() * 4
         out[name] = {"us": us, "GB/s": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak, "launches": 2}
+    return out
+
+
+def other_configs(torch, ctx, QMatrix, peak):
+    """The single-matrix configurations: configs[0] (Q4_K 4096x4096 GEMV, cold: 32 copies = 302 MB cycled, more than
+    twice L2), configs[2] (Q6_K 151936x5120 output head at batch 1 and 64; 638 MB, larger than L2 by itself) and
+    configs[3] (Q4_K 17408x5120 prefill at M = 128 / 512 / 2048)."""
+    from ferric_b200 import synth
+    dev = torch.device("cuda", ctx.device)
+    out = {}
+    # configs[0]
+    rows = cols = 4096
+    ws = [QMatrix.from_device_bytes(ctx, synth.matrix_on_device(12, rows, cols, 100 + i, dev), 12, rows, cols) for i in range(32)]
+    x = torch.randn((1, cols), device=dev)
+    y = torch.empty((1, rows), device=dev)
+
+    def cycle():
+        for w in ws:
+            w.matmul(x, out=y)
+    us = graph_time_us(torch, ctx, cycle, reps=3) / len(ws)
+    nbytes = ws[0].nbytes() + 4 * cols + 4 * rows
+    out["config0_q4k_4096x4096_m1_cold"] = {"us": us, "GB/s": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak,
+                                            "launches": 2}
+    for w in ws:
+        w.close()
+    # configs[2]
+    rows, cols = 151936, 5120
+    head = QMatrix.from_device_bytes(ctx, synth.matrix_on_device(14, rows, cols, 2, dev), 14, rows, cols)
+    for b in (1, 64):
+        x = torch.randn((b, cols), device=dev)
+        y = torch.empty((b, rows), device=dev)
+        us = graph_time_us(torch, ctx, lambda: head.matmul(x, out=y), reps=3)
+        nbytes = head.nbytes() + 4 * b * cols + 4 * b * rows
+        out[f"config2_head_q6k_151936x5120_m{b}"] = {"us": us, "GB/s": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak,
+                                                     "TFLOP/s": 2.0 * b * rows * cols / us / 1e6}
+    head.close()
+    # configs[3]
+    rows, cols = 17408, 5120
+    gate = QMatrix.from_device_bytes(ctx, synth.matrix_on_device(12, rows, cols, 3, dev), 12, rows, cols)
+    out["config3_prefill_q4k_bf16_17408x5120"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, gate, m, 5) for m in (128, 512, 2048)}
+    gate.close()
     return out
 
 

@@ -180,10 +180,13 @@ constexpr int kPeerWaitSpins = 4000000;
 __device__ __forceinline__ float4 peer_sum4(const PeerSum& p, size_t off)
 {
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < p.world; r++) {
-        float4 v;
-        asm volatile("ld.global.cv.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p.part[r] + off) : "memory");
-        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+#pragma unroll   // fully unrolled so that the pointer table stays in the kernel's parameter space
+    for (int r = 0; r < kMaxRanks; r++) {
+        if (r < p.world) {
+            float4 v;
+            asm volatile("ld.global.cv.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p.part[r] + off) : "memory");
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
     }
     return s;
 }
@@ -215,7 +218,7 @@ int32_t launch_tp_signal(cudaStream_t st, unsigned* epoch, unsigned* const* peer
 // Fused residual add + RMSNorm + activation preparation (crates/ferric-tensor/src/lib.rs:372-384
 // followed by the matmul's own input conversion).  One CTA per tile of 2 activation rows; warp w
 // handles super-blocks w, w + nwarps, ...
-template <int TY>
+template <int TY, bool PEERS>
 __global__ void __launch_bounds__(32 * kNormPrepMaxWarps)
 norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wgt, float eps,
                  size_t m, size_t d, size_t nblk, float* __restrict__ sum, float* __restrict__ norm,
@@ -226,7 +229,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
     __shared__ float part[2][kNormPrepMaxWarps];
     pdl_launch_dependents();
     pdl_wait();
-    if (peers.world > 0) {
+    if (PEERS) {
         // every rank's partial must have arrived: peers publish their exchange count into this
         // rank's flag slots; wait (bounded) until each has reached this rank's own count
         if (threadIdx.x < peers.world) {
@@ -260,7 +263,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
                     const float4 g = ld_act(reinterpret_cast<const float4*>(b + off) + i);
                     f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                 }
-                if (peers.world > 0) {
+                if (PEERS) {
                     const float4 g = peer_sum4(peers, off + 4 * i);
                     f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                 }
@@ -292,7 +295,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
                         const float4 g = ld_act(reinterpret_cast<const float4*>(b + off) + i);
                         f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                     }
-                    if (peers.world > 0) {
+                    if (PEERS) {
                         const float4 g = peer_sum4(peers, off + 4 * i);
                         f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                     }
@@ -356,19 +359,18 @@ int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
     static thread_local int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
+    const int max_smem = (int)(kNormPrepMaxWarps * sizeof(PrepSmem));
     if (attr_dev != dev) {
-        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ4K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)(kNormPrepMaxWarps * sizeof(PrepSmem)));
-        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ6K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)(kNormPrepMaxWarps * sizeof(PrepSmem)));
+        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ4K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ6K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ4K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ6K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
         attr_dev = dev;
     }
-    if (ty == kGgmlQ4K)
-        FERRIC_CUDA_TRY(launch_kernel(norm_prep_kernel<(int)kGgmlQ4K>, grid, block, smem, st, tune.pdl, a, b, weight, eps, m,
-                                      w.cols, w.nblk, sum, norm, f, peers));
-    else
-        FERRIC_CUDA_TRY(launch_kernel(norm_prep_kernel<(int)kGgmlQ6K>, grid, block, smem, st, tune.pdl, a, b, weight, eps, m,
-                                      w.cols, w.nblk, sum, norm, f, peers));
+    // the variant without an exchange carries none of the peer-pointer code
+    auto kernel = ty == kGgmlQ4K ? (peers.world > 0 ? norm_prep_kernel<(int)kGgmlQ4K, true> : norm_prep_kernel<(int)kGgmlQ4K, false>)
+                                 : (peers.world > 0 ? norm_prep_kernel<(int)kGgmlQ6K, true> : norm_prep_kernel<(int)kGgmlQ6K, false>);
+    FERRIC_CUDA_TRY(launch_kernel(kernel, grid, block, smem, st, tune.pdl, a, b, weight, eps, m, w.cols, w.nblk, sum, norm, f, peers));
     return kOk;
 }
 
