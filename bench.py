@@ -194,6 +194,7 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ["NCCL_DEBUG"] = "WARN"     # NCCL's version banner goes to stdout, where only the JSON line belongs
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -224,6 +225,10 @@ def run_ours(args):
     if world > 1:
         dist.broadcast(x0, 0)
     stack.h.copy_(x0)
+    # Captured graphs hold the address of the context's activation scratch, and growing the scratch moves it:
+    # size it once for the largest batch measured below, before anything is captured.
+    L0 = stack.layers[0]
+    ctx.reserve_scratch(max(w.scratch_bytes(max(B, 64)) for w in (L0.wqkv, L0.wo, L0.wgu, L0.wdown)))
     if not args.no_graph:
         stack.capture()
     else:
@@ -249,6 +254,46 @@ def run_ours(args):
         group.check()      # raises if any bounded wait on a peer ran out
     ms_per_step = elapsed_ms / K
     value = B * 1e3 / ms_per_step
+
+    # ---- the other batch sizes of the configuration, same weights, same timing rules ------------
+    other_batches = {}
+    if not args.no_extras:
+        for b in (1, 8, 64):
+            if b == B:
+                continue
+            g2 = None
+            if world > 1 and args.allreduce != "nccl":
+                g2 = TPGroup(ctx, rank, world, b, HIDDEN)
+                g2.connect_with_torch_distributed()
+            st2 = DecodeStack(ctx, plan, n_layers=args.layers, batch=b, all_reduce=allreduce, group=g2)
+            for L in stack.layers:
+                st2.add_layer(L.wqkv, L.wo, L.wgu, L.wdown)
+            st2.reserve()
+            xb = torch.randn((b, HIDDEN), device=dev, generator=g)
+            if world > 1:
+                dist.broadcast(xb, 0)
+            st2.h.copy_(xb)
+            if not args.no_graph:
+                st2.capture()
+            for _ in range(3):
+                st2.h.copy_(xb)
+                st2.run()
+            barrier()
+            k2 = max(5, min(K, 20))
+            ev0.record()
+            for _ in range(k2):
+                st2.run()
+            ev1.record()
+            torch.cuda.synchronize(dev)
+            barrier()
+            ms2 = max_over_ranks(ev0.elapsed_time(ev1)) / k2
+            if g2 is not None:
+                g2.check()
+            other_batches[str(b)] = {"tokens_per_s": b * 1e3 / ms2, "ms_per_step": ms2, "steps": k2,
+                                     "finite": bool(torch.isfinite(st2.h).all().item())}
+            st2.layers = []     # the matrices belong to the first stack
+            st2.graph = None
+            del st2
 
     # ---- end to end: host buffers in and out, every step -----------------------------------
     xh = torch.empty((B, HIDDEN), dtype=torch.float32).pin_memory()
@@ -327,6 +372,7 @@ def run_ours(args):
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches_per_step * K), "launches_per_step": int(launches_per_step),
             "clocks": clocks.summary(), "step_weight_gbs_per_gpu": step_gbs, "output_finite": finite,
+            "other_batches": other_batches,
             "extras": extras,
         }
         print(json.dumps(line), flush=True)

@@ -179,13 +179,20 @@ constexpr int kPeerWaitSpins = 4000000;
 // exchanges while this SM may still hold lines of the previous one.
 __device__ __forceinline__ float4 peer_sum4(const PeerSum& p, size_t off)
 {
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll   // fully unrolled so that the pointer table stays in the kernel's parameter space
+    // All loads are issued before the first sum, so the peers' latencies overlap instead of adding up; the sum
+    // itself runs in rank order.  Fully unrolled so that the pointer table stays in the kernel's parameter space.
+    float4 v[kMaxRanks];
+#pragma unroll
     for (int r = 0; r < kMaxRanks; r++) {
+        v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < p.world)
+            asm volatile("ld.global.cv.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v[r].x), "=f"(v[r].y), "=f"(v[r].z), "=f"(v[r].w) : "l"(p.part[r] + off));
+    }
+    float4 s = v[0];
+#pragma unroll
+    for (int r = 1; r < kMaxRanks; r++) {
         if (r < p.world) {
-            float4 v;
-            asm volatile("ld.global.cv.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p.part[r] + off) : "memory");
-            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            s.x += v[r].x; s.y += v[r].y; s.z += v[r].z; s.w += v[r].w;
         }
     }
     return s;

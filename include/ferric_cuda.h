@@ -91,7 +91,10 @@ typedef struct ferric_cuda_caps {
 int32_t ferric_cuda_ctx_caps(const ferric_cuda_ctx *ctx, ferric_cuda_caps *out);
 
 /* Grow the context's activation-fragment scratch to at least `bytes` now, so later calls do not
- * allocate (needed before capturing calls into a CUDA graph). */
+ * allocate (needed before capturing calls into a CUDA graph).  Growing moves the scratch: a graph
+ * captured earlier keeps the old address and must not be replayed after a later call has grown
+ * it -- reserve the largest size any captured or later call will need (the maximum of
+ * ferric_cuda_qmatrix_scratch_bytes(qm, m) over them) before the first capture. */
 int32_t ferric_cuda_ctx_reserve_scratch(ferric_cuda_ctx *ctx, size_t bytes);
 /* Launch counters since creation: kernels this library launched on the context. */
 uint64_t ferric_cuda_ctx_launches(const ferric_cuda_ctx *ctx);
