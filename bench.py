@@ -51,8 +51,8 @@ def parse_args():
     ap.add_argument("--prefill-rows", type=int, default=17408, help="weight rows of the --prefill matrix")
     ap.add_argument("--prefill-cols", type=int, default=5120, help="columns (K) of the --prefill matrix")
     ap.add_argument("--prefill-type", type=int, default=12, choices=[12, 14], help="ggml type of the --prefill matrix")
-    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: the library's own peer-memory exchange (default) or NCCL through torch.distributed")
+    ap.add_argument("--allreduce", default="auto", choices=["auto", "fused", "nccl"],
+                    help="N > 1: the library's own peer-memory exchange, NCCL through torch.distributed, or (default) the former up to batch 4")
     return ap.parse_args()
 
 
@@ -212,12 +212,19 @@ def run_ours(args):
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
     ctx = Context(local)
     plan = TPPlan.make(world, rank, HIDDEN, N_FF, Q_OUT, KV_OUT)
-    allreduce, group = None, None
-    if world > 1 and args.allreduce == "nccl":
-        allreduce = lambda t: dist.all_reduce(t)
-    elif world > 1:
-        group = TPGroup(ctx, rank, world, B, HIDDEN)
-        group.connect_with_torch_distributed()
+    def exchange_for(batch):
+        """(all_reduce callable, exchange group, name) for a batch size.  `auto`: the library's own exchange over peer
+        memory while the payload is latency-bound (up to 4 rows of 20 KB), NCCL above that (measured cross-over)."""
+        if world == 1:
+            return None, None, "none"
+        kind = args.allreduce if args.allreduce != "auto" else ("fused" if batch <= 4 else "nccl")
+        if kind == "nccl":
+            return (lambda t: dist.all_reduce(t)), None, kind
+        grp = TPGroup(ctx, rank, world, batch, HIDDEN)
+        grp.connect_with_torch_distributed()
+        return None, grp, kind
+
+    allreduce, group, ar_name = exchange_for(B)
     stack = DecodeStack(ctx, plan, n_layers=args.layers, batch=B, all_reduce=allreduce, group=group)
     stack.build_synthetic(seed=4)
     g = torch.Generator(device=dev).manual_seed(4)
@@ -261,11 +268,8 @@ def run_ours(args):
         for b in (1, 8, 64):
             if b == B:
                 continue
-            g2 = None
-            if world > 1 and args.allreduce != "nccl":
-                g2 = TPGroup(ctx, rank, world, b, HIDDEN)
-                g2.connect_with_torch_distributed()
-            st2 = DecodeStack(ctx, plan, n_layers=args.layers, batch=b, all_reduce=allreduce, group=g2)
+            ar2, g2, name2 = exchange_for(b)
+            st2 = DecodeStack(ctx, plan, n_layers=args.layers, batch=b, all_reduce=ar2, group=g2)
             for L in stack.layers:
                 st2.add_layer(L.wqkv, L.wo, L.wgu, L.wdown)
             st2.reserve()
@@ -289,7 +293,7 @@ def run_ours(args):
             ms2 = max_over_ranks(ev0.elapsed_time(ev1)) / k2
             if g2 is not None:
                 g2.check()
-            other_batches[str(b)] = {"tokens_per_s": b * 1e3 / ms2, "ms_per_step": ms2, "steps": k2,
+            other_batches[str(b)] = {"tokens_per_s": b * 1e3 / ms2, "ms_per_step": ms2, "steps": k2, "all_reduce": name2,
                                      "finite": bool(torch.isfinite(st2.h).all().item())}
             st2.layers = []     # the matrices belong to the first stack
             st2.graph = None
@@ -368,7 +372,7 @@ def run_ours(args):
             "config": {"workload": WORKLOAD.format(b=B), "batch": B, "layers": args.layers,
                        "parallelism": f"tp{world}", "cuda_graph": not args.no_graph,
                        "l2": f"{stack.weight_bytes_per_step() / 1e9:.2f} GB of weights per GPU per step, larger than L2",
-                       "all_reduce": (args.allreduce if world > 1 else "none")},
+                       "all_reduce": ar_name},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches_per_step * K), "launches_per_step": int(launches_per_step),
             "clocks": clocks.summary(), "step_weight_gbs_per_gpu": step_gbs, "output_finite": finite,
