@@ -211,8 +211,16 @@ int32_t run_matmul(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* 
         if (phases & 2) FERRIC_CUDA_TRY(cudaMemset2DAsync(y, ldy * sizeof(float), 0, out_cols * sizeof(float), m, ctx->stream));
         return kOk;
     }
-    const size_t need = frag_bytes(qm->ty, qm->w, m);
     int32_t rc = kOk;
+    if (phases == 3 && gemv_tc_eligible(qm->ty, qm->w, m)) {
+        // more than a few activation rows: the exact-integer tensor-core kernel (its own activation form)
+        if ((rc = ensure_scratch(ctx, gemv_tc_scratch_bytes(qm->w, m, epi, ctx->tune.sm_count))) != kOk) return rc;
+        int launched = 0;
+        rc = launch_gemv_tc(ctx->stream, qm->w, x, m, ldx, y, ldy, epi, ctx->scratch, ctx->tune, &launched);
+        ctx->launches += launched;
+        return rc;
+    }
+    const size_t need = frag_bytes(qm->ty, qm->w, m);
     if (phases & 1) {
         if ((rc = ensure_scratch(ctx, need)) != kOk) return rc;
         if ((rc = launch_prep(ctx->stream, qm->ty, qm->w, x, m, ldx, ctx->scratch, ctx->tune)) != kOk) return rc;
@@ -428,7 +436,14 @@ void ferric_cuda_qmatrix_free(ferric_qmatrix* qm)
 
 size_t ferric_cuda_qmatrix_scratch_bytes(const ferric_qmatrix* qm, size_t m)
 {
-    return qm ? frag_bytes(qm->ty, qm->w, m) : 0;
+    if (!qm) return 0;
+    size_t need = frag_bytes(qm->ty, qm->w, m);
+    if (gemv_tc_eligible(qm->ty, qm->w, m)) {
+        // the tensor-core decode path keeps limbs, sums and K-split partials there; the SwiGLU form needs the most
+        const size_t tc = gemv_tc_scratch_bytes(qm->w, m, kEpiSwiglu, 148);
+        if (tc > need) need = tc;
+    }
+    return need;
 }
 
 int32_t ferric_cuda_matmul_q(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_dev, size_t m,

@@ -151,6 +151,8 @@ class DecodeStack:
         c, p = self.ctx, self.plan
         before = c.launches()
         n = len(self.layers)
+        if self.batch > 8 and self.group is None:
+            return self._step_wide(before)
         m = self.layers[0].wqkv.add_rmsnorm_prepare(self.h, None, None, self.eps)
         G = self.group
         for i, L in enumerate(self.layers):
@@ -174,6 +176,27 @@ class DecodeStack:
                 if self.all_reduce:
                     self.all_reduce(self.d)
                 nxt.add_rmsnorm_prepare(self.h, self.d, None, self.eps, sum_out=self.h, norm_out=last_norm)
+        self.launches_per_step = c.launches() - before
+        return self.h
+
+    def _step_wide(self, before: int) -> torch.Tensor:
+        """The same step for more than 8 tokens: the products go through ``matmul`` / ``try_matmul_swiglu`` so that the
+        Q4_K ones can take the tensor-core kernel, which prepares its own activation form; add + rmsnorm runs unfused."""
+        c, p = self.ctx, self.plan
+        n = len(self.layers)
+        c.add_rmsnorm(self.h, None, None, self.eps, norm_out=self.xn)
+        for i, L in enumerate(self.layers):
+            L.wqkv.matmul(self.xn, out=self.qkv)
+            L.wo.matmul(self.qkv[:, :p.q_rows], out=self.o)
+            if self.all_reduce:
+                self.all_reduce(self.o)
+            c.add_rmsnorm(self.h, self.o, None, self.eps, sum_out=self.h, norm_out=self.xn)
+            if L.wgu.try_matmul_swiglu(self.xn, out=self.f) is None:
+                raise RuntimeError("gate|up matrix is not fusable")
+            L.wdown.matmul(self.f, out=self.d)
+            if self.all_reduce:
+                self.all_reduce(self.d)
+            c.add_rmsnorm(self.h, self.d, None, self.eps, sum_out=self.h, norm_out=self.xn)
         self.launches_per_step = c.launches() - before
         return self.h
 
