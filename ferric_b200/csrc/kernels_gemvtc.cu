@@ -42,9 +42,9 @@ constexpr int kTcMaxAStages = 8;
 __host__ __device__ constexpr int tc_a_stages(int n_tile) { return n_tile <= 128 ? 8 : 4; }
 constexpr int kTcRawStages = 2;
 constexpr int kTcMetaStages = 8;      // per-row (d, dmin, mins) of the super-blocks between the makers and the drain
-constexpr int kTcMakerWarps = 8, kTcDrainWarps = 4;
+constexpr int kTcMakerWarps = 8, kTcDrainWarps = 8;   // two drain warps per TMEM lane quarter, half the activation rows each
 constexpr int kTcFirstMaker = 3, kTcFirstDrain = kTcFirstMaker + kTcMakerWarps;
-constexpr int kTcThreads = 32 * (kTcFirstDrain + kTcDrainWarps);   // 480
+constexpr int kTcThreads = 32 * (kTcFirstDrain + kTcDrainWarps);   // 608
 constexpr int kTcABytes = kTcRows * 128;
 constexpr int kTcRawBytes = 8 * kQ4KUnit;
 constexpr int kTcMaxBStages = 8;
@@ -340,6 +340,7 @@ gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
                     up8[hi] = tc_make8(w0, w1, 4, sc1);
                 }
                 const int c = 4 * i + j, s = c % kTcAStages;
+                // (every lane polls: one polling lane plus a shuffle was measured 15 % slower -- the wake-up is on the critical path)
                 if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
                 uint8_t* arow = a_stage + s * kTcABytes + arow_off;
 #pragma unroll
@@ -354,10 +355,12 @@ gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
         }
     } else {
         // ---------------- drain: TMEM lane = weight row; column 4b + j = limb j of activation row act0 + b
-        const int q = warp & 3, rloc = 32 * q + lane, wrow = row0 + rloc;
-        float acc[kActs];
+        // two warps share a TMEM lane quarter; warp half h takes the groups of eight activation rows 2g + h
+        const int q = warp & 3, rloc = 32 * q + lane, wrow = row0 + rloc, half = (warp - kTcFirstDrain) >> 2;
+        constexpr int kGroups = kActs / 16;            // groups of eight activation rows per drain warp
+        float acc[kGroups * 8];
 #pragma unroll
-        for (int b = 0; b < kActs; b++) acc[b] = 0.0f;
+        for (int b = 0; b < kGroups * 8; b++) acc[b] = 0.0f;
         pdl_wait();   // ss / up come from the preparation kernel
         // What the drain needs of a super-block besides the accumulator -- the activation rows' eight sub-block sums
         // and their scale -- is fetched one super-block ahead into registers and staged in shared memory.
@@ -395,7 +398,8 @@ gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
                 mf[4 + sb] = (float)((rm.m_hi >> (8 * sb)) & 0xffu);
             }
 #pragma unroll
-            for (int grp = 0; grp < kActs / 8; grp++) {
+            for (int gg = 0; gg < kGroups; gg++) {
+                const int grp = 2 * gg + half;
                 uint32_t v[32];
                 tmem_ld_32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * N_TILE + 32 * grp), v);
 #pragma unroll
@@ -410,7 +414,7 @@ gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
                     float Mn = mf[0] * s0.x;
                     Mn = fmaf(mf[1], s0.y, Mn); Mn = fmaf(mf[2], s0.z, Mn); Mn = fmaf(mf[3], s0.w, Mn);
                     Mn = fmaf(mf[4], s1.x, Mn); Mn = fmaf(mf[5], s1.y, Mn); Mn = fmaf(mf[6], s1.z, Mn); Mn = fmaf(mf[7], s1.w, Mn);
-                    acc[b] = fmaf(scale, fmaf(rm.d, V, -rm.dmin * Mn), acc[b]);
+                    acc[8 * gg + bb] = fmaf(scale, fmaf(rm.d, V, -rm.dmin * Mn), acc[8 * gg + bb]);
                 }
             }
             // every drain thread has finished reading the other slot (it did so one iteration ago and has met the
@@ -424,8 +428,12 @@ gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
         if (!fail && wrow < rows) {
             float* o = out + (size_t)blockIdx.z * split_stride;
 #pragma unroll
-            for (int b = 0; b < kActs; b++)
-                if (act0 + b < m) o[(size_t)(act0 + b) * ld_out + wrow] = acc[b];
+            for (int gg = 0; gg < kGroups; gg++)
+#pragma unroll
+                for (int bb = 0; bb < 8; bb++) {
+                    const int act = act0 + 8 * (2 * gg + half) + bb;
+                    if (act < m) o[(size_t)act * ld_out + wrow] = acc[8 * gg + bb];
+                }
         }
     }
     if (fail) {
