@@ -214,9 +214,9 @@ int32_t run_matmul(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* 
     int32_t rc = kOk;
     if (phases == 3 && gemv_tc_eligible(qm->ty, qm->w, m)) {
         // more than a few activation rows: the exact-integer tensor-core kernel (its own activation form)
-        if ((rc = ensure_scratch(ctx, gemv_tc_scratch_bytes(qm->w, m, epi, ctx->tune.sm_count))) != kOk) return rc;
+        if ((rc = ensure_scratch(ctx, gemv_tc_scratch_bytes(qm->ty, qm->w, m, epi, ctx->tune.sm_count))) != kOk) return rc;
         int launched = 0;
-        rc = launch_gemv_tc(ctx->stream, qm->w, x, m, ldx, y, ldy, epi, ctx->scratch, ctx->tune, &launched);
+        rc = launch_gemv_tc(ctx->stream, qm->ty, qm->w, x, m, ldx, y, ldy, epi, ctx->scratch, ctx->tune, &launched);
         ctx->launches += launched;
         return rc;
     }
@@ -440,7 +440,7 @@ size_t ferric_cuda_qmatrix_scratch_bytes(const ferric_qmatrix* qm, size_t m)
     size_t need = frag_bytes(qm->ty, qm->w, m);
     if (gemv_tc_eligible(qm->ty, qm->w, m)) {
         // the tensor-core decode path keeps limbs, sums and K-split partials there; the SwiGLU form needs the most
-        const size_t tc = gemv_tc_scratch_bytes(qm->w, m, kEpiSwiglu, 148);
+        const size_t tc = gemv_tc_scratch_bytes(qm->ty, qm->w, m, kEpiSwiglu, 148);
         if (tc > need) need = tc;
     }
     return need;

@@ -77,11 +77,11 @@ int32_t launch_add_rmsnorm(cudaStream_t st, const float* a, const float* b, cons
 // dequantised to bf16 (round to nearest even) and bf16 activations x[m, cols] (row stride ldx elements).
 int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint16_t* x_bf16, size_t m, size_t ldx,
                          float* y, size_t ldy);
-// Batched decode product on the tensor cores with exact integer arithmetic (Q4_K, m >= 9 by default): preparation,
+// Batched decode product on the tensor cores with exact integer arithmetic (Q4_K and Q6_K, m >= 9 by default): preparation,
 // product and, for K-split or SwiGLU, a finish kernel.  `scratch` holds gemv_tc_scratch_bytes() bytes.
 bool gemv_tc_eligible(uint32_t ty, const DeviceWeights& w, size_t m);
-size_t gemv_tc_scratch_bytes(const DeviceWeights& w, size_t m, Epilogue epi, int sm_count);
-int32_t launch_gemv_tc(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y, size_t ldy,
+size_t gemv_tc_scratch_bytes(uint32_t ty, const DeviceWeights& w, size_t m, Epilogue epi, int sm_count);
+int32_t launch_gemv_tc(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y, size_t ldy,
                        Epilogue epi, void* scratch, const GemvTuning& tune, int* launches);
 // Synchronise the stream and fetch-and-clear the code a GEMM CTA left when one of its bounded waits ran out.
 int32_t gemm_status(cudaStream_t st, int* code);

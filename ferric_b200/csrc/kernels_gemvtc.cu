@@ -1,4 +1,4 @@
-// Batched decode product (9 <= M, Q4_K) on the tcgen05 tensor cores with exact integer arithmetic.
+// Batched decode product (M > 8; Q4_K and Q6_K) on the tcgen05 tensor cores with exact integer arithmetic.
 //
 // The mma.sync GEMV (kernels_gemv.cu) is bound by instruction issue beyond a few activation rows.  This
 // kernel keeps its number format -- activations as four balanced base-128 limbs of X = rint(x * 2^(27-e)),
@@ -36,17 +36,18 @@ namespace ferric {
 
 constexpr int kTcRows = 128;          // weight rows per CTA (UMMA M)
 constexpr int kTcChunkK = 64;         // K per stage: 64 f16 = one 128-byte swizzle row
-constexpr int kTcMaxAStages = 8;
-// Operand (A) stages: what bounds the kernel at narrow tiles is the round trip of a stage (commit -> maker wakes ->
-// stores -> MMA thread wakes -> issue), so the ring is deep where shared memory allows.
-__host__ __device__ constexpr int tc_a_stages(int n_tile) { return n_tile <= 128 ? 8 : 4; }
 constexpr int kTcRawStages = 2;
 constexpr int kTcMetaStages = 8;      // per-row (d, dmin, mins) of the super-blocks between the makers and the drain
 constexpr int kTcMakerWarps = 8, kTcDrainWarps = 8;   // two drain warps per TMEM lane quarter, half the activation rows each
 constexpr int kTcFirstMaker = 3, kTcFirstDrain = kTcFirstMaker + kTcMakerWarps;
 constexpr int kTcThreads = 32 * (kTcFirstDrain + kTcDrainWarps);   // 608
-constexpr int kTcABytes = kTcRows * 128;
-constexpr int kTcRawBytes = 8 * kQ4KUnit;
+constexpr int kTcABytes = kTcRows * 128;   // one operand plane of one K chunk
+// Q4_K needs one operand plane (sc * q <= 945).  Q6_K's sc * (q - 32) reaches 127 * 32 = 4064, beyond the integers f16
+// holds exactly, so its scale is split as sc = 16 sh + sl (sl 0..15, sh -8..7) into two planes sl * (q - 32) and
+// sh * (q - 32), multiplied into two accumulators and recombined as D1 + 16 D2 in the drain.
+__host__ __device__ constexpr int tc_planes(uint32_t ty) { return ty == kGgmlQ6K ? 2 : 1; }
+__host__ __device__ constexpr int tc_unit_bytes(uint32_t ty) { return ty == kGgmlQ6K ? kQ6KUnit : kQ4KUnit; }
+__host__ __device__ constexpr int tc_raw_bytes(uint32_t ty) { return 8 * tc_unit_bytes(ty); }
 constexpr int kTcMaxBStages = 8;
 
 struct TcRowMeta {
@@ -56,24 +57,28 @@ struct TcRowMeta {
 static_assert(sizeof(TcRowMeta) == 16, "row meta is one 16-byte store");
 
 constexpr int kTcSumFloats = 64 * 9;   // per stage: up to 64 activation rows x (8 sub-block sums + 1 scale)
-__host__ __device__ constexpr int tc_fixed_bytes(int n_tile)
+__host__ __device__ constexpr int tc_a_stages(uint32_t ty, int) { return ty == kGgmlQ6K ? 3 : 4; }
+__host__ __device__ constexpr int tc_fixed_bytes(uint32_t ty, int n_tile)
 {
-    return 1024 /*align*/ + 512 /*barriers*/ + tc_a_stages(n_tile) * kTcABytes + kTcRawStages * kTcRawBytes +
+    return 1024 /*align*/ + 512 /*barriers*/ + tc_a_stages(ty, n_tile) * tc_planes(ty) * kTcABytes + kTcRawStages * tc_raw_bytes(ty) +
            kTcMetaStages * kTcRows * (int)sizeof(TcRowMeta) + 2 * kTcSumFloats * 4;
 }
 __host__ __device__ constexpr int tc_b_bytes(int n_tile) { return n_tile * 128; }
-__host__ __device__ constexpr int tc_b_stages(int n_tile)
+__host__ __device__ constexpr int tc_b_stages(uint32_t ty, int n_tile)
 {
-    return (232448 - tc_fixed_bytes(n_tile)) / tc_b_bytes(n_tile) > kTcMaxBStages
+    return (232448 - tc_fixed_bytes(ty, n_tile)) / tc_b_bytes(n_tile) > kTcMaxBStages
                ? kTcMaxBStages
-               : (232448 - tc_fixed_bytes(n_tile)) / tc_b_bytes(n_tile);
+               : (232448 - tc_fixed_bytes(ty, n_tile)) / tc_b_bytes(n_tile);
 }
-__host__ __device__ constexpr int tc_smem_bytes(int n_tile) { return tc_fixed_bytes(n_tile) + tc_b_stages(n_tile) * tc_b_bytes(n_tile); }
-static_assert(tc_b_stages(256) >= 3, "at least three limb stages at the widest tile");
+__host__ __device__ constexpr int tc_smem_bytes(uint32_t ty, int n_tile)
+{
+    return tc_fixed_bytes(ty, n_tile) + tc_b_stages(ty, n_tile) * tc_b_bytes(n_tile);
+}
+static_assert(tc_b_stages(kGgmlQ4K, 256) >= 3 && tc_b_stages(kGgmlQ6K, 128) >= 3, "limb stages at the widest tiles");
 
 struct TcBarriers {
     uint64_t raw_full[kTcRawStages], raw_empty[kTcRawStages];
-    uint64_t a_full[kTcMaxAStages], a_empty[kTcMaxAStages];
+    uint64_t a_full[4], a_empty[4];
     uint64_t b_full[kTcMaxBStages], b_empty[kTcMaxBStages];
     uint64_t acc_full[2], acc_empty[2];
     uint32_t tmem_base;
@@ -186,17 +191,192 @@ __device__ __forceinline__ uint4 tc_make8(uint32_t w0, uint32_t w1, int shift, u
     return o;
 }
 
-template <int N_TILE>
+// ---------------------------------------------------------------- operand makers
+// One call per maker warp.  Warp = one 16-row unit, lane = (row g / g+8, 8-byte piece t), with the prefill kernel's
+// conflict-free lane map.  Returns 0 or the code of the wait that ran out.
+template <int A_STAGES>
+__device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, TcRowMeta* meta, int nb,
+                                           int tiles_here, int wd, int lane)
+{
+    constexpr int kTcAStages = A_STAGES;
+    int fail = 0;
+    // ---------------- operand makers: warp = one 16-row unit, lane = (row g / g+8, 8-byte piece t); see the
+    // prefill kernel for the conflict-free lane map
+    const int t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
+    const bool unit_ok = wd < tiles_here;
+    const uint32_t arow_off = (uint32_t)(2 * wd * 1024 + g * 128);
+    const uint32_t col_lo = (uint32_t)((t ^ g) << 4), col_hi = (uint32_t)(((4 + t) ^ g) << 4);
+    for (int i = 0; i < nb && !fail; i++) {
+        const int rs = i % kTcRawStages;
+        if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)i / kTcRawStages) & 1u)) { fail = 4; break; }
+        const uint8_t* u = raw_stage + rs * (8 * kQ4KUnit) + wd * kQ4KUnit;
+        uint4 hdr[2], qs[2][2];
+#pragma unroll
+        for (int hi = 0; hi < 2; hi++) {
+            hdr[hi] = qs[hi][0] = qs[hi][1] = make_uint4(0, 0, 0, 0);
+            if (unit_ok) {
+                hdr[hi] = *reinterpret_cast<const uint4*>(u + 16 * (g + 8 * hi));
+                qs[hi][0] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi) + 16 * (4 * g + t));
+                qs[hi][1] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi + 1) + 16 * (4 * g + t));
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar->raw_empty[rs]);
+        if (t == 0) {   // hand (d, dmin, mins) of this super-block's rows to the drain
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                uint32_t mn[8], sc_unused;
+#pragma unroll
+                for (int sb = 0; sb < 8; sb++) q4k_scale_min(hdr[hi], sb, sc_unused, mn[sb]);
+                TcRowMeta rm;
+                rm.d = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x & 0xffffu)));
+                rm.dmin = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x >> 16)));
+                rm.m_lo = mn[0] | (mn[1] << 8) | (mn[2] << 16) | (mn[3] << 24);
+                rm.m_hi = mn[4] | (mn[5] << 8) | (mn[6] << 16) | (mn[7] << 24);
+                *reinterpret_cast<uint4*>(&meta[(i % kTcMetaStages) * kTcRows + 16 * wd + 8 * hi + g]) =
+                    *reinterpret_cast<const uint4*>(&rm);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint4 lo[2], up8[2];
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                uint32_t sc0, sc1, mn_unused;
+                q4k_scale_min(hdr[hi], 2 * j, sc0, mn_unused);
+                q4k_scale_min(hdr[hi], 2 * j + 1, sc1, mn_unused);
+                const uint4 q4 = qs[hi][j >> 1];
+                const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
+                lo[hi] = tc_make8(w0, w1, 0, sc0);
+                up8[hi] = tc_make8(w0, w1, 4, sc1);
+            }
+            const int c = 4 * i + j, s = c % kTcAStages;
+            // (every lane polls: one polling lane plus a shuffle was measured 15 % slower -- the wake-up is on the critical path)
+            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
+            uint8_t* arow = a_stage + s * kTcABytes + arow_off;
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                *reinterpret_cast<uint4*>(arow + hi * 1024 + col_lo) = lo[hi];
+                *reinterpret_cast<uint4*>(arow + hi * 1024 + col_hi) = up8[hi];
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar->a_full[s]);   // also publishes this block's row meta (written above)
+        }
+    }
+    return fail;
+}
+
+// Four Q6_K weights (6-bit values in the bytes of q) times one scale digit -> four f16 integers mult * (q - 32),
+// negated when `neg`: two values per 32-bit multiply (q * mult <= 63 * 15), 0x6400 | v = 1024 + v in f16, and
+// subtracting 1024 + 32 * mult (exact, <= 1504) leaves mult * (q - 32) exactly.
+__device__ __forceinline__ uint2 tc_make4_q6(uint32_t q, uint32_t mult, bool neg)
+{
+    const __half2 bias = __half2half2(__ushort_as_half((unsigned short)(0x6400u + 32u * mult)));   // 1024 + 32 mult: exact bits
+    const uint32_t p02 = ((q & 0x00FF00FFu) * mult) | 0x64006400u;          // values 0, 2
+    const uint32_t p13 = (((q >> 8) & 0x00FF00FFu) * mult) | 0x64006400u;   // values 1, 3
+    const __half2 h02 = __hsub2(*reinterpret_cast<const __half2*>(&p02), bias);
+    const __half2 h13 = __hsub2(*reinterpret_cast<const __half2*>(&p13), bias);
+    const uint32_t sign = neg ? 0x80008000u : 0u;
+    const uint32_t u02 = *reinterpret_cast<const uint32_t*>(&h02) ^ sign, u13 = *reinterpret_cast<const uint32_t*>(&h13) ^ sign;
+    return make_uint2(__byte_perm(u02, u13, 0x5410), __byte_perm(u02, u13, 0x7632));
+}
+
+// Q6_K (unit layout in layout.h; lane ownership as in the prefill kernel's Q6_K stage): two operand planes per chunk,
+// plane 0 = sl * (q - 32), plane 1 = sh * (q - 32) with sc = 16 sh + sl.  Row meta carries d only.
+template <int A_STAGES>
+__device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, TcRowMeta* meta, int nb,
+                                           int tiles_here, int wd, int lane)
+{
+    constexpr int kStageBytes = 2 * kTcABytes;
+    int fail = 0;
+    const int t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
+    const bool unit_ok = wd < tiles_here;
+    const uint32_t arow_off = (uint32_t)(2 * wd * 1024 + g * 128);
+    for (int i = 0; i < nb && !fail; i++) {
+        const int rs = i % kTcRawStages;
+        if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)i / kTcRawStages) & 1u)) { fail = 4; break; }
+        const uint8_t* u = raw_stage + rs * (8 * kQ6KUnit) + wd * kQ6KUnit;
+        uint4 ql[2][2], qh[2], sc[2];
+        uint32_t dpair = 0;
+#pragma unroll
+        for (int hi = 0; hi < 2; hi++) {
+            ql[hi][0] = ql[hi][1] = qh[hi] = sc[hi] = make_uint4(0, 0, 0, 0);
+            if (unit_ok) {
+                ql[hi][0] = *reinterpret_cast<const uint4*>(u + kQ6KOffQl + 512 * (2 * hi) + 16 * (4 * g + t));
+                ql[hi][1] = *reinterpret_cast<const uint4*>(u + kQ6KOffQl + 512 * (2 * hi + 1) + 16 * (4 * g + t));
+                qh[hi] = *reinterpret_cast<const uint4*>(u + kQ6KOffQh + 512 * hi + 16 * (4 * g + t));
+                sc[hi] = *reinterpret_cast<const uint4*>(u + kQ6KOffSc + 16 * (g + 8 * hi));
+            }
+        }
+        if (unit_ok) dpair = *reinterpret_cast<const uint32_t*>(u + 4 * g);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar->raw_empty[rs]);
+        if (t == 0) {
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                TcRowMeta rm;
+                rm.d = __half2float(__ushort_as_half((unsigned short)(hi ? (dpair >> 16) : (dpair & 0xffffu))));
+                rm.dmin = 0.0f;
+                rm.m_lo = rm.m_hi = 0u;
+                *reinterpret_cast<uint4*>(&meta[(i % kTcMetaStages) * kTcRows + 16 * wd + 8 * hi + g]) = *reinterpret_cast<const uint4*>(&rm);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            // chunk j = (h, kp): sub-blocks k = 2 kp + c (c = 0, 1), is = 0, 1; scale byte 4 j + 2 c + is of the row's 16
+            const int h = j >> 1, kp = j & 1;
+            uint2 p0[2][4], p1[2][4];
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                const uint32_t scw = j == 0 ? sc[hi].x : (j == 1 ? sc[hi].y : (j == 2 ? sc[hi].z : sc[hi].w));
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+#pragma unroll
+                    for (int is = 0; is < 2; is++) {
+                        const int scv = (int)(int8_t)(scw >> (8 * (2 * c + is)));
+                        const int sl = scv & 15, sh = scv >> 4;           // scv = 16 sh + sl
+                        const uint4 qlv = ql[hi][c];
+                        const uint32_t lw = (2 * h + is) == 0 ? qlv.x : ((2 * h + is) == 1 ? qlv.y : ((2 * h + is) == 2 ? qlv.z : qlv.w));
+                        const uint32_t hw = (2 * h + is) == 0 ? qh[hi].x : ((2 * h + is) == 1 ? qh[hi].y : ((2 * h + is) == 2 ? qh[hi].z : qh[hi].w));
+                        const uint32_t q = ((lw >> (4 * kp)) & 0x0F0F0F0Fu) | (((hw >> (2 * (2 * kp + c))) & 0x03030303u) << 4);
+                        p0[hi][2 * c + is] = tc_make4_q6(q, (uint32_t)sl, false);
+                        p1[hi][2 * c + is] = tc_make4_q6(q, (uint32_t)(sh < 0 ? -sh : sh), sh < 0);
+                    }
+                }
+            }
+            const int c4 = 4 * i + j, s = c4 % A_STAGES;
+            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c4 / A_STAGES) & 1u) ^ 1u)) { fail = 5; break; }
+            uint8_t* arow = a_stage + s * kStageBytes + arow_off;
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++)
+#pragma unroll
+                for (int k = 0; k < 4; k++) {   // k = 2c + is: 16-byte column 2k + (t >> 1), half t & 1
+                    const uint32_t off = (uint32_t)(hi * 1024 + (((2 * k + (t >> 1)) ^ g) << 4) + 8 * (t & 1));
+                    *reinterpret_cast<uint2*>(arow + off) = p0[hi][k];
+                    *reinterpret_cast<uint2*>(arow + kTcABytes + off) = p1[hi][k];
+                }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar->a_full[s]);
+        }
+    }
+    return fail;
+}
+
+template <uint32_t TY, int N_TILE>
 __global__ void __launch_bounds__(kTcThreads, 1)
-gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap, const float* __restrict__ ss,
+gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap, const float* __restrict__ ss,
                    const float* __restrict__ up, float* __restrict__ out, size_t ld_out, size_t split_stride, int rows, int nblk,
                    int m, int m_pad, int row_tiles16, int blocks_per_split, int* __restrict__ err)
 {
     extern __shared__ uint8_t tc_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int kBStages = tc_b_stages(N_TILE), kBBytes = tc_b_bytes(N_TILE), kActs = N_TILE / 4, kTcAStages = tc_a_stages(N_TILE);
-    uint8_t* a_stage = smem;
-    uint8_t* b_stage = a_stage + kTcAStages * kTcABytes;
+    constexpr int kBStages = tc_b_stages(TY, N_TILE), kBBytes = tc_b_bytes(N_TILE), kActs = N_TILE / 4;
+    constexpr int kTcAStages = tc_a_stages(TY, N_TILE), kPlanes = tc_planes(TY), kAStageBytes = kPlanes * kTcABytes;
+    constexpr int kUnit = tc_unit_bytes(TY), kTcRawBytes = tc_raw_bytes(TY);
+    uint8_t* a_stage = smem;                                  // [kTcAStages][kPlanes][16384]
+    uint8_t* b_stage = a_stage + kTcAStages * kAStageBytes;
     uint8_t* raw_stage = b_stage + kBStages * kBBytes;
     TcRowMeta* meta = reinterpret_cast<TcRowMeta*>(raw_stage + kTcRawStages * kTcRawBytes);   // [kTcMetaStages][128]
     float* sums = reinterpret_cast<float*>(meta + kTcMetaStages * kTcRows);   // [2][kActs * 9]: staged SS and UP of a super-block
@@ -227,7 +407,8 @@ gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
         bar->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    constexpr int kTmemCols = 2 * N_TILE < 32 ? 32 : 2 * N_TILE;   // two accumulators; a power of two >= 32
+    constexpr int kTmemCols = 2 * kPlanes * N_TILE;   // two sets of accumulators (one per operand plane); a power of two >= 128
+    static_assert(kTmemCols <= 512, "tensor memory holds 512 columns");
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
                      "n"(kTmemCols)
@@ -247,10 +428,10 @@ gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
             for (int i = 0; i < nb; i++) {
                 const int rs = i % kTcRawStages;
                 if (!mbar_wait(&bar->raw_empty[rs], (((uint32_t)i / kTcRawStages) & 1u) ^ 1u)) { fail = 1; break; }
-                mbar_expect_tx(&bar->raw_full[rs], (uint32_t)(tiles_here * kQ4KUnit));
+                mbar_expect_tx(&bar->raw_full[rs], (uint32_t)(tiles_here * kUnit));
                 for (int t = 0; t < tiles_here; t++)
-                    bulk_g2s(raw_stage + rs * kTcRawBytes + t * kQ4KUnit, units + ((size_t)(rt0 + t) * nblk + blk0 + i) * kQ4KUnit,
-                             kQ4KUnit, &bar->raw_full[rs]);
+                    bulk_g2s(raw_stage + rs * kTcRawBytes + t * kUnit, units + ((size_t)(rt0 + t) * nblk + blk0 + i) * kUnit, kUnit,
+                             &bar->raw_full[rs]);
             }
         }
     } else if (warp == 2) {
@@ -277,11 +458,13 @@ gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
                     if (!mbar_wait(&bar->a_full[sa], ((uint32_t)c / kTcAStages) & 1u) ||
                         !mbar_wait(&bar->b_full[sb], ((uint32_t)c / kBStages) & 1u)) { fail = 3; break; }
                     tc_fence_after();
-                    const uint32_t a0 = smem_u32(a_stage + sa * kTcABytes), b0 = smem_u32(b_stage + sb * kBBytes);
+                    const uint32_t a0 = smem_u32(a_stage + sa * kAStageBytes), b0 = smem_u32(b_stage + sb * kBBytes);
 #pragma unroll
                     for (int k4 = 0; k4 < 4; k4++)
-                        umma_bf16(tmem_acc + buf * N_TILE, umma_desc_sw128(a0 + 32 * k4), umma_desc_sw128(b0 + 32 * k4), idesc,
-                                  (j | k4) ? 1u : 0u);
+#pragma unroll
+                        for (int pl = 0; pl < kPlanes; pl++)
+                            umma_bf16(tmem_acc + (buf * kPlanes + pl) * N_TILE, umma_desc_sw128(a0 + pl * kTcABytes + 32 * k4),
+                                      umma_desc_sw128(b0 + 32 * k4), idesc, (j | k4) ? 1u : 0u);
                     umma_commit(&bar->a_empty[sa]);
                     umma_commit(&bar->b_empty[sb]);
                 }
@@ -289,70 +472,10 @@ gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
             }
         }
     } else if (warp < kTcFirstDrain) {
-        // ---------------- operand makers: warp = one 16-row unit, lane = (row g / g+8, 8-byte piece t); see the
-        // prefill kernel for the conflict-free lane map
-        const int wd = warp - kTcFirstMaker, t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
-        const bool unit_ok = wd < tiles_here;
-        const uint32_t arow_off = (uint32_t)(2 * wd * 1024 + g * 128);
-        const uint32_t col_lo = (uint32_t)((t ^ g) << 4), col_hi = (uint32_t)(((4 + t) ^ g) << 4);
-        for (int i = 0; i < nb && !fail; i++) {
-            const int rs = i % kTcRawStages;
-            if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)i / kTcRawStages) & 1u)) { fail = 4; break; }
-            const uint8_t* u = raw_stage + rs * kTcRawBytes + wd * kQ4KUnit;
-            uint4 hdr[2], qs[2][2];
-#pragma unroll
-            for (int hi = 0; hi < 2; hi++) {
-                hdr[hi] = qs[hi][0] = qs[hi][1] = make_uint4(0, 0, 0, 0);
-                if (unit_ok) {
-                    hdr[hi] = *reinterpret_cast<const uint4*>(u + 16 * (g + 8 * hi));
-                    qs[hi][0] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi) + 16 * (4 * g + t));
-                    qs[hi][1] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi + 1) + 16 * (4 * g + t));
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar->raw_empty[rs]);
-            if (t == 0) {   // hand (d, dmin, mins) of this super-block's rows to the drain
-#pragma unroll
-                for (int hi = 0; hi < 2; hi++) {
-                    uint32_t mn[8], sc_unused;
-#pragma unroll
-                    for (int sb = 0; sb < 8; sb++) q4k_scale_min(hdr[hi], sb, sc_unused, mn[sb]);
-                    TcRowMeta rm;
-                    rm.d = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x & 0xffffu)));
-                    rm.dmin = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x >> 16)));
-                    rm.m_lo = mn[0] | (mn[1] << 8) | (mn[2] << 16) | (mn[3] << 24);
-                    rm.m_hi = mn[4] | (mn[5] << 8) | (mn[6] << 16) | (mn[7] << 24);
-                    *reinterpret_cast<uint4*>(&meta[(i % kTcMetaStages) * kTcRows + 16 * wd + 8 * hi + g]) =
-                        *reinterpret_cast<const uint4*>(&rm);
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                uint4 lo[2], up8[2];
-#pragma unroll
-                for (int hi = 0; hi < 2; hi++) {
-                    uint32_t sc0, sc1, mn_unused;
-                    q4k_scale_min(hdr[hi], 2 * j, sc0, mn_unused);
-                    q4k_scale_min(hdr[hi], 2 * j + 1, sc1, mn_unused);
-                    const uint4 q4 = qs[hi][j >> 1];
-                    const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
-                    lo[hi] = tc_make8(w0, w1, 0, sc0);
-                    up8[hi] = tc_make8(w0, w1, 4, sc1);
-                }
-                const int c = 4 * i + j, s = c % kTcAStages;
-                // (every lane polls: one polling lane plus a shuffle was measured 15 % slower -- the wake-up is on the critical path)
-                if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
-                uint8_t* arow = a_stage + s * kTcABytes + arow_off;
-#pragma unroll
-                for (int hi = 0; hi < 2; hi++) {
-                    *reinterpret_cast<uint4*>(arow + hi * 1024 + col_lo) = lo[hi];
-                    *reinterpret_cast<uint4*>(arow + hi * 1024 + col_hi) = up8[hi];
-                }
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar->a_full[s]);   // also publishes this block's row meta (written above)
-            }
-        }
+        // ---------------- operand makers (per quant type, above)
+        const int wd = warp - kTcFirstMaker;
+        if (TY == kGgmlQ4K) fail = tc_make_q4k<kTcAStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
+        else fail = tc_make_q6k<kTcAStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
     } else {
         // ---------------- drain: TMEM lane = weight row; column 4b + j = limb j of activation row act0 + b
         // two warps share a TMEM lane quarter; warp half h takes the groups of eight activation rows 2g + h
@@ -401,20 +524,30 @@ gemv_tc_q4k_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
             for (int gg = 0; gg < kGroups; gg++) {
                 const int grp = 2 * gg + half;
                 uint32_t v[32];
-                tmem_ld_32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * N_TILE + 32 * grp), v);
+                tmem_ld_32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * kPlanes * N_TILE + 32 * grp), v);
+                if (kPlanes == 2) {   // second scale digit: D1 + 16 D2
+                    uint32_t w[32];
+                    tmem_ld_32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)((buf * kPlanes + 1) * N_TILE + 32 * grp), w);
+#pragma unroll
+                    for (int e = 0; e < 32; e++) v[e] = __float_as_uint(fmaf(16.0f, __uint_as_float(w[e]), __uint_as_float(v[e])));
+                }
 #pragma unroll
                 for (int bb = 0; bb < 8; bb++) {
                     const int b = 8 * grp + bb;
-                    const float4 s0 = reinterpret_cast<const float4*>(sl)[2 * b], s1 = reinterpret_cast<const float4*>(sl)[2 * b + 1];
                     const float scale = sl[kActs * 8 + b];
                     float V = __uint_as_float(v[4 * bb + 3]);
                     V = fmaf(V, 0.0078125f, __uint_as_float(v[4 * bb + 2]));
                     V = fmaf(V, 0.0078125f, __uint_as_float(v[4 * bb + 1]));
                     V = fmaf(V, 0.0078125f, __uint_as_float(v[4 * bb]));
-                    float Mn = mf[0] * s0.x;
-                    Mn = fmaf(mf[1], s0.y, Mn); Mn = fmaf(mf[2], s0.z, Mn); Mn = fmaf(mf[3], s0.w, Mn);
-                    Mn = fmaf(mf[4], s1.x, Mn); Mn = fmaf(mf[5], s1.y, Mn); Mn = fmaf(mf[6], s1.z, Mn); Mn = fmaf(mf[7], s1.w, Mn);
-                    acc[8 * gg + bb] = fmaf(scale, fmaf(rm.d, V, -rm.dmin * Mn), acc[8 * gg + bb]);
+                    if (TY == kGgmlQ4K) {
+                        const float4 s0 = reinterpret_cast<const float4*>(sl)[2 * b], s1 = reinterpret_cast<const float4*>(sl)[2 * b + 1];
+                        float Mn = mf[0] * s0.x;
+                        Mn = fmaf(mf[1], s0.y, Mn); Mn = fmaf(mf[2], s0.z, Mn); Mn = fmaf(mf[3], s0.w, Mn);
+                        Mn = fmaf(mf[4], s1.x, Mn); Mn = fmaf(mf[5], s1.y, Mn); Mn = fmaf(mf[6], s1.z, Mn); Mn = fmaf(mf[7], s1.w, Mn);
+                        acc[8 * gg + bb] = fmaf(scale, fmaf(rm.d, V, -rm.dmin * Mn), acc[8 * gg + bb]);
+                    } else {
+                        acc[8 * gg + bb] = fmaf(scale * rm.d, V, acc[8 * gg + bb]);
+                    }
                 }
             }
             // every drain thread has finished reading the other slot (it did so one iteration ago and has met the
@@ -504,10 +637,10 @@ struct TcPlan {
     bool needs_finish;
 };
 
-TcPlan tc_plan(const DeviceWeights& w, size_t m, Epilogue epi, int sm_count)
+TcPlan tc_plan(uint32_t ty, const DeviceWeights& w, size_t m, Epilogue epi, int sm_count)
 {
     TcPlan p;
-    p.n_tile = m <= 16 ? 64 : (m <= 32 ? 128 : 256);
+    p.n_tile = m <= 16 ? 64 : ((m <= 32 || ty == kGgmlQ6K) ? 128 : 256);   // Q6_K: two accumulator planes, so half the width
     const size_t row_tiles = (w.rows + kTcRows - 1) / kTcRows, act_tiles = (4 * m + p.n_tile - 1) / p.n_tile;
     const size_t tiles = row_tiles * act_tiles;
     size_t splits = 1;
@@ -525,7 +658,7 @@ TcPlan tc_plan(const DeviceWeights& w, size_t m, Epilogue epi, int sm_count)
     return p;
 }
 
-template <int N_TILE>
+template <uint32_t TY, int N_TILE>
 int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const float* ss, const float* up, float* out,
                        size_t ld_out, size_t split_stride, size_t m, const TcPlan& p, bool pdl)
 {
@@ -533,12 +666,12 @@ int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMa
     int dev = 0;
     FERRIC_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !attr_done[dev]) {
-        FERRIC_CUDA_TRY(cudaFuncSetAttribute(gemv_tc_q4k_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             tc_smem_bytes(N_TILE)));
+        FERRIC_CUDA_TRY(cudaFuncSetAttribute(gemv_tc_kernel<TY, N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             tc_smem_bytes(TY, N_TILE)));
         attr_done[dev] = true;
     }
     dim3 grid((unsigned)((w.rows + kTcRows - 1) / kTcRows), (unsigned)((4 * m + N_TILE - 1) / N_TILE), (unsigned)p.splits);
-    FERRIC_CUDA_TRY(launch_kernel(gemv_tc_q4k_kernel<N_TILE>, grid, dim3(kTcThreads), (size_t)tc_smem_bytes(N_TILE), st, pdl,
+    FERRIC_CUDA_TRY(launch_kernel(gemv_tc_kernel<TY, N_TILE>, grid, dim3(kTcThreads), (size_t)tc_smem_bytes(TY, N_TILE), st, pdl,
                                   (const uint8_t*)w.units, map, ss, up, out, ld_out, split_stride, (int)w.rows, (int)w.nblk,
                                   (int)m, (int)p.m_pad, (int)w.row_tiles(), p.blocks_per_split, gemm_status_word()));
     return kOk;
@@ -547,17 +680,23 @@ int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMa
 
 bool gemv_tc_eligible(uint32_t ty, const DeviceWeights& w, size_t m)
 {
-    static const int min_m = [] {
-        const char* e = getenv("FERRIC_CUDA_GEMV_TC_MIN_M");   // 0 disables the tensor-core decode path
-        return e ? atoi(e) : 9;
+    // Measured cross-over with the mma.sync GEMV (which runs in passes of 8 activation rows): Q4_K from 9 rows, Q6_K --
+    // two operand planes, so twice the MMAs -- from 24.  FERRIC_CUDA_GEMV_TC_MIN_M overrides both; 0 disables the path.
+    static const int forced = [] {
+        const char* e = getenv("FERRIC_CUDA_GEMV_TC_MIN_M");
+        return e ? atoi(e) : -1;
     }();
-    return ty == kGgmlQ4K && min_m > 0 && m >= (size_t)min_m && m <= 4096 && w.nblk > 0 && w.rows > 0 &&
-           w.rows <= (size_t)INT32_MAX / 2;
+    if (ty != kGgmlQ4K && ty != kGgmlQ6K) return false;
+    const int min_m = forced >= 0 ? forced : (ty == kGgmlQ4K ? 9 : 24);
+    return min_m > 0 && m >= (size_t)min_m && m <= 4096 && w.nblk > 0 && w.rows > 0 && w.rows <= (size_t)INT32_MAX / 2;
 }
 
-size_t gemv_tc_scratch_bytes(const DeviceWeights& w, size_t m, Epilogue epi, int sm_count) { return tc_plan(w, m, epi, sm_count).total; }
+size_t gemv_tc_scratch_bytes(uint32_t ty, const DeviceWeights& w, size_t m, Epilogue epi, int sm_count)
+{
+    return tc_plan(ty, w, m, epi, sm_count).total;
+}
 
-int32_t launch_gemv_tc(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y, size_t ldy,
+int32_t launch_gemv_tc(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y, size_t ldy,
                        Epilogue epi, void* scratch, const GemvTuning& tune, int* launches)
 {
     EncodeTiledFn enc = tc_encode_fn();
@@ -565,7 +704,7 @@ int32_t launch_gemv_tc(cudaStream_t st, const DeviceWeights& w, const float* x, 
         set_last_error("the CUDA driver does not export cuTensorMapEncodeTiled");
         return kErrCuda;
     }
-    const TcPlan p = tc_plan(w, m, epi, tune.sm_count);
+    const TcPlan p = tc_plan(ty, w, m, epi, tune.sm_count);
     uint8_t* base = reinterpret_cast<uint8_t*>(scratch);
     __half* xl = reinterpret_cast<__half*>(base);
     float* ss = reinterpret_cast<float*>(base + p.off_ss);
@@ -589,9 +728,14 @@ int32_t launch_gemv_tc(cudaStream_t st, const DeviceWeights& w, const float* x, 
     float* out = p.needs_finish ? part : y;
     const size_t ld_out = p.needs_finish ? w.rows : ldy, split_stride = m * w.rows;
     int32_t rc;
-    if (p.n_tile == 64) rc = launch_tc_tile<64>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
-    else if (p.n_tile == 128) rc = launch_tc_tile<128>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
-    else rc = launch_tc_tile<256>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
+    if (ty == kGgmlQ6K) {
+        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ6K, 64>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
+        else rc = launch_tc_tile<kGgmlQ6K, 128>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
+    } else {
+        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ4K, 64>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
+        else if (p.n_tile == 128) rc = launch_tc_tile<kGgmlQ4K, 128>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
+        else rc = launch_tc_tile<kGgmlQ4K, 256>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
+    }
     if (rc != kOk) return rc;
     *launches += 2;
     if (p.needs_finish) {
