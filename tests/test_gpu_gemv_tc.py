@@ -1,0 +1,127 @@
+"""GPU parity of the batched decode product on the tensor cores (more than 8 activation rows).
+
+The kernel computes exactly what the GEMV computes -- integer products of the quantised weights with the
+activations' base-128 limbs, scaled per super-block in f32 -- so the bar is the decode bar: 1e-3 relative + 1e-4
+absolute against the oracle's dequantise-then-dot product (with the exact float64 product beside it, see
+test_gpu_parity.assert_close).  Every case also reads the kernel's give-up word: no bounded wait may run out.
+
+Shapes walk the kernel's branches: the three tile widths (up to 16 / 32 / 64 activation rows), more than one
+activation tile, ragged weight rows (rows not a multiple of 128 or of 16), a K split (few row tiles, many
+super-blocks) with its finish kernel, the fused SwiGLU finish, Q6_K's two operand planes with scales over the whole
+int8 range, and activations spanning many binades (one scale per row and super-block).
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from ferric_b200 import synth
+from oracle import oracle as O
+from test_gpu_parity import assert_close, exact_product
+
+pytestmark = pytest.mark.gpu
+NCPU = os.cpu_count() or 1
+
+
+@pytest.fixture(scope="module")
+def F():
+    import ferric_b200
+    return ferric_b200
+
+
+@pytest.fixture(scope="module")
+def ctx(F):
+    c = F.Context(0)
+    yield c
+    c.close()
+
+
+def run(F, ctx, raw, ty, rows, cols, x, swiglu=False):
+    qm = F.QMatrix.from_bytes(ctx, raw, ty, rows, cols)
+    xd = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    y = qm.try_matmul_swiglu(xd) if swiglu else qm.matmul(xd)
+    assert qm.gemm_status() == 0
+    out = y.cpu().numpy()
+    qm.close()
+    return out
+
+
+@pytest.mark.parametrize("ty,rows,cols,m", [
+    (12, 128, 256, 9),        # one CTA, one super-block, narrow tile
+    (12, 200, 1024, 16),      # ragged rows
+    (12, 1000, 2048, 33),     # widest tile, ragged rows
+    (12, 272, 512, 64),
+    (12, 130, 768, 70),       # two activation tiles of the widest kind, the second nearly empty
+    (12, 256, 5120, 17),      # few row tiles, 20 super-blocks: K split + finish kernel
+    (14, 128, 256, 24),       # Q6_K: two operand planes
+    (14, 200, 768, 40),       # Q6_K, two activation tiles (its tile holds 32 rows)
+    (14, 640, 4352, 64),      # Q6_K with a K split
+])
+def test_shapes(F, ctx, ty, rows, cols, m):
+    raw = synth.matrix(ty, rows, cols, seed=rows + cols + m)
+    x = synth.activations(m, cols, seed=m + ty)
+    ref = O.matmul_q(raw, ty, rows, cols, x, threads=NCPU)
+    got = run(F, ctx, raw, ty, rows, cols, x)
+    assert_close(got, ref, f"ty{ty} {rows}x{cols} m{m}", exact_product(raw, ty, rows, cols, x))
+
+
+def test_q6k_full_int8_scales(F, ctx):
+    """GGUF files use the whole int8 range for Q6_K scales; sc * (q - 32) then reaches 4064, which is why the kernel
+    splits the scale into two digits."""
+    rows, cols, m = 144, 512, 32
+    rng = np.random.default_rng(11)
+    raw = synth.q6k_blocks(rng, rows * cols // 256).reshape(-1, 210)
+    raw[:, 192:208] = rng.integers(-128, 128, size=(raw.shape[0], 16), dtype=np.int64).astype(np.int8).view(np.uint8)
+    raw[::7, 192:208] = np.array([-128, 127] * 8, dtype=np.int8).view(np.uint8)
+    raw = raw.reshape(-1)
+    x = synth.activations(m, cols, seed=3)
+    ref = O.matmul_q(raw, 14, rows, cols, x, threads=NCPU)
+    assert_close(run(F, ctx, raw, 14, rows, cols, x), ref, "q6k int8 scales", exact_product(raw, 14, rows, cols, x))
+
+
+def test_fused_swiglu_finish(F, ctx):
+    """gate|up + SwiGLU through the finish kernel against the unfused pair of calls: the reference's own bar for its
+    fused kernel is max|d| / max|ref| < 1e-5 (crates/ferric-tensor/examples/ffn_fuse.rs:100-108)."""
+    n_ff, cols, m = 384, 1024, 20
+    raw = synth.matrix(12, 2 * n_ff, cols, seed=5)
+    x = synth.activations(m, cols, seed=6)
+    got = run(F, ctx, raw, 12, 2 * n_ff, cols, x, swiglu=True)
+    assert got.shape == (m, n_ff)
+    unfused = ctx.swiglu(torch.from_numpy(run(F, ctx, raw, 12, 2 * n_ff, cols, x)).cuda(), n_ff).cpu().numpy()
+    assert np.abs(got - unfused).max() <= 1e-5 * np.abs(unfused).max()
+    ref = O.swiglu(O.matmul_q(raw, 12, 2 * n_ff, cols, x, threads=NCPU), n_ff)
+    assert np.abs(got - ref).max() <= 1e-4 * max(1.0, float(np.abs(ref).max()))
+
+
+def test_scaled_activations_zero_rows_and_outliers(F, ctx):
+    """One scale per (activation row, super-block): ranges far outside f16, an all-zero row, an all-zero super-block
+    and an outlier that sets its super-block's scale."""
+    rows, cols, m = 160, 1024, 12
+    raw = synth.matrix(12, rows, cols, seed=9)
+    base = synth.activations(m, cols, seed=9)
+    for scale in (1e-6, 3e4, 1e10):
+        x = (base * np.float32(scale)).astype(np.float32)
+        ref = O.matmul_q(raw, 12, rows, cols, x, threads=NCPU)
+        assert_close(run(F, ctx, raw, 12, rows, cols, x) / scale, ref / scale, f"scale {scale}")
+    x = base.copy()
+    x[3] = 0.0
+    x[5, 256:512] = 0.0
+    x[7, 10] = 3e5
+    got = run(F, ctx, raw, 12, rows, cols, x)
+    assert (got[3] == 0).all()
+    assert_close(got / 1e3, O.matmul_q(raw, 12, rows, cols, x, threads=NCPU) / 1e3, "outlier")
+
+
+def test_same_result_as_the_gemv_passes(F, ctx, monkeypatch):
+    """The tensor-core path and the mma.sync GEMV use the same limbs and the same integer sums; only f32
+    scaling order differs.  Their results agree far inside the tolerance."""
+    rows, cols, m = 256, 1024, 16
+    raw = synth.matrix(12, rows, cols, seed=21)
+    x = synth.activations(m, cols, seed=22)
+    got = run(F, ctx, raw, 12, rows, cols, x)
+    qm = F.QMatrix.from_bytes(ctx, raw, 12, rows, cols)
+    xd = torch.from_numpy(x).cuda()
+    halves = torch.cat([qm.matmul(xd[:8]), qm.matmul(xd[8:])]).cpu().numpy()   # 8 rows at a time: the GEMV
+    qm.close()
+    assert np.abs(got - halves).max() <= 1e-5 * np.abs(halves).max()
