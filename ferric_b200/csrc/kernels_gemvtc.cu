@@ -446,27 +446,36 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer: four K chunks per super-block into accumulator (i & 1)
+        // ---------------- MMA issuer: four K chunks per super-block into accumulator set (i & 1).  This one thread's
+        // instruction stream paces the kernel at narrow tiles, so it is kept lean: running stage counters instead of
+        // modulo / division, barrier addresses and descriptor low words advanced by adds.
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_f16(kTcRows, N_TILE);
+            const uint32_t a_full0 = smem_u32(&bar->a_full[0]), a_empty0 = smem_u32(&bar->a_empty[0]);
+            const uint32_t b_full0 = smem_u32(&bar->b_full[0]), b_empty0 = smem_u32(&bar->b_empty[0]);
+            const uint32_t adesc0 = umma_desc_lo(smem_u32(a_stage)), bdesc0 = umma_desc_lo(smem_u32(b_stage));
+            uint32_t sa = 0, pa = 0, sb = 0, pb = 0;     // stage and phase parity of the A and B rings
             for (int i = 0; i < nb && !fail; i++) {
                 const int buf = i & 1;
                 if (!mbar_wait(&bar->acc_empty[buf], (((uint32_t)i >> 1) & 1u) ^ 1u)) { fail = 3; break; }
                 tc_fence_after();
+                const uint32_t d0 = tmem_acc + (uint32_t)(buf * kPlanes * N_TILE);
+#pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const int c = 4 * i + j, sa = c % kTcAStages, sb = c % kBStages;
-                    if (!mbar_wait(&bar->a_full[sa], ((uint32_t)c / kTcAStages) & 1u) ||
-                        !mbar_wait(&bar->b_full[sb], ((uint32_t)c / kBStages) & 1u)) { fail = 3; break; }
+                    if (!mbar_try(a_full0 + 8 * sa, pa) && !mbar_wait(&bar->a_full[sa], pa)) { fail = 3; break; }
+                    if (!mbar_try(b_full0 + 8 * sb, pb) && !mbar_wait(&bar->b_full[sb], pb)) { fail = 3; break; }
                     tc_fence_after();
-                    const uint32_t a0 = smem_u32(a_stage + sa * kAStageBytes), b0 = smem_u32(b_stage + sb * kBBytes);
+                    const uint32_t ad = adesc0 + sa * (uint32_t)(kAStageBytes >> 4), bd = bdesc0 + sb * (uint32_t)(kBBytes >> 4);
 #pragma unroll
                     for (int k4 = 0; k4 < 4; k4++)
 #pragma unroll
                         for (int pl = 0; pl < kPlanes; pl++)
-                            umma_bf16(tmem_acc + (buf * kPlanes + pl) * N_TILE, umma_desc_sw128(a0 + pl * kTcABytes + 32 * k4),
-                                      umma_desc_sw128(b0 + 32 * k4), idesc, (j | k4) ? 1u : 0u);
-                    umma_commit(&bar->a_empty[sa]);
-                    umma_commit(&bar->b_empty[sb]);
+                            umma_f16_lo(d0 + pl * N_TILE, ad + (uint32_t)(pl * (kTcABytes >> 4) + 2 * k4), bd + 2 * k4, idesc,
+                                        (j | k4) ? 1u : 0u);
+                    umma_commit_addr(a_empty0 + 8 * sa);
+                    umma_commit_addr(b_empty0 + 8 * sb);
+                    if (++sa == (uint32_t)kTcAStages) { sa = 0; pa ^= 1u; }
+                    if (++sb == (uint32_t)kBStages) { sb = 0; pb ^= 1u; }
                 }
                 if (!fail) umma_commit(&bar->acc_full[buf]);
             }

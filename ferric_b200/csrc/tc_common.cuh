@@ -120,6 +120,42 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The same MMA with the shared-memory descriptors given by their low words only (address field | leading-dimension
+// field); the high word is the same for every 128-byte-swizzled K-major tile.  The issuing thread's instruction stream
+// is the critical path of the narrow-tile kernels, so the per-MMA arithmetic is one 32-bit add per operand:
+// advancing a descriptor by b bytes adds b >> 4 to its low word.
+constexpr uint32_t kUmmaDescHiSw128 = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+__device__ __forceinline__ void umma_f16_lo(uint32_t tmem_d, uint32_t adesc_lo, uint32_t bdesc_lo, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{ .reg .pred p; .reg .b64 da, db; mov.b64 da, {%1, %5}; mov.b64 db, {%2, %5}; setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p; }" ::"r"(tmem_d),
+        "r"(adesc_lo), "r"(bdesc_lo), "r"(idesc), "r"(accumulate), "r"(kUmmaDescHiSw128)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_lo_pair(uint32_t tmem_d, uint32_t adesc_lo, uint32_t bdesc_lo, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{ .reg .pred p; .reg .b64 da, db; mov.b64 da, {%1, %5}; mov.b64 db, {%2, %5}; setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p; }" ::"r"(tmem_d),
+        "r"(adesc_lo), "r"(bdesc_lo), "r"(idesc), "r"(accumulate), "r"(kUmmaDescHiSw128)
+        : "memory");
+}
+// One poll of a barrier phase (the fast path of mbar_wait, for loops that keep their own give-up logic).
+__device__ __forceinline__ bool mbar_try(uint32_t bar_addr, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok)
+                 : "r"(bar_addr), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar_addr)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
