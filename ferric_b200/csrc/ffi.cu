@@ -469,8 +469,12 @@ int32_t ferric_cuda_matmul_q_bf16(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm
         return kErrShape;
     }
     DeviceGuard guard(ctx->device);
-    ctx->launches++;
-    return launch_gemm_bf16(ctx->stream, qm->ty, qm->w, x_bf16_dev, m, qm->w.cols, y_dev, qm->w.rows);
+    // tiles of a partly filled last wave are cut along K; their pieces meet in the context's scratch
+    const size_t ws = gemm_workspace_bytes(qm->w, m, ctx->tune.sm_count);
+    if (ws > 0 && (rc = ensure_scratch(ctx, ws)) != kOk) return rc;
+    ctx->launches += ws > 0 ? 2 : 1;
+    return launch_gemm_bf16(ctx->stream, qm->ty, qm->w, x_bf16_dev, m, qm->w.cols, y_dev, qm->w.rows, ws > 0 ? ctx->scratch : nullptr,
+                            ctx->tune.sm_count);
 }
 
 int32_t ferric_cuda_gemm_status(ferric_cuda_ctx* ctx, int32_t* code)

@@ -75,8 +75,10 @@ int32_t launch_add_rmsnorm(cudaStream_t st, const float* a, const float* b, cons
 
 // Prefill product on the tcgen05 tensor cores: y[m, rows] (f32, row stride ldy) = x . W^T with Q4_K or Q6_K weights
 // dequantised to bf16 (round to nearest even) and bf16 activations x[m, cols] (row stride ldx elements).
+// `workspace` holds gemm_workspace_bytes() bytes (0 when no tile of the launch is cut along K); without it no tile is cut.
+size_t gemm_workspace_bytes(const DeviceWeights& w, size_t m, int sm_count);
 int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint16_t* x_bf16, size_t m, size_t ldx,
-                         float* y, size_t ldy);
+                         float* y, size_t ldy, void* workspace, int sm_count);
 // Batched decode product on the tensor cores with exact integer arithmetic (Q4_K and Q6_K, m >= 9 by default): preparation,
 // product and, for K-split or SwiGLU, a finish kernel.  `scratch` holds gemv_tc_scratch_bytes() bytes.
 bool gemv_tc_eligible(uint32_t ty, const DeviceWeights& w, size_t m);

@@ -311,11 +311,23 @@ __device__ __forceinline__ int dequant_loop_q6k(GemmBarriers* bar, uint8_t* a_st
     return fail;
 }
 
+// How a paired launch walks its tiles.  Pair tiles (256 weight rows x N_TILE activation rows) are numbered
+// p = px + pairs_x * ny.  The first `full` of them are computed whole, one pair of CTAs each.  The rest -- the tiles
+// that would make up a partly filled last wave -- are cut along K into `splits` pieces of `bps` super-blocks, each piece
+// a pair of CTAs of its own that writes a partial tile to a workspace; a finish kernel adds the pieces in order.
+struct GemmSplit {
+    int pairs_x;     // pair tiles along the weight rows
+    int full;        // tiles computed whole
+    int splits;      // pieces per remaining tile (1 = none are cut)
+    int bps;         // super-blocks per piece
+};
+
 template <uint32_t TY, int N_TILE, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap,
-                     const __grid_constant__ CUtensorMap ymap, int tma_store, float* __restrict__ y, int rows, int nblk, int m,
-                     size_t ldy, int row_tiles16, int* __restrict__ err)
+                     const __grid_constant__ CUtensorMap ymap, const __grid_constant__ CUtensorMap wsmap, GemmSplit split,
+                     int tma_store, float* __restrict__ y, int rows, int nblk, int m, size_t ldy, int row_tiles16,
+                     int* __restrict__ err)
 {
     extern __shared__ uint8_t gemm_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -330,11 +342,26 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
     GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(raw_stage + kGemmRawStages * kRawBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * kGemmRows, n0 = blockIdx.y * N_TILE;
-    const int rt0 = blockIdx.x * 8;                                        // first 16-row tile of this CTA
-    const int tiles_here = max(0, min(8, row_tiles16 - rt0));              // 0: padding CTA of an odd pair
-    const int nchunks = nblk * 4;
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;                   // rank 0 leads the pair
+    // which tile, and which range of super-blocks of it
+    int tile_x = blockIdx.x, tile_y = blockIdx.y, blk0 = 0, nb = nblk, piece = -1;
+    if (PAIR) {
+        const int item = blockIdx.x >> 1;
+        int p = item;
+        if (item >= split.full) {
+            const int e = item - split.full;
+            p = split.full + e / split.splits;
+            piece = e;                                                     // index of this partial tile in the workspace
+            blk0 = (e % split.splits) * split.bps;
+            nb = max(0, min(nblk, blk0 + split.bps) - blk0);
+        }
+        tile_x = 2 * (p % split.pairs_x) + (int)rank;
+        tile_y = p / split.pairs_x;
+    }
+    const int row0 = tile_x * kGemmRows, n0 = tile_y * N_TILE;
+    const int rt0 = tile_x * 8;                                            // first 16-row tile of this CTA
+    const int tiles_here = max(0, min(8, row_tiles16 - rt0));              // 0: padding CTA of an odd pair
+    const int nchunks = nb * 4;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kGemmRawStages; i++) {
@@ -376,12 +403,12 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
     if (warp == 0) {
         // ---------------- weight producer: raw quant units of one super-block per stage
         if (lane == 0) {
-            for (int b = 0; b < nblk; b++) {
+            for (int b = 0; b < nb; b++) {
                 const int rs = b % kGemmRawStages;
                 if (!mbar_wait(&bar->raw_empty[rs], (((uint32_t)b / kGemmRawStages) & 1u) ^ 1u)) { fail = 1; break; }
                 mbar_expect_tx(&bar->raw_full[rs], (uint32_t)(tiles_here * kUnit));
                 for (int t = 0; t < tiles_here; t++)
-                    bulk_g2s(raw_stage + rs * kRawBytes + t * kUnit, units + ((size_t)(rt0 + t) * nblk + b) * kUnit, kUnit,
+                    bulk_g2s(raw_stage + rs * kRawBytes + t * kUnit, units + ((size_t)(rt0 + t) * nblk + blk0 + b) * kUnit, kUnit,
                              &bar->raw_full[rs]);
             }
         }
@@ -397,7 +424,7 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
                     mbar_expect_tx_cluster(full, (uint32_t)kBBytes);
 #pragma unroll
                     for (int h = 0; h < N_TILE / kNMma; h++)
-                        tma_load_2d_pair(b_stage + s * kBBytes + h * kBoxRows * 128, &xmap, c * kGemmChunkK,
+                        tma_load_2d_pair(b_stage + s * kBBytes + h * kBoxRows * 128, &xmap, (4 * blk0 + c) * kGemmChunkK,
                                          n0 + h * kNMma + (int)rank * kBoxRows, full);
                 } else {
                     mbar_expect_tx(&bar->b_full[s], (uint32_t)kBBytes);
@@ -442,8 +469,8 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
     } else {
         // ---------------- dequantise (per quant type, above), then the epilogue
         const int wq = warp - kGemmFirstDeqWarp;
-        if (TY == kGgmlQ4K) fail = dequant_loop_q4k<PAIR>(bar, a_stage, raw_stage, nblk, tiles_here, wq, lane);
-        else fail = dequant_loop_q6k<PAIR>(bar, a_stage, raw_stage, nblk, tiles_here, wq, lane);
+        if (TY == kGgmlQ4K) fail = dequant_loop_q4k<PAIR>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
+        else fail = dequant_loop_q6k<PAIR>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
         // ---------------- epilogue.  All dequant warps first agree that nobody gave up (the staged path below
         // synchronises them with named barriers, which must not be entered by only some of them).
         if (fail) atomicExch(&bar->abort, fail);
@@ -477,9 +504,14 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
                     fence_proxy_async();
                     named_bar_sync(2 + grp, 128);
                     if (elected && row0 < rows) {
-                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&ymap),
-                                     "r"(row0), "r"(n0 + c0), "r"(smem_u32(stg))
-                                     : "memory");
+                        if (piece < 0)   // a whole tile: straight into y
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&ymap),
+                                         "r"(row0), "r"(n0 + c0), "r"(smem_u32(stg))
+                                         : "memory");
+                        else             // a K piece: into partial tile `piece` of the workspace, [N_TILE][256] f32
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&wsmap),
+                                         "r"((int)rank * kGemmRows), "r"(piece * N_TILE + c0), "r"(smem_u32(stg))
+                                         : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 }
@@ -521,6 +553,20 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
     }
 }
 
+// Adds the K pieces of the cut tiles, in piece order, into y.  One block per (cut tile, activation row of it), one
+// thread per weight row of the 256-row pair tile.
+template <int N_TILE>
+__global__ void __launch_bounds__(256)
+gemm_finish_kernel(const float* __restrict__ ws, GemmSplit split, float* __restrict__ y, size_t ldy, int rows, int m)
+{
+    const int e_tile = blockIdx.x / N_TILE, c = blockIdx.x % N_TILE, r = threadIdx.x;
+    const int p = split.full + e_tile, row = (p % split.pairs_x) * 2 * kGemmRows + r, act = (p / split.pairs_x) * N_TILE + c;
+    if (row >= rows || act >= m) return;
+    float sum = 0.0f;
+    for (int s = 0; s < split.splits; s++) sum += ws[((size_t)(e_tile * split.splits + s) * N_TILE + c) * (2 * kGemmRows) + r];
+    y[(size_t)act * ldy + row] = sum;
+}
+
 // ---------------------------------------------------------------- host side
 // Set by a CTA whose bounded wait ran out (the code says which role gave up); read by gemm_status().
 static __device__ int g_gemm_status = 0;
@@ -552,8 +598,8 @@ EncodeTiledFn encode_tiled_fn()
 }
 
 template <uint32_t TY, int N_TILE, bool PAIR>
-int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& ymap, int tma_store,
-                         size_t m, float* y, size_t ldy)
+int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& ymap,
+                         const CUtensorMap& wsmap, const GemmSplit& split, int tma_store, size_t m, float* y, size_t ldy)
 {
     static bool attr_done[64] = {};
     int dev = 0;
@@ -565,10 +611,18 @@ int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensor
     }
     int* err = nullptr;
     FERRIC_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_gemm_status));
+    const unsigned n_tiles = (unsigned)((m + N_TILE - 1) / N_TILE);
     unsigned gx = (unsigned)((w.rows + kGemmRows - 1) / kGemmRows);
-    if (PAIR) gx = (gx + 1) & ~1u;   // whole pairs; a padding CTA multiplies zeros and stores nothing
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(gx, (unsigned)((m + N_TILE - 1) / N_TILE));
+    if (PAIR) {
+        // one pair of CTAs per work item: the whole tiles, then the K pieces of the cut ones (an odd row-tile count
+        // leaves a padding CTA that multiplies zeros and stores nothing)
+        const unsigned tiles = (unsigned)split.pairs_x * n_tiles;
+        const unsigned items = (unsigned)split.full + (tiles - (unsigned)split.full) * (unsigned)split.splits;
+        cfg.gridDim = dim3(2 * items, 1);
+    } else {
+        cfg.gridDim = dim3(gx, n_tiles);
+    }
     cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -579,8 +633,8 @@ int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensor
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    FERRIC_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_q_bf16_kernel<TY, N_TILE, PAIR>, (const uint8_t*)w.units, map, ymap, tma_store, y,
-                                       (int)w.rows, (int)w.nblk, (int)m, ldy, (int)w.row_tiles(), err));
+    FERRIC_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_q_bf16_kernel<TY, N_TILE, PAIR>, (const uint8_t*)w.units, map, ymap, wsmap, split,
+                                       tma_store, y, (int)w.rows, (int)w.nblk, (int)m, ldy, (int)w.row_tiles(), err));
     return kOk;
 }
 
@@ -596,17 +650,53 @@ bool gemm_pair_enabled()
 }  // namespace
 
 template <uint32_t TY>
-static int32_t launch_gemm_ty(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& ymap, int tma_store,
-                              size_t m, float* y, size_t ldy, int n_tile, bool pair)
+static int32_t launch_gemm_ty(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& ymap,
+                              const CUtensorMap& wsmap, const GemmSplit& split, int tma_store, size_t m, float* y, size_t ldy,
+                              int n_tile, bool pair)
 {
-    if (n_tile == 128) return launch_gemm_tile<TY, 128, false>(st, w, map, ymap, tma_store, m, y, ldy);
-    if (n_tile == 256) return launch_gemm_tile<TY, 256, false>(st, w, map, ymap, tma_store, m, y, ldy);
-    if (!pair) return launch_gemm_tile<TY, 512, false>(st, w, map, ymap, tma_store, m, y, ldy);
-    return launch_gemm_tile<TY, 512, true>(st, w, map, ymap, tma_store, m, y, ldy);
+    if (n_tile == 128) return launch_gemm_tile<TY, 128, false>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy);
+    if (n_tile == 256) return launch_gemm_tile<TY, 256, false>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy);
+    if (!pair) return launch_gemm_tile<TY, 512, false>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy);
+    return launch_gemm_tile<TY, 512, true>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy);
+}
+
+// The cut: with P pair tiles on `slots` pair slots, the P mod slots tiles of the last, partly filled wave are each cut into
+// as many K pieces as fill that wave (fewer tiles than slots: every tile is cut).  FERRIC_CUDA_GEMM_SPLIT=0 disables it.
+GemmSplit gemm_split_plan(const DeviceWeights& w, size_t m, int n_tile, int sm_count)
+{
+    static const bool enabled = [] {
+        const char* e = getenv("FERRIC_CUDA_GEMM_SPLIT");
+        return !(e && e[0] == '0');
+    }();
+    GemmSplit sp;
+    sp.pairs_x = (int)((w.rows + 2 * kGemmRows - 1) / (2 * kGemmRows));
+    const int tiles = sp.pairs_x * (int)((m + n_tile - 1) / n_tile), slots = sm_count / 2 > 0 ? sm_count / 2 : 1;
+    sp.full = tiles;
+    sp.splits = 1;
+    sp.bps = (int)w.nblk;
+    const int excess = tiles % slots;
+    if (!enabled || excess == 0) return sp;
+    int want = slots / excess;                            // pieces per cut tile that fill the last wave
+    if (want > (int)w.nblk / 2) want = (int)w.nblk / 2;   // at least two super-blocks per piece
+    if (want > 16) want = 16;
+    if (want < 2) return sp;
+    sp.bps = ((int)w.nblk + want - 1) / want;
+    sp.splits = ((int)w.nblk + sp.bps - 1) / sp.bps;      // every piece is non-empty
+    sp.full = tiles - excess;
+    return sp;
+}
+
+size_t gemm_workspace_bytes(const DeviceWeights& w, size_t m, int sm_count)
+{
+    if (m <= 256 || !gemm_pair_enabled()) return 0;
+    const GemmSplit sp = gemm_split_plan(w, m, 512, sm_count);
+    if (sp.splits <= 1) return 0;
+    const size_t tiles = (size_t)sp.pairs_x * ((m + 511) / 512);
+    return (tiles - (size_t)sp.full) * (size_t)sp.splits * 512 * (2 * kGemmRows) * sizeof(float);
 }
 
 int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint16_t* x_bf16, size_t m, size_t ldx,
-                         float* y, size_t ldy)
+                         float* y, size_t ldy, void* workspace, int sm_count)
 {
     if (ty != kGgmlQ4K && ty != kGgmlQ6K) return kUnsupported;
     if (m == 0 || w.rows == 0 || w.nblk == 0) return kOk;
@@ -650,8 +740,34 @@ int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
         }
         tma_store = 1;
     }
-    return ty == kGgmlQ4K ? launch_gemm_ty<kGgmlQ4K>(st, w, map, ymap, tma_store, m, y, ldy, n_tile, pair)
-                          : launch_gemm_ty<kGgmlQ6K>(st, w, map, ymap, tma_store, m, y, ldy, n_tile, pair);
+    // The K pieces of cut tiles go to the workspace as partial tiles [piece][512 activation rows][256 weight rows].
+    GemmSplit split = gemm_split_plan(w, m, n_tile, sm_count);
+    if (!pair || !tma_store || !workspace) {
+        split.full = split.pairs_x * (int)((m + n_tile - 1) / n_tile);
+        split.splits = 1;
+        split.bps = (int)w.nblk;
+    }
+    CUtensorMap wsmap;
+    memset(&wsmap, 0, sizeof(wsmap));
+    const size_t cut_tiles = (size_t)split.pairs_x * ((m + n_tile - 1) / n_tile) - (size_t)split.full;
+    if (split.splits > 1) {
+        const cuuint64_t wdims[2] = {(cuuint64_t)(2 * kGemmRows), (cuuint64_t)(cut_tiles * split.splits * n_tile)};
+        const cuuint64_t wstrides[1] = {(cuuint64_t)(2 * kGemmRows) * 4};
+        const cuuint32_t wbox[2] = {(cuuint32_t)kGemmRows, 32};
+        r = enc(&wsmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, workspace, wdims, wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            set_last_error("cuTensorMapEncodeTiled (workspace) failed with code %d", (int)r);
+            return kErrCuda;
+        }
+    }
+    int32_t rc = ty == kGgmlQ4K ? launch_gemm_ty<kGgmlQ4K>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy, n_tile, pair)
+                                : launch_gemm_ty<kGgmlQ6K>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy, n_tile, pair);
+    if (rc != kOk || split.splits <= 1) return rc;
+    gemm_finish_kernel<512><<<(unsigned)(cut_tiles * 512), 256, 0, st>>>(reinterpret_cast<const float*>(workspace), split, y, ldy,
+                                                                        (int)w.rows, (int)m);
+    FERRIC_CUDA_TRY(cudaGetLastError());
+    return kOk;
 }
 
 // Synchronises the stream, returns the code of the first bounded wait that ran out (0 = none) and clears it.

@@ -213,8 +213,10 @@ int32_t ferric_cuda_matmul_q_noalloc(ferric_cuda_ctx *ctx, const ferric_qmatrix 
  * 256 activation rows: a pair of CTAs) owns 128 (256) weight rows x up to 512 activation rows,
  * K advances in chunks of 64, and the multiply is tcgen05.mma with the f32 accumulator in tensor
  * memory.  Q4_K only (other types return FERRIC_UNSUPPORTED); any m >= 1 works but the kernel is
- * meant for m >= 128.  Asynchronous on the context's stream.  FERRIC_CUDA_GEMM_PAIR=0 in the
- * environment keeps every tile on a single CTA. */
+ * meant for m >= 128.  Asynchronous on the context's stream.  Tiles of a partly filled last wave
+ * are cut along K; their pieces meet in the context's scratch (up to 37 MB, grown on demand --
+ * ferric_cuda_ctx_reserve_scratch beforehand when capturing).  FERRIC_CUDA_GEMM_PAIR=0 in the
+ * environment keeps every tile on a single CTA, FERRIC_CUDA_GEMM_SPLIT=0 never cuts a tile. */
 int32_t ferric_cuda_matmul_q_bf16(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const uint16_t *x_bf16_dev, size_t m,
                                   size_t x_cols, float *y_dev);
 
