@@ -443,6 +443,9 @@ size_t ferric_cuda_qmatrix_scratch_bytes(const ferric_qmatrix* qm, size_t m)
         const size_t tc = gemv_tc_scratch_bytes(qm->ty, qm->w, m, kEpiSwiglu, 148);
         if (tc > need) need = tc;
     }
+    // the bf16 prefill product cuts the tiles of a partly filled last wave along K and meets their pieces there
+    const size_t ws = gemm_workspace_bytes(qm->w, m, 148);
+    if (ws > need) need = ws;
     return need;
 }
 

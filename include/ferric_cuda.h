@@ -138,7 +138,7 @@ size_t ferric_cuda_qmatrix_n_shards(const ferric_qmatrix *qm);
 uint32_t ferric_cuda_qmatrix_ggml_type(const ferric_qmatrix *qm);
 void ferric_cuda_qmatrix_free(ferric_qmatrix *qm);
 
-/* Bytes of context scratch one matmul_q with m activation rows needs for this matrix. */
+/* Bytes of context scratch any product call (matmul_q*, matmul_q_bf16) with m activation rows needs for this matrix. */
 size_t ferric_cuda_qmatrix_scratch_bytes(const ferric_qmatrix *qm, size_t m);
 
 /* Tensor::matmul_q(&QMatrix)   crates/ferric-tensor/src/dtype.rs:935-944 -> matmul_q4_k :1426-1473,
