@@ -463,10 +463,6 @@ int32_t ferric_cuda_matmul_q_bf16(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm
 {
     int32_t rc = check_matmul_args(ctx, qm, x_bf16_dev, m, x_cols, y_dev);
     if (rc != kOk) return rc;
-    if (qm->ty != kGgmlQ4K && qm->ty != kGgmlQ6K) {
-        set_last_error("the bf16 tensor-core product is built for Q4_K and Q6_K (ggml types 12, 14), matrix is type %u", qm->ty);
-        return kUnsupported;
-    }
     if (m > (size_t)INT32_MAX || qm->w.rows > (size_t)INT32_MAX) {
         set_last_error("matrix or batch too large");
         return kErrShape;

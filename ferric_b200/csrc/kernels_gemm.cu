@@ -44,7 +44,13 @@ constexpr int kGemmFirstDeqWarp = 3;                   // warp 0 weight producer
 constexpr int kGemmThreads = 32 * (kGemmFirstDeqWarp + kGemmDeqWarps);
 // raw quant bytes of one stage: 8 row tiles x one super-block (18432 for Q4_K, 26880 for Q6_K)
 __host__ __device__ constexpr int gemm_unit_bytes(uint32_t ty) { return ty == kGgmlQ4K ? kQ4KUnit : kQ6KUnit; }
-__host__ __device__ constexpr int gemm_raw_bytes(uint32_t ty) { return 8 * gemm_unit_bytes(ty); }
+// Q8_0 is stored as planes ([rows][cols] int8 and [rows][cols/32] f16); a stage holds the tile of 128 rows x 256 columns
+// of the first (32 KB, fetched as one TMA box) and its 128 x 8 scales (2 KB, a second box).
+constexpr int kGemmQ8QsBytes = kGemmRows * 256, kGemmQ8DBytes = kGemmRows * 16;
+__host__ __device__ constexpr int gemm_raw_bytes(uint32_t ty)
+{
+    return ty == kGgmlQ8_0 ? kGemmQ8QsBytes + kGemmQ8DBytes : 8 * gemm_unit_bytes(ty);
+}
 constexpr int kGemmABytes = kGemmRows * 128;                  // 16384 per stage
 constexpr int kGemmStoreBytes = 32 * kGemmRows * 4;            // one [32 activation rows][128 weight rows] f32 store tile
 
@@ -77,7 +83,10 @@ static_assert(gemm_b_stages(kGgmlQ6K, 128, false) == 7 && gemm_b_stages(kGgmlQ6K
                   gemm_b_stages(kGgmlQ6K, 512, true) == 3,
               "Q6_K stage counts");
 // The epilogue stages its stores in the activation ring: two groups x two [32][128] f32 tiles.
-static_assert(gemm_b_stages(kGgmlQ6K, 256, false) * gemm_b_bytes(256) >= 4 * 32 * 128 * 4, "store staging fits");
+static_assert(gemm_b_stages(kGgmlQ8_0, 128, false) >= 3 && gemm_b_stages(kGgmlQ8_0, 256, false) >= 3 &&
+                  gemm_b_stages(kGgmlQ8_0, 512, true) >= 3,
+              "Q8_0 stage counts (its 512-wide tile exists only in the paired form)");
+static_assert(gemm_b_stages(kGgmlQ8_0, 256, false) * gemm_b_bytes(256) >= 4 * 32 * 128 * 4, "store staging fits");
 
 // ---------------------------------------------------------------- the kernel
 struct GemmBarriers {
@@ -311,6 +320,70 @@ __device__ __forceinline__ int dequant_loop_q6k(GemmBarriers* bar, uint8_t* a_st
     return fail;
 }
 
+// Q8_0 (crates/ferric-gguf/src/lib.rs:608-615: out = q * d): a stage holds [128 rows][256] int8 and [128][8] f16
+// scales.  Thread = (row, 32-value block of the K chunk); q * d is exact in f32 (8 x 11 bits), then rounded to bf16.
+template <bool PAIR>
+__device__ __forceinline__ int dequant_loop_q8_0(GemmBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, int nb, int wq,
+                                                 int lane)
+{
+    int fail = 0;
+    const int td = 32 * wq + lane, r = td >> 1, half = td & 1;
+    const uint32_t arow_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+    const uint64_t mg = pack_f32x2(-8388736.f, -8388736.f);   // -(2^23 + 128)
+    for (int b = 0; b < nb && !fail; b++) {
+        const int rs = b % kGemmRawStages;
+        if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)b / kGemmRawStages) & 1u)) { fail = 4; break; }
+        const uint8_t* st = raw_stage + rs * gemm_raw_bytes(kGgmlQ8_0);
+        uint4 qv[4][2];
+        const uint4 dv = *reinterpret_cast<const uint4*>(st + kGemmQ8QsBytes + 16 * r);   // the row's 8 scales
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            qv[j][0] = *reinterpret_cast<const uint4*>(st + 256 * r + 64 * j + 32 * half);
+            qv[j][1] = *reinterpret_cast<const uint4*>(st + 256 * r + 64 * j + 32 * half + 16);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar->raw_empty[rs]);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t dw = j == 0 ? dv.x : (j == 1 ? dv.y : (j == 2 ? dv.z : dv.w));
+            const float d = __half2float(__ushort_as_half((unsigned short)(half ? (dw >> 16) : (dw & 0xffffu))));
+            const uint64_t dd = pack_f32x2(d, d);
+            uint4 out[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {   // 8 values -> one 16-byte column
+                const uint32_t w0 = (i & 1) ? qv[j][i >> 1].z : qv[j][i >> 1].x, w1 = (i & 1) ? qv[j][i >> 1].w : qv[j][i >> 1].y;
+                auto two = [&](uint32_t w, int e) {
+                    // byte + 128 dropped into the mantissa of 2^23; subtracting 2^23 + 128 leaves the signed value exactly
+                    const uint32_t u = w ^ 0x80808080u;
+                    const uint64_t f = pack_f32x2(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650 + e)),
+                                                  __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651 + e)));
+                    uint64_t q, v;
+                    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(q) : "l"(f), "l"(mg));
+                    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(q), "l"(dd));
+                    float lo, hi;
+                    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+                    uint32_t rr;
+                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(rr) : "f"(hi), "f"(lo));
+                    return rr;
+                };
+                out[i] = make_uint4(two(w0, 0), two(w0, 2), two(w1, 0), two(w1, 2));
+            }
+            const int c = 4 * b + j, s = c % kGemmStages;
+            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
+            uint8_t* arow = a_stage + s * kGemmABytes + arow_off;
+#pragma unroll
+            for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(arow + (((4 * half + i) ^ (r & 7)) << 4)) = out[i];
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
+                else mbar_arrive(&bar->a_full[s]);
+            }
+        }
+    }
+    return fail;
+}
+
 // How a paired launch walks its tiles.  Pair tiles (256 weight rows x N_TILE activation rows) are numbered
 // p = px + pairs_x * ny.  The first `full` of them are computed whole, one pair of CTAs each.  The rest -- the tiles
 // that would make up a partly filled last wave -- are cut along K into `splits` pieces of `bps` super-blocks, each piece
@@ -325,7 +398,8 @@ struct GemmSplit {
 template <uint32_t TY, int N_TILE, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap,
-                     const __grid_constant__ CUtensorMap ymap, const __grid_constant__ CUtensorMap wsmap, GemmSplit split,
+                     const __grid_constant__ CUtensorMap ymap, const __grid_constant__ CUtensorMap wsmap,
+                     const __grid_constant__ CUtensorMap q8map, const __grid_constant__ CUtensorMap q8dmap, GemmSplit split,
                      int tma_store, float* __restrict__ y, int rows, int nblk, int m, size_t ldy, int row_tiles16,
                      int* __restrict__ err)
 {
@@ -406,6 +480,12 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
             for (int b = 0; b < nb; b++) {
                 const int rs = b % kGemmRawStages;
                 if (!mbar_wait(&bar->raw_empty[rs], (((uint32_t)b / kGemmRawStages) & 1u) ^ 1u)) { fail = 1; break; }
+                if (TY == kGgmlQ8_0) {   // two boxes; rows and columns past the matrix read as zeros
+                    mbar_expect_tx(&bar->raw_full[rs], (uint32_t)kRawBytes);
+                    tma_load_2d(raw_stage + rs * kRawBytes, &q8map, 256 * (blk0 + b), row0, &bar->raw_full[rs]);
+                    tma_load_2d(raw_stage + rs * kRawBytes + kGemmQ8QsBytes, &q8dmap, 8 * (blk0 + b), row0, &bar->raw_full[rs]);
+                    continue;
+                }
                 mbar_expect_tx(&bar->raw_full[rs], (uint32_t)(tiles_here * kUnit));
                 for (int t = 0; t < tiles_here; t++)
                     bulk_g2s(raw_stage + rs * kRawBytes + t * kUnit, units + ((size_t)(rt0 + t) * nblk + blk0 + b) * kUnit, kUnit,
@@ -470,7 +550,8 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
         // ---------------- dequantise (per quant type, above), then the epilogue
         const int wq = warp - kGemmFirstDeqWarp;
         if (TY == kGgmlQ4K) fail = dequant_loop_q4k<PAIR>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
-        else fail = dequant_loop_q6k<PAIR>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
+        else if (TY == kGgmlQ6K) fail = dequant_loop_q6k<PAIR>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
+        else fail = dequant_loop_q8_0<PAIR>(bar, a_stage, raw_stage, nb, wq, lane);
         // ---------------- epilogue.  All dequant warps first agree that nobody gave up (the staged path below
         // synchronises them with named barriers, which must not be entered by only some of them).
         if (fail) atomicExch(&bar->abort, fail);
@@ -599,7 +680,8 @@ EncodeTiledFn encode_tiled_fn()
 
 template <uint32_t TY, int N_TILE, bool PAIR>
 int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& ymap,
-                         const CUtensorMap& wsmap, const GemmSplit& split, int tma_store, size_t m, float* y, size_t ldy)
+                         const CUtensorMap& wsmap, const CUtensorMap* q8maps, const GemmSplit& split, int tma_store, size_t m,
+                         float* y, size_t ldy)
 {
     static bool attr_done[64] = {};
     int dev = 0;
@@ -633,8 +715,8 @@ int32_t launch_gemm_tile(cudaStream_t st, const DeviceWeights& w, const CUtensor
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    FERRIC_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_q_bf16_kernel<TY, N_TILE, PAIR>, (const uint8_t*)w.units, map, ymap, wsmap, split,
-                                       tma_store, y, (int)w.rows, (int)w.nblk, (int)m, ldy, (int)w.row_tiles(), err));
+    FERRIC_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_q_bf16_kernel<TY, N_TILE, PAIR>, (const uint8_t*)w.units, map, ymap, wsmap, q8maps[0],
+                                       q8maps[1], split, tma_store, y, (int)w.rows, (int)w.nblk, (int)m, ldy, (int)w.row_tiles(), err));
     return kOk;
 }
 
@@ -651,13 +733,14 @@ bool gemm_pair_enabled()
 
 template <uint32_t TY>
 static int32_t launch_gemm_ty(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& ymap,
-                              const CUtensorMap& wsmap, const GemmSplit& split, int tma_store, size_t m, float* y, size_t ldy,
-                              int n_tile, bool pair)
+                              const CUtensorMap& wsmap, const CUtensorMap* q8maps, const GemmSplit& split, int tma_store, size_t m,
+                              float* y, size_t ldy, int n_tile, bool pair)
 {
-    if (n_tile == 128) return launch_gemm_tile<TY, 128, false>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy);
-    if (n_tile == 256) return launch_gemm_tile<TY, 256, false>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy);
-    if (!pair) return launch_gemm_tile<TY, 512, false>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy);
-    return launch_gemm_tile<TY, 512, true>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy);
+    if (n_tile == 128) return launch_gemm_tile<TY, 128, false>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy);
+    if (n_tile == 256) return launch_gemm_tile<TY, 256, false>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy);
+    if (pair) return launch_gemm_tile<TY, 512, true>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy);
+    if constexpr (TY != kGgmlQ8_0) return launch_gemm_tile<TY, 512, false>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy);
+    return kUnsupported;   // not reached: Q8_0 takes 256-wide tiles when pairing is off
 }
 
 // The cut: with P pair tiles on `slots` pair slots, the P mod slots tiles of the last, partly filled wave are each cut into
@@ -689,17 +772,27 @@ GemmSplit gemm_split_plan(const DeviceWeights& w, size_t m, int n_tile, int sm_c
 size_t gemm_workspace_bytes(const DeviceWeights& w, size_t m, int sm_count)
 {
     if (m <= 256 || !gemm_pair_enabled()) return 0;
-    const GemmSplit sp = gemm_split_plan(w, m, 512, sm_count);
+    DeviceWeights wl = w;
+    if (w.q8_qs) wl.nblk = w.cols / 256;   // Q8_0: the kernel walks K in groups of 256
+    const GemmSplit sp = gemm_split_plan(wl, m, 512, sm_count);
     if (sp.splits <= 1) return 0;
     const size_t tiles = (size_t)sp.pairs_x * ((m + 511) / 512);
     return (tiles - (size_t)sp.full) * (size_t)sp.splits * 512 * (2 * kGemmRows) * sizeof(float);
 }
 
-int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint16_t* x_bf16, size_t m, size_t ldx,
+int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w_in, const uint16_t* x_bf16, size_t m, size_t ldx,
                          float* y, size_t ldy, void* workspace, int sm_count)
 {
-    if (ty != kGgmlQ4K && ty != kGgmlQ6K) return kUnsupported;
-    if (m == 0 || w.rows == 0 || w.nblk == 0) return kOk;
+    if (ty != kGgmlQ4K && ty != kGgmlQ6K && ty != kGgmlQ8_0) return kUnsupported;
+    if (m == 0 || w_in.rows == 0 || w_in.nblk == 0) return kOk;
+    DeviceWeights w = w_in;
+    if (ty == kGgmlQ8_0) {
+        if (w.cols % 256 != 0) {
+            set_last_error("the Q8_0 tensor-core product needs a multiple of 256 columns, matrix has %zu", w.cols);
+            return kUnsupported;
+        }
+        w.nblk = w.cols / 256;   // the kernel walks K in groups of 256 for every format
+    }
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (ldx * 2) % 16 != 0) {
         set_last_error("bf16 activations must be 16-byte aligned with a row stride that is a multiple of 8 elements");
         return kErrInvalidArg;
@@ -709,7 +802,8 @@ int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
         set_last_error("the CUDA driver does not export cuTensorMapEncodeTiled");
         return kErrCuda;
     }
-    const int n_tile = m <= 128 ? 128 : (m <= 256 ? 256 : 512);
+    int n_tile = m <= 128 ? 128 : (m <= 256 ? 256 : 512);
+    if (ty == kGgmlQ8_0 && !gemm_pair_enabled() && n_tile == 512) n_tile = 256;   // its stage leaves room for 512 only in a pair
     const bool pair = n_tile == 512 && gemm_pair_enabled();   // two CTAs share each activation tile
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)w.cols, (cuuint64_t)m};
@@ -761,8 +855,26 @@ int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
             return kErrCuda;
         }
     }
-    int32_t rc = ty == kGgmlQ4K ? launch_gemm_ty<kGgmlQ4K>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy, n_tile, pair)
-                                : launch_gemm_ty<kGgmlQ6K>(st, w, map, ymap, wsmap, split, tma_store, m, y, ldy, n_tile, pair);
+    CUtensorMap q8maps[2];
+    memset(q8maps, 0, sizeof(q8maps));
+    if (ty == kGgmlQ8_0) {
+        const cuuint64_t qdims[2] = {(cuuint64_t)w.cols, (cuuint64_t)w.rows}, qstr[1] = {(cuuint64_t)w.cols};
+        const cuuint32_t qbox[2] = {256, (cuuint32_t)kGemmRows};
+        r = enc(&q8maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w.q8_qs, qdims, qstr, qbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const cuuint64_t ddims[2] = {(cuuint64_t)(w.cols / 32), (cuuint64_t)w.rows}, dstr[1] = {(cuuint64_t)(w.cols / 32) * 2};
+        const cuuint32_t dbox[2] = {8, (cuuint32_t)kGemmRows};
+        if (r == CUDA_SUCCESS)
+            r = enc(&q8maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w.q8_d, ddims, dstr, dbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            set_last_error("cuTensorMapEncodeTiled (Q8_0 planes) failed with code %d", (int)r);
+            return kErrCuda;
+        }
+    }
+    int32_t rc = ty == kGgmlQ4K   ? launch_gemm_ty<kGgmlQ4K>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy, n_tile, pair)
+                 : ty == kGgmlQ6K ? launch_gemm_ty<kGgmlQ6K>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy, n_tile, pair)
+                                  : launch_gemm_ty<kGgmlQ8_0>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy, n_tile, pair);
     if (rc != kOk || split.splits <= 1) return rc;
     gemm_finish_kernel<512><<<(unsigned)(cut_tiles * 512), 256, 0, st>>>(reinterpret_cast<const float*>(workspace), split, y, ldy,
                                                                         (int)w.rows, (int)m);

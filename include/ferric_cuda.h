@@ -207,12 +207,14 @@ int32_t ferric_cuda_matmul_q_noalloc(ferric_cuda_ctx *ctx, const ferric_qmatrix 
 
 /* Prefill product on the tensor cores: y[m, rows] (f32) = x . W^T with bf16 activations x[m, cols]
  * (raw bf16 bits, 16-byte aligned) and the weights dequantised to bf16, round to nearest even.
- * Replaces the reference's cooperative-matrix prefill kernel Tensor::matmul_q4_k_coop
- * (crates/ferric-tensor/src/dtype.rs:1818-1834, WGSL :2059-2096), which dequantises weight tiles
- * into workgroup memory and multiplies them with 8x8x8 subgroup-matrix ops; here a CTA (above
+ * Replaces the reference's cooperative-matrix prefill kernels Tensor::matmul_q4_k_coop
+ * (crates/ferric-tensor/src/dtype.rs:1818-1834, WGSL :2059-2096), matmul_q6_k_coop (:1199-1214) and
+ * matmul_q8_0_coop (:1316-1330), which dequantise weight tiles
+ * into workgroup memory and multiply them with 8x8x8 subgroup-matrix ops; here a CTA (above
  * 256 activation rows: a pair of CTAs) owns 128 (256) weight rows x up to 512 activation rows,
  * K advances in chunks of 64, and the multiply is tcgen05.mma with the f32 accumulator in tensor
- * memory.  Q4_K only (other types return FERRIC_UNSUPPORTED); any m >= 1 works but the kernel is
+ * memory.  Q4_K, Q6_K and Q8_0 (the last with columns in multiples of 256; anything else returns
+ * FERRIC_UNSUPPORTED, the reference's fall-back to the plain kernel); any m >= 1 works but the kernel is
  * meant for m >= 128.  Asynchronous on the context's stream.  Tiles of a partly filled last wave
  * are cut along K; their pieces meet in the context's scratch (up to 37 MB, grown on demand --
  * ferric_cuda_ctx_reserve_scratch beforehand when capturing).  FERRIC_CUDA_GEMM_PAIR=0 in the

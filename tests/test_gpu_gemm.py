@@ -1,4 +1,4 @@
-"""GPU parity of the tensor-core prefill product (Q4_K / Q6_K weights x bf16 activations).
+"""GPU parity of the tensor-core prefill product (Q4_K / Q6_K / Q8_0 weights x bf16 activations).
 
 The reference product for this configuration is: weights dequantised with the reference decoder and
 rounded to bf16 (nearest even), activations bf16, f32 accumulation.  The tensor core sums in a
@@ -43,9 +43,15 @@ def bf16_to_f64(bits):
     return (np.asarray(bits, dtype=np.uint32) << 16).view(np.float32).astype(np.float64)
 
 
+def blocks(ty, rng, n):
+    if ty == 8:
+        return synth.q8_0_blocks(rng, n // 32)
+    return (synth.q4k_blocks if ty == 12 else synth.q6k_blocks)(rng, n // 256)
+
+
 def make_case(rows, cols, m, seed, ty=12):
     rng = np.random.default_rng(seed)
-    raw = (synth.q4k_blocks if ty == 12 else synth.q6k_blocks)(rng, rows * cols // 256)
+    raw = blocks(ty, rng, rows * cols)
     x = torch.from_numpy(rng.standard_normal((m, cols), dtype=np.float32)).to(torch.bfloat16)
     xbits = x.view(torch.int16).numpy().view(np.uint16)
     return raw, x, xbits
@@ -92,7 +98,7 @@ SHAPES = [
 ]
 
 
-@pytest.mark.parametrize("ty", [12, 14])
+@pytest.mark.parametrize("ty", [12, 14, 8])
 @pytest.mark.parametrize("rows,cols,m", SHAPES)
 def test_small_shapes(F, ctx, rows, cols, m, ty):
     rel = check(F, ctx, rows, cols, m, seed=rows + cols + m + ty, ty=ty)
@@ -110,13 +116,13 @@ def test_prefill_down_q6k(F, ctx):
     check(F, ctx, 1024, 17408, 512, seed=5, oracle_rows=16, ty=14)
 
 
-@pytest.mark.parametrize("ty", [12, 14])
+@pytest.mark.parametrize("ty", [12, 14, 8])
 def test_dequant_stage_is_bit_exact(F, ctx, ty):
     """x = identity columns: y[i, r] is then exactly the bf16 weight W[r, i] -- the dequant-to-bf16 stage
     inside the kernel must match the oracle's bf16 dequantisation bit for bit."""
     rows, cols = 256, 256
     rng = np.random.default_rng(7)
-    raw = (synth.q4k_blocks if ty == 12 else synth.q6k_blocks)(rng, rows * cols // 256)
+    raw = blocks(ty, rng, rows * cols)
     qm = F.QMatrix.from_bytes(ctx, raw, ty, rows, cols)
     x = torch.eye(cols, dtype=torch.bfloat16, device="cuda")
     y = qm.matmul_bf16(x)
@@ -130,10 +136,12 @@ def test_dequant_stage_is_bit_exact(F, ctx, ty):
     qm.close()
 
 
-def test_rejects_other_types(F, ctx):
+def test_q8_0_needs_256_column_multiples(F, ctx):
+    """Q8_0 itself only needs columns in multiples of 32; the tensor-core product walks K in groups of 256 and declines
+    other widths (the caller then uses matmul_q)."""
     rng = np.random.default_rng(1)
-    raw = synth.q8_0_blocks(rng, 16 * 256 // 32)
-    qm = F.QMatrix.from_bytes(ctx, raw, 8, 16, 256)
+    raw = synth.q8_0_blocks(rng, 16 * 288 // 32)
+    qm = F.QMatrix.from_bytes(ctx, raw, 8, 16, 288)
     with pytest.raises(F.FerricError):
-        qm.matmul_bf16(torch.zeros(4, 256, dtype=torch.bfloat16, device="cuda"))
+        qm.matmul_bf16(torch.zeros(4, 288, dtype=torch.bfloat16, device="cuda"))
     qm.close()
