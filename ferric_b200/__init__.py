@@ -10,8 +10,9 @@ reference (dcharlot-physicalai-bmi/ferric)              here
 ``ferric_tensor::QMatrix::{block_bytes,from_bytes}``    ``QMatrix.block_bytes`` / ``QMatrix.from_bytes``
 ``Tensor::matmul_q`` / ``try_matmul_swiglu``            ``QMatrix.matmul`` / ``QMatrix.try_matmul_swiglu``
 ``Tensor::swiglu``                                      ``Context.swiglu``
+``ferric_gguf::parse`` / ``GgufFile::open``, ``qm``     ``Gguf.parse`` / ``Gguf(path)``, ``Gguf.qmatrix``
 =====================================================  ===========================================
 
 PyTorch is used only for device memory and streams; all arithmetic runs in ``libferric_cuda.so``.
 """
-from .ops import (Context, FerricError, QMatrix, TPGroup, GGML_Q4_K, GGML_Q6_K, GGML_Q8_0, type_size)  # noqa: F401
+from .ops import (Context, FerricError, Gguf, QMatrix, TPGroup, GGML_Q4_K, GGML_Q6_K, GGML_Q8_0, type_size)  # noqa: F401

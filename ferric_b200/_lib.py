@@ -24,6 +24,12 @@ class Caps(C.Structure):
 
 _P, _SZ, _U32, _I32 = C.c_void_p, C.c_size_t, C.c_uint32, C.c_int32
 
+
+class GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 4), ("ggml_type", C.c_uint32),
+                ("offset", C.c_uint64), ("n_elements", C.c_uint64), ("nbytes", C.c_uint64)]
+
+
 # name -> (restype, argtypes); every symbol include/ferric_cuda.h declares
 SIGNATURES = {
     "ferric_cuda_last_error": (C.c_char_p, []),
@@ -69,6 +75,26 @@ SIGNATURES = {
     "ferric_cuda_tp_add_rmsnorm_prepare": (_I32, [_P, _P, _I32, _P, _P, _P, C.c_float, _SZ, _P, _P]),
     "ferric_cuda_tp_status": (_I32, [_P, _P, C.POINTER(_I32)]),
     "ferric_cuda_tp_free": (None, [_P]),
+    "ferric_gguf_parse": (_I32, [_P, _SZ, C.POINTER(_P)]),
+    "ferric_gguf_open": (_I32, [C.c_char_p, C.POINTER(_P)]),
+    "ferric_gguf_free": (None, [_P]),
+    "ferric_gguf_n_tensors": (_SZ, [_P]),
+    "ferric_gguf_data_start": (_SZ, [_P]),
+    "ferric_gguf_n_meta": (_SZ, [_P]),
+    "ferric_gguf_tensor_at": (_I32, [_P, _SZ, C.POINTER(GgufTensor)]),
+    "ferric_gguf_tensor_by_name": (_I32, [_P, C.c_char_p, C.POINTER(GgufTensor)]),
+    "ferric_gguf_raw": (_I32, [_P, C.c_char_p, C.POINTER(_P), C.POINTER(_SZ)]),
+    "ferric_gguf_meta_key_at": (_I32, [_P, _SZ, _P, _SZ, C.POINTER(_SZ)]),
+    "ferric_gguf_meta_kind": (_I32, [_P, C.c_char_p, C.POINTER(_I32)]),
+    "ferric_gguf_meta_u64": (_I32, [_P, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "ferric_gguf_meta_i64": (_I32, [_P, C.c_char_p, C.POINTER(C.c_int64)]),
+    "ferric_gguf_meta_f64": (_I32, [_P, C.c_char_p, C.POINTER(C.c_double)]),
+    "ferric_gguf_meta_bool": (_I32, [_P, C.c_char_p, C.POINTER(_I32)]),
+    "ferric_gguf_meta_str": (_I32, [_P, C.c_char_p, _P, _SZ, C.POINTER(_SZ)]),
+    "ferric_gguf_meta_arr_len": (_I32, [_P, C.c_char_p, C.POINTER(_SZ)]),
+    "ferric_gguf_meta_arr_str": (_I32, [_P, C.c_char_p, _SZ, _P, _SZ, C.POINTER(_SZ)]),
+    "ferric_gguf_meta_arr_f64": (_I32, [_P, C.c_char_p, _SZ, C.POINTER(C.c_double)]),
+    "ferric_cuda_qmatrix_from_gguf": (_I32, [_P, _P, C.POINTER(C.c_char_p), _SZ, C.POINTER(_P)]),
     "ferric_cuda_dequant_f32": (_I32, [_P, _P, _P]),
     "ferric_cuda_dequant_bf16": (_I32, [_P, _P, _P]),
 }

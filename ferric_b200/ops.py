@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import numpy as np
@@ -399,3 +400,118 @@ class TPGroup:
             self._views = {}
             self._lib.ferric_cuda_tp_free(self._h)
             self._h = None
+
+
+class Gguf:
+    """A parsed GGUF file: ``ferric_gguf::parse`` / ``GgufFile::open`` (crates/ferric-gguf/src/lib.rs:105-132, :533-554).
+
+    ``Gguf(path)`` memory-maps a file; ``Gguf.parse(data)`` reads one already in memory (the bytes are kept alive by
+    this object).  ``metadata`` is a dict of Python values, ``tensors`` a list of dicts in file order."""
+
+    def __init__(self, path: Optional[str] = None, _data: Optional[np.ndarray] = None):
+        self._lib = _lib.load()
+        self._data = _data
+        h = C.c_void_p()
+        if _data is not None:
+            _check(self._lib.ferric_gguf_parse(_data.ctypes.data, _data.size, C.byref(h)), "gguf_parse")
+        else:
+            _check(self._lib.ferric_gguf_open(os.fsencode(path), C.byref(h)), "gguf_open")
+        self._h = h
+        self.tensors = [self._info_at(i) for i in range(self._lib.ferric_gguf_n_tensors(h))]
+        self.metadata = {k: self._meta(k) for k in self._keys()}
+
+    @classmethod
+    def parse(cls, data) -> "Gguf":
+        return cls(_data=np.ascontiguousarray(np.frombuffer(bytes(data), dtype=np.uint8) if not isinstance(data, np.ndarray) else data,
+                                              dtype=np.uint8))
+
+    @property
+    def data_start(self) -> int:
+        return self._lib.ferric_gguf_data_start(self._h)
+
+    @staticmethod
+    def _unpack(t: "_lib.GgufTensor") -> dict:
+        return {"name": t.name.decode("utf-8", "replace"), "dims": [int(t.dims[i]) for i in range(t.n_dims)],
+                "ggml_type": int(t.ggml_type), "offset": int(t.offset), "n_elements": int(t.n_elements), "nbytes": int(t.nbytes)}
+
+    def _info_at(self, i: int) -> dict:
+        t = _lib.GgufTensor()
+        _check(self._lib.ferric_gguf_tensor_at(self._h, i, C.byref(t)), "gguf_tensor_at")
+        return self._unpack(t)
+
+    def tensor(self, name: str) -> Optional[dict]:
+        """``Gguf::tensor`` (:444): None when the file has no such tensor."""
+        t = _lib.GgufTensor()
+        if self._lib.ferric_gguf_tensor_by_name(self._h, name.encode(), C.byref(t)) != _lib.OK:
+            return None
+        return self._unpack(t)
+
+    def raw(self, name: str) -> np.ndarray:
+        """``Gguf::raw`` (:447-453): the tensor's packed bytes, a read-only view into the file."""
+        p, n = C.c_void_p(), C.c_size_t()
+        _check(self._lib.ferric_gguf_raw(self._h, name.encode(), C.byref(p), C.byref(n)), "gguf_raw")
+        if n.value == 0:
+            return np.zeros(0, dtype=np.uint8)
+        arr = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(n.value,))
+        arr.flags.writeable = False
+        return arr
+
+    def _str(self, fn, *args) -> str:
+        n = C.c_size_t()
+        _check(fn(self._h, *args, None, 0, C.byref(n)), "gguf_meta")
+        buf = C.create_string_buffer(n.value + 1)
+        _check(fn(self._h, *args, buf, n.value + 1, C.byref(n)), "gguf_meta")
+        return buf.raw[:n.value].decode("utf-8", "replace")
+
+    def _keys(self):
+        return [self._str(self._lib.ferric_gguf_meta_key_at, i) for i in range(self._lib.ferric_gguf_n_meta(self._h))]
+
+    def _meta(self, key: str):
+        k, kind = key.encode(), C.c_int32()
+        _check(self._lib.ferric_gguf_meta_kind(self._h, k, C.byref(kind)), "gguf_meta_kind")
+        if kind.value == 0:
+            v = C.c_uint64()
+            _check(self._lib.ferric_gguf_meta_u64(self._h, k, C.byref(v)), "gguf_meta_u64")
+            return v.value
+        if kind.value == 1:
+            v = C.c_int64()
+            _check(self._lib.ferric_gguf_meta_i64(self._h, k, C.byref(v)), "gguf_meta_i64")
+            return v.value
+        if kind.value == 2:
+            v = C.c_double()
+            _check(self._lib.ferric_gguf_meta_f64(self._h, k, C.byref(v)), "gguf_meta_f64")
+            return v.value
+        if kind.value == 3:
+            v = C.c_int32()
+            _check(self._lib.ferric_gguf_meta_bool(self._h, k, C.byref(v)), "gguf_meta_bool")
+            return bool(v.value)
+        if kind.value == 4:
+            return self._str(self._lib.ferric_gguf_meta_str, k)
+        n = C.c_size_t()
+        _check(self._lib.ferric_gguf_meta_arr_len(self._h, k, C.byref(n)), "gguf_meta_arr_len")
+        out = []
+        for i in range(n.value):
+            v = C.c_double()
+            if self._lib.ferric_gguf_meta_arr_f64(self._h, k, i, C.byref(v)) == _lib.OK:
+                out.append(v.value)
+            else:
+                out.append(self._str(self._lib.ferric_gguf_meta_arr_str, k, i))
+        return out
+
+    def qmatrix(self, ctx: Context, *names: str) -> "QMatrix":
+        """``qm`` / ``qm_cat`` (crates/ferric-llama/src/qwen35.rs:366-402): one weight, or several stacked along rows."""
+        arr = (C.c_char_p * len(names))(*[n.encode() for n in names])
+        h = C.c_void_p()
+        _check(self._lib.ferric_cuda_qmatrix_from_gguf(ctx._h, self._h, arr, len(names), C.byref(h)), "qmatrix_from_gguf")
+        return QMatrix(ctx, h)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.ferric_gguf_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

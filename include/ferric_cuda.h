@@ -251,6 +251,63 @@ int32_t ferric_cuda_dequant_f32(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, 
  * (crates/ferric-tensor/src/dtype.rs:4159-4163): out[rows * cols] uint16 bf16 bits. */
 int32_t ferric_cuda_dequant_bf16(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, uint16_t *out_dev);
 
+/* ---- GGUF ingest --------------------------------------------------------------------------- */
+/* ferric_gguf::parse   crates/ferric-gguf/src/lib.rs:105-132 (bounds-safe cursor :59-103, stride guard
+ * :387-431): header, metadata and tensor table of a GGUF file held in memory.  `bytes` is borrowed:
+ * it must stay valid for the life of the handle.  Errors as the reference reports them: "not a GGUF
+ * file" (FERRIC_ERR_INVALID_ARG), "GGUF header truncated or malformed" and the two stride refusals
+ * (FERRIC_ERR_SHAPE). */
+typedef struct ferric_gguf ferric_gguf;
+int32_t ferric_gguf_parse(const uint8_t *bytes, size_t len, ferric_gguf **out);
+/* GgufFile::open   :533-554.  The file is memory-mapped read-only; tensor bytes are served from the
+ * mapping without a copy. */
+int32_t ferric_gguf_open(const char *path, ferric_gguf **out);
+void ferric_gguf_free(ferric_gguf *g);
+size_t ferric_gguf_n_tensors(const ferric_gguf *g);
+size_t ferric_gguf_data_start(const ferric_gguf *g); /* GgufFile::data_start :562 */
+size_t ferric_gguf_n_meta(const ferric_gguf *g);
+
+/* TensorInfo :40-45, plus the element count and the byte size by this library's type table
+ * (0 for a type it does not know).  `name` points into the handle. */
+typedef struct {
+    const char *name;
+    uint32_t n_dims;
+    uint64_t dims[4]; /* fastest-varying first: a listed [in, out] is a row-major [out, in] weight */
+    uint32_t ggml_type;
+    uint64_t offset; /* relative to ferric_gguf_data_start */
+    uint64_t n_elements;
+    uint64_t nbytes;
+} ferric_gguf_tensor;
+int32_t ferric_gguf_tensor_at(const ferric_gguf *g, size_t index, ferric_gguf_tensor *out);
+int32_t ferric_gguf_tensor_by_name(const ferric_gguf *g, const char *name, ferric_gguf_tensor *out); /* Gguf::tensor :444 */
+/* Gguf::raw / GgufFile::raw   :447-453, :566-573: the tensor's packed bytes exactly as stored --
+ * a pointer into the file, valid until ferric_gguf_free. */
+int32_t ferric_gguf_raw(const ferric_gguf *g, const char *name, const uint8_t **data, size_t *nbytes);
+
+/* Metadata (enum Meta :37).  A getter of the wrong kind fails with FERRIC_ERR_INVALID_ARG.
+ * String getters copy at most cap - 1 bytes, terminate, and report the full length in *len. */
+enum { FERRIC_GGUF_META_U = 0, FERRIC_GGUF_META_I = 1, FERRIC_GGUF_META_F = 2, FERRIC_GGUF_META_BOOL = 3,
+       FERRIC_GGUF_META_STR = 4, FERRIC_GGUF_META_ARR = 5 };
+int32_t ferric_gguf_meta_key_at(const ferric_gguf *g, size_t index, char *buf, size_t cap, size_t *len);
+int32_t ferric_gguf_meta_kind(const ferric_gguf *g, const char *key, int32_t *kind);
+int32_t ferric_gguf_meta_u64(const ferric_gguf *g, const char *key, uint64_t *out);
+int32_t ferric_gguf_meta_i64(const ferric_gguf *g, const char *key, int64_t *out);
+int32_t ferric_gguf_meta_f64(const ferric_gguf *g, const char *key, double *out);
+int32_t ferric_gguf_meta_bool(const ferric_gguf *g, const char *key, int32_t *out);
+int32_t ferric_gguf_meta_str(const ferric_gguf *g, const char *key, char *buf, size_t cap, size_t *len);
+int32_t ferric_gguf_meta_arr_len(const ferric_gguf *g, const char *key, size_t *n);
+int32_t ferric_gguf_meta_arr_str(const ferric_gguf *g, const char *key, size_t index, char *buf, size_t cap, size_t *len);
+int32_t ferric_gguf_meta_arr_f64(const ferric_gguf *g, const char *key, size_t index, double *out);
+
+/* The model loaders' qm / qm_cat   crates/ferric-llama/src/qwen35.rs:366-402: one device matrix from
+ * one named weight, or from several same-format weights of equal input width stacked along the
+ * output dimension (q|k|v, gate|up) -- rows = sum of dims[1], cols = dims[0].  Mixed formats, a
+ * differing input width or a missing tensor fail as in the reference; a format without a packed
+ * kernel here fails with FERRIC_ERR_UNSUPPORTED_TYPE (the reference dequantises to a dense matrix
+ * instead, which this library does not do). */
+int32_t ferric_cuda_qmatrix_from_gguf(ferric_cuda_ctx *ctx, const ferric_gguf *g, const char *const *names, size_t n_names,
+                                      ferric_qmatrix **out);
+
 /* ---- tensor-parallel exchange (one process per GPU) ------------------------------------- */
 /* The reference shards a QMatrix by rows and concatenates (crates/ferric-tensor/src/dtype.rs:893-908,
  * :935-944) and moves activations between devices through host buffers
