@@ -56,6 +56,7 @@ bool block_info(uint32_t ty, size_t* vals, size_t* bytes)
     switch (ty) {
     case kGgmlQ8_0: *vals = 32; *bytes = 34; return true;
     case kGgmlQ4K: *vals = 256; *bytes = 144; return true;
+    case kGgmlQ5K: *vals = 256; *bytes = 176; return true;
     case kGgmlQ6K: *vals = 256; *bytes = 210; return true;
     default: return false;
     }
@@ -255,6 +256,7 @@ int32_t ferric_gguf_type_size(uint32_t ty, size_t n, size_t* out_bytes)
     case FERRIC_GGML_BF16: *out_bytes = n * 2; return kOk;
     case FERRIC_GGML_Q8_0: *out_bytes = n / 32 * 34; return kOk;
     case FERRIC_GGML_Q4_K: *out_bytes = n / 256 * 144; return kOk;
+    case FERRIC_GGML_Q5_K: *out_bytes = n / 256 * 176; return kOk;
     case FERRIC_GGML_Q6_K: *out_bytes = n / 256 * 210; return kOk;
     default:
         set_last_error("unsupported ggml type %u", ty);

@@ -6,7 +6,7 @@
 
 namespace ferric {
 
-constexpr uint32_t kGgmlQ8_0 = 8, kGgmlQ4K = 12, kGgmlQ6K = 14;
+constexpr uint32_t kGgmlQ8_0 = 8, kGgmlQ4K = 12, kGgmlQ5K = 13, kGgmlQ6K = 14;
 
 // One packed weight matrix in device memory.  rows x cols logical; nblk = blocks per row
 // (256-weight super-blocks for Q4_K/Q6_K, 32-weight blocks for Q8_0).

@@ -335,7 +335,7 @@ static size_t padded_tiles(size_t m)
 size_t frag_bytes(uint32_t ty, const DeviceWeights& w, size_t m)
 {
     if (ty == kGgmlQ8_0 || m == 0) return 0;
-    size_t steps = ty == kGgmlQ4K ? kQ4KSteps : kQ6KSteps;
+    size_t steps = (ty == kGgmlQ4K || ty == kGgmlQ5K) ? kQ4KSteps : kQ6KSteps;   // Q5_K shares Q4_K's fragments
     return padded_tiles(m) * w.nblk * steps * 32 * sizeof(uint2);
 }
 
@@ -346,7 +346,7 @@ int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
     if (warps == 0) return kOk;
     dim3 grid((unsigned)((warps + kPrepWarps - 1) / kPrepWarps)), block(32 * kPrepWarps);
     uint2* f = reinterpret_cast<uint2*>(frag);
-    if (ty == kGgmlQ4K)
+    if (ty == kGgmlQ4K || ty == kGgmlQ5K)
         FERRIC_CUDA_TRY(launch_kernel(prep_kernel<(int)kGgmlQ4K>, grid, block, 0, st, tune.pdl, x, m, ldx, w.nblk, ntiles, f));
     else
         FERRIC_CUDA_TRY(launch_kernel(prep_kernel<(int)kGgmlQ6K>, grid, block, 0, st, tune.pdl, x, m, ldx, w.nblk, ntiles, f));
@@ -375,7 +375,7 @@ int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
         attr_dev = dev;
     }
     // the variant without an exchange carries none of the peer-pointer code
-    auto kernel = ty == kGgmlQ4K ? (peers.world > 0 ? norm_prep_kernel<(int)kGgmlQ4K, true> : norm_prep_kernel<(int)kGgmlQ4K, false>)
+    auto kernel = (ty == kGgmlQ4K || ty == kGgmlQ5K) ? (peers.world > 0 ? norm_prep_kernel<(int)kGgmlQ4K, true> : norm_prep_kernel<(int)kGgmlQ4K, false>)
                                  : (peers.world > 0 ? norm_prep_kernel<(int)kGgmlQ6K, true> : norm_prep_kernel<(int)kGgmlQ6K, false>);
     FERRIC_CUDA_TRY(launch_kernel(kernel, grid, block, smem, st, tune.pdl, a, b, weight, eps, m, w.cols, w.nblk, sum, norm, f, peers));
     return kOk;
@@ -388,7 +388,7 @@ int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
 // registers.
 // ------------------------------------------------------------------------------------------
 constexpr int kStagesQ4K = 4, kStagesQ6K = 3;
-constexpr int kSmemQ4K = 8 * kStagesQ4K * kQ4KUnit, kSmemQ6K = 8 * kStagesQ6K * kQ6KUnit;
+constexpr int kSmemQ4K = 8 * kStagesQ4K * kQ4KUnit, kSmemQ5K = 8 * kStagesQ4K * kQ5KUnit, kSmemQ6K = 8 * kStagesQ6K * kQ6KUnit;
 extern __shared__ __align__(16) uint8_t gemv_smem[];
 
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src)
@@ -482,16 +482,19 @@ __device__ __forceinline__ void pick_tile(int wk, int row_tiles, int ff_tiles, i
 // ------------------------------------------------------------------------------------------
 struct Q4KUnit {
     uint4 hg, hh, q[4];
+    uint4 q5;   // Q5_K only: the fifth bits of this lane's weights, bytes 0..7 row g, bytes 8..15 row g + 8
 };
 // Stage copy: the unit is mirrored byte for byte into the warp's ring slot.  Every lane copies its
 // own four 16-byte quant chunks; lanes 0..15 also copy one header row each.
+template <bool Q5 = false>
 __device__ __forceinline__ void q4k_issue(uint8_t* slot, const uint8_t* units, size_t unit, int lane)
 {
-    const uint8_t* src = units + unit * kQ4KUnit;
+    const uint8_t* src = units + unit * (Q5 ? kQ5KUnit : kQ4KUnit);
     if (lane < 16) cp_async_16(slot + 16 * lane, src + 16 * lane);
 #pragma unroll
-    for (int s = 0; s < 4; s++) cp_async_16(slot + 256 + 512 * s + 16 * lane, src + 256 + 512 * s + 16 * lane);
+    for (int s = 0; s < (Q5 ? 5 : 4); s++) cp_async_16(slot + 256 + 512 * s + 16 * lane, src + 256 + 512 * s + 16 * lane);
 }
+template <bool Q5 = false>
 __device__ __forceinline__ void q4k_read(Q4KUnit& u, const uint8_t* slot, int lane)
 {
     const uint4* p = reinterpret_cast<const uint4*>(slot);
@@ -500,6 +503,7 @@ __device__ __forceinline__ void q4k_read(Q4KUnit& u, const uint8_t* slot, int la
     u.hh = p[8 + g];
 #pragma unroll
     for (int s = 0; s < 4; s++) u.q[s] = p[16 + 32 * s + lane];
+    if (Q5) u.q5 = p[16 + 32 * 4 + lane];
 }
 
 // 6-bit scales / mins of one row's super-block as clean bytes: sc[0..3], sc[4..7], m[0..3], m[4..7]
@@ -518,12 +522,15 @@ __device__ __forceinline__ void q4k_row(const uint4& h, Q4KRow& r)
     r.m_hi = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
 }
 
-template <int NT, int EPI>
+// Q5 = true is the Q5_K kernel (crates/ferric-tensor/src/dtype.rs:1049-1071): the same product with 5-bit quants -- the
+// fifth bit of each weight is OR-ed into its byte before the integer MMA; header, scales and mins are Q4_K's.
+template <int NT, int EPI, bool Q5 = false>
 __global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
                 int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles)
 {
     __shared__ float red[8][NT * 4][32];
+    constexpr int kUnitBytes = Q5 ? kQ5KUnit : kQ4KUnit;
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, t = lane & 3;
     int rt, out_tile;
@@ -543,15 +550,15 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
     // weights never change, so their first pipeline stages are requested before the wait on the
     // preceding kernel; everything that depends on the activations comes after it
     const bool work = active && b0 < b1;
-    uint8_t* ring = gemv_smem + (size_t)warp * (kStagesQ4K * kQ4KUnit);
-    const uint8_t* wsrc = units + ((size_t)(work ? rt : 0) * nblk + (work ? b0 : 0)) * kQ4KUnit;   // next unit to copy
+    uint8_t* ring = gemv_smem + (size_t)warp * (kStagesQ4K * kUnitBytes);
+    const uint8_t* wsrc = units + ((size_t)(work ? rt : 0) * nblk + (work ? b0 : 0)) * kUnitBytes;   // next unit to copy
     int issued = b0, wstage = 0, rstage = 0;
     if (work) {
 #pragma unroll
         for (int i = 0; i < kStagesQ4K - 1; i++) {
             if (issued < b1) {
-                q4k_issue(ring + wstage * kQ4KUnit, wsrc, 0, lane);
-                wsrc += kQ4KUnit;
+                q4k_issue<Q5>(ring + wstage * kUnitBytes, wsrc, 0, lane);
+                wsrc += kUnitBytes;
                 issued++;
                 wstage = wstage + 1 == kStagesQ4K ? 0 : wstage + 1;
             }
@@ -574,8 +581,8 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 
         for (int b = b0; b < b1; b++) {
             if (issued < b1) {
-                q4k_issue(ring + wstage * kQ4KUnit, wsrc, 0, lane);
-                wsrc += kQ4KUnit;
+                q4k_issue<Q5>(ring + wstage * kUnitBytes, wsrc, 0, lane);
+                wsrc += kUnitBytes;
                 issued++;
                 wstage = wstage + 1 == kStagesQ4K ? 0 : wstage + 1;
             }
@@ -601,7 +608,7 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             cp_async_wait<kStagesQ4K - 1>();
             __syncwarp();
             Q4KUnit cur;
-            q4k_read(cur, ring + rstage * kQ4KUnit, lane);
+            q4k_read<Q5>(cur, ring + rstage * kUnitBytes, lane);
             rstage = rstage + 1 == kStagesQ4K ? 0 : rstage + 1;
             __syncwarp();  // every lane has its copy before a later stage copy may overwrite the slot
             Q4KRow rg, rh;
@@ -622,8 +629,14 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 #pragma unroll
                 for (int n = 0; n < 2; n++) {
                     const int s = 2 * p + n;
-                    const uint32_t a0 = (n ? (w0 >> 4) : w0) & 0x0f0f0f0fu, a2 = (n ? (w1 >> 4) : w1) & 0x0f0f0f0fu;
-                    const uint32_t a1 = (n ? (v0 >> 4) : v0) & 0x0f0f0f0fu, a3 = (n ? (v1 >> 4) : v1) & 0x0f0f0f0fu;
+                    uint32_t a0 = (n ? (w0 >> 4) : w0) & 0x0f0f0f0fu, a2 = (n ? (w1 >> 4) : w1) & 0x0f0f0f0fu;
+                    uint32_t a1 = (n ? (v0 >> 4) : v0) & 0x0f0f0f0fu, a3 = (n ? (v1 >> 4) : v1) & 0x0f0f0f0fu;
+                    if (Q5) {   // bit s of the lane's eight qh bytes per row -> bit 4 of the matching weight byte
+                        a0 |= ((cur.q5.x >> s) & 0x01010101u) << 4;
+                        a2 |= ((cur.q5.y >> s) & 0x01010101u) << 4;
+                        a1 |= ((cur.q5.z >> s) & 0x01010101u) << 4;
+                        a3 |= ((cur.q5.w >> s) & 0x01010101u) << 4;
+                    }
                     const int scg = (int)__byte_perm(s < 4 ? rg.sc_lo : rg.sc_hi, 0u, 0x4440u | (uint32_t)(s & 3));
                     const int sch = (int)__byte_perm(s < 4 ? rh.sc_lo : rh.sc_hi, 0u, 0x4440u | (uint32_t)(s & 3));
 #pragma unroll
@@ -902,6 +915,14 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
             attr_dev_q4 = dev;
         }
         launch_kernel(gemv_q4k_kernel<NT, EPI>, grid, dim3(256), kSmemQ4K, st, pdl, w.units, frag, y, (int)w.rows,
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles);
+    } else if (ty == kGgmlQ5K) {
+        static thread_local int attr_dev_q5 = -1;
+        if (attr_dev_q5 != dev) {
+            cudaFuncSetAttribute(gemv_q4k_kernel<NT, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ5K);
+            attr_dev_q5 = dev;
+        }
+        launch_kernel(gemv_q4k_kernel<NT, EPI, true>, grid, dim3(256), kSmemQ5K, st, pdl, w.units, frag, y, (int)w.rows,
                       (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles);
     } else {
         if (attr_dev_q6 != dev) {

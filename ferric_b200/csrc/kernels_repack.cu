@@ -31,6 +31,19 @@ __global__ void repack_q4k_kernel(const uint8_t* __restrict__ src, uint8_t* __re
     }
 }
 
+__global__ void repack_q5k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, size_t nrows,
+                                  size_t nblk, size_t src_nblk, size_t row0, size_t blk0)
+{
+    // 22 pieces of 8 bytes per block (header 2, fifth bits 4, nibbles 16); every aligned 8-byte run stays contiguous
+    size_t total = nrows * nblk * 22;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        size_t c = i % 22, rb = i / 22, b = rb % nblk, r = rb / nblk;
+        const uint8_t* s = src + ((row0 + r) * src_nblk + blk0 + b) * kQ5KBlock + 8 * c;
+        uint8_t* d = dst + ((r >> 4) * nblk + b) * kQ5KUnit + q5k_unit_offset((int)(r & 15), (int)(8 * c));
+        for (int j = 0; j < 8; j++) d[j] = s[j];
+    }
+}
+
 __global__ void repack_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, size_t nrows,
                                   size_t nblk, size_t src_nblk, size_t row0, size_t blk0)
 {
@@ -88,6 +101,8 @@ int32_t launch_repack(cudaStream_t st, uint32_t ty, const uint8_t* src, DeviceWe
         bool aligned = (reinterpret_cast<uintptr_t>(src) & 7) == 0;
         repack_q4k_kernel<<<grid_for(nrows * nblk * 18, 256), 256, 0, st>>>(src, w.units, nrows, nblk, src_nblk,
                                                                             row0, blk0, aligned);
+    } else if (ty == kGgmlQ5K) {
+        repack_q5k_kernel<<<grid_for(nrows * nblk * 22, 256), 256, 0, st>>>(src, w.units, nrows, nblk, src_nblk, row0, blk0);
     } else if (ty == kGgmlQ6K) {
         repack_q6k_kernel<<<grid_for(nrows * nblk * 49, 256), 256, 0, st>>>(src, w.units, nrows, nblk, src_nblk,
                                                                              row0, blk0);
@@ -114,6 +129,14 @@ struct UnitQ4K {
     __device__ uint8_t at(size_t row, size_t blk, int byte) const
     {
         return p[((row >> 4) * nblk + blk) * kQ4KUnit + q4k_unit_offset((int)(row & 15), byte)];
+    }
+};
+struct UnitQ5K {
+    const uint8_t* p;
+    size_t nblk, block;
+    __device__ uint8_t at(size_t row, size_t blk, int byte) const
+    {
+        return p[((row >> 4) * nblk + blk) * kQ5KUnit + q5k_unit_offset((int)(row & 15), byte)];
     }
 };
 struct UnitQ6K {
@@ -171,6 +194,30 @@ __device__ float deq_elem_q4k(const Acc& a, size_t row, size_t col)
     return __fsub_rn(__fmul_rn(d1, (float)q), mm);
 }
 
+// crates/ferric-gguf/src/lib.rs:690-716
+template <class Acc>
+__device__ float deq_elem_q5k(const Acc& a, size_t row, size_t col)
+{
+    size_t blk = col >> 8;
+    int w = (int)(col & 255), grp = w >> 6, n = (w >> 5) & 1, l = w & 31;
+    float d = f16_bits_to_f32(a.at(row, blk, 0), a.at(row, blk, 1));
+    float dmin = f16_bits_to_f32(a.at(row, blk, 2), a.at(row, blk, 3));
+    int j = 2 * grp + n;
+    uint32_t sc, mn;
+    if (j < 4) {
+        sc = a.at(row, blk, 4 + j) & 63;
+        mn = a.at(row, blk, 4 + j + 4) & 63;
+    } else {
+        uint32_t hi4 = a.at(row, blk, 4 + j + 4);
+        sc = (hi4 & 0x0F) | ((a.at(row, blk, 4 + j - 4) >> 6) << 4);
+        mn = (hi4 >> 4) | ((a.at(row, blk, 4 + j) >> 6) << 4);
+    }
+    uint32_t qb = a.at(row, blk, 48 + 32 * grp + l);
+    uint32_t q = (n ? (qb >> 4) : (qb & 0x0F)) + (((a.at(row, blk, 16 + l) >> j) & 1u) ? 16u : 0u);
+    float d1 = __fmul_rn(d, (float)sc), mm = __fmul_rn(dmin, (float)mn);
+    return __fsub_rn(__fmul_rn(d1, (float)q), mm);
+}
+
 template <class Acc>
 __device__ float deq_elem_q6k(const Acc& a, size_t row, size_t col)
 {
@@ -200,8 +247,10 @@ __global__ void dequant_kernel(Acc a, size_t rows, size_t cols, void* __restrict
     size_t total = rows * cols;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t row = i / cols, col = i % cols;
-        float v = TY == kGgmlQ4K ? deq_elem_q4k(a, row, col)
-                : TY == kGgmlQ6K ? deq_elem_q6k(a, row, col) : deq_elem_q8_0(a, row, col);
+        float v = TY == kGgmlQ4K   ? deq_elem_q4k(a, row, col)
+                  : TY == kGgmlQ5K ? deq_elem_q5k(a, row, col)
+                  : TY == kGgmlQ6K ? deq_elem_q6k(a, row, col)
+                                   : deq_elem_q8_0(a, row, col);
         if (BF16) reinterpret_cast<uint16_t*>(out)[i] = bf16_rne_bits(v);
         else reinterpret_cast<float*>(out)[i] = v;
     }
@@ -219,6 +268,7 @@ int32_t launch_dequant_weights(cudaStream_t st, uint32_t ty, const DeviceWeights
 {
     if (w.rows == 0 || w.cols == 0) return kOk;
     if (ty == kGgmlQ4K) launch_deq<kGgmlQ4K>(st, UnitQ4K{w.units, w.nblk, 0}, w.rows, w.cols, out, bf16);
+    else if (ty == kGgmlQ5K) launch_deq<kGgmlQ5K>(st, UnitQ5K{w.units, w.nblk, 0}, w.rows, w.cols, out, bf16);
     else if (ty == kGgmlQ6K) launch_deq<kGgmlQ6K>(st, UnitQ6K{w.units, w.nblk, 0}, w.rows, w.cols, out, bf16);
     else launch_deq<kGgmlQ8_0>(st, PlanesQ8{w.q8_qs, w.q8_d, w.nblk, 0}, w.rows, w.cols, out, bf16);
     FERRIC_CUDA_TRY(cudaGetLastError());
@@ -230,6 +280,7 @@ int32_t launch_dequant_raw(cudaStream_t st, uint32_t ty, const uint8_t* raw, siz
 {
     if (n == 0) return kOk;
     if (ty == kGgmlQ4K) launch_deq<kGgmlQ4K>(st, RawBytes{raw, n / 256, kQ4KBlock}, 1, n / 256 * 256, out, bf16);
+    else if (ty == kGgmlQ5K) launch_deq<kGgmlQ5K>(st, RawBytes{raw, n / 256, kQ5KBlock}, 1, n / 256 * 256, out, bf16);
     else if (ty == kGgmlQ6K) launch_deq<kGgmlQ6K>(st, RawBytes{raw, n / 256, kQ6KBlock}, 1, n / 256 * 256, out, bf16);
     else launch_deq<kGgmlQ8_0>(st, RawBytes{raw, n / 32, kQ8Block}, 1, n / 32 * 32, out, bf16);
     FERRIC_CUDA_TRY(cudaGetLastError());

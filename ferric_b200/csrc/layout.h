@@ -53,6 +53,26 @@ FERRIC_HD uint32_t q4k_unit_offset(int r, int byte)
 // b1 bytes 0..3) of sub-block step s (0..7).
 FERRIC_HD int q4k_frag_weight(int s, int t, int i) { return 32 * s + 8 * t + i; }
 
+// ---------------------------------------------------------------- Q5_K (ggml type 13)
+// Raw block (crates/ferric-gguf/src/lib.rs:690-716): [f16 d][f16 dmin][scales 12][qh 32][qs 128] = 176 B: Q4_K with a
+// fifth bit -- bit j of qh[l] belongs to value l of sub-block j.  Unit (2816 B): the Q4_K unit of the header and the
+// nibbles, followed by one 512-byte segment of fifth bits in which lane 4*(row&7) + t owns 16 bytes: qh[8t, 8t+8) of
+// row (row&7), then qh[8t, 8t+8) of row (row&7) + 8 -- the bits of exactly the eight weights per sub-block whose
+// nibbles the lane holds.
+constexpr int kQ5KBlock = 176;
+constexpr int kQ5KUnit = 16 * kQ5KBlock;  // 2816
+constexpr int kQ5KOffQh = kQ4KUnit;       // 2304
+
+FERRIC_HD uint32_t q5k_unit_offset(int r, int byte)
+{
+    if (byte < 16) return (uint32_t)(r * 16 + byte);
+    if (byte < 48) {
+        int j = byte - 16, g = r & 7, hi = r >> 3;
+        return (uint32_t)(kQ5KOffQh + 16 * (4 * g + (j >> 3)) + 8 * hi + (j & 7));
+    }
+    return q4k_unit_offset(r, byte - 32);   // the 128 quant bytes sit where Q4_K has them
+}
+
 // ---------------------------------------------------------------- Q6_K (ggml type 14)
 // Raw block (crates/ferric-gguf/src/lib.rs:721-746): [ql 128][qh 64][i8 scales 16][f16 d] = 210 B.
 // Sub-block sb = 8h + 2k + is (16 weights: 128h + 32k + 16is + j) takes its low 4 bits from

@@ -12,7 +12,8 @@ from __future__ import annotations
 import numpy as np
 
 GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 8, 12, 14
-BLOCK = {GGML_Q8_0: (32, 34), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210)}
+GGML_Q5_K = 13
+BLOCK = {GGML_Q8_0: (32, 34), GGML_Q4_K: (256, 144), GGML_Q5_K: (256, 176), GGML_Q6_K: (256, 210)}
 
 
 def _f16_bytes(rng: np.random.Generator, n: int, lo: float = 1e-4, hi: float = 2e-3) -> np.ndarray:
@@ -42,6 +43,16 @@ def q4k_blocks(rng: np.random.Generator, nblk: int) -> np.ndarray:
     return out
 
 
+def q5k_blocks(rng: np.random.Generator, nblk: int) -> np.ndarray:
+    """Q5_K: the Q4_K header and nibbles plus 32 bytes whose bit j is the fifth bit of value l of sub-block j."""
+    out = np.empty((nblk, 176), dtype=np.uint8)
+    q4 = q4k_blocks(rng, nblk)
+    out[:, 0:16] = q4[:, 0:16]
+    out[:, 16:48] = rng.integers(0, 256, size=(nblk, 32), dtype=np.uint8)
+    out[:, 48:176] = q4[:, 16:144]
+    return out
+
+
 def q6k_blocks(rng: np.random.Generator, nblk: int) -> np.ndarray:
     out = np.empty((nblk, 210), dtype=np.uint8)
     lo = rng.integers(0, 16, size=(nblk, 2, 128), dtype=np.uint8)
@@ -66,7 +77,7 @@ def matrix(ggml_type: int, rows: int, cols: int, seed: int) -> np.ndarray:
     assert cols % vals == 0
     rng = np.random.default_rng(seed)
     nblk = rows * (cols // vals)
-    gen = {GGML_Q4_K: q4k_blocks, GGML_Q6_K: q6k_blocks, GGML_Q8_0: q8_0_blocks}[ggml_type]
+    gen = {GGML_Q4_K: q4k_blocks, GGML_Q5_K: q5k_blocks, GGML_Q6_K: q6k_blocks, GGML_Q8_0: q8_0_blocks}[ggml_type]
     return gen(rng, nblk).reshape(-1)
 
 
@@ -89,8 +100,8 @@ def matrix_on_device(ggml_type: int, rows: int, cols: int, seed: int, device):
         v = torch.empty(n, dtype=torch.float32, device=device).uniform_(1e-4, 2e-3, generator=g)
         return v.to(torch.float16).view(torch.uint8).reshape(n, 2)
 
-    if ggml_type == GGML_Q4_K:
-        # uniform bytes already give uniform 6-bit scales/mins and uniform nibbles
+    if ggml_type in (GGML_Q4_K, GGML_Q5_K):
+        # uniform bytes already give uniform 6-bit scales/mins, nibbles and fifth bits
         out[:, 0:2] = f16_field(nblk)
         out[:, 2:4] = f16_field(nblk)
     elif ggml_type == GGML_Q6_K:

@@ -43,6 +43,7 @@ extern "C" {
 #define FERRIC_GGML_F16 1u
 #define FERRIC_GGML_Q8_0 8u
 #define FERRIC_GGML_Q4_K 12u
+#define FERRIC_GGML_Q5_K 13u
 #define FERRIC_GGML_Q6_K 14u
 #define FERRIC_GGML_BF16 30u
 

@@ -14,8 +14,9 @@
  * Parity status: PINNED by the reference's own known-answer tests, restated in tests/ and
  * tests/golden/ (f16 specials, the hand-built Q4_K block, the Q8_0 quantise round trip, bf16 RNE,
  * packed-vs-dequant agreement, thread/span invariance).  The reference holds no golden values for
- * Q6_K; its layout here follows the reference decoder line by line and is cross-checked against an
- * independently written numpy decoder.
+ * Q6_K or Q5_K; their layouts here follow the reference decoders line by line and are cross-checked
+ * bit for bit against an independently written numpy decoder (for those two formats that
+ * cross-check, not a reference vector, is the pin).
  *
  * Each function names the reference file:line it follows (paths relative to the reference root).
  */
@@ -31,7 +32,7 @@
 #define FO_ERR_SHAPE -2  /* a reference assert!/panic: cols not a block multiple, wrong byte length */
 #define FO_ERR_ARG -3
 
-enum { GGML_F32 = 0, GGML_F16 = 1, GGML_Q8_0 = 8, GGML_Q4_K = 12, GGML_Q6_K = 14, GGML_BF16 = 30 };
+enum { GGML_F32 = 0, GGML_F16 = 1, GGML_Q8_0 = 8, GGML_Q4_K = 12, GGML_Q5_K = 13, GGML_Q6_K = 14, GGML_BF16 = 30 };
 
 /* ---------------------------------------------------------------------------------------------
  * IEEE binary16 -> f32, including subnormals, inf and nan.
@@ -122,6 +123,7 @@ int fo_type_size(uint32_t ty, size_t n, size_t *out)
     case GGML_BF16: *out = n * 2; return FO_OK;
     case GGML_Q8_0: *out = n / 32 * 34; return FO_OK;
     case GGML_Q4_K: *out = n / 256 * 144; return FO_OK;
+    case GGML_Q5_K: *out = n / 256 * 176; return FO_OK;
     case GGML_Q6_K: *out = n / 256 * 210; return FO_OK;
     default: return FO_ERR_TYPE;
     }
@@ -134,6 +136,7 @@ int fo_block_bytes(uint32_t ty, size_t *vals, size_t *bytes)
     switch (ty) {
     case GGML_Q8_0: *vals = 32; *bytes = 34; return FO_OK;
     case GGML_Q4_K: *vals = 256; *bytes = 144; return FO_OK;
+    case GGML_Q5_K: *vals = 256; *bytes = 176; return FO_OK;
     case GGML_Q6_K: *vals = 256; *bytes = 210; return FO_OK;
     default: return FO_ERR_TYPE;
     }
@@ -219,6 +222,39 @@ static void deq_q4_k(const uint8_t *raw, size_t n, float *out)
     }
 }
 
+/* Q5_K: [f16 d][f16 dmin][scales[12]][qh[32]][qs[128]] = 176 bytes; Q4_K with a fifth bit: group jg takes bit 2*jg
+ * of qh[l] for its low-nibble values and bit 2*jg+1 for its high-nibble values, worth 16.
+ * crates/ferric-gguf/src/lib.rs:690-716. */
+static void deq_q5_k(const uint8_t *raw, size_t n, float *out)
+{
+    size_t nb = n / 256;
+    for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = raw + b * 176;
+        float d = fo_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+        float dmin = fo_f16_to_f32((uint16_t)(blk[2] | (blk[3] << 8)));
+        const uint8_t *scales = blk + 4, *qh = blk + 16, *qs = blk + 48;
+        float *y = out + b * 256;
+        int is = 0;
+        for (int jg = 0; jg < 4; jg++) {
+            uint8_t sc1, m1, sc2, m2;
+            q4k_sc_min(scales, is, &sc1, &m1);
+            q4k_sc_min(scales, is + 1, &sc2, &m2);
+            float d1 = d * (float)sc1, mm1 = dmin * (float)m1;
+            float d2 = d * (float)sc2, mm2 = dmin * (float)m2;
+            uint8_t b1 = (uint8_t)(1u << (2 * jg)), b2 = (uint8_t)(1u << (2 * jg + 1));
+            for (int l = 0; l < 32; l++) {
+                float p = d1 * (float)((qs[l] & 0x0F) + ((qh[l] & b1) ? 16 : 0));
+                y[l] = p - mm1;
+            }
+            for (int l = 0; l < 32; l++) {
+                float p = d2 * (float)((qs[l] >> 4) + ((qh[l] & b2) ? 16 : 0));
+                y[l + 32] = p - mm2;
+            }
+            y += 64; qs += 32; is += 2;
+        }
+    }
+}
+
 /* Dispatch on ggml type id; unknown type is an error, never a silent zero.
  * crates/ferric-gguf/src/lib.rs:497-520.  `raw_len` is checked against type_size so a short
  * buffer is reported instead of read past (the reference slices and would panic). */
@@ -237,6 +273,7 @@ int fo_deq_raw(const uint8_t *raw, size_t raw_len, size_t n, uint32_t ty, float 
         return FO_OK;
     case GGML_Q8_0: deq_q8_0(raw, n, out); return FO_OK;
     case GGML_Q4_K: deq_q4_k(raw, n, out); return FO_OK;
+    case GGML_Q5_K: deq_q5_k(raw, n, out); return FO_OK;
     case GGML_Q6_K: deq_q6_k(raw, n, out); return FO_OK;
     default: return FO_ERR_TYPE;
     }
@@ -291,6 +328,7 @@ static float row_dequant_dot(const float *x, const uint8_t *rowbytes, size_t col
     switch (ty) {
     case GGML_Q8_0: deq_q8_0(rowbytes, cols, scratch); break;
     case GGML_Q4_K: deq_q4_k(rowbytes, cols, scratch); break;
+    case GGML_Q5_K: deq_q5_k(rowbytes, cols, scratch); break;
     default: deq_q6_k(rowbytes, cols, scratch); break;
     }
     float acc = 0.0f;
@@ -305,6 +343,7 @@ static float row_dequant_dot_bf16(const uint16_t *xb, const uint8_t *rowbytes, s
     switch (ty) {
     case GGML_Q8_0: deq_q8_0(rowbytes, cols, scratch); break;
     case GGML_Q4_K: deq_q4_k(rowbytes, cols, scratch); break;
+    case GGML_Q5_K: deq_q5_k(rowbytes, cols, scratch); break;
     default: deq_q6_k(rowbytes, cols, scratch); break;
     }
     float acc = 0.0f;
@@ -496,7 +535,8 @@ static void *span_worker(void *arg)
                 v = row_dequant_dot_bf16((const uint16_t *)j->x + t * j->cols, rb, j->cols, j->ty, scratch);
             } else {
                 const float *x = (const float *)j->x + t * j->cols;
-                if (j->mode == FO_MODE_DEQUANT_DOT) v = row_dequant_dot(x, rb, j->cols, j->ty, scratch);
+                /* Q5_K has neither a CPU kernel nor a separately restated shader order: every mode is the reference product */
+                if (j->mode == FO_MODE_DEQUANT_DOT || j->ty == GGML_Q5_K) v = row_dequant_dot(x, rb, j->cols, j->ty, scratch);
                 else if (j->mode == FO_MODE_FUSED)
                     v = j->ty == GGML_Q8_0 ? row_fused_q8_0(x, rb, j->cols)
                       : j->ty == GGML_Q4_K ? row_fused_q4_k(x, rb, j->cols) : row_fused_q6_k(x, rb, j->cols);

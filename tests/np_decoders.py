@@ -79,3 +79,23 @@ def bf16_rne(x: np.ndarray) -> np.ndarray:
     b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
     r = (b + 0x7FFF + ((b >> 16) & 1)) & 0xFFFFFFFF
     return (r >> 16).astype(np.uint16)
+
+
+def deq_q5_k(raw: np.ndarray, n: int) -> np.ndarray:
+    """Q5_K: 176-byte blocks [d][dmin][scales 12][qh 32][qs 128]; Q4_K with a fifth bit from qh (bit j of qh[l]
+    belongs to value l of sub-block j)."""
+    blk = raw[: n // 256 * 176].reshape(-1, 176)
+    nb = blk.shape[0]
+    d, dmin = _f16(blk[:, 0:2]), _f16(blk[:, 2:4])
+    sc, mn = q4k_scales_mins(blk[:, 4:16])
+    qh = blk[:, 16:48]                                                      # [nb, 32]
+    qs = blk[:, 48:].reshape(nb, 4, 32)
+    lo4 = np.stack([qs & 0x0F, qs >> 4], axis=2).reshape(nb, 8, 32)       # sub-blocks 0..7
+    bit = ((qh[:, None, :] >> np.arange(8, dtype=np.uint8)[None, :, None]) & 1).astype(np.uint8)
+    q = (lo4 + 16 * bit).astype(np.float32)
+    d1 = (d[:, None] * sc.astype(np.float32)).astype(np.float32)
+    mm = (dmin[:, None] * mn.astype(np.float32)).astype(np.float32)
+    val = ((d1[:, :, None] * q).astype(np.float32) - mm[:, :, None]).astype(np.float32)
+    out = np.zeros(n, dtype=np.float32)
+    out[: nb * 256] = val.reshape(-1)
+    return out

@@ -32,10 +32,12 @@ def test_qm_and_qm_cat(F, ctx):
     v = synth.q4k_blocks(rng, 32 * hidden // 256)
     down = synth.q6k_blocks(rng, hidden * 768 // 256)
     head = synth.q8_0_blocks(rng, 40 * hidden // 32)
+    gate = synth.q5k_blocks(rng, 64 * hidden // 256)
     data = W.build([("general.architecture", W.STR, "qwen3")],
                    [("blk.0.attn_q.weight", [hidden, 96], 12, q.tobytes()), ("blk.0.attn_k.weight", [hidden, 32], 12, k.tobytes()),
                     ("blk.0.attn_v.weight", [hidden, 32], 12, v.tobytes()), ("blk.0.ffn_down.weight", [768, hidden], 14, down.tobytes()),
-                    ("output.weight", [hidden, 40], 8, head.tobytes()), ("blk.0.attn_norm.weight", [hidden], 0, np.ones(hidden, np.float32).tobytes())])
+                    ("output.weight", [hidden, 40], 8, head.tobytes()), ("blk.0.ffn_gate.weight", [hidden, 64], 13, gate.tobytes()),
+                    ("blk.0.attn_norm.weight", [hidden], 0, np.ones(hidden, np.float32).tobytes())])
     g = F.Gguf.parse(data)
     x = synth.activations(3, hidden, seed=1)
     xd = torch.from_numpy(x).cuda()
@@ -54,6 +56,13 @@ def test_qm_and_qm_cat(F, ctx):
     ref = O.matmul_q(down, 14, hidden, 768, xf)
     got = d.matmul(torch.from_numpy(xf).cuda()).cpu().numpy()
     assert (np.abs(got - ref) <= 1e-4 + 1e-3 * np.abs(ref)).all()
+
+    g5 = g.qmatrix(ctx, "blk.0.ffn_gate.weight")                                                  # Q5_K (some Q4_K_M files mix it in)
+    assert (g5.rows(), g5.cols(), g5.ggml_type()) == (64, hidden, 13)
+    ref = O.matmul_q(gate.reshape(-1), 13, 64, hidden, x)
+    got = g5.matmul(xd).cpu().numpy()
+    assert (np.abs(got - ref) <= 1e-4 + 1e-3 * np.abs(ref)).all()
+    g5.close()
 
     h = g.qmatrix(ctx, "output.weight")
     assert (h.rows(), h.cols(), h.ggml_type()) == (40, hidden, 8)

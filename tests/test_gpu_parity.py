@@ -112,7 +112,7 @@ def test_deq_raw_partial_block_and_errors(F, ctx):
     assert e.value.status == 3
 
 
-@pytest.mark.parametrize("ty", [12, 14, 8])
+@pytest.mark.parametrize("ty", [12, 13, 14, 8])
 @pytest.mark.parametrize("rows,cols", [(1, 256), (16, 512), (17, 768), (100, 1024), (515, 2048)])
 def test_loaded_matrix_dequantises_bit_exactly(F, ctx, ty, rows, cols):
     raw = synth.matrix(ty, rows, cols, seed=rows * 7 + cols + ty)
@@ -129,7 +129,7 @@ def test_loaded_matrix_dequantises_bit_exactly(F, ctx, ty, rows, cols):
 
 def test_fully_random_bytes_dequantise_bit_exactly(F, ctx):
     rng = np.random.default_rng(77)
-    for ty in (12, 14, 8):
+    for ty in (12, 13, 14, 8):
         vals, bb = synth.BLOCK[ty]
         rows, cols = 48, 4 * 256
         raw = rng.integers(0, 256, size=rows * (cols // vals) * bb, dtype=np.uint8)
@@ -210,7 +210,7 @@ def test_config2_output_head_rows_sampled(F, ctx):
     qm.close()
 
 
-@pytest.mark.parametrize("ty", [12, 14, 8])
+@pytest.mark.parametrize("ty", [12, 13, 14, 8])
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 9, 16, 17, 33, 64])
 def test_batch_sizes(F, ctx, ty, m):
     rows, cols = 200, 1024
@@ -221,7 +221,7 @@ def test_batch_sizes(F, ctx, ty, m):
     assert_close(got, ref, f"ty{ty} m{m}", exact_product(raw, ty, rows, cols, x))
 
 
-@pytest.mark.parametrize("ty", [12, 14, 8])
+@pytest.mark.parametrize("ty", [12, 13, 14, 8])
 def test_edge_shapes_and_ranges(F, ctx, ty):
     vals = synth.BLOCK[ty][0]
     # ragged row counts around the 16-row tile, one block of K, and K deeper than one warp's share
@@ -309,6 +309,25 @@ def test_fused_gate_up_swiglu(F, ctx, ty, t):
     qm.close()
 
 
+@pytest.mark.parametrize("t", [1, 3, 8])
+def test_fused_gate_up_swiglu_q5k(F, ctx, t):
+    """Q5_K gate|up takes the Q4_K kernel with the fifth bit OR-ed in; same bar as the reference's fused-vs-unfused
+    check (crates/ferric-tensor/examples/ffn_fuse.rs:100-108)."""
+    n_ff, n_embd = 1024, 1536
+    raw = synth.matrix(13, 2 * n_ff, n_embd, seed=13)
+    h = synth.activations(t, n_embd, seed=t)
+    qm = F.QMatrix.from_bytes(ctx, raw, 13, 2 * n_ff, n_embd)
+    hx = torch.from_numpy(h).cuda()
+    fused = qm.try_matmul_swiglu(hx)
+    assert fused is not None and tuple(fused.shape) == (t, n_ff)
+    unfused = ctx.swiglu(qm.matmul(hx), n_ff).cpu().numpy()
+    fused = fused.cpu().numpy()
+    assert np.abs(fused - unfused).max() / max(np.abs(unfused).max(), 1e-3) < 1e-5
+    ref = O.swiglu(O.matmul_q(raw, 13, 2 * n_ff, n_embd, h, threads=NCPU), n_ff)
+    assert np.abs(fused - ref).max() / max(np.abs(ref).max(), 1e-3) < 1e-4
+    qm.close()
+
+
 def test_swiglu_declines_what_the_reference_declines(F, ctx):
     raw = synth.matrix(8, 64, 256, seed=1)
     qm = F.QMatrix.from_bytes(ctx, raw, 8, 64, 256)
@@ -336,7 +355,7 @@ def test_add_rmsnorm_matches_reference_kernel(F, ctx, rows, d):
     assert np.abs(n2.cpu().numpy() - O.add_rmsnorm(a, None, None, 1e-6)[1]).max() <= 1e-5 * np.abs(n_ref).max()
 
 
-@pytest.mark.parametrize("ty", [12, 14])
+@pytest.mark.parametrize("ty", [12, 13, 14])
 @pytest.mark.parametrize("m", [1, 2, 5])
 def test_fused_add_rmsnorm_prepare(F, ctx, ty, m):
     rows, d = 96, 1536
@@ -398,7 +417,7 @@ def test_decode_stack_step_matches_layerwise_oracle(F, ctx):
 
 
 # ------------------------------------------------------------------------------ shards
-@pytest.mark.parametrize("ty", [12, 14, 8])
+@pytest.mark.parametrize("ty", [12, 13, 14, 8])
 def test_row_and_k_shards_compose(F, ctx, ty):
     rows, cols = 96, 2048
     vals, bb = synth.BLOCK[ty]

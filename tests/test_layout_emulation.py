@@ -24,7 +24,7 @@ def shim():
     out = os.path.join(tempfile.mkdtemp(prefix="ferric_shim_"), "layout_shim.so")
     subprocess.check_call(["g++", "-O1", "-shared", "-fPIC", "-o", out, os.path.join(HERE, "cpu", "layout_shim.cpp")])
     lib = C.CDLL(out)
-    for name in ("shim_q4k_unit_offset", "shim_q6k_unit_offset"):
+    for name in ("shim_q4k_unit_offset", "shim_q5k_unit_offset", "shim_q6k_unit_offset"):
         getattr(lib, name).restype = C.c_uint32
     return lib
 
@@ -274,3 +274,25 @@ def test_fragment_maps_cover_each_weight_once(shim):
             for i in range(4):
                 seen[shim.shim_q6k_frag_weight(sb, t, i)] += 1
     assert (seen == 1).all()
+
+
+def test_q5k_unit_layout(shim):
+    """The Q5_K unit is a bijection of 16 rows x 176 block bytes onto 2816 bytes; header and nibbles sit where the Q4_K
+    unit has them, and lane 4g + t of the fifth-bit segment holds qh[8t .. 8t+8) of rows g and g + 8 -- the bits of the
+    very weights (8t .. 8t+7 of every sub-block) whose nibbles the lane owns."""
+    n = shim.shim_q5k_unit_bytes()
+    assert n == 16 * 176
+    seen = np.zeros(n, dtype=np.int32)
+    for r in range(16):
+        for byte in range(176):
+            seen[shim.shim_q5k_unit_offset(r, byte)] += 1
+    assert (seen == 1).all()
+    for r in range(16):
+        for byte in range(16):
+            assert shim.shim_q5k_unit_offset(r, byte) == shim.shim_q4k_unit_offset(r, byte)
+        for byte in range(128):
+            assert shim.shim_q5k_unit_offset(r, 48 + byte) == shim.shim_q4k_unit_offset(r, 16 + byte)
+        g, hi = r & 7, r >> 3
+        for l in range(32):
+            t, j = l >> 3, l & 7
+            assert shim.shim_q5k_unit_offset(r, 16 + l) == 2304 + 16 * (4 * g + t) + 8 * hi + j

@@ -208,3 +208,56 @@ def test_swiglu_and_bf16_product():
     w = (D.bf16_rne(O.deq_raw(raw, 16 * 512, 12)).astype(np.uint32) << 16).view(np.float32).reshape(16, 512)
     xf = (xb.astype(np.uint32) << 16).view(np.float32)
     assert np.allclose(y, xf.astype(np.float64) @ w.astype(np.float64).T, rtol=1e-4, atol=1e-4)
+
+
+# ------------------------------------------------------------------------------ Q5_K
+# The reference holds no known-answer vector for Q5_K (its only check is fused-vs-unfused agreement,
+# crates/ferric-tensor/examples/ffn_fuse.rs:100-108).  The oracle's decoder (restated from
+# crates/ferric-gguf/src/lib.rs:690-716) is held against an independent numpy restatement and a hand-built block in the
+# style of the reference's Q4_K one (crates/ferric-gguf/examples/roundtrip.rs:54-87).
+def test_q5k_oracle_matches_independent_decoder_bit_for_bit():
+    rng = np.random.default_rng(50)
+    raw = synth.q5k_blocks(rng, 97).reshape(-1)
+    n = 97 * 256
+    assert O.type_size(13, n) == raw.size == 97 * 176
+    assert np.array_equal(O.deq_raw(raw, n, 13).view(np.uint32), D.deq_q5_k(raw, n).view(np.uint32))
+    wild = rng.integers(0, 256, size=40 * 176, dtype=np.uint8)          # any bytes: every (scale, min, bit) pattern
+    wild.reshape(-1, 176)[:, 0:4] = synth.q5k_blocks(rng, 40)[:, 0:4]    # keep d, dmin finite
+    assert np.array_equal(O.deq_raw(wild, 40 * 256, 13).view(np.uint32), D.deq_q5_k(wild, 40 * 256).view(np.uint32))
+
+
+def test_q5k_hand_built_block():
+    blk = np.zeros(176, dtype=np.uint8)
+    blk[0:2] = np.array([1.0], dtype=np.float16).view(np.uint8)         # d = 1
+    blk[2:4] = 0                                                         # dmin = 0
+    sc = np.arange(1, 9)                                                 # scale of sub-block j = j + 1
+    blk[4:16] = synth.pack_q4k_scales(sc[None, :], np.zeros((1, 8), dtype=np.int64))[0]
+    i = np.arange(128)
+    blk[48:176] = ((i % 8) | (((i + 3) % 8) << 4)).astype(np.uint8)
+    blk[16:48] = (np.arange(32) * 37 + 5).astype(np.uint8)               # fifth bits
+    got = O.deq_raw(blk, 256, 13)
+    want = np.empty(256, dtype=np.float32)
+    for grp in range(4):
+        for l in range(32):
+            b = int(blk[48 + 32 * grp + l])
+            qh = int(blk[16 + l])
+            want[64 * grp + l] = (grp * 2 + 1) * ((b & 15) + 16 * ((qh >> (2 * grp)) & 1))
+            want[64 * grp + 32 + l] = (grp * 2 + 2) * ((b >> 4) + 16 * ((qh >> (2 * grp + 1)) & 1))
+    assert np.array_equal(got, want)
+
+
+def test_q5k_product_modes_and_sizes():
+    rows, cols = 9, 512
+    raw = synth.matrix(13, rows, cols, seed=3)
+    x = synth.activations(2, cols, seed=4)
+    w = O.deq_raw(raw, rows * cols, 13).reshape(rows, cols)
+    ref = np.empty((2, rows), dtype=np.float32)
+    for t in range(2):
+        for r in range(rows):
+            acc = np.float32(0)
+            for c in range(cols):
+                acc = np.float32(acc + np.float32(x[t, c] * w[r, c]))
+            ref[t, r] = acc
+    assert np.array_equal(O.matmul_q(raw, 13, rows, cols, x), ref)
+    assert np.array_equal(O.matmul_q(raw, 13, rows, cols, x, threads=3), ref)
+    assert O.block_bytes(13) == (256, 176)
