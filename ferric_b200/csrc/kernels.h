@@ -30,7 +30,26 @@ struct PeerSum {
     int world = 0;                     // 0 = no exchange
 };
 
-enum Epilogue : int { kEpiStore = 0, kEpiSwiglu = 1 };
+// The same exchange done by pushing: the row-parallel product's epilogue stores every output value, paired with the
+// exchange's sequence number, straight into each rank's receive region; the consumer polls the pairs in its own memory.
+// An 8-byte store arrives whole, so a pair whose number matches carries its value: no flag, no fence, no signal kernel,
+// and only a one-way trip over NVLink on the critical path.  Receive regions are double-buffered on the number's parity.
+struct PushDst {                      // producer side (kernel parameter)
+    uint2* dst[kMaxRanks] = {};       // rank r's receive region for (kind, source = this rank), parity 0
+    const unsigned* epoch = nullptr;  // exchanges of this kind completed on this rank; the stamp is *epoch + 1
+    size_t parity_stride = 0;         // pairs between the two parities of a region
+    int world = 0;
+};
+struct PushSrc {                      // consumer side
+    const uint2* recv = nullptr;      // local memory: [parity][world][elems] pairs for this kind
+    unsigned* epoch = nullptr;        // bumped by the last CTA of the consumer
+    unsigned* ticket = nullptr;       // CTA counter for that
+    int* status = nullptr;            // set to 1 if a wait ran out
+    size_t elems = 0;
+    int world = 0;                    // 0 = not a push exchange
+};
+
+enum Epilogue : int { kEpiStore = 0, kEpiSwiglu = 1, kEpiPush = 2 };
 
 // Tunables read once from the environment (FERRIC_CUDA_*), the counterpart of the reference's
 // FERRIC_* kernel-selection flags (docs/FLAGS.md, crates/ferric-tensor/src/dtype.rs:2173-2187).
@@ -54,14 +73,15 @@ int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
 // w.cols) in one kernel; sum / norm may be null when the caller does not need them in memory.
 int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* a, const float* b,
                          const float* weight, float eps, size_t m, float* sum, float* norm, void* frag,
-                         const GemvTuning& tune, const PeerSum& peers = PeerSum());
+                         const GemvTuning& tune, const PeerSum& peers = PeerSum(), const PushSrc& pushed = PushSrc());
 // One CTA: bump this rank's exchange count and publish it to every peer's flag slot for this rank.
 int32_t launch_tp_signal(cudaStream_t st, unsigned* epoch, unsigned* const* peer_flag_slots, int world,
                          const GemvTuning& tune);
 // y[m, rows] (row stride ldy) = x . W^T from prepared fragments.  With kEpiSwiglu the matrix is
 // [gate rows | up rows] and y is [m, rows/2] = silu(gate) * up.
+// With kEpiPush y is not written: the values go to every rank named by `push` (ldy = row length there).
 int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const void* frag, size_t m, float* y,
-                    size_t ldy, Epilogue epi, const GemvTuning& tune);
+                    size_t ldy, Epilogue epi, const GemvTuning& tune, const PushDst& push = PushDst());
 // Q8_0 needs no fragments: y = x . W^T straight from f32 activations.
 int32_t launch_gemv_q8_0(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y,
                          size_t ldy, const GemvTuning& tune);

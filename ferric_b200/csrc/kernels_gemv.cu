@@ -51,6 +51,7 @@ __device__ __forceinline__ void imma_16816_s8s8(int (&d)[4], uint32_t a0, uint32
 // ------------------------------------------------------------------------------------------
 constexpr int kPrepWarps = 4;
 constexpr int kNormPrepMaxWarps = 32;
+constexpr int kNormPrepPushWarps = 20;   // the pushed-exchange variant holds every rank's values in registers while it polls
 
 // Per-warp staging.  16-byte aligned (and so padded to a multiple of 16 bytes): the limb rows are
 // written with 128-bit stores, and the struct is used in arrays indexed by warp.
@@ -173,6 +174,7 @@ prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk, size
 
 // A bounded wait on a peer: ~1 s of polling, then the kernel records the failure and carries on.
 constexpr int kPeerWaitSpins = 4000000;
+constexpr int kPushWaitSpins = 1000000;   // one round of polls is a trip to L2 for every rank's pairs
 
 // Sum of all ranks' partials at float offset `off`, in rank order (the same order on every rank,
 // so every rank forms bit-identical sums).  Peer memory is read uncached: it changes between
@@ -193,6 +195,42 @@ __device__ __forceinline__ float4 peer_sum4(const PeerSum& p, size_t off)
     for (int r = 1; r < kMaxRanks; r++) {
         if (r < p.world) {
             s.x += v[r].x; s.y += v[r].y; s.z += v[r].z; s.w += v[r].w;
+        }
+    }
+    return s;
+}
+
+// Pushed exchange, consumer side: the four values at pair offset `off` of every rank's slice, each polled (bounded)
+// until its stamp is `want`, summed in rank order.  All loads of a round are issued before the first check.
+__device__ __forceinline__ float4 pushed_sum4(const PushSrc& p, const uint2* base, size_t off, unsigned want, int limit)
+{
+    uint4 a[kMaxRanks], b[kMaxRanks];
+    int spins = 0;
+    for (;;) {
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; r++) {
+            if (r < p.world) {
+                const uint2* src = base + (size_t)r * p.elems + off;
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a[r].x), "=r"(a[r].y), "=r"(a[r].z), "=r"(a[r].w) : "l"(src));
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b[r].x), "=r"(b[r].y), "=r"(b[r].z), "=r"(b[r].w) : "l"(src + 2));
+            }
+        }
+        bool ok = true;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; r++)
+            if (r < p.world) ok = ok && a[r].y == want && a[r].w == want && b[r].y == want && b[r].w == want;
+        if (ok) break;
+        if (++spins > limit) {
+            *p.status = 1;
+            break;
+        }
+    }
+    float4 s = make_float4(__uint_as_float(a[0].x), __uint_as_float(a[0].z), __uint_as_float(b[0].x), __uint_as_float(b[0].z));
+#pragma unroll
+    for (int r = 1; r < kMaxRanks; r++) {
+        if (r < p.world) {
+            s.x += __uint_as_float(a[r].x); s.y += __uint_as_float(a[r].z);
+            s.z += __uint_as_float(b[r].x); s.w += __uint_as_float(b[r].z);
         }
     }
     return s;
@@ -225,21 +263,34 @@ int32_t launch_tp_signal(cudaStream_t st, unsigned* epoch, unsigned* const* peer
 // Fused residual add + RMSNorm + activation preparation (crates/ferric-tensor/src/lib.rs:372-384
 // followed by the matmul's own input conversion).  One CTA per tile of 2 activation rows; warp w
 // handles super-blocks w, w + nwarps, ...
-template <int TY, bool PEERS>
-__global__ void __launch_bounds__(32 * kNormPrepMaxWarps)
+// PEERS: 0 no exchange, 1 partial sums pulled from the peers' memory after their signal, 2 partial sums the peers
+// pushed into this rank's memory.
+template <int TY, int PEERS>
+__global__ void __launch_bounds__(PEERS == 2 ? 32 * kNormPrepPushWarps : 32 * kNormPrepMaxWarps)
 norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wgt, float eps,
                  size_t m, size_t d, size_t nblk, float* __restrict__ sum, float* __restrict__ norm,
-                 uint2* __restrict__ frag, PeerSum peers)
+                 uint2* __restrict__ frag, PeerSum peers, PushSrc pushed)
 {
     extern __shared__ __align__(16) uint8_t np_smem[];
     PrepSmem* sm = reinterpret_cast<PrepSmem*>(np_smem);
     __shared__ float part[2][kNormPrepMaxWarps];
     pdl_launch_dependents();
     pdl_wait();
-    if (PEERS) {
+    unsigned want = 0;
+    const uint2* recv = nullptr;
+    int wait_limit = 0;
+    if (PEERS == 2) {
+        // a wait that ran out earlier stays recorded: later kernels then do not wait again, so a lost peer costs one
+        // bound, not one per kernel
+        wait_limit = *reinterpret_cast<volatile int*>(pushed.status) ? 0 : kPushWaitSpins;
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(want) : "l"(pushed.epoch));
+        want += 1;
+        recv = pushed.recv + (size_t)(want & 1) * pushed.world * pushed.elems;
+    }
+    if (PEERS == 1) {
         // every rank's partial must have arrived: peers publish their exchange count into this
         // rank's flag slots; wait (bounded) until each has reached this rank's own count
-        if (threadIdx.x < peers.world) {
+        if (threadIdx.x < peers.world && *reinterpret_cast<volatile int*>(peers.status) == 0) {
             const unsigned want = *peers.epoch;
             unsigned seen = 0;
             int spins = 0;
@@ -270,8 +321,12 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
                     const float4 g = ld_act(reinterpret_cast<const float4*>(b + off) + i);
                     f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                 }
-                if (PEERS) {
+                if (PEERS == 1) {
                     const float4 g = peer_sum4(peers, off + 4 * i);
+                    f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
+                }
+                if (PEERS == 2) {
+                    const float4 g = pushed_sum4(pushed, recv, off + 4 * i, want, wait_limit);
                     f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                 }
                 if (sum) reinterpret_cast<float4*>(sum + off)[i] = f;
@@ -294,7 +349,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 float4 f;
-                if (sum) {
+                if (sum || PEERS == 2) {   // the pushed form always writes the sum (its launcher insists)
                     f = reinterpret_cast<const float4*>(sum + off)[i];
                 } else {
                     f = ld_act(reinterpret_cast<const float4*>(a + off) + i);
@@ -302,7 +357,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
                         const float4 g = ld_act(reinterpret_cast<const float4*>(b + off) + i);
                         f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                     }
-                    if (PEERS) {
+                    if (PEERS == 1) {
                         const float4 g = peer_sum4(peers, off + 4 * i);
                         f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                     }
@@ -318,6 +373,17 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
             for (int i = 0; i < 16; i++) v[i] = 0.0f;
         }
         prep_block<TY>(v, sm[warp], tile, nblk, blk, frag);
+    }
+    if (PEERS == 2) {
+        // the last CTA to get here closes the exchange: the next one of this kind carries the next number
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(pushed.ticket, 1u) == gridDim.x - 1) {
+                *pushed.ticket = 0;
+                asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(pushed.epoch), "r"(want) : "memory");
+            }
+        }
     }
 }
 
@@ -355,29 +421,33 @@ int32_t launch_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
 
 int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* a, const float* b,
                          const float* weight, float eps, size_t m, float* sum, float* norm, void* frag,
-                         const GemvTuning& tune, const PeerSum& peers)
+                         const GemvTuning& tune, const PeerSum& peers, const PushSrc& pushed)
 {
     size_t ntiles = padded_tiles(m);
     if (ntiles == 0 || w.nblk == 0) return kOk;
-    int nwarps = (int)(w.nblk < (size_t)kNormPrepMaxWarps ? w.nblk : (size_t)kNormPrepMaxWarps);
+    const int mode = pushed.world > 0 ? 2 : peers.world > 0 ? 1 : 0;
+    const int max_warps = mode == 2 ? kNormPrepPushWarps : kNormPrepMaxWarps;
+    int nwarps = (int)(w.nblk < (size_t)max_warps ? w.nblk : (size_t)max_warps);
     dim3 grid((unsigned)ntiles), block(32 * nwarps);
     size_t smem = (size_t)nwarps * sizeof(PrepSmem);
     uint2* f = reinterpret_cast<uint2*>(frag);
+    using Kernel = void (*)(const float*, const float*, const float*, float, size_t, size_t, size_t, float*, float*, uint2*,
+                            PeerSum, PushSrc);
+    // the variant without an exchange carries none of the peer-pointer code
+    static const Kernel table[2][3] = {
+        {norm_prep_kernel<(int)kGgmlQ4K, 0>, norm_prep_kernel<(int)kGgmlQ4K, 1>, norm_prep_kernel<(int)kGgmlQ4K, 2>},
+        {norm_prep_kernel<(int)kGgmlQ6K, 0>, norm_prep_kernel<(int)kGgmlQ6K, 1>, norm_prep_kernel<(int)kGgmlQ6K, 2>}};
     static thread_local int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     const int max_smem = (int)(kNormPrepMaxWarps * sizeof(PrepSmem));
     if (attr_dev != dev) {
-        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ4K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ6K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ4K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        cudaFuncSetAttribute(norm_prep_kernel<(int)kGgmlQ6K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        for (int i = 0; i < 2; i++)
+            for (int j = 0; j < 3; j++) cudaFuncSetAttribute(table[i][j], cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
         attr_dev = dev;
     }
-    // the variant without an exchange carries none of the peer-pointer code
-    auto kernel = (ty == kGgmlQ4K || ty == kGgmlQ5K) ? (peers.world > 0 ? norm_prep_kernel<(int)kGgmlQ4K, true> : norm_prep_kernel<(int)kGgmlQ4K, false>)
-                                 : (peers.world > 0 ? norm_prep_kernel<(int)kGgmlQ6K, true> : norm_prep_kernel<(int)kGgmlQ6K, false>);
-    FERRIC_CUDA_TRY(launch_kernel(kernel, grid, block, smem, st, tune.pdl, a, b, weight, eps, m, w.cols, w.nblk, sum, norm, f, peers));
+    Kernel kernel = table[(ty == kGgmlQ4K || ty == kGgmlQ5K) ? 0 : 1][mode];
+    FERRIC_CUDA_TRY(launch_kernel(kernel, grid, block, smem, st, tune.pdl, a, b, weight, eps, m, w.cols, w.nblk, sum, norm, f, peers, pushed));
     return kOk;
 }
 
@@ -408,10 +478,15 @@ __device__ __forceinline__ void cp_async_wait()
 // acc[nt][0..1] = row g, columns 2t, 2t+1 (activation row t>>1, limbs 2(t&1), 2(t&1)+1);
 // acc[nt][2..3] = row g+8.
 // ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void push_pair(uint2* dst, float v, unsigned stamp)
+{
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(stamp) : "memory");
+}
+
 template <int NT, int EPI>
 __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*red)[NT * 4][32], float* __restrict__ y,
                                                  size_t ldy, int rows, int m, int tile0, int wk, int out_tile,
-                                                 bool active)
+                                                 bool active, const PushDst& push)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int kpart = warp % wk, wr = warp / wk;
@@ -451,7 +526,22 @@ __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*re
         }
         const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
         const int r0 = out_tile * 16 + g;
-        if ((t & 1) == 0 && batch < m) {
+        if (EPI == kEpiPush) {
+            // (value, exchange number) pairs into every rank's receive region; 8-byte stores arrive whole
+            if ((t & 1) == 0 && batch < m) {
+                unsigned stamp;
+                asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(stamp) : "l"(push.epoch));
+                stamp += 1;
+                const size_t at = (size_t)(stamp & 1) * push.parity_stride + (size_t)batch * ldy + r0;
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; r++) {
+                    if (r < push.world) {
+                        if (r0 < rows) push_pair(push.dst[r] + at, lo, stamp);
+                        if (r0 + 8 < rows) push_pair(push.dst[r] + at + 8, hi, stamp);
+                    }
+                }
+            }
+        } else if ((t & 1) == 0 && batch < m) {
             if (r0 < rows) y[(size_t)batch * ldy + r0] = lo;
             if (r0 + 8 < rows) y[(size_t)batch * ldy + r0 + 8] = hi;
         }
@@ -465,7 +555,7 @@ template <int EPI>
 __device__ __forceinline__ void pick_tile(int wk, int row_tiles, int ff_tiles, int& rt, int& out_tile, bool& active)
 {
     const int warp = threadIdx.x >> 5, wr = warp / wk, wr_count = 8 / wk;
-    if (EPI == kEpiStore) {
+    if (EPI != kEpiSwiglu) {
         rt = blockIdx.x * wr_count + wr;
         out_tile = rt;
         active = rt < row_tiles;
@@ -527,7 +617,7 @@ __device__ __forceinline__ void q4k_row(const uint4& h, Q4KRow& r)
 template <int NT, int EPI, bool Q5 = false>
 __global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
-                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles)
+                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push)
 {
     __shared__ float red[8][NT * 4][32];
     constexpr int kUnitBytes = Q5 ? kQ5KUnit : kQ4KUnit;
@@ -673,7 +763,7 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             }
         }
     }
-    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active);
+    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -722,7 +812,7 @@ __device__ __forceinline__ int sc_byte(const uint4& v, int i)
 template <int NT, int EPI>
 __global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
-                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles)
+                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push)
 {
     __shared__ float red[8][NT * 4][32];
     pdl_launch_dependents();
@@ -864,7 +954,7 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             }
         }
     }
-    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active);
+    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -899,11 +989,11 @@ static int choose_wk(const DeviceWeights& w, Epilogue epi, int nt, const GemvTun
 
 template <int NT, int EPI>
 static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint2* frag, size_t m, float* y,
-                          size_t ldy, int wk, unsigned passes, bool pdl)
+                          size_t ldy, int wk, unsigned passes, bool pdl, const PushDst& push)
 {
     const int row_tiles = (int)w.row_tiles(), wr = 8 / wk;
     const int ff_tiles = (int)(w.rows / 2 / 16);
-    unsigned gx = EPI == kEpiStore ? (unsigned)((row_tiles + wr - 1) / wr) : (unsigned)((ff_tiles + wr / 2 - 1) / (wr / 2));
+    unsigned gx = EPI != kEpiSwiglu ? (unsigned)((row_tiles + wr - 1) / wr) : (unsigned)((ff_tiles + wr / 2 - 1) / (wr / 2));
     dim3 grid(gx, passes);
     // opt in to > 48 KB of dynamic shared memory once per kernel instantiation and device
     static thread_local int attr_dev_q4 = -1, attr_dev_q6 = -1;
@@ -915,7 +1005,7 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
             attr_dev_q4 = dev;
         }
         launch_kernel(gemv_q4k_kernel<NT, EPI>, grid, dim3(256), kSmemQ4K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles);
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
     } else if (ty == kGgmlQ5K) {
         static thread_local int attr_dev_q5 = -1;
         if (attr_dev_q5 != dev) {
@@ -923,27 +1013,28 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
             attr_dev_q5 = dev;
         }
         launch_kernel(gemv_q4k_kernel<NT, EPI, true>, grid, dim3(256), kSmemQ5K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles);
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
     } else {
         if (attr_dev_q6 != dev) {
             cudaFuncSetAttribute(gemv_q6k_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ6K);
             attr_dev_q6 = dev;
         }
         launch_kernel(gemv_q6k_kernel<NT, EPI>, grid, dim3(256), kSmemQ6K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles);
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
     }
 }
 
 int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const void* frag, size_t m, float* y,
-                    size_t ldy, Epilogue epi, const GemvTuning& tune)
+                    size_t ldy, Epilogue epi, const GemvTuning& tune, const PushDst& push)
 {
     if (m == 0 || w.rows == 0) return kOk;
     const int nt = tiles_per_pass(m), wk = choose_wk(w, epi, nt, tune);
     const unsigned passes = (unsigned)(padded_tiles(m) / (size_t)nt);
     const uint2* f = reinterpret_cast<const uint2*>(frag);
 #define FERRIC_GEMV_CASE(NT_)                                                                             \
-    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl);             \
-    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl)
+    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push);           \
+    else if (epi == kEpiPush) launch_gemv_t<NT_, kEpiPush>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push);        \
+    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push)
     if (nt == 1) { FERRIC_GEMV_CASE(1); }
     else if (nt == 2) { FERRIC_GEMV_CASE(2); }
     else { FERRIC_GEMV_CASE(4); }

@@ -14,6 +14,13 @@
 // Buffers never need a second copy: a rank can only signal exchange n+1 of a kind after its own
 // consumer of exchange n ran, and that consumer ran only after every peer had signalled n, i.e.
 // had finished the step that read exchange n-1.  No multicast, no multimem: peer loads/stores only.
+//
+// The pushed form of the same exchange (tp_matmul_push + tp_add_rmsnorm_prepare_pushed) takes the
+// signal kernel and the round trip of the peer loads off the critical path: the product's epilogue
+// stores (value, exchange number) pairs into every rank's receive region [kind][parity][source rank],
+// and the consumer polls the pairs in its own memory.  Parity double-buffers the regions: a rank
+// can write exchange n+2 of a kind only after it consumed n+1, which needed every peer's n+1, which
+// each peer produced after its own consumer of n had finished reading.
 #include <string.h>
 
 #include <new>
@@ -36,6 +43,9 @@ struct ferric_tp_group {
     unsigned* epoch = nullptr;        // [2]
     int* status = nullptr;
     unsigned** slot_table[2] = {};    // device arrays [world] of peers' flag-slot addresses for this rank
+    unsigned* push_epoch = nullptr;   // [2] pushed exchanges of each kind completed on this rank
+    unsigned* push_ticket = nullptr;  // [2] CTA counters of the consumers
+    uint2* recv = nullptr;            // [kind][parity][world][elems] (value, exchange number) pairs
     void* peer_base[kMaxRanks] = {};  // IPC mappings of the peers' `local`
     bool connected = false;
 };
@@ -46,7 +56,10 @@ size_t off_flags(size_t elems) { return align_up(2 * elems * sizeof(float), 256)
 size_t off_epoch(size_t elems) { return off_flags(elems) + 2 * kMaxRanks * sizeof(unsigned); }
 size_t off_status(size_t elems) { return off_epoch(elems) + 2 * sizeof(unsigned); }
 size_t off_slots(size_t elems) { return align_up(off_status(elems) + sizeof(int), 256); }
-size_t total_bytes(size_t elems) { return off_slots(elems) + 2 * kMaxRanks * sizeof(void*); }
+size_t off_push_meta(size_t elems) { return align_up(off_slots(elems) + 2 * kMaxRanks * sizeof(void*), 256); }
+size_t off_recv(size_t elems) { return off_push_meta(elems) + 256; }
+size_t recv_pairs(size_t elems, int world) { return (size_t)world * elems; }   // one parity of one kind
+size_t total_bytes(size_t elems, int world) { return off_recv(elems) + 4 * recv_pairs(elems, world) * sizeof(uint2); }
 }  // namespace
 
 extern "C" {
@@ -65,7 +78,7 @@ int32_t ferric_cuda_tp_create(ferric_cuda_ctx* ctx, int32_t rank, int32_t world,
     g->rank = rank;
     g->world = world;
     g->elems = elems;
-    g->local_bytes = total_bytes(elems);
+    g->local_bytes = total_bytes(elems, world);
     cudaError_t e = cudaMalloc(&g->local, g->local_bytes);
     if (e != cudaSuccess) {
         delete g;
@@ -86,6 +99,9 @@ int32_t ferric_cuda_tp_create(ferric_cuda_ctx* ctx, int32_t rank, int32_t world,
     g->status = reinterpret_cast<int*>(base + off_status(elems));
     g->slot_table[0] = reinterpret_cast<unsigned**>(base + off_slots(elems));
     g->slot_table[1] = g->slot_table[0] + kMaxRanks;
+    g->push_epoch = reinterpret_cast<unsigned*>(base + off_push_meta(elems));
+    g->push_ticket = g->push_epoch + 2;
+    g->recv = reinterpret_cast<uint2*>(base + off_recv(elems));
     g->peer_base[rank] = g->local;
     *out = g;
     return kOk;
@@ -170,6 +186,73 @@ int32_t ferric_cuda_tp_add_rmsnorm_prepare(ferric_cuda_ctx* ctx, ferric_tp_group
     ctx->launches++;
     return launch_norm_prep(ctx->stream, qm->ty, qm->w, a_dev, nullptr, weight_dev, eps, m, sum_dev, norm_dev, ctx->scratch,
                             ctx->tune, p);
+}
+
+int32_t ferric_cuda_tp_matmul_push(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t kind, const ferric_qmatrix* qm,
+                                   const float* x_dev, size_t m, size_t ldx)
+{
+    if (!ctx || !g || !qm || kind < 0 || kind > 1 || !g->connected || (m > 0 && !x_dev)) {
+        set_last_error("tp_matmul_push: NULL / unconnected argument or bad kind");
+        return kErrInvalidArg;
+    }
+    if (qm->ty == kGgmlQ8_0) return kUnsupported;
+    if (ldx == 0) ldx = qm->w.cols;
+    if (ldx < qm->w.cols || (ldx & 3)) {
+        set_last_error("row stride ldx %zu must cover the row and be a multiple of 4", ldx);
+        return kErrShape;
+    }
+    if (m * qm->w.rows > g->elems) {
+        set_last_error("exchange buffers hold %zu floats, %zu x %zu requested", g->elems, m, qm->w.rows);
+        return kErrShape;
+    }
+    if (m == 0 || qm->w.rows == 0) return kOk;
+    if (qm->w.nblk == 0) {
+        set_last_error("tp_matmul_push: empty K range");
+        return kErrShape;
+    }
+    DeviceGuard guard(ctx->device);
+    int32_t rc = ensure_scratch(ctx, frag_bytes(qm->ty, qm->w, m));
+    if (rc != kOk) return rc;
+    rc = launch_prep(ctx->stream, qm->ty, qm->w, x_dev, m, ldx, ctx->scratch, ctx->tune);
+    if (rc != kOk) return rc;
+    PushDst p;
+    p.world = g->world;
+    p.epoch = g->push_epoch + kind;
+    p.parity_stride = recv_pairs(g->elems, g->world);
+    for (int r = 0; r < g->world; r++)
+        p.dst[r] = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(g->peer_base[r]) + off_recv(g->elems)) +
+                   (size_t)kind * 2 * p.parity_stride + (size_t)g->rank * g->elems;
+    ctx->launches += 2;
+    return launch_gemv(ctx->stream, qm->ty, qm->w, ctx->scratch, m, nullptr, qm->w.rows, kEpiPush, ctx->tune, p);
+}
+
+int32_t ferric_cuda_tp_add_rmsnorm_prepare_pushed(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t kind,
+                                                  const ferric_qmatrix* qm, const float* a_dev, const float* weight_dev,
+                                                  float eps, size_t m, float* sum_dev, float* norm_dev)
+{
+    if (!ctx || !g || !qm || kind < 0 || kind > 1 || !g->connected || (m > 0 && (!a_dev || !sum_dev))) {
+        set_last_error("tp_add_rmsnorm_prepare_pushed: NULL / unconnected argument (sum_dev is required) or bad kind");
+        return kErrInvalidArg;
+    }
+    if (qm->ty == kGgmlQ8_0) return kUnsupported;
+    if (m * qm->w.cols > g->elems) {
+        set_last_error("exchange buffers hold %zu floats, %zu x %zu requested", g->elems, m, qm->w.cols);
+        return kErrShape;
+    }
+    if (m == 0 || qm->w.nblk == 0) return kOk;
+    DeviceGuard guard(ctx->device);
+    int32_t rc = ensure_scratch(ctx, frag_bytes(qm->ty, qm->w, m));
+    if (rc != kOk) return rc;
+    PushSrc p;
+    p.world = g->world;
+    p.elems = g->elems;
+    p.recv = g->recv + (size_t)kind * 2 * recv_pairs(g->elems, g->world);
+    p.epoch = g->push_epoch + kind;
+    p.ticket = g->push_ticket + kind;
+    p.status = g->status;
+    ctx->launches++;
+    return launch_norm_prep(ctx->stream, qm->ty, qm->w, a_dev, nullptr, weight_dev, eps, m, sum_dev, norm_dev, ctx->scratch,
+                            ctx->tune, PeerSum(), p);
 }
 
 int32_t ferric_cuda_tp_status(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t* timed_out)

@@ -381,14 +381,23 @@ class TPGroup:
 
     def add_rmsnorm_prepare(self, kind: int, qm: "QMatrix", a: torch.Tensor, weight: Optional[torch.Tensor] = None,
                             eps: float = 1e-6, sum_out: Optional[torch.Tensor] = None,
-                            norm_out: Optional[torch.Tensor] = None) -> int:
-        """``qm.add_rmsnorm_prepare(a, b, ..)`` with b = the all-reduced exchange buffer `kind`."""
+                            norm_out: Optional[torch.Tensor] = None, pushed: bool = False) -> int:
+        """``qm.add_rmsnorm_prepare(a, b, ..)`` with b = the all-reduced exchange `kind`: the buffers the ranks
+        signalled, or (``pushed``) what they pushed with ``matmul_push``."""
         m = a.numel() // a.shape[-1]
         ptr = lambda t: t.data_ptr() if t is not None else None
-        _check(self._lib.ferric_cuda_tp_add_rmsnorm_prepare(self.ctx._h, self._h, kind, qm._h, a.data_ptr(), ptr(weight),
-                                                            float(eps), m, ptr(sum_out), ptr(norm_out)),
+        fn = self._lib.ferric_cuda_tp_add_rmsnorm_prepare_pushed if pushed else self._lib.ferric_cuda_tp_add_rmsnorm_prepare
+        _check(fn(self.ctx._h, self._h, kind, qm._h, a.data_ptr(), ptr(weight), float(eps), m, ptr(sum_out), ptr(norm_out)),
                "tp_add_rmsnorm_prepare")
         return m
+
+    def matmul_push(self, kind: int, qm: "QMatrix", x: torch.Tensor) -> None:
+        """The row-parallel product x . W^T of this rank, stored by the kernel's epilogue into every rank's receive
+        region for exchange `kind` instead of a local buffer."""
+        assert x.dtype == torch.float32 and x.is_cuda and x.stride(-1) == 1
+        m = x.numel() // x.shape[-1]
+        ldx = x.stride(0) if x.dim() == 2 else x.shape[-1]
+        _check(self._lib.ferric_cuda_tp_matmul_push(self.ctx._h, self._h, kind, qm._h, x.data_ptr(), m, ldx), "tp_matmul_push")
 
     def check(self) -> None:
         """Synchronise and raise if a wait on a peer ran out."""

@@ -82,12 +82,15 @@ class DecodeStack:
     """``n_layers`` decoder layers' worth of packed-quant matmuls for ``batch`` tokens per step."""
 
     def __init__(self, ctx: Context, plan: TPPlan, n_layers: int = 64, batch: int = 1, eps: float = 1e-6,
-                 all_reduce: Optional[AllReduce] = None, group: Optional[TPGroup] = None):
+                 all_reduce: Optional[AllReduce] = None, group: Optional[TPGroup] = None, push: bool = True):
         """`all_reduce`: a callable summing a tensor over ranks in place (e.g. NCCL through torch.distributed).
-        `group`: a connected TPGroup -- then the exchange is done by this library's own kernels instead."""
+        `group`: a connected TPGroup -- then the exchange is done by this library's own kernels instead; with
+        `push` the o / down products store their partial sums straight into every rank's memory, otherwise each
+        rank signals its buffer and the consumers read the peers' buffers."""
         self.ctx, self.plan, self.n_layers, self.batch, self.eps = ctx, plan, n_layers, batch, eps
         self.all_reduce = all_reduce if (plan.world > 1 and group is None) else None
         self.group = group if plan.world > 1 else None
+        self.push = push
         if plan.world > 1 and all_reduce is None and group is None:
             raise ValueError("a tensor-parallel stack needs an all-reduce or an exchange group")
         self.layers: List[Layer] = []
@@ -157,22 +160,30 @@ class DecodeStack:
         G = self.group
         for i, L in enumerate(self.layers):
             L.wqkv.matmul_prepared(m, out=self.qkv)
-            L.wo.matmul(self.qkv[:, :p.q_rows], out=self.o)          # mixer pass-through: q feeds o
-            if G is not None:
+            if G is not None and self.push:
+                G.matmul_push(0, L.wo, self.qkv[:, :p.q_rows])
+                G.add_rmsnorm_prepare(0, L.wgu, self.h, None, self.eps, sum_out=self.h, pushed=True)
+            elif G is not None:
+                L.wo.matmul(self.qkv[:, :p.q_rows], out=self.o)      # mixer pass-through: q feeds o
                 G.signal(0)
                 G.add_rmsnorm_prepare(0, L.wgu, self.h, None, self.eps, sum_out=self.h)
             else:
+                L.wo.matmul(self.qkv[:, :p.q_rows], out=self.o)
                 if self.all_reduce:
                     self.all_reduce(self.o)
                 L.wgu.add_rmsnorm_prepare(self.h, self.o, None, self.eps, sum_out=self.h)
             L.wgu.matmul_prepared(m, out=self.f, swiglu=True)
-            L.wdown.matmul(self.f, out=self.d)
             nxt = self.layers[i + 1].wqkv if i + 1 < n else self.layers[0].wqkv
             last_norm = self.xn if i + 1 == n else None      # after the last layer the norm itself is the result
-            if G is not None:
+            if G is not None and self.push:
+                G.matmul_push(1, L.wdown, self.f)
+                G.add_rmsnorm_prepare(1, nxt, self.h, None, self.eps, sum_out=self.h, norm_out=last_norm, pushed=True)
+            elif G is not None:
+                L.wdown.matmul(self.f, out=self.d)
                 G.signal(1)
                 G.add_rmsnorm_prepare(1, nxt, self.h, None, self.eps, sum_out=self.h, norm_out=last_norm)
             else:
+                L.wdown.matmul(self.f, out=self.d)
                 if self.all_reduce:
                     self.all_reduce(self.d)
                 nxt.add_rmsnorm_prepare(self.h, self.d, None, self.eps, sum_out=self.h, norm_out=last_norm)

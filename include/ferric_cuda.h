@@ -332,6 +332,19 @@ int32_t ferric_cuda_tp_signal(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t 
 int32_t ferric_cuda_tp_add_rmsnorm_prepare(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t kind,
                                            const ferric_qmatrix *qm, const float *a_dev, const float *weight_dev,
                                            float eps, size_t m, float *sum_dev, float *norm_dev);
+/* The same exchange, pushed (the lower-latency form for a few activation rows): the row-parallel product
+ * x_dev[m, cols] . W^T is not written to a buffer of this rank; its epilogue stores every value, paired with the
+ * exchange's sequence number, into the receive region of every rank (this one included).  Q4_K / Q5_K / Q6_K;
+ * m x rows must fit the group's `elems`. */
+int32_t ferric_cuda_tp_matmul_push(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t kind, const ferric_qmatrix *qm,
+                                   const float *x_dev, size_t m, size_t ldx);
+/* ferric_cuda_add_rmsnorm_prepare with b = the sum over all ranks of what they pushed for exchange `kind`: polls
+ * (bounded) the pairs in this rank's own memory, sums in rank order, then closes the exchange.  Every
+ * tp_matmul_push of a kind must be followed by exactly one of these before the next push of that kind. */
+int32_t ferric_cuda_tp_add_rmsnorm_prepare_pushed(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t kind,
+                                                  const ferric_qmatrix *qm, const float *a_dev,
+                                                  const float *weight_dev, float eps, size_t m, float *sum_dev,
+                                                  float *norm_dev);
 /* Synchronise the context and report whether any wait on a peer ran out (FERRIC_ERR_TIMEOUT). */
 int32_t ferric_cuda_tp_status(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t *timed_out);
 void ferric_cuda_tp_free(ferric_tp_group *g);

@@ -1,6 +1,7 @@
 """Tensor-parallel decode stack on two GPUs: NCCL all-reduce and the library's own peer-memory
-exchange against the unsharded CPU oracle.  Needs 2 GPUs (skipped otherwise); ranks are separate
-processes, one per GPU, NVLS off."""
+exchanges (signalled buffers read by the peers; values pushed by the product's epilogue) against the
+unsharded CPU oracle.  Needs 2 GPUs (skipped otherwise); ranks are separate processes, one per GPU,
+NVLS off.  The pushed exchange also runs with a group of one rank, which needs one GPU only."""
 import os
 import socket
 import subprocess
@@ -41,3 +42,43 @@ def test_two_gpu_stack_matches_unsharded_oracle(tmp_path):
     assert np.abs(got["fused"] - h).max() <= tol
     assert np.array_equal(got["fused"], got["fused_replay"])       # graph replay == eager
     assert np.array_equal(got["nccl"], got["nccl_replay"])
+    assert np.abs(got["push"] - h).max() <= tol
+    assert np.array_equal(got["push"], got["push_replay"])
+    assert np.array_equal(got["push"], got["fused"])               # same partials, same rank-order sum
+
+
+@pytest.mark.parametrize("m", [1, 2, 5, 8])
+def test_pushed_exchange_with_one_rank(m):
+    """A group of one rank pushes to itself: matmul_push + the pushed add+norm+prepare must equal the plain matmul
+    followed by add+norm+prepare bit for bit, for both kinds, with one kind used several times running (the parity
+    double-buffer) and with both formats of the row-parallel products."""
+    import ferric_b200 as F
+    from ferric_b200 import synth
+
+    ctx = F.Context(0)
+    hid, kshard = 1024, 768
+    grp = F.TPGroup(ctx, 0, 1, m, hid)
+    grp.connect([grp.export()])
+    nxt = F.QMatrix.from_bytes(ctx, synth.matrix(12, 64, hid, seed=1), 12, 64, hid)
+    rng = np.random.default_rng(m)
+    for ty, kinds in ((12, (0, 0, 0, 1)), (14, (1, 0, 1, 1, 1))):
+        w = F.QMatrix.from_bytes(ctx, synth.matrix(ty, hid, kshard, seed=ty), ty, hid, kshard)
+        for i, kind in enumerate(kinds):
+            x = torch.from_numpy(synth.activations(m, kshard, seed=10 * ty + i)).cuda()
+            a = torch.from_numpy(rng.standard_normal((m, hid)).astype(np.float32)).cuda()
+            wn = torch.from_numpy(rng.uniform(0.5, 1.5, hid).astype(np.float32)).cuda()
+            s1, n1 = torch.empty_like(a), torch.empty_like(a)
+            mm = nxt.add_rmsnorm_prepare(a, w.matmul(x), wn, 1e-6, sum_out=s1, norm_out=n1)
+            y1 = nxt.matmul_prepared(mm).clone()
+            s2, n2 = torch.empty_like(a), torch.empty_like(a)
+            grp.matmul_push(kind, w, x)
+            grp.add_rmsnorm_prepare(kind, nxt, a, wn, 1e-6, sum_out=s2, norm_out=n2, pushed=True)
+            y2 = nxt.matmul_prepared(mm)
+            grp.check()
+            assert torch.equal(s1, s2) and torch.equal(n1, n2) and torch.equal(y1, y2)
+        w.close()
+    with pytest.raises(F.FerricError):
+        grp.add_rmsnorm_prepare(0, nxt, a, None, 1e-6, pushed=True)       # the pushed form needs sum_out
+    nxt.close()
+    grp.close()
+    ctx.close()

@@ -26,13 +26,14 @@ def main(rank, world, port, out):
     ctx = F.Context(rank)
     plan = TPPlan.make(world, rank, HID, NFF, QOUT, KV)
     results = {}
-    for mode in ("nccl", "fused"):
+    for mode in ("nccl", "fused", "push"):
         group = None
-        if mode == "fused":
+        if mode != "nccl":
             group = F.TPGroup(ctx, rank, world, B, HID)
             group.connect_with_torch_distributed()
         st = DecodeStack(ctx, plan, n_layers=LAYERS, batch=B,
-                         all_reduce=(lambda t: dist.all_reduce(t)) if mode == "nccl" else None, group=group)
+                         all_reduce=(lambda t: dist.all_reduce(t)) if mode == "nccl" else None, group=group,
+                         push=(mode == "push"))
         for l in range(LAYERS):
             sh = layer_shards(plan, full_layer(100 + 10 * l))
             st.add_layer(F.QMatrix.from_bytes(ctx, sh["qkv"], 12, plan.q_rows + 2 * plan.kv_rows, HID),
@@ -55,7 +56,7 @@ def main(rank, world, port, out):
         dist.barrier()
     if rank == 0:
         np.savez(out, nccl=results["nccl"][0], nccl_replay=results["nccl"][1], fused=results["fused"][0],
-                 fused_replay=results["fused"][1])
+                 fused_replay=results["fused"][1], push=results["push"][0], push_replay=results["push"][1])
     dist.barrier()
     os._exit(0)
 
