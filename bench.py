@@ -51,8 +51,9 @@ def parse_args():
     ap.add_argument("--prefill-rows", type=int, default=17408, help="weight rows of the --prefill matrix")
     ap.add_argument("--prefill-cols", type=int, default=5120, help="columns (K) of the --prefill matrix")
     ap.add_argument("--prefill-type", type=int, default=12, choices=[12, 14, 8], help="ggml type of the --prefill matrix")
-    ap.add_argument("--allreduce", default="auto", choices=["auto", "fused", "nccl"],
-                    help="N > 1: the library's own peer-memory exchange, NCCL through torch.distributed, or (default) the former up to batch 4")
+    ap.add_argument("--allreduce", default="auto", choices=["auto", "push", "fused", "nccl"],
+                    help="N > 1: the library's own exchange over peer memory (push: the products store into every rank's memory; "
+                         "fused: signalled buffers read by the peers), NCCL through torch.distributed, or (default) push up to batch 8")
     return ap.parse_args()
 
 
@@ -213,11 +214,11 @@ def run_ours(args):
     ctx = Context(local)
     plan = TPPlan.make(world, rank, HIDDEN, N_FF, Q_OUT, KV_OUT)
     def exchange_for(batch):
-        """(all_reduce callable, exchange group, name) for a batch size.  `auto`: the library's own exchange over peer
-        memory while the payload is latency-bound (up to 4 rows of 20 KB), NCCL above that (measured cross-over)."""
+        """(all_reduce callable, exchange group, name) for a batch size.  `auto`: the library's own pushed exchange
+        while the GEMV serves the batch (up to 8 rows of 20 KB per rank), NCCL above that."""
         if world == 1:
             return None, None, "none"
-        kind = args.allreduce if args.allreduce != "auto" else ("fused" if batch <= 4 else "nccl")
+        kind = args.allreduce if args.allreduce != "auto" else ("push" if batch <= 8 else "nccl")
         if kind == "nccl":
             return (lambda t: dist.all_reduce(t)), None, kind
         grp = TPGroup(ctx, rank, world, batch, HIDDEN)
@@ -225,7 +226,7 @@ def run_ours(args):
         return None, grp, kind
 
     allreduce, group, ar_name = exchange_for(B)
-    stack = DecodeStack(ctx, plan, n_layers=args.layers, batch=B, all_reduce=allreduce, group=group)
+    stack = DecodeStack(ctx, plan, n_layers=args.layers, batch=B, all_reduce=allreduce, group=group, push=(ar_name == "push"))
     stack.build_synthetic(seed=4)
     g = torch.Generator(device=dev).manual_seed(4)
     x0 = torch.randn((B, HIDDEN), device=dev, generator=g)
@@ -269,7 +270,7 @@ def run_ours(args):
             if b == B:
                 continue
             ar2, g2, name2 = exchange_for(b)
-            st2 = DecodeStack(ctx, plan, n_layers=args.layers, batch=b, all_reduce=ar2, group=g2)
+            st2 = DecodeStack(ctx, plan, n_layers=args.layers, batch=b, all_reduce=ar2, group=g2, push=(name2 == "push"))
             for L in stack.layers:
                 st2.add_layer(L.wqkv, L.wo, L.wgu, L.wdown)
             st2.reserve()

@@ -311,6 +311,22 @@ int32_t ferric_cuda_ctx_create_on_stream(int device, void* cuda_stream, ferric_c
     ctx->tune.sm_count = ctx->prop.multiProcessorCount;
     if (const char* s = getenv("FERRIC_CUDA_GEMV_WK")) ctx->tune.wk = atoi(s);
     if (const char* s = getenv("FERRIC_CUDA_PDL")) ctx->tune.pdl = atoi(s) != 0;
+    if (const char* s = getenv("FERRIC_CUDA_PUSH_CLUSTER")) ctx->tune.push_cluster = atoi(s);
+    if (const char* s = getenv("FERRIC_CUDA_GEMV_KSPLIT")) ctx->tune.split = atoi(s);
+    {
+        const size_t bytes = kSplitWsFloats * sizeof(float) + kSplitTickets * sizeof(unsigned);
+        void* ws = nullptr;
+        cudaError_t e2 = cudaMalloc(&ws, bytes);
+        if (e2 == cudaSuccess) e2 = cudaMemset(ws, 0, bytes);
+        if (e2 != cudaSuccess) {
+            if (ws) cudaFree(ws);
+            if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+            delete ctx;
+            return cuda_fail(e2, "cudaMalloc(split workspace)");
+        }
+        ctx->tune.split_ws.partial = reinterpret_cast<float*>(ws);
+        ctx->tune.split_ws.tickets = reinterpret_cast<unsigned*>(ctx->tune.split_ws.partial + kSplitWsFloats);
+    }
     *out = ctx;
     return kOk;
 }
@@ -365,6 +381,7 @@ void ferric_cuda_ctx_free(ferric_cuda_ctx* ctx)
     DeviceGuard guard(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->tune.split_ws.partial) cudaFree(ctx->tune.split_ws.partial);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }

@@ -51,11 +51,23 @@ struct PushSrc {                      // consumer side
 
 enum Epilogue : int { kEpiStore = 0, kEpiSwiglu = 1, kEpiPush = 2 };
 
+// Workspace of a GEMV whose K range is cut across CTAs (grid z): every CTA of a tile group leaves its partial sums
+// here, and the last one to arrive (a ticket per group) adds them in z order and stores the result.
+struct SplitWs {
+    float* partial = nullptr;     // [z][m][rows]
+    unsigned* tickets = nullptr;  // [grid y][grid x], zero between launches
+};
+constexpr size_t kSplitWsFloats = 1u << 20;   // 4 MiB of partial sums per context
+constexpr size_t kSplitTickets = 1u << 14;
+
 // Tunables read once from the environment (FERRIC_CUDA_*), the counterpart of the reference's
 // FERRIC_* kernel-selection flags (docs/FLAGS.md, crates/ferric-tensor/src/dtype.rs:2173-2187).
 struct GemvTuning {
     int wk = 0;        // warps of a CTA that split K (0 = choose from the shape)
     int sm_count = 148;
+    int push_cluster = 0;   // CTAs (a cluster) sharing one tile of the pushed exchange's consumer: 1, 2, 4 or 8; 0 = from the world size
+    int split = -1;         // CTAs along K per row-tile group of the GEMV (FERRIC_CUDA_GEMV_KSPLIT); -1 = choose from the shape
+    SplitWs split_ws;       // the context's workspace for that (not a tunable: it rides here to reach the launchers)
     bool pdl = true;   // programmatic dependent launch between consecutive kernels (FERRIC_CUDA_PDL=0 disables)
 };
 

@@ -263,6 +263,32 @@ int32_t launch_tp_signal(cudaStream_t st, unsigned* epoch, unsigned* const* peer
 // Fused residual add + RMSNorm + activation preparation (crates/ferric-tensor/src/lib.rs:372-384
 // followed by the matmul's own input conversion).  One CTA per tile of 2 activation rows; warp w
 // handles super-blocks w, w + nwarps, ...
+// Thread-block cluster helpers of the pushed consumer (a launch without clusters reads rank 0 of 1).
+__device__ __forceinline__ unsigned cl_rank()
+{
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned cl_size()
+{
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cl_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float cl_load_f32(const float* own_smem, unsigned rank)
+{
+    unsigned a;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"((unsigned)__cvta_generic_to_shared(own_smem)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+    return v;
+}
+
 // PEERS: 0 no exchange, 1 partial sums pulled from the peers' memory after their signal, 2 partial sums the peers
 // pushed into this rank's memory.
 template <int TY, int PEERS>
@@ -307,11 +333,15 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int prow = lane >> 4, q = lane & 15;
-    const size_t tile = blockIdx.x, batch = tile * kRowsPerTile + (size_t)prow;
+    // The pushed form may run one tile on a cluster of CTAs: polling every rank's pairs is a lot of L2 traffic for
+    // one SM, so the super-blocks are dealt round the cluster and only the sums of squares cross it.
+    const unsigned crank = PEERS == 2 ? cl_rank() : 0u, csize = PEERS == 2 ? cl_size() : 1u;
+    const size_t blk_first = (size_t)crank * nwarps + warp, blk_step = (size_t)csize * nwarps;
+    const size_t tile = blockIdx.x / csize, batch = tile * kRowsPerTile + (size_t)prow;
     const bool valid = batch < m;
     // pass 1: s = a + b, sum of squares per row
     float ms = 0.0f;
-    for (size_t blk = warp; blk < nblk; blk += nwarps) {
+    for (size_t blk = blk_first; blk < nblk; blk += blk_step) {
         if (valid) {
             const size_t off = batch * d + blk * 256 + 16 * q;
 #pragma unroll
@@ -339,10 +369,18 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
     if (q == 0) part[prow][warp] = ms;
     __syncthreads();
     float tot = 0.0f;
-    for (int i = 0; i < nwarps; i++) tot += part[prow][i];
+    if (PEERS == 2 && csize > 1) {
+        // every CTA adds all the cluster's per-warp sums in super-block order: the same order in every CTA, and the
+        // order of a single CTA with one warp per super-block
+        cl_sync();
+        for (unsigned c = 0; c < csize; c++)
+            for (int i = 0; i < nwarps; i++) tot += cl_load_f32(&part[prow][i], c);
+    } else {
+        for (int i = 0; i < nwarps; i++) tot += part[prow][i];
+    }
     const float inv = 1.0f / sqrtf(tot / (float)d + eps);
     // pass 2: normalise and convert
-    for (size_t blk = warp; blk < nblk; blk += nwarps) {
+    for (size_t blk = blk_first; blk < nblk; blk += blk_step) {
         float v[16];
         if (valid) {
             const size_t off = batch * d + blk * 256 + 16 * q;
@@ -374,6 +412,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
         }
         prep_block<TY>(v, sm[warp], tile, nblk, blk, frag);
     }
+    if (PEERS == 2 && csize > 1) cl_sync();   // no CTA leaves while another may still read its sums
     if (PEERS == 2) {
         // the last CTA to get here closes the exchange: the next one of this kind carries the next number
         __syncthreads();
@@ -427,8 +466,15 @@ int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
     if (ntiles == 0 || w.nblk == 0) return kOk;
     const int mode = pushed.world > 0 ? 2 : peers.world > 0 ? 1 : 0;
     const int max_warps = mode == 2 ? kNormPrepPushWarps : kNormPrepMaxWarps;
-    int nwarps = (int)(w.nblk < (size_t)max_warps ? w.nblk : (size_t)max_warps);
-    dim3 grid((unsigned)ntiles), block(32 * nwarps);
+    unsigned cluster = 1;
+    if (mode == 2) {
+        int c = tune.push_cluster > 0 ? tune.push_cluster : (pushed.world >= 4 ? 4 : 1);
+        while (c > 1 && ((c & (c - 1)) || c > 8 || (size_t)c > w.nblk)) c--;   // a power of two up to 8, at most one CTA per super-block
+        cluster = (unsigned)c;
+    }
+    const size_t per_cta = (w.nblk + cluster - 1) / cluster;
+    int nwarps = (int)(per_cta < (size_t)max_warps ? per_cta : (size_t)max_warps);
+    dim3 grid((unsigned)ntiles * cluster), block(32 * nwarps);
     size_t smem = (size_t)nwarps * sizeof(PrepSmem);
     uint2* f = reinterpret_cast<uint2*>(frag);
     using Kernel = void (*)(const float*, const float*, const float*, float, size_t, size_t, size_t, float*, float*, uint2*,
@@ -447,7 +493,11 @@ int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
         attr_dev = dev;
     }
     Kernel kernel = table[(ty == kGgmlQ4K || ty == kGgmlQ5K) ? 0 : 1][mode];
-    FERRIC_CUDA_TRY(launch_kernel(kernel, grid, block, smem, st, tune.pdl, a, b, weight, eps, m, w.cols, w.nblk, sum, norm, f, peers, pushed));
+    if (cluster > 1)
+        FERRIC_CUDA_TRY(launch_kernel_cluster(kernel, grid, block, smem, st, tune.pdl, cluster, a, b, weight, eps, m, w.cols, w.nblk, sum,
+                                              norm, f, peers, pushed));
+    else
+        FERRIC_CUDA_TRY(launch_kernel(kernel, grid, block, smem, st, tune.pdl, a, b, weight, eps, m, w.cols, w.nblk, sum, norm, f, peers, pushed));
     return kOk;
 }
 
@@ -483,10 +533,34 @@ __device__ __forceinline__ void push_pair(uint2* dst, float v, unsigned stamp)
     asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(stamp) : "memory");
 }
 
+// One lane's two results (rows r0 and r0 + 8 of activation row `batch`): into y, or, for the pushed exchange, as
+// (value, exchange number) pairs into every rank's receive region (8-byte stores arrive whole).
+template <int EPI>
+__device__ __forceinline__ void store_result(float* __restrict__ y, size_t ldy, int rows, int batch, int r0, float lo, float hi,
+                                             const PushDst& push)
+{
+    if (EPI == kEpiPush) {
+        unsigned stamp;
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(stamp) : "l"(push.epoch));
+        stamp += 1;
+        const size_t at = (size_t)(stamp & 1) * push.parity_stride + (size_t)batch * ldy + r0;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; r++) {
+            if (r < push.world) {
+                if (r0 < rows) push_pair(push.dst[r] + at, lo, stamp);
+                if (r0 + 8 < rows) push_pair(push.dst[r] + at + 8, hi, stamp);
+            }
+        }
+    } else {
+        if (r0 < rows) y[(size_t)batch * ldy + r0] = lo;
+        if (r0 + 8 < rows) y[(size_t)batch * ldy + r0 + 8] = hi;
+    }
+}
+
 template <int NT, int EPI>
 __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*red)[NT * 4][32], float* __restrict__ y,
                                                  size_t ldy, int rows, int m, int tile0, int wk, int out_tile,
-                                                 bool active, const PushDst& push)
+                                                 bool active, const PushDst& push, const SplitWs& split)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int kpart = warp % wk, wr = warp / wk;
@@ -495,55 +569,75 @@ __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*re
 #pragma unroll
         for (int i = 0; i < 4; i++) red[warp][nt * 4 + i][lane] = acc[nt][i];
     __syncthreads();
-    if (kpart != 0 || !active) return;
-    if (EPI == kEpiSwiglu && (wr & 1)) return;
+    const bool ksplit = EPI != kEpiSwiglu && gridDim.z > 1;   // K is also cut across CTAs
+    const bool writer = kpart == 0 && active && !(EPI == kEpiSwiglu && (wr & 1));
+    if (!writer && !ksplit) return;
     // limb weights of this lane's two columns: 2^(-7*limb)
     const float w0 = (t & 1) ? 6.103515625e-05f : 1.0f;          // 2^-14 : 2^0
     const float w1 = (t & 1) ? 4.76837158203125e-07f : 0.0078125f; // 2^-21 : 2^-7
+    const int r0 = out_tile * 16 + g;
+    if (writer) {
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-        float v[4], u[4];
+        for (int nt = 0; nt < NT; nt++) {
+            float v[4], u[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float s = 0.0f;
-            for (int k = 0; k < wk; k++) s += red[warp + k][nt * 4 + i][lane];
-            v[i] = s;
-            if (EPI == kEpiSwiglu) {
-                float s2 = 0.0f;
-                for (int k = 0; k < wk; k++) s2 += red[warp + wk + k][nt * 4 + i][lane];
-                u[i] = s2;
-            }
-        }
-        float lo = v[0] * w0 + v[1] * w1, hi = v[2] * w0 + v[3] * w1;
-        lo += __shfl_xor_sync(0xffffffffu, lo, 1);
-        hi += __shfl_xor_sync(0xffffffffu, hi, 1);
-        if (EPI == kEpiSwiglu) {
-            float ulo = u[0] * w0 + u[1] * w1, uhi = u[2] * w0 + u[3] * w1;
-            ulo += __shfl_xor_sync(0xffffffffu, ulo, 1);
-            uhi += __shfl_xor_sync(0xffffffffu, uhi, 1);
-            lo = silu_mul(lo, ulo);
-            hi = silu_mul(hi, uhi);
-        }
-        const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
-        const int r0 = out_tile * 16 + g;
-        if (EPI == kEpiPush) {
-            // (value, exchange number) pairs into every rank's receive region; 8-byte stores arrive whole
-            if ((t & 1) == 0 && batch < m) {
-                unsigned stamp;
-                asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(stamp) : "l"(push.epoch));
-                stamp += 1;
-                const size_t at = (size_t)(stamp & 1) * push.parity_stride + (size_t)batch * ldy + r0;
-#pragma unroll
-                for (int r = 0; r < kMaxRanks; r++) {
-                    if (r < push.world) {
-                        if (r0 < rows) push_pair(push.dst[r] + at, lo, stamp);
-                        if (r0 + 8 < rows) push_pair(push.dst[r] + at + 8, hi, stamp);
-                    }
+            for (int i = 0; i < 4; i++) {
+                float s = 0.0f;
+                for (int k = 0; k < wk; k++) s += red[warp + k][nt * 4 + i][lane];
+                v[i] = s;
+                if (EPI == kEpiSwiglu) {
+                    float s2 = 0.0f;
+                    for (int k = 0; k < wk; k++) s2 += red[warp + wk + k][nt * 4 + i][lane];
+                    u[i] = s2;
                 }
             }
-        } else if ((t & 1) == 0 && batch < m) {
-            if (r0 < rows) y[(size_t)batch * ldy + r0] = lo;
-            if (r0 + 8 < rows) y[(size_t)batch * ldy + r0 + 8] = hi;
+            float lo = v[0] * w0 + v[1] * w1, hi = v[2] * w0 + v[3] * w1;
+            lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+            hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+            if (EPI == kEpiSwiglu) {
+                float ulo = u[0] * w0 + u[1] * w1, uhi = u[2] * w0 + u[3] * w1;
+                ulo += __shfl_xor_sync(0xffffffffu, ulo, 1);
+                uhi += __shfl_xor_sync(0xffffffffu, uhi, 1);
+                lo = silu_mul(lo, ulo);
+                hi = silu_mul(hi, uhi);
+            }
+            const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
+            if ((t & 1) == 0 && batch < m) {
+                if (ksplit) {
+                    float* dst = split.partial + ((size_t)blockIdx.z * m + batch) * rows + r0;
+                    if (r0 < rows) __stcg(dst, lo);
+                    if (r0 + 8 < rows) __stcg(dst + 8, hi);
+                } else {
+                    store_result<EPI>(y, ldy, rows, batch, r0, lo, hi, push);
+                }
+            }
+        }
+    }
+    if (!ksplit) return;
+    // The CTAs that share these row tiles (grid z) each left a partial; the last to arrive adds them in z order.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* ticket = split.tickets + (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+        const unsigned seen = atomicAdd(ticket, 1u);
+        is_last = seen == gridDim.z - 1;
+        if (is_last) *ticket = 0;   // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last || !writer) return;
+    __threadfence();
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
+        if ((t & 1) == 0 && batch < m) {
+            float lo = 0.0f, hi = 0.0f;
+            for (unsigned z = 0; z < gridDim.z; z++) {
+                const float* src = split.partial + ((size_t)z * m + batch) * rows + r0;
+                if (r0 < rows) lo += __ldcg(src);
+                if (r0 + 8 < rows) hi += __ldcg(src + 8);
+            }
+            store_result<EPI>(y, ldy, rows, batch, r0, lo, hi, push);
         }
     }
 }
@@ -617,7 +711,7 @@ __device__ __forceinline__ void q4k_row(const uint4& h, Q4KRow& r)
 template <int NT, int EPI, bool Q5 = false>
 __global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
-                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push)
+                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push, SplitWs split)
 {
     __shared__ float red[8][NT * 4][32];
     constexpr int kUnitBytes = Q5 ? kQ5KUnit : kQ4KUnit;
@@ -626,8 +720,9 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
     int rt, out_tile;
     bool active;
     pick_tile<EPI>(wk, row_tiles, ff_tiles, rt, out_tile, active);
-    const int kpart = warp % wk, per = (nblk + wk - 1) / wk;
-    const int b0 = kpart * per, b1 = min(nblk, b0 + per);
+    // K is cut over the wk warps of a CTA and, when the grid has a z extent, over that many CTAs as well
+    const int kparts = wk * (int)gridDim.z, kpart = (int)blockIdx.z * wk + warp % wk, per = (nblk + kparts - 1) / kparts;
+    const int b0 = min(nblk, kpart * per), b1 = min(nblk, b0 + per);
     const int tile0 = blockIdx.y * NT;
     const int zero[4] = {0, 0, 0, 0};
 
@@ -763,7 +858,7 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             }
         }
     }
-    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push);
+    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push, split);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -812,7 +907,7 @@ __device__ __forceinline__ int sc_byte(const uint4& v, int i)
 template <int NT, int EPI>
 __global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
-                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push)
+                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push, SplitWs split)
 {
     __shared__ float red[8][NT * 4][32];
     pdl_launch_dependents();
@@ -820,8 +915,9 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
     int rt, out_tile;
     bool active;
     pick_tile<EPI>(wk, row_tiles, ff_tiles, rt, out_tile, active);
-    const int kpart = warp % wk, per = (nblk + wk - 1) / wk;
-    const int b0 = kpart * per, b1 = min(nblk, b0 + per);
+    // K is cut over the wk warps of a CTA and, when the grid has a z extent, over that many CTAs as well
+    const int kparts = wk * (int)gridDim.z, kpart = (int)blockIdx.z * wk + warp % wk, per = (nblk + kparts - 1) / kparts;
+    const int b0 = min(nblk, kpart * per), b1 = min(nblk, b0 + per);
     const int tile0 = blockIdx.y * NT;
     const int zero[4] = {0, 0, 0, 0};
 
@@ -954,7 +1050,7 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             }
         }
     }
-    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push);
+    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push, split);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -964,37 +1060,52 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 // in as few waves of resident CTAs as possible -- every wave pays its own pipeline fill and
 // drain -- and within that, K-splitting shortens each warp's serial walk.  Cost model: waves x
 // (super-blocks per warp + a fixed fill/drain term), measured in super-block times.
-static int choose_wk(const DeviceWeights& w, Epilogue epi, int nt, const GemvTuning& tune)
+static int choose_wk(const DeviceWeights& w, Epilogue epi, int nt, const GemvTuning& tune, int* ksplit)
 {
     int forced = tune.wk;
     const int ctas_per_sm = nt <= 2 ? 2 : 1;
     const size_t slots = (size_t)tune.sm_count * ctas_per_sm;
     const size_t tiles = epi == kEpiSwiglu ? w.rows / 2 / 16 * 2 : w.row_tiles();
-    int best = 1;
+    int best = 1, best_split = 1;
     double best_cost = 1e30;
     for (int wk = 1; wk <= 8; wk *= 2) {
         if ((size_t)wk > w.nblk && wk > 1) break;
         if (epi == kEpiSwiglu && wk > 4) break;
-        if (forced == wk) return wk;
-        const size_t ctas = (tiles + (size_t)(8 / wk) - 1) / (size_t)(8 / wk);
-        const size_t waves = (ctas + slots - 1) / slots;
-        const double cost = (double)waves * ((double)((w.nblk + wk - 1) / wk) + 4.0);
-        if (cost < best_cost - 1e-9) {
-            best_cost = cost;
-            best = wk;
+        if (forced > 0 && forced != wk) continue;
+        const size_t ctas1 = (tiles + (size_t)(8 / wk) - 1) / (size_t)(8 / wk);
+        // K cut across CTAs as well (plain and pushed stores only): more, shorter CTAs even out the last wave when the
+        // row tiles alone leave it part empty; every cut costs a partial-sum round trip at the end
+        const int max_split = epi == kEpiSwiglu ? 1 : 12;
+        for (int sp = 1; sp <= max_split; sp++) {
+            if (tune.split >= 1 && sp != tune.split) continue;
+            if (tune.split < 0 && sp > 1) break;   // cuts are chosen from the shape only once measured; until then forced only
+            if (sp > 1 && (size_t)(wk * sp) > w.nblk) break;
+            const size_t ctas = ctas1 * (size_t)sp;
+            const size_t waves = (ctas + slots - 1) / slots;
+            const size_t per = (w.nblk + (size_t)(wk * sp) - 1) / (size_t)(wk * sp);
+            const double cost = (double)waves * ((double)per + 4.0) + (sp > 1 ? 2.0 : 0.0);
+            if (cost < best_cost - 1e-9) {
+                best_cost = cost;
+                best = wk;
+                best_split = sp;
+            }
         }
     }
+    *ksplit = best_split;
     return best;
 }
 
 template <int NT, int EPI>
 static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint2* frag, size_t m, float* y,
-                          size_t ldy, int wk, unsigned passes, bool pdl, const PushDst& push)
+                          size_t ldy, int wk, int ksplit, unsigned passes, bool pdl, const PushDst& push, const SplitWs& split)
 {
     const int row_tiles = (int)w.row_tiles(), wr = 8 / wk;
     const int ff_tiles = (int)(w.rows / 2 / 16);
     unsigned gx = EPI != kEpiSwiglu ? (unsigned)((row_tiles + wr - 1) / wr) : (unsigned)((ff_tiles + wr / 2 - 1) / (wr / 2));
-    dim3 grid(gx, passes);
+    // a K split across CTAs needs its partial sums and tickets to fit the context's workspace
+    if (EPI == kEpiSwiglu || !split.partial || (size_t)ksplit * m * w.rows > kSplitWsFloats || (size_t)gx * passes > kSplitTickets)
+        ksplit = 1;
+    dim3 grid(gx, passes, (unsigned)ksplit);
     // opt in to > 48 KB of dynamic shared memory once per kernel instantiation and device
     static thread_local int attr_dev_q4 = -1, attr_dev_q6 = -1;
     int dev = 0;
@@ -1005,7 +1116,7 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
             attr_dev_q4 = dev;
         }
         launch_kernel(gemv_q4k_kernel<NT, EPI>, grid, dim3(256), kSmemQ4K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push, split);
     } else if (ty == kGgmlQ5K) {
         static thread_local int attr_dev_q5 = -1;
         if (attr_dev_q5 != dev) {
@@ -1013,14 +1124,14 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
             attr_dev_q5 = dev;
         }
         launch_kernel(gemv_q4k_kernel<NT, EPI, true>, grid, dim3(256), kSmemQ5K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push, split);
     } else {
         if (attr_dev_q6 != dev) {
             cudaFuncSetAttribute(gemv_q6k_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ6K);
             attr_dev_q6 = dev;
         }
         launch_kernel(gemv_q6k_kernel<NT, EPI>, grid, dim3(256), kSmemQ6K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push, split);
     }
 }
 
@@ -1028,13 +1139,15 @@ int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
                     size_t ldy, Epilogue epi, const GemvTuning& tune, const PushDst& push)
 {
     if (m == 0 || w.rows == 0) return kOk;
-    const int nt = tiles_per_pass(m), wk = choose_wk(w, epi, nt, tune);
+    const int nt = tiles_per_pass(m);
+    int ksplit = 1;
+    const int wk = choose_wk(w, epi, nt, tune, &ksplit);
     const unsigned passes = (unsigned)(padded_tiles(m) / (size_t)nt);
     const uint2* f = reinterpret_cast<const uint2*>(frag);
 #define FERRIC_GEMV_CASE(NT_)                                                                             \
-    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push);           \
-    else if (epi == kEpiPush) launch_gemv_t<NT_, kEpiPush>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push);        \
-    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push)
+    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, ksplit, passes, tune.pdl, push, tune.split_ws);   \
+    else if (epi == kEpiPush) launch_gemv_t<NT_, kEpiPush>(st, ty, w, f, m, y, ldy, wk, ksplit, passes, tune.pdl, push, tune.split_ws); \
+    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, 1, passes, tune.pdl, push, tune.split_ws)
     if (nt == 1) { FERRIC_GEMV_CASE(1); }
     else if (nt == 2) { FERRIC_GEMV_CASE(2); }
     else { FERRIC_GEMV_CASE(4); }

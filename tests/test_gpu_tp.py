@@ -47,16 +47,20 @@ def test_two_gpu_stack_matches_unsharded_oracle(tmp_path):
     assert np.array_equal(got["push"], got["fused"])               # same partials, same rank-order sum
 
 
+@pytest.mark.parametrize("cluster", [0, 2, 4, 8])
 @pytest.mark.parametrize("m", [1, 2, 5, 8])
-def test_pushed_exchange_with_one_rank(m):
+def test_pushed_exchange_with_one_rank(m, cluster, monkeypatch):
     """A group of one rank pushes to itself: matmul_push + the pushed add+norm+prepare must equal the plain matmul
     followed by add+norm+prepare bit for bit, for both kinds, with one kind used several times running (the parity
-    double-buffer) and with both formats of the row-parallel products."""
+    double-buffer) and with both formats of the row-parallel products.  `cluster`: CTAs sharing one consumer tile
+    (0 = the library's choice, which is one CTA for a single rank)."""
     import ferric_b200 as F
     from ferric_b200 import synth
 
+    if cluster:
+        monkeypatch.setenv("FERRIC_CUDA_PUSH_CLUSTER", str(cluster))
     ctx = F.Context(0)
-    hid, kshard = 1024, 768
+    hid, kshard = 1536, 768
     grp = F.TPGroup(ctx, 0, 1, m, hid)
     grp.connect([grp.export()])
     nxt = F.QMatrix.from_bytes(ctx, synth.matrix(12, 64, hid, seed=1), 12, 64, hid)
@@ -75,6 +79,7 @@ def test_pushed_exchange_with_one_rank(m):
             grp.add_rmsnorm_prepare(kind, nxt, a, wn, 1e-6, sum_out=s2, norm_out=n2, pushed=True)
             y2 = nxt.matmul_prepared(mm)
             grp.check()
+            # the cluster adds the per-super-block sums of squares in the order one CTA does: the same bits
             assert torch.equal(s1, s2) and torch.equal(n1, n2) and torch.equal(y1, y2)
         w.close()
     with pytest.raises(F.FerricError):
