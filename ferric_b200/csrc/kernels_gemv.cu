@@ -51,7 +51,8 @@ __device__ __forceinline__ void imma_16816_s8s8(int (&d)[4], uint32_t a0, uint32
 // ------------------------------------------------------------------------------------------
 constexpr int kPrepWarps = 4;
 constexpr int kNormPrepMaxWarps = 32;
-constexpr int kNormPrepPushWarps = 20;   // the pushed-exchange variant holds every rank's values in registers while it polls
+constexpr int kNormPrepPushWarps = 16;   // the pushed-exchange variant holds every rank's values in registers while it polls
+constexpr int kNormPrepWideWarps = 8;    // ... and with more than two ranks it needs still more registers per thread
 
 // Per-warp staging.  16-byte aligned (and so padded to a multiple of 16 bytes): the limb rows are
 // written with 128-bit stores, and the struct is used in arrays indexed by warp.
@@ -200,40 +201,51 @@ __device__ __forceinline__ float4 peer_sum4(const PeerSum& p, size_t off)
     return s;
 }
 
-// Pushed exchange, consumer side: the four values at pair offset `off` of every rank's slice, each polled (bounded)
-// until its stamp is `want`, summed in rank order.  All loads of a round are issued before the first check.
-__device__ __forceinline__ float4 pushed_sum4(const PushSrc& p, const uint2* base, size_t off, unsigned want, int limit)
+// Pushed exchange, consumer side: R runs of four values starting at pair offset `off` of every rank's slice, each value
+// polled (bounded) until its stamp is `want`, summed in rank order.  All loads of a round are issued before the first
+// check, so a round costs one trip to L2 however many ranks and runs it covers; WMAX (the largest world size this
+// instantiation serves) and R are traded against each other to keep the values in flight in registers.
+template <int R, int WMAX>
+__device__ __forceinline__ void pushed_sum(const PushSrc& p, const uint2* base, size_t off, unsigned want, int limit, float4* out)
 {
-    uint4 a[kMaxRanks], b[kMaxRanks];
+    uint4 a[WMAX][R], b[WMAX][R];
     int spins = 0;
     for (;;) {
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; r++) {
+        for (int r = 0; r < WMAX; r++) {
             if (r < p.world) {
-                const uint2* src = base + (size_t)r * p.elems + off;
-                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a[r].x), "=r"(a[r].y), "=r"(a[r].z), "=r"(a[r].w) : "l"(src));
-                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b[r].x), "=r"(b[r].y), "=r"(b[r].z), "=r"(b[r].w) : "l"(src + 2));
+#pragma unroll
+                for (int j = 0; j < R; j++) {
+                    const uint2* src = base + (size_t)r * p.elems + off + 4 * j;
+                    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a[r][j].x), "=r"(a[r][j].y), "=r"(a[r][j].z), "=r"(a[r][j].w) : "l"(src));
+                    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b[r][j].x), "=r"(b[r][j].y), "=r"(b[r][j].z), "=r"(b[r][j].w) : "l"(src + 2));
+                }
             }
         }
         bool ok = true;
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; r++)
-            if (r < p.world) ok = ok && a[r].y == want && a[r].w == want && b[r].y == want && b[r].w == want;
+        for (int r = 0; r < WMAX; r++)
+            if (r < p.world)
+#pragma unroll
+                for (int j = 0; j < R; j++) ok = ok && a[r][j].y == want && a[r][j].w == want && b[r][j].y == want && b[r][j].w == want;
         if (ok) break;
         if (++spins > limit) {
             *p.status = 1;
             break;
         }
     }
-    float4 s = make_float4(__uint_as_float(a[0].x), __uint_as_float(a[0].z), __uint_as_float(b[0].x), __uint_as_float(b[0].z));
 #pragma unroll
-    for (int r = 1; r < kMaxRanks; r++) {
-        if (r < p.world) {
-            s.x += __uint_as_float(a[r].x); s.y += __uint_as_float(a[r].z);
-            s.z += __uint_as_float(b[r].x); s.w += __uint_as_float(b[r].z);
+    for (int j = 0; j < R; j++) {
+        float4 s = make_float4(__uint_as_float(a[0][j].x), __uint_as_float(a[0][j].z), __uint_as_float(b[0][j].x), __uint_as_float(b[0][j].z));
+#pragma unroll
+        for (int r = 1; r < WMAX; r++) {
+            if (r < p.world) {
+                s.x += __uint_as_float(a[r][j].x); s.y += __uint_as_float(a[r][j].z);
+                s.z += __uint_as_float(b[r][j].x); s.w += __uint_as_float(b[r][j].z);
+            }
         }
+        out[j] = s;
     }
-    return s;
 }
 
 // Publish this rank's next exchange count to every peer (one thread per peer).
@@ -291,8 +303,11 @@ __device__ __forceinline__ float cl_load_f32(const float* own_smem, unsigned ran
 
 // PEERS: 0 no exchange, 1 partial sums pulled from the peers' memory after their signal, 2 partial sums the peers
 // pushed into this rank's memory.
-template <int TY, int PEERS>
-__global__ void __launch_bounds__(PEERS == 2 ? 32 * kNormPrepPushWarps : 32 * kNormPrepMaxWarps)
+// WMAX (pushed form only): the largest world size the instantiation serves; up to 2 ranks CTAs of up to 16 warps
+// polls all 16 of a lane's values in one round, above that CTAs of up to 8 warps (the tile is spread over a cluster)
+// poll 8 values per round.
+template <int TY, int PEERS, int WMAX>
+__global__ void __launch_bounds__(PEERS == 2 ? (WMAX <= 2 ? 32 * kNormPrepPushWarps : 32 * kNormPrepWideWarps) : 32 * kNormPrepMaxWarps)
 norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wgt, float eps,
                  size_t m, size_t d, size_t nblk, float* __restrict__ sum, float* __restrict__ norm,
                  uint2* __restrict__ frag, PeerSum peers, PushSrc pushed)
@@ -344,6 +359,12 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
     for (size_t blk = blk_first; blk < nblk; blk += blk_step) {
         if (valid) {
             const size_t off = batch * d + blk * 256 + 16 * q;
+            float4 gp[4];
+            if (PEERS == 2) {
+                constexpr int R = WMAX <= 2 ? 4 : 2;
+#pragma unroll
+                for (int i0 = 0; i0 < 4; i0 += R) pushed_sum<R, (WMAX > 0 ? WMAX : 1)>(pushed, recv, off + 4 * i0, want, wait_limit, gp + i0);
+            }
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 float4 f = ld_act(reinterpret_cast<const float4*>(a + off) + i);
@@ -356,8 +377,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
                     f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
                 }
                 if (PEERS == 2) {
-                    const float4 g = pushed_sum4(pushed, recv, off + 4 * i, want, wait_limit);
-                    f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
+                    f.x += gp[i].x; f.y += gp[i].y; f.z += gp[i].z; f.w += gp[i].w;
                 }
                 if (sum) reinterpret_cast<float4*>(sum + off)[i] = f;
                 ms = fmaf(f.x, f.x, ms); ms = fmaf(f.y, f.y, ms); ms = fmaf(f.z, f.z, ms); ms = fmaf(f.w, f.w, ms);
@@ -464,11 +484,11 @@ int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
 {
     size_t ntiles = padded_tiles(m);
     if (ntiles == 0 || w.nblk == 0) return kOk;
-    const int mode = pushed.world > 0 ? 2 : peers.world > 0 ? 1 : 0;
-    const int max_warps = mode == 2 ? kNormPrepPushWarps : kNormPrepMaxWarps;
+    const int mode = pushed.world > 2 ? 3 : pushed.world > 0 ? 2 : peers.world > 0 ? 1 : 0;
+    const int max_warps = mode == 3 ? kNormPrepWideWarps : mode == 2 ? kNormPrepPushWarps : kNormPrepMaxWarps;
     unsigned cluster = 1;
-    if (mode == 2) {
-        int c = tune.push_cluster > 0 ? tune.push_cluster : (pushed.world >= 4 ? 4 : 1);
+    if (mode >= 2) {
+        int c = tune.push_cluster > 0 ? tune.push_cluster : (pushed.world > 2 ? 4 : w.nblk > (size_t)kNormPrepPushWarps ? 2 : 1);
         while (c > 1 && ((c & (c - 1)) || c > 8 || (size_t)c > w.nblk)) c--;   // a power of two up to 8, at most one CTA per super-block
         cluster = (unsigned)c;
     }
@@ -480,16 +500,18 @@ int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
     using Kernel = void (*)(const float*, const float*, const float*, float, size_t, size_t, size_t, float*, float*, uint2*,
                             PeerSum, PushSrc);
     // the variant without an exchange carries none of the peer-pointer code
-    static const Kernel table[2][3] = {
-        {norm_prep_kernel<(int)kGgmlQ4K, 0>, norm_prep_kernel<(int)kGgmlQ4K, 1>, norm_prep_kernel<(int)kGgmlQ4K, 2>},
-        {norm_prep_kernel<(int)kGgmlQ6K, 0>, norm_prep_kernel<(int)kGgmlQ6K, 1>, norm_prep_kernel<(int)kGgmlQ6K, 2>}};
+    static const Kernel table[2][4] = {
+        {norm_prep_kernel<(int)kGgmlQ4K, 0, 0>, norm_prep_kernel<(int)kGgmlQ4K, 1, 0>, norm_prep_kernel<(int)kGgmlQ4K, 2, 2>,
+         norm_prep_kernel<(int)kGgmlQ4K, 2, kMaxRanks>},
+        {norm_prep_kernel<(int)kGgmlQ6K, 0, 0>, norm_prep_kernel<(int)kGgmlQ6K, 1, 0>, norm_prep_kernel<(int)kGgmlQ6K, 2, 2>,
+         norm_prep_kernel<(int)kGgmlQ6K, 2, kMaxRanks>}};
     static thread_local int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     const int max_smem = (int)(kNormPrepMaxWarps * sizeof(PrepSmem));
     if (attr_dev != dev) {
         for (int i = 0; i < 2; i++)
-            for (int j = 0; j < 3; j++) cudaFuncSetAttribute(table[i][j], cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+            for (int j = 0; j < 4; j++) cudaFuncSetAttribute(table[i][j], cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
         attr_dev = dev;
     }
     Kernel kernel = table[(ty == kGgmlQ4K || ty == kGgmlQ5K) ? 0 : 1][mode];
@@ -1060,7 +1082,7 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
 // in as few waves of resident CTAs as possible -- every wave pays its own pipeline fill and
 // drain -- and within that, K-splitting shortens each warp's serial walk.  Cost model: waves x
 // (super-blocks per warp + a fixed fill/drain term), measured in super-block times.
-static int choose_wk(const DeviceWeights& w, Epilogue epi, int nt, const GemvTuning& tune, int* ksplit)
+static int choose_wk(uint32_t ty, const DeviceWeights& w, Epilogue epi, int nt, const GemvTuning& tune, int* ksplit)
 {
     int forced = tune.wk;
     const int ctas_per_sm = nt <= 2 ? 2 : 1;
@@ -1081,9 +1103,9 @@ static int choose_wk(const DeviceWeights& w, Epilogue epi, int nt, const GemvTun
             if (tune.split < 0 && sp > 1) break;   // cuts are chosen from the shape only once measured; until then forced only
             if (sp > 1 && (size_t)(wk * sp) > w.nblk) break;
             const size_t ctas = ctas1 * (size_t)sp;
-            const size_t waves = (ctas + slots - 1) / slots;
+            const double waves = (double)((ctas + slots - 1) / slots);
             const size_t per = (w.nblk + (size_t)(wk * sp) - 1) / (size_t)(wk * sp);
-            const double cost = (double)waves * ((double)per + 4.0) + (sp > 1 ? 2.0 : 0.0);
+            const double cost = waves * ((double)per + 4.0) + (sp > 1 ? 2.0 : 0.0);
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
                 best = wk;
@@ -1141,7 +1163,7 @@ int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
     if (m == 0 || w.rows == 0) return kOk;
     const int nt = tiles_per_pass(m);
     int ksplit = 1;
-    const int wk = choose_wk(w, epi, nt, tune, &ksplit);
+    const int wk = choose_wk(ty, w, epi, nt, tune, &ksplit);
     const unsigned passes = (unsigned)(padded_tiles(m) / (size_t)nt);
     const uint2* f = reinterpret_cast<const uint2*>(frag);
 #define FERRIC_GEMV_CASE(NT_)                                                                             \

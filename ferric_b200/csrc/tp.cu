@@ -48,6 +48,7 @@ struct ferric_tp_group {
     uint2* recv = nullptr;            // [kind][parity][world][elems] (value, exchange number) pairs
     void* peer_base[kMaxRanks] = {};  // IPC mappings of the peers' `local`
     bool connected = false;
+    bool local_peers = false;         // peers are groups of this process (no IPC mappings to close)
 };
 
 namespace {
@@ -136,6 +137,47 @@ int32_t ferric_cuda_tp_connect(ferric_tp_group* g, const uint8_t* handles)
         FERRIC_CUDA_TRY(cudaIpcOpenMemHandle(&g->peer_base[r], h, cudaIpcMemLazyEnablePeerAccess));
     }
     // where this rank announces itself: slot [kind][rank] of every rank's flag array
+    unsigned* slots[2][kMaxRanks] = {};
+    for (int k = 0; k < 2; k++)
+        for (int r = 0; r < g->world; r++)
+            slots[k][r] = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(g->peer_base[r]) + off_flags(g->elems)) +
+                          k * kMaxRanks + g->rank;
+    FERRIC_CUDA_TRY(cudaMemcpy(g->slot_table[0], slots, sizeof(slots), cudaMemcpyHostToDevice));
+    g->connected = true;
+    return kOk;
+}
+
+int32_t ferric_cuda_tp_connect_local(ferric_tp_group* g, ferric_tp_group* const* groups)
+{
+    if (!g || !groups) {
+        set_last_error("NULL group or group table");
+        return kErrInvalidArg;
+    }
+    if (g->connected) return kOk;
+    for (int r = 0; r < g->world; r++) {
+        const ferric_tp_group* o = groups[r];
+        if (!o || o->world != g->world || o->rank != r || o->elems != g->elems || (r == g->rank && o != g)) {
+            set_last_error("tp_connect_local: entry %d is not rank %d of a group of the same shape", r, r);
+            return kErrInvalidArg;
+        }
+    }
+    DeviceGuard guard(g->device);
+    for (int r = 0; r < g->world; r++) {
+        if (r == g->rank) continue;
+        if (groups[r]->device != g->device) {
+            int can = 0;
+            FERRIC_CUDA_TRY(cudaDeviceCanAccessPeer(&can, g->device, groups[r]->device));
+            if (!can) {
+                set_last_error("device %d cannot address device %d", g->device, groups[r]->device);
+                return kErrCuda;
+            }
+            cudaError_t e = cudaDeviceEnablePeerAccess(groups[r]->device, 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return cuda_fail(e, "cudaDeviceEnablePeerAccess");
+            cudaGetLastError();
+        }
+        g->peer_base[r] = groups[r]->local;
+    }
+    g->local_peers = true;
     unsigned* slots[2][kMaxRanks] = {};
     for (int k = 0; k < 2; k++)
         for (int r = 0; r < g->world; r++)
@@ -279,7 +321,7 @@ void ferric_cuda_tp_free(ferric_tp_group* g)
     DeviceGuard guard(g->device);
     cudaDeviceSynchronize();
     for (int r = 0; r < g->world; r++)
-        if (r != g->rank && g->peer_base[r]) cudaIpcCloseMemHandle(g->peer_base[r]);
+        if (r != g->rank && g->peer_base[r] && !g->local_peers) cudaIpcCloseMemHandle(g->peer_base[r]);
     cudaFree(g->local);
     delete g;
 }

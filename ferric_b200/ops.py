@@ -361,6 +361,13 @@ class TPGroup:
         assert len(blob) == 64 * self.world
         _check(self._lib.ferric_cuda_tp_connect(self._h, blob), "tp_connect")
 
+    @staticmethod
+    def connect_local(groups) -> None:
+        """Connect groups that all live in this process (rank order, one per rank)."""
+        table = (C.c_void_p * len(groups))(*[g._h.value for g in groups])
+        for g in groups:
+            _check(g._lib.ferric_cuda_tp_connect_local(g._h, table), "tp_connect_local")
+
     def connect_with_torch_distributed(self) -> None:
         import torch.distributed as dist
         handles = [None] * self.world

@@ -323,6 +323,9 @@ int32_t ferric_cuda_tp_create(ferric_cuda_ctx *ctx, int32_t rank, int32_t world,
 int32_t ferric_cuda_tp_export(ferric_tp_group *g, uint8_t *handle64);
 /* Map the peers' exchange memory: `handles` holds world x 64 bytes in rank order. */
 int32_t ferric_cuda_tp_connect(ferric_tp_group *g, const uint8_t *handles);
+/* The same for ranks that live in this process (one thread or one loop driving several GPUs): `groups` holds the
+ * `world` groups in rank order, this one included; peer access between their devices is switched on as needed. */
+int32_t ferric_cuda_tp_connect_local(ferric_tp_group *g, ferric_tp_group *const *groups);
 /* Device address of this rank's exchange buffer `kind`: pass it as y_dev of the row-parallel matmul. */
 void *ferric_cuda_tp_partial(ferric_tp_group *g, int32_t kind);
 /* Announce to all peers that exchange buffer `kind` holds this rank's next partial (stream-ordered). */

@@ -87,3 +87,45 @@ def test_pushed_exchange_with_one_rank(m, cluster, monkeypatch):
     nxt.close()
     grp.close()
     ctx.close()
+
+
+@pytest.mark.parametrize("world,m", [(2, 1), (3, 2), (4, 1), (8, 1), (8, 4)])
+def test_pushed_exchange_many_ranks_in_one_process(world, m):
+    """`world` ranks as groups of this process on one GPU (connected by address, not by IPC handle).  All ranks push,
+    the device is synchronised, then all ranks consume: no kernel ever waits for one that has not run.  Every rank
+    must form the same sum -- the partial products added in rank order -- and the same norm, bit for bit, twice over
+    (both parities of the receive regions)."""
+    import ferric_b200 as F
+    from ferric_b200 import synth
+
+    hid, kshard = 2048, 256
+    ctxs = [F.Context(0) for _ in range(world)]
+    grps = [F.TPGroup(ctxs[r], r, world, m, hid) for r in range(world)]
+    F.TPGroup.connect_local(grps)
+    ws = [F.QMatrix.from_bytes(ctxs[r], synth.matrix(12 if r % 2 == 0 else 14, hid, kshard, seed=r), 12 if r % 2 == 0 else 14, hid, kshard)
+          for r in range(world)]
+    nxt = [F.QMatrix.from_bytes(ctxs[r], synth.matrix(12, 64, hid, seed=99), 12, 64, hid) for r in range(world)]
+    rng = np.random.default_rng(world * 10 + m)
+    wn = torch.from_numpy(rng.uniform(0.5, 1.5, hid).astype(np.float32)).cuda()
+    for it in range(3):
+        kind = it & 1 if it < 2 else 1
+        xs = [torch.from_numpy(synth.activations(m, kshard, seed=100 * it + r)).cuda() for r in range(world)]
+        a = torch.from_numpy(rng.standard_normal((m, hid)).astype(np.float32)).cuda()
+        total = ws[0].matmul(xs[0]).clone()
+        for r in range(1, world):
+            total += ws[r].matmul(xs[r])
+        s_ref, n_ref = torch.empty_like(a), torch.empty_like(a)
+        mm = nxt[0].add_rmsnorm_prepare(a, total, wn, 1e-6, sum_out=s_ref, norm_out=n_ref)
+        y_ref = nxt[0].matmul_prepared(mm).clone()
+        torch.cuda.synchronize()
+        for r in range(world):
+            grps[r].matmul_push(kind, ws[r], xs[r])
+        torch.cuda.synchronize()
+        for r in range(world):
+            s, n = torch.empty_like(a), torch.empty_like(a)
+            grps[r].add_rmsnorm_prepare(kind, nxt[r], a, wn, 1e-6, sum_out=s, norm_out=n, pushed=True)
+            y = nxt[r].matmul_prepared(mm)
+            grps[r].check()
+            assert torch.equal(s, s_ref) and torch.equal(n, n_ref) and torch.equal(y, y_ref), (it, r)
+    for o in ws + nxt + grps + ctxs:
+        o.close()
