@@ -53,7 +53,7 @@ def parse_args():
     ap.add_argument("--prefill-type", type=int, default=12, choices=[12, 14, 8], help="ggml type of the --prefill matrix")
     ap.add_argument("--allreduce", default="auto", choices=["auto", "push", "fused", "nccl"],
                     help="N > 1: the library's own exchange over peer memory (push: the products store into every rank's memory; "
-                         "fused: signalled buffers read by the peers), NCCL through torch.distributed, or (default) push up to batch 8")
+                         "fused: signalled buffers read by the peers), NCCL through torch.distributed, or (default) push for small batches")
     return ap.parse_args()
 
 
@@ -215,10 +215,11 @@ def run_ours(args):
     plan = TPPlan.make(world, rank, HIDDEN, N_FF, Q_OUT, KV_OUT)
     def exchange_for(batch):
         """(all_reduce callable, exchange group, name) for a batch size.  `auto`: the library's own pushed exchange
-        while the GEMV serves the batch (up to 8 rows of 20 KB per rank), NCCL above that."""
+        up to batch 4 (up to batch 8 from 4 GPUs on: measured 1306 against 1027 tokens/s at 8 GPUs, but 904 against 957
+        at 2), NCCL above that."""
         if world == 1:
             return None, None, "none"
-        kind = args.allreduce if args.allreduce != "auto" else ("push" if batch <= 8 else "nccl")
+        kind = args.allreduce if args.allreduce != "auto" else ("push" if batch <= (8 if world >= 4 else 4) else "nccl")
         if kind == "nccl":
             return (lambda t: dist.all_reduce(t)), None, kind
         grp = TPGroup(ctx, rank, world, batch, HIDDEN)

@@ -67,6 +67,8 @@ struct GemvTuning {
     int sm_count = 148;
     int push_cluster = 0;   // CTAs (a cluster) sharing one tile of the pushed exchange's consumer: 1, 2, 4 or 8; 0 = from the world size
     int split = -1;         // CTAs along K per row-tile group of the GEMV (FERRIC_CUDA_GEMV_KSPLIT); -1 = choose from the shape
+    bool stream = false;    // Q6_K plain / pushed GEMV in its unit-balanced form (FERRIC_CUDA_GEMV_STREAM=1; measured no faster)
+    int stream_ctas = 0;    // its grid; 0 = one CTA per resident slot (FERRIC_CUDA_GEMV_STREAM_CTAS, for tests on small matrices)
     SplitWs split_ws;       // the context's workspace for that (not a tunable: it rides here to reach the launchers)
     bool pdl = true;   // programmatic dependent launch between consecutive kernels (FERRIC_CUDA_PDL=0 disables)
 };

@@ -926,6 +926,66 @@ __device__ __forceinline__ int sc_byte(const uint4& v, int i)
     return (int)d;
 }
 
+// One unit (16 rows x one super-block) times the prepared activation fragments of NT tiles: integer sub-block sums
+// scaled by the int8 sub-block scales, the -32 offset taken off through the fragments' sub-block sums, then d and the
+// activation block scale in f32.
+template <int NT>
+__device__ __forceinline__ void q6k_unit_mac(const Q6KUnit& cur, const uint2 (&bf)[NT][kQ6KSteps], float (&acc)[NT][4], int t)
+{
+    const int zero[4] = {0, 0, 0, 0};
+    int ai[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) ai[nt][i] = 0;
+
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            // double step 4h + k: sub-blocks sb = 8h + 2k + is, is = 0 (.x) and 1 (.y)
+#pragma unroll
+            for (int is = 0; is < 2; is++) {
+                const int wi = 2 * h + is, sb = 8 * h + 2 * k + is;
+                // 6-bit weights of rows g and g+8: low nibble source word, high-bit source word
+                const uint32_t lg = u4_word(cur.ql[k & 1], wi), lh = u4_word(cur.ql[2 + (k & 1)], wi);
+                const uint32_t hg = u4_word(cur.qh[0], wi), hh = u4_word(cur.qh[1], wi);
+                const uint32_t lo_g = ((k & 2) ? (lg >> 4) : lg) & 0x0f0f0f0fu;
+                const uint32_t lo_h = ((k & 2) ? (lh >> 4) : lh) & 0x0f0f0f0fu;
+                const uint32_t hi_g = (k == 0 ? (hg << 4) : k == 1 ? (hg << 2) : k == 2 ? hg : (hg >> 2)) & 0x30303030u;
+                const uint32_t hi_h = (k == 0 ? (hh << 4) : k == 1 ? (hh << 2) : k == 2 ? hh : (hh >> 2)) & 0x30303030u;
+                const uint32_t a0 = lo_g | hi_g, a1 = lo_h | hi_h;
+                const int scg = sc_byte(cur.scg, sb), sch = sc_byte(cur.sch, sb);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    int c[4];
+                    imma_16816_u8s8(c, a0, a1, is ? bf[nt][4 * h + k].y : bf[nt][4 * h + k].x, zero);
+                    ai[nt][0] += scg * c[0];
+                    ai[nt][1] += scg * c[1];
+                    ai[nt][2] += sch * c[2];
+                    ai[nt][3] += sch * c[3];
+                }
+            }
+        }
+    }
+    // the -32 offset: sum_sb sc[sb] * (limb sum of sub-block sb); k slot 4t+i <-> sub-block 4t+i
+    const uint32_t sg = u4_word(cur.scg, t), sh = u4_word(cur.sch, t);
+    const float dg = __half2float(__ushort_as_half((unsigned short)(cur.dpair & 0xffffu)));
+    const float dh = __half2float(__ushort_as_half((unsigned short)(cur.dpair >> 16)));
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        int c0[4], c1[4];
+        imma_16816_s8s8(c0, sg, sh, bf[nt][8].x, zero);
+        imma_16816_s8s8(c1, sg, sh, bf[nt][8].y, zero);
+        const float up = __uint_as_float(bf[nt][9].x);
+        const float fg = dg * up, fh = dh * up;
+        acc[nt][0] = fmaf(fg, (float)(ai[nt][0] - 32 * (c0[0] + 128 * c1[0])), acc[nt][0]);
+        acc[nt][1] = fmaf(fg, (float)(ai[nt][1] - 32 * (c0[1] + 128 * c1[1])), acc[nt][1]);
+        acc[nt][2] = fmaf(fh, (float)(ai[nt][2] - 32 * (c0[2] + 128 * c1[2])), acc[nt][2]);
+        acc[nt][3] = fmaf(fh, (float)(ai[nt][3] - 32 * (c0[3] + 128 * c1[3])), acc[nt][3]);
+    }
+}
+
 template <int NT, int EPI>
 __global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
@@ -1013,57 +1073,7 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             rstage = rstage + 1 == kStagesQ6K ? 0 : rstage + 1;
             __syncwarp();
 
-            int ai[NT][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) ai[nt][i] = 0;
-
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    // double step 4h + k: sub-blocks sb = 8h + 2k + is, is = 0 (.x) and 1 (.y)
-#pragma unroll
-                    for (int is = 0; is < 2; is++) {
-                        const int wi = 2 * h + is, sb = 8 * h + 2 * k + is;
-                        // 6-bit weights of rows g and g+8: low nibble source word, high-bit source word
-                        const uint32_t lg = u4_word(cur.ql[k & 1], wi), lh = u4_word(cur.ql[2 + (k & 1)], wi);
-                        const uint32_t hg = u4_word(cur.qh[0], wi), hh = u4_word(cur.qh[1], wi);
-                        const uint32_t lo_g = ((k & 2) ? (lg >> 4) : lg) & 0x0f0f0f0fu;
-                        const uint32_t lo_h = ((k & 2) ? (lh >> 4) : lh) & 0x0f0f0f0fu;
-                        const uint32_t hi_g = (k == 0 ? (hg << 4) : k == 1 ? (hg << 2) : k == 2 ? hg : (hg >> 2)) & 0x30303030u;
-                        const uint32_t hi_h = (k == 0 ? (hh << 4) : k == 1 ? (hh << 2) : k == 2 ? hh : (hh >> 2)) & 0x30303030u;
-                        const uint32_t a0 = lo_g | hi_g, a1 = lo_h | hi_h;
-                        const int scg = sc_byte(cur.scg, sb), sch = sc_byte(cur.sch, sb);
-#pragma unroll
-                        for (int nt = 0; nt < NT; nt++) {
-                            int c[4];
-                            imma_16816_u8s8(c, a0, a1, is ? bf[nt][4 * h + k].y : bf[nt][4 * h + k].x, zero);
-                            ai[nt][0] += scg * c[0];
-                            ai[nt][1] += scg * c[1];
-                            ai[nt][2] += sch * c[2];
-                            ai[nt][3] += sch * c[3];
-                        }
-                    }
-                }
-            }
-            // the -32 offset: sum_sb sc[sb] * (limb sum of sub-block sb); k slot 4t+i <-> sub-block 4t+i
-            const uint32_t sg = u4_word(cur.scg, t), sh = u4_word(cur.sch, t);
-            const float dg = __half2float(__ushort_as_half((unsigned short)(cur.dpair & 0xffffu)));
-            const float dh = __half2float(__ushort_as_half((unsigned short)(cur.dpair >> 16)));
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                int c0[4], c1[4];
-                imma_16816_s8s8(c0, sg, sh, bf[nt][8].x, zero);
-                imma_16816_s8s8(c1, sg, sh, bf[nt][8].y, zero);
-                const float up = __uint_as_float(bf[nt][9].x);
-                const float fg = dg * up, fh = dh * up;
-                acc[nt][0] = fmaf(fg, (float)(ai[nt][0] - 32 * (c0[0] + 128 * c1[0])), acc[nt][0]);
-                acc[nt][1] = fmaf(fg, (float)(ai[nt][1] - 32 * (c0[1] + 128 * c1[1])), acc[nt][1]);
-                acc[nt][2] = fmaf(fh, (float)(ai[nt][2] - 32 * (c0[2] + 128 * c1[2])), acc[nt][2]);
-                acc[nt][3] = fmaf(fh, (float)(ai[nt][3] - 32 * (c0[3] + 128 * c1[3])), acc[nt][3]);
-            }
+            q6k_unit_mac<NT>(cur, bf, acc, t);
             if (kAhead) {
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++)
@@ -1073,6 +1083,180 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
         }
     }
     reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push, split);
+}
+
+// ------------------------------------------------------------------------------------------
+// Q6_K, unit-balanced: the matrix's units (row tile major, super-block minor -- the order they lie in memory) are
+// dealt out evenly to all resident warps, so a warp streams one contiguous byte range whatever the shape, and the
+// machine is equally loaded even when the row tiles do not fill a whole number of waves.  A warp's range may start
+// and end inside a row tile; such partial sums go to the workspace and the last warp to arrive at a tile (a ticket
+// per tile) adds the tile's pieces in warp order -- a fixed order, so results do not depend on timing.
+// Off by default (FERRIC_CUDA_GEMV_STREAM=1 turns it on): on the 5120 x 17408 down projection it measured the same
+// 22 us as the row-tile form, whose 320 CTAs leave a part-filled second wave -- the kernel is bound by instruction
+// issue (about 360 instructions per unit, issue slots half used), not by how evenly the units are dealt.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned stream_first_unit(unsigned long long units, unsigned w, unsigned warps)
+{
+    return (unsigned)(units * w / warps);
+}
+__device__ __forceinline__ unsigned stream_warp_of(unsigned long long units, unsigned unit, unsigned warps)
+{
+    return (unsigned)((((unsigned long long)unit + 1) * warps - 1) / units);   // the largest w with first_unit(w) <= unit
+}
+
+template <int NT, int EPI>
+__global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
+gemv_q6k_stream_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
+                       int nblk, int m, size_t ldy, int row_tiles, PushDst push, SplitWs split)
+{
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const unsigned warps = gridDim.x * 8, w = blockIdx.x * 8 + warp;
+    const unsigned long long total = (unsigned long long)row_tiles * nblk;
+    const unsigned u0 = stream_first_unit(total, w, warps), u1 = stream_first_unit(total, w + 1, warps);
+    const int tile0 = blockIdx.y * NT;
+
+    uint8_t* ring = gemv_smem + (size_t)warp * (kStagesQ6K * kQ6KUnit);
+    const uint8_t* wsrc = units + (size_t)u0 * kQ6KUnit;   // next unit to copy: the range is contiguous in memory
+    unsigned issued = u0;
+    int wstage = 0, rstage = 0;
+#pragma unroll
+    for (int i = 0; i < kStagesQ6K - 1; i++) {
+        if (issued < u1) {
+            q6k_issue(ring + wstage * kQ6KUnit, wsrc, 0, lane);
+            wsrc += kQ6KUnit;
+            issued++;
+            wstage = wstage + 1 == kStagesQ6K ? 0 : wstage + 1;
+        }
+        cp_async_commit();
+    }
+    pdl_wait();
+    if (u0 >= u1) return;
+
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+    int tile = (int)(u0 / (unsigned)nblk), b = (int)(u0 % (unsigned)nblk), seg_b0 = b;
+    const float w0 = (t & 1) ? 6.103515625e-05f : 1.0f;            // limb weights, as in reduce_and_store
+    const float w1 = (t & 1) ? 4.76837158203125e-07f : 0.0078125f;
+    float* my_slots = split.partial + ((size_t)blockIdx.y * warps + w) * 2 * (NT * 64);
+    constexpr bool kAhead = NT == 1;
+    uint2 bf[NT][kQ6KSteps];
+    if (kAhead) {
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const uint2* fsrc = frag + ((size_t)(tile0 + nt) * nblk + b) * (kQ6KSteps * 32) + lane;
+#pragma unroll
+            for (int s = 0; s < kQ6KSteps; s++) bf[nt][s] = ld_act(fsrc + s * 32);
+        }
+    }
+
+    for (unsigned u = u0; u < u1; u++) {
+        if (issued < u1) {
+            q6k_issue(ring + wstage * kQ6KUnit, wsrc, 0, lane);
+            wsrc += kQ6KUnit;
+            issued++;
+            wstage = wstage + 1 == kStagesQ6K ? 0 : wstage + 1;
+        }
+        cp_async_commit();
+        // activation fragments: with one tile they are fetched one unit ahead (the fragments depend on the super-block
+        // only, so the one after the last of a row tile is the first again)
+        uint2 bn[kAhead ? NT : 1][kQ6KSteps];
+        if (kAhead) {
+            if (u + 1 < u1) {
+                const int nb = b + 1 == nblk ? 0 : b + 1;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const uint2* fsrc = frag + ((size_t)(tile0 + nt) * nblk + nb) * (kQ6KSteps * 32) + lane;
+#pragma unroll
+                    for (int s = 0; s < kQ6KSteps; s++) bn[nt][s] = ld_act(fsrc + s * 32);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const uint2* fsrc = frag + ((size_t)(tile0 + nt) * nblk + b) * (kQ6KSteps * 32) + lane;
+#pragma unroll
+                for (int s = 0; s < kQ6KSteps; s++) bf[nt][s] = ld_act(fsrc + s * 32);
+            }
+        }
+        cp_async_wait<kStagesQ6K - 1>();
+        __syncwarp();
+        Q6KUnit cur;
+        q6k_read(cur, ring + rstage * kQ6KUnit, lane);
+        rstage = rstage + 1 == kStagesQ6K ? 0 : rstage + 1;
+        __syncwarp();
+        q6k_unit_mac<NT>(cur, bf, acc, t);
+        if (kAhead) {
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int s = 0; s < kQ6KSteps; s++) bf[nt][s] = bn[nt][s];
+        }
+        b++;
+        if (b < nblk && u + 1 < u1) continue;
+
+        // ---- the segment [seg_b0, b) of row tile `tile` ends here
+        const bool whole = seg_b0 == 0 && b == nblk;
+        const int r0 = tile * 16 + g;
+        float lo[NT], hi[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            lo[nt] = acc[nt][0] * w0 + acc[nt][1] * w1;
+            hi[nt] = acc[nt][2] * w0 + acc[nt][3] * w1;
+            lo[nt] += __shfl_xor_sync(0xffffffffu, lo[nt], 1);
+            hi[nt] += __shfl_xor_sync(0xffffffffu, hi[nt], 1);
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+        }
+        if (whole) {
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
+                if ((t & 1) == 0 && batch < m) store_result<EPI>(y, ldy, rows, batch, r0, lo[nt], hi[nt], push);
+            }
+        } else {
+            // slot 0: a piece that starts inside the tile (only a warp's first piece can); slot 1: one that starts with it
+            float* slot = my_slots + (seg_b0 > 0 ? 0 : 1) * (NT * 64);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) __stcg(reinterpret_cast<float2*>(slot + nt * 64) + lane, make_float2(lo[nt], hi[nt]));
+            __threadfence();
+            __syncwarp();
+            const unsigned t_first = (unsigned)tile * (unsigned)nblk, t_last = t_first + (unsigned)nblk - 1;
+            const unsigned w_lo = stream_warp_of(total, t_first, warps), w_hi = stream_warp_of(total, t_last, warps);
+            unsigned seen = 0;
+            unsigned* ticket = split.tickets + (size_t)blockIdx.y * row_tiles + tile;
+            if (lane == 0) seen = atomicAdd(ticket, 1u);
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            if (seen == w_hi - w_lo) {   // every other piece of this tile is in the workspace: add them in warp order
+                __threadfence();
+                float slo[NT], shi[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) slo[nt] = shi[nt] = 0.0f;
+                for (unsigned ww = w_lo; ww <= w_hi; ww++) {
+                    const unsigned s0 = stream_first_unit(total, ww, warps);
+                    const float* src = split.partial + (((size_t)blockIdx.y * warps + ww) * 2 + (s0 > t_first ? 0 : 1)) * (NT * 64);
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        const float2 v = __ldcg(reinterpret_cast<const float2*>(src + nt * 64) + lane);
+                        slo[nt] += v.x;
+                        shi[nt] += v.y;
+                    }
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
+                    if ((t & 1) == 0 && batch < m) store_result<EPI>(y, ldy, rows, batch, r0, slo[nt], shi[nt], push);
+                }
+                if (lane == 0) *ticket = 0;   // ready for the next launch
+            }
+        }
+        tile++;
+        b = 0;
+        seg_b0 = 0;
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1119,7 +1303,8 @@ static int choose_wk(uint32_t ty, const DeviceWeights& w, Epilogue epi, int nt, 
 
 template <int NT, int EPI>
 static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint2* frag, size_t m, float* y,
-                          size_t ldy, int wk, int ksplit, unsigned passes, bool pdl, const PushDst& push, const SplitWs& split)
+                          size_t ldy, int wk, int ksplit, unsigned passes, bool pdl, const PushDst& push, const SplitWs& split,
+                          bool stream, int stream_ctas, int sm_count)
 {
     const int row_tiles = (int)w.row_tiles(), wr = 8 / wk;
     const int ff_tiles = (int)(w.rows / 2 / 16);
@@ -1150,7 +1335,20 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
     } else {
         if (attr_dev_q6 != dev) {
             cudaFuncSetAttribute(gemv_q6k_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ6K);
+            if (EPI != kEpiSwiglu)
+                cudaFuncSetAttribute(gemv_q6k_stream_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ6K);
             attr_dev_q6 = dev;
+        }
+        if constexpr (EPI != kEpiSwiglu) {
+            // the unit-balanced form: one resident CTA per slot, every warp an equal share of the units
+            const unsigned ctas = stream_ctas > 0 ? (unsigned)stream_ctas : (unsigned)sm_count * (NT <= 2 ? 2u : 1u);
+            const size_t total = (size_t)row_tiles * w.nblk, warps = (size_t)ctas * 8;
+            if (stream && split.partial && passes == 1 && total >= warps && (size_t)row_tiles <= kSplitTickets &&
+                warps * 2 * NT * 64 <= kSplitWsFloats) {
+                launch_kernel(gemv_q6k_stream_kernel<NT, EPI>, dim3(ctas, passes), dim3(256), kSmemQ6K, st, pdl, w.units, frag, y,
+                              (int)w.rows, (int)w.nblk, (int)m, ldy, row_tiles, push, split);
+                return;
+            }
         }
         launch_kernel(gemv_q6k_kernel<NT, EPI>, grid, dim3(256), kSmemQ6K, st, pdl, w.units, frag, y, (int)w.rows,
                       (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push, split);
@@ -1167,9 +1365,9 @@ int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
     const unsigned passes = (unsigned)(padded_tiles(m) / (size_t)nt);
     const uint2* f = reinterpret_cast<const uint2*>(frag);
 #define FERRIC_GEMV_CASE(NT_)                                                                             \
-    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, ksplit, passes, tune.pdl, push, tune.split_ws);   \
-    else if (epi == kEpiPush) launch_gemv_t<NT_, kEpiPush>(st, ty, w, f, m, y, ldy, wk, ksplit, passes, tune.pdl, push, tune.split_ws); \
-    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, 1, passes, tune.pdl, push, tune.split_ws)
+    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, ksplit, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count);   \
+    else if (epi == kEpiPush) launch_gemv_t<NT_, kEpiPush>(st, ty, w, f, m, y, ldy, wk, ksplit, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count); \
+    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, 1, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count)
     if (nt == 1) { FERRIC_GEMV_CASE(1); }
     else if (nt == 2) { FERRIC_GEMV_CASE(2); }
     else { FERRIC_GEMV_CASE(4); }

@@ -492,3 +492,38 @@ def test_k_split_across_ctas(F, ty, ksplit, monkeypatch):
             assert np.array_equal(qm.matmul(xd).cpu().numpy(), got)
         qm.close()
     c.close()
+
+
+@pytest.mark.parametrize("ctas", [1, 3, 7, 0])
+def test_q6k_unit_balanced_form(F, ctas, monkeypatch):
+    """The Q6_K GEMV in its unit-balanced form: every warp takes an equal run of units, whatever the row tiles; runs
+    that start or end inside a row tile leave partial sums that the last warp to arrive adds in warp order.  A forced
+    small grid makes small matrices walk all of it: warps spanning several row tiles, row tiles cut into several
+    pieces, a tile exactly one warp's run.  Same bar against the oracle, the same bits on every run, close to the
+    other form, tickets back at zero (the repeated runs would fail otherwise)."""
+    if ctas:
+        monkeypatch.setenv("FERRIC_CUDA_GEMV_STREAM_CTAS", str(ctas))
+    monkeypatch.setenv("FERRIC_CUDA_GEMV_STREAM", "1")     # opt-in: it measured no faster than the row-tile form
+    c = F.Context(0)
+    monkeypatch.setenv("FERRIC_CUDA_GEMV_STREAM", "0")
+    c_off = F.Context(0)
+    shapes = [(200, 1024, 1), (33, 4352, 2), (515, 2048, 5), (1000, 5120, 8), (96, 7168, 3), (16, 256 * 24, 1), (384, 256, 2)]
+    if not ctas:
+        shapes = [(5120, 17408, 1), (5120, 2304, 2), (4000, 5120, 4)]
+    for rows, cols, m in shapes:
+        raw = synth.matrix(14, rows, cols, seed=rows + ctas)
+        x = synth.activations(m, cols, seed=m)
+        xd = torch.from_numpy(x).cuda()
+        qm = F.QMatrix.from_bytes(c, raw, 14, rows, cols)
+        got = qm.matmul(xd).cpu().numpy()
+        ref = O.matmul_q(raw, 14, rows, cols, x, threads=NCPU)
+        assert_close(got, ref, f"{rows}x{cols} m{m} ctas{ctas}", exact_product(raw, 14, rows, cols, x))
+        for _ in range(3):
+            assert np.array_equal(qm.matmul(xd).cpu().numpy(), got)
+        q2 = F.QMatrix.from_bytes(c_off, raw, 14, rows, cols)
+        other = q2.matmul(xd).cpu().numpy()
+        assert np.abs(other - got).max() <= 2e-6 * max(1.0, float(np.abs(ref).max())) + 1e-5 * np.abs(ref).max()
+        qm.close()
+        q2.close()
+    c.close()
+    c_off.close()
