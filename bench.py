@@ -51,9 +51,10 @@ def parse_args():
     ap.add_argument("--prefill-rows", type=int, default=17408, help="weight rows of the --prefill matrix")
     ap.add_argument("--prefill-cols", type=int, default=5120, help="columns (K) of the --prefill matrix")
     ap.add_argument("--prefill-type", type=int, default=12, choices=[12, 14, 8], help="ggml type of the --prefill matrix")
-    ap.add_argument("--allreduce", default="auto", choices=["auto", "push", "fused", "nccl"],
+    ap.add_argument("--allreduce", default="auto", choices=["auto", "push", "fused", "wide", "nccl"],
                     help="N > 1: the library's own exchange over peer memory (push: the products store into every rank's memory; "
-                         "fused: signalled buffers read by the peers), NCCL through torch.distributed, or (default) push for small batches")
+                         "fused: signalled buffers read by the peers; wide: the two-step pushed all-reduce of the batched decode path, batch > 8), "
+                         "NCCL through torch.distributed, or (default) the library's own")
     return ap.parse_args()
 
 
@@ -219,7 +220,11 @@ def run_ours(args):
         at 2), NCCL above that."""
         if world == 1:
             return None, None, "none"
-        kind = args.allreduce if args.allreduce != "auto" else ("push" if batch <= (8 if world >= 4 else 4) else "nccl")
+        kind = args.allreduce
+        if kind == "auto":
+            kind = "push" if batch <= (8 if world >= 4 else 4) else "wide" if batch > 8 else "nccl"
+        if batch > 8 and kind in ("push", "fused"):
+            kind = "wide"        # the GEMV's exchanges serve up to 8 rows
         if kind == "nccl":
             return (lambda t: dist.all_reduce(t)), None, kind
         grp = TPGroup(ctx, rank, world, batch, HIDDEN)

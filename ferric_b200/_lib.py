@@ -76,6 +76,8 @@ SIGNATURES = {
     "ferric_cuda_tp_connect_local": (_I32, [_P, C.POINTER(_P)]),
     "ferric_cuda_tp_matmul_push": (_I32, [_P, _P, _I32, _P, _P, _SZ, _SZ]),
     "ferric_cuda_tp_add_rmsnorm_prepare_pushed": (_I32, [_P, _P, _I32, _P, _P, _P, C.c_float, _SZ, _P, _P]),
+    "ferric_cuda_tp_allreduce_add_rmsnorm": (_I32, [_P, _P, _I32, _P, _P, _P, C.c_float, _SZ, _SZ, _P, _P]),
+    "ferric_cuda_tp_allreduce_add_rmsnorm_steps": (_I32, [_P, _P, _I32, _P, _P, _P, C.c_float, _SZ, _SZ, _P, _P, _I32]),
     "ferric_cuda_tp_status": (_I32, [_P, _P, C.POINTER(_I32)]),
     "ferric_cuda_tp_free": (None, [_P]),
     "ferric_gguf_parse": (_I32, [_P, _SZ, C.POINTER(_P)]),

@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(HERE, "libferric_cuda.so")
 
-SOURCES = ["ffi.cu", "kernels_repack.cu", "kernels_gemv.cu", "kernels_glue.cu", "kernels_gemm.cu", "kernels_gemvtc.cu", "gguf.cu", "tp.cu"]
+SOURCES = ["ffi.cu", "kernels_repack.cu", "kernels_gemv.cu", "kernels_glue.cu", "kernels_gemm.cu", "kernels_gemvtc.cu", "kernels_tpwide.cu", "gguf.cu", "tp.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -49,6 +49,25 @@ struct PushSrc {                      // consumer side
     int world = 0;                    // 0 = not a push exchange
 };
 
+// The two-step pushed all-reduce of a whole activation matrix (kernels_tpwide.cu), seen from one rank.
+struct WideDst {
+    uint2* stage1[kMaxRanks] = {};    // rank r's stage-1 region for (kind, source = this rank), parity 0
+    uint2* stage2[kMaxRanks] = {};    // rank r's stage-2 region for this kind, parity 0
+    const uint2* recv1 = nullptr;     // local stage 1 for this kind: [parity][source rank][slice]
+    const uint2* recv2 = nullptr;     // local stage 2 for this kind: [parity][elems]
+    unsigned* epoch = nullptr;        // exchanges of this kind completed on this rank
+    unsigned* ticket = nullptr;
+    int* status = nullptr;
+    size_t slice = 0;                 // floats per rank's slice, a multiple of 4
+    size_t parity_stride1 = 0, parity_stride2 = 0;   // pairs
+    int world = 0, rank = 0;
+};
+// (sum, norm) = add_rmsnorm(a, all-reduce(partial)) over the ranks of `dst`; rows x d floats, d a multiple of 4.
+// `steps`: 1 scatter, 2 reduce, 4 consume (7 = the whole exchange).
+int32_t launch_wide_allreduce_add_rmsnorm(cudaStream_t st, const float* partial, const float* a, const float* weight, float eps,
+                                          size_t rows, size_t d, float* sum, float* norm, const WideDst& dst,
+                                          const struct GemvTuning& tune, int steps = 7);
+
 enum Epilogue : int { kEpiStore = 0, kEpiSwiglu = 1, kEpiPush = 2 };
 
 // Workspace of a GEMV whose K range is cut across CTAs (grid z): every CTA of a tile group leaves its partial sums

@@ -46,6 +46,8 @@ struct ferric_tp_group {
     unsigned* push_epoch = nullptr;   // [2] pushed exchanges of each kind completed on this rank
     unsigned* push_ticket = nullptr;  // [2] CTA counters of the consumers
     uint2* recv = nullptr;            // [kind][parity][world][elems] (value, exchange number) pairs
+    unsigned* wide_epoch = nullptr;   // [2] two-step all-reduces of each kind completed on this rank
+    unsigned* wide_ticket = nullptr;  // [2]
     void* peer_base[kMaxRanks] = {};  // IPC mappings of the peers' `local`
     bool connected = false;
     bool local_peers = false;         // peers are groups of this process (no IPC mappings to close)
@@ -60,7 +62,14 @@ size_t off_slots(size_t elems) { return align_up(off_status(elems) + sizeof(int)
 size_t off_push_meta(size_t elems) { return align_up(off_slots(elems) + 2 * kMaxRanks * sizeof(void*), 256); }
 size_t off_recv(size_t elems) { return off_push_meta(elems) + 256; }
 size_t recv_pairs(size_t elems, int world) { return (size_t)world * elems; }   // one parity of one kind
-size_t total_bytes(size_t elems, int world) { return off_recv(elems) + 4 * recv_pairs(elems, world) * sizeof(uint2); }
+size_t off_wide_meta(size_t elems, int world) { return off_recv(elems) + 4 * recv_pairs(elems, world) * sizeof(uint2); }
+// the two-step all-reduce of whole matrices: slices of `wide_slice` floats per rank; per kind and parity, stage 1 holds
+// every source's copy of this rank's slice and stage 2 the summed vector
+size_t wide_slice(size_t elems, int world) { return ((elems + world - 1) / world + 3) / 4 * 4; }
+size_t wide_pairs(size_t elems, int world) { return (size_t)world * wide_slice(elems, world); }   // one parity of one kind, either stage
+size_t off_wide1(size_t elems, int world) { return off_wide_meta(elems, world) + 256; }
+size_t off_wide2(size_t elems, int world) { return off_wide1(elems, world) + 4 * wide_pairs(elems, world) * sizeof(uint2); }
+size_t total_bytes(size_t elems, int world) { return off_wide2(elems, world) + 4 * wide_pairs(elems, world) * sizeof(uint2); }
 }  // namespace
 
 extern "C" {
@@ -103,6 +112,8 @@ int32_t ferric_cuda_tp_create(ferric_cuda_ctx* ctx, int32_t rank, int32_t world,
     g->push_epoch = reinterpret_cast<unsigned*>(base + off_push_meta(elems));
     g->push_ticket = g->push_epoch + 2;
     g->recv = reinterpret_cast<uint2*>(base + off_recv(elems));
+    g->wide_epoch = reinterpret_cast<unsigned*>(base + off_wide_meta(elems, world));
+    g->wide_ticket = g->wide_epoch + 2;
     g->peer_base[rank] = g->local;
     *out = g;
     return kOk;
@@ -295,6 +306,56 @@ int32_t ferric_cuda_tp_add_rmsnorm_prepare_pushed(ferric_cuda_ctx* ctx, ferric_t
     ctx->launches++;
     return launch_norm_prep(ctx->stream, qm->ty, qm->w, a_dev, nullptr, weight_dev, eps, m, sum_dev, norm_dev, ctx->scratch,
                             ctx->tune, PeerSum(), p);
+}
+
+int32_t ferric_cuda_tp_allreduce_add_rmsnorm(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t kind, const float* partial_dev,
+                                             const float* a_dev, const float* weight_dev, float eps, size_t rows, size_t d,
+                                             float* sum_dev, float* norm_dev)
+{
+    return ferric_cuda_tp_allreduce_add_rmsnorm_steps(ctx, g, kind, partial_dev, a_dev, weight_dev, eps, rows, d, sum_dev, norm_dev, 7);
+}
+
+int32_t ferric_cuda_tp_allreduce_add_rmsnorm_steps(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t kind, const float* partial_dev,
+                                                   const float* a_dev, const float* weight_dev, float eps, size_t rows, size_t d,
+                                                   float* sum_dev, float* norm_dev, int32_t steps)
+{
+    if (steps < 1 || steps > 7) {
+        set_last_error("tp_allreduce_add_rmsnorm_steps: steps is a mask of 1 (scatter), 2 (reduce), 4 (consume)");
+        return kErrInvalidArg;
+    }
+    if (!ctx || !g || kind < 0 || kind > 1 || !g->connected || (rows * d > 0 && (!partial_dev || !a_dev || !sum_dev))) {
+        set_last_error("tp_allreduce_add_rmsnorm: NULL / unconnected argument (sum_dev is required) or bad kind");
+        return kErrInvalidArg;
+    }
+    if (rows * d > g->elems || (d & 3) || (reinterpret_cast<uintptr_t>(partial_dev) & 15) || (reinterpret_cast<uintptr_t>(a_dev) & 15) ||
+        (reinterpret_cast<uintptr_t>(sum_dev) & 15) || (reinterpret_cast<uintptr_t>(norm_dev) & 15) ||
+        (reinterpret_cast<uintptr_t>(weight_dev) & 15)) {
+        set_last_error("tp_allreduce_add_rmsnorm: %zu x %zu floats must fit the group's %zu, d be a multiple of 4 and the buffers 16-byte aligned",
+                       rows, d, g->elems);
+        return kErrShape;
+    }
+    if (rows * d == 0) return kOk;
+    DeviceGuard guard(ctx->device);
+    const size_t pairs = wide_pairs(g->elems, g->world);
+    WideDst w;
+    w.world = g->world;
+    w.rank = g->rank;
+    w.slice = wide_slice(g->elems, g->world);
+    w.parity_stride1 = w.parity_stride2 = pairs;
+    w.epoch = g->wide_epoch + kind;
+    w.ticket = g->wide_ticket + kind;
+    w.status = g->status;
+    uint8_t* local = reinterpret_cast<uint8_t*>(g->local);
+    w.recv1 = reinterpret_cast<const uint2*>(local + off_wide1(g->elems, g->world)) + (size_t)kind * 2 * pairs;
+    w.recv2 = reinterpret_cast<const uint2*>(local + off_wide2(g->elems, g->world)) + (size_t)kind * 2 * pairs;
+    for (int r = 0; r < g->world; r++) {
+        uint8_t* peer = reinterpret_cast<uint8_t*>(g->peer_base[r]);
+        w.stage1[r] = reinterpret_cast<uint2*>(peer + off_wide1(g->elems, g->world)) + (size_t)kind * 2 * pairs + (size_t)g->rank * w.slice;
+        w.stage2[r] = reinterpret_cast<uint2*>(peer + off_wide2(g->elems, g->world)) + (size_t)kind * 2 * pairs;
+    }
+    ctx->launches += (steps & 1) + ((steps >> 1) & 1) + ((steps >> 2) & 1);
+    return launch_wide_allreduce_add_rmsnorm(ctx->stream, partial_dev, a_dev, weight_dev, eps, rows, d, sum_dev, norm_dev, w, ctx->tune,
+                                             steps);
 }
 
 int32_t ferric_cuda_tp_status(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t* timed_out)

@@ -398,6 +398,17 @@ class TPGroup:
                "tp_add_rmsnorm_prepare")
         return m
 
+    def allreduce_add_rmsnorm(self, kind: int, partial: torch.Tensor, a: torch.Tensor, weight: Optional[torch.Tensor] = None,
+                              eps: float = 1e-6, sum_out: Optional[torch.Tensor] = None,
+                              norm_out: Optional[torch.Tensor] = None, steps: int = 7) -> None:
+        """(sum, norm) = add_rmsnorm(a, all-reduce(partial)) through the two-step pushed all-reduce; for many rows.
+        `steps`: 1 scatter, 2 reduce, 4 consume (a host driving several ranks on one GPU runs them one at a time)."""
+        rows, d = a.numel() // a.shape[-1], a.shape[-1]
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        _check(self._lib.ferric_cuda_tp_allreduce_add_rmsnorm_steps(self.ctx._h, self._h, kind, partial.data_ptr(), a.data_ptr(),
+                                                                    ptr(weight), float(eps), rows, d, ptr(sum_out), ptr(norm_out), steps),
+               "tp_allreduce_add_rmsnorm")
+
     def matmul_push(self, kind: int, qm: "QMatrix", x: torch.Tensor) -> None:
         """The row-parallel product x . W^T of this rank, stored by the kernel's epilogue into every rank's receive
         region for exchange `kind` instead of a local buffer."""

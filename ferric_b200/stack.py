@@ -154,7 +154,7 @@ class DecodeStack:
         c, p = self.ctx, self.plan
         before = c.launches()
         n = len(self.layers)
-        if self.batch > 8 and self.group is None:
+        if self.batch > 8:
             return self._step_wide(before)
         m = self.layers[0].wqkv.add_rmsnorm_prepare(self.h, None, None, self.eps)
         G = self.group
@@ -199,15 +199,21 @@ class DecodeStack:
         for i, L in enumerate(self.layers):
             L.wqkv.matmul(self.xn, out=self.qkv)
             L.wo.matmul(self.qkv[:, :p.q_rows], out=self.o)
-            if self.all_reduce:
-                self.all_reduce(self.o)
-            c.add_rmsnorm(self.h, self.o, None, self.eps, sum_out=self.h, norm_out=self.xn)
+            if self.group is not None:      # the library's two-step pushed all-reduce, fused into add + rmsnorm
+                self.group.allreduce_add_rmsnorm(0, self.o, self.h, None, self.eps, sum_out=self.h, norm_out=self.xn)
+            else:
+                if self.all_reduce:
+                    self.all_reduce(self.o)
+                c.add_rmsnorm(self.h, self.o, None, self.eps, sum_out=self.h, norm_out=self.xn)
             if L.wgu.try_matmul_swiglu(self.xn, out=self.f) is None:
                 raise RuntimeError("gate|up matrix is not fusable")
             L.wdown.matmul(self.f, out=self.d)
-            if self.all_reduce:
-                self.all_reduce(self.d)
-            c.add_rmsnorm(self.h, self.d, None, self.eps, sum_out=self.h, norm_out=self.xn)
+            if self.group is not None:
+                self.group.allreduce_add_rmsnorm(1, self.d, self.h, None, self.eps, sum_out=self.h, norm_out=self.xn)
+            else:
+                if self.all_reduce:
+                    self.all_reduce(self.d)
+                c.add_rmsnorm(self.h, self.d, None, self.eps, sum_out=self.h, norm_out=self.xn)
         self.launches_per_step = c.launches() - before
         return self.h
 

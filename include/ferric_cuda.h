@@ -348,6 +348,20 @@ int32_t ferric_cuda_tp_add_rmsnorm_prepare_pushed(ferric_cuda_ctx *ctx, ferric_t
                                                   const ferric_qmatrix *qm, const float *a_dev,
                                                   const float *weight_dev, float eps, size_t m, float *sum_dev,
                                                   float *norm_dev);
+/* For many activation rows (the batched decode path): (sum, norm) = add_rmsnorm(a, all-reduce over the ranks of
+ * partial_dev[rows, d]) by the library's own kernels in two pushed steps -- every rank stores slice s of its partial into
+ * rank s's memory, rank s adds the copies in rank order and stores the sums into every rank's memory, and the add +
+ * RMSNorm reads them there.  rows x d must fit the group's `elems`; d a multiple of 4; buffers 16-byte aligned;
+ * sum_dev is required (it may be a_dev), norm_dev and weight_dev may be NULL. */
+int32_t ferric_cuda_tp_allreduce_add_rmsnorm(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t kind,
+                                             const float *partial_dev, const float *a_dev, const float *weight_dev,
+                                             float eps, size_t rows, size_t d, float *sum_dev, float *norm_dev);
+/* The same exchange one step at a time (`steps`: 1 scatter, 2 reduce, 4 consume, or-ed together), for a host that
+ * drives several ranks on one GPU and therefore must not queue a step that waits for a kernel it has not launched. */
+int32_t ferric_cuda_tp_allreduce_add_rmsnorm_steps(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t kind,
+                                                   const float *partial_dev, const float *a_dev,
+                                                   const float *weight_dev, float eps, size_t rows, size_t d,
+                                                   float *sum_dev, float *norm_dev, int32_t steps);
 /* Synchronise the context and report whether any wait on a peer ran out (FERRIC_ERR_TIMEOUT). */
 int32_t ferric_cuda_tp_status(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t *timed_out);
 void ferric_cuda_tp_free(ferric_tp_group *g);

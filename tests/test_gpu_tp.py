@@ -42,6 +42,13 @@ def test_two_gpu_stack_matches_unsharded_oracle(tmp_path):
     assert np.abs(got["fused"] - h).max() <= tol
     assert np.array_equal(got["fused"], got["fused_replay"])       # graph replay == eager
     assert np.array_equal(got["nccl"], got["nccl_replay"])
+    wide = np.load(out + ".wide.npz")
+    hw = synth.activations(W.WIDE_B, W.HID, seed=6)
+    for l in range(W.LAYERS):
+        hw = T.layer_forward(plan1, layer_shards(plan1, T.full_layer(100 + 10 * l)), hw, lambda a: None)
+    tolw = 1e-4 + 1e-3 * np.abs(hw).max()
+    assert np.abs(wide["nccl"] - hw).max() <= tolw and np.abs(wide["wide"] - hw).max() <= tolw
+    assert np.array_equal(wide["wide"], wide["wide_replay"])
     assert np.abs(got["push"] - h).max() <= tol
     assert np.array_equal(got["push"], got["push_replay"])
     assert np.array_equal(got["push"], got["fused"])               # same partials, same rank-order sum
@@ -128,4 +135,41 @@ def test_pushed_exchange_many_ranks_in_one_process(world, m):
             grps[r].check()
             assert torch.equal(s, s_ref) and torch.equal(n, n_ref) and torch.equal(y, y_ref), (it, r)
     for o in ws + nxt + grps + ctxs:
+        o.close()
+
+
+@pytest.mark.parametrize("world,cap_rows,rows,d", [(1, 9, 9, 1024), (2, 16, 16, 1024), (3, 16, 10, 512), (8, 64, 64, 1536), (8, 8, 5, 260),
+                                                   (4, 64, 3, 5120)])
+def test_two_step_allreduce_many_ranks_in_one_process(world, cap_rows, rows, d):
+    """The all-reduce for many activation rows (scatter to slice owners, reduce, store to all, add + RMSNorm) with
+    `world` ranks as groups of this process on one GPU.  The three steps run as phases with a device synchronise
+    between them, so no kernel waits for one that has not been launched.  Every rank must end with a + (the partials
+    added in rank order), bit for bit, three exchanges running (both kinds, both parities); rows below the group's
+    capacity leave some ranks without a slice."""
+    import ferric_b200 as F
+
+    ctxs = [F.Context(0) for _ in range(world)]
+    grps = [F.TPGroup(ctxs[r], r, world, cap_rows, d) for r in range(world)]
+    F.TPGroup.connect_local(grps)
+    gen = torch.Generator(device="cuda").manual_seed(world * 100 + rows)
+    wn = torch.rand(d, device="cuda", generator=gen) + 0.5
+    for it, kind in enumerate((0, 1, 1)):
+        parts = [torch.randn(rows, d, device="cuda", generator=gen) * (r + 1) for r in range(world)]
+        a = torch.randn(rows, d, device="cuda", generator=gen)
+        total = parts[0].clone()
+        for r in range(1, world):
+            total += parts[r]
+        s_ref, n_ref = torch.empty_like(a), torch.empty_like(a)
+        ctxs[0].add_rmsnorm(a, total, wn, 1e-6, sum_out=s_ref, norm_out=n_ref)
+        outs = [(torch.empty_like(a), torch.empty_like(a)) for _ in range(world)]
+        for step in (1, 2, 4):
+            torch.cuda.synchronize()
+            for r in range(world):
+                grps[r].allreduce_add_rmsnorm(kind, parts[r], a, wn, 1e-6, sum_out=outs[r][0], norm_out=outs[r][1], steps=step)
+        for r in range(world):
+            grps[r].check()
+            assert torch.equal(outs[r][0], s_ref), (it, r)
+            assert torch.allclose(outs[r][1], n_ref, rtol=2e-6, atol=1e-7), (it, r)
+            assert torch.equal(outs[r][1], outs[0][1])         # the same bits on every rank
+    for o in grps + ctxs:
         o.close()

@@ -11,6 +11,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 HID, NFF, QOUT, KV, LAYERS, B = 1024, 1536, 1024, 512, 3, 2
+WIDE_B = 12
 
 
 def main(rank, world, port, out):
@@ -54,6 +55,36 @@ def main(rank, world, port, out):
         results[mode] = (eager.cpu().numpy(), replay.cpu().numpy())
         st.close()
         dist.barrier()
+    # the batched decode path (more than 8 rows): NCCL against the library's two-step pushed all-reduce
+    wide = {}
+    for mode in ("nccl", "wide"):
+        group = None
+        if mode == "wide":
+            group = F.TPGroup(ctx, rank, world, WIDE_B, HID)
+            group.connect_with_torch_distributed()
+        st = DecodeStack(ctx, plan, n_layers=LAYERS, batch=WIDE_B,
+                         all_reduce=(lambda t: dist.all_reduce(t)) if mode == "nccl" else None, group=group)
+        for l in range(LAYERS):
+            sh = layer_shards(plan, full_layer(100 + 10 * l))
+            st.add_layer(F.QMatrix.from_bytes(ctx, sh["qkv"], 12, plan.q_rows + 2 * plan.kv_rows, HID),
+                         F.QMatrix.from_bytes(ctx, sh["o"], 12, HID, plan.q_rows),
+                         F.QMatrix.from_bytes(ctx, sh["gate_up"], 12, 2 * plan.ff_rows, HID),
+                         F.QMatrix.from_bytes(ctx, sh["down"], 14, HID, plan.ff_rows))
+        st.reserve()
+        h0 = torch.from_numpy(synth.activations(WIDE_B, HID, seed=6)).cuda()
+        st.h.copy_(h0)
+        eager = st.step().clone()
+        st.capture()
+        st.h.copy_(h0)
+        replay = st.run().clone()
+        torch.cuda.synchronize()
+        if group is not None:
+            group.check()
+        wide[mode] = (eager.cpu().numpy(), replay.cpu().numpy())
+        st.close()
+        dist.barrier()
+    if rank == 0:
+        np.savez(out + ".wide.npz", nccl=wide["nccl"][0], wide=wide["wide"][0], wide_replay=wide["wide"][1])
     if rank == 0:
         np.savez(out, nccl=results["nccl"][0], nccl_replay=results["nccl"][1], fused=results["fused"][0],
                  fused_replay=results["fused"][1], push=results["push"][0], push_replay=results["push"][1])
