@@ -45,6 +45,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch kernels directly instead of replaying a CUDA graph")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-matrix table")
+    ap.add_argument("--shard-of", type=int, default=0, metavar="N",
+                    help="diagnostic, 1 GPU only: time rank 0's shard of an N-way tensor-parallel plan with the exchange "
+                         "replaced by nothing (what N GPUs would reach if the exchange were free); not a valid result")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--prefill", type=int, default=0, metavar="M",
                     help="time only the tensor-core prefill product (Q4_K x bf16, M activation rows) and print its line")
@@ -214,12 +217,14 @@ def run_ours(args):
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
     ctx = Context(local)
     plan = TPPlan.make(world, rank, HIDDEN, N_FF, Q_OUT, KV_OUT)
+    if args.shard_of > 1 and world == 1:
+        plan = TPPlan.make(args.shard_of, 0, HIDDEN, N_FF, Q_OUT, KV_OUT)
     def exchange_for(batch):
         """(all_reduce callable, exchange group, name) for a batch size.  `auto`: the library's own pushed exchange
         up to batch 4 (up to batch 8 from 4 GPUs on: measured 1306 against 1027 tokens/s at 8 GPUs, but 904 against 957
         at 2), NCCL above that."""
         if world == 1:
-            return None, None, "none"
+            return ((lambda t: None) if args.shard_of > 1 else None), None, "none"
         kind = args.allreduce
         if kind == "auto":
             kind = "push" if batch <= (8 if world >= 4 else 4) else "wide" if batch > 8 else "nccl"
@@ -386,7 +391,8 @@ def run_ours(args):
             "config": {"workload": WORKLOAD.format(b=B), "batch": B, "layers": args.layers,
                        "parallelism": f"tp{world}", "cuda_graph": not args.no_graph,
                        "l2": f"{stack.weight_bytes_per_step() / 1e9:.2f} GB of weights per GPU per step, larger than L2",
-                       "all_reduce": ar_name},
+                       "all_reduce": ar_name, **({"diagnostic": f"rank 0's shard of tp{args.shard_of}, no exchange: not a result"}
+                                                  if args.shard_of > 1 and world == 1 else {})},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches_per_step * K), "launches_per_step": int(launches_per_step),
             "clocks": clocks.summary(), "step_weight_gbs_per_gpu": step_gbs, "output_finite": finite,

@@ -312,7 +312,6 @@ int32_t ferric_cuda_ctx_create_on_stream(int device, void* cuda_stream, ferric_c
     if (const char* s = getenv("FERRIC_CUDA_GEMV_WK")) ctx->tune.wk = atoi(s);
     if (const char* s = getenv("FERRIC_CUDA_PDL")) ctx->tune.pdl = atoi(s) != 0;
     if (const char* s = getenv("FERRIC_CUDA_PUSH_CLUSTER")) ctx->tune.push_cluster = atoi(s);
-    if (const char* s = getenv("FERRIC_CUDA_GEMV_KSPLIT")) ctx->tune.split = atoi(s);
     if (const char* s = getenv("FERRIC_CUDA_GEMV_STREAM")) ctx->tune.stream = atoi(s) != 0;
     if (const char* s = getenv("FERRIC_CUDA_GEMV_STREAM_CTAS")) ctx->tune.stream_ctas = atoi(s);
     {

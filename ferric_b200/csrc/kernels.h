@@ -70,11 +70,11 @@ int32_t launch_wide_allreduce_add_rmsnorm(cudaStream_t st, const float* partial,
 
 enum Epilogue : int { kEpiStore = 0, kEpiSwiglu = 1, kEpiPush = 2 };
 
-// Workspace of a GEMV whose K range is cut across CTAs (grid z): every CTA of a tile group leaves its partial sums
-// here, and the last one to arrive (a ticket per group) adds them in z order and stores the result.
+// Workspace of the unit-balanced GEMV: warps whose run of units starts or ends inside a row tile leave their partial
+// sums here, and the last one to arrive at a tile (a ticket per tile) adds them in warp order and stores the result.
 struct SplitWs {
-    float* partial = nullptr;     // [z][m][rows]
-    unsigned* tickets = nullptr;  // [grid y][grid x], zero between launches
+    float* partial = nullptr;     // [pass][warp][2 slots][tiles per pass x 64]
+    unsigned* tickets = nullptr;  // [pass][row tile], zero between launches
 };
 constexpr size_t kSplitWsFloats = 1u << 20;   // 4 MiB of partial sums per context
 constexpr size_t kSplitTickets = 1u << 14;
@@ -85,7 +85,6 @@ struct GemvTuning {
     int wk = 0;        // warps of a CTA that split K (0 = choose from the shape)
     int sm_count = 148;
     int push_cluster = 0;   // CTAs (a cluster) sharing one tile of the pushed exchange's consumer: 1, 2, 4 or 8; 0 = from the world size
-    int split = -1;         // CTAs along K per row-tile group of the GEMV (FERRIC_CUDA_GEMV_KSPLIT); -1 = choose from the shape
     bool stream = false;    // Q6_K plain / pushed GEMV in its unit-balanced form (FERRIC_CUDA_GEMV_STREAM=1; measured no faster)
     int stream_ctas = 0;    // its grid; 0 = one CTA per resident slot (FERRIC_CUDA_GEMV_STREAM_CTAS, for tests on small matrices)
     SplitWs split_ws;       // the context's workspace for that (not a tunable: it rides here to reach the launchers)

@@ -582,7 +582,7 @@ __device__ __forceinline__ void store_result(float* __restrict__ y, size_t ldy, 
 template <int NT, int EPI>
 __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*red)[NT * 4][32], float* __restrict__ y,
                                                  size_t ldy, int rows, int m, int tile0, int wk, int out_tile,
-                                                 bool active, const PushDst& push, const SplitWs& split)
+                                                 bool active, const PushDst& push)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int kpart = warp % wk, wr = warp / wk;
@@ -591,76 +591,38 @@ __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*re
 #pragma unroll
         for (int i = 0; i < 4; i++) red[warp][nt * 4 + i][lane] = acc[nt][i];
     __syncthreads();
-    const bool ksplit = EPI != kEpiSwiglu && gridDim.z > 1;   // K is also cut across CTAs
-    const bool writer = kpart == 0 && active && !(EPI == kEpiSwiglu && (wr & 1));
-    if (!writer && !ksplit) return;
+    if (kpart != 0 || !active) return;
+    if (EPI == kEpiSwiglu && (wr & 1)) return;
     // limb weights of this lane's two columns: 2^(-7*limb)
     const float w0 = (t & 1) ? 6.103515625e-05f : 1.0f;          // 2^-14 : 2^0
     const float w1 = (t & 1) ? 4.76837158203125e-07f : 0.0078125f; // 2^-21 : 2^-7
-    const int r0 = out_tile * 16 + g;
-    if (writer) {
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            float v[4], u[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                float s = 0.0f;
-                for (int k = 0; k < wk; k++) s += red[warp + k][nt * 4 + i][lane];
-                v[i] = s;
-                if (EPI == kEpiSwiglu) {
-                    float s2 = 0.0f;
-                    for (int k = 0; k < wk; k++) s2 += red[warp + wk + k][nt * 4 + i][lane];
-                    u[i] = s2;
-                }
-            }
-            float lo = v[0] * w0 + v[1] * w1, hi = v[2] * w0 + v[3] * w1;
-            lo += __shfl_xor_sync(0xffffffffu, lo, 1);
-            hi += __shfl_xor_sync(0xffffffffu, hi, 1);
-            if (EPI == kEpiSwiglu) {
-                float ulo = u[0] * w0 + u[1] * w1, uhi = u[2] * w0 + u[3] * w1;
-                ulo += __shfl_xor_sync(0xffffffffu, ulo, 1);
-                uhi += __shfl_xor_sync(0xffffffffu, uhi, 1);
-                lo = silu_mul(lo, ulo);
-                hi = silu_mul(hi, uhi);
-            }
-            const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
-            if ((t & 1) == 0 && batch < m) {
-                if (ksplit) {
-                    float* dst = split.partial + ((size_t)blockIdx.z * m + batch) * rows + r0;
-                    if (r0 < rows) __stcg(dst, lo);
-                    if (r0 + 8 < rows) __stcg(dst + 8, hi);
-                } else {
-                    store_result<EPI>(y, ldy, rows, batch, r0, lo, hi, push);
-                }
-            }
-        }
-    }
-    if (!ksplit) return;
-    // The CTAs that share these row tiles (grid z) each left a partial; the last to arrive adds them in z order.
-    __shared__ int is_last;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned* ticket = split.tickets + (size_t)blockIdx.y * gridDim.x + blockIdx.x;
-        const unsigned seen = atomicAdd(ticket, 1u);
-        is_last = seen == gridDim.z - 1;
-        if (is_last) *ticket = 0;   // ready for the next launch
-    }
-    __syncthreads();
-    if (!is_last || !writer) return;
-    __threadfence();
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
-        const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
-        if ((t & 1) == 0 && batch < m) {
-            float lo = 0.0f, hi = 0.0f;
-            for (unsigned z = 0; z < gridDim.z; z++) {
-                const float* src = split.partial + ((size_t)z * m + batch) * rows + r0;
-                if (r0 < rows) lo += __ldcg(src);
-                if (r0 + 8 < rows) hi += __ldcg(src + 8);
+        float v[4], u[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float s = 0.0f;
+            for (int k = 0; k < wk; k++) s += red[warp + k][nt * 4 + i][lane];
+            v[i] = s;
+            if (EPI == kEpiSwiglu) {
+                float s2 = 0.0f;
+                for (int k = 0; k < wk; k++) s2 += red[warp + wk + k][nt * 4 + i][lane];
+                u[i] = s2;
             }
-            store_result<EPI>(y, ldy, rows, batch, r0, lo, hi, push);
         }
+        float lo = v[0] * w0 + v[1] * w1, hi = v[2] * w0 + v[3] * w1;
+        lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+        hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+        if (EPI == kEpiSwiglu) {
+            float ulo = u[0] * w0 + u[1] * w1, uhi = u[2] * w0 + u[3] * w1;
+            ulo += __shfl_xor_sync(0xffffffffu, ulo, 1);
+            uhi += __shfl_xor_sync(0xffffffffu, uhi, 1);
+            lo = silu_mul(lo, ulo);
+            hi = silu_mul(hi, uhi);
+        }
+        const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
+        const int r0 = out_tile * 16 + g;
+        if ((t & 1) == 0 && batch < m) store_result<EPI>(y, ldy, rows, batch, r0, lo, hi, push);
     }
 }
 
@@ -733,7 +695,7 @@ __device__ __forceinline__ void q4k_row(const uint4& h, Q4KRow& r)
 template <int NT, int EPI, bool Q5 = false>
 __global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
-                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push, SplitWs split)
+                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push)
 {
     __shared__ float red[8][NT * 4][32];
     constexpr int kUnitBytes = Q5 ? kQ5KUnit : kQ4KUnit;
@@ -742,9 +704,8 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
     int rt, out_tile;
     bool active;
     pick_tile<EPI>(wk, row_tiles, ff_tiles, rt, out_tile, active);
-    // K is cut over the wk warps of a CTA and, when the grid has a z extent, over that many CTAs as well
-    const int kparts = wk * (int)gridDim.z, kpart = (int)blockIdx.z * wk + warp % wk, per = (nblk + kparts - 1) / kparts;
-    const int b0 = min(nblk, kpart * per), b1 = min(nblk, b0 + per);
+    const int kpart = warp % wk, per = (nblk + wk - 1) / wk;
+    const int b0 = kpart * per, b1 = min(nblk, b0 + per);
     const int tile0 = blockIdx.y * NT;
     const int zero[4] = {0, 0, 0, 0};
 
@@ -880,7 +841,7 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             }
         }
     }
-    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push, split);
+    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -989,7 +950,7 @@ __device__ __forceinline__ void q6k_unit_mac(const Q6KUnit& cur, const uint2 (&b
 template <int NT, int EPI>
 __global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
-                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push, SplitWs split)
+                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push)
 {
     __shared__ float red[8][NT * 4][32];
     pdl_launch_dependents();
@@ -997,9 +958,8 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
     int rt, out_tile;
     bool active;
     pick_tile<EPI>(wk, row_tiles, ff_tiles, rt, out_tile, active);
-    // K is cut over the wk warps of a CTA and, when the grid has a z extent, over that many CTAs as well
-    const int kparts = wk * (int)gridDim.z, kpart = (int)blockIdx.z * wk + warp % wk, per = (nblk + kparts - 1) / kparts;
-    const int b0 = min(nblk, kpart * per), b1 = min(nblk, b0 + per);
+    const int kpart = warp % wk, per = (nblk + wk - 1) / wk;
+    const int b0 = kpart * per, b1 = min(nblk, b0 + per);
     const int tile0 = blockIdx.y * NT;
     const int zero[4] = {0, 0, 0, 0};
 
@@ -1082,7 +1042,7 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             }
         }
     }
-    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push, split);
+    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1266,53 +1226,42 @@ gemv_q6k_stream_kernel(const uint8_t* __restrict__ units, const uint2* __restric
 // in as few waves of resident CTAs as possible -- every wave pays its own pipeline fill and
 // drain -- and within that, K-splitting shortens each warp's serial walk.  Cost model: waves x
 // (super-blocks per warp + a fixed fill/drain term), measured in super-block times.
-static int choose_wk(uint32_t ty, const DeviceWeights& w, Epilogue epi, int nt, const GemvTuning& tune, int* ksplit)
+static int choose_wk(uint32_t ty, const DeviceWeights& w, Epilogue epi, int nt, const GemvTuning& tune)
 {
     int forced = tune.wk;
     const int ctas_per_sm = nt <= 2 ? 2 : 1;
     const size_t slots = (size_t)tune.sm_count * ctas_per_sm;
     const size_t tiles = epi == kEpiSwiglu ? w.rows / 2 / 16 * 2 : w.row_tiles();
-    int best = 1, best_split = 1;
+    int best = 1;
     double best_cost = 1e30;
     for (int wk = 1; wk <= 8; wk *= 2) {
         if ((size_t)wk > w.nblk && wk > 1) break;
         if (epi == kEpiSwiglu && wk > 4) break;
-        if (forced > 0 && forced != wk) continue;
-        const size_t ctas1 = (tiles + (size_t)(8 / wk) - 1) / (size_t)(8 / wk);
-        // K cut across CTAs as well (plain and pushed stores only): more, shorter CTAs even out the last wave when the
-        // row tiles alone leave it part empty; every cut costs a partial-sum round trip at the end
-        const int max_split = epi == kEpiSwiglu ? 1 : 12;
-        for (int sp = 1; sp <= max_split; sp++) {
-            if (tune.split >= 1 && sp != tune.split) continue;
-            if (tune.split < 0 && sp > 1) break;   // cuts are chosen from the shape only once measured; until then forced only
-            if (sp > 1 && (size_t)(wk * sp) > w.nblk) break;
-            const size_t ctas = ctas1 * (size_t)sp;
-            const double waves = (double)((ctas + slots - 1) / slots);
-            const size_t per = (w.nblk + (size_t)(wk * sp) - 1) / (size_t)(wk * sp);
-            const double cost = waves * ((double)per + 4.0) + (sp > 1 ? 2.0 : 0.0);
-            if (cost < best_cost - 1e-9) {
-                best_cost = cost;
-                best = wk;
-                best_split = sp;
-            }
+        if (forced == wk) return wk;
+        const size_t ctas = (tiles + (size_t)(8 / wk) - 1) / (size_t)(8 / wk);
+        // Q6_K's ring is a stage shallower and a CTA alone on an SM does not keep enough loads in flight, so for it a
+        // part-filled second wave is charged its share rather than a whole wave
+        // (measured on the 5120 x 17408 down projection: 22.2 us with 320 CTAs against 23.3 us with 160)
+        const double waves = ty == kGgmlQ6K ? ((double)ctas > (double)slots ? (double)ctas / (double)slots : 1.0)
+                                            : (double)((ctas + slots - 1) / slots);
+        const double cost = waves * ((double)((w.nblk + wk - 1) / wk) + 4.0);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = wk;
         }
     }
-    *ksplit = best_split;
     return best;
 }
 
 template <int NT, int EPI>
 static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint2* frag, size_t m, float* y,
-                          size_t ldy, int wk, int ksplit, unsigned passes, bool pdl, const PushDst& push, const SplitWs& split,
+                          size_t ldy, int wk, unsigned passes, bool pdl, const PushDst& push, const SplitWs& split,
                           bool stream, int stream_ctas, int sm_count)
 {
     const int row_tiles = (int)w.row_tiles(), wr = 8 / wk;
     const int ff_tiles = (int)(w.rows / 2 / 16);
     unsigned gx = EPI != kEpiSwiglu ? (unsigned)((row_tiles + wr - 1) / wr) : (unsigned)((ff_tiles + wr / 2 - 1) / (wr / 2));
-    // a K split across CTAs needs its partial sums and tickets to fit the context's workspace
-    if (EPI == kEpiSwiglu || !split.partial || (size_t)ksplit * m * w.rows > kSplitWsFloats || (size_t)gx * passes > kSplitTickets)
-        ksplit = 1;
-    dim3 grid(gx, passes, (unsigned)ksplit);
+    dim3 grid(gx, passes);
     // opt in to > 48 KB of dynamic shared memory once per kernel instantiation and device
     static thread_local int attr_dev_q4 = -1, attr_dev_q6 = -1;
     int dev = 0;
@@ -1323,7 +1272,7 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
             attr_dev_q4 = dev;
         }
         launch_kernel(gemv_q4k_kernel<NT, EPI>, grid, dim3(256), kSmemQ4K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push, split);
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
     } else if (ty == kGgmlQ5K) {
         static thread_local int attr_dev_q5 = -1;
         if (attr_dev_q5 != dev) {
@@ -1331,7 +1280,7 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
             attr_dev_q5 = dev;
         }
         launch_kernel(gemv_q4k_kernel<NT, EPI, true>, grid, dim3(256), kSmemQ5K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push, split);
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
     } else {
         if (attr_dev_q6 != dev) {
             cudaFuncSetAttribute(gemv_q6k_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ6K);
@@ -1351,7 +1300,7 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
             }
         }
         launch_kernel(gemv_q6k_kernel<NT, EPI>, grid, dim3(256), kSmemQ6K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push, split);
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
     }
 }
 
@@ -1359,15 +1308,13 @@ int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
                     size_t ldy, Epilogue epi, const GemvTuning& tune, const PushDst& push)
 {
     if (m == 0 || w.rows == 0) return kOk;
-    const int nt = tiles_per_pass(m);
-    int ksplit = 1;
-    const int wk = choose_wk(ty, w, epi, nt, tune, &ksplit);
+    const int nt = tiles_per_pass(m), wk = choose_wk(ty, w, epi, nt, tune);
     const unsigned passes = (unsigned)(padded_tiles(m) / (size_t)nt);
     const uint2* f = reinterpret_cast<const uint2*>(frag);
 #define FERRIC_GEMV_CASE(NT_)                                                                             \
-    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, ksplit, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count);   \
-    else if (epi == kEpiPush) launch_gemv_t<NT_, kEpiPush>(st, ty, w, f, m, y, ldy, wk, ksplit, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count); \
-    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, 1, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count)
+    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count);   \
+    else if (epi == kEpiPush) launch_gemv_t<NT_, kEpiPush>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count); \
+    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count)
     if (nt == 1) { FERRIC_GEMV_CASE(1); }
     else if (nt == 2) { FERRIC_GEMV_CASE(2); }
     else { FERRIC_GEMV_CASE(4); }

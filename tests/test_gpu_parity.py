@@ -471,29 +471,7 @@ def test_launch_counter_counts_native_kernels(F, ctx):
     qm.close()
 
 
-# ------------------------------------------------------------------------------ K cut across CTAs
-@pytest.mark.parametrize("ksplit", [2, 3, 7])
-@pytest.mark.parametrize("ty", [12, 13, 14])
-def test_k_split_across_ctas(F, ty, ksplit, monkeypatch):
-    """The GEMV with its K range also cut across CTAs (partial sums in the context's workspace, added in a fixed order
-    by the last CTA to arrive): same bar against the oracle, the same bits on every run, and a workspace that is
-    clean for the next launch (tickets back at zero)."""
-    monkeypatch.setenv("FERRIC_CUDA_GEMV_KSPLIT", str(ksplit))
-    c = F.Context(0)
-    for rows, cols, m in [(200, 2048, 1), (1000, 5120, 2), (33, 4352, 5), (515, 2048, 8), (96, 7168, 17)]:
-        raw = synth.matrix(ty, rows, cols, seed=rows + ksplit)
-        x = synth.activations(m, cols, seed=m)
-        qm = F.QMatrix.from_bytes(c, raw, ty, rows, cols)
-        xd = torch.from_numpy(x).cuda()
-        got = qm.matmul(xd).cpu().numpy()
-        assert_close(got, O.matmul_q(raw, ty, rows, cols, x, threads=NCPU), f"ty{ty} {rows}x{cols} m{m} split{ksplit}",
-                     exact_product(raw, ty, rows, cols, x))
-        for _ in range(3):
-            assert np.array_equal(qm.matmul(xd).cpu().numpy(), got)
-        qm.close()
-    c.close()
-
-
+# ------------------------------------------------------------------------------ unit-balanced Q6_K form
 @pytest.mark.parametrize("ctas", [1, 3, 7, 0])
 def test_q6k_unit_balanced_form(F, ctas, monkeypatch):
     """The Q6_K GEMV in its unit-balanced form: every warp takes an equal run of units, whatever the row tiles; runs
