@@ -53,7 +53,7 @@ def parse_args():
                     help="time only the tensor-core prefill product (Q4_K x bf16, M activation rows) and print its line")
     ap.add_argument("--prefill-rows", type=int, default=17408, help="weight rows of the --prefill matrix")
     ap.add_argument("--prefill-cols", type=int, default=5120, help="columns (K) of the --prefill matrix")
-    ap.add_argument("--prefill-type", type=int, default=12, choices=[12, 14, 8], help="ggml type of the --prefill matrix")
+    ap.add_argument("--prefill-type", type=int, default=12, choices=[12, 13, 14, 8], help="ggml type of the --prefill matrix")
     ap.add_argument("--allreduce", default="auto", choices=["auto", "push", "fused", "wide", "nccl"],
                     help="N > 1: the library's own exchange over peer memory (push: the products store into every rank's memory; "
                          "fused: signalled buffers read by the peers; wide: the two-step pushed all-reduce of the batched decode path, batch > 8), "
@@ -546,7 +546,7 @@ def run_prefill(args):
     print(json.dumps({
         "metric": "prefill_tflops", "value": r["TFLOP/s"], "unit": "TFLOP/s", "n_gpus": 1, "steps": max(args.steps, 1),
         "warmup": 3, "ms_per_step": r["us"] / 1e3, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{ {12: 'Q4_K', 14: 'Q6_K', 8: 'Q8_0'}[ty] } [{rows}x{cols}] x bf16 [{m}x{cols}] -> f32, weights dequantised in-kernel"},
+        "config": {"workload": f"{ {12: 'Q4_K', 13: 'Q5_K', 14: 'Q6_K', 8: 'Q8_0'}[ty] } [{rows}x{cols}] x bf16 [{m}x{cols}] -> f32, weights dequantised in-kernel"},
         "roofline": {"kernel": "gemm_q_bf16_kernel", "bound": "tensor", "achieved": r["TFLOP/s"], "peak": burst,
                      "unit": "TFLOP/s", "frac": r["TFLOP/s"] / burst, "peak_source": kind, "traffic": None},
         "gpu_launches": max(args.steps, 1), "clocks": clocks.summary(), "output_finite": r["finite"]}), flush=True)

@@ -42,8 +42,8 @@ constexpr int kGemmDeqWarps = 8;      // one per 16-row unit of the 128-row tile
 constexpr int kGemmHalves = 2;        // the two 8-row halves of its unit a dequant warp converts
 constexpr int kGemmFirstDeqWarp = 3;                   // warp 0 weight producer, 1 MMA issuer, 2 activation producer
 constexpr int kGemmThreads = 32 * (kGemmFirstDeqWarp + kGemmDeqWarps);
-// raw quant bytes of one stage: 8 row tiles x one super-block (18432 for Q4_K, 26880 for Q6_K)
-__host__ __device__ constexpr int gemm_unit_bytes(uint32_t ty) { return ty == kGgmlQ4K ? kQ4KUnit : kQ6KUnit; }
+// raw quant bytes of one stage: 8 row tiles x one super-block (18432 for Q4_K, 22528 for Q5_K, 26880 for Q6_K)
+__host__ __device__ constexpr int gemm_unit_bytes(uint32_t ty) { return ty == kGgmlQ4K ? kQ4KUnit : ty == kGgmlQ5K ? kQ5KUnit : kQ6KUnit; }
 // Q8_0 is stored as planes ([rows][cols] int8 and [rows][cols/32] f16); a stage holds the tile of 128 rows x 256 columns
 // of the first (32 KB, fetched as one TMA box) and its 128 x 8 scales (2 KB, a second box).
 constexpr int kGemmQ8QsBytes = kGemmRows * 256, kGemmQ8DBytes = kGemmRows * 16;
@@ -79,6 +79,9 @@ __host__ __device__ constexpr int gemm_smem_bytes(uint32_t ty, int n_tile, bool 
 static_assert(gemm_b_stages(kGgmlQ4K, 128, false) == 8 && gemm_b_stages(kGgmlQ4K, 256, false) == 4 &&
                   gemm_b_stages(kGgmlQ4K, 512, false) == 2 && gemm_b_stages(kGgmlQ4K, 512, true) == 4,
               "Q4_K stage counts");
+static_assert(gemm_b_stages(kGgmlQ5K, 128, false) >= 7 && gemm_b_stages(kGgmlQ5K, 256, false) >= 3 &&
+                  gemm_b_stages(kGgmlQ5K, 512, false) >= 1 && gemm_b_stages(kGgmlQ5K, 512, true) >= 3,
+              "Q5_K stage counts");
 static_assert(gemm_b_stages(kGgmlQ6K, 128, false) == 7 && gemm_b_stages(kGgmlQ6K, 256, false) == 3 &&
                   gemm_b_stages(kGgmlQ6K, 512, true) == 3,
               "Q6_K stage counts");
@@ -141,10 +144,13 @@ __device__ __forceinline__ uint4 deq8(uint32_t w0, uint32_t w1, float d1, float 
 // One call per dequant warp: for every super-block, wait for its raw units, pull this warp's 16-row unit into
 // registers, and for each of its four K chunks convert 16 rows x 64 weights to bf16, wait for a free A stage,
 // store, and announce it.  Returns 0, or the code of the wait that ran out.
-template <bool PAIR>
+template <bool PAIR, bool Q5>
 __device__ __forceinline__ int dequant_loop_q4k(GemmBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, int nblk,
                                                 int tiles_here, int wq, int lane)
 {
+    // Q5: the Q5_K unit is the Q4_K unit plus a fifth-bit segment (lane 4g + t: qh[8t .. 8t+8) of rows g and g + 8); bit s
+    // of qh[l] lifts value l of sub-block s by 16 (crates/ferric-gguf/src/lib.rs:690-716), the rest is Q4_K's arithmetic.
+    constexpr int kUnitBytes = Q5 ? kQ5KUnit : kQ4KUnit;
     // ---------------- dequantise: warp = one 16-row unit (or eight rows of it), lane = (row g, 8-byte piece t)
     // The lane -> (g, t) map keeps both the 16-byte loads of the raw unit and the 16-byte stores into the
     // swizzled A tile free of bank conflicts: the two rows of a quarter-warp differ in bits 0 and 2.
@@ -157,17 +163,20 @@ __device__ __forceinline__ int dequant_loop_q4k(GemmBarriers* bar, uint8_t* a_st
     for (int b = 0; b < nblk && !fail; b++) {
         const int rs = b % kGemmRawStages;
         if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)b / kGemmRawStages) & 1u)) { fail = 4; break; }
-        const uint8_t* u = raw_stage + rs * (8 * kQ4KUnit) + wd * kQ4KUnit;
+        const uint8_t* u = raw_stage + rs * (8 * kUnitBytes) + wd * kUnitBytes;
         uint4 hdr[kGemmHalves], qs[kGemmHalves][2];
+        uint2 q5[kGemmHalves];
         float d[kGemmHalves], dmin[kGemmHalves];
 #pragma unroll
         for (int hh = 0; hh < kGemmHalves; hh++) {
             const int hi = hh;
             hdr[hh] = qs[hh][0] = qs[hh][1] = make_uint4(0, 0, 0, 0);
+            q5[hh] = make_uint2(0, 0);
             if (unit_ok) {
                 hdr[hh] = *reinterpret_cast<const uint4*>(u + 16 * (g + 8 * hi));
                 qs[hh][0] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi) + 16 * (4 * g + t));
                 qs[hh][1] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi + 1) + 16 * (4 * g + t));
+                if (Q5) q5[hh] = *reinterpret_cast<const uint2*>(u + kQ5KOffQh + 16 * (4 * g + t) + 8 * hi);
             }
             d[hh] = __half2float(__ushort_as_half((unsigned short)(hdr[hh].x & 0xffffu)));
             dmin[hh] = __half2float(__ushort_as_half((unsigned short)(hdr[hh].x >> 16)));
@@ -197,8 +206,15 @@ __device__ __forceinline__ int dequant_loop_q4k(GemmBarriers* bar, uint8_t* a_st
                 const float d1b = __shfl_sync(0xffffffffu, my_d1b[hh], src), mmb = __shfl_sync(0xffffffffu, my_mmb[hh], src);
                 const uint4 q4 = qs[hh][j >> 1];
                 const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
-                lo[hh] = deq8(w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, d1a, mma);
-                up[hh] = deq8((w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, d1b, mmb);
+                uint32_t l0 = w0 & 0x0F0F0F0Fu, l1 = w1 & 0x0F0F0F0Fu, u0 = (w0 >> 4) & 0x0F0F0F0Fu, u1 = (w1 >> 4) & 0x0F0F0F0Fu;
+                if (Q5) {   // sub-blocks 2j (low nibbles) and 2j + 1 (high nibbles)
+                    l0 |= ((q5[hh].x >> (2 * j)) & 0x01010101u) << 4;
+                    l1 |= ((q5[hh].y >> (2 * j)) & 0x01010101u) << 4;
+                    u0 |= ((q5[hh].x >> (2 * j + 1)) & 0x01010101u) << 4;
+                    u1 |= ((q5[hh].y >> (2 * j + 1)) & 0x01010101u) << 4;
+                }
+                lo[hh] = deq8(l0, l1, d1a, mma);
+                up[hh] = deq8(u0, u1, d1b, mmb);
             }
             const int c = 4 * b + j, s = c % kGemmStages;
             if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
@@ -549,7 +565,8 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
     } else {
         // ---------------- dequantise (per quant type, above), then the epilogue
         const int wq = warp - kGemmFirstDeqWarp;
-        if (TY == kGgmlQ4K) fail = dequant_loop_q4k<PAIR>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
+        if (TY == kGgmlQ4K) fail = dequant_loop_q4k<PAIR, false>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
+        else if (TY == kGgmlQ5K) fail = dequant_loop_q4k<PAIR, true>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
         else if (TY == kGgmlQ6K) fail = dequant_loop_q6k<PAIR>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
         else fail = dequant_loop_q8_0<PAIR>(bar, a_stage, raw_stage, nb, wq, lane);
         // ---------------- epilogue.  All dequant warps first agree that nobody gave up (the staged path below
@@ -783,7 +800,7 @@ size_t gemm_workspace_bytes(const DeviceWeights& w, size_t m, int sm_count)
 int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w_in, const uint16_t* x_bf16, size_t m, size_t ldx,
                          float* y, size_t ldy, void* workspace, int sm_count)
 {
-    if (ty != kGgmlQ4K && ty != kGgmlQ6K && ty != kGgmlQ8_0) return kUnsupported;
+    if (ty != kGgmlQ4K && ty != kGgmlQ5K && ty != kGgmlQ6K && ty != kGgmlQ8_0) return kUnsupported;
     if (m == 0 || w_in.rows == 0 || w_in.nblk == 0) return kOk;
     DeviceWeights w = w_in;
     if (ty == kGgmlQ8_0) {
@@ -873,6 +890,7 @@ int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w_in
         }
     }
     int32_t rc = ty == kGgmlQ4K   ? launch_gemm_ty<kGgmlQ4K>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy, n_tile, pair)
+                 : ty == kGgmlQ5K ? launch_gemm_ty<kGgmlQ5K>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy, n_tile, pair)
                  : ty == kGgmlQ6K ? launch_gemm_ty<kGgmlQ6K>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy, n_tile, pair)
                                   : launch_gemm_ty<kGgmlQ8_0>(st, w, map, ymap, wsmap, q8maps, split, tma_store, m, y, ldy, n_tile, pair);
     if (rc != kOk || split.splits <= 1) return rc;

@@ -244,7 +244,7 @@ class QMatrix:
 
     def matmul_bf16(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Prefill product on the tensor cores: ``x`` [m, cols] bfloat16, result [m, rows] float32 with the
-        weights rounded to bf16 (``Tensor::matmul_q4_k_coop``, ferric-tensor/src/dtype.rs:1818-1834).  Q4_K only."""
+        weights rounded to bf16 (``Tensor::matmul_q4_k_coop``, ferric-tensor/src/dtype.rs:1818-1834).  Q4_K, Q5_K, Q6_K and Q8_0."""
         if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()):
             raise TypeError("matmul_bf16 needs a contiguous 2-D bfloat16 CUDA tensor")
         m = x.shape[0]

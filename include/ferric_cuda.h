@@ -214,7 +214,7 @@ int32_t ferric_cuda_matmul_q_noalloc(ferric_cuda_ctx *ctx, const ferric_qmatrix 
  * into workgroup memory and multiply them with 8x8x8 subgroup-matrix ops; here a CTA (above
  * 256 activation rows: a pair of CTAs) owns 128 (256) weight rows x up to 512 activation rows,
  * K advances in chunks of 64, and the multiply is tcgen05.mma with the f32 accumulator in tensor
- * memory.  Q4_K, Q6_K and Q8_0 (the last with columns in multiples of 256; anything else returns
+ * memory.  Q4_K, Q5_K, Q6_K and Q8_0 (the last with columns in multiples of 256; anything else returns
  * FERRIC_UNSUPPORTED, the reference's fall-back to the plain kernel); any m >= 1 works but the kernel is
  * meant for m >= 128.  Asynchronous on the context's stream.  Tiles of a partly filled last wave
  * are cut along K; their pieces meet in the context's scratch (up to 37 MB, grown on demand --

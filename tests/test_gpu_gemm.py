@@ -46,7 +46,7 @@ def bf16_to_f64(bits):
 def blocks(ty, rng, n):
     if ty == 8:
         return synth.q8_0_blocks(rng, n // 32)
-    return (synth.q4k_blocks if ty == 12 else synth.q6k_blocks)(rng, n // 256)
+    return {12: synth.q4k_blocks, 13: synth.q5k_blocks, 14: synth.q6k_blocks}[ty](rng, n // 256)
 
 
 def make_case(rows, cols, m, seed, ty=12):
@@ -98,7 +98,7 @@ SHAPES = [
 ]
 
 
-@pytest.mark.parametrize("ty", [12, 14, 8])
+@pytest.mark.parametrize("ty", [12, 13, 14, 8])
 @pytest.mark.parametrize("rows,cols,m", SHAPES)
 def test_small_shapes(F, ctx, rows, cols, m, ty):
     rel = check(F, ctx, rows, cols, m, seed=rows + cols + m + ty, ty=ty)
@@ -116,7 +116,7 @@ def test_prefill_down_q6k(F, ctx):
     check(F, ctx, 1024, 17408, 512, seed=5, oracle_rows=16, ty=14)
 
 
-@pytest.mark.parametrize("ty", [12, 14, 8])
+@pytest.mark.parametrize("ty", [12, 13, 14, 8])
 def test_dequant_stage_is_bit_exact(F, ctx, ty):
     """x = identity columns: y[i, r] is then exactly the bf16 weight W[r, i] -- the dequant-to-bf16 stage
     inside the kernel must match the oracle's bf16 dequantisation bit for bit."""
