@@ -49,6 +49,10 @@ def parse_args():
                     help="diagnostic, 1 GPU only: time rank 0's shard of an N-way tensor-parallel plan with the exchange "
                          "replaced by nothing (what N GPUs would reach if the exchange were free); not a valid result")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-chain", action="store_true",
+                    help="launch the norms and activation preparation as kernels of their own (8 launches per layer) instead of "
+                         "inside the products' launches (4 per layer)")
+    ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the sharded-against-unsharded parity stage")
     ap.add_argument("--prefill", type=int, default=0, metavar="M",
                     help="time only the tensor-core prefill product (Q4_K x bf16, M activation rows) and print its line")
     ap.add_argument("--prefill-rows", type=int, default=17408, help="weight rows of the --prefill matrix")
@@ -85,12 +89,12 @@ class CpuLayer:
         self.data = [(ty, r, c, synth.matrix(ty, r, c, seed=4 + i), synth.activations(batch, c, seed=4 + i))
                      for i, (ty, r, c) in enumerate(mats)]
 
-    def seconds(self, mode_name: str = "dequant_dot") -> float:
+    def seconds(self, mode_name: str = "dequant_dot", threads: int = 0) -> float:
         O = self.O
         mode = {"dequant_dot": O.MODE_DEQUANT_DOT, "fused": O.MODE_FUSED}[mode_name]
         t0 = time.perf_counter()
         for ty, r, c, raw, x in self.data:
-            y = O.matmul_q(raw, ty, r, c, x, threads=self.cores, mode=mode)
+            y = O.matmul_q(raw, ty, r, c, x, threads=threads or self.cores, mode=mode)
             if r == 2 * N_FF:
                 O.swiglu(y, N_FF)
         return time.perf_counter() - t0
@@ -199,7 +203,10 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ["NCCL_DEBUG"] = "WARN"     # NCCL's version banner goes to stdout, where only the JSON line belongs
+        os.environ.setdefault("NCCL_DEBUG", "WARN")   # quiet by default; a caller's own setting (e.g. INFO) is kept
+        # No NVLink multicast bindings: nothing here needs in-switch reduction, and a rank must never leave while its
+        # memory is bound to a multicast object.
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -236,8 +243,14 @@ def run_ours(args):
         grp.connect_with_torch_distributed()
         return None, grp, kind
 
+    chain = None if not args.no_chain else False
+    parity = None
+    if world > 1 and not args.no_parity:
+        parity = tp_parity_check(torch, dist, ctx, world, rank, dev, exchange_for, chain)
+
     allreduce, group, ar_name = exchange_for(B)
-    stack = DecodeStack(ctx, plan, n_layers=args.layers, batch=B, all_reduce=allreduce, group=group, push=(ar_name == "push"))
+    stack = DecodeStack(ctx, plan, n_layers=args.layers, batch=B, all_reduce=allreduce, group=group, push=(ar_name == "push"),
+                        chain=chain)
     stack.build_synthetic(seed=4)
     g = torch.Generator(device=dev).manual_seed(4)
     x0 = torch.randn((B, HIDDEN), device=dev, generator=g)
@@ -258,16 +271,21 @@ def run_ours(args):
     for _ in range(W):
         stack.h.copy_(x0)
         stack.run()
-    barrier()
+    # The K-step block is timed (CUDA events, max over ranks) as often as fills half a second, at least three times;
+    # the reported step time is the median block.
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    block_ms = []
     with ClockSampler(local) as clocks:
-        ev0.record()
-        for _ in range(K):
-            stack.run()
-        ev1.record()
-        torch.cuda.synchronize(dev)
-    barrier()
-    elapsed_ms = max_over_ranks(ev0.elapsed_time(ev1))
+        while len(block_ms) < 3 or (sum(block_ms) < 500.0 and len(block_ms) < 25):
+            barrier()
+            ev0.record()
+            for _ in range(K):
+                stack.run()
+            ev1.record()
+            torch.cuda.synchronize(dev)
+            barrier()
+            block_ms.append(max_over_ranks(ev0.elapsed_time(ev1)))
+    elapsed_ms = statistics.median(block_ms)
     finite = bool(torch.isfinite(stack.h).all().item())
     if group is not None:
         group.check()      # raises if any bounded wait on a peer ran out
@@ -281,7 +299,7 @@ def run_ours(args):
             if b == B:
                 continue
             ar2, g2, name2 = exchange_for(b)
-            st2 = DecodeStack(ctx, plan, n_layers=args.layers, batch=b, all_reduce=ar2, group=g2, push=(name2 == "push"))
+            st2 = DecodeStack(ctx, plan, n_layers=args.layers, batch=b, all_reduce=ar2, group=g2, push=(name2 == "push"), chain=chain)
             for L in stack.layers:
                 st2.add_layer(L.wqkv, L.wo, L.wgu, L.wdown)
             st2.reserve()
@@ -306,6 +324,7 @@ def run_ours(args):
             if g2 is not None:
                 g2.check()
             other_batches[str(b)] = {"tokens_per_s": b * 1e3 / ms2, "ms_per_step": ms2, "steps": k2, "all_reduce": name2,
+                                     "launches_per_step": int(st2.launches_per_step),
                                      "finite": bool(torch.isfinite(st2.h).all().item())}
             st2.layers = []     # the matrices belong to the first stack
             st2.graph = None
@@ -345,7 +364,8 @@ def run_ours(args):
                 L.wgu.matmul_prepared(m, out=stack.f, swiglu=True)
         roof_kernel = "gemv_q4k_kernel<swiglu>"
 
-    us_per_launch = graph_time_us(torch, ctx, gate_up_pass, reps=3) / len(stack.layers)
+    with ClockSampler(local) as roof_clocks:
+        us_per_launch = graph_time_us(torch, ctx, gate_up_pass, reps=9) / len(stack.layers)
     algo_bytes = L0.wgu.nbytes() + B * HIDDEN * 4 + B * plan.ff_rows * 4
     achieved = algo_bytes / (us_per_launch * 1e-6) / 1e9
     traffic = None
@@ -358,19 +378,23 @@ def run_ours(args):
         pass
     roofline = {"kernel": roof_kernel, "shape": [L0.wgu.rows(), L0.wgu.cols(), B], "bound": "hbm",
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                "algorithmic_bytes_per_launch": algo_bytes, "us_per_launch": us_per_launch, "traffic": traffic}
+                "algorithmic_bytes_per_launch": algo_bytes, "us_per_launch": us_per_launch, "traffic": traffic,
+                "timing": "median of 9 graph replays of 64 launches over 64 distinct matrices", "clocks": roof_clocks.summary()}
 
     # whole-step HBM efficiency, for context: weight bytes per step per GPU / device time
     step_gbs = stack.weight_bytes_per_step() / (ms_per_step * 1e-3) / 1e9
 
     extras = None
     if rank == 0 and world == 1 and not args.no_extras:
-        extras = per_matrix_table(torch, ctx, stack, QMatrix, B, peak)
-        extras.update(other_configs(torch, ctx, QMatrix, peak))
-        extras["prefill_q4k_bf16_34816x5120"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, stack.layers[0].wgu, m, 5)
-                                                 for m in (128, 512, 2048)}
-        extras["prefill_q6k_bf16_5120x17408"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, stack.layers[0].wdown, m, 5)
-                                                 for m in (512, 2048)}
+        with ClockSampler(local) as extra_clocks:
+            extras = per_matrix_table(torch, ctx, stack, QMatrix, B, peak)
+            extras.update(other_configs(torch, ctx, QMatrix, peak))
+            extras["prefill_q4k_bf16_34816x5120"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, stack.layers[0].wgu, m, 9)
+                                                     for m in (128, 512, 2048)}
+            extras["prefill_q6k_bf16_5120x17408"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, stack.layers[0].wdown, m, 9)
+                                                     for m in (512, 2048)}
+        extras["timing"] = "every entry: median of 9 individually timed replays (CUDA events)"
+        extras["clocks"] = extra_clocks.summary()
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -378,10 +402,12 @@ def run_ours(args):
         cores = layer.cores
         t_layer = min(layer.seconds() for _ in range(3))
         t_fused = min(layer.seconds("fused") for _ in range(2))
+        t_one = layer.seconds(threads=1)
         cpu = {"value": B / (t_layer * args.layers), "unit": "tokens/s", "cores": cores, "kind": "port",
                "sample": f"1 of {args.layers} layers (208.8 MB of weights), best of 3, dequantise-then-dot order, "
                          f"{cores} threads; step time = {args.layers} x layer time",
-               "fused_order_value": B / (t_fused * args.layers)}
+               "fused_order_value": B / (t_fused * args.layers),
+               "one_thread_value": B / (t_one * args.layers)}
 
     if rank == 0:
         line = {
@@ -390,28 +416,126 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD.format(b=B), "batch": B, "layers": args.layers,
                        "parallelism": f"tp{world}", "cuda_graph": not args.no_graph,
+                       "launch_form": ("chained: one launch per matrix, norms / residual adds / activation preparation inside them"
+                                       if stack.chain else "one kernel per stage"),
                        "l2": f"{stack.weight_bytes_per_step() / 1e9:.2f} GB of weights per GPU per step, larger than L2",
                        "all_reduce": ar_name, **({"diagnostic": f"rank 0's shard of tp{args.shard_of}, no exchange: not a result"}
                                                   if args.shard_of > 1 and world == 1 else {})},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches_per_step * K), "launches_per_step": int(launches_per_step),
             "clocks": clocks.summary(), "step_weight_gbs_per_gpu": step_gbs, "output_finite": finite,
+            "timed_blocks": {"blocks": len(block_ms), "ms_per_block_median": elapsed_ms, "ms_per_block_min": min(block_ms),
+                             "ms_per_block_max": max(block_ms)},
+            "parity_check": parity,
             "other_batches": other_batches,
             "extras": extras,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        # Captured graphs hold NCCL work; tearing the process group down under them can block for
-        # minutes.  All ranks meet once more, then leave without the collective teardown.
+        # Leave in order: no captured graph (they may hold NCCL work), nothing in flight, then the collective teardown.
+        # Tearing a process group down has been seen to block for minutes; a watchdog ends the process if it does.
+        stack.graph = None
         barrier()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        watchdog = threading.Timer(60.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
+        torch.cuda.synchronize(dev)
+        dist.destroy_process_group()
+        watchdog.cancel()
+        os._exit(0)        # the exchange groups' peer mappings are released with the process
     stack.close()
 
 
-def graph_time_us(torch, ctx, fn, reps=3):
-    """Microseconds for one call of `fn` (a sequence of launches on the context), replayed from a CUDA graph."""
+def tp_parity_check(torch, dist, ctx, world, rank, dev, exchange_for, chain):
+    """N > 1, outside every timed region: two full-shape layers, cut into this run's shards, run through the exchange
+    the timed run uses at batch 1, 8 and 64, against the same two layers run unsharded on rank 0.  The bytes are drawn
+    on rank 0 and broadcast, so every rank cuts the same tensors.  Element-wise bar: 1e-4 + 1e-3 |ref|."""
+    from ferric_b200 import QMatrix, synth
+    from ferric_b200.stack import DecodeStack, TPPlan
+
+    layers = 2
+    plan = TPPlan.make(world, rank, HIDDEN, N_FF, Q_OUT, KV_OUT)
+    plan1 = TPPlan.make(1, 0, HIDDEN, N_FF, Q_OUT, KV_OUT)
+    shapes = {"q": (12, Q_OUT, HIDDEN), "k": (12, KV_OUT, HIDDEN), "v": (12, KV_OUT, HIDDEN), "o": (12, HIDDEN, Q_OUT),
+              "gate": (12, N_FF, HIDDEN), "up": (12, N_FF, HIDDEN), "down": (14, HIDDEN, N_FF)}
+
+    def cut(raw, ty, rows, cols, row0, nrows, col0, ncols):
+        vals, bb = synth.BLOCK[ty]
+        return raw.view(rows, cols // vals, bb)[row0:row0 + nrows, col0 // vals:(col0 + ncols) // vals, :].contiguous().view(-1)
+
+    def build(p, full):
+        qkv = torch.cat([cut(full["q"], 12, Q_OUT, HIDDEN, p.q_row0, p.q_rows, 0, HIDDEN),
+                         cut(full["k"], 12, KV_OUT, HIDDEN, p.kv_row0, p.kv_rows, 0, HIDDEN),
+                         cut(full["v"], 12, KV_OUT, HIDDEN, p.kv_row0, p.kv_rows, 0, HIDDEN)])
+        gu = torch.cat([cut(full["gate"], 12, N_FF, HIDDEN, p.ff_row0, p.ff_rows, 0, HIDDEN),
+                        cut(full["up"], 12, N_FF, HIDDEN, p.ff_row0, p.ff_rows, 0, HIDDEN)])
+        return (QMatrix.from_device_bytes(ctx, qkv, 12, p.q_rows + 2 * p.kv_rows, HIDDEN),
+                QMatrix.from_device_bytes(ctx, cut(full["o"], 12, HIDDEN, Q_OUT, 0, HIDDEN, p.q_row0, p.q_rows), 12, HIDDEN, p.q_rows),
+                QMatrix.from_device_bytes(ctx, gu, 12, 2 * p.ff_rows, HIDDEN),
+                QMatrix.from_device_bytes(ctx, cut(full["down"], 14, HIDDEN, N_FF, 0, HIDDEN, p.ff_row0, p.ff_rows), 14, HIDDEN, p.ff_rows))
+
+    sharded, whole = [], []
+    for l in range(layers):
+        full = {}
+        for i, (name, (ty, r, c)) in enumerate(shapes.items()):
+            t = synth.matrix_on_device(ty, r, c, 9000 + 16 * l + i, dev)
+            dist.broadcast(t, 0)
+            full[name] = t
+        sharded.append(build(plan, full))
+        if rank == 0:
+            whole.append(build(plan1, full))
+        del full
+    result = {"world": world, "layers": layers, "batches": [], "all_reduce": {}, "worst_ratio": 0.0, "worst_ratio_maxnorm": 0.0,
+              "bar": "element-wise |sharded - unsharded| <= 1e-4 + 1e-3 |unsharded| on rank 0's residual stream after the layers; "
+                     "worst_ratio_maxnorm uses 1e-4 + 1e-3 max|unsharded| instead"}
+    g = torch.Generator(device=dev).manual_seed(77)
+    for b in (1, 8, 64):
+        x = torch.randn((b, HIDDEN), device=dev, generator=g)
+        dist.broadcast(x, 0)
+        ar, grp, name = exchange_for(b)
+        st = DecodeStack(ctx, plan, n_layers=layers, batch=b, all_reduce=ar, group=grp, push=(name == "push"), chain=chain)
+        for mats in sharded:
+            st.add_layer(*mats)
+        st.reserve()
+        st.h.copy_(x)
+        got = st.step().clone()
+        torch.cuda.synchronize(dev)
+        if grp is not None:
+            grp.check()
+        dist.barrier()
+        if rank == 0:
+            ref_st = DecodeStack(ctx, plan1, n_layers=layers, batch=b, chain=chain)
+            for mats in whole:
+                ref_st.add_layer(*mats)
+            ref_st.reserve()
+            ref_st.h.copy_(x)
+            ref = ref_st.step().clone()
+            torch.cuda.synchronize(dev)
+            err = (got - ref).abs().double()
+            ratio = float((err / (1e-4 + 1e-3 * ref.abs().double())).max().item())
+            ratio_max = float((err.max() / (1e-4 + 1e-3 * ref.abs().max().double())).item())
+            result["worst_ratio"] = max(result["worst_ratio"], ratio)
+            result["worst_ratio_maxnorm"] = max(result["worst_ratio_maxnorm"], ratio_max)
+            ref_st.layers = []
+        result["batches"].append(b)
+        result["all_reduce"][str(b)] = name + ("+chain" if st.chain else "")
+        st.layers = []
+        dist.barrier()
+    for mats in sharded + whole:
+        for w in mats:
+            w.close()
+    flag = torch.tensor([result["worst_ratio"]], dtype=torch.float64, device=dev)
+    dist.broadcast(flag, 0)
+    result["worst_ratio"] = float(flag.item())
+    result["ok"] = bool(result["worst_ratio"] <= 1.0)
+    return result
+
+
+def graph_time_us(torch, ctx, fn, reps=9):
+    """Microseconds for one call of `fn` (a sequence of launches on the context), replayed from a CUDA graph: 3 warm-up
+    replays, then the median of `reps` (at least 9) replays, each bracketed by its own pair of CUDA events."""
     dev = ctx.device
     side = torch.cuda.Stream(device=dev)
     side.wait_stream(torch.cuda.current_stream(dev))
@@ -425,15 +549,17 @@ def graph_time_us(torch, ctx, fn, reps=3):
         ctx.use_torch_stream()
         fn()
     ctx.use_torch_stream()
-    gr.replay()
-    torch.cuda.synchronize(dev)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
+    for _ in range(3):
         gr.replay()
-    e1.record()
     torch.cuda.synchronize(dev)
-    return e0.elapsed_time(e1) * 1e3 / reps
+    reps = max(reps, 9)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for e0, e1 in evs:
+        e0.record()
+        gr.replay()
+        e1.record()
+    torch.cuda.synchronize(dev)
+    return statistics.median(e0.elapsed_time(e1) for e0, e1 in evs) * 1e3
 
 
 def per_matrix_table(torch, ctx, stack, QMatrix, B, peak):
@@ -452,7 +578,7 @@ def per_matrix_table(torch, ctx, stack, QMatrix, B, peak):
                     w.try_matmul_swiglu(x, out=y)
                 else:
                     w.matmul(x, out=y)
-        us = graph_time_us(torch, ctx, once, reps=2) / len(stack.layers)
+        us = graph_time_us(torch, ctx, once) / len(stack.layers)
         w = getattr(stack.layers[0], attr)
         nbytes = w.nbytes() + x.shape[0] * x.shape[1] * 4 + y.numel() * 4
         out[name] = {"us": us, "GB/s": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak, "launches": 2}
@@ -475,7 +601,7 @@ def other_configs(torch, ctx, QMatrix, peak):
     def cycle():
         for w in ws:
             w.matmul(x, out=y)
-    us = graph_time_us(torch, ctx, cycle, reps=3) / len(ws)
+    us = graph_time_us(torch, ctx, cycle) / len(ws)
     nbytes = ws[0].nbytes() + 4 * cols + 4 * rows
     out["config0_q4k_4096x4096_m1_cold"] = {"us": us, "GB/s": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak,
                                             "launches": 2}
@@ -487,7 +613,7 @@ def other_configs(torch, ctx, QMatrix, peak):
     for b in (1, 64):
         x = torch.randn((b, cols), device=dev)
         y = torch.empty((b, rows), device=dev)
-        us = graph_time_us(torch, ctx, lambda: head.matmul(x, out=y), reps=3)
+        us = graph_time_us(torch, ctx, lambda: head.matmul(x, out=y))
         nbytes = head.nbytes() + 4 * b * cols + 4 * b * rows
         out[f"config2_head_q6k_151936x5120_m{b}"] = {"us": us, "GB/s": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak,
                                                      "TFLOP/s": 2.0 * b * rows * cols / us / 1e6}
@@ -495,8 +621,22 @@ def other_configs(torch, ctx, QMatrix, peak):
     # configs[3]
     rows, cols = 17408, 5120
     gate = QMatrix.from_device_bytes(ctx, synth.matrix_on_device(12, rows, cols, 3, dev), 12, rows, cols)
-    out["config3_prefill_q4k_bf16_17408x5120"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, gate, m, 5) for m in (128, 512, 2048)}
+    out["config3_prefill_q4k_bf16_17408x5120"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, gate, m, 9) for m in (128, 512, 2048)}
     gate.close()
+    # Q8_0 GEMV (the third format of the path): gate-sized matrix, 32 copies cycled (2.96 GB, far more than L2)
+    rows, cols = 17408, 5120
+    ws = [QMatrix.from_device_bytes(ctx, synth.matrix_on_device(8, rows, cols, 300 + i, dev), 8, rows, cols) for i in range(32)]
+    x = torch.randn((1, cols), device=dev)
+    y = torch.empty((1, rows), device=dev)
+
+    def cycle8():
+        for w in ws:
+            w.matmul(x, out=y)
+    us = graph_time_us(torch, ctx, cycle8) / len(ws)
+    nbytes = ws[0].nbytes() + 4 * cols + 4 * rows
+    out["gemv_q8_0_17408x5120_m1_cold"] = {"us": us, "GB/s": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak, "launches": 1}
+    for w in ws:
+        w.close()
     return out
 
 
@@ -510,7 +650,8 @@ def bf16_peaks():
 
 
 def prefill_case(torch, ctx, QMatrix, w, m, reps):
-    """TFLOP/s of y[m, rows] = x[m, cols] . W^T on the tensor cores (weights dequantised to bf16 in the kernel).
+    """TFLOP/s of y[m, rows] = x[m, cols] . W^T on the tensor cores (weights dequantised to bf16 in the kernel): the
+    median of `reps` (at least 9) individually timed launches after 3 warm-up launches.
     x (bf16) and y (f32) are resident; the weights of one matrix (100 MB at full size) are re-read from L2/HBM."""
     dev = torch.device("cuda", ctx.device)
     x = torch.randn((m, w.cols()), device=dev).to(torch.bfloat16)
@@ -518,13 +659,14 @@ def prefill_case(torch, ctx, QMatrix, w, m, reps):
     for _ in range(3):
         w.matmul_bf16(x, out=y)
     assert w.gemm_status() == 0
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
+    reps = max(reps, 9)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for e0, e1 in evs:
+        e0.record()
         w.matmul_bf16(x, out=y)
-    e1.record()
+        e1.record()
     torch.cuda.synchronize(dev)
-    us = e0.elapsed_time(e1) * 1e3 / reps
+    us = statistics.median(e0.elapsed_time(e1) for e0, e1 in evs) * 1e3
     tf = 2.0 * m * w.rows() * w.cols() / us / 1e6
     burst, sustained, kind = bf16_peaks()
     return {"us": us, "TFLOP/s": tf, "frac_of_bf16_peak": tf / burst, "frac_of_sustained_bf16_peak": tf / sustained,

@@ -25,6 +25,13 @@ class Caps(C.Structure):
 _P, _SZ, _U32, _I32 = C.c_void_p, C.c_size_t, C.c_uint32, C.c_int32
 
 
+class ChainLink(C.Structure):
+    """``ferric_chain_link`` of include/ferric_cuda.h."""
+    _fields_ = [("qm", C.c_void_p), ("swiglu", C.c_int32), ("in_slot", C.c_int32), ("in_rms", C.c_int32), ("eps", C.c_float),
+                ("y_dev", C.c_void_p), ("ldy", C.c_size_t), ("next", C.c_int32), ("next_qm", C.c_void_p),
+                ("h_dev", C.c_void_p), ("norm_weight_dev", C.c_void_p)]
+
+
 class GgufTensor(C.Structure):
     _fields_ = [("name", C.c_char_p), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 4), ("ggml_type", C.c_uint32),
                 ("offset", C.c_uint64), ("n_elements", C.c_uint64), ("nbytes", C.c_uint64)]
@@ -79,6 +86,10 @@ SIGNATURES = {
     "ferric_cuda_tp_allreduce_add_rmsnorm": (_I32, [_P, _P, _I32, _P, _P, _P, C.c_float, _SZ, _SZ, _P, _P]),
     "ferric_cuda_tp_allreduce_add_rmsnorm_steps": (_I32, [_P, _P, _I32, _P, _P, _P, C.c_float, _SZ, _SZ, _P, _P, _I32]),
     "ferric_cuda_tp_status": (_I32, [_P, _P, C.POINTER(_I32)]),
+    "ferric_cuda_tp_reset": (_I32, [_P, _P]),
+    "ferric_cuda_tp_chain_matmul": (_I32, [_P, _P, _I32, C.POINTER(ChainLink), _SZ]),
+    "ferric_cuda_chain_reserve": (_I32, [_P, _SZ]),
+    "ferric_cuda_chain_matmul": (_I32, [_P, C.POINTER(ChainLink), _SZ]),
     "ferric_cuda_tp_free": (None, [_P]),
     "ferric_gguf_parse": (_I32, [_P, _SZ, C.POINTER(_P)]),
     "ferric_gguf_open": (_I32, [C.c_char_p, C.POINTER(_P)]),

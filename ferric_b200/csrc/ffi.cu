@@ -314,8 +314,10 @@ int32_t ferric_cuda_ctx_create_on_stream(int device, void* cuda_stream, ferric_c
     if (const char* s = getenv("FERRIC_CUDA_PUSH_CLUSTER")) ctx->tune.push_cluster = atoi(s);
     if (const char* s = getenv("FERRIC_CUDA_GEMV_STREAM")) ctx->tune.stream = atoi(s) != 0;
     if (const char* s = getenv("FERRIC_CUDA_GEMV_STREAM_CTAS")) ctx->tune.stream_ctas = atoi(s);
+    if (const char* s = getenv("FERRIC_CUDA_PEER_WAIT_SPINS")) ctx->tune.wait_spins = atoi(s) > 0 ? atoi(s) : 0;
     {
-        const size_t bytes = kSplitWsFloats * sizeof(float) + kSplitTickets * sizeof(unsigned);
+        const size_t chain_words = kChainMaxRows * kChainMaxBlocks + kChainMaxBlocks + 64;
+        const size_t bytes = kSplitWsFloats * sizeof(float) + kSplitTickets * sizeof(unsigned) + chain_words * 4;
         void* ws = nullptr;
         cudaError_t e2 = cudaMalloc(&ws, bytes);
         if (e2 == cudaSuccess) e2 = cudaMemset(ws, 0, bytes);
@@ -327,6 +329,9 @@ int32_t ferric_cuda_ctx_create_on_stream(int device, void* cuda_stream, ferric_c
         }
         ctx->tune.split_ws.partial = reinterpret_cast<float*>(ws);
         ctx->tune.split_ws.tickets = reinterpret_cast<unsigned*>(ctx->tune.split_ws.partial + kSplitWsFloats);
+        ctx->chain_ssq = reinterpret_cast<float*>(ctx->tune.split_ws.tickets + kSplitTickets);
+        ctx->chain_tickets = reinterpret_cast<unsigned*>(ctx->chain_ssq + kChainMaxRows * kChainMaxBlocks);
+        ctx->chain_done = ctx->chain_tickets + kChainMaxBlocks;
     }
     *out = ctx;
     return kOk;
@@ -708,6 +713,149 @@ int32_t ferric_gguf_deq_raw(ferric_cuda_ctx* ctx, const uint8_t* raw, size_t raw
     e = cudaStreamSynchronize(ctx->stream);
     if (rc == kOk && e != cudaSuccess) rc = cuda_fail(e, "cudaStreamSynchronize");
     return rc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Chained products: a decoder layer's matmuls with the glue between them (activation preparation,
+// residual add, RMSNorm statistics) done inside the products' own launches.
+// ---------------------------------------------------------------------------------------------
+}  // extern "C"
+
+namespace ferric {
+int32_t chain_setup(ferric_cuda_ctx* ctx, const ferric_chain_link* link, size_t m, bool pushed, Chain* chain,
+                    const void** frag_in, Epilogue* epi, size_t* ldy_out)
+{
+    if (!ctx || !link || !link->qm) {
+        set_last_error("chain_matmul: NULL context, link or matrix");
+        return kErrInvalidArg;
+    }
+    const ferric_qmatrix* qm = link->qm;
+    if (qm->device != ctx->device) {
+        set_last_error("matrix lives on device %d, context on device %d", qm->device, ctx->device);
+        return kErrInvalidArg;
+    }
+    if (qm->ty == kGgmlQ8_0) {
+        set_last_error("Q8_0 has no prepared form, so it cannot be a chain link");
+        return kUnsupported;
+    }
+    if (link->swiglu && qm->w.rows % 32 != 0) return kUnsupported;
+    if (m > kChainMaxRows) {
+        set_last_error("a chained product takes at most %zu activation rows (%zu given)", kChainMaxRows, m);
+        return kErrShape;
+    }
+    if (link->in_slot != 0 && link->in_slot != 1) {
+        set_last_error("in_slot must be 0 or 1");
+        return kErrInvalidArg;
+    }
+    if (ctx->chain_slot_bytes == 0 || ctx->scratch_bytes < 2 * ctx->chain_slot_bytes) {
+        set_last_error("call ferric_cuda_chain_reserve before the first chain link");
+        return kErrInvalidArg;
+    }
+    const size_t out_cols = link->swiglu ? qm->w.rows / 2 : qm->w.rows;
+    size_t ldy = link->ldy ? link->ldy : out_cols;
+    if (ldy < out_cols || (ldy & 3)) {
+        set_last_error("ldy %zu must cover the %zu result columns and be a multiple of 4", ldy, out_cols);
+        return kErrShape;
+    }
+    if (!pushed && m > 0 && out_cols > 0 && (!link->y_dev || (reinterpret_cast<uintptr_t>(link->y_dev) & 15))) {
+        set_last_error("chain_matmul: y_dev must be a 16-byte aligned device buffer");
+        return kErrInvalidArg;
+    }
+    if (frag_bytes(qm->ty, qm->w, m) > ctx->chain_slot_bytes || qm->w.nblk > kChainMaxBlocks) {
+        set_last_error("chain_matmul: the product's prepared activations (%zu bytes) do not fit the reserved slot (%zu)",
+                       frag_bytes(qm->ty, qm->w, m), ctx->chain_slot_bytes);
+        return kErrShape;
+    }
+    *chain = Chain();
+    if (link->in_rms) {
+        chain->ssq_in = ctx->chain_ssq;
+        chain->ssq_blocks = (int)qm->w.nblk;
+        chain->eps = link->eps;
+        chain->d = (float)qm->w.cols;
+    }
+    ChainJob& j = chain->job;
+    if (link->next != FERRIC_CHAIN_NONE) {
+        const ferric_qmatrix* nx = link->next_qm;
+        if (link->next != FERRIC_CHAIN_PREPARE && link->next != FERRIC_CHAIN_RESIDUAL) {
+            set_last_error("chain_matmul: unknown `next` %d", link->next);
+            return kErrInvalidArg;
+        }
+        if (!nx || nx->device != ctx->device || nx->ty == kGgmlQ8_0) {
+            set_last_error("chain_matmul: next_qm must be a Q4_K / Q5_K / Q6_K matrix on the context's device");
+            return kErrInvalidArg;
+        }
+        if (nx->w.cols > out_cols || (link->next == FERRIC_CHAIN_RESIDUAL && nx->w.cols != out_cols)) {
+            set_last_error("chain_matmul: the next product reads %zu columns, this one yields %zu", nx->w.cols, out_cols);
+            return kErrShape;
+        }
+        if (frag_bytes(nx->ty, nx->w, m) > ctx->chain_slot_bytes || nx->w.nblk > kChainMaxBlocks) {
+            set_last_error("chain_matmul: the next product's prepared activations do not fit the reserved slot");
+            return kErrShape;
+        }
+        if (pushed && (link->next != FERRIC_CHAIN_RESIDUAL || link->swiglu)) {
+            set_last_error("a pushed chain link must be a plain residual link");
+            return kErrInvalidArg;
+        }
+        if (link->next == FERRIC_CHAIN_RESIDUAL &&
+            (!link->h_dev || ((reinterpret_cast<uintptr_t>(link->h_dev) | reinterpret_cast<uintptr_t>(link->norm_weight_dev)) & 15))) {
+            set_last_error("chain_matmul: a residual link needs h_dev (16-byte aligned, as norm_weight_dev)");
+            return kErrInvalidArg;
+        }
+        j.kind = link->next == FERRIC_CHAIN_PREPARE ? 1 : pushed ? 3 : 2;
+        j.out_ty = nx->ty == kGgmlQ6K ? (int)kGgmlQ6K : (int)kGgmlQ4K;
+        j.blocks = (int)nx->w.nblk;
+        j.tiles = (int)gemv_padded_tiles(m);
+        j.tickets = ctx->chain_tickets;
+        j.done = ctx->chain_done;
+        j.y = link->y_dev;
+        j.ldy = ldy;
+        j.frag = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(ctx->scratch) + (size_t)(1 - link->in_slot) * ctx->chain_slot_bytes);
+        j.h = link->h_dev;
+        j.weight = link->norm_weight_dev;
+        j.ssq = ctx->chain_ssq;
+    } else if (pushed) {
+        set_last_error("a pushed chain link must be a residual link");
+        return kErrInvalidArg;
+    }
+    *frag_in = reinterpret_cast<const uint8_t*>(ctx->scratch) + (size_t)link->in_slot * ctx->chain_slot_bytes;
+    *epi = link->swiglu ? kEpiSwiglu : pushed ? kEpiPush : kEpiStore;
+    *ldy_out = ldy;
+    return kOk;
+}
+}  // namespace ferric
+
+extern "C" {
+
+int32_t ferric_cuda_chain_reserve(ferric_cuda_ctx* ctx, size_t slot_bytes)
+{
+    if (!ctx) {
+        set_last_error("NULL context");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    const size_t slot = (slot_bytes + 255) / 256 * 256 + 256;
+    int32_t rc = ensure_scratch(ctx, 2 * slot);
+    if (rc != kOk) return rc;
+    ctx->chain_slot_bytes = slot;
+    return kOk;
+}
+
+int32_t ferric_cuda_chain_matmul(ferric_cuda_ctx* ctx, const ferric_chain_link* link, size_t m)
+{
+    Chain chain;
+    const void* frag = nullptr;
+    Epilogue epi = kEpiStore;
+    size_t ldy = 0;
+    int32_t rc = chain_setup(ctx, link, m, false, &chain, &frag, &epi, &ldy);
+    if (rc != kOk) return rc;
+    if (m == 0 || link->qm->w.rows == 0) return kOk;
+    if (link->qm->w.nblk == 0) {
+        set_last_error("chain_matmul: empty K range");
+        return kErrShape;
+    }
+    DeviceGuard guard(ctx->device);
+    ctx->launches++;
+    return launch_gemv(ctx->stream, link->qm->ty, link->qm->w, frag, m, link->y_dev, ldy, epi, ctx->tune, PushDst(), &chain);
 }
 
 // ---------------------------------------------------------------------------------------------

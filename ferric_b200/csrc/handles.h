@@ -15,6 +15,12 @@ struct ferric_cuda_ctx {
     uint64_t launches = 0;
     ferric::GemvTuning tune;
     cudaDeviceProp prop;
+    // chained products (ferric_cuda_chain_*): the scratch holds two prepared-activation slots, slot 1 at this offset
+    // (0 until ferric_cuda_chain_reserve); sums of squares, block tickets and the job counter live beside the split workspace
+    size_t chain_slot_bytes = 0;
+    float* chain_ssq = nullptr;
+    unsigned* chain_tickets = nullptr;
+    unsigned* chain_done = nullptr;
 };
 
 struct ferric_qmatrix {
@@ -44,5 +50,16 @@ struct DeviceGuard {
 
 // Grow the context's activation scratch (stream-ordered); defined in ffi.cu.
 int32_t ensure_scratch(ferric_cuda_ctx* ctx, size_t bytes);
+
+}  // namespace ferric
+
+struct ferric_chain_link;
+
+namespace ferric {
+
+// Argument checks of a chain link and the Chain record for its launch (the exchange parts are the caller's); defined
+// in ffi.cu.
+int32_t chain_setup(ferric_cuda_ctx* ctx, const ferric_chain_link* link, size_t m, bool pushed, Chain* chain,
+                    const void** frag_in, Epilogue* epi, size_t* ldy);
 
 }  // namespace ferric

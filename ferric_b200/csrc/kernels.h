@@ -28,6 +28,7 @@ struct PeerSum {
     const unsigned* epoch = nullptr;   // local: how many exchanges of this kind this rank has signalled
     int* status = nullptr;             // set to 1 if a wait ran out
     int world = 0;                     // 0 = no exchange
+    int wait_spins = 4000000;          // polls of a peer's flag before the wait gives up (about a second)
 };
 
 // The same exchange done by pushing: the row-parallel product's epilogue stores every output value, paired with the
@@ -47,6 +48,7 @@ struct PushSrc {                      // consumer side
     int* status = nullptr;            // set to 1 if a wait ran out
     size_t elems = 0;
     int world = 0;                    // 0 = not a push exchange
+    int wait_spins = 1000000;         // polling rounds (each a trip to L2 for every rank's pairs) before a wait gives up
 };
 
 // The two-step pushed all-reduce of a whole activation matrix (kernels_tpwide.cu), seen from one rank.
@@ -61,6 +63,7 @@ struct WideDst {
     size_t slice = 0;                 // floats per rank's slice, a multiple of 4
     size_t parity_stride1 = 0, parity_stride2 = 0;   // pairs
     int world = 0, rank = 0;
+    int wait_spins = 1000000;         // polling rounds (about a second) before a wait gives up
 };
 // (sum, norm) = add_rmsnorm(a, all-reduce(partial)) over the ranks of `dst`; rows x d floats, d a multiple of 4.
 // `steps`: 1 scatter, 2 reduce, 4 consume (7 = the whole exchange).
@@ -69,6 +72,38 @@ int32_t launch_wide_allreduce_add_rmsnorm(cudaStream_t st, const float* partial,
                                           const struct GemvTuning& tune, int steps = 7);
 
 enum Epilogue : int { kEpiStore = 0, kEpiSwiglu = 1, kEpiPush = 2 };
+
+// A link of a decoder layer's chain of products: what one GEMV launch does besides the product itself, so that the
+// layer needs no launches between its products.
+//  * Input side: the activations may have been prepared un-normalised (h * weight) by the preceding link's residual
+//    job; the product is then scaled by 1 / sqrt(mean(h^2) + eps), with the squares summed per 256-wide block by that
+//    job -- the scalar commutes with the product, so nothing has to wait for the whole row before it is converted.
+//  * Output side, the "job": every warp that stores a 16-row tile of the result takes a ticket of the tile's 256-wide
+//    block; the warp that takes the sixteenth turns the block into the next product's activation fragments, optionally
+//    adding it to the residual stream first (kinds 2, 3).  Kind 3 reads the block from the pairs all ranks pushed.
+struct ChainJob {
+    int kind = 0;                   // 0 none, 1 prepare y, 2 h += y and prepare h * weight, 3 as 2 with y = sum over ranks of the pushed pairs
+    int out_ty = 0;                 // fragment format of the next product: kGgmlQ4K (also Q5_K) or kGgmlQ6K
+    int blocks = 0;                 // 256-wide blocks of the result that feed the next product (= its super-blocks per row)
+    int tiles = 0;                  // activation tiles of two rows (padded as the GEMV pads them)
+    unsigned* tickets = nullptr;    // [blocks], zero between launches
+    unsigned* done = nullptr;       // kind 3: jobs finished; the last one closes the exchange
+    const float* y = nullptr;       // kinds 1, 2: the product's own result, row stride ldy
+    size_t ldy = 0;
+    uint2* frag = nullptr;          // the next product's fragments
+    float* h = nullptr;             // kinds 2, 3: residual stream [m, 256 * blocks], updated in place
+    const float* weight = nullptr;  // RMSNorm weight or null
+    float* ssq = nullptr;           // kinds 2, 3: [activation row][blocks] sums of squares of the updated residual
+    PushSrc pushed;                 // kind 3
+};
+struct Chain {
+    const float* ssq_in = nullptr;  // [activation row][ssq_blocks], or null: no scaling
+    int ssq_blocks = 0;
+    float eps = 0.0f, d = 1.0f;     // row length of the normalised vector, as a float
+    ChainJob job;
+};
+constexpr size_t kChainMaxBlocks = 1024;   // super-blocks per row a chained product may have on either side
+constexpr size_t kChainMaxRows = 8;        // activation rows of a chained product (one GEMV pass)
 
 // Workspace of the unit-balanced GEMV: warps whose run of units starts or ends inside a row tile leave their partial
 // sums here, and the last one to arrive at a tile (a ticket per tile) adds them in warp order and stores the result.
@@ -88,6 +123,7 @@ struct GemvTuning {
     bool stream = false;    // Q6_K plain / pushed GEMV in its unit-balanced form (FERRIC_CUDA_GEMV_STREAM=1; measured no faster)
     int stream_ctas = 0;    // its grid; 0 = one CTA per resident slot (FERRIC_CUDA_GEMV_STREAM_CTAS, for tests on small matrices)
     SplitWs split_ws;       // the context's workspace for that (not a tunable: it rides here to reach the launchers)
+    int wait_spins = 0;     // bound of every wait on a peer, in polling rounds (FERRIC_CUDA_PEER_WAIT_SPINS; 0 = the defaults, about a second)
     bool pdl = true;   // programmatic dependent launch between consecutive kernels (FERRIC_CUDA_PDL=0 disables)
 };
 
@@ -112,8 +148,12 @@ int32_t launch_tp_signal(cudaStream_t st, unsigned* epoch, unsigned* const* peer
 // y[m, rows] (row stride ldy) = x . W^T from prepared fragments.  With kEpiSwiglu the matrix is
 // [gate rows | up rows] and y is [m, rows/2] = silu(gate) * up.
 // With kEpiPush y is not written: the values go to every rank named by `push` (ldy = row length there).
+// `chain` (one pass of at most kChainMaxRows activation rows only) adds the input scaling and the output job above.
 int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const void* frag, size_t m, float* y,
-                    size_t ldy, Epilogue epi, const GemvTuning& tune, const PushDst& push = PushDst());
+                    size_t ldy, Epilogue epi, const GemvTuning& tune, const PushDst& push = PushDst(),
+                    const Chain* chain = nullptr);
+// Activation tiles (of two rows) the GEMV works on for m rows, padded to whole passes.
+size_t gemv_padded_tiles(size_t m);
 // Q8_0 needs no fragments: y = x . W^T straight from f32 activations.
 int32_t launch_gemv_q8_0(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y,
                          size_t ldy, const GemvTuning& tune);

@@ -173,9 +173,8 @@ prep_kernel(const float* __restrict__ x, size_t m, size_t ldx, size_t nblk, size
     prep_block<TY>(v, sm[warp], tile, nblk, blk, frag);
 }
 
-// A bounded wait on a peer: ~1 s of polling, then the kernel records the failure and carries on.
-constexpr int kPeerWaitSpins = 4000000;
-constexpr int kPushWaitSpins = 1000000;   // one round of polls is a trip to L2 for every rank's pairs
+// Every wait on a peer is bounded (PeerSum / PushSrc::wait_spins, about a second of polling by default): when it runs
+// out the kernel records the failure in the exchange's status word and carries on.
 
 // Sum of all ranks' partials at float offset `off`, in rank order (the same order on every rank,
 // so every rank forms bit-identical sums).  Peer memory is read uncached: it changes between
@@ -323,7 +322,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
     if (PEERS == 2) {
         // a wait that ran out earlier stays recorded: later kernels then do not wait again, so a lost peer costs one
         // bound, not one per kernel
-        wait_limit = *reinterpret_cast<volatile int*>(pushed.status) ? 0 : kPushWaitSpins;
+        wait_limit = *reinterpret_cast<volatile int*>(pushed.status) ? 0 : pushed.wait_spins;
         asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(want) : "l"(pushed.epoch));
         want += 1;
         recv = pushed.recv + (size_t)(want & 1) * pushed.world * pushed.elems;
@@ -338,7 +337,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
             for (;;) {
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(peers.flags + threadIdx.x) : "memory");
                 if ((int)(seen - want) >= 0) break;
-                if (++spins > kPeerWaitSpins) {
+                if (++spins > peers.wait_spins) {
                     *peers.status = 1;
                     break;
                 }
@@ -456,6 +455,8 @@ static size_t padded_tiles(size_t m)
     size_t nt = (size_t)tiles_per_pass(m), ntiles = (m + kRowsPerTile - 1) / kRowsPerTile;
     return (ntiles + nt - 1) / nt * nt;
 }
+
+size_t gemv_padded_tiles(size_t m) { return padded_tiles(m); }
 
 size_t frag_bytes(uint32_t ty, const DeviceWeights& w, size_t m)
 {
@@ -579,10 +580,112 @@ __device__ __forceinline__ void store_result(float* __restrict__ y, size_t ldy, 
     }
 }
 
-template <int NT, int EPI>
+// The job of a chain link (kernels.h, ChainJob): turn block `blk` of the result -- complete in memory, or, for the
+// pushed exchange, arriving in this rank's receive region -- into the next product's activation fragments.  Run by one
+// whole warp; `sm` is scratch of that warp (its weight ring, drained by now).
+template <int EPI>
+__device__ __forceinline__ void chain_job(const ChainJob& j, int blk, int m, PrepSmem& sm)
+{
+    const int lane = threadIdx.x & 31, prow = lane >> 4, q = lane & 15;
+    if (lane == 0) j.tickets[blk] = 0;   // ready for the next launch
+    __threadfence();                     // the other tiles' stores came before their tickets
+    unsigned want = 0;
+    const uint2* recv = nullptr;
+    int wait_limit = 0;
+    if (EPI == kEpiPush && j.kind == 3) {
+        wait_limit = *reinterpret_cast<volatile int*>(j.pushed.status) ? 0 : j.pushed.wait_spins;
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(want) : "l"(j.pushed.epoch));
+        want += 1;
+        recv = j.pushed.recv + (size_t)(want & 1) * j.pushed.world * j.pushed.elems;
+    }
+    const size_t nblk = (size_t)j.blocks, d = nblk * 256;
+    for (int tile = 0; tile < j.tiles; tile++) {
+        const size_t batch = (size_t)tile * kRowsPerTile + (size_t)prow;
+        const bool valid = batch < (size_t)m;   // the same for the 16 lanes of a row
+        float4 f[4];
+        float ms = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) f[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid) {
+            if (EPI == kEpiPush && j.kind == 3) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) pushed_sum<1, kMaxRanks>(j.pushed, recv, batch * d + (size_t)blk * 256 + 16 * q + 4 * i, want, wait_limit, f + i);
+            } else {
+                const float4* yp = reinterpret_cast<const float4*>(j.y + batch * j.ldy + (size_t)blk * 256 + 16 * q);
+#pragma unroll
+                for (int i = 0; i < 4; i++) f[i] = __ldcg(yp + i);
+            }
+            if (j.kind >= 2) {
+                float4* hp = reinterpret_cast<float4*>(j.h + batch * d + (size_t)blk * 256 + 16 * q);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float4 a = __ldcg(hp + i);
+                    f[i].x = a.x + f[i].x; f[i].y = a.y + f[i].y; f[i].z = a.z + f[i].z; f[i].w = a.w + f[i].w;
+                    hp[i] = f[i];
+                    ms = fmaf(f[i].x, f[i].x, ms); ms = fmaf(f[i].y, f[i].y, ms); ms = fmaf(f[i].z, f[i].z, ms); ms = fmaf(f[i].w, f[i].w, ms);
+                }
+            }
+        }
+        if (j.kind >= 2) {
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) ms += __shfl_xor_sync(0xffffffffu, ms, o);
+            if (valid && q == 0) j.ssq[batch * nblk + (size_t)blk] = ms;
+            if (valid && j.weight) {
+                const float4* wp = reinterpret_cast<const float4*>(j.weight + (size_t)blk * 256 + 16 * q);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float4 w4 = __ldg(wp + i);
+                    f[i].x *= w4.x; f[i].y *= w4.y; f[i].z *= w4.z; f[i].w *= w4.w;
+                }
+            }
+        }
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            v[4 * i] = f[i].x; v[4 * i + 1] = f[i].y; v[4 * i + 2] = f[i].z; v[4 * i + 3] = f[i].w;
+        }
+        __syncwarp();
+        if (j.out_ty == (int)kGgmlQ6K) prep_block<(int)kGgmlQ6K>(v, sm, (size_t)tile, nblk, (size_t)blk, j.frag);
+        else prep_block<(int)kGgmlQ4K>(v, sm, (size_t)tile, nblk, (size_t)blk, j.frag);
+    }
+    if (EPI == kEpiPush && j.kind == 3) {
+        // the last job to finish closes the exchange: every tile of this launch has been pushed by then
+        __threadfence();
+        __syncwarp();
+        if (lane == 0 && atomicAdd(j.done, 1u) == (unsigned)j.blocks - 1u) {
+            *j.done = 0;
+            asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(j.pushed.epoch), "r"(want) : "memory");
+        }
+    }
+}
+
+// 1 / sqrt(mean of squares + eps) of the activation rows this lane's result columns belong to (Chain::ssq_in), summed
+// over the blocks in block order -- the order of the one-CTA norm kernel with a warp per block.
+template <int NT, bool CHAIN>
+__device__ __forceinline__ void chain_scales(float (&inv)[NT], const Chain& chain, int tile0, int m)
+{
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) inv[nt] = 1.0f;
+    if (CHAIN && chain.ssq_in) {
+        const int t = threadIdx.x & 3;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
+            if (batch < m) {
+                const float* p = chain.ssq_in + (size_t)batch * chain.ssq_blocks;
+                float tot = 0.0f;
+                for (int i = 0; i < chain.ssq_blocks; i++) tot += __ldcg(p + i);
+                inv[nt] = 1.0f / sqrtf(tot / chain.d + chain.eps);
+            }
+        }
+    }
+}
+
+template <int NT, int EPI, bool CHAIN = false>
 __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*red)[NT * 4][32], float* __restrict__ y,
                                                  size_t ldy, int rows, int m, int tile0, int wk, int out_tile,
-                                                 bool active, const PushDst& push)
+                                                 bool active, const PushDst& push, const float (&inv)[NT], const Chain& chain,
+                                                 uint8_t* warp_smem)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int kpart = warp % wk, wr = warp / wk;
@@ -613,16 +716,36 @@ __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*re
         float lo = v[0] * w0 + v[1] * w1, hi = v[2] * w0 + v[3] * w1;
         lo += __shfl_xor_sync(0xffffffffu, lo, 1);
         hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+        if (CHAIN) {
+            lo *= inv[nt];
+            hi *= inv[nt];
+        }
         if (EPI == kEpiSwiglu) {
             float ulo = u[0] * w0 + u[1] * w1, uhi = u[2] * w0 + u[3] * w1;
             ulo += __shfl_xor_sync(0xffffffffu, ulo, 1);
             uhi += __shfl_xor_sync(0xffffffffu, uhi, 1);
+            if (CHAIN) {
+                ulo *= inv[nt];
+                uhi *= inv[nt];
+            }
             lo = silu_mul(lo, ulo);
             hi = silu_mul(hi, uhi);
         }
         const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
         const int r0 = out_tile * 16 + g;
         if ((t & 1) == 0 && batch < m) store_result<EPI>(y, ldy, rows, batch, r0, lo, hi, push);
+    }
+    if (CHAIN) {
+        // this warp stored one 16-row tile of the result for every activation row; the warp that completes a 256-wide
+        // block runs the block's job
+        if (chain.job.kind != 0 && (out_tile >> 4) < chain.job.blocks) {
+            __threadfence();
+            __syncwarp();
+            unsigned seen = 0;
+            if (lane == 0) seen = atomicAdd(chain.job.tickets + (out_tile >> 4), 1u);
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            if (seen == 15u) chain_job<EPI>(chain.job, out_tile >> 4, m, *reinterpret_cast<PrepSmem*>(warp_smem));
+        }
     }
 }
 
@@ -692,10 +815,10 @@ __device__ __forceinline__ void q4k_row(const uint4& h, Q4KRow& r)
 
 // Q5 = true is the Q5_K kernel (crates/ferric-tensor/src/dtype.rs:1049-1071): the same product with 5-bit quants -- the
 // fifth bit of each weight is OR-ed into its byte before the integer MMA; header, scales and mins are Q4_K's.
-template <int NT, int EPI, bool Q5 = false>
+template <int NT, int EPI, bool Q5 = false, bool CHAIN = false>
 __global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
-                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push)
+                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push, Chain chain)
 {
     __shared__ float red[8][NT * 4][32];
     constexpr int kUnitBytes = Q5 ? kQ5KUnit : kQ4KUnit;
@@ -734,6 +857,8 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
         }
     }
     pdl_wait();
+    float inv[NT];
+    chain_scales<NT, CHAIN>(inv, chain, tile0, m);
     if (work) {
         const uint2* fsrc[NT];                                                 // fragments of the next unit to use
 #pragma unroll
@@ -841,7 +966,8 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             }
         }
     }
-    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push);
+    reduce_and_store<NT, EPI, CHAIN>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push, inv,
+                                     chain, ring);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -947,10 +1073,10 @@ __device__ __forceinline__ void q6k_unit_mac(const Q6KUnit& cur, const uint2 (&b
     }
 }
 
-template <int NT, int EPI>
+template <int NT, int EPI, bool CHAIN = false>
 __global__ void __launch_bounds__(256, NT <= 2 ? 2 : 1)
 gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ frag, float* __restrict__ y, int rows,
-                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push)
+                int nblk, int m, size_t ldy, int row_tiles, int wk, int ff_tiles, PushDst push, Chain chain)
 {
     __shared__ float red[8][NT * 4][32];
     pdl_launch_dependents();
@@ -988,6 +1114,8 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
         }
     }
     pdl_wait();
+    float inv[NT];
+    chain_scales<NT, CHAIN>(inv, chain, tile0, m);
     if (work) {
         const uint2* fsrc[NT];                                                 // fragments of the next unit to use
 #pragma unroll
@@ -1042,7 +1170,8 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
             }
         }
     }
-    reduce_and_store<NT, EPI>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push);
+    reduce_and_store<NT, EPI, CHAIN>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push, inv,
+                                     chain, ring);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1253,10 +1382,10 @@ static int choose_wk(uint32_t ty, const DeviceWeights& w, Epilogue epi, int nt, 
     return best;
 }
 
-template <int NT, int EPI>
+template <int NT, int EPI, bool CHAIN>
 static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint2* frag, size_t m, float* y,
                           size_t ldy, int wk, unsigned passes, bool pdl, const PushDst& push, const SplitWs& split,
-                          bool stream, int stream_ctas, int sm_count)
+                          bool stream, int stream_ctas, int sm_count, const Chain& chain)
 {
     const int row_tiles = (int)w.row_tiles(), wr = 8 / wk;
     const int ff_tiles = (int)(w.rows / 2 / 16);
@@ -1268,27 +1397,27 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
     cudaGetDevice(&dev);
     if (ty == kGgmlQ4K) {
         if (attr_dev_q4 != dev) {
-            cudaFuncSetAttribute(gemv_q4k_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ4K);
+            cudaFuncSetAttribute(gemv_q4k_kernel<NT, EPI, false, CHAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ4K);
             attr_dev_q4 = dev;
         }
-        launch_kernel(gemv_q4k_kernel<NT, EPI>, grid, dim3(256), kSmemQ4K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
+        launch_kernel(gemv_q4k_kernel<NT, EPI, false, CHAIN>, grid, dim3(256), kSmemQ4K, st, pdl, w.units, frag, y, (int)w.rows,
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push, chain);
     } else if (ty == kGgmlQ5K) {
         static thread_local int attr_dev_q5 = -1;
         if (attr_dev_q5 != dev) {
-            cudaFuncSetAttribute(gemv_q4k_kernel<NT, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ5K);
+            cudaFuncSetAttribute(gemv_q4k_kernel<NT, EPI, true, CHAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ5K);
             attr_dev_q5 = dev;
         }
-        launch_kernel(gemv_q4k_kernel<NT, EPI, true>, grid, dim3(256), kSmemQ5K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
+        launch_kernel(gemv_q4k_kernel<NT, EPI, true, CHAIN>, grid, dim3(256), kSmemQ5K, st, pdl, w.units, frag, y, (int)w.rows,
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push, chain);
     } else {
         if (attr_dev_q6 != dev) {
-            cudaFuncSetAttribute(gemv_q6k_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ6K);
-            if (EPI != kEpiSwiglu)
+            cudaFuncSetAttribute(gemv_q6k_kernel<NT, EPI, CHAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ6K);
+            if (EPI != kEpiSwiglu && !CHAIN)
                 cudaFuncSetAttribute(gemv_q6k_stream_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemQ6K);
             attr_dev_q6 = dev;
         }
-        if constexpr (EPI != kEpiSwiglu) {
+        if constexpr (EPI != kEpiSwiglu && !CHAIN) {
             // the unit-balanced form: one resident CTA per slot, every warp an equal share of the units
             const unsigned ctas = stream_ctas > 0 ? (unsigned)stream_ctas : (unsigned)sm_count * (NT <= 2 ? 2u : 1u);
             const size_t total = (size_t)row_tiles * w.nblk, warps = (size_t)ctas * 8;
@@ -1299,26 +1428,35 @@ static void launch_gemv_t(cudaStream_t st, uint32_t ty, const DeviceWeights& w, 
                 return;
             }
         }
-        launch_kernel(gemv_q6k_kernel<NT, EPI>, grid, dim3(256), kSmemQ6K, st, pdl, w.units, frag, y, (int)w.rows,
-                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push);
+        launch_kernel(gemv_q6k_kernel<NT, EPI, CHAIN>, grid, dim3(256), kSmemQ6K, st, pdl, w.units, frag, y, (int)w.rows,
+                      (int)w.nblk, (int)m, ldy, row_tiles, wk, ff_tiles, push, chain);
     }
 }
 
 int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const void* frag, size_t m, float* y,
-                    size_t ldy, Epilogue epi, const GemvTuning& tune, const PushDst& push)
+                    size_t ldy, Epilogue epi, const GemvTuning& tune, const PushDst& push, const Chain* chain)
 {
     if (m == 0 || w.rows == 0) return kOk;
     const int nt = tiles_per_pass(m), wk = choose_wk(ty, w, epi, nt, tune);
     const unsigned passes = (unsigned)(padded_tiles(m) / (size_t)nt);
     const uint2* f = reinterpret_cast<const uint2*>(frag);
-#define FERRIC_GEMV_CASE(NT_)                                                                             \
-    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count);   \
-    else if (epi == kEpiPush) launch_gemv_t<NT_, kEpiPush>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count); \
-    else launch_gemv_t<NT_, kEpiSwiglu>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count)
-    if (nt == 1) { FERRIC_GEMV_CASE(1); }
-    else if (nt == 2) { FERRIC_GEMV_CASE(2); }
-    else { FERRIC_GEMV_CASE(4); }
+    if (chain && passes != 1) {
+        set_last_error("a chained product takes at most %zu activation rows", kChainMaxRows);
+        return kErrShape;
+    }
+    const Chain none;
+#define FERRIC_GEMV_CASE2(NT_, CH_, ARG_)                                                                 \
+    if (epi == kEpiStore) launch_gemv_t<NT_, kEpiStore, CH_>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count, ARG_);   \
+    else if (epi == kEpiPush) launch_gemv_t<NT_, kEpiPush, CH_>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count, ARG_); \
+    else launch_gemv_t<NT_, kEpiSwiglu, CH_>(st, ty, w, f, m, y, ldy, wk, passes, tune.pdl, push, tune.split_ws, tune.stream, tune.stream_ctas, tune.sm_count, ARG_)
+#define FERRIC_GEMV_CASE(NT_)                         \
+    if (chain) { FERRIC_GEMV_CASE2(NT_, true, *chain); } \
+    else { FERRIC_GEMV_CASE2(NT_, false, none); }
+    if (nt == 1) { FERRIC_GEMV_CASE(1) }
+    else if (nt == 2) { FERRIC_GEMV_CASE(2) }
+    else { FERRIC_GEMV_CASE(4) }
 #undef FERRIC_GEMV_CASE
+#undef FERRIC_GEMV_CASE2
     FERRIC_CUDA_TRY(cudaGetLastError());
     return kOk;
 }

@@ -17,7 +17,6 @@ namespace ferric {
 
 namespace {
 
-constexpr int kWideWaitSpins = 1000000;   // rounds of polling (about a second) before a wait gives up
 
 __device__ __forceinline__ unsigned wide_stamp(const unsigned* epoch)
 {
@@ -66,7 +65,7 @@ __global__ void __launch_bounds__(256) wide_reduce_kernel(size_t n, WideDst dst)
     const size_t off = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (off >= len) return;
     const uint2* mine = dst.recv1 + (size_t)(stamp & 1) * dst.parity_stride1 + off;   // [source rank][slice]
-    const int limit = *reinterpret_cast<volatile int*>(dst.status) ? 0 : kWideWaitSpins;
+    const int limit = *reinterpret_cast<volatile int*>(dst.status) ? 0 : dst.wait_spins;
     uint4 a[kMaxRanks], b[kMaxRanks];
     int spins = 0;
     for (;;) {
@@ -107,7 +106,7 @@ __global__ void __launch_bounds__(256) wide_add_rmsnorm_kernel(const float* __re
     pdl_launch_dependents();
     pdl_wait();
     const unsigned stamp = wide_stamp(dst.epoch);
-    const int limit = *reinterpret_cast<volatile int*>(dst.status) ? 0 : kWideWaitSpins;
+    const int limit = *reinterpret_cast<volatile int*>(dst.status) ? 0 : dst.wait_spins;
     const size_t base = blockIdx.x * d;
     const uint2* pairs = dst.recv2 + (size_t)(stamp & 1) * dst.parity_stride2 + base;
     float ms = 0.0f;

@@ -11,9 +11,12 @@
 //   3. the consumer (the fused add + rmsnorm + prepare kernel) waits, bounded, until all flag
 //      slots have reached its own count, then reads every rank's partial with plain peer loads
 //      and sums them in rank order -- bit-identical on every rank.
-// Buffers never need a second copy: a rank can only signal exchange n+1 of a kind after its own
-// consumer of exchange n ran, and that consumer ran only after every peer had signalled n, i.e.
-// had finished the step that read exchange n-1.  No multicast, no multimem: peer loads/stores only.
+// One buffer per kind suffices only because consecutive exchanges alternate between the two kinds (after o, after
+// down, after o, ...): a rank overwrites its kind-k buffer for exchange n+1 after its own consumer of the kind-(1-k)
+// exchange in between ran, which needed every peer's signal for that exchange, which each peer gave only after its
+// consumer of the kind-k exchange n had finished reading.  The same kind twice in a row would let a rank overwrite a
+// buffer a slower peer is still reading, so ferric_cuda_tp_signal refuses it.  No multicast, no multimem: peer
+// loads/stores only.
 //
 // The pushed form of the same exchange (tp_matmul_push + tp_add_rmsnorm_prepare_pushed) takes the
 // signal kernel and the round trip of the peer loads off the critical path: the product's epilogue
@@ -51,6 +54,7 @@ struct ferric_tp_group {
     void* peer_base[kMaxRanks] = {};  // IPC mappings of the peers' `local`
     bool connected = false;
     bool local_peers = false;         // peers are groups of this process (no IPC mappings to close)
+    int last_signal_kind = -1;        // the signalled (pull) form keeps one buffer per kind: kinds must alternate
 };
 
 namespace {
@@ -71,6 +75,26 @@ size_t off_wide1(size_t elems, int world) { return off_wide_meta(elems, world) +
 size_t off_wide2(size_t elems, int world) { return off_wide1(elems, world) + 4 * wide_pairs(elems, world) * sizeof(uint2); }
 size_t total_bytes(size_t elems, int world) { return off_wide2(elems, world) + 4 * wide_pairs(elems, world) * sizeof(uint2); }
 }  // namespace
+
+static void fill_push_dst(const ferric_tp_group* g, int kind, PushDst& p)
+{
+    p.world = g->world;
+    p.epoch = g->push_epoch + kind;
+    p.parity_stride = recv_pairs(g->elems, g->world);
+    for (int r = 0; r < g->world; r++)
+        p.dst[r] = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(g->peer_base[r]) + off_recv(g->elems)) +
+                   (size_t)kind * 2 * p.parity_stride + (size_t)g->rank * g->elems;
+}
+static void fill_push_src(const ferric_cuda_ctx* ctx, const ferric_tp_group* g, int kind, PushSrc& p)
+{
+    p.world = g->world;
+    p.elems = g->elems;
+    p.recv = g->recv + (size_t)kind * 2 * recv_pairs(g->elems, g->world);
+    p.epoch = g->push_epoch + kind;
+    p.ticket = g->push_ticket + kind;
+    p.status = g->status;
+    if (ctx->tune.wait_spins > 0) p.wait_spins = ctx->tune.wait_spins;
+}
 
 extern "C" {
 
@@ -207,6 +231,11 @@ int32_t ferric_cuda_tp_signal(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t 
         set_last_error("tp_signal: NULL / unconnected group or bad kind");
         return kErrInvalidArg;
     }
+    if (g->world > 1 && kind == g->last_signal_kind) {
+        set_last_error("tp_signal: exchange kind %d signalled twice in a row; the signalled form has one buffer per kind and must alternate kinds", kind);
+        return kErrInvalidArg;
+    }
+    g->last_signal_kind = kind;
     DeviceGuard guard(ctx->device);
     ctx->launches++;
     return launch_tp_signal(ctx->stream, g->epoch + kind, g->slot_table[kind], g->world, ctx->tune);
@@ -236,6 +265,7 @@ int32_t ferric_cuda_tp_add_rmsnorm_prepare(ferric_cuda_ctx* ctx, ferric_tp_group
     p.flags = g->flags[kind];
     p.epoch = g->epoch + kind;
     p.status = g->status;
+    if (ctx->tune.wait_spins > 0) p.wait_spins = ctx->tune.wait_spins;
     ctx->launches++;
     return launch_norm_prep(ctx->stream, qm->ty, qm->w, a_dev, nullptr, weight_dev, eps, m, sum_dev, norm_dev, ctx->scratch,
                             ctx->tune, p);
@@ -269,12 +299,7 @@ int32_t ferric_cuda_tp_matmul_push(ferric_cuda_ctx* ctx, ferric_tp_group* g, int
     rc = launch_prep(ctx->stream, qm->ty, qm->w, x_dev, m, ldx, ctx->scratch, ctx->tune);
     if (rc != kOk) return rc;
     PushDst p;
-    p.world = g->world;
-    p.epoch = g->push_epoch + kind;
-    p.parity_stride = recv_pairs(g->elems, g->world);
-    for (int r = 0; r < g->world; r++)
-        p.dst[r] = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(g->peer_base[r]) + off_recv(g->elems)) +
-                   (size_t)kind * 2 * p.parity_stride + (size_t)g->rank * g->elems;
+    fill_push_dst(g, kind, p);
     ctx->launches += 2;
     return launch_gemv(ctx->stream, qm->ty, qm->w, ctx->scratch, m, nullptr, qm->w.rows, kEpiPush, ctx->tune, p);
 }
@@ -297,12 +322,7 @@ int32_t ferric_cuda_tp_add_rmsnorm_prepare_pushed(ferric_cuda_ctx* ctx, ferric_t
     int32_t rc = ensure_scratch(ctx, frag_bytes(qm->ty, qm->w, m));
     if (rc != kOk) return rc;
     PushSrc p;
-    p.world = g->world;
-    p.elems = g->elems;
-    p.recv = g->recv + (size_t)kind * 2 * recv_pairs(g->elems, g->world);
-    p.epoch = g->push_epoch + kind;
-    p.ticket = g->push_ticket + kind;
-    p.status = g->status;
+    fill_push_src(ctx, g, kind, p);
     ctx->launches++;
     return launch_norm_prep(ctx->stream, qm->ty, qm->w, a_dev, nullptr, weight_dev, eps, m, sum_dev, norm_dev, ctx->scratch,
                             ctx->tune, PeerSum(), p);
@@ -345,6 +365,7 @@ int32_t ferric_cuda_tp_allreduce_add_rmsnorm_steps(ferric_cuda_ctx* ctx, ferric_
     w.epoch = g->wide_epoch + kind;
     w.ticket = g->wide_ticket + kind;
     w.status = g->status;
+    if (ctx->tune.wait_spins > 0) w.wait_spins = ctx->tune.wait_spins;
     uint8_t* local = reinterpret_cast<uint8_t*>(g->local);
     w.recv1 = reinterpret_cast<const uint2*>(local + off_wide1(g->elems, g->world)) + (size_t)kind * 2 * pairs;
     w.recv2 = reinterpret_cast<const uint2*>(local + off_wide2(g->elems, g->world)) + (size_t)kind * 2 * pairs;
@@ -373,6 +394,53 @@ int32_t ferric_cuda_tp_status(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t*
         set_last_error("a peer did not announce its partial within the wait bound");
         return kErrTimeout;
     }
+    return kOk;
+}
+
+int32_t ferric_cuda_tp_chain_matmul(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t kind, const ferric_chain_link* link, size_t m)
+{
+    if (!g || kind < 0 || kind > 1 || !g->connected) {
+        set_last_error("tp_chain_matmul: NULL / unconnected group or bad kind");
+        return kErrInvalidArg;
+    }
+    Chain chain;
+    const void* frag = nullptr;
+    Epilogue epi = kEpiStore;
+    size_t ldy = 0;
+    int32_t rc = chain_setup(ctx, link, m, true, &chain, &frag, &epi, &ldy);
+    if (rc != kOk) return rc;
+    const ferric_qmatrix* qm = link->qm;
+    if (m * qm->w.rows > g->elems) {
+        set_last_error("exchange buffers hold %zu floats, %zu x %zu requested", g->elems, m, qm->w.rows);
+        return kErrShape;
+    }
+    if (m == 0 || qm->w.rows == 0) return kOk;
+    if (qm->w.nblk == 0) {
+        set_last_error("tp_chain_matmul: empty K range");
+        return kErrShape;
+    }
+    DeviceGuard guard(ctx->device);
+    PushDst p;
+    fill_push_dst(g, kind, p);
+    fill_push_src(ctx, g, kind, chain.job.pushed);
+    ctx->launches++;
+    // ldy of a pushed product is the row length in the receive regions
+    return launch_gemv(ctx->stream, qm->ty, qm->w, frag, m, nullptr, qm->w.rows, kEpiPush, ctx->tune, p, &chain);
+}
+
+int32_t ferric_cuda_tp_reset(ferric_cuda_ctx* ctx, ferric_tp_group* g)
+{
+    if (!ctx || !g) {
+        set_last_error("NULL argument");
+        return kErrInvalidArg;
+    }
+    DeviceGuard guard(ctx->device);
+    FERRIC_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    // everything but the peers' slot tables: partial buffers, flags, counters, status, receive regions
+    uint8_t* base = reinterpret_cast<uint8_t*>(g->local);
+    FERRIC_CUDA_TRY(cudaMemset(base, 0, off_slots(g->elems)));
+    FERRIC_CUDA_TRY(cudaMemset(base + off_push_meta(g->elems), 0, g->local_bytes - off_push_meta(g->elems)));
+    g->last_signal_kind = -1;
     return kOk;
 }
 

@@ -95,6 +95,10 @@ class Context:
     def reserve_scratch(self, nbytes: int) -> None:
         _check(self._lib.ferric_cuda_ctx_reserve_scratch(self._h, nbytes), "reserve_scratch")
 
+    def chain_reserve(self, slot_bytes: int) -> None:
+        """Size the two prepared-activation slots chained products use (``ferric_cuda_chain_reserve``)."""
+        _check(self._lib.ferric_cuda_chain_reserve(self._h, slot_bytes), "chain_reserve")
+
     def deq_raw(self, raw, n: int, ggml_type: int) -> np.ndarray:
         """``ferric_gguf::deq_raw`` (crates/ferric-gguf/src/lib.rs:497-520), decoded on the device."""
         raw = _as_u8(raw)
@@ -290,6 +294,24 @@ class QMatrix:
                "matmul_q_prepared")
         return y
 
+    def _link(self, m: int, out: Optional[torch.Tensor], swiglu: bool, in_slot: int, in_rms: bool, eps: float, next: int,
+              next_qm: Optional["QMatrix"], h: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor]) -> "_lib.ChainLink":
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        ldy = out.stride(0) if (out is not None and out.dim() == 2 and m > 1) else 0
+        return _lib.ChainLink(self._h, int(swiglu), in_slot, int(in_rms), float(eps), ptr(out), ldy, next,
+                              next_qm._h if next_qm is not None else None, ptr(h), ptr(norm_weight))
+
+    def chain_matmul(self, m: int, out: torch.Tensor, swiglu: bool = False, in_slot: int = 0, in_rms: bool = False,
+                     eps: float = 1e-6, next: int = 0, next_qm: Optional["QMatrix"] = None, h: Optional[torch.Tensor] = None,
+                     norm_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One link of a decoder layer's chain (``ferric_cuda_chain_matmul``): the product from prepared-activation
+        slot ``in_slot``, then, in the same launch, what the next product needs -- ``next=1`` prepares the result for
+        ``next_qm``, ``next=2`` adds it to the residual stream ``h`` first and leaves the 1/rms factor to the next link
+        (``in_rms``).  Returns ``out``."""
+        link = self._link(m, out, swiglu, in_slot, in_rms, eps, next, next_qm, h, norm_weight)
+        _check(self._lib.ferric_cuda_chain_matmul(self.ctx._h, C.byref(link), m), "chain_matmul")
+        return out
+
     def matmul_host(self, x: np.ndarray) -> np.ndarray:
         """The same product with host buffers (copies in, runs, copies out, synchronises)."""
         x = np.ascontiguousarray(x, dtype=np.float32)
@@ -417,10 +439,21 @@ class TPGroup:
         ldx = x.stride(0) if x.dim() == 2 else x.shape[-1]
         _check(self._lib.ferric_cuda_tp_matmul_push(self.ctx._h, self._h, kind, qm._h, x.data_ptr(), m, ldx), "tp_matmul_push")
 
+    def chain_matmul(self, kind: int, qm: "QMatrix", m: int, in_slot: int, next_qm: "QMatrix", h: torch.Tensor,
+                     norm_weight: Optional[torch.Tensor] = None) -> None:
+        """A residual chain link whose product is row-parallel (``ferric_cuda_tp_chain_matmul``): push, all-reduce,
+        residual add and preparation of the next product in one launch."""
+        link = qm._link(m, None, False, in_slot, False, 0.0, 2, next_qm, h, norm_weight)
+        _check(self._lib.ferric_cuda_tp_chain_matmul(self.ctx._h, self._h, kind, C.byref(link), m), "tp_chain_matmul")
+
     def check(self) -> None:
         """Synchronise and raise if a wait on a peer ran out."""
         t = C.c_int32(0)
         _check(self._lib.ferric_cuda_tp_status(self.ctx._h, self._h, C.byref(t)), "tp_status")
+
+    def reset(self) -> None:
+        """After a time-out: clear this rank's status, counters and receive regions (every rank must)."""
+        _check(self._lib.ferric_cuda_tp_reset(self.ctx._h, self._h), "tp_reset")
 
     def close(self) -> None:
         if getattr(self, "_h", None):

@@ -82,12 +82,17 @@ class DecodeStack:
     """``n_layers`` decoder layers' worth of packed-quant matmuls for ``batch`` tokens per step."""
 
     def __init__(self, ctx: Context, plan: TPPlan, n_layers: int = 64, batch: int = 1, eps: float = 1e-6,
-                 all_reduce: Optional[AllReduce] = None, group: Optional[TPGroup] = None, push: bool = True):
+                 all_reduce: Optional[AllReduce] = None, group: Optional[TPGroup] = None, push: bool = True,
+                 chain: Optional[bool] = None):
         """`all_reduce`: a callable summing a tensor over ranks in place (e.g. NCCL through torch.distributed).
         `group`: a connected TPGroup -- then the exchange is done by this library's own kernels instead; with
         `push` the o / down products store their partial sums straight into every rank's memory, otherwise each
-        rank signals its buffer and the consumers read the peers' buffers."""
+        rank signals its buffer and the consumers read the peers' buffers.
+        `chain` (default: whenever it applies -- up to 8 tokens, one rank or the pushed exchange): one launch per
+        matrix, the norms, residual adds and activation preparation riding in the products' own launches."""
         self.ctx, self.plan, self.n_layers, self.batch, self.eps = ctx, plan, n_layers, batch, eps
+        can_chain = batch <= 8 and (plan.world == 1 or (group is not None and push))
+        self.chain = can_chain if chain is None else (chain and can_chain)
         self.all_reduce = all_reduce if (plan.world > 1 and group is None) else None
         self.group = group if plan.world > 1 else None
         self.push = push
@@ -139,7 +144,10 @@ class DecodeStack:
         need = 0
         for L in self.layers[:1]:
             need = max(w.scratch_bytes(self.batch) for w in (L.wqkv, L.wo, L.wgu, L.wdown))
-        self.ctx.reserve_scratch(need)
+        if self.chain:
+            self.ctx.chain_reserve(need)
+        else:
+            self.ctx.reserve_scratch(need)
 
     def weight_bytes_per_step(self) -> int:
         return sum(w.nbytes() for L in self.layers for w in (L.wqkv, L.wo, L.wgu, L.wdown))
@@ -156,6 +164,8 @@ class DecodeStack:
         n = len(self.layers)
         if self.batch > 8:
             return self._step_wide(before)
+        if self.chain:
+            return self._step_chain(before)
         m = self.layers[0].wqkv.add_rmsnorm_prepare(self.h, None, None, self.eps)
         G = self.group
         for i, L in enumerate(self.layers):
@@ -187,6 +197,29 @@ class DecodeStack:
                 if self.all_reduce:
                     self.all_reduce(self.d)
                 nxt.add_rmsnorm_prepare(self.h, self.d, None, self.eps, sum_out=self.h, norm_out=last_norm)
+        self.launches_per_step = c.launches() - before
+        return self.h
+
+    def _step_chain(self, before: int) -> torch.Tensor:
+        """The same step as four launches per layer: q|k|v prepares o's input, o adds to the residual stream and prepares
+        gate|up's (whose result takes the 1/rms factor), gate|up+SwiGLU prepares down's, down adds to the residual
+        stream and prepares the next layer's q|k|v.  Slots alternate 0 -> 1 -> 0 -> 1 -> 0 through a layer."""
+        c, p, G = self.ctx, self.plan, self.group
+        n = len(self.layers)
+        m = self.layers[0].wqkv.add_rmsnorm_prepare(self.h, None, None, self.eps)       # slot 0, already normalised
+        for i, L in enumerate(self.layers):
+            nxt = self.layers[i + 1].wqkv if i + 1 < n else self.layers[0].wqkv
+            L.wqkv.chain_matmul(m, self.qkv, in_slot=0, in_rms=i > 0, eps=self.eps, next=1, next_qm=L.wo)
+            if G is not None:
+                G.chain_matmul(0, L.wo, m, 1, L.wgu, self.h)
+            else:
+                L.wo.chain_matmul(m, self.o, in_slot=1, next=2, next_qm=L.wgu, h=self.h)
+            L.wgu.chain_matmul(m, self.f, swiglu=True, in_slot=0, in_rms=True, eps=self.eps, next=1, next_qm=L.wdown)
+            if G is not None:
+                G.chain_matmul(1, L.wdown, m, 1, nxt, self.h)
+            else:
+                L.wdown.chain_matmul(m, self.d, in_slot=1, next=2, next_qm=nxt, h=self.h)
+        c.add_rmsnorm(self.h, None, None, self.eps, norm_out=self.xn)      # after the last layer the norm itself is the result
         self.launches_per_step = c.launches() - before
         return self.h
 

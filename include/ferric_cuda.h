@@ -188,6 +188,45 @@ int32_t ferric_cuda_add_rmsnorm_prepare(ferric_cuda_ctx *ctx, const ferric_qmatr
                                         const float *b_dev, const float *weight_dev, float eps, size_t m,
                                         float *sum_dev, float *norm_dev);
 
+/* ---- chained decoder-layer products ----------------------------------------------------------- */
+/* The reference batches a decoder layer's kernels -- norm, projections, residual adds -- into one submit
+ * (crates/ferric-llama/src/qwen35.rs:985-996, the layer loop :953-1014).  Here the glue between the products moves into
+ * the products' own launches, so a layer is one launch per matrix and nothing else:
+ *   - a link may PREPARE: once a 256-wide block of its result is complete, the warp that stored the block's last tile
+ *     converts it into the activation form of the next product (what ferric_cuda_prepare_x would do in a launch of
+ *     its own) -- e.g. q|k|v -> o, gate|up+SwiGLU -> down;
+ *   - or be a RESIDUAL link: the block is added to the residual stream h in place (Tensor::add_rmsnorm's sum,
+ *     crates/ferric-tensor/src/lib.rs:372-384), its sum of squares recorded, and h * norm_weight prepared for the next
+ *     product WITHOUT the 1/rms factor -- that scalar commutes with the product, so the next link (in_rms = 1) applies
+ *     1 / sqrt(mean(h^2) + eps) to its result instead -- e.g. o -> gate|up, down -> the next layer's q|k|v.
+ * The context's scratch holds two prepared-activation slots; a link reads slot `in_slot` and prepares into the other.
+ * ferric_cuda_add_rmsnorm_prepare / ferric_cuda_prepare_x write slot 0 (already normalised: in_rms = 0 for their
+ * consumer), which is how a chain starts.  Up to 8 activation rows; Q4_K / Q5_K / Q6_K. */
+#define FERRIC_CHAIN_NONE 0
+#define FERRIC_CHAIN_PREPARE 1
+#define FERRIC_CHAIN_RESIDUAL 2
+typedef struct ferric_chain_link {
+    const ferric_qmatrix *qm;     /* this product's matrix */
+    int32_t swiglu;               /* 1: [gate | up] matrix, result silu(gate . x) * (up . x) (try_matmul_swiglu) */
+    int32_t in_slot;              /* slot holding the prepared input: 0 or 1 */
+    int32_t in_rms;               /* 1: input prepared by a RESIDUAL link; scale the result by 1 / sqrt(mean(h^2) + eps) */
+    float eps;                    /* RMSNorm epsilon (with in_rms) */
+    float *y_dev;                 /* result [m, rows] (rows / 2 with swiglu), 16-byte aligned */
+    size_t ldy;                   /* its row stride in floats, 0 = contiguous */
+    int32_t next;                 /* FERRIC_CHAIN_NONE / _PREPARE / _RESIDUAL */
+    const ferric_qmatrix *next_qm; /* the consumer of what this link prepares: its format and inner dimension; PREPARE
+                                     feeds it the first `cols(next_qm)` result columns, RESIDUAL needs cols == rows here */
+    float *h_dev;                 /* RESIDUAL: residual stream [m, rows], contiguous, updated in place */
+    const float *norm_weight_dev; /* RESIDUAL: RMSNorm weight [rows] or NULL (weightless) */
+} ferric_chain_link;
+/* Size both slots for prepared activations of up to `slot_bytes` (the largest
+ * ferric_cuda_qmatrix_scratch_bytes(qm, m) of any matrix in the chain).  Call before the first link and before any
+ * capture; other calls that grow the scratch afterwards invalidate it as they do a captured graph. */
+int32_t ferric_cuda_chain_reserve(ferric_cuda_ctx *ctx, size_t slot_bytes);
+/* One link: y = x . W^T from slot in_slot (+ epilogue), then the link's job.  Asynchronous on the context's stream;
+ * links on one context must be issued one after the other (they share the block tickets). */
+int32_t ferric_cuda_chain_matmul(ferric_cuda_ctx *ctx, const ferric_chain_link *link, size_t m);
+
 /* No counterpart in the reference.  matmul_q for hosts that cannot let this library allocate: a
  * server that has already divided the device's memory among its own pools, a latency-critical
  * loop that cannot take the device-wide stall of cudaMalloc / cudaFree, a restricted plugin host.
@@ -328,7 +367,9 @@ int32_t ferric_cuda_tp_connect(ferric_tp_group *g, const uint8_t *handles);
 int32_t ferric_cuda_tp_connect_local(ferric_tp_group *g, ferric_tp_group *const *groups);
 /* Device address of this rank's exchange buffer `kind`: pass it as y_dev of the row-parallel matmul. */
 void *ferric_cuda_tp_partial(ferric_tp_group *g, int32_t kind);
-/* Announce to all peers that exchange buffer `kind` holds this rank's next partial (stream-ordered). */
+/* Announce to all peers that exchange buffer `kind` holds this rank's next partial (stream-ordered).  Each kind has
+ * one buffer, which is safe only while consecutive exchanges of this signalled form alternate between the kinds (a
+ * decoder layer's o / down pattern): signalling the same kind twice in a row is refused with FERRIC_ERR_INVALID_ARG. */
 int32_t ferric_cuda_tp_signal(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t kind);
 /* ferric_cuda_add_rmsnorm_prepare with b = the sum over all ranks of exchange buffer `kind`
  * (waits, bounded, for every rank's announcement; sums in rank order, identically on every rank). */
@@ -362,8 +403,20 @@ int32_t ferric_cuda_tp_allreduce_add_rmsnorm_steps(ferric_cuda_ctx *ctx, ferric_
                                                    const float *partial_dev, const float *a_dev,
                                                    const float *weight_dev, float eps, size_t rows, size_t d,
                                                    float *sum_dev, float *norm_dev, int32_t steps);
-/* Synchronise the context and report whether any wait on a peer ran out (FERRIC_ERR_TIMEOUT). */
+/* A RESIDUAL chain link (ferric_cuda_chain_matmul) whose product is row-parallel: the epilogue pushes the partial
+ * sums to every rank as ferric_cuda_tp_matmul_push does, and the link's job polls (bounded) all ranks' pairs for its
+ * block in this rank's memory, adds them in rank order to h and prepares the next product -- product, all-reduce,
+ * residual add and preparation in one launch.  link->y_dev is not used.  The last job closes the exchange. */
+int32_t ferric_cuda_tp_chain_matmul(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t kind, const ferric_chain_link *link,
+                                    size_t m);
+/* Synchronise the context and report whether any wait on a peer ran out (FERRIC_ERR_TIMEOUT).  Every wait is bounded
+ * (about a second by default; FERRIC_CUDA_PEER_WAIT_SPINS in the environment, read when the context is created, sets
+ * the number of polling rounds); once one ran out, later kernels of the group do not wait again. */
 int32_t ferric_cuda_tp_status(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t *timed_out);
+/* After a time-out: synchronise, then clear the status word, the exchange counters and every receive region of this
+ * rank, so that the ranks count exchanges from zero again.  Every rank of the group must do this, with no exchange in
+ * flight, before the next one. */
+int32_t ferric_cuda_tp_reset(ferric_cuda_ctx *ctx, ferric_tp_group *g);
 void ferric_cuda_tp_free(ferric_tp_group *g);
 
 #ifdef __cplusplus

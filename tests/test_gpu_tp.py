@@ -15,8 +15,18 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_gpu_stack_matches_unsharded_oracle(tmp_path):
+def elementwise_ok(got, ref, exact):
+    """The path's bar, element by element: |got - ref| <= 1e-4 + 1e-3 |ref|, where the oracle's own f32 rounding
+    (its distance from the same layers evaluated in float64) is not charged to the kernels."""
+    tol = 1e-4 + 1e-3 * np.abs(ref) + np.abs(ref.astype(np.float64) - exact)
+    return float((np.abs(got - ref) / tol).max())
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_multi_gpu_stack_matches_unsharded_oracle(tmp_path, world):
+    """`world` GPUs, one process each: every exchange form against the unsharded layers on the CPU oracle."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import test_tp_gloo as T
     import tp_worker as W
     from ferric_b200 import synth
@@ -26,32 +36,33 @@ def test_two_gpu_stack_matches_unsharded_oracle(tmp_path):
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
-    out = str(tmp_path / "tp2.npz")
-    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), "2", str(port), out])
-             for r in range(2)]
+    out = str(tmp_path / f"tp{world}.npz")
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), str(world), str(port), out])
+             for r in range(world)]
     for p in procs:
-        assert p.wait(timeout=300) == 0
+        assert p.wait(timeout=600) == 0
     got = np.load(out)
-    T.HID, T.NFF, T.QOUT, T.KV = W.HID, W.NFF, W.QOUT, W.KV
-    plan1 = TPPlan.make(1, 0, W.HID, W.NFF, W.QOUT, W.KV)
-    h = synth.activations(W.B, W.HID, seed=5)
-    for l in range(W.LAYERS):
-        h = T.layer_forward(plan1, layer_shards(plan1, T.full_layer(100 + 10 * l)), h, lambda a: None)
-    tol = 1e-4 + 1e-3 * np.abs(h).max()
-    assert np.abs(got["nccl"] - h).max() <= tol
-    assert np.abs(got["fused"] - h).max() <= tol
-    assert np.array_equal(got["fused"], got["fused_replay"])       # graph replay == eager
-    assert np.array_equal(got["nccl"], got["nccl_replay"])
-    wide = np.load(out + ".wide.npz")
-    hw = synth.activations(W.WIDE_B, W.HID, seed=6)
-    for l in range(W.LAYERS):
-        hw = T.layer_forward(plan1, layer_shards(plan1, T.full_layer(100 + 10 * l)), hw, lambda a: None)
-    tolw = 1e-4 + 1e-3 * np.abs(hw).max()
-    assert np.abs(wide["nccl"] - hw).max() <= tolw and np.abs(wide["wide"] - hw).max() <= tolw
-    assert np.array_equal(wide["wide"], wide["wide_replay"])
-    assert np.abs(got["push"] - h).max() <= tol
-    assert np.array_equal(got["push"], got["push_replay"])
+    HID, NFF, QOUT, KV = W.dims(world)
+    T.HID, T.NFF, T.QOUT, T.KV = HID, NFF, QOUT, KV
+    plan1 = TPPlan.make(1, 0, HID, NFF, QOUT, KV)
+
+    def reference(h):
+        h64 = h.astype(np.float64)
+        for l in range(W.LAYERS):
+            sh = layer_shards(plan1, T.full_layer(100 + 10 * l))
+            h = T.layer_forward(plan1, sh, h, lambda a: None)
+            h64 = T.layer_forward_f64(plan1, sh, h64)
+        return h, h64
+
+    h, h64 = reference(synth.activations(W.B, HID, seed=5))
+    for mode in ("nccl", "fused", "push", "chain"):
+        assert elementwise_ok(got[mode], h, h64) <= 1.0, mode
+        assert np.array_equal(got[mode], got[mode + "_replay"]), mode      # graph replay == eager
     assert np.array_equal(got["push"], got["fused"])               # same partials, same rank-order sum
+    wide = np.load(out + ".wide.npz")
+    hw, hw64 = reference(synth.activations(W.WIDE_B, HID, seed=6))
+    assert elementwise_ok(wide["nccl"], hw, hw64) <= 1.0 and elementwise_ok(wide["wide"], hw, hw64) <= 1.0
+    assert np.array_equal(wide["wide"], wide["wide_replay"])
 
 
 @pytest.mark.parametrize("cluster", [0, 2, 4, 8])
@@ -171,5 +182,116 @@ def test_two_step_allreduce_many_ranks_in_one_process(world, cap_rows, rows, d):
             assert torch.equal(outs[r][0], s_ref), (it, r)
             assert torch.allclose(outs[r][1], n_ref, rtol=2e-6, atol=1e-7), (it, r)
             assert torch.equal(outs[r][1], outs[0][1])         # the same bits on every rank
+    for o in grps + ctxs:
+        o.close()
+
+
+# ---------------------------------------------------------------------------------- a peer that never arrives
+def _two_local_ranks(F, m, hid):
+    ctxs = [F.Context(0) for _ in range(2)]
+    grps = [F.TPGroup(ctxs[r], r, 2, m, hid) for r in range(2)]
+    F.TPGroup.connect_local(grps)
+    return ctxs, grps
+
+
+def test_a_missing_peer_runs_out_the_pushed_wait_and_the_group_recovers(monkeypatch):
+    """Rank 1 never pushes.  Rank 0's consumer polls its own memory a bounded number of rounds (set small here through
+    FERRIC_CUDA_PEER_WAIT_SPINS), gives up, and says so through ferric_cuda_tp_status; nothing hangs or faults.  A later
+    consumer of the group does not wait again.  After both ranks reset, a full exchange is correct."""
+    import ferric_b200 as F
+    from ferric_b200 import synth
+
+    monkeypatch.setenv("FERRIC_CUDA_PEER_WAIT_SPINS", "2000")
+    m, hid, k = 2, 1024, 256
+    ctxs, grps = _two_local_ranks(F, m, hid)
+    ws = [F.QMatrix.from_bytes(ctxs[r], synth.matrix(12, hid, k, seed=r), 12, hid, k) for r in range(2)]
+    nxt = [F.QMatrix.from_bytes(ctxs[r], synth.matrix(12, 64, hid, seed=9), 12, 64, hid) for r in range(2)]
+    xs = [torch.from_numpy(synth.activations(m, k, seed=20 + r)).cuda() for r in range(2)]
+    a = torch.randn((m, hid), device="cuda")
+    s = torch.empty_like(a)
+    grps[0].matmul_push(0, ws[0], xs[0])                          # only rank 0 pushes
+    grps[0].add_rmsnorm_prepare(0, nxt[0], a, None, 1e-6, sum_out=s, pushed=True)
+    with pytest.raises(F.FerricError) as e:
+        grps[0].check()                                           # returns: the wait ran out
+    assert e.value.status == 7
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    grps[0].matmul_push(1, ws[0], xs[0])
+    t0.record()
+    grps[0].add_rmsnorm_prepare(1, nxt[0], a, None, 1e-6, sum_out=s, pushed=True)      # status is set: no second wait
+    t1.record()
+    torch.cuda.synchronize()
+    assert t0.elapsed_time(t1) < 50.0
+    # the chained form of the same exchange: product, poll and job in one launch
+    ctxs[0].chain_reserve(max(ws[0].scratch_bytes(m), nxt[0].scratch_bytes(m)))
+    for g in grps:
+        g.reset()
+    ws[0].prepare(xs[0])
+    h = a.clone()
+    grps[0].chain_matmul(0, ws[0], m, 0, nxt[0], h)
+    with pytest.raises(F.FerricError) as e:
+        grps[0].check()
+    assert e.value.status == 7
+    for g in grps:
+        g.reset()
+    # both ranks push, the device is synchronised, both consume: correct again
+    total = ws[0].matmul(xs[0]) + ws[1].matmul(xs[1])
+    s_ref = torch.empty_like(a)
+    nxt[0].add_rmsnorm_prepare(a, total, None, 1e-6, sum_out=s_ref)
+    for r in range(2):
+        grps[r].matmul_push(0, ws[r], xs[r])
+    torch.cuda.synchronize()
+    for r in range(2):
+        s_r = torch.empty_like(a)
+        grps[r].add_rmsnorm_prepare(0, nxt[r], a, None, 1e-6, sum_out=s_r, pushed=True)
+        grps[r].check()
+        assert torch.equal(s_r, s_ref)
+    for o in ws + nxt + grps + ctxs:
+        o.close()
+
+
+def test_a_missing_peer_runs_out_the_two_step_allreduce_wait(monkeypatch):
+    """The same for the all-reduce of many rows: rank 1's scatter is left out, so rank 0's reduce step finds only its
+    own copy of its slice, gives up after the bound and reports it; after a reset the exchange works."""
+    import ferric_b200 as F
+
+    monkeypatch.setenv("FERRIC_CUDA_PEER_WAIT_SPINS", "2000")
+    rows, d = 12, 1024
+    ctxs, grps = _two_local_ranks(F, rows, d)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    parts = [torch.randn(rows, d, device="cuda", generator=gen) for _ in range(2)]
+    a = torch.randn(rows, d, device="cuda", generator=gen)
+    outs = [(torch.empty_like(a), torch.empty_like(a)) for _ in range(2)]
+    grps[0].allreduce_add_rmsnorm(0, parts[0], a, None, 1e-6, sum_out=outs[0][0], norm_out=outs[0][1], steps=1)
+    torch.cuda.synchronize()
+    grps[0].allreduce_add_rmsnorm(0, parts[0], a, None, 1e-6, sum_out=outs[0][0], norm_out=outs[0][1], steps=2)
+    with pytest.raises(F.FerricError) as e:
+        grps[0].check()
+    assert e.value.status == 7
+    for g in grps:
+        g.reset()
+    s_ref, n_ref = ctxs[0].add_rmsnorm(a, parts[0] + parts[1], None, 1e-6)
+    for step in (1, 2, 4):
+        torch.cuda.synchronize()
+        for r in range(2):
+            grps[r].allreduce_add_rmsnorm(0, parts[r], a, None, 1e-6, sum_out=outs[r][0], norm_out=outs[r][1], steps=step)
+    for r in range(2):
+        grps[r].check()
+        assert torch.equal(outs[r][0], s_ref)
+    for o in grps + ctxs:
+        o.close()
+
+
+def test_signalled_exchange_refuses_the_same_kind_twice():
+    """The signalled (pull) form has one buffer per kind and is safe only while kinds alternate."""
+    import ferric_b200 as F
+
+    ctxs, grps = _two_local_ranks(F, 1, 256)
+    grps[0].signal(0)
+    with pytest.raises(F.FerricError) as e:
+        grps[0].signal(0)
+    assert e.value.status == 1 and "alternate" in str(e.value)
+    grps[0].signal(1)
+    grps[0].signal(0)
     for o in grps + ctxs:
         o.close()

@@ -40,6 +40,24 @@ def layer_forward(plan, sh, h, reduce):
     return O.add_rmsnorm(h, d, None, 1e-6)[0]
 
 
+def layer_forward_f64(plan, sh, h):
+    """The same layer (unsharded) with the oracle-dequantised weights and float64 arithmetic throughout: what the f32
+    oracle itself deviates from, so that a parity bar can leave the oracle's own rounding out."""
+    def w64(raw, ty, rows, cols):
+        return O.deq_raw(raw, rows * cols, ty).reshape(rows, cols).astype(np.float64)
+
+    def norm(v):
+        return v / np.sqrt((v * v).mean(axis=-1, keepdims=True) + 1e-6)
+
+    xn = norm(h)
+    qkv = xn @ w64(sh["qkv"], 12, plan.q_rows + 2 * plan.kv_rows, plan.hidden).T
+    h = h + qkv[:, :plan.q_rows] @ w64(sh["o"], 12, plan.hidden, plan.q_rows).T
+    gu = norm(h) @ w64(sh["gate_up"], 12, 2 * plan.ff_rows, plan.hidden).T
+    g, u = gu[:, :plan.ff_rows], gu[:, plan.ff_rows:]
+    f = g / (1.0 + np.exp(-g)) * u
+    return h + f @ w64(sh["down"], 14, plan.hidden, plan.ff_rows).T
+
+
 def _worker(rank, world, port, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)

@@ -1,4 +1,4 @@
-"""Worker for the 2-GPU tensor-parallel test: one process per GPU, launched by test_gpu_tp.py."""
+"""Worker for the multi-GPU tensor-parallel test: one process per GPU, launched by test_gpu_tp.py."""
 import os
 import sys
 
@@ -14,6 +14,11 @@ HID, NFF, QOUT, KV, LAYERS, B = 1024, 1536, 1024, 512, 3, 2
 WIDE_B = 12
 
 
+def dims(world):
+    """(hidden, n_ff, q_out, kv_out): every rank needs at least one 256-column block of q and of n_ff."""
+    return (1024, 1536, 1024, 512) if world <= 4 else (1024, 2304, 2048, 512)
+
+
 def main(rank, world, port, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -22,19 +27,20 @@ def main(rank, world, port, out):
     from ferric_b200.stack import DecodeStack, TPPlan, layer_shards
     from test_tp_gloo import full_layer  # same synthetic layers as the CPU test (sizes overridden below)
     import test_tp_gloo as T
+    HID, NFF, QOUT, KV = dims(world)
     T.HID, T.NFF, T.QOUT, T.KV = HID, NFF, QOUT, KV
 
     ctx = F.Context(rank)
     plan = TPPlan.make(world, rank, HID, NFF, QOUT, KV)
     results = {}
-    for mode in ("nccl", "fused", "push"):
+    for mode in ("nccl", "fused", "push", "chain"):
         group = None
         if mode != "nccl":
             group = F.TPGroup(ctx, rank, world, B, HID)
             group.connect_with_torch_distributed()
         st = DecodeStack(ctx, plan, n_layers=LAYERS, batch=B,
                          all_reduce=(lambda t: dist.all_reduce(t)) if mode == "nccl" else None, group=group,
-                         push=(mode == "push"))
+                         push=(mode in ("push", "chain")), chain=(mode == "chain"))
         for l in range(LAYERS):
             sh = layer_shards(plan, full_layer(100 + 10 * l))
             st.add_layer(F.QMatrix.from_bytes(ctx, sh["qkv"], 12, plan.q_rows + 2 * plan.kv_rows, HID),
@@ -86,8 +92,7 @@ def main(rank, world, port, out):
     if rank == 0:
         np.savez(out + ".wide.npz", nccl=wide["nccl"][0], wide=wide["wide"][0], wide_replay=wide["wide"][1])
     if rank == 0:
-        np.savez(out, nccl=results["nccl"][0], nccl_replay=results["nccl"][1], fused=results["fused"][0],
-                 fused_replay=results["fused"][1], push=results["push"][0], push_replay=results["push"][1])
+        np.savez(out, **{k: v[0] for k, v in results.items()}, **{k + "_replay": v[1] for k, v in results.items()})
     dist.barrier()
     os._exit(0)
 
