@@ -587,7 +587,6 @@ template <int EPI>
 __device__ __forceinline__ void chain_job(const ChainJob& j, int blk, int m, PrepSmem& sm)
 {
     const int lane = threadIdx.x & 31, prow = lane >> 4, q = lane & 15;
-    if (lane == 0) j.tickets[blk] = 0;   // ready for the next launch
     __threadfence();                     // the other tiles' stores came before their tickets
     unsigned want = 0;
     const uint2* recv = nullptr;
@@ -648,6 +647,7 @@ __device__ __forceinline__ void chain_job(const ChainJob& j, int blk, int m, Pre
         if (j.out_ty == (int)kGgmlQ6K) prep_block<(int)kGgmlQ6K>(v, sm, (size_t)tile, nblk, (size_t)blk, j.frag);
         else prep_block<(int)kGgmlQ4K>(v, sm, (size_t)tile, nblk, (size_t)blk, j.frag);
     }
+    if (lane == 0) j.tickets[blk] = 0;   // ready for the next launch
     if (EPI == kEpiPush && j.kind == 3) {
         // the last job to finish closes the exchange: every tile of this launch has been pushed by then
         __threadfence();
@@ -659,24 +659,35 @@ __device__ __forceinline__ void chain_job(const ChainJob& j, int blk, int m, Pre
     }
 }
 
-// 1 / sqrt(mean of squares + eps) of the activation rows this lane's result columns belong to (Chain::ssq_in), summed
-// over the blocks in block order -- the order of the one-CTA norm kernel with a warp per block.
+// 1 / sqrt(mean of squares + eps) of the activation rows this lane's result columns belong to (Chain::ssq_in).  The
+// per-block sums are fetched by the whole warp at once (one trip to L2 for all of them) and added in a fixed order --
+// a lane's blocks in turn, then a butterfly over the lanes -- so every warp of every CTA forms the same bits.
 template <int NT, bool CHAIN>
 __device__ __forceinline__ void chain_scales(float (&inv)[NT], const Chain& chain, int tile0, int m)
 {
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) inv[nt] = 1.0f;
     if (CHAIN && chain.ssq_in) {
-        const int t = threadIdx.x & 3;
+        const int lane = threadIdx.x & 31, t = lane & 3;
+        float tot[NT][kRowsPerTile];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int r = 0; r < kRowsPerTile; r++) {
+                const int batch = (tile0 + nt) * kRowsPerTile + r;
+                float s = 0.0f;
+                if (batch < m)
+                    for (int i = lane; i < chain.ssq_blocks; i += 32) s += __ldcg(chain.ssq_in + (size_t)batch * chain.ssq_blocks + i);
+                tot[nt][r] = s;
+            }
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+            for (int r = 0; r < kRowsPerTile; r++)
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) tot[nt][r] += __shfl_xor_sync(0xffffffffu, tot[nt][r], o);
             const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
-            if (batch < m) {
-                const float* p = chain.ssq_in + (size_t)batch * chain.ssq_blocks;
-                float tot = 0.0f;
-                for (int i = 0; i < chain.ssq_blocks; i++) tot += __ldcg(p + i);
-                inv[nt] = 1.0f / sqrtf(tot / chain.d + chain.eps);
-            }
+            if (batch < m) inv[nt] = 1.0f / sqrtf(((t >> 1) ? tot[nt][1] : tot[nt][0]) / chain.d + chain.eps);
         }
     }
 }
