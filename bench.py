@@ -451,7 +451,10 @@ def run_ours(args):
 def tp_parity_check(torch, dist, ctx, world, rank, dev, exchange_for, chain):
     """N > 1, outside every timed region: two full-shape layers, cut into this run's shards, run through the exchange
     the timed run uses at batch 1, 8 and 64, against the same two layers run unsharded on rank 0.  The bytes are drawn
-    on rank 0 and broadcast, so every rank cuts the same tensors.  Element-wise bar: 1e-4 + 1e-3 |ref|."""
+    on rank 0 and broadcast, so every rank cuts the same tensors.  Compared element by element, bar 1e-4 + 1e-3 |ref|:
+    the stack's result, the RMS-normalised residual stream after the last layer (values of order one, like the
+    activations the bar is stated for).  The raw residual stream grows to ~1e4 with these random-init weights, so an
+    absolute 1e-4 on it would be below one f32 ulp; it is compared against 1e-4 + 1e-3 max|ref| instead."""
     from ferric_b200 import QMatrix, synth
     from ferric_b200.stack import DecodeStack, TPPlan
 
@@ -488,8 +491,9 @@ def tp_parity_check(torch, dist, ctx, world, rank, dev, exchange_for, chain):
             whole.append(build(plan1, full))
         del full
     result = {"world": world, "layers": layers, "batches": [], "all_reduce": {}, "worst_ratio": 0.0, "worst_ratio_maxnorm": 0.0,
-              "bar": "element-wise |sharded - unsharded| <= 1e-4 + 1e-3 |unsharded| on rank 0's residual stream after the layers; "
-                     "worst_ratio_maxnorm uses 1e-4 + 1e-3 max|unsharded| instead"}
+              "bar": "worst_ratio: element-wise |sharded - unsharded| / (1e-4 + 1e-3 |unsharded|) on rank 0's normalised residual "
+                     "stream after the layers (the stack's result); worst_ratio_maxnorm: max|sharded - unsharded| / "
+                     "(1e-4 + 1e-3 max|unsharded|) on the raw residual stream"}
     g = torch.Generator(device=dev).manual_seed(77)
     for b in (1, 8, 64):
         x = torch.randn((b, HIDDEN), device=dev, generator=g)
@@ -501,6 +505,7 @@ def tp_parity_check(torch, dist, ctx, world, rank, dev, exchange_for, chain):
         st.reserve()
         st.h.copy_(x)
         got = st.step().clone()
+        got_n = st.xn.clone()
         torch.cuda.synchronize(dev)
         if grp is not None:
             grp.check()
@@ -512,10 +517,10 @@ def tp_parity_check(torch, dist, ctx, world, rank, dev, exchange_for, chain):
             ref_st.reserve()
             ref_st.h.copy_(x)
             ref = ref_st.step().clone()
+            ref_n = ref_st.xn.clone()
             torch.cuda.synchronize(dev)
-            err = (got - ref).abs().double()
-            ratio = float((err / (1e-4 + 1e-3 * ref.abs().double())).max().item())
-            ratio_max = float((err.max() / (1e-4 + 1e-3 * ref.abs().max().double())).item())
+            ratio = float(((got_n - ref_n).abs().double() / (1e-4 + 1e-3 * ref_n.abs().double())).max().item())
+            ratio_max = float(((got - ref).abs().double().max() / (1e-4 + 1e-3 * ref.abs().max().double())).item())
             result["worst_ratio"] = max(result["worst_ratio"], ratio)
             result["worst_ratio_maxnorm"] = max(result["worst_ratio_maxnorm"], ratio_max)
             ref_st.layers = []

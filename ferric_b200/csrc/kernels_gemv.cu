@@ -607,8 +607,15 @@ __device__ __forceinline__ void chain_job(const ChainJob& j, int blk, int m, Pre
         for (int i = 0; i < 4; i++) f[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (valid) {
             if (EPI == kEpiPush && j.kind == 3) {
-#pragma unroll
-                for (int i = 0; i < 4; i++) pushed_sum<1, kMaxRanks>(j.pushed, recv, batch * d + (size_t)blk * 256 + 16 * q + 4 * i, want, wait_limit, f + i);
+                // as many of the lane's 16 values per polling round as the registers hold for the group's size
+                const size_t off = batch * d + (size_t)blk * 256 + 16 * q;
+                if (j.pushed.world <= 2) {
+#pragma unroll 1
+                    for (int i = 0; i < 4; i += 2) pushed_sum<2, 2>(j.pushed, recv, off + 4 * i, want, wait_limit, f + i);
+                } else {
+#pragma unroll 1
+                    for (int i = 0; i < 4; i++) pushed_sum<1, kMaxRanks>(j.pushed, recv, off + 4 * i, want, wait_limit, f + i);
+                }
             } else {
                 const float4* yp = reinterpret_cast<const float4*>(j.y + batch * j.ldy + (size_t)blk * 256 + 16 * q);
 #pragma unroll
