@@ -11,8 +11,9 @@ reference (dcharlot-physicalai-bmi/ferric)              here
 ``Tensor::matmul_q`` / ``try_matmul_swiglu``            ``QMatrix.matmul`` / ``QMatrix.try_matmul_swiglu``
 ``Tensor::swiglu``                                      ``Context.swiglu``
 ``ferric_gguf::parse`` / ``GgufFile::open``, ``qm``     ``Gguf.parse`` / ``Gguf(path)``, ``Gguf.qmatrix``
+``ferric_llama::Proj::{load,matmul,gate_up_swiglu}``     ``Gguf.proj`` / ``Proj.matmul`` / ``Proj.gate_up_swiglu``
 =====================================================  ===========================================
 
 PyTorch is used only for device memory and streams; all arithmetic runs in ``libferric_cuda.so``.
 """
-from .ops import (Context, FerricError, Gguf, QMatrix, TPGroup, GGML_Q4_K, GGML_Q6_K, GGML_Q8_0, type_size)  # noqa: F401
+from .ops import (Context, FerricError, Gguf, Proj, QMatrix, TPGroup, GGML_Q4_K, GGML_Q6_K, GGML_Q8_0, type_size)  # noqa: F401

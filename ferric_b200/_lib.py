@@ -74,6 +74,8 @@ SIGNATURES = {
     "ferric_cuda_matmul_q_host": (_I32, [_P, _P, _P, _SZ, _SZ, _P]),
     "ferric_cuda_matmul_q_swiglu": (_I32, [_P, _P, _P, _SZ, _SZ, _P]),
     "ferric_cuda_swiglu": (_I32, [_P, _P, _SZ, _SZ, _P]),
+    "ferric_cuda_matmul_q_swiglu_id": (_I32, [_P, _P, _P, _SZ, _SZ, _P, _SZ, _SZ, _P]),
+    "ferric_cuda_matmul_q_id_wsum": (_I32, [_P, _P, _P, _SZ, _SZ, _SZ, _P, _SZ, _P]),
     "ferric_cuda_tp_create": (_I32, [_P, _I32, _I32, _SZ, C.POINTER(_P)]),
     "ferric_cuda_tp_export": (_I32, [_P, _P]),
     "ferric_cuda_tp_connect": (_I32, [_P, _P]),
@@ -111,6 +113,15 @@ SIGNATURES = {
     "ferric_gguf_meta_arr_str": (_I32, [_P, C.c_char_p, _SZ, _P, _SZ, C.POINTER(_SZ)]),
     "ferric_gguf_meta_arr_f64": (_I32, [_P, C.c_char_p, _SZ, C.POINTER(C.c_double)]),
     "ferric_cuda_qmatrix_from_gguf": (_I32, [_P, _P, C.POINTER(C.c_char_p), _SZ, C.POINTER(_P)]),
+    "ferric_cuda_proj_from_gguf": (_I32, [_P, _P, C.POINTER(C.c_char_p), _SZ, C.POINTER(_P)]),
+    "ferric_cuda_proj_from_parts": (_I32, [C.POINTER(_P), _SZ, C.POINTER(_P)]),
+    "ferric_cuda_proj_n_parts": (_SZ, [_P]),
+    "ferric_cuda_proj_rows": (_SZ, [_P]),
+    "ferric_cuda_proj_cols": (_SZ, [_P]),
+    "ferric_cuda_proj_part": (_P, [_P, _SZ]),
+    "ferric_cuda_proj_free": (None, [_P]),
+    "ferric_cuda_proj_matmul": (_I32, [_P, _P, _P, _SZ, _SZ, _P]),
+    "ferric_cuda_proj_gate_up_swiglu": (_I32, [_P, _P, _P, _SZ, _SZ, _SZ, _P]),
     "ferric_cuda_dequant_f32": (_I32, [_P, _P, _P]),
     "ferric_cuda_dequant_bf16": (_I32, [_P, _P, _P]),
 }

@@ -106,9 +106,18 @@ int32_t build_matrix(ferric_cuda_ctx* ctx, const uint8_t* bytes, bool on_device,
         set_last_error("cols (%zu) must be a multiple of %zu for ggml type %u", cols, vals, ty);
         return kErrShape;
     }
-    if (len != rows * (cols / vals) * bbytes) {
-        set_last_error("unexpected byte length %zu for [%zu, %zu] of ggml type %u (want %zu)", len, rows, cols, ty,
-                       rows * (cols / vals) * bbytes);
+    // the kernels index rows and columns with 32-bit integers, and the size arithmetic below must not wrap
+    if (rows > (size_t)INT32_MAX || cols > (size_t)INT32_MAX) {
+        set_last_error("matrix [%zu, %zu] is larger than this backend indexes (2^31 - 1 rows / columns)", rows, cols);
+        return kErrShape;
+    }
+    size_t want_len = 0;
+    if (__builtin_mul_overflow(rows, cols / vals, &want_len) || __builtin_mul_overflow(want_len, bbytes, &want_len)) {
+        set_last_error("byte size of [%zu, %zu] of ggml type %u overflows", rows, cols, ty);
+        return kErrShape;
+    }
+    if (len != want_len) {
+        set_last_error("unexpected byte length %zu for [%zu, %zu] of ggml type %u (want %zu)", len, rows, cols, ty, want_len);
         return kErrShape;
     }
     if (row0 + nrows > rows || col0 + ncols > cols || col0 % vals != 0 || ncols % vals != 0) {
@@ -249,6 +258,10 @@ int32_t ferric_gguf_type_size(uint32_t ty, size_t n, size_t* out_bytes)
     if (!out_bytes) {
         set_last_error("NULL output pointer");
         return kErrInvalidArg;
+    }
+    if ((ty == FERRIC_GGML_F32 && n > SIZE_MAX / 4) || ((ty == FERRIC_GGML_F16 || ty == FERRIC_GGML_BF16) && n > SIZE_MAX / 2)) {
+        set_last_error("byte size of %zu elements of ggml type %u overflows", n, ty);
+        return kErrShape;
     }
     switch (ty) {
     case FERRIC_GGML_F32: *out_bytes = n * 4; return kOk;
@@ -713,6 +726,208 @@ int32_t ferric_gguf_deq_raw(ferric_cuda_ctx* ctx, const uint8_t* raw, size_t raw
     e = cudaStreamSynchronize(ctx->stream);
     if (rc == kOk && e != cudaSuccess) rc = cuda_fail(e, "cudaStreamSynchronize");
     return rc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Proj (crates/ferric-llama/src/qwen3.rs:192-228): a projection with several stacked outputs that is one matrix when
+// the parts share a quant format and one matrix per part when they do not.
+// ---------------------------------------------------------------------------------------------
+int32_t ferric_cuda_proj_from_parts(ferric_qmatrix* const* parts, size_t n_parts, ferric_proj** out)
+{
+    if (!parts || n_parts == 0 || n_parts > 8 || !out) {
+        set_last_error("proj_from_parts: NULL argument, or not 1..8 parts");
+        return kErrInvalidArg;
+    }
+    *out = nullptr;
+    for (size_t k = 0; k < n_parts; k++) {
+        if (!parts[k] || parts[k]->device != parts[0]->device || parts[k]->w.cols != parts[0]->w.cols) {
+            set_last_error("proj_from_parts: part %zu is NULL, on another device or has another input dim", k);
+            return parts[k] && parts[k]->w.cols != parts[0]->w.cols ? kErrShape : kErrInvalidArg;
+        }
+    }
+    ferric_proj* p = new (std::nothrow) ferric_proj;
+    if (!p) return kErrOom;
+    p->n_parts = n_parts;
+    p->cols = parts[0]->w.cols;
+    for (size_t k = 0; k < n_parts; k++) {
+        p->parts[k] = parts[k];
+        p->rows += parts[k]->w.rows;
+    }
+    *out = p;
+    return kOk;
+}
+
+size_t ferric_cuda_proj_n_parts(const ferric_proj* p) { return p ? p->n_parts : 0; }
+size_t ferric_cuda_proj_rows(const ferric_proj* p) { return p ? p->rows : 0; }
+size_t ferric_cuda_proj_cols(const ferric_proj* p) { return p ? p->cols : 0; }
+const ferric_qmatrix* ferric_cuda_proj_part(const ferric_proj* p, size_t i) { return (p && i < p->n_parts) ? p->parts[i] : nullptr; }
+
+void ferric_cuda_proj_free(ferric_proj* p)
+{
+    if (!p) return;
+    for (size_t k = 0; k < p->n_parts; k++) ferric_cuda_qmatrix_free(p->parts[k]);
+    delete p;
+}
+
+// Proj::matmul: every part's product lands at its column offset of y[m, rows] -- the reference's matmul + cat.
+// Parts that share an activation format (Q4_K and Q5_K; Q6_K) share one preparation of x.
+static int32_t proj_matmul_ld(ferric_cuda_ctx* ctx, const ferric_proj* p, const float* x, size_t m, float* y, size_t ldy)
+{
+    int32_t rc = kOk;
+    const ferric_qmatrix* prepared_for = nullptr;
+    auto family = [](uint32_t ty) { return ty == kGgmlQ5K ? kGgmlQ4K : ty; };
+    size_t col = 0;
+    for (size_t k = 0; k < p->n_parts && rc == kOk; k++) {
+        const ferric_qmatrix* qm = p->parts[k];
+        float* yk = y + col;
+        col += qm->w.rows;
+        if (qm->ty == kGgmlQ8_0 || gemv_tc_eligible(qm->ty, qm->w, m) || qm->w.nblk == 0) {
+            rc = run_matmul(ctx, qm, x, m, 0, yk, ldy, kEpiStore);
+            prepared_for = nullptr;   // the tensor-core path uses the scratch for its own activation form
+            continue;
+        }
+        if (!prepared_for || family(prepared_for->ty) != family(qm->ty)) {
+            if ((rc = run_matmul(ctx, qm, x, m, 0, nullptr, 0, kEpiStore, 1)) != kOk) break;
+            prepared_for = qm;
+        }
+        rc = run_matmul(ctx, qm, nullptr, m, 0, yk, ldy, kEpiStore, 2);
+    }
+    return rc;
+}
+
+static int32_t check_proj_args(const ferric_cuda_ctx* ctx, const ferric_proj* p, const void* x, size_t m, size_t x_cols, const void* y)
+{
+    if (!ctx || !p || p->n_parts == 0) {
+        set_last_error("NULL context or projection");
+        return kErrInvalidArg;
+    }
+    return check_matmul_args(ctx, p->parts[0], x, m, x_cols, y);
+}
+
+int32_t ferric_cuda_proj_matmul(ferric_cuda_ctx* ctx, const ferric_proj* p, const float* x_dev, size_t m, size_t x_cols, float* y_dev)
+{
+    int32_t rc = check_proj_args(ctx, p, x_dev, m, x_cols, y_dev);
+    if (rc != kOk) return rc;
+    DeviceGuard guard(ctx->device);
+    if (p->n_parts == 1) return run_matmul(ctx, p->parts[0], x_dev, m, 0, y_dev, 0, kEpiStore);
+    return proj_matmul_ld(ctx, p, x_dev, m, y_dev, p->rows);
+}
+
+// Proj::gate_up_swiglu: the fused kernel when gate|up is one fusable matrix, otherwise matmul + cat, then swiglu.
+int32_t ferric_cuda_proj_gate_up_swiglu(ferric_cuda_ctx* ctx, const ferric_proj* p, const float* x_dev, size_t m, size_t x_cols,
+                                        size_t n_ff, float* y_dev)
+{
+    int32_t rc = check_proj_args(ctx, p, x_dev, m, x_cols, y_dev);
+    if (rc != kOk) return rc;
+    if (p->rows != 2 * n_ff) {
+        set_last_error("gate_up_swiglu: the projection has %zu rows, not 2 x n_ff = %zu", p->rows, 2 * n_ff);
+        return kErrShape;
+    }
+    if (m == 0 || n_ff == 0) return kOk;
+    DeviceGuard guard(ctx->device);
+    if (p->n_parts == 1 && p->parts[0]->ty != kGgmlQ8_0 && p->parts[0]->w.rows % 32 == 0)
+        return run_matmul(ctx, p->parts[0], x_dev, m, 0, y_dev, 0, kEpiSwiglu);
+    float* gu = nullptr;
+    FERRIC_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&gu), m * p->rows * sizeof(float), ctx->stream));
+    rc = p->n_parts == 1 ? run_matmul(ctx, p->parts[0], x_dev, m, 0, gu, 0, kEpiStore) : proj_matmul_ld(ctx, p, x_dev, m, gu, p->rows);
+    if (rc == kOk) {
+        ctx->launches++;
+        rc = launch_swiglu(ctx->stream, gu, m, n_ff, y_dev, ctx->tune);
+    }
+    cudaFreeAsync(gu, ctx->stream);
+    return rc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Indexed (mixture-of-experts) products, crates/ferric-tensor/src/dtype.rs:1620-1677: the matrix stacks all experts,
+// expert-major; the router's [T, 2k] output (weights | indices as f32) picks k experts per token on the device.
+// ---------------------------------------------------------------------------------------------
+static int32_t check_id_args(const ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const void* x, const void* selw, const void* y,
+                             size_t t, size_t k, size_t x_cols, size_t rows_per_expert)
+{
+    if (!ctx || !qm) {
+        set_last_error("NULL context or matrix handle");
+        return kErrInvalidArg;
+    }
+    if (qm->device != ctx->device) {
+        set_last_error("matrix lives on device %d, context on device %d", qm->device, ctx->device);
+        return kErrInvalidArg;
+    }
+    if (qm->ty != kGgmlQ4K && qm->ty != kGgmlQ5K && qm->ty != kGgmlQ6K) {
+        set_last_error("indexed products take Q4_K / Q5_K / Q6_K expert stacks (ggml type %u given)", qm->ty);
+        return kErrUnsupportedType;
+    }
+    if (k < 1 || k > 8) {
+        set_last_error("k must be 1..=8");
+        return kErrShape;
+    }
+    if (x_cols != qm->w.cols) {
+        set_last_error("inner dim mismatch: x[..,%zu] vs W[..,%zu]", x_cols, qm->w.cols);
+        return kErrShape;
+    }
+    if (rows_per_expert == 0 || rows_per_expert % 16 != 0 || qm->w.rows % rows_per_expert != 0) {
+        set_last_error("the matrix's %zu rows are not a whole number of experts of %zu rows (a multiple of 16)", qm->w.rows,
+                       rows_per_expert);
+        return kErrShape;
+    }
+    if (t > 0 && (!x || !selw || !y)) {
+        set_last_error("NULL activation, selection or result buffer");
+        return kErrInvalidArg;
+    }
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 3) || (reinterpret_cast<uintptr_t>(selw) & 3)) {
+        set_last_error("activation buffer must be 16-byte aligned (selection and result 4-byte)");
+        return kErrInvalidArg;
+    }
+    return kOk;
+}
+
+int32_t ferric_cuda_matmul_q_swiglu_id(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_dev, size_t t, size_t x_cols,
+                                       const float* selw_dev, size_t k, size_t eff, float* y_dev)
+{
+    int32_t rc = check_id_args(ctx, qm, x_dev, selw_dev, y_dev, t, k, x_cols, 2 * eff);
+    if (rc != kOk) return rc;
+    if (eff % 16 != 0) {
+        set_last_error("eff (%zu) must be a multiple of 16", eff);
+        return kErrShape;
+    }
+    if (t == 0 || qm->w.nblk == 0) return kOk;
+    DeviceGuard guard(ctx->device);
+    if ((rc = ensure_scratch(ctx, frag_bytes(qm->ty, qm->w, t))) != kOk) return rc;
+    if ((rc = launch_prep(ctx->stream, qm->ty, qm->w, x_dev, t, qm->w.cols, ctx->scratch, ctx->tune)) != kOk) return rc;
+    IdSel id;
+    id.selw = selw_dev;
+    id.k = (int)k;
+    id.rows_per_expert = (int)(2 * eff);
+    id.n_expert = (int)(qm->w.rows / (2 * eff));
+    id.x_per_pair = 0;
+    ctx->launches += 2;
+    return launch_gemv_id(ctx->stream, qm->ty, qm->w, ctx->scratch, t, t * k, y_dev, eff, kEpiSwiglu, ctx->tune, id);
+}
+
+int32_t ferric_cuda_matmul_q_id_wsum(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* x_dev, size_t t, size_t k,
+                                     size_t x_cols, const float* selw_dev, size_t out_pe, float* y_dev)
+{
+    int32_t rc = check_id_args(ctx, qm, x_dev, selw_dev, y_dev, t, k, x_cols, out_pe);
+    if (rc != kOk) return rc;
+    if (t == 0) return kOk;
+    DeviceGuard guard(ctx->device);
+    if (qm->w.nblk == 0) {
+        FERRIC_CUDA_TRY(cudaMemsetAsync(y_dev, 0, t * out_pe * sizeof(float), ctx->stream));
+        return kOk;
+    }
+    const size_t pairs = t * k, frag = (frag_bytes(qm->ty, qm->w, pairs) + 255) / 256 * 256;
+    if ((rc = ensure_scratch(ctx, frag + pairs * out_pe * sizeof(float))) != kOk) return rc;
+    float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ctx->scratch) + frag);
+    if ((rc = launch_prep(ctx->stream, qm->ty, qm->w, x_dev, pairs, qm->w.cols, ctx->scratch, ctx->tune)) != kOk) return rc;
+    IdSel id;
+    id.selw = selw_dev;
+    id.k = (int)k;
+    id.rows_per_expert = (int)out_pe;
+    id.n_expert = (int)(qm->w.rows / out_pe);
+    id.x_per_pair = 1;
+    if ((rc = launch_gemv_id(ctx->stream, qm->ty, qm->w, ctx->scratch, pairs, pairs, part, out_pe, kEpiStore, ctx->tune, id)) != kOk) return rc;
+    ctx->launches += 3;
+    return launch_id_wsum(ctx->stream, part, selw_dev, t, k, out_pe, y_dev, ctx->tune);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -46,11 +46,20 @@ struct TensorInfo {
     std::vector<uint64_t> dims;
     uint32_t ggml_type = 0;
     uint64_t offset = 0;
-    uint64_t n_elements() const
+    // The element count, or false when the product of the (untrusted) dims does not fit 63 bits.
+    bool n_elements_checked(uint64_t* out) const
     {
         uint64_t n = 1;
-        for (uint64_t d : dims) n *= d;
-        return n;
+        for (uint64_t d : dims)
+            if (__builtin_mul_overflow(n, d, &n)) return false;
+        if (n >> 63) return false;
+        *out = n;
+        return true;
+    }
+    uint64_t n_elements() const   // after parse_into has vetted the dims
+    {
+        uint64_t n = 0;
+        return n_elements_checked(&n) ? n : 0;
     }
 };
 
@@ -212,6 +221,12 @@ int32_t parse_into(ferric_gguf* g, const uint8_t* bytes, size_t len)
         for (uint32_t k = 0; k < nd && c.ok; k++) t.dims.push_back(c.le<uint64_t>());
         t.ggml_type = c.le<uint32_t>();
         t.offset = c.le<uint64_t>();
+        uint64_t n = 0;
+        if (c.ok && !t.n_elements_checked(&n)) {
+            // dims whose product wraps would pass every later size check with a small, wrong byte count
+            set_last_error("tensor '%s': the product of its dims overflows; refusing to load", t.name.c_str());
+            return kErrShape;
+        }
         if (c.ok) g->tensors.push_back(std::move(t));
     }
     if (!c.ok) {
@@ -540,6 +555,56 @@ int32_t ferric_cuda_qmatrix_from_gguf(ferric_cuda_ctx* ctx, const ferric_gguf* g
     cat.reserve(total);
     for (auto& pr : parts) cat.insert(cat.end(), pr.first, pr.first + pr.second);
     return ferric_cuda_qmatrix_from_bytes(ctx, cat.data(), cat.size(), ty, rows, inn, out);
+}
+
+// Proj::load (crates/ferric-llama/src/qwen3.rs:199-208).
+int32_t ferric_cuda_proj_from_gguf(ferric_cuda_ctx* ctx, const ferric_gguf* g, const char* const* names, size_t n_names,
+                                   ferric_proj** out)
+{
+    if (!ctx || !g || !names || n_names == 0 || n_names > 8 || !out) {
+        set_last_error("NULL argument, or not 1..8 tensor names");
+        return kErrInvalidArg;
+    }
+    *out = nullptr;
+    bool same = true;
+    uint32_t ty0 = 0;
+    for (size_t k = 0; k < n_names; k++) {
+        const TensorInfo* t = names[k] ? find_tensor(g, names[k]) : nullptr;
+        if (!t) {
+            set_last_error("no tensor '%s'", names[k] ? names[k] : "(null)");
+            return kErrInvalidArg;
+        }
+        if (k == 0) ty0 = t->ggml_type;
+        else if (t->ggml_type != ty0) same = false;
+    }
+    ferric_proj* p = new (std::nothrow) ferric_proj;
+    if (!p) return kErrOom;
+    int32_t rc = kOk;
+    if (same) {   // Fused: the parts' bytes stacked into one matrix (qm_cat), or the single weight (qm)
+        rc = ferric_cuda_qmatrix_from_gguf(ctx, g, names, n_names, &p->parts[0]);
+        p->n_parts = rc == kOk ? 1 : 0;
+    } else {      // Split: one matrix per part
+        for (size_t k = 0; k < n_names && rc == kOk; k++) {
+            rc = ferric_cuda_qmatrix_from_gguf(ctx, g, names + k, 1, &p->parts[k]);
+            if (rc == kOk) p->n_parts++;
+        }
+    }
+    if (rc == kOk) {
+        p->cols = ferric_cuda_qmatrix_cols(p->parts[0]);
+        for (size_t k = 0; k < p->n_parts; k++) {
+            p->rows += ferric_cuda_qmatrix_rows(p->parts[k]);
+            if (ferric_cuda_qmatrix_cols(p->parts[k]) != p->cols) {
+                set_last_error("%s: input dim differs", names[k]);
+                rc = kErrShape;
+            }
+        }
+    }
+    if (rc != kOk) {
+        ferric_cuda_proj_free(p);
+        return rc;
+    }
+    *out = p;
+    return kOk;
 }
 
 }  // extern "C"

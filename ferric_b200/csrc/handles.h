@@ -31,6 +31,13 @@ struct ferric_qmatrix {
     size_t storage_bytes = 0;
 };
 
+// Proj (crates/ferric-llama/src/qwen3.rs:192-228): one logical projection whose stacked outputs live in one matrix
+// (Fused: a single part) or, when the parts' quant formats differ, in one matrix per part (Split).
+struct ferric_proj {
+    ferric_qmatrix* parts[8] = {};
+    size_t n_parts = 0, rows = 0, cols = 0;
+};
+
 namespace ferric {
 
 // Makes `dev` current for the scope of a call and restores the caller's device afterwards.

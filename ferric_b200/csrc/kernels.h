@@ -96,7 +96,18 @@ struct ChainJob {
     float* ssq = nullptr;           // kinds 2, 3: [activation row][blocks] sums of squares of the updated residual
     PushSrc pushed;                 // kind 3
 };
+// Indexed (mixture-of-experts) products: the matrix stacks every expert's rows, expert-major, and each launch "pass"
+// (blockIdx.y) is one (token, expert slot) pair whose expert index is read on the device from the router's output
+// selw[token][w_0..w_{k-1} | idx_0..idx_{k-1}] (indices stored as f32).
+struct IdSel {
+    const float* selw = nullptr;   // null: not an indexed product
+    int k = 0;                     // expert slots per token
+    int n_expert = 0;              // an index outside [0, n_expert) yields zeros
+    int rows_per_expert = 0;       // matrix rows per expert (2 * eff for gate|up)
+    int x_per_pair = 0;            // 1: activation row = pair number (x is [T, k, in]); 0: activation row = token
+};
 struct Chain {
+    IdSel id;
     const float* ssq_in = nullptr;  // [activation row][ssq_blocks], or null: no scaling
     int ssq_blocks = 0;
     float eps = 0.0f, d = 1.0f;     // row length of the normalised vector, as a float
@@ -154,6 +165,13 @@ int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
                     const Chain* chain = nullptr);
 // Activation tiles (of two rows) the GEMV works on for m rows, padded to whole passes.
 size_t gemv_padded_tiles(size_t m);
+// Indexed products (IdSel): `pairs` = tokens x k launch passes over an expert-major matrix; y[pair][rows per expert]
+// (rows per expert / 2 with kEpiSwiglu), row stride ldy.
+int32_t launch_gemv_id(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const void* frag, size_t m, size_t pairs, float* y,
+                       size_t ldy, Epilogue epi, const GemvTuning& tune, const IdSel& id);
+// out[t][o] = sum over s in slot order of selw[t][s] * part[t * k + s][o]
+int32_t launch_id_wsum(cudaStream_t st, const float* part, const float* selw, size_t t, size_t k, size_t out_pe, float* out,
+                       const GemvTuning& tune);
 // Q8_0 needs no fragments: y = x . W^T straight from f32 activations.
 int32_t launch_gemv_q8_0(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y,
                          size_t ldy, const GemvTuning& tune);

@@ -699,11 +699,29 @@ __device__ __forceinline__ void chain_scales(float (&inv)[NT], const Chain& chai
     }
 }
 
+// Indexed product: which expert, activation row and result row this launch pass (blockIdx.y) works on.
+struct IdPick {
+    int batch = -1, out = 0, expert = 0;
+    bool ok = true;
+};
+__device__ __forceinline__ IdPick id_pick(const IdSel& id)
+{
+    IdPick p;
+    const int pair = blockIdx.y, tok = pair / id.k, slot = pair - tok * id.k;
+    const float fe = __ldcg(id.selw + (size_t)tok * 2 * id.k + id.k + slot);
+    p.expert = (int)fe;
+    p.ok = p.expert >= 0 && p.expert < id.n_expert;
+    if (!p.ok) p.expert = 0;
+    p.batch = id.x_per_pair ? pair : tok;
+    p.out = pair;
+    return p;
+}
+
 template <int NT, int EPI, bool CHAIN = false>
 __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*red)[NT * 4][32], float* __restrict__ y,
                                                  size_t ldy, int rows, int m, int tile0, int wk, int out_tile,
                                                  bool active, const PushDst& push, const float (&inv)[NT], const Chain& chain,
-                                                 uint8_t* warp_smem)
+                                                 uint8_t* warp_smem, int id_batch = -1, int id_out = 0, bool id_ok = true)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int kpart = warp % wk, wr = warp / wk;
@@ -751,7 +769,9 @@ __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*re
         }
         const int batch = (tile0 + nt) * kRowsPerTile + (t >> 1);
         const int r0 = out_tile * 16 + g;
-        if ((t & 1) == 0 && batch < m) store_result<EPI>(y, ldy, rows, batch, r0, lo, hi, push);
+        if (CHAIN && id_batch >= 0) {   // an indexed product keeps one activation row and stores it as its pair's row
+            if ((t & 1) == 0 && batch == id_batch) store_result<EPI>(y, ldy, rows, id_out, r0, id_ok ? lo : 0.0f, id_ok ? hi : 0.0f, push);
+        } else if ((t & 1) == 0 && batch < m) store_result<EPI>(y, ldy, rows, batch, r0, lo, hi, push);
     }
     if (CHAIN) {
         // this warp stored one 16-row tile of the result for every activation row; the warp that completes a 256-wide
@@ -847,8 +867,16 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
     pick_tile<EPI>(wk, row_tiles, ff_tiles, rt, out_tile, active);
     const int kpart = warp % wk, per = (nblk + wk - 1) / wk;
     const int b0 = kpart * per, b1 = min(nblk, b0 + per);
-    const int tile0 = blockIdx.y * NT;
+    int tile0 = blockIdx.y * NT;
     const int zero[4] = {0, 0, 0, 0};
+    IdPick idp;
+    if (CHAIN && chain.id.selw) {
+        // an indexed product learns its expert from the router's output, so nothing can be requested before the wait
+        pdl_wait();
+        idp = id_pick(chain.id);
+        units += (size_t)idp.expert * (chain.id.rows_per_expert / 16) * nblk * kUnitBytes;
+        tile0 = idp.batch / kRowsPerTile;
+    }
 
     float acc[NT][4];
 #pragma unroll
@@ -985,7 +1013,7 @@ gemv_q4k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
         }
     }
     reduce_and_store<NT, EPI, CHAIN>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push, inv,
-                                     chain, ring);
+                                     chain, ring, idp.batch, idp.out, idp.ok);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1104,8 +1132,15 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
     pick_tile<EPI>(wk, row_tiles, ff_tiles, rt, out_tile, active);
     const int kpart = warp % wk, per = (nblk + wk - 1) / wk;
     const int b0 = kpart * per, b1 = min(nblk, b0 + per);
-    const int tile0 = blockIdx.y * NT;
-    const int zero[4] = {0, 0, 0, 0};
+    int tile0 = blockIdx.y * NT;
+    IdPick idp;
+    if (CHAIN && chain.id.selw) {
+        // an indexed product learns its expert from the router's output, so nothing can be requested before the wait
+        pdl_wait();
+        idp = id_pick(chain.id);
+        units += (size_t)idp.expert * (chain.id.rows_per_expert / 16) * nblk * kQ6KUnit;
+        tile0 = idp.batch / kRowsPerTile;
+    }
 
     float acc[NT][4];
 #pragma unroll
@@ -1189,7 +1224,7 @@ gemv_q6k_kernel(const uint8_t* __restrict__ units, const uint2* __restrict__ fra
         }
     }
     reduce_and_store<NT, EPI, CHAIN>(acc, red, y, ldy, EPI == kEpiSwiglu ? rows / 2 : rows, m, tile0, wk, out_tile, active, push, inv,
-                                     chain, ring);
+                                     chain, ring, idp.batch, idp.out, idp.ok);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1476,6 +1511,57 @@ int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
 #undef FERRIC_GEMV_CASE
 #undef FERRIC_GEMV_CASE2
     FERRIC_CUDA_TRY(cudaGetLastError());
+    return kOk;
+}
+
+// Indexed products (crates/ferric-tensor/src/dtype.rs:1620-1677): one launch pass per (token, expert slot) pair over the
+// selected expert's rows, one activation tile per pass.
+int32_t launch_gemv_id(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const void* frag, size_t m, size_t pairs, float* y,
+                       size_t ldy, Epilogue epi, const GemvTuning& tune, const IdSel& id)
+{
+    if (pairs == 0 || id.rows_per_expert == 0) return kOk;
+    if (pairs > 65535) {
+        set_last_error("an indexed product takes at most 65535 (token, expert) pairs per call (%zu given)", pairs);
+        return kErrShape;
+    }
+    // the launch sees one expert's sub-matrix; the kernel moves the base to the pair's expert
+    DeviceWeights one = w;
+    one.rows = (size_t)id.rows_per_expert;
+    Chain chain;
+    chain.id = id;
+    const int wk = choose_wk(ty, one, epi, 1, tune);
+    const uint2* f = reinterpret_cast<const uint2*>(frag);
+    const PushDst none;
+    if (epi == kEpiSwiglu)
+        launch_gemv_t<1, kEpiSwiglu, true>(st, ty, one, f, m, y, ldy, wk, (unsigned)pairs, tune.pdl, none, tune.split_ws, false, 0, tune.sm_count, chain);
+    else
+        launch_gemv_t<1, kEpiStore, true>(st, ty, one, f, m, y, ldy, wk, (unsigned)pairs, tune.pdl, none, tune.split_ws, false, 0, tune.sm_count, chain);
+    FERRIC_CUDA_TRY(cudaGetLastError());
+    return kOk;
+}
+
+__global__ void id_wsum_kernel(const float* __restrict__ part, const float* __restrict__ selw, size_t t, size_t k, size_t out_pe,
+                               float* __restrict__ out)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t total = t * out_pe;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t ti = i / out_pe, o = i - ti * out_pe;
+        float tot = 0.0f;
+        for (size_t s = 0; s < k; s++) tot = tot + selw[ti * 2 * k + s] * part[(ti * k + s) * out_pe + o];   // slot order, as the reference sums
+        out[i] = tot;
+    }
+}
+
+int32_t launch_id_wsum(cudaStream_t st, const float* part, const float* selw, size_t t, size_t k, size_t out_pe, float* out,
+                       const GemvTuning& tune)
+{
+    const size_t total = t * out_pe;
+    if (total == 0) return kOk;
+    size_t g = (total + 255) / 256;
+    if (g > 148 * 16) g = 148 * 16;
+    FERRIC_CUDA_TRY(launch_kernel(id_wsum_kernel, dim3((unsigned)g), dim3(256), 0, st, tune.pdl, part, selw, t, k, out_pe, out));
     return kOk;
 }
 

@@ -333,6 +333,30 @@ class QMatrix:
         _check(rc, "matmul_q_swiglu")
         return y
 
+    def matmul_swiglu_id(self, x: torch.Tensor, selw: torch.Tensor, k: int, eff: int) -> torch.Tensor:
+        """``x.matmul_q4_k_swiglu_id(w, selw, k, eff)`` (crates/ferric-tensor/src/dtype.rs:1620-1637): this matrix stacks
+        every expert's gate|up rows; ``selw`` [t, 2k] holds the router's weights, then the expert indices as f32.
+        Returns [t, k, eff]."""
+        x, selw = x.contiguous(), selw.contiguous()
+        t = x.shape[0]
+        y = torch.empty((t, k, eff), dtype=torch.float32, device=x.device)
+        _check(self._lib.ferric_cuda_matmul_q_swiglu_id(self.ctx._h, self._h, x.data_ptr(), t, x.shape[1], selw.data_ptr(), k, eff,
+                                                        y.data_ptr()), "matmul_q_swiglu_id")
+        return y
+
+    def matmul_id_wsum(self, x: torch.Tensor, selw: torch.Tensor, out_pe: int) -> torch.Tensor:
+        """``x.matmul_q6_k_id_wsum(w, selw, out_pe)`` (crates/ferric-tensor/src/dtype.rs:1660-1677): ``x`` is [t, k, in]
+        (2-D [k, in] means one token); returns [t, out_pe], the selected experts' down products summed with the
+        router's weights."""
+        x, selw = x.contiguous(), selw.contiguous()
+        if x.dim() == 2:
+            x = x[None]
+        t, k = x.shape[0], x.shape[1]
+        y = torch.empty((t, out_pe), dtype=torch.float32, device=x.device)
+        _check(self._lib.ferric_cuda_matmul_q_id_wsum(self.ctx._h, self._h, x.data_ptr(), t, k, x.shape[2], selw.data_ptr(), out_pe,
+                                                      y.data_ptr()), "matmul_q_id_wsum")
+        return y
+
     def gate_up_swiglu(self, x: torch.Tensor) -> torch.Tensor:
         """``Proj::gate_up_swiglu`` (crates/ferric-llama/src/qwen3.rs:219-227): fused if possible."""
         y = self.try_matmul_swiglu(x)
@@ -350,6 +374,65 @@ class QMatrix:
             out = torch.empty((self.rows(), self.cols()), dtype=torch.float32, device=dev)
             _check(self._lib.ferric_cuda_dequant_f32(self.ctx._h, self._h, out.data_ptr()), "dequant_f32")
         return out
+
+
+class Proj:
+    """``Proj`` (crates/ferric-llama/src/qwen3.rs:192-228): q|k|v or gate|up as one fused matrix when the parts share a
+    quant format, else one matrix per part with the results written side by side."""
+
+    def __init__(self, ctx: Context, handle: C.c_void_p):
+        self.ctx, self._lib, self._h = ctx, ctx._lib, handle
+
+    @classmethod
+    def from_parts(cls, ctx: Context, parts) -> "Proj":
+        """A projection over matrices already built; it takes ownership of them."""
+        table = (C.c_void_p * len(parts))(*[q._h.value for q in parts])
+        h = C.c_void_p()
+        _check(ctx._lib.ferric_cuda_proj_from_parts(table, len(parts), C.byref(h)), "proj_from_parts")
+        for q in parts:
+            q._h = None
+        return cls(ctx, h)
+
+    def n_parts(self) -> int:
+        return int(self._lib.ferric_cuda_proj_n_parts(self._h))
+
+    def fused(self) -> bool:
+        return self.n_parts() == 1
+
+    def rows(self) -> int:
+        return int(self._lib.ferric_cuda_proj_rows(self._h))
+
+    def cols(self) -> int:
+        return int(self._lib.ferric_cuda_proj_cols(self._h))
+
+    def part_types(self):
+        return [int(self._lib.ferric_cuda_qmatrix_ggml_type(self._lib.ferric_cuda_proj_part(self._h, i))) for i in range(self.n_parts())]
+
+    def matmul(self, x: torch.Tensor) -> torch.Tensor:
+        """``Proj::matmul`` (:209-218)."""
+        x = x.contiguous() if x.dim() == 2 else x[None, :].contiguous()
+        y = torch.empty((x.shape[0], self.rows()), dtype=torch.float32, device=x.device)
+        _check(self._lib.ferric_cuda_proj_matmul(self.ctx._h, self._h, x.data_ptr(), x.shape[0], x.shape[1], y.data_ptr()), "proj_matmul")
+        return y
+
+    def gate_up_swiglu(self, x: torch.Tensor, n_ff: int) -> torch.Tensor:
+        """``Proj::gate_up_swiglu`` (:221-228)."""
+        x = x.contiguous() if x.dim() == 2 else x[None, :].contiguous()
+        y = torch.empty((x.shape[0], n_ff), dtype=torch.float32, device=x.device)
+        _check(self._lib.ferric_cuda_proj_gate_up_swiglu(self.ctx._h, self._h, x.data_ptr(), x.shape[0], x.shape[1], n_ff, y.data_ptr()),
+               "proj_gate_up_swiglu")
+        return y
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.ferric_cuda_proj_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class _DevView:
@@ -564,6 +647,13 @@ class Gguf:
         h = C.c_void_p()
         _check(self._lib.ferric_cuda_qmatrix_from_gguf(ctx._h, self._h, arr, len(names), C.byref(h)), "qmatrix_from_gguf")
         return QMatrix(ctx, h)
+
+    def proj(self, ctx: Context, *names: str) -> "Proj":
+        """``Proj::load`` (crates/ferric-llama/src/qwen3.rs:199-208): fused when the named weights share a format, split otherwise."""
+        arr = (C.c_char_p * len(names))(*[n.encode() for n in names])
+        h = C.c_void_p()
+        _check(self._lib.ferric_cuda_proj_from_gguf(ctx._h, self._h, arr, len(names), C.byref(h)), "proj_from_gguf")
+        return Proj(ctx, h)
 
     def close(self) -> None:
         if getattr(self, "_h", None):

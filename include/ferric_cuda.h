@@ -281,6 +281,22 @@ int32_t ferric_cuda_matmul_q_host(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm
 int32_t ferric_cuda_matmul_q_swiglu(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t m,
                                     size_t x_cols, float *y_dev);
 
+/* Tensor::matmul_q4_k_swiglu_id   crates/ferric-tensor/src/dtype.rs:1620-1637 (kernel :2463-2516), for Q4_K, Q5_K and
+ * Q6_K stacks: batched selected-expert gate|up + SwiGLU of a mixture-of-experts layer.  The matrix packs ALL experts'
+ * fused gate|up weights, expert-major: rows = n_expert * 2 * eff (expert e: eff gate rows, then eff up rows).
+ * x[t, cols]: one hidden row per token; selw[t, 2k] is the router's output (Tensor::moe_topk, :1582-1612): the k
+ * weights, then the k expert indices stored as f32.  y[t, k, eff] = silu(gate_e . x_t) * (up_e . x_t) for every
+ * (token, selected expert).  k in 1..8 (the reference's assert), eff a multiple of 16; an index outside the stack
+ * yields zeros.  All buffers on the device. */
+int32_t ferric_cuda_matmul_q_swiglu_id(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t t,
+                                       size_t x_cols, const float *selw_dev, size_t k, size_t eff, float *y_dev);
+/* Tensor::matmul_q6_k_id_wsum   crates/ferric-tensor/src/dtype.rs:1660-1677 (kernel :2538-2566; its Q4_K twin
+ * :2569-...): the selected experts' down projections with the weighted sum fused.  The matrix packs all experts' down
+ * weights, expert-major (rows = n_expert * out_pe); x[t, k, cols] holds row (t, s) = token t's slot-s SwiGLU output;
+ * y[t, out_pe] = sum over s, in slot order, of w_{t,s} * (down_{e_{t,s}} . x_{t,s}).  out_pe a multiple of 16. */
+int32_t ferric_cuda_matmul_q_id_wsum(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t t, size_t k,
+                                     size_t x_cols, const float *selw_dev, size_t out_pe, float *y_dev);
+
 /* Tensor::swiglu(d)   crates/ferric-tensor/src/lib.rs:726-737: gu[t, 2d] -> out[t, d]. */
 int32_t ferric_cuda_swiglu(ferric_cuda_ctx *ctx, const float *gu_dev, size_t t, size_t d, float *out_dev);
 
@@ -347,6 +363,30 @@ int32_t ferric_gguf_meta_arr_f64(const ferric_gguf *g, const char *key, size_t i
  * instead, which this library does not do). */
 int32_t ferric_cuda_qmatrix_from_gguf(ferric_cuda_ctx *ctx, const ferric_gguf *g, const char *const *names, size_t n_names,
                                       ferric_qmatrix **out);
+
+/* Proj   crates/ferric-llama/src/qwen3.rs:192-228: a projection that is logically one matmul with several stacked
+ * outputs (q|k|v, gate|up).  Proj::load (:199-208): when every named weight has the same quant format the bytes are
+ * stacked into ONE matrix (Fused: qm_cat, or qm for a single name); real Q4_K_M files mix formats inside q|k|v (V in
+ * Q6_K beside Q4_K Q and K, :188-191), and then each weight becomes a matrix of its own (Split).  Up to 8 names. */
+typedef struct ferric_proj ferric_proj;
+int32_t ferric_cuda_proj_from_gguf(ferric_cuda_ctx *ctx, const ferric_gguf *g, const char *const *names, size_t n_names,
+                                   ferric_proj **out);
+/* The same from matrices the caller built (a Split projection of `n_parts` parts, or Fused with one); the projection
+ * takes ownership of them and frees them with ferric_cuda_proj_free.  All parts: same device, same input dim. */
+int32_t ferric_cuda_proj_from_parts(ferric_qmatrix *const *parts, size_t n_parts, ferric_proj **out);
+size_t ferric_cuda_proj_n_parts(const ferric_proj *p); /* 1 = Proj::Fused */
+size_t ferric_cuda_proj_rows(const ferric_proj *p);    /* sum of the parts' rows */
+size_t ferric_cuda_proj_cols(const ferric_proj *p);
+const ferric_qmatrix *ferric_cuda_proj_part(const ferric_proj *p, size_t i);
+void ferric_cuda_proj_free(ferric_proj *p);
+/* Proj::matmul (:209-218): y[m, rows] = x . W^T, one product per part written at the part's column offset (the
+ * reference concatenates the parts' results); parts with the same activation form share one preparation of x. */
+int32_t ferric_cuda_proj_matmul(ferric_cuda_ctx *ctx, const ferric_proj *p, const float *x_dev, size_t m, size_t x_cols,
+                                float *y_dev);
+/* Proj::gate_up_swiglu (:221-228): y[m, n_ff] = silu(gate . x) * (up . x); one fused kernel when gate|up is a single
+ * Q4_K / Q5_K / Q6_K matrix (try_matmul_swiglu), otherwise the plain products followed by Tensor::swiglu. */
+int32_t ferric_cuda_proj_gate_up_swiglu(ferric_cuda_ctx *ctx, const ferric_proj *p, const float *x_dev, size_t m,
+                                        size_t x_cols, size_t n_ff, float *y_dev);
 
 /* ---- tensor-parallel exchange (one process per GPU) ------------------------------------- */
 /* The reference shards a QMatrix by rows and concatenates (crates/ferric-tensor/src/dtype.rs:893-908,

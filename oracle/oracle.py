@@ -178,6 +178,53 @@ def swiglu(gu: np.ndarray, d: int) -> np.ndarray:
     return out
 
 
+def _expert_rows(raw: np.ndarray, ty: int, cols: int, row0: int, nrows: int) -> np.ndarray:
+    vals, bb = block_bytes(ty)
+    rb = cols // vals * bb
+    return raw[row0 * rb:(row0 + nrows) * rb]
+
+
+def matmul_q_swiglu_id(raw, ty: int, n_expert: int, eff: int, cols: int, x: np.ndarray, selw: np.ndarray, k: int,
+                       mode: int = MODE_DEQUANT_DOT) -> np.ndarray:
+    """``Tensor::matmul_q4_k_swiglu_id`` (crates/ferric-tensor/src/dtype.rs:1620-1637, kernel :2463-2516): the stack
+    holds every expert's gate|up rows, expert-major; for token t and slot s the expert is ``u32(selw[t, k + s])``
+    (:2508), its gate row o is ``e * 2 eff + o`` and its up row ``e * 2 eff + eff + o`` (:2509-2512), and the result is
+    ``silu(g) * u`` (:2513).  Returns [t, k, eff]."""
+    raw = _bytes(raw)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    t = x.shape[0]
+    out = np.empty((t, k, eff), dtype=np.float32)
+    for ti in range(t):
+        for s in range(k):
+            e = int(np.uint32(selw[ti, k + s]))
+            assert 0 <= e < n_expert
+            gu = matmul_q(_expert_rows(raw, ty, cols, e * 2 * eff, 2 * eff), ty, 2 * eff, cols, x[ti:ti + 1], mode=mode)
+            out[ti, s] = swiglu(gu, eff)[0]
+    return out
+
+
+def matmul_q_id_wsum(raw, ty: int, n_expert: int, out_pe: int, cols: int, x: np.ndarray, selw: np.ndarray,
+                     mode: int = MODE_DEQUANT_DOT) -> np.ndarray:
+    """``Tensor::matmul_q6_k_id_wsum`` (crates/ferric-tensor/src/dtype.rs:1660-1677, kernel :2538-2566): x is
+    [t, k, in]; row t of the result is ``total = total + selw[t, s] * acc_s`` over the slots in order (:2562), acc_s
+    being expert ``u32(selw[t, k + s])``'s down rows times x[t, s] (:2553-2561).  Returns [t, out_pe]."""
+    raw = _bytes(raw)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    if x.ndim == 2:
+        x = x[None]
+    t, k = x.shape[0], x.shape[1]
+    out = np.zeros((t, out_pe), dtype=np.float32)
+    for ti in range(t):
+        total = np.zeros(out_pe, dtype=np.float32)
+        for s in range(k):
+            e = int(np.uint32(selw[ti, k + s]))
+            assert 0 <= e < n_expert
+            acc = matmul_q(_expert_rows(raw, ty, cols, e * out_pe, out_pe), ty, out_pe, cols, x[ti, s:s + 1], mode=mode)[0]
+            total = (total + np.float32(selw[ti, s]) * acc).astype(np.float32)
+        out[ti] = total
+    return out
+
+
 def add_rmsnorm(a: np.ndarray, b=None, w=None, eps: float = 1e-6):
     """(sum, norm) as the reference's add_rmsnorm kernel computes them; b=None is plain rmsnorm."""
     a = np.ascontiguousarray(a, dtype=np.float32)

@@ -138,3 +138,25 @@ def test_stride_guards():
     with pytest.raises(FerricError):
         g.raw("odd")
     assert g.raw("a").tobytes() == q4
+
+
+def test_dims_whose_product_wraps_are_refused_before_any_size_arithmetic():
+    """Hostile dims: rows = 2^60 + 1 with 256 columns of Q4_K multiply to a byte count that wraps to 144 in 64 bits and
+    would pass every later length check; the parser refuses the header (status FERRIC_ERR_SHAPE), so no allocation is
+    sized and no kernel is launched from such a record.  The matrix constructor applies the same rule to its own
+    arguments, which needs no device: it fails on the size before it looks for one."""
+    rng = np.random.default_rng(6)
+    q4 = synth.q4k_blocks(rng, 1).tobytes()                        # 144 bytes: what the wrapped product asks for
+    for dims in ([256, 2 ** 60 + 1], [2 ** 32, 2 ** 32], [2 ** 63, 2], [256, 2 ** 63]):
+        with pytest.raises(FerricError) as e:
+            Gguf.parse(W.build([], [("a", dims, 12, q4)]))
+        assert e.value.status == 3 and "overflow" in str(e.value)
+    # an honest large count still parses (it is then refused for not fitting the file)
+    with pytest.raises(FerricError, match="leaves only"):
+        Gguf.parse(W.build([], [("a", [256, 2 ** 40], 12, q4)]))
+    from ferric_b200 import _lib
+    import ctypes as C
+    lib = _lib.load()
+    out = C.c_size_t(0)
+    assert lib.ferric_gguf_type_size(0, 2 ** 63, C.byref(out)) == 3          # n * 4 would wrap
+    assert lib.ferric_gguf_type_size(12, 2 ** 63, C.byref(out)) == 0 and out.value == 2 ** 63 // 256 * 144

@@ -90,3 +90,64 @@ def _mismatch(F, ctx):
         g.qmatrix(ctx, "a", "b")
     finally:
         g.close()
+
+
+def test_proj_fused_and_split(F, ctx):
+    """Proj::load / matmul / gate_up_swiglu (crates/ferric-llama/src/qwen3.rs:192-228): q|k|v with V in Q6_K beside
+    Q4_K Q and K -- the mix real Q4_K_M files carry -- loads as a Split projection and its product equals the
+    reference's matmul-per-part-and-concatenate on the oracle; same formats load Fused; gate|up goes through the fused
+    SwiGLU kernel when it is one matrix and through matmul + swiglu when it is not, with the same result."""
+    rng = np.random.default_rng(3)
+    hidden, nq, nkv, n_ff = 512, 96, 32, 64
+    q = synth.q4k_blocks(rng, nq * hidden // 256)
+    k = synth.q4k_blocks(rng, nkv * hidden // 256)
+    v6 = synth.q6k_blocks(rng, nkv * hidden // 256)
+    v4 = synth.q4k_blocks(rng, nkv * hidden // 256)
+    gate = synth.q4k_blocks(rng, n_ff * hidden // 256)
+    up4 = synth.q4k_blocks(rng, n_ff * hidden // 256)
+    up6 = synth.q6k_blocks(rng, n_ff * hidden // 256)
+    v8 = synth.q8_0_blocks(rng, nkv * hidden // 32)
+    g = F.Gguf.parse(W.build([], [("q", [hidden, nq], 12, q.tobytes()), ("k", [hidden, nkv], 12, k.tobytes()),
+                                  ("v6", [hidden, nkv], 14, v6.tobytes()), ("v4", [hidden, nkv], 12, v4.tobytes()),
+                                  ("v8", [hidden, nkv], 8, v8.tobytes()),
+                                  ("gate", [hidden, n_ff], 12, gate.tobytes()), ("up4", [hidden, n_ff], 12, up4.tobytes()),
+                                  ("up6", [hidden, n_ff], 14, up6.tobytes())]))
+    tol = lambda got, ref: (np.abs(got - ref) <= 1e-4 + 1e-3 * np.abs(ref)).all()
+    for m in (1, 3, 20):                                            # 20 rows: the tensor-core decode kernel on the Q4_K parts
+        x = synth.activations(m, hidden, seed=m)
+        xd = torch.from_numpy(x).cuda()
+        split = g.proj(ctx, "q", "k", "v6")
+        assert not split.fused() and split.part_types() == [12, 12, 14] and (split.rows(), split.cols()) == (nq + 2 * nkv, hidden)
+        ref = np.concatenate([O.matmul_q(q, 12, nq, hidden, x), O.matmul_q(k, 12, nkv, hidden, x), O.matmul_q(v6, 14, nkv, hidden, x)], axis=1)
+        assert tol(split.matmul(xd).cpu().numpy(), ref)
+        three = g.proj(ctx, "q", "v8", "v6")                        # a part without a prepared form between two that have one
+        ref3 = np.concatenate([O.matmul_q(q, 12, nq, hidden, x), O.matmul_q(v8, 8, nkv, hidden, x), O.matmul_q(v6, 14, nkv, hidden, x)], axis=1)
+        assert tol(three.matmul(xd).cpu().numpy(), ref3)
+        fused = g.proj(ctx, "q", "k", "v4")
+        assert fused.fused() and fused.part_types() == [12]
+        reff = O.matmul_q(np.concatenate([q, k, v4]), 12, nq + 2 * nkv, hidden, x)
+        assert tol(fused.matmul(xd).cpu().numpy(), reff)
+        gu_f, gu_s = g.proj(ctx, "gate", "up4"), g.proj(ctx, "gate", "up6")
+        assert gu_f.fused() and not gu_s.fused()
+        ref_f = O.swiglu(O.matmul_q(np.concatenate([gate, up4]), 12, 2 * n_ff, hidden, x), n_ff)
+        ref_s = O.swiglu(np.concatenate([O.matmul_q(gate, 12, n_ff, hidden, x), O.matmul_q(up6, 14, n_ff, hidden, x)], axis=1), n_ff)
+        assert tol(gu_f.gate_up_swiglu(xd, n_ff).cpu().numpy(), ref_f)
+        assert tol(gu_s.gate_up_swiglu(xd, n_ff).cpu().numpy(), ref_s)
+        with pytest.raises(F.FerricError) as e:
+            gu_s.gate_up_swiglu(xd, n_ff + 16)
+        assert e.value.status == 3
+        for p in (split, three, fused, gu_f, gu_s):
+            p.close()
+    single = g.proj(ctx, "q")
+    assert single.fused() and single.rows() == nq
+    single.close()
+    with pytest.raises(F.FerricError, match="no tensor"):
+        g.proj(ctx, "q", "nope")
+    # a projection over matrices built by hand
+    parts = [F.QMatrix.from_bytes(ctx, q, 12, nq, hidden), F.QMatrix.from_bytes(ctx, v6, 14, nkv, hidden)]
+    p = F.Proj.from_parts(ctx, parts)
+    x = synth.activations(2, hidden, seed=9)
+    ref = np.concatenate([O.matmul_q(q, 12, nq, hidden, x), O.matmul_q(v6, 14, nkv, hidden, x)], axis=1)
+    assert tol(p.matmul(torch.from_numpy(x).cuda()).cpu().numpy(), ref)
+    p.close()
+    g.close()

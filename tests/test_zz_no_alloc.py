@@ -14,6 +14,7 @@ import pytest
 import torch
 
 from ferric_b200 import synth
+from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -57,4 +58,33 @@ def test_noalloc_matches_matmul_q_on_two_calls_in_a_row():
     assert e.value.status == 3 and "fixed" in str(e.value)
     for qm in mats + [big]:
         qm.close()
+    ctx.close()
+
+
+@pytest.mark.parametrize("ty,rows,cols", [(12, 272, 1024), (14, 144, 768)])
+@pytest.mark.parametrize("m", [9, 16])
+def test_noalloc_above_eight_rows_against_the_oracle(ty, rows, cols, m):
+    """Above 8 activation rows the ordinary entry point may pick another kernel (the tensor-core decode kernel) while
+    the allocation-free one runs GEMV passes out of its fixed array, so here the check is against the CPU oracle
+    directly, element by element (1e-3 relative + 1e-4 absolute), twice in a row -- and against ``ferric_cuda_matmul_q``
+    within the same bar."""
+    import ferric_b200 as F
+    from ferric_b200 import _lib
+
+    lib = _lib.load()
+    ctx = F.Context(0)
+    raw = synth.matrix(ty, rows, cols, seed=70 + m)
+    qm = F.QMatrix.from_bytes(ctx, raw, ty, rows, cols)
+    for rep in range(2):
+        x = synth.activations(m, cols, seed=80 + rep)
+        xd = torch.from_numpy(x).cuda()
+        out = torch.full((m, rows), float("nan"), device="cuda")
+        rc = lib.ferric_cuda_matmul_q_noalloc(ctx._h, qm._h, C.c_void_p(xd.data_ptr()), m, cols, C.c_void_p(out.data_ptr()))
+        assert rc == 0, lib.ferric_cuda_last_error()
+        got = out.cpu().numpy()
+        ref = O.matmul_q(raw, ty, rows, cols, x)
+        assert (np.abs(got - ref) <= 1e-4 + 1e-3 * np.abs(ref)).all()
+        other = qm.matmul(xd).cpu().numpy()
+        assert (np.abs(got - other) <= 1e-4 + 1e-3 * np.abs(other)).all()
+    qm.close()
     ctx.close()
