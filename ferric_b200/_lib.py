@@ -55,6 +55,7 @@ SIGNATURES = {
     "ferric_cuda_qmatrix_from_bytes": (_I32, [_P, _P, _SZ, _U32, _SZ, _SZ, C.POINTER(_P)]),
     "ferric_cuda_qmatrix_from_bytes_view": (_I32, [_P, _P, _SZ, _U32, _SZ, _SZ, _SZ, _SZ, _SZ, _SZ, C.POINTER(_P)]),
     "ferric_cuda_qmatrix_from_device_bytes": (_I32, [_P, _P, _SZ, _U32, _SZ, _SZ, C.POINTER(_P)]),
+    "ferric_cuda_qmatrix_from_dense": (_I32, [_P, _P, _SZ, _SZ, C.POINTER(_P)]),
     "ferric_cuda_qmatrix_rows": (_SZ, [_P]),
     "ferric_cuda_qmatrix_cols": (_SZ, [_P]),
     "ferric_cuda_qmatrix_nbytes": (_SZ, [_P]),

@@ -208,13 +208,15 @@ int32_t run_matmul(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, const float* 
         set_last_error("row strides (ldx %zu, ldy %zu) must cover the rows and ldx be a multiple of 4", ldx, ldy);
         return kErrShape;
     }
-    if (qm->ty == kGgmlQ8_0) {
+    if (!has_prepared_form(qm->ty)) {
         if (!(phases & 2)) return kOk;
         if (!x) {
-            set_last_error("Q8_0 has no prepared form: pass the activations");
+            set_last_error("this format has no prepared form: pass the activations");
             return kErrInvalidArg;
         }
+        if (epi != kEpiStore) return kUnsupported;
         ctx->launches++;
+        if (qm->ty == kGgmlF32) return launch_gemv_f32(ctx->stream, qm->w, x, m, ldx, y, ldy, ctx->tune);
         return launch_gemv_q8_0(ctx->stream, qm->w, x, m, ldx, y, ldy, ctx->tune);
     }
     if (qm->w.nblk == 0) {  // cols == 0: an empty sum
@@ -452,11 +454,47 @@ int32_t ferric_cuda_qmatrix_from_device_bytes(ferric_cuda_ctx* ctx, const uint8_
     return build_matrix(ctx, bytes_dev, true, len, ty, rows, cols, 0, rows, 0, cols, out);
 }
 
+int32_t ferric_cuda_qmatrix_from_dense(ferric_cuda_ctx* ctx, const float* w_host, size_t rows, size_t cols, ferric_qmatrix** out)
+{
+    if (!ctx || !out || (rows * cols > 0 && !w_host)) {
+        set_last_error("NULL context, weights or output pointer");
+        return kErrInvalidArg;
+    }
+    *out = nullptr;
+    size_t bytes = 0;
+    if (rows > (size_t)INT32_MAX || cols > (size_t)INT32_MAX || __builtin_mul_overflow(rows, cols, &bytes) ||
+        __builtin_mul_overflow(bytes, sizeof(float), &bytes)) {
+        set_last_error("matrix [%zu, %zu] is larger than this backend indexes", rows, cols);
+        return kErrShape;
+    }
+    DeviceGuard guard(ctx->device);
+    if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+    ferric_qmatrix* qm = new (std::nothrow) ferric_qmatrix;
+    if (!qm) return kErrOom;
+    qm->ty = kGgmlF32;
+    qm->device = ctx->device;
+    qm->w.rows = rows;
+    qm->w.cols = cols;
+    qm->storage_bytes = bytes ? bytes : 16;
+    cudaError_t e = cudaMalloc(&qm->storage, qm->storage_bytes);
+    if (e == cudaSuccess && bytes) e = cudaMemcpyAsync(qm->storage, w_host, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);   // the host pointer is not kept
+    if (e != cudaSuccess) {
+        if (qm->storage) cudaFree(qm->storage);
+        delete qm;
+        return cuda_fail(e, "qmatrix_from_dense");
+    }
+    qm->w.dense = reinterpret_cast<float*>(qm->storage);
+    *out = qm;
+    return kOk;
+}
+
 size_t ferric_cuda_qmatrix_rows(const ferric_qmatrix* qm) { return qm ? qm->w.rows : 0; }
 size_t ferric_cuda_qmatrix_cols(const ferric_qmatrix* qm) { return qm ? qm->w.cols : 0; }
 size_t ferric_cuda_qmatrix_nbytes(const ferric_qmatrix* qm)
 {
     if (!qm) return 0;
+    if (qm->ty == kGgmlF32) return qm->w.rows * qm->w.cols * sizeof(float);   // DenseWeight::nbytes, dtype.rs:826
     size_t vals, bytes;
     block_info(qm->ty, &vals, &bytes);
     return qm->w.rows * (qm->w.cols / vals) * bytes;
@@ -537,7 +575,7 @@ int32_t ferric_cuda_matmul_q_swiglu(ferric_cuda_ctx* ctx, const ferric_qmatrix* 
 {
     int32_t rc = check_matmul_args(ctx, qm, x_dev, m, x_cols, y_dev);
     if (rc != kOk) return rc;
-    if (qm->ty == kGgmlQ8_0 || qm->w.rows % 32 != 0) return kUnsupported;
+    if (!has_prepared_form(qm->ty) || qm->w.rows % 32 != 0) return kUnsupported;
     DeviceGuard guard(ctx->device);
     return run_matmul(ctx, qm, x_dev, m, 0, y_dev, 0, kEpiSwiglu);
 }
@@ -557,6 +595,10 @@ int32_t ferric_cuda_prepare_x(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, co
     float dummy;
     int32_t rc = check_matmul_args(ctx, qm, x_dev, m, x_cols, &dummy);
     if (rc != kOk) return rc;
+    if (!has_prepared_form(qm->ty)) {
+        set_last_error("Q8_0 and dense matrices have no prepared form");
+        return kUnsupported;
+    }
     DeviceGuard guard(ctx->device);
     return run_matmul(ctx, qm, x_dev, m, ldx, nullptr, 0, kEpiStore, 1);
 }
@@ -568,8 +610,8 @@ int32_t ferric_cuda_matmul_q_prepared(ferric_cuda_ctx* ctx, const ferric_qmatrix
         set_last_error("NULL context, matrix or result buffer");
         return kErrInvalidArg;
     }
-    if (qm->ty == kGgmlQ8_0) {
-        set_last_error("Q8_0 has no prepared form");
+    if (!has_prepared_form(qm->ty)) {
+        set_last_error("Q8_0 and dense matrices have no prepared form");
         return kUnsupported;
     }
     if (swiglu && qm->w.rows % 32 != 0) return kUnsupported;
@@ -597,8 +639,8 @@ int32_t ferric_cuda_add_rmsnorm_prepare(ferric_cuda_ctx* ctx, const ferric_qmatr
         set_last_error("NULL context, matrix or buffer");
         return kErrInvalidArg;
     }
-    if (qm->ty == kGgmlQ8_0) {
-        set_last_error("Q8_0 has no prepared form");
+    if (!has_prepared_form(qm->ty)) {
+        set_last_error("Q8_0 and dense matrices have no prepared form");
         return kUnsupported;
     }
     if ((reinterpret_cast<uintptr_t>(a_dev) | reinterpret_cast<uintptr_t>(b_dev) | reinterpret_cast<uintptr_t>(sum_dev) |
@@ -669,6 +711,10 @@ int32_t ferric_cuda_dequant_f32(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm, 
         return kErrInvalidArg;
     }
     DeviceGuard guard(ctx->device);
+    if (qm->ty == kGgmlF32) {
+        FERRIC_CUDA_TRY(cudaMemcpyAsync(out_dev, qm->w.dense, qm->w.rows * qm->w.cols * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+        return kOk;
+    }
     ctx->launches++;
     return launch_dequant_weights(ctx->stream, qm->ty, qm->w, out_dev, false);
 }
@@ -678,6 +724,10 @@ int32_t ferric_cuda_dequant_bf16(ferric_cuda_ctx* ctx, const ferric_qmatrix* qm,
     if (!ctx || !qm || (!out_dev && qm->w.rows * qm->w.cols > 0)) {
         set_last_error("NULL context, matrix or output");
         return kErrInvalidArg;
+    }
+    if (qm->ty == kGgmlF32) {
+        set_last_error("a dense matrix has no bf16 decode");
+        return kUnsupported;
     }
     DeviceGuard guard(ctx->device);
     ctx->launches++;
@@ -781,7 +831,7 @@ static int32_t proj_matmul_ld(ferric_cuda_ctx* ctx, const ferric_proj* p, const 
         const ferric_qmatrix* qm = p->parts[k];
         float* yk = y + col;
         col += qm->w.rows;
-        if (qm->ty == kGgmlQ8_0 || gemv_tc_eligible(qm->ty, qm->w, m) || qm->w.nblk == 0) {
+        if (!has_prepared_form(qm->ty) || gemv_tc_eligible(qm->ty, qm->w, m) || qm->w.nblk == 0) {
             rc = run_matmul(ctx, qm, x, m, 0, yk, ldy, kEpiStore);
             prepared_for = nullptr;   // the tensor-core path uses the scratch for its own activation form
             continue;
@@ -825,7 +875,7 @@ int32_t ferric_cuda_proj_gate_up_swiglu(ferric_cuda_ctx* ctx, const ferric_proj*
     }
     if (m == 0 || n_ff == 0) return kOk;
     DeviceGuard guard(ctx->device);
-    if (p->n_parts == 1 && p->parts[0]->ty != kGgmlQ8_0 && p->parts[0]->w.rows % 32 == 0)
+    if (p->n_parts == 1 && has_prepared_form(p->parts[0]->ty) && p->parts[0]->w.rows % 32 == 0)
         return run_matmul(ctx, p->parts[0], x_dev, m, 0, y_dev, 0, kEpiSwiglu);
     float* gu = nullptr;
     FERRIC_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&gu), m * p->rows * sizeof(float), ctx->stream));
@@ -949,8 +999,8 @@ int32_t chain_setup(ferric_cuda_ctx* ctx, const ferric_chain_link* link, size_t 
         set_last_error("matrix lives on device %d, context on device %d", qm->device, ctx->device);
         return kErrInvalidArg;
     }
-    if (qm->ty == kGgmlQ8_0) {
-        set_last_error("Q8_0 has no prepared form, so it cannot be a chain link");
+    if (!has_prepared_form(qm->ty)) {
+        set_last_error("Q8_0 and dense matrices have no prepared form, so they cannot be chain links");
         return kUnsupported;
     }
     if (link->swiglu && qm->w.rows % 32 != 0) return kUnsupported;
@@ -995,7 +1045,7 @@ int32_t chain_setup(ferric_cuda_ctx* ctx, const ferric_chain_link* link, size_t 
             set_last_error("chain_matmul: unknown `next` %d", link->next);
             return kErrInvalidArg;
         }
-        if (!nx || nx->device != ctx->device || nx->ty == kGgmlQ8_0) {
+        if (!nx || nx->device != ctx->device || !has_prepared_form(nx->ty)) {
             set_last_error("chain_matmul: next_qm must be a Q4_K / Q5_K / Q6_K matrix on the context's device");
             return kErrInvalidArg;
         }
@@ -1117,8 +1167,9 @@ int32_t ferric_cuda_matmul_q_noalloc(ferric_cuda_ctx* ctx, const ferric_qmatrix*
     if (rc != kOk) return rc;
     if (m == 0 || qm->w.rows == 0) return kOk;
     DeviceGuard guard(ctx->device);
-    if (qm->ty == kGgmlQ8_0) {  // this format needs no scratch at all
+    if (!has_prepared_form(qm->ty)) {  // these formats need no scratch at all
         ctx->launches++;
+        if (qm->ty == kGgmlF32) return launch_gemv_f32(ctx->stream, qm->w, x_dev, m, qm->w.cols, y_dev, qm->w.rows, ctx->tune);
         return launch_gemv_q8_0(ctx->stream, qm->w, x_dev, m, qm->w.cols, y_dev, qm->w.rows, ctx->tune);
     }
     if (qm->w.nblk == 0) {

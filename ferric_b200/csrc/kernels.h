@@ -6,7 +6,9 @@
 
 namespace ferric {
 
-constexpr uint32_t kGgmlQ8_0 = 8, kGgmlQ4K = 12, kGgmlQ5K = 13, kGgmlQ6K = 14;
+constexpr uint32_t kGgmlF32 = 0, kGgmlQ8_0 = 8, kGgmlQ4K = 12, kGgmlQ5K = 13, kGgmlQ6K = 14;
+// The formats whose product runs from prepared activation fragments (the tensor-core GEMV kernels).
+inline bool has_prepared_form(uint32_t ty) { return ty == kGgmlQ4K || ty == kGgmlQ5K || ty == kGgmlQ6K; }
 
 // One packed weight matrix in device memory.  rows x cols logical; nblk = blocks per row
 // (256-weight super-blocks for Q4_K/Q6_K, 32-weight blocks for Q8_0).
@@ -14,6 +16,7 @@ struct DeviceWeights {
     uint8_t* units = nullptr;    // Q4_K / Q6_K: ceil(rows/16) * nblk units, zero padded past `rows`
     int8_t* q8_qs = nullptr;     // Q8_0: [rows][cols] int8
     uint16_t* q8_d = nullptr;    // Q8_0: [rows][cols/32] f16 bits
+    float* dense = nullptr;      // dense f32 (QMatrix::from_dense): [rows][cols] row-major
     size_t rows = 0, cols = 0, nblk = 0;
     size_t row_tiles() const { return (rows + 15) / 16; }
 };
@@ -175,6 +178,9 @@ int32_t launch_id_wsum(cudaStream_t st, const float* part, const float* selw, si
 // Q8_0 needs no fragments: y = x . W^T straight from f32 activations.
 int32_t launch_gemv_q8_0(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y,
                          size_t ldy, const GemvTuning& tune);
+// Dense f32 weights [rows, cols] (the fallback for formats without a packed kernel): y = x . W^T.
+int32_t launch_gemv_f32(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y,
+                        size_t ldy, const GemvTuning& tune);
 // out[t, d] = silu(gu[t, d]) * gu[t, d + ..] on a [t, 2d] tensor (the unfused twin).
 int32_t launch_swiglu(cudaStream_t st, const float* gu, size_t t, size_t d, float* out, const GemvTuning& tune);
 

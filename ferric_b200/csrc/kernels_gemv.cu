@@ -460,7 +460,7 @@ size_t gemv_padded_tiles(size_t m) { return padded_tiles(m); }
 
 size_t frag_bytes(uint32_t ty, const DeviceWeights& w, size_t m)
 {
-    if (ty == kGgmlQ8_0 || m == 0) return 0;
+    if (!has_prepared_form(ty) || m == 0) return 0;
     size_t steps = (ty == kGgmlQ4K || ty == kGgmlQ5K) ? kQ4KSteps : kQ6KSteps;   // Q5_K shares Q4_K's fragments
     return padded_tiles(m) * w.nblk * steps * 32 * sizeof(uint2);
 }
@@ -1626,6 +1626,58 @@ int32_t launch_gemv_q8_0(cudaStream_t st, const DeviceWeights& w, const float* x
     dim3 grid((unsigned)((w.rows + 7) / 8), (unsigned)((m + 3) / 4));
     FERRIC_CUDA_TRY(launch_kernel(gemv_q8_0_kernel<4>, grid, dim3(256), 0, st, tune.pdl, w.q8_qs, w.q8_d, x, (int)m, ldx, y,
                                   ldy, (int)w.rows, (int)w.cols));
+    return kOk;
+}
+
+// Dense f32 weights (QMatrix::from_dense, crates/ferric-tensor/src/dtype.rs:912-926: the fallback for formats without a
+// packed kernel, which the loader dequantises): one warp per output row, 128-bit loads, warp-shuffle reduction.
+template <int MB>
+__global__ void __launch_bounds__(256) gemv_f32_kernel(const float* __restrict__ w, const float* __restrict__ x, int m, size_t ldx,
+                                                       float* __restrict__ y, size_t ldy, int rows, int cols)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * 8 + warp;
+    if (row >= rows) return;
+    const int batch0 = blockIdx.y * MB;
+    float acc[MB];
+#pragma unroll
+    for (int i = 0; i < MB; i++) acc[i] = 0.0f;
+    const float* wrow = w + (size_t)row * cols;
+    const int nvec = ((reinterpret_cast<uintptr_t>(wrow) & 15) == 0) ? cols / 4 : 0;   // rows of an odd length are not all 16-byte aligned
+    for (int c = lane; c < nvec; c += 32) {
+        const uint4 wb = ld_stream_u4(wrow + 4 * c);
+        const float w0 = __uint_as_float(wb.x), w1 = __uint_as_float(wb.y), w2 = __uint_as_float(wb.z), w3 = __uint_as_float(wb.w);
+#pragma unroll
+        for (int i = 0; i < MB; i++) {
+            if (batch0 + i >= m) break;
+            const float4 xv = ld_act(reinterpret_cast<const float4*>(x + (size_t)(batch0 + i) * ldx) + c);
+            acc[i] = fmaf(xv.w, w3, fmaf(xv.z, w2, fmaf(xv.y, w1, fmaf(xv.x, w0, acc[i]))));
+        }
+    }
+    for (int c = 4 * nvec + lane; c < cols; c += 32) {
+        const float wv = wrow[c];
+#pragma unroll
+        for (int i = 0; i < MB; i++)
+            if (batch0 + i < m) acc[i] = fmaf(x[(size_t)(batch0 + i) * ldx + c], wv, acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < MB; i++) {
+        float v = acc[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && batch0 + i < m) y[(size_t)(batch0 + i) * ldy + row] = v;
+    }
+}
+
+int32_t launch_gemv_f32(cudaStream_t st, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y, size_t ldy,
+                        const GemvTuning& tune)
+{
+    if (m == 0 || w.rows == 0) return kOk;
+    dim3 grid((unsigned)((w.rows + 7) / 8), (unsigned)((m + 3) / 4));
+    FERRIC_CUDA_TRY(launch_kernel(gemv_f32_kernel<4>, grid, dim3(256), 0, st, tune.pdl, w.dense, x, (int)m, ldx, y, ldy, (int)w.rows,
+                                  (int)w.cols));
     return kOk;
 }
 

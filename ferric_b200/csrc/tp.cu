@@ -249,7 +249,7 @@ int32_t ferric_cuda_tp_add_rmsnorm_prepare(ferric_cuda_ctx* ctx, ferric_tp_group
         set_last_error("tp_add_rmsnorm_prepare: NULL / unconnected argument or bad kind");
         return kErrInvalidArg;
     }
-    if (qm->ty == kGgmlQ8_0) return kUnsupported;
+    if (!has_prepared_form(qm->ty)) return kUnsupported;
     if (m * qm->w.cols > g->elems) {
         set_last_error("exchange buffers hold %zu floats, %zu x %zu requested", g->elems, m, qm->w.cols);
         return kErrShape;
@@ -278,7 +278,7 @@ int32_t ferric_cuda_tp_matmul_push(ferric_cuda_ctx* ctx, ferric_tp_group* g, int
         set_last_error("tp_matmul_push: NULL / unconnected argument or bad kind");
         return kErrInvalidArg;
     }
-    if (qm->ty == kGgmlQ8_0) return kUnsupported;
+    if (!has_prepared_form(qm->ty)) return kUnsupported;
     if (ldx == 0) ldx = qm->w.cols;
     if (ldx < qm->w.cols || (ldx & 3)) {
         set_last_error("row stride ldx %zu must cover the row and be a multiple of 4", ldx);
@@ -312,7 +312,7 @@ int32_t ferric_cuda_tp_add_rmsnorm_prepare_pushed(ferric_cuda_ctx* ctx, ferric_t
         set_last_error("tp_add_rmsnorm_prepare_pushed: NULL / unconnected argument (sum_dev is required) or bad kind");
         return kErrInvalidArg;
     }
-    if (qm->ty == kGgmlQ8_0) return kUnsupported;
+    if (!has_prepared_form(qm->ty)) return kUnsupported;
     if (m * qm->w.cols > g->elems) {
         set_last_error("exchange buffers hold %zu floats, %zu x %zu requested", g->elems, m, qm->w.cols);
         return kErrShape;

@@ -181,6 +181,15 @@ class QMatrix:
                                                               cols, C.byref(h)), "QMatrix.from_device_bytes")
         return cls(ctx, h)
 
+    @classmethod
+    def from_dense(cls, ctx: Context, w: np.ndarray) -> "QMatrix":
+        """``QMatrix::from_dense`` (crates/ferric-tensor/src/dtype.rs:912-926): an already dequantised row-major
+        [rows, cols] weight, the fallback for formats without a packed kernel."""
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        h = C.c_void_p()
+        _check(ctx._lib.ferric_cuda_qmatrix_from_dense(ctx._h, w.ctypes.data, w.shape[0], w.shape[1], C.byref(h)), "QMatrix.from_dense")
+        return cls(ctx, h)
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             self._lib.ferric_cuda_qmatrix_free(self._h)

@@ -130,6 +130,13 @@ int32_t ferric_cuda_qmatrix_from_bytes_view(ferric_cuda_ctx *ctx, const uint8_t 
 int32_t ferric_cuda_qmatrix_from_device_bytes(ferric_cuda_ctx *ctx, const uint8_t *bytes_dev, size_t len,
                                               uint32_t ggml_type, size_t rows, size_t cols, ferric_qmatrix **out);
 
+/* QMatrix::from_dense(ctx, w, rows, cols)   crates/ferric-tensor/src/dtype.rs:912-926 (DenseWeight :817-834): the
+ * fallback for GGUF quants with no packed kernel -- the loader dequantises them to f32 and hands the row-major
+ * [rows, cols] weight here (HOST pointer, copied).  matmul_q on such a matrix is a plain f32 product; it reports ggml
+ * type FERRIC_GGML_F32, nbytes = rows * cols * 4, has no prepared form, no fused SwiGLU and no bf16 product
+ * (FERRIC_UNSUPPORTED), as in the reference. */
+int32_t ferric_cuda_qmatrix_from_dense(ferric_cuda_ctx *ctx, const float *w_host, size_t rows, size_t cols, ferric_qmatrix **out);
+
 /* QMatrix::rows / cols / nbytes / n_shards   crates/ferric-tensor/src/dtype.rs:927-930.
  * nbytes is the on-disk format size (rows * cols / 256 * 144 for Q4_K, :1421). */
 size_t ferric_cuda_qmatrix_rows(const ferric_qmatrix *qm);

@@ -416,6 +416,34 @@ def test_decode_stack_step_matches_layerwise_oracle(F, ctx):
     st.close()
 
 
+def test_dense_fallback_matrix(F, ctx):
+    """QMatrix::from_dense (crates/ferric-tensor/src/dtype.rs:912-926): a format without a packed kernel reaches the
+    matmul as an already dequantised f32 weight; the product is the reference's dense x . W^T."""
+    rows, cols = 203, 1000                                         # neither a tile nor a vector multiple
+    rng = np.random.default_rng(17)
+    w = rng.standard_normal((rows, cols)).astype(np.float32) * np.float32(0.05)
+    qm = F.QMatrix.from_dense(ctx, w)
+    assert (qm.rows(), qm.cols(), qm.ggml_type(), qm.n_shards(), qm.nbytes()) == (rows, cols, 0, 1, rows * cols * 4)
+    assert np.array_equal(qm.dequant().cpu().numpy(), w)
+    for m in (1, 3, 9):
+        x = synth.activations(m, cols, seed=m)
+        got = qm.matmul(torch.from_numpy(x).cuda()).cpu().numpy()
+        assert_close(got, O.matmul_bt(x, w), f"dense m={m}", x.astype(np.float64) @ w.astype(np.float64).T)
+    assert qm.try_matmul_swiglu(torch.zeros((1, cols), device="cuda")) is None       # the reference's None
+    with pytest.raises(F.FerricError) as e:
+        qm.prepare(torch.zeros((1, cols), device="cuda"))
+    assert e.value.status == 6
+    qm.close()
+    # dequantise a packed format on the host, load it dense: same product as the packed matrix within the bar
+    raw = synth.matrix(12, 64, 512, seed=5)
+    dense = F.QMatrix.from_dense(ctx, O.deq_raw(raw, 64 * 512, 12).reshape(64, 512))
+    packed = F.QMatrix.from_bytes(ctx, raw, 12, 64, 512)
+    x = torch.from_numpy(synth.activations(2, 512, seed=6)).cuda()
+    assert_close(dense.matmul(x).cpu().numpy(), packed.matmul(x).cpu().numpy(), "dense vs packed")
+    dense.close()
+    packed.close()
+
+
 # ------------------------------------------------------------------------------ shards
 @pytest.mark.parametrize("ty", [12, 13, 14, 8])
 def test_row_and_k_shards_compose(F, ctx, ty):
