@@ -52,6 +52,7 @@ def parse_args():
     ap.add_argument("--no-chain", action="store_true",
                     help="launch the norms and activation preparation as kernels of their own (8 launches per layer) instead of "
                          "inside the products' launches (4 per layer)")
+    ap.add_argument("--chain", action="store_true", help="force the chained form wherever it applies (also across ranks)")
     ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the sharded-against-unsharded parity stage")
     ap.add_argument("--prefill", type=int, default=0, metavar="M",
                     help="time only the tensor-core prefill product (Q4_K x bf16, M activation rows) and print its line")
@@ -243,7 +244,7 @@ def run_ours(args):
         grp.connect_with_torch_distributed()
         return None, grp, kind
 
-    chain = None if not args.no_chain else False
+    chain = False if args.no_chain else (True if args.chain else None)
     parity = None
     if world > 1 and not args.no_parity:
         parity = tp_parity_check(torch, dist, ctx, world, rank, dev, exchange_for, chain)

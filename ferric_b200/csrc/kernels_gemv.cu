@@ -587,7 +587,7 @@ template <int EPI>
 __device__ __forceinline__ void chain_job(const ChainJob& j, int blk, int m, PrepSmem& sm)
 {
     const int lane = threadIdx.x & 31, prow = lane >> 4, q = lane & 15;
-    __threadfence();                     // the other tiles' stores came before their tickets
+    if (!(EPI == kEpiPush && j.kind == 3)) __threadfence();   // the other tiles' stores came before their tickets
     unsigned want = 0;
     const uint2* recv = nullptr;
     int wait_limit = 0;
@@ -610,8 +610,7 @@ __device__ __forceinline__ void chain_job(const ChainJob& j, int blk, int m, Pre
                 // as many of the lane's 16 values per polling round as the registers hold for the group's size
                 const size_t off = batch * d + (size_t)blk * 256 + 16 * q;
                 if (j.pushed.world <= 2) {
-#pragma unroll 1
-                    for (int i = 0; i < 4; i += 2) pushed_sum<2, 2>(j.pushed, recv, off + 4 * i, want, wait_limit, f + i);
+                    pushed_sum<4, 2>(j.pushed, recv, off, want, wait_limit, f);
                 } else {
 #pragma unroll 1
                     for (int i = 0; i < 4; i++) pushed_sum<1, kMaxRanks>(j.pushed, recv, off + 4 * i, want, wait_limit, f + i);
@@ -777,7 +776,10 @@ __device__ __forceinline__ void reduce_and_store(float (&acc)[NT][4], float (*re
         // this warp stored one 16-row tile of the result for every activation row; the warp that completes a 256-wide
         // block runs the block's job
         if (chain.job.kind != 0 && (out_tile >> 4) < chain.job.blocks) {
-            __threadfence();
+            // Pushed results need no fence: the job polls every pair's stamp, which is what tells it a value has landed
+            // (a fence here would wait for the peers' acknowledgements over NVLink, microseconds per warp); the
+            // ticket then only picks the warp that runs the job.
+            if (!(EPI == kEpiPush && chain.job.kind == 3)) __threadfence();
             __syncwarp();
             unsigned seen = 0;
             if (lane == 0) seen = atomicAdd(chain.job.tickets + (out_tile >> 4), 1u);
