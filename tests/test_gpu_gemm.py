@@ -111,6 +111,50 @@ def test_prefill_config(F, ctx, m):
     check(F, ctx, 4096, 5120, m, seed=m, oracle_rows=32)
 
 
+def bare_bar_stats(got, ref):
+    """How far the plain bar |got - ref| <= 1e-4 + 1e-3 |ref| (no allowance for either side's rounding) is from holding:
+    (elements over it, elements compared, worst error / bar)."""
+    ratio = np.abs(got - ref) / (ATOL + RTOL * np.abs(ref))
+    return int((ratio > 1.0).sum()), int(ratio.size), float(ratio.max())
+
+
+@pytest.mark.parametrize("m", [128, 512, 2048])
+def test_prefill_config_full_size(F, ctx, m):
+    """configs[3] at its full size: W 17408 x 5120 Q4_K, bf16 activations [m, 5120].  The GPU computes every row; the
+    float64 product and the oracle's sequential f32 product are formed on sampled row spans (rows are independent).  The
+    number of sampled elements over the plain bar, and by how much, is printed."""
+    rows, cols = 17408, 5120
+    raw = synth.matrix_on_device(12, rows, cols, seed=3, device="cuda")
+    qm = F.QMatrix.from_device_bytes(ctx, raw, 12, rows, cols)
+    rb = cols // 256 * 144
+    spans = [(0, 48), (8696, 8744), (17360, 17408)]
+    host = {sp: raw[sp[0] * rb:sp[1] * rb].cpu().numpy() for sp in spans}
+    del raw
+    x = torch.from_numpy(synth.activations(m, cols, seed=3)).to(torch.bfloat16)
+    xbits = x.view(torch.int16).numpy().view(np.uint16)
+    y = qm.matmul_bf16(x.cuda())
+    assert qm.gemm_status() == 0
+    got_all = y.cpu().numpy().astype(np.float64)
+    assert got_all.shape == (m, rows) and np.isfinite(got_all).all()
+    over = total = 0
+    worst = 0.0
+    mo = min(m, 32)                                    # the oracle is a scalar loop: a slice of the batch
+    for (lo, hi), rbytes in host.items():
+        got = got_all[:, lo:hi]
+        exact, mag = exact_bf16_product(rbytes, hi - lo, cols, xbits)
+        e = np.abs(got - exact)
+        tol = ATOL + RTOL * np.abs(exact) + U_ACC * mag
+        assert (e <= tol).all(), f"rows {lo}:{hi} vs exact: worst ratio {(e / tol).max():.3f}"
+        ref = O.matmul_q(rbytes, 12, hi - lo, cols, xbits[:mo], threads=8, mode=O.MODE_BF16).astype(np.float64)
+        e = np.abs(got[:mo] - ref)
+        tol = ATOL + RTOL * np.abs(ref) + U_ACC * mag[:mo] + np.abs(ref - exact[:mo])
+        assert (e <= tol).all(), f"rows {lo}:{hi} vs oracle: worst ratio {(e / tol).max():.3f}"
+        o, t, w = bare_bar_stats(got[:mo], ref)
+        over, total, worst = over + o, total + t, max(worst, w)
+    print(f"BARE-BAR config3 m={m}: {over} of {total} sampled elements over 1e-4 + 1e-3|ref|, worst ratio {worst:.2f}")
+    qm.close()
+
+
 def test_prefill_down_q6k(F, ctx):
     """The Q6_K down projection of the same layer (K = 17408), a 1024-row slice, batch 512."""
     check(F, ctx, 1024, 17408, 512, seed=5, oracle_rows=16, ty=14)

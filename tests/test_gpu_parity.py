@@ -64,6 +64,13 @@ def assert_close(got, ref, what="", exact=None):
     return float((err / tol).max())
 
 
+def bare_bar(got, ref, what):
+    """Print how far the plain bar |got - ref| <= 1e-4 + 1e-3 |ref| -- with no allowance for the reference product's own
+    f32 rounding -- is from holding: elements over it and the worst error / bar ratio."""
+    ratio = np.abs(np.asarray(got, np.float64) - np.asarray(ref, np.float64)) / (ATOL + RTOL * np.abs(np.asarray(ref, np.float64)))
+    print(f"BARE-BAR {what}: {int((ratio > 1).sum())} of {ratio.size} elements over 1e-4 + 1e-3|ref|, worst ratio {ratio.max():.2f}")
+
+
 def exact_product(raw, ty, rows, cols, x):
     """x . W^T with the oracle-dequantised weights (exact f32 values) accumulated in float64."""
     vals, bb = synth.BLOCK[ty]
@@ -171,6 +178,7 @@ def test_config0_q4k_4096(F, ctx):
     got = gpu_matmul(F, ctx, raw, 12, 4096, 4096, x)
     exact = exact_product(raw, 12, 4096, 4096, x)
     assert_close(got, ref, "config 0", exact)
+    bare_bar(got, ref, "config0 q4k 4096x4096")
     # the reference's other accumulation orders (fused per-block rows, GPU kernel order) agree too
     assert_close(got, O.matmul_q(raw, 12, 4096, 4096, x, threads=NCPU, mode=O.MODE_FUSED), "config 0 fused order", exact)
     assert_close(got, O.matmul_q(raw, 12, 4096, 4096, x, threads=NCPU, mode=O.MODE_SHADER), "config 0 kernel order", exact)
@@ -185,6 +193,8 @@ def test_config1_layer_matrices(F, ctx, name, ty, rows, cols):
     got = gpu_matmul(F, ctx, raw, ty, rows, cols, x)
     exact = exact_product(raw, ty, rows, cols, x)
     assert_close(got, ref, f"config 1 {name}", exact)
+    bare_bar(got, ref, f"config1 {name} {rows}x{cols}")
+    bare_bar(ref, exact, f"config1 {name}: the reference product itself against the float64 product")
     print(f"config 1 {name}: max|gpu-exact| {np.abs(got - exact).max():.2e}  max|cpu_ref-exact| {np.abs(ref - exact).max():.2e}")
 
 
@@ -207,6 +217,7 @@ def test_config2_output_head_rows_sampled(F, ctx):
         for (lo, hi), rb in host.items():
             ref = O.matmul_q(rb, 14, hi - lo, cols, x, threads=NCPU)
             assert_close(y[:, lo:hi], ref, f"config 2 m={m} rows {lo}:{hi}", exact_product(rb, 14, hi - lo, cols, x))
+            bare_bar(y[:, lo:hi], ref, f"config2 head m={m} rows {lo}:{hi}")
     qm.close()
 
 
