@@ -349,7 +349,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
     const int prow = lane >> 4, q = lane & 15;
     // The pushed form may run one tile on a cluster of CTAs: polling every rank's pairs is a lot of L2 traffic for
     // one SM, so the super-blocks are dealt round the cluster and only the sums of squares cross it.
-    const unsigned crank = PEERS == 2 ? cl_rank() : 0u, csize = PEERS == 2 ? cl_size() : 1u;
+    const unsigned crank = PEERS != 1 ? cl_rank() : 0u, csize = PEERS != 1 ? cl_size() : 1u;
     const size_t blk_first = (size_t)crank * nwarps + warp, blk_step = (size_t)csize * nwarps;
     const size_t tile = blockIdx.x / csize, batch = tile * kRowsPerTile + (size_t)prow;
     const bool valid = batch < m;
@@ -388,7 +388,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
     if (q == 0) part[prow][warp] = ms;
     __syncthreads();
     float tot = 0.0f;
-    if (PEERS == 2 && csize > 1) {
+    if (PEERS != 1 && csize > 1) {
         // every CTA adds all the cluster's per-warp sums in super-block order: the same order in every CTA, and the
         // order of a single CTA with one warp per super-block
         cl_sync();
@@ -431,7 +431,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
         }
         prep_block<TY>(v, sm[warp], tile, nblk, blk, frag);
     }
-    if (PEERS == 2 && csize > 1) cl_sync();   // no CTA leaves while another may still read its sums
+    if (PEERS != 1 && csize > 1) cl_sync();   // no CTA leaves while another may still read its sums
     if (PEERS == 2) {
         // the last CTA to get here closes the exchange: the next one of this kind carries the next number
         __syncthreads();
@@ -488,6 +488,7 @@ int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
     const int mode = pushed.world > 2 ? 3 : pushed.world > 0 ? 2 : peers.world > 0 ? 1 : 0;
     const int max_warps = mode == 3 ? kNormPrepWideWarps : mode == 2 ? kNormPrepPushWarps : kNormPrepMaxWarps;
     unsigned cluster = 1;
+    if (mode == 0 && w.nblk >= 8) cluster = 4;   // one CTA alone is latency-bound on a 5120-wide row (8 us); four share the blocks
     if (mode >= 2) {
         int c = tune.push_cluster > 0 ? tune.push_cluster : (pushed.world > 2 ? 4 : w.nblk > (size_t)kNormPrepPushWarps ? 2 : 1);
         while (c > 1 && ((c & (c - 1)) || c > 8 || (size_t)c > w.nblk)) c--;   // a power of two up to 8, at most one CTA per super-block

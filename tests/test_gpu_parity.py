@@ -367,9 +367,10 @@ def test_add_rmsnorm_matches_reference_kernel(F, ctx, rows, d):
 
 
 @pytest.mark.parametrize("ty", [12, 13, 14])
-@pytest.mark.parametrize("m", [1, 2, 5])
-def test_fused_add_rmsnorm_prepare(F, ctx, ty, m):
-    rows, d = 96, 1536
+@pytest.mark.parametrize("m,d", [(1, 1536), (2, 1536), (5, 1536), (1, 5120), (8, 5120), (3, 2304)])
+def test_fused_add_rmsnorm_prepare(F, ctx, ty, m, d):
+    """(from 8 super-blocks per row on, the kernel spreads a row over a cluster of four CTAs)"""
+    rows = 96
     raw = synth.matrix(ty, rows, d, seed=21)
     rng = np.random.default_rng(m)
     a = rng.standard_normal((m, d)).astype(np.float32) * np.float32(2)
