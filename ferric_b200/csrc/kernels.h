@@ -117,7 +117,7 @@ struct Chain {
     ChainJob job;
 };
 constexpr size_t kChainMaxBlocks = 1024;   // super-blocks per row a chained product may have on either side
-constexpr size_t kChainMaxRows = 8;        // activation rows of a chained product (one GEMV pass)
+constexpr size_t kChainMaxRows = 4;        // activation rows of a chained product (one GEMV pass of two tiles)
 
 // Workspace of the unit-balanced GEMV: warps whose run of units starts or ends inside a row tile leave their partial
 // sums here, and the last one to arrive at a tile (a ticket per tile) adds them in warp order and stores the result.

@@ -445,10 +445,13 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
     }
 }
 
+// Activation tiles (of two rows) a launch pass covers.  Two at most: a warp that carries four tiles needs over 200
+// registers, which leaves one CTA per SM, and measured slower than two passes of two tiles that re-read the weights
+// (gate|up at 8 rows: 56.8 us against 48.7 us; the 64-layer step 11.0 ms against 8.6 ms).
 static int tiles_per_pass(size_t m)
 {
     size_t ntiles = (m + kRowsPerTile - 1) / kRowsPerTile;
-    return ntiles >= 3 ? 4 : ntiles == 2 ? 2 : 1;
+    return ntiles >= 2 ? 2 : 1;
 }
 static size_t padded_tiles(size_t m)
 {
@@ -1509,8 +1512,7 @@ int32_t launch_gemv(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const 
     if (chain) { FERRIC_GEMV_CASE2(NT_, true, *chain); } \
     else { FERRIC_GEMV_CASE2(NT_, false, none); }
     if (nt == 1) { FERRIC_GEMV_CASE(1) }
-    else if (nt == 2) { FERRIC_GEMV_CASE(2) }
-    else { FERRIC_GEMV_CASE(4) }
+    else { FERRIC_GEMV_CASE(2) }
 #undef FERRIC_GEMV_CASE
 #undef FERRIC_GEMV_CASE2
     FERRIC_CUDA_TRY(cudaGetLastError());

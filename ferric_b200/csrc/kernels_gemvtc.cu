@@ -689,14 +689,13 @@ int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMa
 
 bool gemv_tc_eligible(uint32_t ty, const DeviceWeights& w, size_t m)
 {
-    // Measured cross-over with the mma.sync GEMV (which runs in passes of 8 activation rows): Q4_K from 9 rows, Q6_K --
-    // two operand planes, so twice the MMAs -- from 24.  FERRIC_CUDA_GEMV_TC_MIN_M overrides both; 0 disables the path.
-    static const int forced = [] {
-        const char* e = getenv("FERRIC_CUDA_GEMV_TC_MIN_M");
-        return e ? atoi(e) : -1;
-    }();
+    // Measured cross-over with the mma.sync GEMV (which runs in passes of 4 activation rows; 64-layer step at 12 / 16 / 24
+    // rows: 12.4 / 15.3 / 21.0 ms in passes against 14.5 / 15.5 / 19.9 ms here): Q4_K from 17 rows, Q6_K -- two operand
+    // planes, so twice the MMAs -- from 24.  FERRIC_CUDA_GEMV_TC_MIN_M overrides both; 0 disables the path.
+    const char* env = getenv("FERRIC_CUDA_GEMV_TC_MIN_M");   // read per call: tests move the threshold
+    const int forced = env ? atoi(env) : -1;
     if (ty != kGgmlQ4K && ty != kGgmlQ6K) return false;
-    const int min_m = forced >= 0 ? forced : (ty == kGgmlQ4K ? 9 : 24);
+    const int min_m = forced >= 0 ? forced : (ty == kGgmlQ4K ? 17 : 24);
     return min_m > 0 && m >= (size_t)min_m && m <= 4096 && w.nblk > 0 && w.rows > 0 && w.rows <= (size_t)INT32_MAX / 2;
 }
 

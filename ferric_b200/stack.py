@@ -89,13 +89,13 @@ class DecodeStack:
         `push` the o / down products store their partial sums straight into every rank's memory, otherwise each
         rank signals its buffer and the consumers read the peers' buffers.
         `chain`: one launch per matrix, the norms, residual adds and activation preparation riding in the products' own
-        launches.  It applies up to 8 tokens with one rank or the pushed exchange; by default it is used on one rank up
+        launches.  It applies up to 4 tokens (one pass of the GEMV) with one rank or the pushed exchange; by default it is used on one rank up
         to 2 tokens (one activation tile), where it measured faster (4.06 against 4.29 ms per step).  With more tiles
         the one warp that prepares a block becomes the tail of every launch (13.2 against 11.1 ms at 8 tokens), and
         across ranks the exchange's own consumer kernel, spread over a cluster, polls faster than one warp per block
         (3.77 against 3.46 ms per step on 2 GPUs)."""
         self.ctx, self.plan, self.n_layers, self.batch, self.eps = ctx, plan, n_layers, batch, eps
-        can_chain = batch <= 8 and (plan.world == 1 or (group is not None and push))
+        can_chain = batch <= 4 and (plan.world == 1 or (group is not None and push))
         self.chain = (can_chain and batch <= 2 and plan.world == 1) if chain is None else (chain and can_chain)
         self.all_reduce = all_reduce if (plan.world > 1 and group is None) else None
         self.group = group if plan.world > 1 else None

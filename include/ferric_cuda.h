@@ -154,7 +154,7 @@ size_t ferric_cuda_qmatrix_scratch_bytes(const ferric_qmatrix *qm, size_t m);
  * y[m, rows] = x[m, cols] . W^T, f32 in, f32 out, both DEVICE buffers, contiguous row-major,
  * 16-byte aligned.  m >= 0.  `x_cols` is the activation's inner dimension; a mismatch with the
  * matrix is the reference's "inner dim mismatch" panic -> FERRIC_ERR_SHAPE.
- * Up to 8 activation rows (and Q8_0 at any m) run the GEMV kernels; Q4_K from 9 rows and Q6_K from
+ * Few activation rows (and Q8_0 at any m) run the GEMV kernels, in passes of 4 rows; Q4_K from 17 rows and Q6_K from
  * 24 run an exact-integer tensor-core kernel (FERRIC_CUDA_GEMV_TC_MIN_M in the environment moves
  * that threshold, 0 switches the kernel off); ferric_cuda_gemm_status reports its bounded waits. */
 int32_t ferric_cuda_matmul_q(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t m,
@@ -208,7 +208,7 @@ int32_t ferric_cuda_add_rmsnorm_prepare(ferric_cuda_ctx *ctx, const ferric_qmatr
  *     1 / sqrt(mean(h^2) + eps) to its result instead -- e.g. o -> gate|up, down -> the next layer's q|k|v.
  * The context's scratch holds two prepared-activation slots; a link reads slot `in_slot` and prepares into the other.
  * ferric_cuda_add_rmsnorm_prepare / ferric_cuda_prepare_x write slot 0 (already normalised: in_rms = 0 for their
- * consumer), which is how a chain starts.  Up to 8 activation rows; Q4_K / Q5_K / Q6_K. */
+ * consumer), which is how a chain starts.  Up to 4 activation rows (one pass of the GEMV); Q4_K / Q5_K / Q6_K. */
 #define FERRIC_CHAIN_NONE 0
 #define FERRIC_CHAIN_PREPARE 1
 #define FERRIC_CHAIN_RESIDUAL 2

@@ -38,7 +38,7 @@ def cuda(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-@pytest.mark.parametrize("m", [1, 2, 5, 8])
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
 @pytest.mark.parametrize("ty,ty_next", [(12, 12), (12, 14), (14, 12), (13, 14)])
 def test_prepare_link_is_the_unchained_pair_bit_for_bit(F, ctx, ty, ty_next, m):
     rows, cols, cols_next, rows_next = 800, 512, 768, 96       # the next product reads the first 768 of 800 columns
@@ -59,7 +59,7 @@ def test_prepare_link_is_the_unchained_pair_bit_for_bit(F, ctx, ty, ty_next, m):
     nx.close()
 
 
-@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("m", [1, 3, 4])
 def test_swiglu_prepare_link(F, ctx, m):
     n_ff, cols = 512, 768
     gu = F.QMatrix.from_bytes(ctx, synth.matrix(12, 2 * n_ff, cols, seed=5), 12, 2 * n_ff, cols)
@@ -77,7 +77,7 @@ def test_swiglu_prepare_link(F, ctx, m):
     dn.close()
 
 
-@pytest.mark.parametrize("m", [1, 2, 5, 8])
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
 @pytest.mark.parametrize("ty,ty_next,weighted", [(12, 12, True), (14, 12, False), (12, 14, True)])
 def test_residual_link_against_add_rmsnorm_and_the_oracle(F, ctx, ty, ty_next, weighted, m):
     hid, k, rows_next = 1280, 512, 208
@@ -113,7 +113,7 @@ def test_residual_link_against_add_rmsnorm_and_the_oracle(F, ctx, ty, ty_next, w
     nx.close()
 
 
-@pytest.mark.parametrize("batch", [1, 2, 6, 8])
+@pytest.mark.parametrize("batch", [1, 2, 3, 4])
 def test_chained_stack_equals_the_stack_kernel_by_kernel(F, ctx, batch):
     from ferric_b200.stack import DecodeStack, TPPlan
     plan = TPPlan.make(1, 0, hidden=768, n_ff=1024, q_out=512, kv_out=256)
@@ -155,7 +155,7 @@ def test_chained_stack_equals_the_stack_kernel_by_kernel(F, ctx, batch):
     st.close()
 
 
-@pytest.mark.parametrize("m", [1, 2, 7])
+@pytest.mark.parametrize("m", [1, 2, 4])
 def test_pushed_residual_link_with_one_rank(F, ctx, m):
     """A group of one rank pushes to itself: product, exchange, residual add and preparation in ONE launch must
     equal the local residual link bit for bit -- both kinds, one of them twice running (the receive regions'
@@ -193,14 +193,14 @@ def test_chain_argument_errors(F):
     nx = F.QMatrix.from_bytes(ctx, synth.matrix(12, 32, 512, seed=2), 12, 32, 512)
     wide = F.QMatrix.from_bytes(ctx, synth.matrix(12, 32, 1024, seed=3), 12, 32, 1024)
     q8 = F.QMatrix.from_bytes(ctx, synth.matrix(8, 32, 256, seed=4), 8, 32, 256)
-    y = torch.empty((9, 512), device="cuda")
+    y = torch.empty((5, 512), device="cuda")
     with pytest.raises(F.FerricError) as e:                      # no slots reserved yet
         w.chain_matmul(1, y)
     assert e.value.status == 1
-    ctx.chain_reserve(max(w.scratch_bytes(8), nx.scratch_bytes(8)))
+    ctx.chain_reserve(max(w.scratch_bytes(4), nx.scratch_bytes(4)))
     w.prepare(torch.zeros((1, 256), device="cuda"))
     with pytest.raises(F.FerricError) as e:                      # more rows than one GEMV pass
-        w.chain_matmul(9, y)
+        w.chain_matmul(5, y)
     assert e.value.status == 3
     with pytest.raises(F.FerricError) as e:                      # the next product would read more columns than there are
         w.chain_matmul(1, y, next=1, next_qm=wide)

@@ -37,6 +37,12 @@ def ctx(F):
     c.close()
 
 
+@pytest.fixture(autouse=True)
+def tensor_core_path_from_nine_rows(monkeypatch):
+    """By default Q4_K takes this kernel from 17 activation rows; the tests here also cover its narrowest tile."""
+    monkeypatch.setenv("FERRIC_CUDA_GEMV_TC_MIN_M", "9")
+
+
 def run(F, ctx, raw, ty, rows, cols, x, swiglu=False):
     qm = F.QMatrix.from_bytes(ctx, raw, ty, rows, cols)
     xd = torch.from_numpy(np.ascontiguousarray(x)).cuda()
@@ -122,6 +128,6 @@ def test_same_result_as_the_gemv_passes(F, ctx, monkeypatch):
     got = run(F, ctx, raw, 12, rows, cols, x)
     qm = F.QMatrix.from_bytes(ctx, raw, 12, rows, cols)
     xd = torch.from_numpy(x).cuda()
-    halves = torch.cat([qm.matmul(xd[:8]), qm.matmul(xd[8:])]).cpu().numpy()   # 8 rows at a time: the GEMV
+    halves = torch.cat([qm.matmul(xd[:8]), qm.matmul(xd[8:])]).cpu().numpy()   # 8 rows at a time: below the threshold, the GEMV
     qm.close()
     assert np.abs(got - halves).max() <= 1e-5 * np.abs(halves).max()
