@@ -128,7 +128,10 @@ def run_reference(args):
         "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup, "ms_per_step": step_s * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD.format(b=batch), "batch": batch, "layers": args.layers, "parallelism": "cpu"},
+        # the same workload keys as the GPU arm's line (the host cores run the unsharded layer whatever --gpus says)
+        "config": {"workload": WORKLOAD.format(b=batch), "batch": batch, "layers": args.layers, "parallelism": f"tp{args.gpus}",
+                   "host": f"cpu, {cores} threads"},
+        "sampled_ms_per_step": per_layer * 1e3,
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
