@@ -51,6 +51,9 @@ SIGNATURES = {
     "ferric_cuda_ctx_caps": (_I32, [_P, C.POINTER(Caps)]),
     "ferric_cuda_ctx_reserve_scratch": (_I32, [_P, _SZ]),
     "ferric_cuda_ctx_launches": (C.c_uint64, [_P]),
+    "ferric_cuda_prof_enable": (_I32, [_P, _I32]),
+    "ferric_cuda_prof": (_I32, [_P, C.c_char_p]),
+    "ferric_cuda_prof_report": (_I32, [_P, _P, _SZ, C.POINTER(_SZ)]),
     "ferric_cuda_qmatrix_block_bytes": (_I32, [_U32, C.POINTER(_SZ), C.POINTER(_SZ)]),
     "ferric_cuda_qmatrix_from_bytes": (_I32, [_P, _P, _SZ, _U32, _SZ, _SZ, C.POINTER(_P)]),
     "ferric_cuda_qmatrix_from_bytes_view": (_I32, [_P, _P, _SZ, _U32, _SZ, _SZ, _SZ, _SZ, _SZ, _SZ, C.POINTER(_P)]),

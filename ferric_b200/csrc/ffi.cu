@@ -4,7 +4,12 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <time.h>
+
+#include <algorithm>
 #include <new>
+#include <string>
+#include <vector>
 
 #include "../../include/ferric_cuda.h"
 #include "common.cuh"
@@ -434,6 +439,73 @@ int32_t ferric_cuda_ctx_reserve_scratch(ferric_cuda_ctx* ctx, size_t bytes)
 }
 
 uint64_t ferric_cuda_ctx_launches(const ferric_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// prof / prof_report (crates/ferric-tensor/src/lib.rs:3017-3046): synchronise, then charge the time since the previous
+// mark to a named bucket.  It serialises the stream, so it shows where the time goes, not the fastest achievable.
+static double host_ms()
+{
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6;
+}
+
+int32_t ferric_cuda_prof_enable(ferric_cuda_ctx* ctx, int32_t on)
+{
+    if (!ctx) {
+        set_last_error("NULL context");
+        return kErrInvalidArg;
+    }
+    ctx->prof_on = on != 0;
+    ctx->prof_marked = false;
+    return kOk;
+}
+
+int32_t ferric_cuda_prof(ferric_cuda_ctx* ctx, const char* label)
+{
+    if (!ctx || !label) {
+        set_last_error("NULL context or label");
+        return kErrInvalidArg;
+    }
+    if (!ctx->prof_on) return kOk;
+    DeviceGuard guard(ctx->device);
+    FERRIC_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    const double now = host_ms();
+    if (ctx->prof_marked) ctx->prof[label] += now - ctx->prof_prev_ms;
+    ctx->prof_prev_ms = now;
+    ctx->prof_marked = true;
+    return kOk;
+}
+
+int32_t ferric_cuda_prof_report(ferric_cuda_ctx* ctx, char* buf, size_t cap, size_t* len)
+{
+    if (!ctx) {
+        set_last_error("NULL context");
+        return kErrInvalidArg;
+    }
+    std::vector<std::pair<std::string, double>> v(ctx->prof.begin(), ctx->prof.end());
+    std::sort(v.begin(), v.end(), [](const auto& a, const auto& b) { return a.second > b.second; });
+    double total = 0.0;
+    for (const auto& e : v) total += e.second;
+    char line[256];
+    std::string out;
+    snprintf(line, sizeof line, "profile (ms, %.3f total)\n", total);
+    out += line;
+    for (const auto& e : v) {
+        snprintf(line, sizeof line, "  %-24s %10.3f  %5.1f%%\n", e.first.c_str(), e.second, total > 0 ? 100.0 * e.second / total : 0.0);
+        out += line;
+    }
+    if (len) *len = out.size();
+    if (buf && cap > 0) {
+        const size_t n = std::min(cap - 1, out.size());
+        memcpy(buf, out.data(), n);
+        buf[n] = 0;
+        if (cap > out.size()) {   // the whole report was delivered: reset, as the reference does after printing
+            ctx->prof.clear();
+            ctx->prof_marked = false;
+        }
+    }
+    return kOk;
+}
 
 int32_t ferric_cuda_qmatrix_from_bytes(ferric_cuda_ctx* ctx, const uint8_t* bytes, size_t len, uint32_t ty,
                                        size_t rows, size_t cols, ferric_qmatrix** out)

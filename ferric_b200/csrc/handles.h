@@ -4,6 +4,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <map>
+#include <string>
+
 #include "kernels.h"
 
 struct ferric_cuda_ctx {
@@ -18,6 +21,10 @@ struct ferric_cuda_ctx {
     // chained products (ferric_cuda_chain_*): the scratch holds two prepared-activation slots, slot 1 at this offset
     // (0 until ferric_cuda_chain_reserve); sums of squares, block tickets and the job counter live beside the split workspace
     size_t chain_slot_bytes = 0;
+    // profiling buckets (ferric_cuda_prof / _prof_report): label -> milliseconds, and the previous mark
+    bool prof_on = false, prof_marked = false;
+    double prof_prev_ms = 0.0;
+    std::map<std::string, double> prof;
     float* chain_ssq = nullptr;
     unsigned* chain_tickets = nullptr;
     unsigned* chain_done = nullptr;

@@ -92,6 +92,22 @@ class Context:
     def launches(self) -> int:
         return int(self._lib.ferric_cuda_ctx_launches(self._h))
 
+    def prof_enable(self, on: bool = True) -> None:
+        """Switch the per-op timing buckets on or off (the reference's FERRIC_PROFILE)."""
+        _check(self._lib.ferric_cuda_prof_enable(self._h, int(on)), "prof_enable")
+
+    def prof(self, label: str) -> None:
+        """``prof(ctx, label)`` (crates/ferric-tensor/src/lib.rs:3017-3031): sync, charge the time since the last mark to `label`."""
+        _check(self._lib.ferric_cuda_prof(self._h, label.encode()), "prof")
+
+    def prof_report(self) -> str:
+        """``prof_report()`` (:3033-3046): the buckets, largest first, as text; resets them."""
+        n = C.c_size_t()
+        _check(self._lib.ferric_cuda_prof_report(self._h, None, 0, C.byref(n)), "prof_report")
+        buf = C.create_string_buffer(n.value + 1)
+        _check(self._lib.ferric_cuda_prof_report(self._h, buf, n.value + 1, C.byref(n)), "prof_report")
+        return buf.value.decode()
+
     def reserve_scratch(self, nbytes: int) -> None:
         _check(self._lib.ferric_cuda_ctx_reserve_scratch(self._h, nbytes), "reserve_scratch")
 

@@ -100,6 +100,15 @@ int32_t ferric_cuda_ctx_reserve_scratch(ferric_cuda_ctx *ctx, size_t bytes);
 /* Launch counters since creation: kernels this library launched on the context. */
 uint64_t ferric_cuda_ctx_launches(const ferric_cuda_ctx *ctx);
 
+/* prof(ctx, label) / prof_report()   crates/ferric-tensor/src/lib.rs:3017-3046: per-op timing buckets.  When enabled
+ * (the reference's FERRIC_PROFILE), ferric_cuda_prof synchronises the context's stream and charges the time since the
+ * previous mark to `label` (the first mark only starts the clock) -- it serialises the stream, so it measures where the
+ * work is, not the fastest achievable.  ferric_cuda_prof_report writes the buckets, largest first, as text (at most
+ * cap - 1 bytes, full length in *len) and, when the whole text fitted, resets them. */
+int32_t ferric_cuda_prof_enable(ferric_cuda_ctx *ctx, int32_t on);
+int32_t ferric_cuda_prof(ferric_cuda_ctx *ctx, const char *label);
+int32_t ferric_cuda_prof_report(ferric_cuda_ctx *ctx, char *buf, size_t cap, size_t *len);
+
 /* ---- ferric-tensor: QMatrix ------------------------------------------------------------- */
 
 /* QMatrix::block_bytes(ty) -> Option<(values, bytes)>   crates/ferric-tensor/src/dtype.rs:873-889

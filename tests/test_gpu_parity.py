@@ -428,6 +428,28 @@ def test_decode_stack_step_matches_layerwise_oracle(F, ctx):
     st.close()
 
 
+def test_profile_buckets(F):
+    """prof / prof_report (crates/ferric-tensor/src/lib.rs:3017-3046): time between marks lands in named buckets."""
+    c = F.Context(0)
+    qm = F.QMatrix.from_bytes(c, synth.matrix(12, 4096, 4096, seed=0), 12, 4096, 4096)
+    x = torch.randn((1, 4096), device="cuda")
+    c.prof("ignored")                                           # off: a no-op
+    assert c.prof_report().strip().endswith("0.000 total)")
+    c.prof_enable(True)
+    c.prof("start")                                             # the first mark only starts the clock
+    for _ in range(50):
+        qm.matmul(x)
+    c.prof("matmul_q")
+    c.add_rmsnorm(x, None, None, 1e-6)
+    c.prof("rmsnorm")
+    rep = c.prof_report()
+    lines = [l.split() for l in rep.splitlines()[1:]]
+    assert [l[0] for l in lines] == ["matmul_q", "rmsnorm"] and float(lines[0][1]) > float(lines[1][1]) > 0
+    assert "start" not in rep and c.prof_report().strip().endswith("0.000 total)")      # reset after a full report
+    qm.close()
+    c.close()
+
+
 def test_dense_fallback_matrix(F, ctx):
     """QMatrix::from_dense (crates/ferric-tensor/src/dtype.rs:912-926): a format without a packed kernel reaches the
     matmul as an already dequantised f32 weight; the product is the reference's dense x . W^T."""
