@@ -235,6 +235,11 @@ def run_ours(args):
         up to batch 4 (up to batch 8 from 4 GPUs on: measured 1306 against 1027 tokens/s at 8 GPUs, but 904 against 957
         at 2), NCCL above that."""
         if world == 1:
+            if args.shard_of > 1 and args.chain and batch <= 4:
+                # diagnostic: rank 0's shard with the chained pushed exchange, the "group" being this rank alone
+                grp = TPGroup(ctx, 0, 1, batch, HIDDEN)
+                grp.connect([grp.export()])
+                return None, grp, "push"
             return ((lambda t: None) if args.shard_of > 1 else None), None, "none"
         kind = args.allreduce
         if kind == "auto":

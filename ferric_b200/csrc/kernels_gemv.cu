@@ -306,7 +306,7 @@ __device__ __forceinline__ float cl_load_f32(const float* own_smem, unsigned ran
 // polls all 16 of a lane's values in one round, above that CTAs of up to 8 warps (the tile is spread over a cluster)
 // poll 8 values per round.
 template <int TY, int PEERS, int WMAX>
-__global__ void __launch_bounds__(PEERS == 2 ? (WMAX <= 2 ? 32 * kNormPrepPushWarps : 32 * kNormPrepWideWarps) : 32 * kNormPrepMaxWarps)
+__global__ void __launch_bounds__(PEERS == 2 ? (WMAX <= 2 ? 32 * kNormPrepPushWarps : 32 * kNormPrepWideWarps) : PEERS == 0 ? 32 * kNormPrepPushWarps : 32 * kNormPrepMaxWarps)
 norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wgt, float eps,
                  size_t m, size_t d, size_t nblk, float* __restrict__ sum, float* __restrict__ norm,
                  uint2* __restrict__ frag, PeerSum peers, PushSrc pushed)
@@ -353,7 +353,10 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
     const size_t blk_first = (size_t)crank * nwarps + warp, blk_step = (size_t)csize * nwarps;
     const size_t tile = blockIdx.x / csize, batch = tile * kRowsPerTile + (size_t)prow;
     const bool valid = batch < m;
-    // pass 1: s = a + b, sum of squares per row
+    // pass 1: s = a + b, sum of squares per row.  A warp's first block stays in registers for pass 2 (with enough warps
+    // that is its only block), which saves the second trip to memory.
+    constexpr bool kKeep = PEERS != 1;
+    float4 keep[4];
     float ms = 0.0f;
     for (size_t blk = blk_first; blk < nblk; blk += blk_step) {
         if (valid) {
@@ -379,6 +382,7 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
                     f.x += gp[i].x; f.y += gp[i].y; f.z += gp[i].z; f.w += gp[i].w;
                 }
                 if (sum) reinterpret_cast<float4*>(sum + off)[i] = f;
+                if (kKeep && blk == blk_first) keep[i] = f;
                 ms = fmaf(f.x, f.x, ms); ms = fmaf(f.y, f.y, ms); ms = fmaf(f.z, f.z, ms); ms = fmaf(f.w, f.w, ms);
             }
         }
@@ -406,7 +410,9 @@ norm_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, const
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 float4 f;
-                if (sum || PEERS == 2) {   // the pushed form always writes the sum (its launcher insists)
+                if (kKeep && blk == blk_first) {
+                    f = keep[i];
+                } else if (sum || PEERS == 2) {   // the pushed form always writes the sum (its launcher insists)
                     f = reinterpret_cast<const float4*>(sum + off)[i];
                 } else {
                     f = ld_act(reinterpret_cast<const float4*>(a + off) + i);
@@ -489,7 +495,7 @@ int32_t launch_norm_prep(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
     size_t ntiles = padded_tiles(m);
     if (ntiles == 0 || w.nblk == 0) return kOk;
     const int mode = pushed.world > 2 ? 3 : pushed.world > 0 ? 2 : peers.world > 0 ? 1 : 0;
-    const int max_warps = mode == 3 ? kNormPrepWideWarps : mode == 2 ? kNormPrepPushWarps : kNormPrepMaxWarps;
+    const int max_warps = mode == 3 ? kNormPrepWideWarps : (mode == 2 || mode == 0) ? kNormPrepPushWarps : kNormPrepMaxWarps;
     unsigned cluster = 1;
     if (mode == 0 && w.nblk >= 8) cluster = 4;   // one CTA alone is latency-bound on a 5120-wide row (8 us); four share the blocks
     if (mode >= 2) {
