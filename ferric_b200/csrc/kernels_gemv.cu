@@ -1577,11 +1577,13 @@ int32_t launch_id_wsum(cudaStream_t st, const float* part, const float* selw, si
 }
 
 // ------------------------------------------------------------------------------------------
-// Q8_0: one warp per output row, lanes stride 16-weight runs, warp-shuffle reduction.
-// Per 32-weight block the partial is scaled once by d, the order of the reference's CPU row
-// kernel (crates/ferric-tensor/src/cpu_simd.rs:57-72).
+// Q8_0: a warp owns kQ8Rows consecutive output rows; lanes stride 16-weight runs of K.  A lane loads its 16 activations
+// of a run once into registers and uses them for all the warp's rows (one activation row at a time when there are
+// several), so the activation traffic through L1 is 1/kQ8Rows of the weight traffic instead of four times it.  Each
+// 16-weight half of a 32-weight block is summed in f32 and scaled by the block's d (crates/ferric-tensor/src/cpu_simd.rs:
+// 57-72 scales per block); the lanes' partial sums meet in a warp-shuffle reduction.
 // ------------------------------------------------------------------------------------------
-template <int MB>
+constexpr int kQ8Rows = 8;
 __global__ void __launch_bounds__(256) gemv_q8_0_kernel(const int8_t* __restrict__ qs, const uint16_t* __restrict__ dpl,
                                                         const float* __restrict__ x, int m, size_t ldx,
                                                         float* __restrict__ y, size_t ldy, int rows, int cols)
@@ -1589,44 +1591,66 @@ __global__ void __launch_bounds__(256) gemv_q8_0_kernel(const int8_t* __restrict
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int row = blockIdx.x * 8 + warp;
-    if (row >= rows) return;
-    const int batch0 = blockIdx.y * MB, nchunks = cols / 16, nb = cols / 32;
-    float acc[MB];
+    const int row0 = (blockIdx.x * 8 + warp) * kQ8Rows;
+    if (row0 >= rows) return;
+    const int nchunks = cols / 16, nb = cols / 32;
+    for (int batch = blockIdx.y; batch < m; batch += gridDim.y) {
+        float acc[kQ8Rows];
 #pragma unroll
-    for (int i = 0; i < MB; i++) acc[i] = 0.0f;
-    const int8_t* wrow = qs + (size_t)row * cols;
-    for (int c = lane; c < nchunks; c += 32) {
-        const uint4 wv = ld_stream_u4(wrow + 16 * c);
-        const float d = __half2float(__ushort_as_half(dpl[(size_t)row * nb + (c >> 1)]));
-        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-        float wf[16];
+        for (int r = 0; r < kQ8Rows; r++) acc[r] = 0.0f;
+        const float* xrow = x + (size_t)batch * ldx;
+        // two runs per lane and trip, all their weight loads issued before the first use: bytes in flight are what this
+        // kernel lives on (a row is only 10 runs per lane at 5120 columns)
+        for (int c0 = lane; c0 < nchunks; c0 += 64) {
+            uint4 wv[2][kQ8Rows];
+            float dv[2][kQ8Rows];
 #pragma unroll
-        for (int k = 0; k < 4; k++)
+            for (int u = 0; u < 2; u++) {
+                const int c = c0 + 32 * u;
 #pragma unroll
-            for (int j = 0; j < 4; j++) wf[4 * k + j] = (float)(int8_t)((ww[k] >> (8 * j)) & 0xffu);
-#pragma unroll
-        for (int i = 0; i < MB; i++) {
-            if (batch0 + i >= m) break;
-            const float4* xp = reinterpret_cast<const float4*>(x + (size_t)(batch0 + i) * ldx + 16 * c);
-            float part = 0.0f;
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const float4 xv = ld_act(xp + k);
-                part = fmaf(xv.x, wf[4 * k], part);
-                part = fmaf(xv.y, wf[4 * k + 1], part);
-                part = fmaf(xv.z, wf[4 * k + 2], part);
-                part = fmaf(xv.w, wf[4 * k + 3], part);
+                for (int r = 0; r < kQ8Rows; r++) {
+                    const int row = row0 + r;
+                    wv[u][r] = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);   // int8 zeros after the sign flip below
+                    dv[u][r] = 0.0f;
+                    if (row < rows && c < nchunks) {
+                        wv[u][r] = ld_stream_u4(qs + (size_t)row * cols + 16 * c);
+                        dv[u][r] = __half2float(__ushort_as_half(dpl[(size_t)row * nb + (c >> 1)]));
+                    }
+                }
             }
-            acc[i] = fmaf(part, d, acc[i]);
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int c = c0 + 32 * u;
+                if (c >= nchunks) break;
+                float xv[16];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float4 f = ld_act(reinterpret_cast<const float4*>(xrow + 16 * c) + k);
+                    xv[4 * k] = f.x; xv[4 * k + 1] = f.y; xv[4 * k + 2] = f.z; xv[4 * k + 3] = f.w;
+                }
+#pragma unroll
+                for (int r = 0; r < kQ8Rows; r++) {
+                    const uint32_t ww[4] = {wv[u][r].x ^ 0x80808080u, wv[u][r].y ^ 0x80808080u, wv[u][r].z ^ 0x80808080u,
+                                            wv[u][r].w ^ 0x80808080u};
+                    float part = 0.0f;
+                    // int8 -> f32 without the conversion unit: the sign-flipped byte (0..255) dropped into the mantissa of
+                    // 2^23 by a byte permute, minus 2^23 + 128 -- exact
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            part = fmaf(xv[4 * k + j], __uint_as_float(__byte_perm(ww[k], 0x4B000000u, 0x7650 + j)) - 8388736.0f, part);
+                    acc[r] = fmaf(part, dv[u][r], acc[r]);
+                }
+            }
         }
-    }
 #pragma unroll
-    for (int i = 0; i < MB; i++) {
-        float v = acc[i];
+        for (int r = 0; r < kQ8Rows; r++) {
+            float v = acc[r];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && batch0 + i < m) y[(size_t)(batch0 + i) * ldy + row] = v;
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && row0 + r < rows) y[(size_t)batch * ldy + row0 + r] = v;
+        }
     }
 }
 
@@ -1634,8 +1658,10 @@ int32_t launch_gemv_q8_0(cudaStream_t st, const DeviceWeights& w, const float* x
                          size_t ldy, const GemvTuning& tune)
 {
     if (m == 0 || w.rows == 0) return kOk;
-    dim3 grid((unsigned)((w.rows + 7) / 8), (unsigned)((m + 3) / 4));
-    FERRIC_CUDA_TRY(launch_kernel(gemv_q8_0_kernel<4>, grid, dim3(256), 0, st, tune.pdl, w.q8_qs, w.q8_d, x, (int)m, ldx, y,
+    // one grid row of CTAs per activation row up to 8, beyond that each CTA walks several (the weights of its 64 rows
+    // then come from L1 / L2)
+    dim3 grid((unsigned)((w.rows + 8 * kQ8Rows - 1) / (8 * kQ8Rows)), (unsigned)(m < 8 ? m : 8));
+    FERRIC_CUDA_TRY(launch_kernel(gemv_q8_0_kernel, grid, dim3(256), 0, st, tune.pdl, w.q8_qs, w.q8_d, x, (int)m, ldx, y,
                                   ldy, (int)w.rows, (int)w.cols));
     return kOk;
 }
