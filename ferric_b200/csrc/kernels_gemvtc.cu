@@ -1,26 +1,28 @@
-// Batched decode product (M > 8; Q4_K and Q6_K) on the tcgen05 tensor cores with exact integer arithmetic.
+// Batched decode product (M > 8; Q4_K and Q6_K) on the tcgen05 tensor cores with integer-valued f16 operands.
 //
-// The mma.sync GEMV (kernels_gemv.cu) is bound by instruction issue beyond a few activation rows.  This
-// kernel keeps its number format -- activations as four balanced base-128 limbs of X = rint(x * 2^(27-e)),
-// one e per (activation row, super-block) -- and moves the multiply-accumulates to tcgen05.mma kind::f16 on
-// INTEGER-VALUED f16 operands, which makes the tensor core an exact integer engine:
-//   A[row][k] = sc(row, sub-block of k) * q(row, k)      0 .. 63 * 15 = 945        exact in f16
-//   B[4b+j][k] = limb j of activation row b               -64 .. 63                 exact in f16
-//   one super-block (K = 256) accumulates at most 256 * 945 * 64 < 2^24 in f32 -- every partial sum is an
-//   integer the accumulator represents exactly, so neither rounding nor the order of the adds matters.
-// After each super-block four drain warps read the accumulator back and apply what differs per row and
-// super-block in f32: y[b][row] += 2^(e-6) * (d * V - dmin * sum_sb m_sb * S_sb), V = the limbs recombined,
-// S_sb = the activation sums of the eight sub-blocks (from the preparation kernel).  The accumulator is
-// double-buffered in tensor memory, so the drain of one super-block overlaps the MMAs of the next.
+// The mma.sync GEMV (kernels_gemv.cu) is bound by instruction issue beyond a few activation rows.  This kernel
+// moves the multiply-accumulates to tcgen05.mma kind::f16 and keeps every operand an integer that f16 holds exactly:
+//   A[row][k]     = sc(row, sub-block of k) * q(row, k)     0 .. 63 * 15 = 945
+//   B[2b + j][k]  = limb j of activation row b: X = rint(x * 2^(22-e)) = 2048 hi + lo, |hi| <= 1024, |lo| <= 1024,
+//                   one e per (activation row, super-block)
+// so every product is exact and the f32 accumulator (one super-block, K = 256, per pass) rounds only where a running
+// sum passes 2^24, i.e. by 2^-24 of that sum: the precision of an f32 product of the exact weights with X.  X keeps
+// 21 bits below the super-block's largest activation.
+// The Q4_K min term rides the tensor core too: one more K = 16 step per super-block multiplies the rows' eight 6-bit
+// mins (twice) with the two pieces of each limb's sub-block sums (from the preparation kernel) into a second
+// accumulator.  After each super-block the drain warps read both accumulators back and apply what differs per row
+// and super-block in f32: y[b][row] += 2^(e-11) * (d * V - dmin * Mn), V and Mn recombined from their two limb
+// columns.  The accumulators are double-buffered in tensor memory, so the drain of one super-block overlaps the MMAs
+// of the next.
 // This replaces, for M > 8, the same reference operator as the GEMV: Tensor::matmul_q4_k
 // (crates/ferric-tensor/src/dtype.rs:1426-1473).
 //
-// CTA = 128 weight rows x N_TILE / 4 activation rows (N_TILE = 64, 128, 256 operand rows) x a range of
-// super-blocks (K split across blockIdx.z for matrices with few row tiles; partials are summed in a fixed order
-// by the finish kernel, which also applies the SwiGLU epilogue).
+// CTA = 128 weight rows x N_TILE / 2 activation rows (N_TILE = 64 or 128 operand rows) x a range of super-blocks
+// (K split across blockIdx.z for matrices with few row tiles; partials are summed in a fixed order by the finish
+// kernel, which also applies the SwiGLU epilogue).
 //   warp 0   weight producer (bulk copies of raw quant units)        warp 2      limb producer (TMA)
 //   warp 1   MMA issuer, tensor-memory owner                         warps 3..10 operand makers (sc * q -> f16)
-//   warps 11..14 drain
+//   warps 11..18 drain
 // Every mbarrier wait is bounded; a wait that runs out records a code that ferric_cuda_gemm_status reports.
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -35,6 +37,10 @@
 namespace ferric {
 
 constexpr int kTcRows = 128;          // weight rows per CTA (UMMA M)
+constexpr int kTcLimbs = 2;           // operand rows per activation row
+// Operand order along K: within every aligned group of four positions the values sit as 0, 2, 1, 3 (what the operand
+// makers produce without a byte shuffle); tc_kpos(i) = the position of value i.
+__host__ __device__ constexpr int tc_kpos(int i) { return (i & ~3) | ((i & 1) << 1) | ((i >> 1) & 1); }
 constexpr int kTcChunkK = 64;         // K per stage: 64 f16 = one 128-byte swizzle row
 constexpr int kTcRawStages = 2;
 constexpr int kTcMetaStages = 8;      // per-row (d, dmin, mins) of the super-blocks between the makers and the drain
@@ -52,11 +58,12 @@ constexpr int kTcMaxBStages = 8;
 
 struct TcRowMeta {
     float d, dmin;
-    uint32_t m_lo, m_hi;   // the eight 6-bit mins, one per byte
 };
-static_assert(sizeof(TcRowMeta) == 16, "row meta is one 16-byte store");
+static_assert(sizeof(TcRowMeta) == 8, "row meta is one 8-byte store");
+// ring entries per super-block: four K chunks, and for Q4_K the min step
+__host__ __device__ constexpr int tc_per_block(uint32_t ty) { return ty == kGgmlQ4K ? 5 : 4; }
 
-constexpr int kTcSumFloats = 64 * 9;   // per stage: up to 64 activation rows x (8 sub-block sums + 1 scale)
+constexpr int kTcSumFloats = 64;   // per stage: the scales 2^(e-11) of up to 64 activation rows
 __host__ __device__ constexpr int tc_a_stages(uint32_t ty, int) { return ty == kGgmlQ6K ? 3 : 4; }
 __host__ __device__ constexpr int tc_fixed_bytes(uint32_t ty, int n_tile)
 {
@@ -74,7 +81,7 @@ __host__ __device__ constexpr int tc_smem_bytes(uint32_t ty, int n_tile)
 {
     return tc_fixed_bytes(ty, n_tile) + tc_b_stages(ty, n_tile) * tc_b_bytes(n_tile);
 }
-static_assert(tc_b_stages(kGgmlQ4K, 256) >= 3 && tc_b_stages(kGgmlQ6K, 128) >= 3, "limb stages at the widest tiles");
+static_assert(tc_b_stages(kGgmlQ4K, 128) >= 3 && tc_b_stages(kGgmlQ6K, 128) >= 3, "limb stages at the widest tiles");
 
 struct TcBarriers {
     uint64_t raw_full[kTcRawStages], raw_empty[kTcRawStages];
@@ -93,16 +100,21 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n)
 }
 
 // ------------------------------------------------------------------------------------------
-// Activation preparation for this kernel: x (f32) -> limb matrix XL[4 * m][cols] (f16 integers, row 4b + j =
-// limb j of activation row b), SS[nblk][m_pad][8] = sub-block sums of X scaled by 2^-21, UP[nblk][m_pad] = 2^(e-6)
-// (super-block major, so that what one CTA needs for one super-block is contiguous).
-// One warp per (pair of activation rows, super-block), lanes 0..15 row 0, lanes 16..31 row 1, 16 values each --
-// the same scaling and limb split as the GEMV's preparation.
+// Activation preparation for this kernel: x (f32) -> X = rint(x * 2^(22-e)), one e per (activation row, super-block)
+// with 2^e > 2 max|x|, so |X| < 2^21, split as X = 2048 hi + lo (lo in [-1024, 1023], |hi| <= 1024: both integers
+// f16 holds exactly).  Outputs:
+//   XL[2 * m][cols]        f16, row 2b = hi, row 2b + 1 = lo of activation row b, in the operand order tc_kpos
+//   SB[2 * m][64 * nblk]   f16 (Q4_K only): what the tensor core needs for the min term -- per super-block 16 values
+//                          per row, [sb] and [8 + sb] = the two pieces (|piece| <= 128, and a multiple of 256 up to
+//                          2^15: both exact) of the sum of that row's limb over sub-block sb; columns 16..63 of each 64
+//                          are never read
+//   UP[nblk][m_pad]        2^(e-11): V = D_hi + 2^-11 D_lo times UP is the product in x's units
+// One warp per (pair of activation rows, super-block), lanes 0..15 row 0, lanes 16..31 row 1, 16 values each.
 // ------------------------------------------------------------------------------------------
 constexpr int kTcPrepWarps = 4;
 __global__ void __launch_bounds__(32 * kTcPrepWarps)
 tc_prep_kernel(const float* __restrict__ x, size_t m, size_t m_pad, size_t ldx, size_t nblk, __half* __restrict__ xl, size_t ldxl,
-               float* __restrict__ ss, float* __restrict__ up)
+               __half* __restrict__ sb, float* __restrict__ up)
 {
     pdl_launch_dependents();
     pdl_wait();
@@ -130,65 +142,84 @@ tc_prep_kernel(const float* __restrict__ x, size_t m, size_t m_pad, size_t ldx, 
     int e = 0;
     if (amax > 0.0f && amax < INFINITY) {
         (void)frexpf(amax, &e);
-        e += 1;                  // 2^e >= 2 max|x|
+        e += 1;                  // 2^e > 2 max|x|
         if (e < -80) e = -80;
         if (e > 120) e = 120;
     }
-    const float to_int = ldexpf(1.0f, 27 - e);
-    int sum = 0;
-    uint32_t h[kLimbs][8];     // limb j of values 2i, 2i+1 as two f16 integers
+    const float to_int = ldexpf(1.0f, 22 - e);
+    int sum_hi = 0, sum_lo = 0;
+    uint32_t h[kTcLimbs][8];     // limb j of values 2i, 2i+1 as two f16 integers
 #pragma unroll
     for (int i = 0; i < 16; i++) {
-        int X = __float2int_rn(v[i] * to_int);
-        sum += X;                // |X| <= 2^26, sixteen of them fit
-        int a[kLimbs];
-        a[3] = ((X + 64) & 127) - 64; X = (X - a[3]) >> 7;
-        a[2] = ((X + 64) & 127) - 64; X = (X - a[2]) >> 7;
-        a[1] = ((X + 64) & 127) - 64; X = (X - a[1]) >> 7;
-        a[0] = X;
-#pragma unroll
-        for (int j = 0; j < kLimbs; j++) {
-            const uint32_t bits = (uint32_t)__half_as_ushort(__int2half_rn(a[j]));
-            if (i & 1) h[j][i >> 1] |= bits << 16;
-            else h[j][i >> 1] = bits;
+        const int X = __float2int_rn(v[i] * to_int);
+        const int lo = ((X + 1024) & 2047) - 1024, hi = (X - lo) >> 11;
+        sum_hi += hi;
+        sum_lo += lo;
+        const uint32_t bh = (uint32_t)__half_as_ushort(__int2half_rn(hi)), bl = (uint32_t)__half_as_ushort(__int2half_rn(lo));
+        const int pos = tc_kpos(i);
+        if (pos & 1) {
+            h[0][pos >> 1] |= bh << 16;
+            h[1][pos >> 1] |= bl << 16;
+        } else {
+            h[0][pos >> 1] = bh;
+            h[1][pos >> 1] = bl;
         }
     }
     if (valid) {
 #pragma unroll
-        for (int j = 0; j < kLimbs; j++) {
-            uint4* dst = reinterpret_cast<uint4*>(xl + (4 * b + j) * ldxl + blk * 256 + 16 * q);
+        for (int j = 0; j < kTcLimbs; j++) {
+            uint4* dst = reinterpret_cast<uint4*>(xl + (kTcLimbs * b + j) * ldxl + blk * 256 + 16 * q);
             dst[0] = make_uint4(h[j][0], h[j][1], h[j][2], h[j][3]);
             dst[1] = make_uint4(h[j][4], h[j][5], h[j][6], h[j][7]);
         }
     }
-    // sub-block (32 values = two lanes) sums, scaled so that they combine with V (units of 2^-21 * 2^21)
-    const float s16 = (float)sum * 4.76837158203125e-07f;   // 2^-21
-    const float s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 1);
-    if (valid && (q & 1) == 0) ss[(blk * m_pad + b) * 8 + (q >> 1)] = s32;
-    if (valid && q == 0) up[blk * m_pad + b] = ldexpf(1.0f, e - 6);
+    // sub-block (32 values = two lanes) sums of each limb, in two exact pieces
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+    if (sb != nullptr && valid && (q & 1) == 0) {
+#pragma unroll
+        for (int j = 0; j < kTcLimbs; j++) {
+            const int s = j ? sum_lo : sum_hi, low = ((s + 128) & 255) - 128;
+            __half* dst = sb + (kTcLimbs * b + j) * (nblk * 64) + blk * 64 + (q >> 1);
+            dst[0] = __int2half_rn(low);
+            dst[8] = __int2half_rn(s - low);
+        }
+    }
+    if (valid && q == 0) up[blk * m_pad + b] = ldexpf(1.0f, e - 11);
 }
 
 // ------------------------------------------------------------------------------------------
-// Eight weights (one 4-bit value in each byte of w0, w1, at bit `shift`) times the integer scale -> eight f16
-// integers.  Two values per 32-bit multiply (products <= 945 stay inside their 16-bit lanes); 0x6400 | v is
-// the f16 1024 + v, and subtracting 1024 is exact for v < 1024.
+// Operand making.  A small integer v sitting in a mantissa field of an f16 bit pattern is an exact number: bits 0..9
+// under exponent pattern 0x6400 read 1024 + v, bits 4..7 under 0x5400 read 64 + v.  One half-precision fused
+// multiply-add per PAIR of weights then gives scale * v exactly: (1024 + v) * sc - 1024 sc (the product is exact
+// inside the FMA, the bias 1024 sc <= 64512 and the result <= 945 are f16 numbers).  A 32-bit word holds four weights,
+// one per byte; bytes 0 and 2 form one pair, bytes 1 and 3 (after one shift) the other, and the pairs are stored as
+// they come: within every aligned group of four K positions the operand order is 0, 2, 1, 3, and the preparation
+// kernel stores the activation limbs in that same order.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint4 tc_make8(uint32_t w0, uint32_t w1, int shift, uint32_t sc)
+__device__ __forceinline__ __half2 tc_h2(uint32_t u) { return *reinterpret_cast<const __half2*>(&u); }
+__device__ __forceinline__ uint32_t tc_u32(__half2 h) { return *reinterpret_cast<const uint32_t*>(&h); }
+
+// (1024 + b, 1024 + b) for byte `idx` (0..3) of `bytes`: one byte permute against the exponent byte 0x64
+__device__ __forceinline__ __half2 tc_bcast_byte(uint32_t bytes, int idx)
 {
-    const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
-    auto four = [&](uint32_t w, uint32_t& lo, uint32_t& hi) {
-        const uint32_t p02 = (((w >> shift) & 0x000F000Fu) * sc) | 0x64006400u;         // values 0, 2
-        const uint32_t p13 = (((w >> (shift + 8)) & 0x000F000Fu) * sc) | 0x64006400u;   // values 1, 3
-        const __half2 h02 = __hsub2(*reinterpret_cast<const __half2*>(&p02), k1024);
-        const __half2 h13 = __hsub2(*reinterpret_cast<const __half2*>(&p13), k1024);
-        const uint32_t u02 = *reinterpret_cast<const uint32_t*>(&h02), u13 = *reinterpret_cast<const uint32_t*>(&h13);
-        lo = __byte_perm(u02, u13, 0x5410);   // values 0, 1
-        hi = __byte_perm(u02, u13, 0x7632);   // values 2, 3
+    return tc_h2(__byte_perm(bytes, 0x64u, 0x4040u | (uint32_t)idx | ((uint32_t)idx << 8)));
+}
+
+// Sixteen Q4_K weights -- the low nibbles (sub-block 2j, scale sc_lo) and the high nibbles (sub-block 2j + 1, scale
+// sc_hi) of the eight bytes of w0, w1 -- as f16 integers sc * q.  bias_lo = -1024 sc_lo, bias_hi = -64 sc_hi.
+__device__ __forceinline__ void tc_make16(uint32_t w0, uint32_t w1, __half2 sc_lo, __half2 bias_lo, __half2 sc_hi, __half2 bias_hi,
+                                          uint4& lo, uint4& hi)
+{
+    auto word = [&](uint32_t w, uint32_t& l02, uint32_t& l13, uint32_t& h02, uint32_t& h13) {
+        const uint32_t t = w >> 8;
+        l02 = tc_u32(__hfma2(tc_h2((w & 0x000F000Fu) | 0x64006400u), sc_lo, bias_lo));
+        l13 = tc_u32(__hfma2(tc_h2((t & 0x000F000Fu) | 0x64006400u), sc_lo, bias_lo));
+        h02 = tc_u32(__hfma2(tc_h2((w & 0x00F000F0u) | 0x54005400u), sc_hi, bias_hi));
+        h13 = tc_u32(__hfma2(tc_h2((t & 0x00F000F0u) | 0x54005400u), sc_hi, bias_hi));
     };
-    uint4 o;
-    four(w0, o.x, o.y);
-    four(w1, o.z, o.w);
-    return o;
+    word(w0, lo.x, lo.y, hi.x, hi.y);
+    word(w1, lo.z, lo.w, hi.z, hi.w);
 }
 
 // ---------------------------------------------------------------- operand makers
@@ -200,12 +231,12 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
 {
     constexpr int kTcAStages = A_STAGES;
     int fail = 0;
-    // ---------------- operand makers: warp = one 16-row unit, lane = (row g / g+8, 8-byte piece t); see the
-    // prefill kernel for the conflict-free lane map
     const int t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
     const bool unit_ok = wd < tiles_here;
     const uint32_t arow_off = (uint32_t)(2 * wd * 1024 + g * 128);
     const uint32_t col_lo = (uint32_t)((t ^ g) << 4), col_hi = (uint32_t)(((4 + t) ^ g) << 4);
+    const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
+    const __half2 km1024 = __half2half2(__ushort_as_half((unsigned short)0xE400)), km64 = __half2half2(__ushort_as_half((unsigned short)0xD400));
     for (int i = 0; i < nb && !fail; i++) {
         const int rs = i % kTcRawStages;
         if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)i / kTcRawStages) & 1u)) { fail = 4; break; }
@@ -222,19 +253,21 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar->raw_empty[rs]);
-        if (t == 0) {   // hand (d, dmin, mins) of this super-block's rows to the drain
+        // the rows' eight 6-bit scales and mins, one per byte (crates/ferric-gguf/src/lib.rs:795-804)
+        uint32_t scb[2][2], mnb[2][2];
+#pragma unroll
+        for (int hi = 0; hi < 2; hi++) {
+            scb[hi][0] = hdr[hi].y & 0x3F3F3F3Fu;
+            scb[hi][1] = (hdr[hi].w & 0x0F0F0F0Fu) | ((hdr[hi].y >> 2) & 0x30303030u);
+            mnb[hi][0] = hdr[hi].z & 0x3F3F3F3Fu;
+            mnb[hi][1] = ((hdr[hi].w >> 4) & 0x0F0F0F0Fu) | ((hdr[hi].z >> 2) & 0x30303030u);
+        }
+        if (t == 0) {   // hand (d, dmin) of this super-block's rows to the drain
 #pragma unroll
             for (int hi = 0; hi < 2; hi++) {
-                uint32_t mn[8], sc_unused;
-#pragma unroll
-                for (int sb = 0; sb < 8; sb++) q4k_scale_min(hdr[hi], sb, sc_unused, mn[sb]);
-                TcRowMeta rm;
-                rm.d = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x & 0xffffu)));
-                rm.dmin = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x >> 16)));
-                rm.m_lo = mn[0] | (mn[1] << 8) | (mn[2] << 16) | (mn[3] << 24);
-                rm.m_hi = mn[4] | (mn[5] << 8) | (mn[6] << 16) | (mn[7] << 24);
-                *reinterpret_cast<uint4*>(&meta[(i % kTcMetaStages) * kTcRows + 16 * wd + 8 * hi + g]) =
-                    *reinterpret_cast<const uint4*>(&rm);
+                const float dv = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x & 0xffffu)));
+                const float dm = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x >> 16)));
+                *reinterpret_cast<float2*>(&meta[(i % kTcMetaStages) * kTcRows + 16 * wd + 8 * hi + g]) = make_float2(dv, dm);
             }
         }
 #pragma unroll
@@ -242,15 +275,14 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
             uint4 lo[2], up8[2];
 #pragma unroll
             for (int hi = 0; hi < 2; hi++) {
-                uint32_t sc0, sc1, mn_unused;
-                q4k_scale_min(hdr[hi], 2 * j, sc0, mn_unused);
-                q4k_scale_min(hdr[hi], 2 * j + 1, sc1, mn_unused);
+                // sub-blocks 2j (low nibbles) and 2j + 1 (high nibbles): bytes 2j & 3, (2j + 1) & 3 of scale word j >> 1
+                const __half2 s0 = __hsub2(tc_bcast_byte(scb[hi][j >> 1], (2 * j) & 3), k1024);
+                const __half2 s1 = __hsub2(tc_bcast_byte(scb[hi][j >> 1], (2 * j + 1) & 3), k1024);
                 const uint4 q4 = qs[hi][j >> 1];
                 const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
-                lo[hi] = tc_make8(w0, w1, 0, sc0);
-                up8[hi] = tc_make8(w0, w1, 4, sc1);
+                tc_make16(w0, w1, s0, __hmul2(s0, km1024), s1, __hmul2(s1, km64), lo[hi], up8[hi]);
             }
-            const int c = 4 * i + j, s = c % kTcAStages;
+            const int c = 5 * i + j, s = c % kTcAStages;
             // (every lane polls: one polling lane plus a shuffle was measured 15 % slower -- the wake-up is on the critical path)
             if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
             uint8_t* arow = a_stage + s * kTcABytes + arow_off;
@@ -263,23 +295,38 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar->a_full[s]);   // also publishes this block's row meta (written above)
         }
+        if (fail) break;
+        {   // the min step: A[row][sb] = A[row][8 + sb] = min of sub-block sb (K = 16: columns 0, 1 of the row's eight)
+            uint4 mins[2];
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                mins[hi].x = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][0], 0x64u, 0x4140u)), k1024));   // mins 0, 1
+                mins[hi].y = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][0], 0x64u, 0x4342u)), k1024));   // mins 2, 3
+                mins[hi].z = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][1], 0x64u, 0x4140u)), k1024));
+                mins[hi].w = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][1], 0x64u, 0x4342u)), k1024));
+            }
+            const int c = 5 * i + 4, s = c % kTcAStages;
+            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
+            if (t < 2) {
+                uint8_t* arow = a_stage + s * kTcABytes + arow_off;
+#pragma unroll
+                for (int hi = 0; hi < 2; hi++) *reinterpret_cast<uint4*>(arow + hi * 1024 + col_lo) = mins[hi];
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar->a_full[s]);
+        }
     }
     return fail;
 }
 
-// Four Q6_K weights (6-bit values in the bytes of q) times one scale digit -> four f16 integers mult * (q - 32),
-// negated when `neg`: two values per 32-bit multiply (q * mult <= 63 * 15), 0x6400 | v = 1024 + v in f16, and
-// subtracting 1024 + 32 * mult (exact, <= 1504) leaves mult * (q - 32) exactly.
-__device__ __forceinline__ uint2 tc_make4_q6(uint32_t q, uint32_t mult, bool neg)
+// Four Q6_K weights (6-bit values in the bytes of q) times both scale digits -> f16 integers sl * (q - 32) and
+// sh * (q - 32), in the order bytes 0, 2, 1, 3: (1024 + q) * s - 1056 s, exact as above (1056 s = 33 s * 32).
+__device__ __forceinline__ void tc_make4_q6(uint32_t q, __half2 sl, __half2 bl, __half2 sh, __half2 bh, uint2& p0, uint2& p1)
 {
-    const __half2 bias = __half2half2(__ushort_as_half((unsigned short)(0x6400u + 32u * mult)));   // 1024 + 32 mult: exact bits
-    const uint32_t p02 = ((q & 0x00FF00FFu) * mult) | 0x64006400u;          // values 0, 2
-    const uint32_t p13 = (((q >> 8) & 0x00FF00FFu) * mult) | 0x64006400u;   // values 1, 3
-    const __half2 h02 = __hsub2(*reinterpret_cast<const __half2*>(&p02), bias);
-    const __half2 h13 = __hsub2(*reinterpret_cast<const __half2*>(&p13), bias);
-    const uint32_t sign = neg ? 0x80008000u : 0u;
-    const uint32_t u02 = *reinterpret_cast<const uint32_t*>(&h02) ^ sign, u13 = *reinterpret_cast<const uint32_t*>(&h13) ^ sign;
-    return make_uint2(__byte_perm(u02, u13, 0x5410), __byte_perm(u02, u13, 0x7632));
+    const __half2 a02 = tc_h2((q & 0x003F003Fu) | 0x64006400u), a13 = tc_h2(((q >> 8) & 0x003F003Fu) | 0x64006400u);
+    p0 = make_uint2(tc_u32(__hfma2(a02, sl, bl)), tc_u32(__hfma2(a13, sl, bl)));
+    p1 = make_uint2(tc_u32(__hfma2(a02, sh, bh)), tc_u32(__hfma2(a13, sh, bh)));
 }
 
 // Q6_K (unit layout in layout.h; lane ownership as in the prefill kernel's Q6_K stage): two operand planes per chunk,
@@ -293,6 +340,8 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
     const int t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
     const bool unit_ok = wd < tiles_here;
     const uint32_t arow_off = (uint32_t)(2 * wd * 1024 + g * 128);
+    const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400)), k1032 = __half2half2(__ushort_as_half((unsigned short)0x6408));
+    const __half2 km1056 = __half2half2(__ushort_as_half((unsigned short)0xE420));
     for (int i = 0; i < nb && !fail; i++) {
         const int rs = i % kTcRawStages;
         if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)i / kTcRawStages) & 1u)) { fail = 4; break; }
@@ -315,11 +364,8 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
         if (t == 0) {
 #pragma unroll
             for (int hi = 0; hi < 2; hi++) {
-                TcRowMeta rm;
-                rm.d = __half2float(__ushort_as_half((unsigned short)(hi ? (dpair >> 16) : (dpair & 0xffffu))));
-                rm.dmin = 0.0f;
-                rm.m_lo = rm.m_hi = 0u;
-                *reinterpret_cast<uint4*>(&meta[(i % kTcMetaStages) * kTcRows + 16 * wd + 8 * hi + g]) = *reinterpret_cast<const uint4*>(&rm);
+                const float dv = __half2float(__ushort_as_half((unsigned short)(hi ? (dpair >> 16) : (dpair & 0xffffu))));
+                *reinterpret_cast<float2*>(&meta[(i % kTcMetaStages) * kTcRows + 16 * wd + 8 * hi + g]) = make_float2(dv, 0.0f);
             }
         }
 #pragma unroll
@@ -330,18 +376,18 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
 #pragma unroll
             for (int hi = 0; hi < 2; hi++) {
                 const uint32_t scw = j == 0 ? sc[hi].x : (j == 1 ? sc[hi].y : (j == 2 ? sc[hi].z : sc[hi].w));
+                const uint32_t slb = scw & 0x0F0F0F0Fu, shb = ((scw >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // digits sl, sh + 8
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
 #pragma unroll
                     for (int is = 0; is < 2; is++) {
-                        const int scv = (int)(int8_t)(scw >> (8 * (2 * c + is)));
-                        const int sl = scv & 15, sh = scv >> 4;           // scv = 16 sh + sl
+                        const __half2 sl = __hsub2(tc_bcast_byte(slb, 2 * c + is), k1024);      // sc = 16 sh + sl, sl 0..15
+                        const __half2 sh = __hsub2(tc_bcast_byte(shb, 2 * c + is), k1032);      // sh -8..7
                         const uint4 qlv = ql[hi][c];
                         const uint32_t lw = (2 * h + is) == 0 ? qlv.x : ((2 * h + is) == 1 ? qlv.y : ((2 * h + is) == 2 ? qlv.z : qlv.w));
                         const uint32_t hw = (2 * h + is) == 0 ? qh[hi].x : ((2 * h + is) == 1 ? qh[hi].y : ((2 * h + is) == 2 ? qh[hi].z : qh[hi].w));
                         const uint32_t q = ((lw >> (4 * kp)) & 0x0F0F0F0Fu) | (((hw >> (2 * (2 * kp + c))) & 0x03030303u) << 4);
-                        p0[hi][2 * c + is] = tc_make4_q6(q, (uint32_t)sl, false);
-                        p1[hi][2 * c + is] = tc_make4_q6(q, (uint32_t)(sh < 0 ? -sh : sh), sh < 0);
+                        tc_make4_q6(q, sl, __hmul2(sl, km1056), sh, __hmul2(sh, km1056), p0[hi][2 * c + is], p1[hi][2 * c + is]);
                     }
                 }
             }
@@ -366,20 +412,21 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
 
 template <uint32_t TY, int N_TILE>
 __global__ void __launch_bounds__(kTcThreads, 1)
-gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap, const float* __restrict__ ss,
-                   const float* __restrict__ up, float* __restrict__ out, size_t ld_out, size_t split_stride, int rows, int nblk,
-                   int m, int m_pad, int row_tiles16, int blocks_per_split, int* __restrict__ err)
+gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap smap,
+               const float* __restrict__ up, float* __restrict__ out, size_t ld_out, size_t split_stride, int rows, int nblk,
+               int m, int m_pad, int row_tiles16, int blocks_per_split, int* __restrict__ err)
 {
     extern __shared__ uint8_t tc_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int kBStages = tc_b_stages(TY, N_TILE), kBBytes = tc_b_bytes(N_TILE), kActs = N_TILE / 4;
+    constexpr int kBStages = tc_b_stages(TY, N_TILE), kBBytes = tc_b_bytes(N_TILE), kActs = N_TILE / kTcLimbs;
+    constexpr int kPer = tc_per_block(TY);   // ring entries per super-block
     constexpr int kTcAStages = tc_a_stages(TY, N_TILE), kPlanes = tc_planes(TY), kAStageBytes = kPlanes * kTcABytes;
     constexpr int kUnit = tc_unit_bytes(TY), kTcRawBytes = tc_raw_bytes(TY);
     uint8_t* a_stage = smem;                                  // [kTcAStages][kPlanes][16384]
     uint8_t* b_stage = a_stage + kTcAStages * kAStageBytes;
     uint8_t* raw_stage = b_stage + kBStages * kBBytes;
     TcRowMeta* meta = reinterpret_cast<TcRowMeta*>(raw_stage + kTcRawStages * kTcRawBytes);   // [kTcMetaStages][128]
-    float* sums = reinterpret_cast<float*>(meta + kTcMetaStages * kTcRows);   // [2][kActs * 9]: staged SS and UP of a super-block
+    float* sums = reinterpret_cast<float*>(meta + kTcMetaStages * kTcRows);   // [2][kActs]: staged UP of a super-block
     TcBarriers* bar = reinterpret_cast<TcBarriers*>(sums + 2 * kTcSumFloats);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -407,7 +454,8 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
         bar->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    constexpr int kTmemCols = 2 * kPlanes * N_TILE;   // two sets of accumulators (one per operand plane); a power of two >= 128
+    // two sets of two accumulators (Q4_K: product and min term; Q6_K: one per operand plane); a power of two >= 128
+    constexpr int kTmemCols = 2 * 2 * N_TILE;
     static_assert(kTmemCols <= 512, "tensor memory holds 512 columns");
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
@@ -435,14 +483,20 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             }
         }
     } else if (warp == 2) {
-        // ---------------- limb producer: [64 k x N_TILE operand rows] f16 per stage
+        // ---------------- limb producer: [64 k x N_TILE operand rows] f16 per stage; after a super-block's four chunks,
+        // for Q4_K, the tile of its sub-block sums
         if (lane == 0) {
             pdl_wait();   // the limbs come from the preparation kernel launched just before
-            for (int c = 0; c < 4 * nb; c++) {
-                const int s = c % kBStages;
-                if (!mbar_wait(&bar->b_empty[s], (((uint32_t)c / kBStages) & 1u) ^ 1u)) { fail = 2; break; }
-                mbar_expect_tx(&bar->b_full[s], (uint32_t)kBBytes);
-                tma_load_2d(b_stage + s * kBBytes, &xmap, (4 * blk0 + c) * kTcChunkK, 4 * act0, &bar->b_full[s]);
+            uint32_t s = 0, ph = 0;
+            for (int i = 0; i < nb && !fail; i++) {
+#pragma unroll 1
+                for (int j = 0; j < kPer; j++) {
+                    if (!mbar_wait(&bar->b_empty[s], ph ^ 1u)) { fail = 2; break; }
+                    mbar_expect_tx(&bar->b_full[s], (uint32_t)kBBytes);
+                    if (j < 4) tma_load_2d(b_stage + s * kBBytes, &xmap, (4 * (blk0 + i) + j) * kTcChunkK, kTcLimbs * act0, &bar->b_full[s]);
+                    else tma_load_2d(b_stage + s * kBBytes, &smap, (blk0 + i) * kTcChunkK, kTcLimbs * act0, &bar->b_full[s]);
+                    if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
+                }
             }
         }
     } else if (warp == 1) {
@@ -459,19 +513,23 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
                 const int buf = i & 1;
                 if (!mbar_wait(&bar->acc_empty[buf], (((uint32_t)i >> 1) & 1u) ^ 1u)) { fail = 3; break; }
                 tc_fence_after();
-                const uint32_t d0 = tmem_acc + (uint32_t)(buf * kPlanes * N_TILE);
+                const uint32_t d0 = tmem_acc + (uint32_t)(buf * 2 * N_TILE);
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
+                for (int j = 0; j < kPer; j++) {
                     if (!mbar_try(a_full0 + 8 * sa, pa) && !mbar_wait(&bar->a_full[sa], pa)) { fail = 3; break; }
                     if (!mbar_try(b_full0 + 8 * sb, pb) && !mbar_wait(&bar->b_full[sb], pb)) { fail = 3; break; }
                     tc_fence_after();
                     const uint32_t ad = adesc0 + sa * (uint32_t)(kAStageBytes >> 4), bd = bdesc0 + sb * (uint32_t)(kBBytes >> 4);
+                    if (j < 4) {
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; k4++)
+                        for (int k4 = 0; k4 < 4; k4++)
 #pragma unroll
-                        for (int pl = 0; pl < kPlanes; pl++)
-                            umma_f16_lo(d0 + pl * N_TILE, ad + (uint32_t)(pl * (kTcABytes >> 4) + 2 * k4), bd + 2 * k4, idesc,
-                                        (j | k4) ? 1u : 0u);
+                            for (int pl = 0; pl < kPlanes; pl++)
+                                umma_f16_lo(d0 + pl * N_TILE, ad + (uint32_t)(pl * (kTcABytes >> 4) + 2 * k4), bd + 2 * k4, idesc,
+                                            (j | k4) ? 1u : 0u);
+                    } else {
+                        umma_f16_lo(d0 + N_TILE, ad, bd, idesc, 0u);   // mins x sub-block sums, K = 16
+                    }
                     umma_commit_addr(a_empty0 + 8 * sa);
                     umma_commit_addr(b_empty0 + 8 * sb);
                     if (++sa == (uint32_t)kTcAStages) { sa = 0; pa ^= 1u; }
@@ -486,82 +544,57 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
         if (TY == kGgmlQ4K) fail = tc_make_q4k<kTcAStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
         else fail = tc_make_q6k<kTcAStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
     } else {
-        // ---------------- drain: TMEM lane = weight row; column 4b + j = limb j of activation row act0 + b
-        // two warps share a TMEM lane quarter; warp half h takes the groups of eight activation rows 2g + h
+        // ---------------- drain: TMEM lane = weight row; columns 2b, 2b + 1 = the hi and lo limb of activation row act0 + b.
+        // Two warps share a TMEM lane quarter; warp half h takes the groups of eight activation rows 2g + h.
         const int q = warp & 3, rloc = 32 * q + lane, wrow = row0 + rloc, half = (warp - kTcFirstDrain) >> 2;
-        constexpr int kGroups = kActs / 16;            // groups of eight activation rows per drain warp
+        constexpr int kGroups = N_TILE / 32;           // groups of eight activation rows (16 columns) per drain warp
         float acc[kGroups * 8];
 #pragma unroll
         for (int b = 0; b < kGroups * 8; b++) acc[b] = 0.0f;
-        pdl_wait();   // ss / up come from the preparation kernel
-        // What the drain needs of a super-block besides the accumulator -- the activation rows' eight sub-block sums
-        // and their scale -- is fetched one super-block ahead into registers and staged in shared memory.
-        const int dt = threadIdx.x - 32 * kTcFirstDrain;          // 0..127
-        auto fetch = [&](int i, float4& sv, float& uv) {
-            sv = make_float4(0.f, 0.f, 0.f, 0.f);
-            uv = 0.f;
-            if (i < nb) {
-                const size_t base = (size_t)(blk0 + i) * m_pad + act0;
-                if (dt < kActs * 2) sv = __ldg(reinterpret_cast<const float4*>(ss + base * 8) + dt);
-                if (dt < kActs) uv = __ldg(up + base + dt);
-            }
+        pdl_wait();   // up comes from the preparation kernel
+        // The activation rows' scales of a super-block are fetched one super-block ahead into a register and staged in
+        // shared memory.
+        const int dt = threadIdx.x - 32 * kTcFirstDrain;          // 0..255
+        auto fetch = [&](int i) {
+            float uv = 0.f;
+            if (i < nb && dt < kActs) uv = __ldg(up + (size_t)(blk0 + i) * m_pad + act0 + dt);
+            return uv;
         };
-        auto stage = [&](int slot, const float4& sv, float uv) {
-            float* dst = sums + slot * kTcSumFloats;
-            if (dt < kActs * 2) reinterpret_cast<float4*>(dst)[dt] = sv;
-            if (dt < kActs) dst[kActs * 8 + dt] = uv;
-        };
-        float4 sv;
-        float uv;
-        fetch(0, sv, uv);
-        stage(0, sv, uv);
+        float uv = fetch(0);
+        if (dt < kActs) sums[dt] = uv;
         named_bar_sync(1, 32 * kTcDrainWarps);
+        const uint32_t lane_base = tmem_acc + ((uint32_t)(32 * q) << 16);
         for (int i = 0; i < nb && !fail; i++) {
             const int buf = i & 1;
-            fetch(i + 1, sv, uv);
+            uv = fetch(i + 1);
             if (!mbar_wait(&bar->acc_full[buf], ((uint32_t)i >> 1) & 1u)) { fail = 6; break; }
             tc_fence_after();
             const TcRowMeta rm = meta[(i % kTcMetaStages) * kTcRows + rloc];
             const float* sl = sums + (i & 1) * kTcSumFloats;
-            float mf[8];
-#pragma unroll
-            for (int sb = 0; sb < 4; sb++) {
-                mf[sb] = (float)((rm.m_lo >> (8 * sb)) & 0xffu);
-                mf[4 + sb] = (float)((rm.m_hi >> (8 * sb)) & 0xffu);
-            }
+            const float ndmin = -rm.dmin;
 #pragma unroll
             for (int gg = 0; gg < kGroups; gg++) {
                 const int grp = 2 * gg + half;
-                uint32_t v[32];
-                tmem_ld_32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * kPlanes * N_TILE + 32 * grp), v);
-                if (kPlanes == 2) {   // second scale digit: D1 + 16 D2
-                    uint32_t w[32];
-                    tmem_ld_32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)((buf * kPlanes + 1) * N_TILE + 32 * grp), w);
-#pragma unroll
-                    for (int e = 0; e < 32; e++) v[e] = __float_as_uint(fmaf(16.0f, __uint_as_float(w[e]), __uint_as_float(v[e])));
-                }
+                uint32_t v[16], w[16];
+                const uint32_t c0 = lane_base + (uint32_t)(buf * 2 * N_TILE + 16 * grp);
+                tmem_ld_16x2(c0, c0 + (uint32_t)N_TILE, v, w);
 #pragma unroll
                 for (int bb = 0; bb < 8; bb++) {
-                    const int b = 8 * grp + bb;
-                    const float scale = sl[kActs * 8 + b];
-                    float V = __uint_as_float(v[4 * bb + 3]);
-                    V = fmaf(V, 0.0078125f, __uint_as_float(v[4 * bb + 2]));
-                    V = fmaf(V, 0.0078125f, __uint_as_float(v[4 * bb + 1]));
-                    V = fmaf(V, 0.0078125f, __uint_as_float(v[4 * bb]));
-                    if (TY == kGgmlQ4K) {
-                        const float4 s0 = reinterpret_cast<const float4*>(sl)[2 * b], s1 = reinterpret_cast<const float4*>(sl)[2 * b + 1];
-                        float Mn = mf[0] * s0.x;
-                        Mn = fmaf(mf[1], s0.y, Mn); Mn = fmaf(mf[2], s0.z, Mn); Mn = fmaf(mf[3], s0.w, Mn);
-                        Mn = fmaf(mf[4], s1.x, Mn); Mn = fmaf(mf[5], s1.y, Mn); Mn = fmaf(mf[6], s1.z, Mn); Mn = fmaf(mf[7], s1.w, Mn);
-                        acc[8 * gg + bb] = fmaf(scale, fmaf(rm.d, V, -rm.dmin * Mn), acc[8 * gg + bb]);
-                    } else {
-                        acc[8 * gg + bb] = fmaf(scale * rm.d, V, acc[8 * gg + bb]);
+                    const float scale = sl[8 * grp + bb];
+                    if (TY == kGgmlQ4K) {      // w = the min term's accumulator
+                        const float V = fmaf(__uint_as_float(v[2 * bb + 1]), 0.00048828125f, __uint_as_float(v[2 * bb]));
+                        const float Mn = fmaf(__uint_as_float(w[2 * bb + 1]), 0.00048828125f, __uint_as_float(w[2 * bb]));
+                        acc[8 * gg + bb] = fmaf(scale, fmaf(rm.d, V, ndmin * Mn), acc[8 * gg + bb]);
+                    } else {                   // w = the second scale digit's plane: D1 + 16 D2
+                        const float hi = fmaf(16.0f, __uint_as_float(w[2 * bb]), __uint_as_float(v[2 * bb]));
+                        const float lo = fmaf(16.0f, __uint_as_float(w[2 * bb + 1]), __uint_as_float(v[2 * bb + 1]));
+                        acc[8 * gg + bb] = fmaf(scale * rm.d, fmaf(lo, 0.00048828125f, hi), acc[8 * gg + bb]);
                     }
                 }
             }
             // every drain thread has finished reading the other slot (it did so one iteration ago and has met the
             // barrier below since), so the next super-block's values can go there
-            stage((i + 1) & 1, sv, uv);
+            if (dt < kActs) sums[((i + 1) & 1) * kTcSumFloats + dt] = uv;
             named_bar_sync(1, 32 * kTcDrainWarps);
             tc_fence_before();
             __syncwarp();
@@ -642,34 +675,41 @@ size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 struct TcPlan {
     int n_tile, splits, blocks_per_split;
     size_t m_pad;                              // activation rows rounded up to whole tiles
-    size_t off_ss, off_up, off_part, total;   // scratch offsets (XL at 0)
+    size_t off_sb, off_up, off_part, total;   // scratch offsets (XL at 0)
     bool needs_finish;
 };
 
 TcPlan tc_plan(uint32_t ty, const DeviceWeights& w, size_t m, Epilogue epi, int sm_count)
 {
     TcPlan p;
-    p.n_tile = m <= 16 ? 64 : ((m <= 32 || ty == kGgmlQ6K) ? 128 : 256);   // Q6_K: two accumulator planes, so half the width
-    const size_t row_tiles = (w.rows + kTcRows - 1) / kTcRows, act_tiles = (4 * m + p.n_tile - 1) / p.n_tile;
+    p.n_tile = m <= 32 ? 64 : 128;   // operand rows per tile: 32 or 64 activation rows (tensor memory holds 4 x n_tile columns)
+    const size_t row_tiles = (w.rows + kTcRows - 1) / kTcRows, act_tiles = (kTcLimbs * m + p.n_tile - 1) / p.n_tile;
     const size_t tiles = row_tiles * act_tiles;
-    size_t splits = 1;
-    if (tiles * 5 < (size_t)sm_count * 4) splits = ((size_t)sm_count + tiles - 1) / tiles;   // fill the machine along K
-    if (splits > w.nblk) splits = w.nblk;
-    if (splits > 16) splits = 16;
+    // Cut K so that the CTAs come in whole waves: the cost of a cut is the number of waves times the super-blocks of one
+    // CTA (plus two for filling and emptying its pipeline).
+    size_t splits = 1, best = ~(size_t)0;
+    for (size_t s = 1; s <= 16 && s <= w.nblk; s++) {
+        const size_t waves = (tiles * s + (size_t)sm_count - 1) / (size_t)sm_count;
+        const size_t cost = 2 * waves * ((w.nblk + s - 1) / s + 2) + s;   // each piece also costs the finish kernel half a super-block
+        if (cost < best) {
+            best = cost;
+            splits = s;
+        }
+    }
     p.blocks_per_split = (int)((w.nblk + splits - 1) / splits);
     p.splits = (int)((w.nblk + p.blocks_per_split - 1) / p.blocks_per_split);
     p.needs_finish = p.splits > 1 || epi == kEpiSwiglu;
-    p.m_pad = act_tiles * (size_t)(p.n_tile / 4);
-    p.off_ss = align256(4 * m * w.cols * sizeof(__half));
-    p.off_up = p.off_ss + align256(p.m_pad * w.nblk * 8 * sizeof(float));
+    p.m_pad = act_tiles * (size_t)(p.n_tile / kTcLimbs);
+    p.off_sb = align256(kTcLimbs * m * w.cols * sizeof(__half));
+    p.off_up = p.off_sb + (ty == kGgmlQ4K ? align256(kTcLimbs * m * w.nblk * 64 * sizeof(__half)) : 0);
     p.off_part = p.off_up + align256(p.m_pad * w.nblk * sizeof(float));
     p.total = p.off_part + (p.needs_finish ? align256((size_t)p.splits * m * w.rows * sizeof(float)) : 0);
     return p;
 }
 
 template <uint32_t TY, int N_TILE>
-int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const float* ss, const float* up, float* out,
-                       size_t ld_out, size_t split_stride, size_t m, const TcPlan& p, bool pdl)
+int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& smap, const float* up,
+                       float* out, size_t ld_out, size_t split_stride, size_t m, const TcPlan& p, bool pdl)
 {
     static bool attr_done[64] = {};
     int dev = 0;
@@ -679,9 +719,9 @@ int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMa
                                              tc_smem_bytes(TY, N_TILE)));
         attr_done[dev] = true;
     }
-    dim3 grid((unsigned)((w.rows + kTcRows - 1) / kTcRows), (unsigned)((4 * m + N_TILE - 1) / N_TILE), (unsigned)p.splits);
+    dim3 grid((unsigned)((w.rows + kTcRows - 1) / kTcRows), (unsigned)((kTcLimbs * m + N_TILE - 1) / N_TILE), (unsigned)p.splits);
     FERRIC_CUDA_TRY(launch_kernel(gemv_tc_kernel<TY, N_TILE>, grid, dim3(kTcThreads), (size_t)tc_smem_bytes(TY, N_TILE), st, pdl,
-                                  (const uint8_t*)w.units, map, ss, up, out, ld_out, split_stride, (int)w.rows, (int)w.nblk,
+                                  (const uint8_t*)w.units, map, smap, up, out, ld_out, split_stride, (int)w.rows, (int)w.nblk,
                                   (int)m, (int)p.m_pad, (int)w.row_tiles(), p.blocks_per_split, gemm_status_word()));
     return kOk;
 }
@@ -689,13 +729,13 @@ int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMa
 
 bool gemv_tc_eligible(uint32_t ty, const DeviceWeights& w, size_t m)
 {
-    // Measured cross-over with the mma.sync GEMV (which runs in passes of 4 activation rows; 64-layer step at 12 / 16 / 24
-    // rows: 12.4 / 15.3 / 21.0 ms in passes against 14.5 / 15.5 / 19.9 ms here): Q4_K from 17 rows, Q6_K -- two operand
-    // planes, so twice the MMAs -- from 24.  FERRIC_CUDA_GEMV_TC_MIN_M overrides both; 0 disables the path.
+    // Measured cross-over with the mma.sync GEMV, which runs in passes of 4 activation rows (us per product, GEMV / this
+    // kernel: gate|up 34816 x 5120 at 12 rows 71 / 82, at 13 rows 91 / 82; down Q6_K 5120 x 17408 58 / 68 and 71 / 70;
+    // q|k|v 24 / 26 and 28 / 26): from 13 rows for both formats.  FERRIC_CUDA_GEMV_TC_MIN_M overrides it; 0 disables the path.
     const char* env = getenv("FERRIC_CUDA_GEMV_TC_MIN_M");   // read per call: tests move the threshold
     const int forced = env ? atoi(env) : -1;
     if (ty != kGgmlQ4K && ty != kGgmlQ6K) return false;
-    const int min_m = forced >= 0 ? forced : (ty == kGgmlQ4K ? 17 : 24);
+    const int min_m = forced >= 0 ? forced : 13;
     return min_m > 0 && m >= (size_t)min_m && m <= 4096 && w.nblk > 0 && w.rows > 0 && w.rows <= (size_t)INT32_MAX / 2;
 }
 
@@ -715,34 +755,46 @@ int32_t launch_gemv_tc(cudaStream_t st, uint32_t ty, const DeviceWeights& w, con
     const TcPlan p = tc_plan(ty, w, m, epi, tune.sm_count);
     uint8_t* base = reinterpret_cast<uint8_t*>(scratch);
     __half* xl = reinterpret_cast<__half*>(base);
-    float* ss = reinterpret_cast<float*>(base + p.off_ss);
+    __half* sb = ty == kGgmlQ4K ? reinterpret_cast<__half*>(base + p.off_sb) : nullptr;
     float* up = reinterpret_cast<float*>(base + p.off_up);
     float* part = reinterpret_cast<float*>(base + p.off_part);
 
     const size_t pairs = (m + 1) / 2, warps = pairs * w.nblk;
     FERRIC_CUDA_TRY(launch_kernel(tc_prep_kernel, dim3((unsigned)((warps + kTcPrepWarps - 1) / kTcPrepWarps)), dim3(32 * kTcPrepWarps),
-                                  0, st, tune.pdl, x, m, p.m_pad, ldx, w.nblk, xl, w.cols, ss, up));
-    CUtensorMap map;
-    const cuuint64_t dims[2] = {(cuuint64_t)w.cols, (cuuint64_t)(4 * m)};
-    const cuuint64_t strides[1] = {(cuuint64_t)w.cols * 2};
+                                  0, st, tune.pdl, x, m, p.m_pad, ldx, w.nblk, xl, w.cols, sb, up));
+    CUtensorMap map, smap;
     const cuuint32_t box[2] = {(cuuint32_t)kTcChunkK, (cuuint32_t)p.n_tile};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xl, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_last_error("cuTensorMapEncodeTiled (limbs) failed with code %d", (int)r);
-        return kErrCuda;
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)w.cols, (cuuint64_t)(kTcLimbs * m)};
+        const cuuint64_t strides[1] = {(cuuint64_t)w.cols * 2};
+        CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xl, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            set_last_error("cuTensorMapEncodeTiled (limbs) failed with code %d", (int)r);
+            return kErrCuda;
+        }
+    }
+    smap = map;   // Q6_K has no min term and never reads it
+    if (sb != nullptr) {
+        const cuuint64_t dims[2] = {(cuuint64_t)w.nblk * 64, (cuuint64_t)(kTcLimbs * m)};
+        const cuuint64_t strides[1] = {(cuuint64_t)w.nblk * 64 * 2};
+        CUresult r = enc(&smap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, sb, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            set_last_error("cuTensorMapEncodeTiled (sub-block sums) failed with code %d", (int)r);
+            return kErrCuda;
+        }
     }
     float* out = p.needs_finish ? part : y;
     const size_t ld_out = p.needs_finish ? w.rows : ldy, split_stride = m * w.rows;
     int32_t rc;
     if (ty == kGgmlQ6K) {
-        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ6K, 64>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
-        else rc = launch_tc_tile<kGgmlQ6K, 128>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
+        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ6K, 64>(st, w, map, smap, up, out, ld_out, split_stride, m, p, tune.pdl);
+        else rc = launch_tc_tile<kGgmlQ6K, 128>(st, w, map, smap, up, out, ld_out, split_stride, m, p, tune.pdl);
     } else {
-        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ4K, 64>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
-        else if (p.n_tile == 128) rc = launch_tc_tile<kGgmlQ4K, 128>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
-        else rc = launch_tc_tile<kGgmlQ4K, 256>(st, w, map, ss, up, out, ld_out, split_stride, m, p, tune.pdl);
+        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ4K, 64>(st, w, map, smap, up, out, ld_out, split_stride, m, p, tune.pdl);
+        else rc = launch_tc_tile<kGgmlQ4K, 128>(st, w, map, smap, up, out, ld_out, split_stride, m, p, tune.pdl);
     }
     if (rc != kOk) return rc;
     *launches += 2;

@@ -196,6 +196,21 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&v)[32])
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// Two runs of 16 consecutive accumulator columns (both loads in flight, then the wait, as one statement so that no
+// use of the registers can move ahead of the wait): v[j] = D[lane][c0 + j], w[j] = D[lane][c1 + j].
+__device__ __forceinline__ void tmem_ld_16x2(uint32_t taddr0, uint32_t taddr1, uint32_t (&v)[16], uint32_t (&w)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%32];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%33];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(w[0]), "=r"(w[1]), "=r"(w[2]),
+          "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]), "=r"(w[8]), "=r"(w[9]), "=r"(w[10]), "=r"(w[11]),
+          "=r"(w[12]), "=r"(w[13]), "=r"(w[14]), "=r"(w[15])
+        : "r"(taddr0), "r"(taddr1)
+        : "memory");
+}
 
 // 6-bit (scale, min) of sub-block j from the 12 packed bytes (crates/ferric-gguf/src/lib.rs:795-804); the raw
 // block's first 16 bytes sit in `hdr` (x = d | dmin << 16, y..w = the 12 bytes).

@@ -1,14 +1,16 @@
 """GPU parity of the batched decode product on the tensor cores (more than 8 activation rows).
 
-The kernel computes exactly what the GEMV computes -- integer products of the quantised weights with the
-activations' base-128 limbs, scaled per super-block in f32 -- so the bar is the decode bar: 1e-3 relative + 1e-4
-absolute against the oracle's dequantise-then-dot product (with the exact float64 product beside it, see
-test_gpu_parity.assert_close).  Every case also reads the kernel's give-up word: no bounded wait may run out.
+The kernel multiplies the quantised weights' integers with the activations rounded to 22-bit integers per
+(row, super-block), split into two 11-bit limbs, on the tensor cores and scales per super-block in f32 -- at least the
+precision of an f32 product -- so the bar is the decode bar: 1e-3 relative + 1e-4 absolute against the oracle's
+dequantise-then-dot product (with the exact float64 product beside it, see test_gpu_parity.assert_close).  Every case
+also reads the kernel's give-up word: no bounded wait may run out.
 
-Shapes walk the kernel's branches: the three tile widths (up to 16 / 32 / 64 activation rows), more than one
+Shapes walk the kernel's branches: the two tile widths (up to 32 / 64 activation rows), more than one
 activation tile, ragged weight rows (rows not a multiple of 128 or of 16), a K split (few row tiles, many
-super-blocks) with its finish kernel, the fused SwiGLU finish, Q6_K's two operand planes with scales over the whole
-int8 range, and activations spanning many binades (one scale per row and super-block).
+super-blocks) with its finish kernel, the fused SwiGLU finish, Q4_K's min term on the tensor core, Q6_K's two operand
+planes with scales over the whole int8 range, and activations spanning many binades (one scale per row and
+super-block).
 """
 import os
 
@@ -39,7 +41,7 @@ def ctx(F):
 
 @pytest.fixture(autouse=True)
 def tensor_core_path_from_nine_rows(monkeypatch):
-    """By default Q4_K takes this kernel from 17 activation rows; the tests here also cover its narrowest tile."""
+    """By default this kernel takes over from 13 activation rows; the tests here also run it below that."""
     monkeypatch.setenv("FERRIC_CUDA_GEMV_TC_MIN_M", "9")
 
 
@@ -59,6 +61,7 @@ def run(F, ctx, raw, ty, rows, cols, x, swiglu=False):
     (12, 1000, 2048, 33),     # widest tile, ragged rows
     (12, 272, 512, 64),
     (12, 130, 768, 70),       # two activation tiles of the widest kind, the second nearly empty
+    (12, 256, 512, 128),      # two full activation tiles
     (12, 256, 5120, 17),      # few row tiles, 20 super-blocks: K split + finish kernel
     (14, 128, 256, 24),       # Q6_K: two operand planes
     (14, 200, 768, 40),       # Q6_K, two activation tiles (its tile holds 32 rows)
@@ -84,6 +87,25 @@ def test_q6k_full_int8_scales(F, ctx):
     x = synth.activations(m, cols, seed=3)
     ref = O.matmul_q(raw, 14, rows, cols, x, threads=NCPU)
     assert_close(run(F, ctx, raw, 14, rows, cols, x), ref, "q6k int8 scales", exact_product(raw, 14, rows, cols, x))
+
+
+def test_q4k_min_term_at_its_extremes(F, ctx):
+    """The min term is computed on the tensor core from the 6-bit mins and the sums of the activation limbs over each
+    sub-block: all scales and mins at 63 with all quants at 15 (the largest operands), and all quants at 0 (only the
+    min term is left), with activations of one sign so that the sub-block sums are as large as they get."""
+    rows, cols, m = 144, 1024, 40
+    rng = np.random.default_rng(5)
+    nblocks = rows * cols // 256
+    for qbyte in (0xFF, 0x00):
+        raw = np.zeros((nblocks, 144), dtype=np.uint8)
+        raw[:, 0:2] = rng.uniform(0.001, 0.01, nblocks).astype(np.float16).view(np.uint8).reshape(-1, 2)
+        raw[:, 2:4] = rng.uniform(0.001, 0.01, nblocks).astype(np.float16).view(np.uint8).reshape(-1, 2)
+        raw[:, 4:16] = 0xFF
+        raw[:, 16:] = qbyte
+        raw = raw.reshape(-1)
+        x = np.abs(synth.activations(m, cols, seed=8)) + np.float32(0.5)
+        ref = O.matmul_q(raw, 12, rows, cols, x, threads=NCPU)
+        assert_close(run(F, ctx, raw, 12, rows, cols, x), ref, f"q4k extremes {qbyte:#x}", exact_product(raw, 12, rows, cols, x))
 
 
 def test_fused_swiglu_finish(F, ctx):
@@ -120,8 +142,8 @@ def test_scaled_activations_zero_rows_and_outliers(F, ctx):
 
 
 def test_same_result_as_the_gemv_passes(F, ctx, monkeypatch):
-    """The tensor-core path and the mma.sync GEMV use the same limbs and the same integer sums; only f32
-    scaling order differs.  Their results agree far inside the tolerance."""
+    """The tensor-core path keeps 22 bits of each activation under its super-block's largest, the mma.sync GEMV 28;
+    both sum exact integer products.  Their results agree far inside the tolerance."""
     rows, cols, m = 256, 1024, 16
     raw = synth.matrix(12, rows, cols, seed=21)
     x = synth.activations(m, cols, seed=22)
