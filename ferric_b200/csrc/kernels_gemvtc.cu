@@ -414,8 +414,10 @@ template <uint32_t TY, int N_TILE>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap smap,
                const float* __restrict__ up, float* __restrict__ out, size_t ld_out, size_t split_stride, int rows, int nblk,
-               int m, int m_pad, int row_tiles16, int blocks_per_split, int* __restrict__ err)
+               int m, int m_pad, int row_tiles16, int blocks_per_split, int gu16, int* __restrict__ err)
 {
+    // gu16 > 0: the matrix is [gate rows | up rows] of gu16 sixteen-row units each, this CTA takes 64 gate rows and the
+    // 64 up rows of the same outputs, and the drain stores silu(gate) * up (rows / 2 a multiple of 64, no K split).
     extern __shared__ uint8_t tc_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int kBStages = tc_b_stages(TY, N_TILE), kBBytes = tc_b_bytes(N_TILE), kActs = N_TILE / kTcLimbs;
@@ -431,7 +433,7 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * kTcRows, rt0 = blockIdx.x * 8, act0 = blockIdx.y * kActs;
-    const int tiles_here = max(0, min(8, row_tiles16 - rt0));
+    const int tiles_here = gu16 > 0 ? 8 : max(0, min(8, row_tiles16 - rt0));
     const int blk0 = blockIdx.z * blocks_per_split, nb = max(0, min(nblk, blk0 + blocks_per_split) - blk0);
 
     if (threadIdx.x == 0) {
@@ -477,9 +479,11 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
                 const int rs = i % kTcRawStages;
                 if (!mbar_wait(&bar->raw_empty[rs], (((uint32_t)i / kTcRawStages) & 1u) ^ 1u)) { fail = 1; break; }
                 mbar_expect_tx(&bar->raw_full[rs], (uint32_t)(tiles_here * kUnit));
-                for (int t = 0; t < tiles_here; t++)
-                    bulk_g2s(raw_stage + rs * kTcRawBytes + t * kUnit, units + ((size_t)(rt0 + t) * nblk + blk0 + i) * kUnit, kUnit,
+                for (int t = 0; t < tiles_here; t++) {
+                    const int rt = gu16 > 0 ? (t < 4 ? 4 * (int)blockIdx.x + t : gu16 + 4 * (int)blockIdx.x + t - 4) : rt0 + t;
+                    bulk_g2s(raw_stage + rs * kTcRawBytes + t * kUnit, units + ((size_t)rt * nblk + blk0 + i) * kUnit, kUnit,
                              &bar->raw_full[rs]);
+                }
             }
         }
     } else if (warp == 2) {
@@ -600,7 +604,28 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar->acc_empty[buf]);
         }
-        if (!fail && wrow < rows) {
+        if (gu16 > 0) {
+            // TMEM lanes 0..63 hold gate rows, 64..127 the up rows of the same outputs: the up half hands its sums over
+            // through shared memory (the operand ring is idle by now: every MMA has completed)
+            float* xch = reinterpret_cast<float*>(a_stage);       // [kActs][64]
+            if (q >= 2 && !fail) {
+#pragma unroll
+                for (int gg = 0; gg < kGroups; gg++)
+#pragma unroll
+                    for (int bb = 0; bb < 8; bb++) xch[(8 * (2 * gg + half) + bb) * 64 + rloc - 64] = acc[8 * gg + bb];
+            }
+            named_bar_sync(1, 32 * kTcDrainWarps);
+            if (q < 2 && !fail) {
+                const size_t col = (size_t)blockIdx.x * 64 + rloc;
+#pragma unroll
+                for (int gg = 0; gg < kGroups; gg++)
+#pragma unroll
+                    for (int bb = 0; bb < 8; bb++) {
+                        const int al = 8 * (2 * gg + half) + bb, act = act0 + al;
+                        if (act < m) out[(size_t)act * ld_out + col] = silu_mul(acc[8 * gg + bb], xch[al * 64 + rloc]);
+                    }
+            }
+        } else if (!fail && wrow < rows) {
             float* o = out + (size_t)blockIdx.z * split_stride;
 #pragma unroll
             for (int gg = 0; gg < kGroups; gg++)
@@ -676,7 +701,7 @@ struct TcPlan {
     int n_tile, splits, blocks_per_split;
     size_t m_pad;                              // activation rows rounded up to whole tiles
     size_t off_sb, off_up, off_part, total;   // scratch offsets (XL at 0)
-    bool needs_finish;
+    bool needs_finish, fused_swiglu;
 };
 
 TcPlan tc_plan(uint32_t ty, const DeviceWeights& w, size_t m, Epilogue epi, int sm_count)
@@ -698,7 +723,8 @@ TcPlan tc_plan(uint32_t ty, const DeviceWeights& w, size_t m, Epilogue epi, int 
     }
     p.blocks_per_split = (int)((w.nblk + splits - 1) / splits);
     p.splits = (int)((w.nblk + p.blocks_per_split - 1) / p.blocks_per_split);
-    p.needs_finish = p.splits > 1 || epi == kEpiSwiglu;
+    p.fused_swiglu = epi == kEpiSwiglu && p.splits == 1 && w.rows % 128 == 0;   // the kernel's own gate / up pairing
+    p.needs_finish = p.splits > 1 || (epi == kEpiSwiglu && !p.fused_swiglu);
     p.m_pad = act_tiles * (size_t)(p.n_tile / kTcLimbs);
     p.off_sb = align256(kTcLimbs * m * w.cols * sizeof(__half));
     p.off_up = p.off_sb + (ty == kGgmlQ4K ? align256(kTcLimbs * m * w.nblk * 64 * sizeof(__half)) : 0);
@@ -722,7 +748,8 @@ int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMa
     dim3 grid((unsigned)((w.rows + kTcRows - 1) / kTcRows), (unsigned)((kTcLimbs * m + N_TILE - 1) / N_TILE), (unsigned)p.splits);
     FERRIC_CUDA_TRY(launch_kernel(gemv_tc_kernel<TY, N_TILE>, grid, dim3(kTcThreads), (size_t)tc_smem_bytes(TY, N_TILE), st, pdl,
                                   (const uint8_t*)w.units, map, smap, up, out, ld_out, split_stride, (int)w.rows, (int)w.nblk,
-                                  (int)m, (int)p.m_pad, (int)w.row_tiles(), p.blocks_per_split, gemm_status_word()));
+                                  (int)m, (int)p.m_pad, (int)w.row_tiles(), p.blocks_per_split,
+                                  p.fused_swiglu ? (int)(w.rows / 32) : 0, gemm_status_word()));
     return kOk;
 }
 }  // namespace

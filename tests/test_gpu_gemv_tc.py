@@ -122,6 +122,27 @@ def test_fused_swiglu_finish(F, ctx):
     assert np.abs(got - ref).max() <= 1e-4 * max(1.0, float(np.abs(ref).max()))
 
 
+@pytest.mark.parametrize("m", [20, 40])
+def test_swiglu_fused_into_the_drain(F, ctx, m):
+    """With enough row tiles to fill the machine K is not cut, and each CTA pairs 64 gate rows with the 64 up rows of the
+    same outputs and applies SwiGLU itself (no finish kernel)."""
+    n_ff, cols = 64 * 150, 512
+    raw = synth.matrix(12, 2 * n_ff, cols, seed=31)
+    x = synth.activations(m, cols, seed=32)
+    qm = F.QMatrix.from_bytes(ctx, raw, 12, 2 * n_ff, cols)
+    xd = torch.from_numpy(x).cuda()
+    before = ctx.launches()
+    got = qm.try_matmul_swiglu(xd).cpu().numpy()
+    assert ctx.launches() - before == 2          # preparation + product
+    assert qm.gemm_status() == 0
+    qm.close()
+    assert got.shape == (m, n_ff)
+    ref = O.swiglu(O.matmul_q(raw, 12, 2 * n_ff, cols, x, threads=NCPU), n_ff)
+    assert np.abs(got - ref).max() <= 1e-4 * max(1.0, float(np.abs(ref).max()))
+    unfused = ctx.swiglu(torch.from_numpy(run(F, ctx, raw, 12, 2 * n_ff, cols, x)).cuda(), n_ff).cpu().numpy()
+    assert np.abs(got - unfused).max() <= 1e-5 * np.abs(unfused).max()
+
+
 def test_scaled_activations_zero_rows_and_outliers(F, ctx):
     """One scale per (activation row, super-block): ranges far outside f16, an all-zero row, an all-zero super-block
     and an outlier that sets its super-block's scale."""
