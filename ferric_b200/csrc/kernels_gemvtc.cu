@@ -54,7 +54,7 @@ constexpr int kTcABytes = kTcRows * 128;   // one operand plane of one K chunk
 __host__ __device__ constexpr int tc_planes(uint32_t ty) { return ty == kGgmlQ6K ? 2 : 1; }
 __host__ __device__ constexpr int tc_unit_bytes(uint32_t ty) { return ty == kGgmlQ6K ? kQ6KUnit : kQ4KUnit; }
 __host__ __device__ constexpr int tc_raw_bytes(uint32_t ty) { return 8 * tc_unit_bytes(ty); }
-constexpr int kTcMaxBStages = 8;
+constexpr int kTcMaxStages = 8;
 
 struct TcRowMeta {
     float d, dmin;
@@ -64,29 +64,30 @@ static_assert(sizeof(TcRowMeta) == 8, "row meta is one 8-byte store");
 __host__ __device__ constexpr int tc_per_block(uint32_t ty) { return ty == kGgmlQ4K ? 5 : 4; }
 
 constexpr int kTcSumFloats = 64;   // per stage: the scales 2^(e-11) of up to 64 activation rows
-__host__ __device__ constexpr int tc_a_stages(uint32_t ty, int) { return ty == kGgmlQ6K ? 3 : 4; }
-__host__ __device__ constexpr int tc_fixed_bytes(uint32_t ty, int n_tile)
-{
-    return 1024 /*align*/ + 512 /*barriers*/ + tc_a_stages(ty, n_tile) * tc_planes(ty) * kTcABytes + kTcRawStages * tc_raw_bytes(ty) +
-           kTcMetaStages * kTcRows * (int)sizeof(TcRowMeta) + 2 * kTcSumFloats * 4;
-}
+// One ring for both operands: a stage holds the A planes of one K chunk (made by the maker warps) and its B tile (the
+// limbs, by TMA), filled under ONE barrier (eight maker arrivals + the producer's expect-tx) and released by ONE
+// tcgen05.commit -- the MMA thread's waits and commits are what paces this kernel.
 __host__ __device__ constexpr int tc_b_bytes(int n_tile) { return n_tile * 128; }
-__host__ __device__ constexpr int tc_b_stages(uint32_t ty, int n_tile)
+__host__ __device__ constexpr int tc_stage_bytes(uint32_t ty, int n_tile) { return tc_planes(ty) * kTcABytes + tc_b_bytes(n_tile); }
+__host__ __device__ constexpr int tc_fixed_bytes(uint32_t ty)
 {
-    return (232448 - tc_fixed_bytes(ty, n_tile)) / tc_b_bytes(n_tile) > kTcMaxBStages
-               ? kTcMaxBStages
-               : (232448 - tc_fixed_bytes(ty, n_tile)) / tc_b_bytes(n_tile);
+    return 1024 /*align*/ + 512 /*barriers*/ + kTcRawStages * tc_raw_bytes(ty) + kTcMetaStages * kTcRows * (int)sizeof(TcRowMeta) +
+           2 * kTcSumFloats * 4;
+}
+__host__ __device__ constexpr int tc_stages(uint32_t ty, int n_tile)
+{
+    return (232448 - tc_fixed_bytes(ty)) / tc_stage_bytes(ty, n_tile) > kTcMaxStages ? kTcMaxStages
+                                                                                      : (232448 - tc_fixed_bytes(ty)) / tc_stage_bytes(ty, n_tile);
 }
 __host__ __device__ constexpr int tc_smem_bytes(uint32_t ty, int n_tile)
 {
-    return tc_fixed_bytes(ty, n_tile) + tc_b_stages(ty, n_tile) * tc_b_bytes(n_tile);
+    return tc_fixed_bytes(ty) + tc_stages(ty, n_tile) * tc_stage_bytes(ty, n_tile);
 }
-static_assert(tc_b_stages(kGgmlQ4K, 128) >= 3 && tc_b_stages(kGgmlQ6K, 128) >= 3, "limb stages at the widest tiles");
+static_assert(tc_stages(kGgmlQ4K, 128) >= 4 && tc_stages(kGgmlQ6K, 128) >= 3, "ring depth at the widest tiles");
 
 struct TcBarriers {
     uint64_t raw_full[kTcRawStages], raw_empty[kTcRawStages];
-    uint64_t a_full[4], a_empty[4];
-    uint64_t b_full[kTcMaxBStages], b_empty[kTcMaxBStages];
+    uint64_t full[kTcMaxStages], empty[kTcMaxStages];
     uint64_t acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     int abort;
@@ -284,7 +285,7 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
             }
             const int c = 5 * i + j, s = c % kTcAStages;
             // (every lane polls: one polling lane plus a shuffle was measured 15 % slower -- the wake-up is on the critical path)
-            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
+            if (!mbar_wait(&bar->empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
             uint8_t* arow = a_stage + s * kTcABytes + arow_off;
 #pragma unroll
             for (int hi = 0; hi < 2; hi++) {
@@ -293,7 +294,7 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar->a_full[s]);   // also publishes this block's row meta (written above)
+            if (lane == 0) mbar_arrive(&bar->full[s]);   // also publishes this block's row meta (written above)
         }
         if (fail) break;
         {   // the min step: A[row][sb] = A[row][8 + sb] = min of sub-block sb (K = 16: columns 0, 1 of the row's eight)
@@ -306,7 +307,7 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
                 mins[hi].w = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][1], 0x64u, 0x4342u)), k1024));
             }
             const int c = 5 * i + 4, s = c % kTcAStages;
-            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
+            if (!mbar_wait(&bar->empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
             if (t < 2) {
                 uint8_t* arow = a_stage + s * kTcABytes + arow_off;
 #pragma unroll
@@ -314,7 +315,7 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar->a_full[s]);
+            if (lane == 0) mbar_arrive(&bar->full[s]);
         }
     }
     return fail;
@@ -392,7 +393,7 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
                 }
             }
             const int c4 = 4 * i + j, s = c4 % A_STAGES;
-            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c4 / A_STAGES) & 1u) ^ 1u)) { fail = 5; break; }
+            if (!mbar_wait(&bar->empty[s], (((uint32_t)c4 / A_STAGES) & 1u) ^ 1u)) { fail = 5; break; }
             uint8_t* arow = a_stage + s * kStageBytes + arow_off;
 #pragma unroll
             for (int hi = 0; hi < 2; hi++)
@@ -404,7 +405,7 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
                 }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar->a_full[s]);
+            if (lane == 0) mbar_arrive(&bar->full[s]);
         }
     }
     return fail;
@@ -420,13 +421,13 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     // 64 up rows of the same outputs, and the drain stores silu(gate) * up (rows / 2 a multiple of 64, no K split).
     extern __shared__ uint8_t tc_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int kBStages = tc_b_stages(TY, N_TILE), kBBytes = tc_b_bytes(N_TILE), kActs = N_TILE / kTcLimbs;
+    constexpr int kStages = tc_stages(TY, N_TILE), kBBytes = tc_b_bytes(N_TILE), kActs = N_TILE / kTcLimbs;
     constexpr int kPer = tc_per_block(TY);   // ring entries per super-block
-    constexpr int kTcAStages = tc_a_stages(TY, N_TILE), kPlanes = tc_planes(TY), kAStageBytes = kPlanes * kTcABytes;
+    constexpr int kPlanes = tc_planes(TY), kAStageBytes = kPlanes * kTcABytes;
     constexpr int kUnit = tc_unit_bytes(TY), kTcRawBytes = tc_raw_bytes(TY);
-    uint8_t* a_stage = smem;                                  // [kTcAStages][kPlanes][16384]
-    uint8_t* b_stage = a_stage + kTcAStages * kAStageBytes;
-    uint8_t* raw_stage = b_stage + kBStages * kBBytes;
+    uint8_t* a_stage = smem;                                  // [kStages][kPlanes][16384]
+    uint8_t* b_stage = a_stage + kStages * kAStageBytes;      // [kStages][N_TILE * 128]
+    uint8_t* raw_stage = b_stage + kStages * kBBytes;
     TcRowMeta* meta = reinterpret_cast<TcRowMeta*>(raw_stage + kTcRawStages * kTcRawBytes);   // [kTcMetaStages][128]
     float* sums = reinterpret_cast<float*>(meta + kTcMetaStages * kTcRows);   // [2][kActs]: staged UP of a super-block
     TcBarriers* bar = reinterpret_cast<TcBarriers*>(sums + 2 * kTcSumFloats);
@@ -441,13 +442,9 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             mbar_init(&bar->raw_full[i], 1);
             mbar_init(&bar->raw_empty[i], kTcMakerWarps);
         }
-        for (int i = 0; i < kTcAStages; i++) {
-            mbar_init(&bar->a_full[i], kTcMakerWarps);
-            mbar_init(&bar->a_empty[i], 1);
-        }
-        for (int i = 0; i < kBStages; i++) {
-            mbar_init(&bar->b_full[i], 1);
-            mbar_init(&bar->b_empty[i], 1);
+        for (int i = 0; i < kStages; i++) {
+            mbar_init(&bar->full[i], kTcMakerWarps + 1);
+            mbar_init(&bar->empty[i], 1);
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(&bar->acc_full[i], 1);
@@ -495,11 +492,11 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             for (int i = 0; i < nb && !fail; i++) {
 #pragma unroll 1
                 for (int j = 0; j < kPer; j++) {
-                    if (!mbar_wait(&bar->b_empty[s], ph ^ 1u)) { fail = 2; break; }
-                    mbar_expect_tx(&bar->b_full[s], (uint32_t)kBBytes);
-                    if (j < 4) tma_load_2d(b_stage + s * kBBytes, &xmap, (4 * (blk0 + i) + j) * kTcChunkK, kTcLimbs * act0, &bar->b_full[s]);
-                    else tma_load_2d(b_stage + s * kBBytes, &smap, (blk0 + i) * kTcChunkK, kTcLimbs * act0, &bar->b_full[s]);
-                    if (++s == (uint32_t)kBStages) { s = 0; ph ^= 1u; }
+                    if (!mbar_wait(&bar->empty[s], ph ^ 1u)) { fail = 2; break; }
+                    mbar_expect_tx(&bar->full[s], (uint32_t)kBBytes);
+                    if (j < 4) tma_load_2d(b_stage + s * kBBytes, &xmap, (4 * (blk0 + i) + j) * kTcChunkK, kTcLimbs * act0, &bar->full[s]);
+                    else tma_load_2d(b_stage + s * kBBytes, &smap, (blk0 + i) * kTcChunkK, kTcLimbs * act0, &bar->full[s]);
+                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -509,10 +506,9 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
         // modulo / division, barrier addresses and descriptor low words advanced by adds.
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_f16(kTcRows, N_TILE);
-            const uint32_t a_full0 = smem_u32(&bar->a_full[0]), a_empty0 = smem_u32(&bar->a_empty[0]);
-            const uint32_t b_full0 = smem_u32(&bar->b_full[0]), b_empty0 = smem_u32(&bar->b_empty[0]);
+            const uint32_t full0 = smem_u32(&bar->full[0]), empty0 = smem_u32(&bar->empty[0]);
             const uint32_t adesc0 = umma_desc_lo(smem_u32(a_stage)), bdesc0 = umma_desc_lo(smem_u32(b_stage));
-            uint32_t sa = 0, pa = 0, sb = 0, pb = 0;     // stage and phase parity of the A and B rings
+            uint32_t sa = 0, pa = 0;     // stage and phase parity of the ring
             for (int i = 0; i < nb && !fail; i++) {
                 const int buf = i & 1;
                 if (!mbar_wait(&bar->acc_empty[buf], (((uint32_t)i >> 1) & 1u) ^ 1u)) { fail = 3; break; }
@@ -520,10 +516,9 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
                 const uint32_t d0 = tmem_acc + (uint32_t)(buf * 2 * N_TILE);
 #pragma unroll
                 for (int j = 0; j < kPer; j++) {
-                    if (!mbar_try(a_full0 + 8 * sa, pa) && !mbar_wait(&bar->a_full[sa], pa)) { fail = 3; break; }
-                    if (!mbar_try(b_full0 + 8 * sb, pb) && !mbar_wait(&bar->b_full[sb], pb)) { fail = 3; break; }
+                    if (!mbar_try(full0 + 8 * sa, pa) && !mbar_wait(&bar->full[sa], pa)) { fail = 3; break; }
                     tc_fence_after();
-                    const uint32_t ad = adesc0 + sa * (uint32_t)(kAStageBytes >> 4), bd = bdesc0 + sb * (uint32_t)(kBBytes >> 4);
+                    const uint32_t ad = adesc0 + sa * (uint32_t)(kAStageBytes >> 4), bd = bdesc0 + sa * (uint32_t)(kBBytes >> 4);
                     if (j < 4) {
 #pragma unroll
                         for (int k4 = 0; k4 < 4; k4++)
@@ -534,10 +529,8 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
                     } else {
                         umma_f16_lo(d0 + N_TILE, ad, bd, idesc, 0u);   // mins x sub-block sums, K = 16
                     }
-                    umma_commit_addr(a_empty0 + 8 * sa);
-                    umma_commit_addr(b_empty0 + 8 * sb);
-                    if (++sa == (uint32_t)kTcAStages) { sa = 0; pa ^= 1u; }
-                    if (++sb == (uint32_t)kBStages) { sb = 0; pb ^= 1u; }
+                    umma_commit_addr(empty0 + 8 * sa);
+                    if (++sa == (uint32_t)kStages) { sa = 0; pa ^= 1u; }
                 }
                 if (!fail) umma_commit(&bar->acc_full[buf]);
             }
@@ -545,8 +538,8 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     } else if (warp < kTcFirstDrain) {
         // ---------------- operand makers (per quant type, above)
         const int wd = warp - kTcFirstMaker;
-        if (TY == kGgmlQ4K) fail = tc_make_q4k<kTcAStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
-        else fail = tc_make_q6k<kTcAStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
+        if (TY == kGgmlQ4K) fail = tc_make_q4k<kStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
+        else fail = tc_make_q6k<kStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
     } else {
         // ---------------- drain: TMEM lane = weight row; columns 2b, 2b + 1 = the hi and lo limb of activation row act0 + b.
         // Two warps share a TMEM lane quarter; warp half h takes the groups of eight activation rows 2g + h.
