@@ -60,8 +60,10 @@ struct TcRowMeta {
     float d, dmin;
 };
 static_assert(sizeof(TcRowMeta) == 8, "row meta is one 8-byte store");
-// ring entries per super-block: four K chunks, and for Q4_K the min step
-__host__ __device__ constexpr int tc_per_block(uint32_t ty) { return ty == kGgmlQ4K ? 5 : 4; }
+// The Q4_K min step has its own operand tiles outside the ring, both in the swizzled 128-byte-row layout of which a K = 16
+// step reads 32 bytes per row: A2 (128 rows; slot i & 3 of its four 32-byte columns holds super-block i's mins) and B2
+// (n_tile rows; slot i & 1).
+__host__ __device__ constexpr int tc_min_bytes(uint32_t ty, int n_tile) { return ty == kGgmlQ4K ? kTcABytes + n_tile * 128 : 0; }
 
 constexpr int kTcSumFloats = 64;   // per stage: the scales 2^(e-11) of up to 64 activation rows
 // One ring for both operands: a stage holds the A planes of one K chunk (made by the maker warps) and its B tile (the
@@ -69,19 +71,20 @@ constexpr int kTcSumFloats = 64;   // per stage: the scales 2^(e-11) of up to 64
 // tcgen05.commit -- the MMA thread's waits and commits are what paces this kernel.
 __host__ __device__ constexpr int tc_b_bytes(int n_tile) { return n_tile * 128; }
 __host__ __device__ constexpr int tc_stage_bytes(uint32_t ty, int n_tile) { return tc_planes(ty) * kTcABytes + tc_b_bytes(n_tile); }
-__host__ __device__ constexpr int tc_fixed_bytes(uint32_t ty)
+__host__ __device__ constexpr int tc_fixed_bytes(uint32_t ty, int n_tile)
 {
-    return 1024 /*align*/ + 512 /*barriers*/ + kTcRawStages * tc_raw_bytes(ty) + kTcMetaStages * kTcRows * (int)sizeof(TcRowMeta) +
-           2 * kTcSumFloats * 4;
+    return 1024 /*align*/ + 512 /*barriers*/ + tc_min_bytes(ty, n_tile) + kTcRawStages * tc_raw_bytes(ty) +
+           kTcMetaStages * kTcRows * (int)sizeof(TcRowMeta) + 2 * kTcSumFloats * 4;
 }
 __host__ __device__ constexpr int tc_stages(uint32_t ty, int n_tile)
 {
-    return (232448 - tc_fixed_bytes(ty)) / tc_stage_bytes(ty, n_tile) > kTcMaxStages ? kTcMaxStages
-                                                                                      : (232448 - tc_fixed_bytes(ty)) / tc_stage_bytes(ty, n_tile);
+    return (232448 - tc_fixed_bytes(ty, n_tile)) / tc_stage_bytes(ty, n_tile) > kTcMaxStages
+               ? kTcMaxStages
+               : (232448 - tc_fixed_bytes(ty, n_tile)) / tc_stage_bytes(ty, n_tile);
 }
 __host__ __device__ constexpr int tc_smem_bytes(uint32_t ty, int n_tile)
 {
-    return tc_fixed_bytes(ty) + tc_stages(ty, n_tile) * tc_stage_bytes(ty, n_tile);
+    return tc_fixed_bytes(ty, n_tile) + tc_stages(ty, n_tile) * tc_stage_bytes(ty, n_tile);
 }
 static_assert(tc_stages(kGgmlQ4K, 128) >= 4 && tc_stages(kGgmlQ6K, 128) >= 3, "ring depth at the widest tiles");
 
@@ -105,10 +108,9 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n)
 // with 2^e > 2 max|x|, so |X| < 2^21, split as X = 2048 hi + lo (lo in [-1024, 1023], |hi| <= 1024: both integers
 // f16 holds exactly).  Outputs:
 //   XL[2 * m][cols]        f16, row 2b = hi, row 2b + 1 = lo of activation row b, in the operand order tc_kpos
-//   SB[2 * m][64 * nblk]   f16 (Q4_K only): what the tensor core needs for the min term -- per super-block 16 values
-//                          per row, [sb] and [8 + sb] = the two pieces (|piece| <= 128, and a multiple of 256 up to
-//                          2^15: both exact) of the sum of that row's limb over sub-block sb; columns 16..63 of each 64
-//                          are never read
+//   SB[nblk][2 * m_pad][16] f16 (Q4_K only): what the tensor core needs for the min term -- per super-block 16 values
+//                          per operand row, [sb] and [8 + sb] = the two pieces (|piece| <= 128, and a multiple of 256
+//                          up to 2^15: both exact) of the sum of that row's limb over sub-block sb
 //   UP[nblk][m_pad]        2^(e-11): V = D_hi + 2^-11 D_lo times UP is the product in x's units
 // One warp per (pair of activation rows, super-block), lanes 0..15 row 0, lanes 16..31 row 1, 16 values each.
 // ------------------------------------------------------------------------------------------
@@ -181,7 +183,7 @@ tc_prep_kernel(const float* __restrict__ x, size_t m, size_t m_pad, size_t ldx, 
 #pragma unroll
         for (int j = 0; j < kTcLimbs; j++) {
             const int s = j ? sum_lo : sum_hi, low = ((s + 128) & 255) - 128;
-            __half* dst = sb + (kTcLimbs * b + j) * (nblk * 64) + blk * 64 + (q >> 1);
+            __half* dst = sb + ((blk * m_pad + b) * kTcLimbs + j) * 16 + (q >> 1);
             dst[0] = __int2half_rn(low);
             dst[8] = __int2half_rn(s - low);
         }
@@ -227,8 +229,8 @@ __device__ __forceinline__ void tc_make16(uint32_t w0, uint32_t w1, __half2 sc_l
 // One call per maker warp.  Warp = one 16-row unit, lane = (row g / g+8, 8-byte piece t), with the prefill kernel's
 // conflict-free lane map.  Returns 0 or the code of the wait that ran out.
 template <int A_STAGES>
-__device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, TcRowMeta* meta, int nb,
-                                           int tiles_here, int wd, int lane)
+__device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, uint8_t* a2_tile, const uint8_t* raw_stage, TcRowMeta* meta,
+                                           int nb, int tiles_here, int wd, int lane)
 {
     constexpr int kTcAStages = A_STAGES;
     int fail = 0;
@@ -263,6 +265,22 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
             mnb[hi][0] = hdr[hi].z & 0x3F3F3F3Fu;
             mnb[hi][1] = ((hdr[hi].w >> 4) & 0x0F0F0F0Fu) | ((hdr[hi].z >> 2) & 0x30303030u);
         }
+        if (t < 2) {
+            // the min step's A operand: A2[row][sb] = A2[row][8 + sb] = min of sub-block sb, in slot i & 3 (16-byte columns
+            // 2 slot + t of the row).  That slot was last read by the min MMA of super-block i - 4, which completed before
+            // any ring stage this warp has since been granted was released.
+            uint8_t* arow = a2_tile + arow_off;
+            const uint32_t col = (uint32_t)(((2 * (i & 3) + t) ^ g) << 4);
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                uint4 mins;
+                mins.x = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][0], 0x64u, 0x4140u)), k1024));   // mins 0, 1
+                mins.y = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][0], 0x64u, 0x4342u)), k1024));   // mins 2, 3
+                mins.z = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][1], 0x64u, 0x4140u)), k1024));
+                mins.w = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][1], 0x64u, 0x4342u)), k1024));
+                *reinterpret_cast<uint4*>(arow + hi * 1024 + col) = mins;
+            }
+        }
         if (t == 0) {   // hand (d, dmin) of this super-block's rows to the drain
 #pragma unroll
             for (int hi = 0; hi < 2; hi++) {
@@ -283,7 +301,7 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
                 const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
                 tc_make16(w0, w1, s0, __hmul2(s0, km1024), s1, __hmul2(s1, km64), lo[hi], up8[hi]);
             }
-            const int c = 5 * i + j, s = c % kTcAStages;
+            const int c = 4 * i + j, s = c % kTcAStages;
             // (every lane polls: one polling lane plus a shuffle was measured 15 % slower -- the wake-up is on the critical path)
             if (!mbar_wait(&bar->empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
             uint8_t* arow = a_stage + s * kTcABytes + arow_off;
@@ -295,27 +313,6 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, co
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar->full[s]);   // also publishes this block's row meta (written above)
-        }
-        if (fail) break;
-        {   // the min step: A[row][sb] = A[row][8 + sb] = min of sub-block sb (K = 16: columns 0, 1 of the row's eight)
-            uint4 mins[2];
-#pragma unroll
-            for (int hi = 0; hi < 2; hi++) {
-                mins[hi].x = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][0], 0x64u, 0x4140u)), k1024));   // mins 0, 1
-                mins[hi].y = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][0], 0x64u, 0x4342u)), k1024));   // mins 2, 3
-                mins[hi].z = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][1], 0x64u, 0x4140u)), k1024));
-                mins[hi].w = tc_u32(__hsub2(tc_h2(__byte_perm(mnb[hi][1], 0x64u, 0x4342u)), k1024));
-            }
-            const int c = 5 * i + 4, s = c % kTcAStages;
-            if (!mbar_wait(&bar->empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
-            if (t < 2) {
-                uint8_t* arow = a_stage + s * kTcABytes + arow_off;
-#pragma unroll
-                for (int hi = 0; hi < 2; hi++) *reinterpret_cast<uint4*>(arow + hi * 1024 + col_lo) = mins[hi];
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar->full[s]);
         }
     }
     return fail;
@@ -413,7 +410,7 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
 
 template <uint32_t TY, int N_TILE>
 __global__ void __launch_bounds__(kTcThreads, 1)
-gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap smap,
+gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtensorMap xmap, const __half* __restrict__ sbsum,
                const float* __restrict__ up, float* __restrict__ out, size_t ld_out, size_t split_stride, int rows, int nblk,
                int m, int m_pad, int row_tiles16, int blocks_per_split, int gu16, int* __restrict__ err)
 {
@@ -422,12 +419,13 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     extern __shared__ uint8_t tc_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int kStages = tc_stages(TY, N_TILE), kBBytes = tc_b_bytes(N_TILE), kActs = N_TILE / kTcLimbs;
-    constexpr int kPer = tc_per_block(TY);   // ring entries per super-block
     constexpr int kPlanes = tc_planes(TY), kAStageBytes = kPlanes * kTcABytes;
     constexpr int kUnit = tc_unit_bytes(TY), kTcRawBytes = tc_raw_bytes(TY);
     uint8_t* a_stage = smem;                                  // [kStages][kPlanes][16384]
     uint8_t* b_stage = a_stage + kStages * kAStageBytes;      // [kStages][N_TILE * 128]
-    uint8_t* raw_stage = b_stage + kStages * kBBytes;
+    uint8_t* a2_tile = b_stage + kStages * kBBytes;           // Q4_K: the min step's operands
+    uint8_t* b2_tile = a2_tile + (TY == kGgmlQ4K ? kTcABytes : 0);
+    uint8_t* raw_stage = a2_tile + tc_min_bytes(TY, N_TILE);
     TcRowMeta* meta = reinterpret_cast<TcRowMeta*>(raw_stage + kTcRawStages * kTcRawBytes);   // [kTcMetaStages][128]
     float* sums = reinterpret_cast<float*>(meta + kTcMetaStages * kTcRows);   // [2][kActs]: staged UP of a super-block
     TcBarriers* bar = reinterpret_cast<TcBarriers*>(sums + 2 * kTcSumFloats);
@@ -484,20 +482,15 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             }
         }
     } else if (warp == 2) {
-        // ---------------- limb producer: [64 k x N_TILE operand rows] f16 per stage; after a super-block's four chunks,
-        // for Q4_K, the tile of its sub-block sums
+        // ---------------- limb producer: [64 k x N_TILE operand rows] f16 per stage
         if (lane == 0) {
             pdl_wait();   // the limbs come from the preparation kernel launched just before
             uint32_t s = 0, ph = 0;
-            for (int i = 0; i < nb && !fail; i++) {
-#pragma unroll 1
-                for (int j = 0; j < kPer; j++) {
-                    if (!mbar_wait(&bar->empty[s], ph ^ 1u)) { fail = 2; break; }
-                    mbar_expect_tx(&bar->full[s], (uint32_t)kBBytes);
-                    if (j < 4) tma_load_2d(b_stage + s * kBBytes, &xmap, (4 * (blk0 + i) + j) * kTcChunkK, kTcLimbs * act0, &bar->full[s]);
-                    else tma_load_2d(b_stage + s * kBBytes, &smap, (blk0 + i) * kTcChunkK, kTcLimbs * act0, &bar->full[s]);
-                    if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
-                }
+            for (int c = 0; c < 4 * nb; c++) {
+                if (!mbar_wait(&bar->empty[s], ph ^ 1u)) { fail = 2; break; }
+                mbar_expect_tx(&bar->full[s], (uint32_t)kBBytes);
+                tma_load_2d(b_stage + s * kBBytes, &xmap, (4 * blk0 + c) * kTcChunkK, kTcLimbs * act0, &bar->full[s]);
+                if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -509,26 +502,27 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             const uint32_t full0 = smem_u32(&bar->full[0]), empty0 = smem_u32(&bar->empty[0]);
             const uint32_t adesc0 = umma_desc_lo(smem_u32(a_stage)), bdesc0 = umma_desc_lo(smem_u32(b_stage));
             uint32_t sa = 0, pa = 0;     // stage and phase parity of the ring
+            const uint32_t a2desc = umma_desc_lo(smem_u32(a2_tile)), b2desc = umma_desc_lo(smem_u32(b2_tile));
             for (int i = 0; i < nb && !fail; i++) {
                 const int buf = i & 1;
-                if (!mbar_wait(&bar->acc_empty[buf], (((uint32_t)i >> 1) & 1u) ^ 1u)) { fail = 3; break; }
+                // (the drain arrives once on both buffers before its loop, after it has staged the first two super-blocks'
+                // sub-block sums: every wait here is a real one)
+                if (!mbar_wait(&bar->acc_empty[buf], ((uint32_t)i >> 1) & 1u)) { fail = 3; break; }
                 tc_fence_after();
                 const uint32_t d0 = tmem_acc + (uint32_t)(buf * 2 * N_TILE);
 #pragma unroll
-                for (int j = 0; j < kPer; j++) {
+                for (int j = 0; j < 4; j++) {
                     if (!mbar_try(full0 + 8 * sa, pa) && !mbar_wait(&bar->full[sa], pa)) { fail = 3; break; }
                     tc_fence_after();
                     const uint32_t ad = adesc0 + sa * (uint32_t)(kAStageBytes >> 4), bd = bdesc0 + sa * (uint32_t)(kBBytes >> 4);
-                    if (j < 4) {
 #pragma unroll
-                        for (int k4 = 0; k4 < 4; k4++)
+                    for (int k4 = 0; k4 < 4; k4++)
 #pragma unroll
-                            for (int pl = 0; pl < kPlanes; pl++)
-                                umma_f16_lo(d0 + pl * N_TILE, ad + (uint32_t)(pl * (kTcABytes >> 4) + 2 * k4), bd + 2 * k4, idesc,
-                                            (j | k4) ? 1u : 0u);
-                    } else {
-                        umma_f16_lo(d0 + N_TILE, ad, bd, idesc, 0u);   // mins x sub-block sums, K = 16
-                    }
+                        for (int pl = 0; pl < kPlanes; pl++)
+                            umma_f16_lo(d0 + pl * N_TILE, ad + (uint32_t)(pl * (kTcABytes >> 4) + 2 * k4), bd + 2 * k4, idesc,
+                                        (j | k4) ? 1u : 0u);
+                    if (TY == kGgmlQ4K && j == 3)   // mins x sub-block sums, K = 16 (operands in place since the first chunk / since acc_empty)
+                        umma_f16_lo(d0 + N_TILE, a2desc + 2 * (uint32_t)(i & 3), b2desc + 2 * (uint32_t)(i & 1), idesc, 0u);
                     umma_commit_addr(empty0 + 8 * sa);
                     if (++sa == (uint32_t)kStages) { sa = 0; pa ^= 1u; }
                 }
@@ -538,7 +532,7 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     } else if (warp < kTcFirstDrain) {
         // ---------------- operand makers (per quant type, above)
         const int wd = warp - kTcFirstMaker;
-        if (TY == kGgmlQ4K) fail = tc_make_q4k<kStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
+        if (TY == kGgmlQ4K) fail = tc_make_q4k<kStages>(bar, a_stage, a2_tile, raw_stage, meta, nb, tiles_here, wd, lane);
         else fail = tc_make_q6k<kStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
     } else {
         // ---------------- drain: TMEM lane = weight row; columns 2b, 2b + 1 = the hi and lo limb of activation row act0 + b.
@@ -557,9 +551,28 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             if (i < nb && dt < kActs) uv = __ldg(up + (size_t)(blk0 + i) * m_pad + act0 + dt);
             return uv;
         };
+        // The min step's B operand: 16 f16 per operand row and super-block (two 16-byte pieces), copied by the drain
+        // threads into slot i & 1 of the B2 tile two super-blocks ahead -- the slot's last reader, the min MMA of
+        // super-block i, has completed when acc_full(i) fires, and the copy is published by this iteration's acc_empty
+        // arrival, which the MMAs of super-block i + 2 wait for.
+        auto stage_b2 = [&](int i) {
+            if (TY != kGgmlQ4K || i >= nb || dt >= 2 * N_TILE) return;
+            const int r = dt >> 1, c = dt & 1;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (kTcLimbs * act0 + r < kTcLimbs * m)
+                val = __ldg(reinterpret_cast<const uint4*>(sbsum + ((size_t)(blk0 + i) * m_pad * kTcLimbs + kTcLimbs * act0 + r) * 16) + c);
+            *reinterpret_cast<uint4*>(b2_tile + r * 128 + (((2 * (i & 1) + c) ^ (r & 7)) << 4)) = val;
+        };
         float uv = fetch(0);
         if (dt < kActs) sums[dt] = uv;
+        stage_b2(0);
+        stage_b2(1);
+        fence_proxy_async();
         named_bar_sync(1, 32 * kTcDrainWarps);
+        if (lane == 0) {
+            mbar_arrive(&bar->acc_empty[0]);
+            mbar_arrive(&bar->acc_empty[1]);
+        }
         const uint32_t lane_base = tmem_acc + ((uint32_t)(32 * q) << 16);
         for (int i = 0; i < nb && !fail; i++) {
             const int buf = i & 1;
@@ -592,6 +605,8 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             // every drain thread has finished reading the other slot (it did so one iteration ago and has met the
             // barrier below since), so the next super-block's values can go there
             if (dt < kActs) sums[((i + 1) & 1) * kTcSumFloats + dt] = uv;
+            stage_b2(i + 2);
+            fence_proxy_async();
             named_bar_sync(1, 32 * kTcDrainWarps);
             tc_fence_before();
             __syncwarp();
@@ -720,14 +735,14 @@ TcPlan tc_plan(uint32_t ty, const DeviceWeights& w, size_t m, Epilogue epi, int 
     p.needs_finish = p.splits > 1 || (epi == kEpiSwiglu && !p.fused_swiglu);
     p.m_pad = act_tiles * (size_t)(p.n_tile / kTcLimbs);
     p.off_sb = align256(kTcLimbs * m * w.cols * sizeof(__half));
-    p.off_up = p.off_sb + (ty == kGgmlQ4K ? align256(kTcLimbs * m * w.nblk * 64 * sizeof(__half)) : 0);
+    p.off_up = p.off_sb + (ty == kGgmlQ4K ? align256(kTcLimbs * p.m_pad * w.nblk * 16 * sizeof(__half)) : 0);
     p.off_part = p.off_up + align256(p.m_pad * w.nblk * sizeof(float));
     p.total = p.off_part + (p.needs_finish ? align256((size_t)p.splits * m * w.rows * sizeof(float)) : 0);
     return p;
 }
 
 template <uint32_t TY, int N_TILE>
-int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const CUtensorMap& smap, const float* up,
+int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMap& map, const __half* sb, const float* up,
                        float* out, size_t ld_out, size_t split_stride, size_t m, const TcPlan& p, bool pdl)
 {
     static bool attr_done[64] = {};
@@ -740,7 +755,7 @@ int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMa
     }
     dim3 grid((unsigned)((w.rows + kTcRows - 1) / kTcRows), (unsigned)((kTcLimbs * m + N_TILE - 1) / N_TILE), (unsigned)p.splits);
     FERRIC_CUDA_TRY(launch_kernel(gemv_tc_kernel<TY, N_TILE>, grid, dim3(kTcThreads), (size_t)tc_smem_bytes(TY, N_TILE), st, pdl,
-                                  (const uint8_t*)w.units, map, smap, up, out, ld_out, split_stride, (int)w.rows, (int)w.nblk,
+                                  (const uint8_t*)w.units, map, sb, up, out, ld_out, split_stride, (int)w.rows, (int)w.nblk,
                                   (int)m, (int)p.m_pad, (int)w.row_tiles(), p.blocks_per_split,
                                   p.fused_swiglu ? (int)(w.rows / 32) : 0, gemm_status_word()));
     return kOk;
@@ -782,7 +797,7 @@ int32_t launch_gemv_tc(cudaStream_t st, uint32_t ty, const DeviceWeights& w, con
     const size_t pairs = (m + 1) / 2, warps = pairs * w.nblk;
     FERRIC_CUDA_TRY(launch_kernel(tc_prep_kernel, dim3((unsigned)((warps + kTcPrepWarps - 1) / kTcPrepWarps)), dim3(32 * kTcPrepWarps),
                                   0, st, tune.pdl, x, m, p.m_pad, ldx, w.nblk, xl, w.cols, sb, up));
-    CUtensorMap map, smap;
+    CUtensorMap map;
     const cuuint32_t box[2] = {(cuuint32_t)kTcChunkK, (cuuint32_t)p.n_tile};
     const cuuint32_t estr[2] = {1, 1};
     {
@@ -795,26 +810,15 @@ int32_t launch_gemv_tc(cudaStream_t st, uint32_t ty, const DeviceWeights& w, con
             return kErrCuda;
         }
     }
-    smap = map;   // Q6_K has no min term and never reads it
-    if (sb != nullptr) {
-        const cuuint64_t dims[2] = {(cuuint64_t)w.nblk * 64, (cuuint64_t)(kTcLimbs * m)};
-        const cuuint64_t strides[1] = {(cuuint64_t)w.nblk * 64 * 2};
-        CUresult r = enc(&smap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, sb, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) {
-            set_last_error("cuTensorMapEncodeTiled (sub-block sums) failed with code %d", (int)r);
-            return kErrCuda;
-        }
-    }
     float* out = p.needs_finish ? part : y;
     const size_t ld_out = p.needs_finish ? w.rows : ldy, split_stride = m * w.rows;
     int32_t rc;
     if (ty == kGgmlQ6K) {
-        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ6K, 64>(st, w, map, smap, up, out, ld_out, split_stride, m, p, tune.pdl);
-        else rc = launch_tc_tile<kGgmlQ6K, 128>(st, w, map, smap, up, out, ld_out, split_stride, m, p, tune.pdl);
+        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ6K, 64>(st, w, map, sb, up, out, ld_out, split_stride, m, p, tune.pdl);
+        else rc = launch_tc_tile<kGgmlQ6K, 128>(st, w, map, sb, up, out, ld_out, split_stride, m, p, tune.pdl);
     } else {
-        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ4K, 64>(st, w, map, smap, up, out, ld_out, split_stride, m, p, tune.pdl);
-        else rc = launch_tc_tile<kGgmlQ4K, 128>(st, w, map, smap, up, out, ld_out, split_stride, m, p, tune.pdl);
+        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ4K, 64>(st, w, map, sb, up, out, ld_out, split_stride, m, p, tune.pdl);
+        else rc = launch_tc_tile<kGgmlQ4K, 128>(st, w, map, sb, up, out, ld_out, split_stride, m, p, tune.pdl);
     }
     if (rc != kOk) return rc;
     *launches += 2;
