@@ -70,7 +70,12 @@ constexpr int kTcSumFloats = 64;   // per stage: the scales 2^(e-11) of up to 64
 // limbs, by TMA), filled under ONE barrier (eight maker arrivals + the producer's expect-tx) and released by ONE
 // tcgen05.commit -- the MMA thread's waits and commits are what paces this kernel.
 __host__ __device__ constexpr int tc_b_bytes(int n_tile) { return n_tile * 128; }
-__host__ __device__ constexpr int tc_stage_bytes(uint32_t ty, int n_tile) { return tc_planes(ty) * kTcABytes + tc_b_bytes(n_tile); }
+// K chunks per ring stage: two (half as many hand-overs) where two such stages fit -- not for Q6_K's two planes at the wide tile
+__host__ __device__ constexpr int tc_chunks(uint32_t ty, int n_tile) { return (ty == kGgmlQ4K || n_tile <= 64) ? 2 : 1; }
+__host__ __device__ constexpr int tc_stage_bytes(uint32_t ty, int n_tile)
+{
+    return tc_chunks(ty, n_tile) * (tc_planes(ty) * kTcABytes + tc_b_bytes(n_tile));
+}
 __host__ __device__ constexpr int tc_fixed_bytes(uint32_t ty, int n_tile)
 {
     return 1024 /*align*/ + 512 /*barriers*/ + tc_min_bytes(ty, n_tile) + kTcRawStages * tc_raw_bytes(ty) +
@@ -86,7 +91,8 @@ __host__ __device__ constexpr int tc_smem_bytes(uint32_t ty, int n_tile)
 {
     return tc_fixed_bytes(ty, n_tile) + tc_stages(ty, n_tile) * tc_stage_bytes(ty, n_tile);
 }
-static_assert(tc_stages(kGgmlQ4K, 128) >= 4 && tc_stages(kGgmlQ6K, 128) >= 3, "ring depth at the widest tiles");
+static_assert(tc_stages(kGgmlQ4K, 128) >= 2 && tc_stages(kGgmlQ4K, 64) >= 2 && tc_stages(kGgmlQ6K, 128) >= 3 && tc_stages(kGgmlQ6K, 64) >= 2,
+              "ring depth");
 
 struct TcBarriers {
     uint64_t raw_full[kTcRawStages], raw_empty[kTcRawStages];
@@ -290,29 +296,34 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, ui
             }
         }
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            uint4 lo[2], up8[2];
+        for (int e = 0; e < 2 && !fail; e++) {       // a ring stage holds two K chunks
+            const int c = 2 * i + e, s = c % kTcAStages;
 #pragma unroll
-            for (int hi = 0; hi < 2; hi++) {
-                // sub-blocks 2j (low nibbles) and 2j + 1 (high nibbles): bytes 2j & 3, (2j + 1) & 3 of scale word j >> 1
-                const __half2 s0 = __hsub2(tc_bcast_byte(scb[hi][j >> 1], (2 * j) & 3), k1024);
-                const __half2 s1 = __hsub2(tc_bcast_byte(scb[hi][j >> 1], (2 * j + 1) & 3), k1024);
-                const uint4 q4 = qs[hi][j >> 1];
-                const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
-                tc_make16(w0, w1, s0, __hmul2(s0, km1024), s1, __hmul2(s1, km64), lo[hi], up8[hi]);
-            }
-            const int c = 4 * i + j, s = c % kTcAStages;
-            // (every lane polls: one polling lane plus a shuffle was measured 15 % slower -- the wake-up is on the critical path)
-            if (!mbar_wait(&bar->empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
-            uint8_t* arow = a_stage + s * kTcABytes + arow_off;
+            for (int cc = 0; cc < 2; cc++) {
+                const int j = 2 * e + cc;
+                uint4 lo[2], up8[2];
 #pragma unroll
-            for (int hi = 0; hi < 2; hi++) {
-                *reinterpret_cast<uint4*>(arow + hi * 1024 + col_lo) = lo[hi];
-                *reinterpret_cast<uint4*>(arow + hi * 1024 + col_hi) = up8[hi];
+                for (int hi = 0; hi < 2; hi++) {
+                    // sub-blocks 2j (low nibbles) and 2j + 1 (high nibbles): bytes 2j & 3, (2j + 1) & 3 of scale word j >> 1
+                    const __half2 s0 = __hsub2(tc_bcast_byte(scb[hi][j >> 1], (2 * j) & 3), k1024);
+                    const __half2 s1 = __hsub2(tc_bcast_byte(scb[hi][j >> 1], (2 * j + 1) & 3), k1024);
+                    const uint4 q4 = qs[hi][j >> 1];
+                    const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
+                    tc_make16(w0, w1, s0, __hmul2(s0, km1024), s1, __hmul2(s1, km64), lo[hi], up8[hi]);
+                }
+                // (every lane polls: one polling lane plus a shuffle was measured 15 % slower -- the wake-up is on the critical path)
+                if (cc == 0 && !mbar_wait(&bar->empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
+                uint8_t* arow = a_stage + (s * 2 + cc) * kTcABytes + arow_off;
+#pragma unroll
+                for (int hi = 0; hi < 2; hi++) {
+                    *reinterpret_cast<uint4*>(arow + hi * 1024 + col_lo) = lo[hi];
+                    *reinterpret_cast<uint4*>(arow + hi * 1024 + col_hi) = up8[hi];
+                }
             }
+            if (fail) break;
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar->full[s]);   // also publishes this block's row meta (written above)
+            if (lane == 0) mbar_arrive(&bar->full[s]);   // also publishes this block's row meta and mins (written above)
         }
     }
     return fail;
@@ -329,11 +340,11 @@ __device__ __forceinline__ void tc_make4_q6(uint32_t q, __half2 sl, __half2 bl, 
 
 // Q6_K (unit layout in layout.h; lane ownership as in the prefill kernel's Q6_K stage): two operand planes per chunk,
 // plane 0 = sl * (q - 32), plane 1 = sh * (q - 32) with sc = 16 sh + sl.  Row meta carries d only.
-template <int A_STAGES>
+template <int A_STAGES, int CH>
 __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, TcRowMeta* meta, int nb,
                                            int tiles_here, int wd, int lane)
 {
-    constexpr int kStageBytes = 2 * kTcABytes;
+    constexpr int kChunkBytes = 2 * kTcABytes;   // both planes of one K chunk
     int fail = 0;
     const int t = lane & 3, qd = lane >> 3, g = ((lane >> 2) & 1) ? (qd ^ 5) : qd;
     const bool unit_ok = wd < tiles_here;
@@ -389,9 +400,10 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
                     }
                 }
             }
-            const int c4 = 4 * i + j, s = c4 % A_STAGES;
-            if (!mbar_wait(&bar->empty[s], (((uint32_t)c4 / A_STAGES) & 1u) ^ 1u)) { fail = 5; break; }
-            uint8_t* arow = a_stage + s * kStageBytes + arow_off;
+            // ring entry of this chunk: CH chunks share a stage; wait for it before its first chunk, hand it over after its last
+            const int c4 = (4 * i + j) / CH, cc = j % CH, s = c4 % A_STAGES;
+            if (cc == 0 && !mbar_wait(&bar->empty[s], (((uint32_t)c4 / A_STAGES) & 1u) ^ 1u)) { fail = 5; break; }
+            uint8_t* arow = a_stage + (s * CH + cc) * kChunkBytes + arow_off;
 #pragma unroll
             for (int hi = 0; hi < 2; hi++)
 #pragma unroll
@@ -400,9 +412,11 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
                     *reinterpret_cast<uint2*>(arow + off) = p0[hi][k];
                     *reinterpret_cast<uint2*>(arow + kTcABytes + off) = p1[hi][k];
                 }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar->full[s]);
+            if (cc == CH - 1) {
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar->full[s]);
+            }
         }
     }
     return fail;
@@ -419,11 +433,11 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     extern __shared__ uint8_t tc_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int kStages = tc_stages(TY, N_TILE), kBBytes = tc_b_bytes(N_TILE), kActs = N_TILE / kTcLimbs;
-    constexpr int kPlanes = tc_planes(TY), kAStageBytes = kPlanes * kTcABytes;
+    constexpr int kCh = tc_chunks(TY, N_TILE), kPlanes = tc_planes(TY), kAStageBytes = kCh * kPlanes * kTcABytes, kBStageBytes = kCh * kBBytes;
     constexpr int kUnit = tc_unit_bytes(TY), kTcRawBytes = tc_raw_bytes(TY);
-    uint8_t* a_stage = smem;                                  // [kStages][kPlanes][16384]
-    uint8_t* b_stage = a_stage + kStages * kAStageBytes;      // [kStages][N_TILE * 128]
-    uint8_t* a2_tile = b_stage + kStages * kBBytes;           // Q4_K: the min step's operands
+    uint8_t* a_stage = smem;                                  // [kStages][kCh][kPlanes][16384]
+    uint8_t* b_stage = a_stage + kStages * kAStageBytes;      // [kStages][kCh][N_TILE * 128]
+    uint8_t* a2_tile = b_stage + kStages * kBStageBytes;      // Q4_K: the min step's operands
     uint8_t* b2_tile = a2_tile + (TY == kGgmlQ4K ? kTcABytes : 0);
     uint8_t* raw_stage = a2_tile + tc_min_bytes(TY, N_TILE);
     TcRowMeta* meta = reinterpret_cast<TcRowMeta*>(raw_stage + kTcRawStages * kTcRawBytes);   // [kTcMetaStages][128]
@@ -486,10 +500,13 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
         if (lane == 0) {
             pdl_wait();   // the limbs come from the preparation kernel launched just before
             uint32_t s = 0, ph = 0;
-            for (int c = 0; c < 4 * nb; c++) {
+            for (int c = 0; c < (4 / kCh) * nb; c++) {
                 if (!mbar_wait(&bar->empty[s], ph ^ 1u)) { fail = 2; break; }
-                mbar_expect_tx(&bar->full[s], (uint32_t)kBBytes);
-                tma_load_2d(b_stage + s * kBBytes, &xmap, (4 * blk0 + c) * kTcChunkK, kTcLimbs * act0, &bar->full[s]);
+                mbar_expect_tx(&bar->full[s], (uint32_t)kBStageBytes);
+#pragma unroll
+                for (int cc = 0; cc < kCh; cc++)
+                    tma_load_2d(b_stage + s * kBStageBytes + cc * kBBytes, &xmap, (4 * blk0 + kCh * c + cc) * kTcChunkK, kTcLimbs * act0,
+                                &bar->full[s]);
                 if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
             }
         }
@@ -511,17 +528,21 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
                 tc_fence_after();
                 const uint32_t d0 = tmem_acc + (uint32_t)(buf * 2 * N_TILE);
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
+                for (int e = 0; e < 4 / kCh; e++) {
                     if (!mbar_try(full0 + 8 * sa, pa) && !mbar_wait(&bar->full[sa], pa)) { fail = 3; break; }
                     tc_fence_after();
-                    const uint32_t ad = adesc0 + sa * (uint32_t)(kAStageBytes >> 4), bd = bdesc0 + sa * (uint32_t)(kBBytes >> 4);
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; k4++)
+                    for (int cc = 0; cc < kCh; cc++) {
+                        const uint32_t ad = adesc0 + (sa * (uint32_t)kCh + cc) * (uint32_t)((kPlanes * kTcABytes) >> 4);
+                        const uint32_t bd = bdesc0 + (sa * (uint32_t)kCh + cc) * (uint32_t)(kBBytes >> 4);
 #pragma unroll
-                        for (int pl = 0; pl < kPlanes; pl++)
-                            umma_f16_lo(d0 + pl * N_TILE, ad + (uint32_t)(pl * (kTcABytes >> 4) + 2 * k4), bd + 2 * k4, idesc,
-                                        (j | k4) ? 1u : 0u);
-                    if (TY == kGgmlQ4K && j == 3)   // mins x sub-block sums, K = 16 (operands in place since the first chunk / since acc_empty)
+                        for (int k4 = 0; k4 < 4; k4++)
+#pragma unroll
+                            for (int pl = 0; pl < kPlanes; pl++)
+                                umma_f16_lo(d0 + pl * N_TILE, ad + (uint32_t)(pl * (kTcABytes >> 4) + 2 * k4), bd + 2 * k4, idesc,
+                                            (e | cc | k4) ? 1u : 0u);
+                    }
+                    if (TY == kGgmlQ4K && e == 4 / kCh - 1)   // mins x sub-block sums, K = 16 (operands in place since the first chunk / since acc_empty)
                         umma_f16_lo(d0 + N_TILE, a2desc + 2 * (uint32_t)(i & 3), b2desc + 2 * (uint32_t)(i & 1), idesc, 0u);
                     umma_commit_addr(empty0 + 8 * sa);
                     if (++sa == (uint32_t)kStages) { sa = 0; pa ^= 1u; }
@@ -533,7 +554,7 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
         // ---------------- operand makers (per quant type, above)
         const int wd = warp - kTcFirstMaker;
         if (TY == kGgmlQ4K) fail = tc_make_q4k<kStages>(bar, a_stage, a2_tile, raw_stage, meta, nb, tiles_here, wd, lane);
-        else fail = tc_make_q6k<kStages>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
+        else fail = tc_make_q6k<kStages, kCh>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
     } else {
         // ---------------- drain: TMEM lane = weight row; columns 2b, 2b + 1 = the hi and lo limb of activation row act0 + b.
         // Two warps share a TMEM lane quarter; warp half h takes the groups of eight activation rows 2g + h.
@@ -765,12 +786,13 @@ int32_t launch_tc_tile(cudaStream_t st, const DeviceWeights& w, const CUtensorMa
 bool gemv_tc_eligible(uint32_t ty, const DeviceWeights& w, size_t m)
 {
     // Measured cross-over with the mma.sync GEMV, which runs in passes of 4 activation rows (us per product, GEMV / this
-    // kernel: gate|up 34816 x 5120 at 12 rows 71 / 82, at 13 rows 91 / 82; down Q6_K 5120 x 17408 58 / 68 and 71 / 70;
-    // q|k|v 24 / 26 and 28 / 26): from 13 rows for both formats.  FERRIC_CUDA_GEMV_TC_MIN_M overrides it; 0 disables the path.
+    // kernel: gate|up 34816 x 5120 at 8 rows 50 / 63, at 9 rows 71 / 63; q|k|v at 9 rows 24 / 22; down Q6_K 5120 x 17408
+    // at 12 rows 59 / 64, at 13 rows 71 / 64): Q4_K from 9 rows, Q6_K from 13.
+    // FERRIC_CUDA_GEMV_TC_MIN_M overrides both; 0 disables the path.
     const char* env = getenv("FERRIC_CUDA_GEMV_TC_MIN_M");   // read per call: tests move the threshold
     const int forced = env ? atoi(env) : -1;
     if (ty != kGgmlQ4K && ty != kGgmlQ6K) return false;
-    const int min_m = forced >= 0 ? forced : 13;
+    const int min_m = forced >= 0 ? forced : (ty == kGgmlQ4K ? 9 : 13);
     return min_m > 0 && m >= (size_t)min_m && m <= 4096 && w.nblk > 0 && w.rows > 0 && w.rows <= (size_t)INT32_MAX / 2;
 }
 

@@ -41,7 +41,7 @@ def ctx(F):
 
 @pytest.fixture(autouse=True)
 def tensor_core_path_from_nine_rows(monkeypatch):
-    """By default this kernel takes over from 13 activation rows; the tests here also run it below that."""
+    """By default this kernel takes over from 9 (Q4_K) or 13 (Q6_K) activation rows; the tests here run both from 9."""
     monkeypatch.setenv("FERRIC_CUDA_GEMV_TC_MIN_M", "9")
 
 
