@@ -122,6 +122,26 @@ def test_fused_swiglu_finish(F, ctx):
     assert np.abs(got - ref).max() <= 1e-4 * max(1.0, float(np.abs(ref).max()))
 
 
+@pytest.mark.parametrize("ty,rows,cols,m", [(12, 256, 5120, 17), (14, 640, 4352, 64), (12, 200, 2048, 33)])
+def test_k_cut_repeats_bit_for_bit(F, ctx, ty, rows, cols, m):
+    """Few row tiles: K is cut across CTAs and a finish kernel adds the pieces in their order -- three launches
+    (preparation, product, finish) and the same bits on every repeat, ragged rows included."""
+    raw = synth.matrix(ty, rows, cols, seed=rows + m)
+    x = synth.activations(m, cols, seed=cols + m)
+    qm = F.QMatrix.from_bytes(ctx, raw, ty, rows, cols)
+    xd = torch.from_numpy(x).cuda()
+    before = ctx.launches()
+    first = qm.matmul(xd).cpu().numpy()
+    assert ctx.launches() - before == 3
+    for _ in range(3):
+        again = qm.matmul(xd).cpu().numpy()
+        assert (again.view(np.uint32) == first.view(np.uint32)).all()
+    assert qm.gemm_status() == 0
+    qm.close()
+    ref = O.matmul_q(raw, ty, rows, cols, x, threads=NCPU)
+    assert_close(first, ref, f"k cut ty{ty} {rows}x{cols} m{m}", exact_product(raw, ty, rows, cols, x))
+
+
 @pytest.mark.parametrize("m", [20, 40])
 def test_swiglu_fused_into_the_drain(F, ctx, m):
     """With enough row tiles to fill the machine K is not cut, and each CTA pairs 64 gate rows with the 64 up rows of the
