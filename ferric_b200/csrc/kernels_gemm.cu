@@ -72,10 +72,24 @@ __host__ __device__ constexpr int gemm_b_stages(uint32_t ty, int n_tile, bool pa
                ? kGemmMaxBStages
                : (kGemmSmemMax - gemm_fixed_bytes(ty)) / gemm_b_bytes(n_tile, pair);
 }
+// The narrow tile (at most 128 activation rows, where a K chunk's four MMAs are short and the MMA thread's barrier
+// waits and commits -- about a hundred cycles each -- pace the kernel) runs ONE ring for both operands with two K chunks
+// per stage: a stage is filled under one barrier (the dequant warps' arrivals + the activation producer's expect-tx)
+// and released by one tcgen05.commit, a quarter of the hand-overs of the two-ring form.
+__host__ __device__ constexpr bool gemm_merged(int n_tile, bool pair) { return n_tile == 128 && !pair; }
+constexpr int kGemmMergedChunks = 2, kGemmMergedStages = 2;
 __host__ __device__ constexpr int gemm_smem_bytes(uint32_t ty, int n_tile, bool pair)
 {
-    return gemm_fixed_bytes(ty) + gemm_b_stages(ty, n_tile, pair) * gemm_b_bytes(n_tile, pair);
+    return gemm_merged(n_tile, pair)
+               ? 1024 + 256 + kGemmRawStages * gemm_raw_bytes(ty) +
+                     kGemmMergedStages * kGemmMergedChunks * (kGemmABytes + gemm_b_bytes(n_tile, pair))
+               : gemm_fixed_bytes(ty) + gemm_b_stages(ty, n_tile, pair) * gemm_b_bytes(n_tile, pair);
 }
+static_assert(gemm_smem_bytes(kGgmlQ4K, 128, false) <= kGemmSmemMax && gemm_smem_bytes(kGgmlQ5K, 128, false) <= kGemmSmemMax &&
+                  gemm_smem_bytes(kGgmlQ6K, 128, false) <= kGemmSmemMax && gemm_smem_bytes(kGgmlQ8_0, 128, false) <= kGemmSmemMax,
+              "the merged ring fits");
+static_assert(kGemmMergedStages <= kGemmStages, "barrier slots");
+static_assert(kGemmMergedStages * kGemmMergedChunks * gemm_b_bytes(128) >= 4 * 32 * 128 * 4, "store staging fits the merged ring");
 static_assert(gemm_b_stages(kGgmlQ4K, 128, false) == 8 && gemm_b_stages(kGgmlQ4K, 256, false) == 4 &&
                   gemm_b_stages(kGgmlQ4K, 512, false) == 2 && gemm_b_stages(kGgmlQ4K, 512, true) == 4,
               "Q4_K stage counts");
@@ -140,11 +154,29 @@ __device__ __forceinline__ uint4 deq8(uint32_t w0, uint32_t w1, float d1, float 
     return o;
 }
 
+// Where K chunk j of super-block b goes in a ring of S stages of CH chunks: the stage, its wait parity, whether this
+// chunk opens the stage (wait for it to be free) or closes it (announce it), and the chunk's A tile inside it.
+template <int S, int CH>
+struct GemmRingPos {
+    int s, cc;
+    uint32_t parity;
+    __device__ __forceinline__ GemmRingPos(int b, int j)
+    {
+        const int e = (4 * b + j) / CH;
+        cc = j % CH;
+        s = e % S;
+        parity = (((uint32_t)e / S) & 1u) ^ 1u;
+    }
+    __device__ __forceinline__ bool opens() const { return cc == 0; }
+    __device__ __forceinline__ bool closes() const { return cc == CH - 1; }
+    __device__ __forceinline__ uint32_t a_off() const { return (uint32_t)((s * CH + cc) * kGemmABytes); }
+};
+
 // ---------------------------------------------------------------- dequant stages
 // One call per dequant warp: for every super-block, wait for its raw units, pull this warp's 16-row unit into
 // registers, and for each of its four K chunks convert 16 rows x 64 weights to bf16, wait for a free A stage,
 // store, and announce it.  Returns 0, or the code of the wait that ran out.
-template <bool PAIR, bool Q5>
+template <bool PAIR, bool Q5, int S, int CH>
 __device__ __forceinline__ int dequant_loop_q4k(GemmBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, int nblk,
                                                 int tiles_here, int wq, int lane)
 {
@@ -216,19 +248,22 @@ __device__ __forceinline__ int dequant_loop_q4k(GemmBarriers* bar, uint8_t* a_st
                 lo[hh] = deq8(l0, l1, d1a, mma);
                 up[hh] = deq8(u0, u1, d1b, mmb);
             }
-            const int c = 4 * b + j, s = c % kGemmStages;
-            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
-            uint8_t* arow = a_stage + s * kGemmABytes + arow_off;
+            const GemmRingPos<S, CH> pos(b, j);
+            const int s = pos.s;
+            if (pos.opens() && !mbar_wait(&bar->a_empty[s], pos.parity)) { fail = 5; break; }
+            uint8_t* arow = a_stage + pos.a_off() + arow_off;
 #pragma unroll
             for (int hh = 0; hh < kGemmHalves; hh++) {
                 *reinterpret_cast<uint4*>(arow + hh * 1024 + col_lo) = lo[hh];
                 *reinterpret_cast<uint4*>(arow + hh * 1024 + col_hi) = up[hh];
             }
-            fence_proxy_async();     // generic-proxy stores -> visible to the tensor core's async reads
-            __syncwarp();
-            if (lane == 0) {
-                if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
-                else mbar_arrive(&bar->a_full[s]);
+            if (pos.closes()) {
+                fence_proxy_async();     // generic-proxy stores -> visible to the tensor core's async reads
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
+                    else mbar_arrive(&bar->a_full[s]);
+                }
             }
         }
     }
@@ -260,7 +295,7 @@ __device__ __forceinline__ uint2 deq4_q6(uint32_t q, float t)
 // Lane (g, t) holds, per row, ql words (c, h, is) = raw ql bytes [64h + 32c + 16is + 4t, +4) and qh words
 // (h, is) = raw qh bytes [32h + 16is + 4t, +4).  K chunk j = (h, kp) = (j >> 1, j & 1) takes sub-blocks
 // k = 2kp + c: nibble kp of the ql word, bits 2k..2k+1 of the qh word, chunk-local position 32c + 16is + 4t.
-template <bool PAIR>
+template <bool PAIR, int S, int CH>
 __device__ __forceinline__ int dequant_loop_q6k(GemmBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, int nblk,
                                                 int tiles_here, int wq, int lane)
 {
@@ -317,19 +352,22 @@ __device__ __forceinline__ int dequant_loop_q6k(GemmBarriers* bar, uint8_t* a_st
                     }
                 }
             }
-            const int c4 = 4 * b + j, s = c4 % kGemmStages;
-            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c4 / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
-            uint8_t* arow = a_stage + s * kGemmABytes + arow_off;
+            const GemmRingPos<S, CH> pos(b, j);
+            const int s = pos.s;
+            if (pos.opens() && !mbar_wait(&bar->a_empty[s], pos.parity)) { fail = 5; break; }
+            uint8_t* arow = a_stage + pos.a_off() + arow_off;
 #pragma unroll
             for (int hi = 0; hi < 2; hi++)
 #pragma unroll
                 for (int i = 0; i < 4; i++)   // i = 2c + is: 16-byte column 2i + (t >> 1), half t & 1
                     *reinterpret_cast<uint2*>(arow + hi * 1024 + (((2 * i + (t >> 1)) ^ g) << 4) + 8 * (t & 1)) = out[hi][i];
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
-                if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
-                else mbar_arrive(&bar->a_full[s]);
+            if (pos.closes()) {
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
+                    else mbar_arrive(&bar->a_full[s]);
+                }
             }
         }
     }
@@ -338,7 +376,7 @@ __device__ __forceinline__ int dequant_loop_q6k(GemmBarriers* bar, uint8_t* a_st
 
 // Q8_0 (crates/ferric-gguf/src/lib.rs:608-615: out = q * d): a stage holds [128 rows][256] int8 and [128][8] f16
 // scales.  Thread = (row, 32-value block of the K chunk); q * d is exact in f32 (8 x 11 bits), then rounded to bf16.
-template <bool PAIR>
+template <bool PAIR, int S, int CH>
 __device__ __forceinline__ int dequant_loop_q8_0(GemmBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, int nb, int wq,
                                                  int lane)
 {
@@ -384,16 +422,19 @@ __device__ __forceinline__ int dequant_loop_q8_0(GemmBarriers* bar, uint8_t* a_s
                 };
                 out[i] = make_uint4(two(w0, 0), two(w0, 2), two(w1, 0), two(w1, 2));
             }
-            const int c = 4 * b + j, s = c % kGemmStages;
-            if (!mbar_wait(&bar->a_empty[s], (((uint32_t)c / kGemmStages) & 1u) ^ 1u)) { fail = 5; break; }
-            uint8_t* arow = a_stage + s * kGemmABytes + arow_off;
+            const GemmRingPos<S, CH> pos(b, j);
+            const int s = pos.s;
+            if (pos.opens() && !mbar_wait(&bar->a_empty[s], pos.parity)) { fail = 5; break; }
+            uint8_t* arow = a_stage + pos.a_off() + arow_off;
 #pragma unroll
             for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(arow + (((4 * half + i) ^ (r & 7)) << 4)) = out[i];
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
-                if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
-                else mbar_arrive(&bar->a_full[s]);
+            if (pos.closes()) {
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(cluster_addr(&bar->a_full[s], 0));
+                    else mbar_arrive(&bar->a_full[s]);
+                }
             }
         }
     }
@@ -421,13 +462,16 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
 {
     extern __shared__ uint8_t gemm_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* a_stage = smem;                                               // [S][16384]
-    constexpr int kBStages = gemm_b_stages(TY, N_TILE, PAIR), kBBytes = gemm_b_bytes(N_TILE, PAIR);
+    uint8_t* a_stage = smem;                                               // [S][CH][16384]
+    constexpr bool kMerged = gemm_merged(N_TILE, PAIR);                    // one ring, two chunks per stage (see above)
+    constexpr int kAStages = kMerged ? kGemmMergedStages : kGemmStages, kCh = kMerged ? kGemmMergedChunks : 1;
+    constexpr int kBBytes = gemm_b_bytes(N_TILE, PAIR);
+    constexpr int kBStages = kMerged ? kGemmMergedStages * kGemmMergedChunks : gemm_b_stages(TY, N_TILE, PAIR);   // B tiles held
     constexpr int kUnit = gemm_unit_bytes(TY), kRawBytes = gemm_raw_bytes(TY);
     constexpr int kNMma = N_TILE > 256 ? 256 : N_TILE;                     // activation rows per tcgen05.mma
     constexpr int kBoxRows = PAIR ? kNMma / 2 : kNMma;                     // of them, rows this CTA holds
     constexpr int kPeers = PAIR ? 2 : 1;
-    uint8_t* b_stage = a_stage + kGemmStages * kGemmABytes;                // [kBStages][kBBytes]
+    uint8_t* b_stage = a_stage + kAStages * kCh * kGemmABytes;             // [kBStages][kBBytes]
     uint8_t* raw_stage = b_stage + kBStages * kBBytes;                     // [2][18432]
     GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(raw_stage + kGemmRawStages * kRawBytes);
 
@@ -458,8 +502,8 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
             mbar_init(&bar->raw_full[i], 1);
             mbar_init(&bar->raw_empty[i], kGemmDeqWarps);
         }
-        for (int i = 0; i < kGemmStages; i++) {
-            mbar_init(&bar->a_full[i], kGemmDeqWarps * kPeers);   // in a pair only the leader's is used
+        for (int i = 0; i < kAStages; i++) {
+            mbar_init(&bar->a_full[i], kGemmDeqWarps * kPeers + (kMerged ? 1 : 0));   // in a pair only the leader's is used
             mbar_init(&bar->a_empty[i], 1);
         }
         for (int i = 0; i < kBStages; i++) {
@@ -510,7 +554,16 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
         }
     } else if (warp == 2) {
         // ---------------- activation producer: one [64 k x N_TILE rows] bf16 tile per stage
-        if (lane == 0) {
+        if (lane == 0 && kMerged) {
+            for (int e = 0; e < nchunks / kCh; e++) {
+                const int s = e % kAStages;
+                if (!mbar_wait(&bar->a_empty[s], (((uint32_t)e / kAStages) & 1u) ^ 1u)) { fail = 2; break; }
+                mbar_expect_tx(&bar->a_full[s], (uint32_t)(kCh * kBBytes));
+#pragma unroll
+                for (int cc = 0; cc < kCh; cc++)
+                    tma_load_2d(b_stage + (s * kCh + cc) * kBBytes, &xmap, (kCh * e + cc) * kGemmChunkK, n0, &bar->a_full[s]);
+            }
+        } else if (lane == 0) {
             for (int c = 0; c < nchunks; c++) {
                 const int s = c % kBStages;
                 if (!mbar_wait(&bar->b_empty[s], (((uint32_t)c / kBStages) & 1u) ^ 1u)) { fail = 2; break; }
@@ -532,7 +585,23 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer
-        if (lane == 0 && rank == 0) {
+        if (lane == 0 && kMerged) {
+            constexpr uint32_t idesc = umma_idesc_bf16(kGemmRows, kNMma);
+            for (int e = 0; e < nchunks / kCh; e++) {
+                const int s = e % kAStages;
+                if (!mbar_wait(&bar->a_full[s], ((uint32_t)e / kAStages) & 1u)) { fail = 3; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int cc = 0; cc < kCh; cc++) {
+                    const uint32_t a0 = smem_u32(a_stage + (s * kCh + cc) * kGemmABytes), b0 = smem_u32(b_stage + (s * kCh + cc) * kBBytes);
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; k4++)
+                        umma_bf16(tmem_acc, umma_desc_sw128(a0 + 32 * k4), umma_desc_sw128(b0 + 32 * k4), idesc, (e | cc | k4) ? 1u : 0u);
+                }
+                umma_commit(&bar->a_empty[s]);   // frees the stage once the MMAs above have read it
+            }
+            if (!fail) umma_commit(&bar->acc_full);
+        } else if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(kGemmRows * kPeers, kNMma);
             for (int c = 0; c < nchunks; c++) {
                 const int sa = c % kGemmStages, sb = c % kBStages;
@@ -565,10 +634,10 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
     } else {
         // ---------------- dequantise (per quant type, above), then the epilogue
         const int wq = warp - kGemmFirstDeqWarp;
-        if (TY == kGgmlQ4K) fail = dequant_loop_q4k<PAIR, false>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
-        else if (TY == kGgmlQ5K) fail = dequant_loop_q4k<PAIR, true>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
-        else if (TY == kGgmlQ6K) fail = dequant_loop_q6k<PAIR>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
-        else fail = dequant_loop_q8_0<PAIR>(bar, a_stage, raw_stage, nb, wq, lane);
+        if (TY == kGgmlQ4K) fail = dequant_loop_q4k<PAIR, false, kAStages, kCh>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
+        else if (TY == kGgmlQ5K) fail = dequant_loop_q4k<PAIR, true, kAStages, kCh>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
+        else if (TY == kGgmlQ6K) fail = dequant_loop_q6k<PAIR, kAStages, kCh>(bar, a_stage, raw_stage, nb, tiles_here, wq, lane);
+        else fail = dequant_loop_q8_0<PAIR, kAStages, kCh>(bar, a_stage, raw_stage, nb, wq, lane);
         // ---------------- epilogue.  All dequant warps first agree that nobody gave up (the staged path below
         // synchronises them with named barriers, which must not be entered by only some of them).
         if (fail) atomicExch(&bar->abort, fail);
