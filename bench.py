@@ -397,6 +397,8 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_extras:
         with ClockSampler(local) as extra_clocks:
             extras = per_matrix_table(torch, ctx, stack, QMatrix, B, peak)
+            if B == 1 and stack.plan.world == 1:      # the same four products at 64 activation rows
+                extras.update(per_matrix_table(torch, ctx, stack, QMatrix, 64, peak, suffix="_m64"))
             extras.update(other_configs(torch, ctx, QMatrix, peak))
             extras["prefill_q4k_bf16_34816x5120"] = {f"m{m}": prefill_case(torch, ctx, QMatrix, stack.layers[0].wgu, m, 9)
                                                      for m in (128, 512, 2048)}
@@ -576,15 +578,24 @@ def graph_time_us(torch, ctx, fn, reps=9):
     return statistics.median(e0.elapsed_time(e1) for e0, e1 in evs) * 1e3
 
 
-def per_matrix_table(torch, ctx, stack, QMatrix, B, peak):
-    """GB/s of each product of the layer (prepare + GEMV), cold: cycling over all layers' copies."""
+def per_matrix_table(torch, ctx, stack, QMatrix, B, peak, suffix=""):
+    """GB/s of each product of the layer (prepare + product), cold: cycling over all layers' copies.  With a suffix the
+    table is taken at that many activation rows on buffers of its own (the tensor-core decode kernel's range)."""
     out = {}
     p = stack.plan
-    xh = torch.randn((B, p.hidden), device=stack.h.device)
-    xf = torch.randn((B, p.ff_rows), device=stack.h.device)
-    cases = [("qkv_q4k_7168x5120", "wqkv", xh, stack.qkv), ("o_q4k_5120x5120", "wo", stack.qkv[:, :p.q_rows], stack.o),
-             ("gate_up_swiglu_q4k_34816x5120", "wgu", xh, stack.f), ("down_q6k_5120x17408", "wdown", xf, stack.d)]
+    dev = stack.h.device
+    xh = torch.randn((B, p.hidden), device=dev)
+    xf = torch.randn((B, p.ff_rows), device=dev)
+    if suffix:
+        qkv, o = torch.empty((B, stack.qkv.shape[1]), device=dev), torch.empty((B, stack.o.shape[1]), device=dev)
+        f, d = torch.empty((B, stack.f.shape[1]), device=dev), torch.empty((B, stack.d.shape[1]), device=dev)
+        ctx.reserve_scratch(max(getattr(stack.layers[0], a).scratch_bytes(B) for a in ("wqkv", "wo", "wgu", "wdown")))
+    else:
+        qkv, o, f, d = stack.qkv, stack.o, stack.f, stack.d
+    cases = [("qkv_q4k_7168x5120", "wqkv", xh, qkv), ("o_q4k_5120x5120", "wo", qkv[:, :p.q_rows], o),
+             ("gate_up_swiglu_q4k_34816x5120", "wgu", xh, f), ("down_q6k_5120x17408", "wdown", xf, d)]
     for name, attr, x, y in cases:
+        name += suffix
         def once():
             for L in stack.layers:
                 w = getattr(L, attr)

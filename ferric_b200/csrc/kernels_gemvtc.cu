@@ -62,7 +62,7 @@ struct TcRowMeta {
 static_assert(sizeof(TcRowMeta) == 8, "row meta is one 8-byte store");
 // The Q4_K min step has its own operand tiles outside the ring, both in the swizzled 128-byte-row layout of which a K = 16
 // step reads 32 bytes per row: A2 (128 rows; slot i & 3 of its four 32-byte columns holds super-block i's mins) and B2
-// (n_tile rows; slot i & 1).
+// (n_tile rows; slot i mod the number of accumulator sets).
 __host__ __device__ constexpr int tc_min_bytes(uint32_t ty, int n_tile) { return ty == kGgmlQ4K ? kTcABytes + n_tile * 128 : 0; }
 
 constexpr int kTcSumFloats = 64;   // per stage: the scales 2^(e-11) of up to 64 activation rows
@@ -97,7 +97,7 @@ static_assert(tc_stages(kGgmlQ4K, 128) >= 2 && tc_stages(kGgmlQ4K, 64) >= 2 && t
 struct TcBarriers {
     uint64_t raw_full[kTcRawStages], raw_empty[kTcRawStages];
     uint64_t full[kTcMaxStages], empty[kTcMaxStages];
-    uint64_t acc_full[2], acc_empty[2];
+    uint64_t acc_full[4], acc_empty[4];
     uint32_t tmem_base;
     int abort;
 };
@@ -433,6 +433,9 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     extern __shared__ uint8_t tc_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int kStages = tc_stages(TY, N_TILE), kBBytes = tc_b_bytes(N_TILE), kActs = N_TILE / kTcLimbs;
+    // accumulator sets in tensor memory (each two accumulators wide): as many as its 512 columns hold, so that at the
+    // narrow tile the MMAs run up to four super-blocks ahead of the drain
+    constexpr int kAcc = 256 / N_TILE;
     constexpr int kCh = tc_chunks(TY, N_TILE), kPlanes = tc_planes(TY), kAStageBytes = kCh * kPlanes * kTcABytes, kBStageBytes = kCh * kBBytes;
     constexpr int kUnit = tc_unit_bytes(TY), kTcRawBytes = tc_raw_bytes(TY);
     uint8_t* a_stage = smem;                                  // [kStages][kCh][kPlanes][16384]
@@ -458,15 +461,15 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             mbar_init(&bar->full[i], kTcMakerWarps + 1);
             mbar_init(&bar->empty[i], 1);
         }
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < kAcc; i++) {
             mbar_init(&bar->acc_full[i], 1);
             mbar_init(&bar->acc_empty[i], kTcDrainWarps);
         }
         bar->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // two sets of two accumulators (Q4_K: product and min term; Q6_K: one per operand plane); a power of two >= 128
-    constexpr int kTmemCols = 2 * 2 * N_TILE;
+    // kAcc sets of two accumulators (Q4_K: product and min term; Q6_K: one per operand plane); a power of two >= 128
+    constexpr int kTmemCols = kAcc * 2 * N_TILE;
     static_assert(kTmemCols <= 512, "tensor memory holds 512 columns");
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
@@ -521,10 +524,10 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             uint32_t sa = 0, pa = 0;     // stage and phase parity of the ring
             const uint32_t a2desc = umma_desc_lo(smem_u32(a2_tile)), b2desc = umma_desc_lo(smem_u32(b2_tile));
             for (int i = 0; i < nb && !fail; i++) {
-                const int buf = i & 1;
-                // (the drain arrives once on both buffers before its loop, after it has staged the first two super-blocks'
+                const int buf = i % kAcc;
+                // (the drain arrives once on every set before its loop, after it has staged the first super-blocks'
                 // sub-block sums: every wait here is a real one)
-                if (!mbar_wait(&bar->acc_empty[buf], ((uint32_t)i >> 1) & 1u)) { fail = 3; break; }
+                if (!mbar_wait(&bar->acc_empty[buf], ((uint32_t)i / kAcc) & 1u)) { fail = 3; break; }
                 tc_fence_after();
                 const uint32_t d0 = tmem_acc + (uint32_t)(buf * 2 * N_TILE);
 #pragma unroll
@@ -543,7 +546,7 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
                                             (e | cc | k4) ? 1u : 0u);
                     }
                     if (TY == kGgmlQ4K && e == 4 / kCh - 1)   // mins x sub-block sums, K = 16 (operands in place since the first chunk / since acc_empty)
-                        umma_f16_lo(d0 + N_TILE, a2desc + 2 * (uint32_t)(i & 3), b2desc + 2 * (uint32_t)(i & 1), idesc, 0u);
+                        umma_f16_lo(d0 + N_TILE, a2desc + 2 * (uint32_t)(i & 3), b2desc + 2 * (uint32_t)(i % kAcc), idesc, 0u);
                     umma_commit_addr(empty0 + 8 * sa);
                     if (++sa == (uint32_t)kStages) { sa = 0; pa ^= 1u; }
                 }
@@ -573,32 +576,37 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             return uv;
         };
         // The min step's B operand: 16 f16 per operand row and super-block (two 16-byte pieces), copied by the drain
-        // threads into slot i & 1 of the B2 tile two super-blocks ahead -- the slot's last reader, the min MMA of
+        // threads into slot i mod kAcc of the B2 tile kAcc super-blocks ahead -- the slot's last reader, the min MMA of
         // super-block i, has completed when acc_full(i) fires, and the copy is published by this iteration's acc_empty
-        // arrival, which the MMAs of super-block i + 2 wait for.
-        auto stage_b2 = [&](int i) {
+        // arrival, which the MMAs of super-block i + kAcc wait for.
+        auto load_b2 = [&](int i) {
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (TY == kGgmlQ4K && i < nb && dt < 2 * N_TILE && kTcLimbs * act0 + (dt >> 1) < kTcLimbs * m)
+                val = __ldg(reinterpret_cast<const uint4*>(sbsum + ((size_t)(blk0 + i) * m_pad * kTcLimbs + kTcLimbs * act0 + (dt >> 1)) * 16) +
+                            (dt & 1));
+            return val;
+        };
+        auto store_b2 = [&](int i, const uint4& val) {
             if (TY != kGgmlQ4K || i >= nb || dt >= 2 * N_TILE) return;
             const int r = dt >> 1, c = dt & 1;
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (kTcLimbs * act0 + r < kTcLimbs * m)
-                val = __ldg(reinterpret_cast<const uint4*>(sbsum + ((size_t)(blk0 + i) * m_pad * kTcLimbs + kTcLimbs * act0 + r) * 16) + c);
-            *reinterpret_cast<uint4*>(b2_tile + r * 128 + (((2 * (i & 1) + c) ^ (r & 7)) << 4)) = val;
+            *reinterpret_cast<uint4*>(b2_tile + r * 128 + (((2 * (i % kAcc) + c) ^ (r & 7)) << 4)) = val;
         };
         float uv = fetch(0);
         if (dt < kActs) sums[dt] = uv;
-        stage_b2(0);
-        stage_b2(1);
+#pragma unroll
+        for (int i = 0; i < kAcc; i++) store_b2(i, load_b2(i));
         fence_proxy_async();
         named_bar_sync(1, 32 * kTcDrainWarps);
         if (lane == 0) {
-            mbar_arrive(&bar->acc_empty[0]);
-            mbar_arrive(&bar->acc_empty[1]);
+#pragma unroll
+            for (int i = 0; i < kAcc; i++) mbar_arrive(&bar->acc_empty[i]);
         }
         const uint32_t lane_base = tmem_acc + ((uint32_t)(32 * q) << 16);
         for (int i = 0; i < nb && !fail; i++) {
-            const int buf = i & 1;
+            const int buf = i % kAcc;
             uv = fetch(i + 1);
-            if (!mbar_wait(&bar->acc_full[buf], ((uint32_t)i >> 1) & 1u)) { fail = 6; break; }
+            const uint4 b2v = load_b2(i + kAcc);   // in flight under the wait and the accumulator reads below
+            if (!mbar_wait(&bar->acc_full[buf], ((uint32_t)i / kAcc) & 1u)) { fail = 6; break; }
             tc_fence_after();
             const TcRowMeta rm = meta[(i % kTcMetaStages) * kTcRows + rloc];
             const float* sl = sums + (i & 1) * kTcSumFloats;
@@ -626,7 +634,7 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             // every drain thread has finished reading the other slot (it did so one iteration ago and has met the
             // barrier below since), so the next super-block's values can go there
             if (dt < kActs) sums[((i + 1) & 1) * kTcSumFloats + dt] = uv;
-            stage_b2(i + 2);
+            store_b2(i + kAcc, b2v);
             fence_proxy_async();
             named_bar_sync(1, 32 * kTcDrainWarps);
             tc_fence_before();
