@@ -76,20 +76,33 @@ __host__ __device__ constexpr int gemm_b_stages(uint32_t ty, int n_tile, bool pa
 // waits and commits -- about a hundred cycles each -- pace the kernel) runs ONE ring for both operands with two K chunks
 // per stage: a stage is filled under one barrier (the dequant warps' arrivals + the activation producer's expect-tx)
 // and released by one tcgen05.commit, a quarter of the hand-overs of the two-ring form.
-__host__ __device__ constexpr bool gemm_merged(int n_tile, bool pair) { return n_tile == 128 && !pair; }
-constexpr int kGemmMergedChunks = 2, kGemmMergedStages = 2;
+// The paired 512-wide tile runs one ring too (one chunk per stage, three stages): its eight MMAs per chunk keep the tensor
+// pipe busy for about as long as the issuing thread needs for them plus four waits / commits, so halving those leaves slack.
+__host__ __device__ constexpr bool gemm_merged(int n_tile, bool pair)
+{
+    return (n_tile == 128 && !pair) || (n_tile == 256 && !pair) || (n_tile == 512 && pair);
+}
+__host__ __device__ constexpr int gemm_merged_chunks(int n_tile) { return n_tile == 128 ? 2 : 1; }
+__host__ __device__ constexpr int gemm_merged_stages(int n_tile) { return n_tile == 128 ? 2 : 3; }
 __host__ __device__ constexpr int gemm_smem_bytes(uint32_t ty, int n_tile, bool pair)
 {
     return gemm_merged(n_tile, pair)
                ? 1024 + 256 + kGemmRawStages * gemm_raw_bytes(ty) +
-                     kGemmMergedStages * kGemmMergedChunks * (kGemmABytes + gemm_b_bytes(n_tile, pair))
+                     gemm_merged_stages(n_tile) * gemm_merged_chunks(n_tile) * (kGemmABytes + gemm_b_bytes(n_tile, pair))
                : gemm_fixed_bytes(ty) + gemm_b_stages(ty, n_tile, pair) * gemm_b_bytes(n_tile, pair);
 }
+static_assert(gemm_smem_bytes(kGgmlQ4K, 256, false) <= kGemmSmemMax && gemm_smem_bytes(kGgmlQ6K, 256, false) <= kGemmSmemMax &&
+                  gemm_smem_bytes(kGgmlQ8_0, 256, false) <= kGemmSmemMax && gemm_smem_bytes(kGgmlQ4K, 512, true) <= kGemmSmemMax && gemm_smem_bytes(kGgmlQ5K, 512, true) <= kGemmSmemMax &&
+                  gemm_smem_bytes(kGgmlQ6K, 512, true) <= kGemmSmemMax && gemm_smem_bytes(kGgmlQ8_0, 512, true) <= kGemmSmemMax,
+              "the merged ring of the paired tile fits");
 static_assert(gemm_smem_bytes(kGgmlQ4K, 128, false) <= kGemmSmemMax && gemm_smem_bytes(kGgmlQ5K, 128, false) <= kGemmSmemMax &&
                   gemm_smem_bytes(kGgmlQ6K, 128, false) <= kGemmSmemMax && gemm_smem_bytes(kGgmlQ8_0, 128, false) <= kGemmSmemMax,
               "the merged ring fits");
-static_assert(kGemmMergedStages <= kGemmStages, "barrier slots");
-static_assert(kGemmMergedStages * kGemmMergedChunks * gemm_b_bytes(128) >= 4 * 32 * 128 * 4, "store staging fits the merged ring");
+static_assert(gemm_merged_stages(128) <= kGemmStages && gemm_merged_stages(512) <= kGemmStages, "barrier slots");
+static_assert(gemm_merged_stages(128) * gemm_merged_chunks(128) * gemm_b_bytes(128) >= 4 * 32 * 128 * 4 &&
+                  gemm_merged_stages(256) * gemm_b_bytes(256) >= 4 * 32 * 128 * 4 &&
+                  gemm_merged_stages(512) * gemm_b_bytes(512, true) >= 4 * 32 * 128 * 4,
+              "store staging fits the merged rings");
 static_assert(gemm_b_stages(kGgmlQ4K, 128, false) == 8 && gemm_b_stages(kGgmlQ4K, 256, false) == 4 &&
                   gemm_b_stages(kGgmlQ4K, 512, false) == 2 && gemm_b_stages(kGgmlQ4K, 512, true) == 4,
               "Q4_K stage counts");
@@ -464,9 +477,9 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* a_stage = smem;                                               // [S][CH][16384]
     constexpr bool kMerged = gemm_merged(N_TILE, PAIR);                    // one ring, two chunks per stage (see above)
-    constexpr int kAStages = kMerged ? kGemmMergedStages : kGemmStages, kCh = kMerged ? kGemmMergedChunks : 1;
+    constexpr int kAStages = kMerged ? gemm_merged_stages(N_TILE) : kGemmStages, kCh = kMerged ? gemm_merged_chunks(N_TILE) : 1;
     constexpr int kBBytes = gemm_b_bytes(N_TILE, PAIR);
-    constexpr int kBStages = kMerged ? kGemmMergedStages * kGemmMergedChunks : gemm_b_stages(TY, N_TILE, PAIR);   // B tiles held
+    constexpr int kBStages = kMerged ? kAStages * kCh : gemm_b_stages(TY, N_TILE, PAIR);   // B tiles held
     constexpr int kUnit = gemm_unit_bytes(TY), kRawBytes = gemm_raw_bytes(TY);
     constexpr int kNMma = N_TILE > 256 ? 256 : N_TILE;                     // activation rows per tcgen05.mma
     constexpr int kBoxRows = PAIR ? kNMma / 2 : kNMma;                     // of them, rows this CTA holds
@@ -503,7 +516,7 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
             mbar_init(&bar->raw_empty[i], kGemmDeqWarps);
         }
         for (int i = 0; i < kAStages; i++) {
-            mbar_init(&bar->a_full[i], kGemmDeqWarps * kPeers + (kMerged ? 1 : 0));   // in a pair only the leader's is used
+            mbar_init(&bar->a_full[i], kGemmDeqWarps * kPeers + (kMerged ? kPeers : 0));   // in a pair only the leader's is used
             mbar_init(&bar->a_empty[i], 1);
         }
         for (int i = 0; i < kBStages; i++) {
@@ -558,10 +571,22 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
             for (int e = 0; e < nchunks / kCh; e++) {
                 const int s = e % kAStages;
                 if (!mbar_wait(&bar->a_empty[s], (((uint32_t)e / kAStages) & 1u) ^ 1u)) { fail = 2; break; }
-                mbar_expect_tx(&bar->a_full[s], (uint32_t)(kCh * kBBytes));
+                if (PAIR) {
+                    // each CTA fetches its half of every 256-row operand; the bytes of both are counted by the leader
+                    const uint32_t full = cluster_addr(&bar->a_full[s], 0);
+                    mbar_expect_tx_cluster(full, (uint32_t)(kCh * kBBytes));
 #pragma unroll
-                for (int cc = 0; cc < kCh; cc++)
-                    tma_load_2d(b_stage + (s * kCh + cc) * kBBytes, &xmap, (kCh * e + cc) * kGemmChunkK, n0, &bar->a_full[s]);
+                    for (int cc = 0; cc < kCh; cc++)
+#pragma unroll
+                        for (int h = 0; h < N_TILE / kNMma; h++)
+                            tma_load_2d_pair(b_stage + (s * kCh + cc) * kBBytes + h * kBoxRows * 128, &xmap,
+                                             (4 * blk0 + kCh * e + cc) * kGemmChunkK, n0 + h * kNMma + (int)rank * kBoxRows, full);
+                } else {
+                    mbar_expect_tx(&bar->a_full[s], (uint32_t)(kCh * kBBytes));
+#pragma unroll
+                    for (int cc = 0; cc < kCh; cc++)
+                        tma_load_2d(b_stage + (s * kCh + cc) * kBBytes, &xmap, (kCh * e + cc) * kGemmChunkK, n0, &bar->a_full[s]);
+                }
             }
         } else if (lane == 0) {
             for (int c = 0; c < nchunks; c++) {
@@ -586,21 +611,33 @@ gemm_q_bf16_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CU
     } else if (warp == 1) {
         // ---------------- MMA issuer
         if (lane == 0 && kMerged) {
-            constexpr uint32_t idesc = umma_idesc_bf16(kGemmRows, kNMma);
-            for (int e = 0; e < nchunks / kCh; e++) {
-                const int s = e % kAStages;
-                if (!mbar_wait(&bar->a_full[s], ((uint32_t)e / kAStages) & 1u)) { fail = 3; break; }
-                tc_fence_after();
+            if (rank == 0) {
+                constexpr uint32_t idesc = umma_idesc_bf16(kGemmRows * kPeers, kNMma);
+                for (int e = 0; e < nchunks / kCh; e++) {
+                    const int s = e % kAStages;
+                    if (!mbar_wait(&bar->a_full[s], ((uint32_t)e / kAStages) & 1u)) { fail = 3; break; }
+                    tc_fence_after();
 #pragma unroll
-                for (int cc = 0; cc < kCh; cc++) {
-                    const uint32_t a0 = smem_u32(a_stage + (s * kCh + cc) * kGemmABytes), b0 = smem_u32(b_stage + (s * kCh + cc) * kBBytes);
+                    for (int cc = 0; cc < kCh; cc++) {
+                        const uint32_t a0 = smem_u32(a_stage + (s * kCh + cc) * kGemmABytes), b0 = smem_u32(b_stage + (s * kCh + cc) * kBBytes);
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; k4++)
-                        umma_bf16(tmem_acc, umma_desc_sw128(a0 + 32 * k4), umma_desc_sw128(b0 + 32 * k4), idesc, (e | cc | k4) ? 1u : 0u);
+                        for (int k4 = 0; k4 < 4; k4++)
+#pragma unroll
+                            for (int h = 0; h < N_TILE / kNMma; h++) {
+                                const uint64_t ad = umma_desc_sw128(a0 + 32 * k4), bd = umma_desc_sw128(b0 + h * kBoxRows * 128 + 32 * k4);
+                                if (PAIR) umma_bf16_pair(tmem_acc + h * kNMma, ad, bd, idesc, (e | cc | k4) ? 1u : 0u);
+                                else umma_bf16(tmem_acc + h * kNMma, ad, bd, idesc, (e | cc | k4) ? 1u : 0u);
+                            }
+                    }
+                    // one commit frees the stage (in both CTAs of a pair) once the MMAs above have read it
+                    if (PAIR) umma_commit_pair(&bar->a_empty[s]);
+                    else umma_commit(&bar->a_empty[s]);
                 }
-                umma_commit(&bar->a_empty[s]);   // frees the stage once the MMAs above have read it
+                if (!fail) {
+                    if (PAIR) umma_commit_pair(&bar->acc_full);
+                    else umma_commit(&bar->acc_full);
+                }
             }
-            if (!fail) umma_commit(&bar->acc_full);
         } else if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(kGemmRows * kPeers, kNMma);
             for (int c = 0; c < nchunks; c++) {
