@@ -1,14 +1,14 @@
-// Batched decode product (M > 8; Q4_K and Q6_K) on the tcgen05 tensor cores with integer-valued f16 operands.
+// Batched decode product (M > 8; Q4_K, Q5_K and Q6_K) on the tcgen05 tensor cores with integer-valued f16 operands.
 //
 // The mma.sync GEMV (kernels_gemv.cu) is bound by instruction issue beyond a few activation rows.  This kernel
 // moves the multiply-accumulates to tcgen05.mma kind::f16 and keeps every operand an integer that f16 holds exactly:
-//   A[row][k]     = sc(row, sub-block of k) * q(row, k)     0 .. 63 * 15 = 945
+//   A[row][k]     = sc(row, sub-block of k) * q(row, k)     0 .. 63 * 15 = 945 (Q5_K: 63 * 31 = 1953)
 //   B[2b + j][k]  = limb j of activation row b: X = rint(x * 2^(22-e)) = 2048 hi + lo, |hi| <= 1024, |lo| <= 1024,
 //                   one e per (activation row, super-block)
 // so every product is exact and the f32 accumulator (one super-block, K = 256, per pass) rounds only where a running
 // sum passes 2^24, i.e. by 2^-24 of that sum: the precision of an f32 product of the exact weights with X.  X keeps
 // 21 bits below the super-block's largest activation.
-// The Q4_K min term rides the tensor core too: one more K = 16 step per super-block multiplies the rows' eight 6-bit
+// The Q4_K / Q5_K min term rides the tensor core too: one more K = 16 step per super-block multiplies the rows' eight 6-bit
 // mins (twice) with the two pieces of each limb's sub-block sums (from the preparation kernel) into a second
 // accumulator.  After each super-block the drain warps read both accumulators back and apply what differs per row
 // and super-block in f32: y[b][row] += 2^(e-11) * (d * V - dmin * Mn), V and Mn recombined from their two limb
@@ -52,7 +52,9 @@ constexpr int kTcABytes = kTcRows * 128;   // one operand plane of one K chunk
 // holds exactly, so its scale is split as sc = 16 sh + sl (sl 0..15, sh -8..7) into two planes sl * (q - 32) and
 // sh * (q - 32), multiplied into two accumulators and recombined as D1 + 16 D2 in the drain.
 __host__ __device__ constexpr int tc_planes(uint32_t ty) { return ty == kGgmlQ6K ? 2 : 1; }
-__host__ __device__ constexpr int tc_unit_bytes(uint32_t ty) { return ty == kGgmlQ6K ? kQ6KUnit : kQ4KUnit; }
+__host__ __device__ constexpr int tc_unit_bytes(uint32_t ty) { return ty == kGgmlQ6K ? kQ6KUnit : ty == kGgmlQ5K ? kQ5KUnit : kQ4KUnit; }
+// Q4_K and Q5_K (the same block with a fifth bit per weight: sc * q <= 63 * 31 = 1953, still an integer f16 holds) have mins
+__host__ __device__ constexpr bool tc_has_mins(uint32_t ty) { return ty == kGgmlQ4K || ty == kGgmlQ5K; }
 __host__ __device__ constexpr int tc_raw_bytes(uint32_t ty) { return 8 * tc_unit_bytes(ty); }
 constexpr int kTcMaxStages = 8;
 
@@ -60,10 +62,10 @@ struct TcRowMeta {
     float d, dmin;
 };
 static_assert(sizeof(TcRowMeta) == 8, "row meta is one 8-byte store");
-// The Q4_K min step has its own operand tiles outside the ring, both in the swizzled 128-byte-row layout of which a K = 16
+// The Q4_K / Q5_K min step has its own operand tiles outside the ring, both in the swizzled 128-byte-row layout of which a K = 16
 // step reads 32 bytes per row: A2 (128 rows; slot i & 3 of its four 32-byte columns holds super-block i's mins) and B2
 // (n_tile rows; slot i mod the number of accumulator sets).
-__host__ __device__ constexpr int tc_min_bytes(uint32_t ty, int n_tile) { return ty == kGgmlQ4K ? kTcABytes + n_tile * 128 : 0; }
+__host__ __device__ constexpr int tc_min_bytes(uint32_t ty, int n_tile) { return tc_has_mins(ty) ? kTcABytes + n_tile * 128 : 0; }
 
 constexpr int kTcSumFloats = 64;   // per stage: the scales 2^(e-11) of up to 64 activation rows
 // One ring for both operands: a stage holds the A planes of one K chunk (made by the maker warps) and its B tile (the
@@ -71,7 +73,7 @@ constexpr int kTcSumFloats = 64;   // per stage: the scales 2^(e-11) of up to 64
 // tcgen05.commit -- the MMA thread's waits and commits are what paces this kernel.
 __host__ __device__ constexpr int tc_b_bytes(int n_tile) { return n_tile * 128; }
 // K chunks per ring stage: two (half as many hand-overs) where two such stages fit -- not for Q6_K's two planes at the wide tile
-__host__ __device__ constexpr int tc_chunks(uint32_t ty, int n_tile) { return (ty == kGgmlQ4K || n_tile <= 64) ? 2 : 1; }
+__host__ __device__ constexpr int tc_chunks(uint32_t ty, int n_tile) { return (tc_has_mins(ty) || n_tile <= 64) ? 2 : 1; }
 __host__ __device__ constexpr int tc_stage_bytes(uint32_t ty, int n_tile)
 {
     return tc_chunks(ty, n_tile) * (tc_planes(ty) * kTcABytes + tc_b_bytes(n_tile));
@@ -91,7 +93,8 @@ __host__ __device__ constexpr int tc_smem_bytes(uint32_t ty, int n_tile)
 {
     return tc_fixed_bytes(ty, n_tile) + tc_stages(ty, n_tile) * tc_stage_bytes(ty, n_tile);
 }
-static_assert(tc_stages(kGgmlQ4K, 128) >= 2 && tc_stages(kGgmlQ4K, 64) >= 2 && tc_stages(kGgmlQ6K, 128) >= 3 && tc_stages(kGgmlQ6K, 64) >= 2,
+static_assert(tc_stages(kGgmlQ4K, 128) >= 2 && tc_stages(kGgmlQ4K, 64) >= 2 && tc_stages(kGgmlQ5K, 128) >= 2 && tc_stages(kGgmlQ5K, 64) >= 2 &&
+                  tc_stages(kGgmlQ6K, 128) >= 3 && tc_stages(kGgmlQ6K, 64) >= 2,
               "ring depth");
 
 struct TcBarriers {
@@ -114,7 +117,7 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n)
 // with 2^e > 2 max|x|, so |X| < 2^21, split as X = 2048 hi + lo (lo in [-1024, 1023], |hi| <= 1024: both integers
 // f16 holds exactly).  Outputs:
 //   XL[2 * m][cols]        f16, row 2b = hi, row 2b + 1 = lo of activation row b, in the operand order tc_kpos
-//   SB[nblk][2 * m_pad][16] f16 (Q4_K only): what the tensor core needs for the min term -- per super-block 16 values
+//   SB[nblk][2 * m_pad][16] f16 (Q4_K, Q5_K): what the tensor core needs for the min term -- per super-block 16 values
 //                          per operand row, [sb] and [8 + sb] = the two pieces (|piece| <= 128, and a multiple of 256
 //                          up to 2^15: both exact) of the sum of that row's limb over sub-block sb
 //   UP[nblk][m_pad]        2^(e-11): V = D_hi + 2^-11 D_lo times UP is the product in x's units
@@ -231,10 +234,21 @@ __device__ __forceinline__ void tc_make16(uint32_t w0, uint32_t w1, __half2 sc_l
     word(w1, lo.z, lo.w, hi.z, hi.w);
 }
 
+// Eight weights given as one value per byte of b0, b1 (Q5_K: up to 31) -> f16 integers sc * v, bias = -1024 sc.
+__device__ __forceinline__ uint4 tc_make8_bytes(uint32_t b0, uint32_t b1, __half2 sc, __half2 bias)
+{
+    uint4 o;
+    o.x = tc_u32(__hfma2(tc_h2((b0 & 0x00FF00FFu) | 0x64006400u), sc, bias));
+    o.y = tc_u32(__hfma2(tc_h2(((b0 >> 8) & 0x00FF00FFu) | 0x64006400u), sc, bias));
+    o.z = tc_u32(__hfma2(tc_h2((b1 & 0x00FF00FFu) | 0x64006400u), sc, bias));
+    o.w = tc_u32(__hfma2(tc_h2(((b1 >> 8) & 0x00FF00FFu) | 0x64006400u), sc, bias));
+    return o;
+}
+
 // ---------------------------------------------------------------- operand makers
 // One call per maker warp.  Warp = one 16-row unit, lane = (row g / g+8, 8-byte piece t), with the prefill kernel's
 // conflict-free lane map.  Returns 0 or the code of the wait that ran out.
-template <int A_STAGES>
+template <int A_STAGES, bool Q5>
 __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, uint8_t* a2_tile, const uint8_t* raw_stage, TcRowMeta* meta,
                                            int nb, int tiles_here, int wd, int lane)
 {
@@ -249,15 +263,21 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, ui
     for (int i = 0; i < nb && !fail; i++) {
         const int rs = i % kTcRawStages;
         if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)i / kTcRawStages) & 1u)) { fail = 4; break; }
-        const uint8_t* u = raw_stage + rs * (8 * kQ4KUnit) + wd * kQ4KUnit;
+        // Q5: the Q5_K unit is the Q4_K unit plus a fifth-bit segment (lane 4g + t: qh[8t .. 8t+8) of rows g and g + 8); bit s
+        // of qh[l] lifts value l of sub-block s by 16 (crates/ferric-gguf/src/lib.rs:690-716), the rest is Q4_K's arithmetic.
+        constexpr int kUnitBytes = Q5 ? kQ5KUnit : kQ4KUnit;
+        const uint8_t* u = raw_stage + rs * (8 * kUnitBytes) + wd * kUnitBytes;
         uint4 hdr[2], qs[2][2];
+        uint2 q5[2];
 #pragma unroll
         for (int hi = 0; hi < 2; hi++) {
             hdr[hi] = qs[hi][0] = qs[hi][1] = make_uint4(0, 0, 0, 0);
+            q5[hi] = make_uint2(0, 0);
             if (unit_ok) {
                 hdr[hi] = *reinterpret_cast<const uint4*>(u + 16 * (g + 8 * hi));
                 qs[hi][0] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi) + 16 * (4 * g + t));
                 qs[hi][1] = *reinterpret_cast<const uint4*>(u + 256 + 512 * (2 * hi + 1) + 16 * (4 * g + t));
+                if (Q5) q5[hi] = *reinterpret_cast<const uint2*>(u + kQ5KOffQh + 16 * (4 * g + t) + 8 * hi);
             }
         }
         __syncwarp();
@@ -309,7 +329,16 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, ui
                     const __half2 s1 = __hsub2(tc_bcast_byte(scb[hi][j >> 1], (2 * j + 1) & 3), k1024);
                     const uint4 q4 = qs[hi][j >> 1];
                     const uint32_t w0 = (j & 1) ? q4.z : q4.x, w1 = (j & 1) ? q4.w : q4.y;
-                    tc_make16(w0, w1, s0, __hmul2(s0, km1024), s1, __hmul2(s1, km64), lo[hi], up8[hi]);
+                    if (Q5) {   // five-bit values, one per byte, then the byte form of the maker
+                        const uint32_t l0 = (w0 & 0x0F0F0F0Fu) | (((q5[hi].x >> (2 * j)) & 0x01010101u) << 4);
+                        const uint32_t l1 = (w1 & 0x0F0F0F0Fu) | (((q5[hi].y >> (2 * j)) & 0x01010101u) << 4);
+                        const uint32_t u0 = ((w0 >> 4) & 0x0F0F0F0Fu) | (((q5[hi].x >> (2 * j + 1)) & 0x01010101u) << 4);
+                        const uint32_t u1 = ((w1 >> 4) & 0x0F0F0F0Fu) | (((q5[hi].y >> (2 * j + 1)) & 0x01010101u) << 4);
+                        lo[hi] = tc_make8_bytes(l0, l1, s0, __hmul2(s0, km1024));
+                        up8[hi] = tc_make8_bytes(u0, u1, s1, __hmul2(s1, km1024));
+                    } else {
+                        tc_make16(w0, w1, s0, __hmul2(s0, km1024), s1, __hmul2(s1, km64), lo[hi], up8[hi]);
+                    }
                 }
                 // (every lane polls: one polling lane plus a shuffle was measured 15 % slower -- the wake-up is on the critical path)
                 if (cc == 0 && !mbar_wait(&bar->empty[s], (((uint32_t)c / kTcAStages) & 1u) ^ 1u)) { fail = 5; break; }
@@ -440,8 +469,8 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     constexpr int kUnit = tc_unit_bytes(TY), kTcRawBytes = tc_raw_bytes(TY);
     uint8_t* a_stage = smem;                                  // [kStages][kCh][kPlanes][16384]
     uint8_t* b_stage = a_stage + kStages * kAStageBytes;      // [kStages][kCh][N_TILE * 128]
-    uint8_t* a2_tile = b_stage + kStages * kBStageBytes;      // Q4_K: the min step's operands
-    uint8_t* b2_tile = a2_tile + (TY == kGgmlQ4K ? kTcABytes : 0);
+    uint8_t* a2_tile = b_stage + kStages * kBStageBytes;      // Q4_K, Q5_K: the min step's operands
+    uint8_t* b2_tile = a2_tile + (tc_has_mins(TY) ? kTcABytes : 0);
     uint8_t* raw_stage = a2_tile + tc_min_bytes(TY, N_TILE);
     TcRowMeta* meta = reinterpret_cast<TcRowMeta*>(raw_stage + kTcRawStages * kTcRawBytes);   // [kTcMetaStages][128]
     float* sums = reinterpret_cast<float*>(meta + kTcMetaStages * kTcRows);   // [2][kActs]: staged UP of a super-block
@@ -545,7 +574,7 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
                                 umma_f16_lo(d0 + pl * N_TILE, ad + (uint32_t)(pl * (kTcABytes >> 4) + 2 * k4), bd + 2 * k4, idesc,
                                             (e | cc | k4) ? 1u : 0u);
                     }
-                    if (TY == kGgmlQ4K && e == 4 / kCh - 1)   // mins x sub-block sums, K = 16 (operands in place since the first chunk / since acc_empty)
+                    if (tc_has_mins(TY) && e == 4 / kCh - 1)   // mins x sub-block sums, K = 16 (operands in place since the first chunk / since acc_empty)
                         umma_f16_lo(d0 + N_TILE, a2desc + 2 * (uint32_t)(i & 3), b2desc + 2 * (uint32_t)(i % kAcc), idesc, 0u);
                     umma_commit_addr(empty0 + 8 * sa);
                     if (++sa == (uint32_t)kStages) { sa = 0; pa ^= 1u; }
@@ -556,7 +585,8 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     } else if (warp < kTcFirstDrain) {
         // ---------------- operand makers (per quant type, above)
         const int wd = warp - kTcFirstMaker;
-        if (TY == kGgmlQ4K) fail = tc_make_q4k<kStages>(bar, a_stage, a2_tile, raw_stage, meta, nb, tiles_here, wd, lane);
+        if (TY == kGgmlQ4K) fail = tc_make_q4k<kStages, false>(bar, a_stage, a2_tile, raw_stage, meta, nb, tiles_here, wd, lane);
+        else if (TY == kGgmlQ5K) fail = tc_make_q4k<kStages, true>(bar, a_stage, a2_tile, raw_stage, meta, nb, tiles_here, wd, lane);
         else fail = tc_make_q6k<kStages, kCh>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
     } else {
         // ---------------- drain: TMEM lane = weight row; columns 2b, 2b + 1 = the hi and lo limb of activation row act0 + b.
@@ -581,13 +611,13 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
         // arrival, which the MMAs of super-block i + kAcc wait for.
         auto load_b2 = [&](int i) {
             uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (TY == kGgmlQ4K && i < nb && dt < 2 * N_TILE && kTcLimbs * act0 + (dt >> 1) < kTcLimbs * m)
+            if (tc_has_mins(TY) && i < nb && dt < 2 * N_TILE && kTcLimbs * act0 + (dt >> 1) < kTcLimbs * m)
                 val = __ldg(reinterpret_cast<const uint4*>(sbsum + ((size_t)(blk0 + i) * m_pad * kTcLimbs + kTcLimbs * act0 + (dt >> 1)) * 16) +
                             (dt & 1));
             return val;
         };
         auto store_b2 = [&](int i, const uint4& val) {
-            if (TY != kGgmlQ4K || i >= nb || dt >= 2 * N_TILE) return;
+            if (!tc_has_mins(TY) || i >= nb || dt >= 2 * N_TILE) return;
             const int r = dt >> 1, c = dt & 1;
             *reinterpret_cast<uint4*>(b2_tile + r * 128 + (((2 * (i % kAcc) + c) ^ (r & 7)) << 4)) = val;
         };
@@ -620,7 +650,7 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
 #pragma unroll
                 for (int bb = 0; bb < 8; bb++) {
                     const float scale = sl[8 * grp + bb];
-                    if (TY == kGgmlQ4K) {      // w = the min term's accumulator
+                    if (tc_has_mins(TY)) {     // w = the min term's accumulator
                         const float V = fmaf(__uint_as_float(v[2 * bb + 1]), 0.00048828125f, __uint_as_float(v[2 * bb]));
                         const float Mn = fmaf(__uint_as_float(w[2 * bb + 1]), 0.00048828125f, __uint_as_float(w[2 * bb]));
                         acc[8 * gg + bb] = fmaf(scale, fmaf(rm.d, V, ndmin * Mn), acc[8 * gg + bb]);
@@ -764,7 +794,7 @@ TcPlan tc_plan(uint32_t ty, const DeviceWeights& w, size_t m, Epilogue epi, int 
     p.needs_finish = p.splits > 1 || (epi == kEpiSwiglu && !p.fused_swiglu);
     p.m_pad = act_tiles * (size_t)(p.n_tile / kTcLimbs);
     p.off_sb = align256(kTcLimbs * m * w.cols * sizeof(__half));
-    p.off_up = p.off_sb + (ty == kGgmlQ4K ? align256(kTcLimbs * p.m_pad * w.nblk * 16 * sizeof(__half)) : 0);
+    p.off_up = p.off_sb + (tc_has_mins(ty) ? align256(kTcLimbs * p.m_pad * w.nblk * 16 * sizeof(__half)) : 0);
     p.off_part = p.off_up + align256(p.m_pad * w.nblk * sizeof(float));
     p.total = p.off_part + (p.needs_finish ? align256((size_t)p.splits * m * w.rows * sizeof(float)) : 0);
     return p;
@@ -795,12 +825,12 @@ bool gemv_tc_eligible(uint32_t ty, const DeviceWeights& w, size_t m)
 {
     // Measured cross-over with the mma.sync GEMV, which runs in passes of 4 activation rows (us per product, GEMV / this
     // kernel: gate|up 34816 x 5120 at 8 rows 50 / 63, at 9 rows 71 / 63; q|k|v at 9 rows 24 / 22; down Q6_K 5120 x 17408
-    // at 12 rows 59 / 64, at 13 rows 71 / 64): Q4_K from 9 rows, Q6_K from 13.
+    // at 12 rows 59 / 64, at 13 rows 71 / 64): Q4_K (and Q5_K, the same kernel) from 9 rows, Q6_K from 13.
     // FERRIC_CUDA_GEMV_TC_MIN_M overrides both; 0 disables the path.
     const char* env = getenv("FERRIC_CUDA_GEMV_TC_MIN_M");   // read per call: tests move the threshold
     const int forced = env ? atoi(env) : -1;
-    if (ty != kGgmlQ4K && ty != kGgmlQ6K) return false;
-    const int min_m = forced >= 0 ? forced : (ty == kGgmlQ4K ? 9 : 13);
+    if (ty != kGgmlQ4K && ty != kGgmlQ5K && ty != kGgmlQ6K) return false;
+    const int min_m = forced >= 0 ? forced : (ty == kGgmlQ6K ? 13 : 9);
     return min_m > 0 && m >= (size_t)min_m && m <= 4096 && w.nblk > 0 && w.rows > 0 && w.rows <= (size_t)INT32_MAX / 2;
 }
 
@@ -820,7 +850,7 @@ int32_t launch_gemv_tc(cudaStream_t st, uint32_t ty, const DeviceWeights& w, con
     const TcPlan p = tc_plan(ty, w, m, epi, tune.sm_count);
     uint8_t* base = reinterpret_cast<uint8_t*>(scratch);
     __half* xl = reinterpret_cast<__half*>(base);
-    __half* sb = ty == kGgmlQ4K ? reinterpret_cast<__half*>(base + p.off_sb) : nullptr;
+    __half* sb = tc_has_mins(ty) ? reinterpret_cast<__half*>(base + p.off_sb) : nullptr;
     float* up = reinterpret_cast<float*>(base + p.off_up);
     float* part = reinterpret_cast<float*>(base + p.off_part);
 
@@ -846,6 +876,9 @@ int32_t launch_gemv_tc(cudaStream_t st, uint32_t ty, const DeviceWeights& w, con
     if (ty == kGgmlQ6K) {
         if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ6K, 64>(st, w, map, sb, up, out, ld_out, split_stride, m, p, tune.pdl);
         else rc = launch_tc_tile<kGgmlQ6K, 128>(st, w, map, sb, up, out, ld_out, split_stride, m, p, tune.pdl);
+    } else if (ty == kGgmlQ5K) {
+        if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ5K, 64>(st, w, map, sb, up, out, ld_out, split_stride, m, p, tune.pdl);
+        else rc = launch_tc_tile<kGgmlQ5K, 128>(st, w, map, sb, up, out, ld_out, split_stride, m, p, tune.pdl);
     } else {
         if (p.n_tile == 64) rc = launch_tc_tile<kGgmlQ4K, 64>(st, w, map, sb, up, out, ld_out, split_stride, m, p, tune.pdl);
         else rc = launch_tc_tile<kGgmlQ4K, 128>(st, w, map, sb, up, out, ld_out, split_stride, m, p, tune.pdl);

@@ -163,7 +163,7 @@ size_t ferric_cuda_qmatrix_scratch_bytes(const ferric_qmatrix *qm, size_t m);
  * y[m, rows] = x[m, cols] . W^T, f32 in, f32 out, both DEVICE buffers, contiguous row-major,
  * 16-byte aligned.  m >= 0.  `x_cols` is the activation's inner dimension; a mismatch with the
  * matrix is the reference's "inner dim mismatch" panic -> FERRIC_ERR_SHAPE.
- * Few activation rows (and Q8_0 at any m) run the GEMV kernels, in passes of 4 rows; Q4_K from 9 rows and Q6_K from 13
+ * Few activation rows (and Q8_0 at any m) run the GEMV kernels, in passes of 4 rows; Q4_K / Q5_K from 9 rows and Q6_K from 13
  * run a tensor-core kernel on integer-valued f16 operands (FERRIC_CUDA_GEMV_TC_MIN_M in the environment moves
  * that threshold, 0 switches the kernel off); ferric_cuda_gemm_status reports its bounded waits. */
 int32_t ferric_cuda_matmul_q(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *x_dev, size_t m,

@@ -63,6 +63,9 @@ def run(F, ctx, raw, ty, rows, cols, x, swiglu=False):
     (12, 130, 768, 70),       # two activation tiles of the widest kind, the second nearly empty
     (12, 256, 512, 128),      # two full activation tiles
     (12, 256, 5120, 17),      # few row tiles, 20 super-blocks: K split + finish kernel
+    (13, 200, 1024, 16),      # Q5_K: the Q4_K kernel with the fifth bit, ragged rows
+    (13, 272, 512, 64),       # Q5_K, widest tile
+    (13, 256, 5120, 17),      # Q5_K with a K split
     (14, 128, 256, 24),       # Q6_K: two operand planes
     (14, 200, 768, 40),       # Q6_K, two activation tiles (its tile holds 32 rows)
     (14, 640, 4352, 64),      # Q6_K with a K split
