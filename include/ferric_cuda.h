@@ -199,7 +199,9 @@ int32_t ferric_cuda_add_rmsnorm(ferric_cuda_ctx *ctx, const float *a_dev, const 
  * inner dimension) is converted straight into the context's activation scratch, ready for
  * matmul_q_prepared on `qm` or any matrix of the same format and inner dimension -- the
  * `x.add_rmsnorm(..)` -> `matmul_q` pair of a decoder layer (crates/ferric-llama/src/qwen35.rs:986-996)
- * in one launch.  b_dev, weight_dev, sum_dev (may alias a_dev) and norm_dev may each be NULL. */
+ * in one launch.  b_dev, weight_dev, sum_dev (may alias a_dev) and norm_dev may each be NULL.
+ * The prepared form is the GEMV's: matmul_q_prepared runs the GEMV kernels in passes of 4 rows whatever m is, so from the
+ * tensor-core kernel's threshold on (9 rows, Q6_K 13) the pair ferric_cuda_add_rmsnorm + ferric_cuda_matmul_q is faster. */
 int32_t ferric_cuda_add_rmsnorm_prepare(ferric_cuda_ctx *ctx, const ferric_qmatrix *qm, const float *a_dev,
                                         const float *b_dev, const float *weight_dev, float eps, size_t m,
                                         float *sum_dev, float *norm_dev);
