@@ -42,8 +42,13 @@ constexpr int kTcLimbs = 2;           // operand rows per activation row
 // makers produce without a byte shuffle); tc_kpos(i) = the position of value i.
 __host__ __device__ constexpr int tc_kpos(int i) { return (i & ~3) | ((i & 1) << 1) | ((i >> 1) & 1); }
 constexpr int kTcChunkK = 64;         // K per stage: 64 f16 = one 128-byte swizzle row
-constexpr int kTcRawStages = 2;
-constexpr int kTcMetaStages = 8;      // per-row (d, dmin, mins) of the super-blocks between the makers and the drain
+constexpr int kTcMaxRawStages = 2;
+// Raw quant stages: two, except for Q6_K at the wide tile, where one leaves room for two K chunks per ring stage.  The makers
+// copy a raw super-block into registers before they convert any of it, so its successor is in flight while they work.
+__host__ __device__ constexpr int tc_raw_stages(uint32_t ty, int n_tile) { return (ty == kGgmlQ6K && n_tile > 64) ? 1 : 2; }
+// Per-row (d, dmin) of the super-blocks between the makers and the drain: the makers run at most one super-block of ring
+// plus the accumulator sets ahead of the drain -- 1 + 2 at the wide tile, 1 + 4 at the narrow one.
+__host__ __device__ constexpr int tc_meta_stages(int n_tile) { return n_tile > 64 ? 4 : 8; }
 constexpr int kTcMakerWarps = 8, kTcDrainWarps = 8;   // two drain warps per TMEM lane quarter, half the activation rows each
 constexpr int kTcFirstMaker = 3, kTcFirstDrain = kTcFirstMaker + kTcMakerWarps;
 constexpr int kTcThreads = 32 * (kTcFirstDrain + kTcDrainWarps);   // 608
@@ -72,16 +77,16 @@ constexpr int kTcSumFloats = 64;   // per stage: the scales 2^(e-11) of up to 64
 // limbs, by TMA), filled under ONE barrier (eight maker arrivals + the producer's expect-tx) and released by ONE
 // tcgen05.commit -- the MMA thread's waits and commits are what paces this kernel.
 __host__ __device__ constexpr int tc_b_bytes(int n_tile) { return n_tile * 128; }
-// K chunks per ring stage: two (half as many hand-overs) where two such stages fit -- not for Q6_K's two planes at the wide tile
-__host__ __device__ constexpr int tc_chunks(uint32_t ty, int n_tile) { return (tc_has_mins(ty) || n_tile <= 64) ? 2 : 1; }
+// K chunks per ring stage: two (half as many hand-overs than one)
+__host__ __device__ constexpr int tc_chunks(uint32_t, int) { return 2; }
 __host__ __device__ constexpr int tc_stage_bytes(uint32_t ty, int n_tile)
 {
     return tc_chunks(ty, n_tile) * (tc_planes(ty) * kTcABytes + tc_b_bytes(n_tile));
 }
 __host__ __device__ constexpr int tc_fixed_bytes(uint32_t ty, int n_tile)
 {
-    return 1024 /*align*/ + 512 /*barriers*/ + tc_min_bytes(ty, n_tile) + kTcRawStages * tc_raw_bytes(ty) +
-           kTcMetaStages * kTcRows * (int)sizeof(TcRowMeta) + 2 * kTcSumFloats * 4;
+    return 1024 /*align*/ + 512 /*barriers*/ + tc_min_bytes(ty, n_tile) + tc_raw_stages(ty, n_tile) * tc_raw_bytes(ty) +
+           tc_meta_stages(n_tile) * kTcRows * (int)sizeof(TcRowMeta) + 2 * kTcSumFloats * 4;
 }
 __host__ __device__ constexpr int tc_stages(uint32_t ty, int n_tile)
 {
@@ -94,11 +99,11 @@ __host__ __device__ constexpr int tc_smem_bytes(uint32_t ty, int n_tile)
     return tc_fixed_bytes(ty, n_tile) + tc_stages(ty, n_tile) * tc_stage_bytes(ty, n_tile);
 }
 static_assert(tc_stages(kGgmlQ4K, 128) >= 2 && tc_stages(kGgmlQ4K, 64) >= 2 && tc_stages(kGgmlQ5K, 128) >= 2 && tc_stages(kGgmlQ5K, 64) >= 2 &&
-                  tc_stages(kGgmlQ6K, 128) >= 3 && tc_stages(kGgmlQ6K, 64) >= 2,
+                  tc_stages(kGgmlQ6K, 128) >= 2 && tc_stages(kGgmlQ6K, 64) >= 2,
               "ring depth");
 
 struct TcBarriers {
-    uint64_t raw_full[kTcRawStages], raw_empty[kTcRawStages];
+    uint64_t raw_full[kTcMaxRawStages], raw_empty[kTcMaxRawStages];
     uint64_t full[kTcMaxStages], empty[kTcMaxStages];
     uint64_t acc_full[4], acc_empty[4];
     uint32_t tmem_base;
@@ -248,7 +253,7 @@ __device__ __forceinline__ uint4 tc_make8_bytes(uint32_t b0, uint32_t b1, __half
 // ---------------------------------------------------------------- operand makers
 // One call per maker warp.  Warp = one 16-row unit, lane = (row g / g+8, 8-byte piece t), with the prefill kernel's
 // conflict-free lane map.  Returns 0 or the code of the wait that ran out.
-template <int A_STAGES, bool Q5>
+template <int A_STAGES, bool Q5, int RAW, int META>
 __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, uint8_t* a2_tile, const uint8_t* raw_stage, TcRowMeta* meta,
                                            int nb, int tiles_here, int wd, int lane)
 {
@@ -261,8 +266,8 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, ui
     const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
     const __half2 km1024 = __half2half2(__ushort_as_half((unsigned short)0xE400)), km64 = __half2half2(__ushort_as_half((unsigned short)0xD400));
     for (int i = 0; i < nb && !fail; i++) {
-        const int rs = i % kTcRawStages;
-        if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)i / kTcRawStages) & 1u)) { fail = 4; break; }
+        const int rs = i % RAW;
+        if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)i / RAW) & 1u)) { fail = 4; break; }
         // Q5: the Q5_K unit is the Q4_K unit plus a fifth-bit segment (lane 4g + t: qh[8t .. 8t+8) of rows g and g + 8); bit s
         // of qh[l] lifts value l of sub-block s by 16 (crates/ferric-gguf/src/lib.rs:690-716), the rest is Q4_K's arithmetic.
         constexpr int kUnitBytes = Q5 ? kQ5KUnit : kQ4KUnit;
@@ -312,7 +317,7 @@ __device__ __forceinline__ int tc_make_q4k(TcBarriers* bar, uint8_t* a_stage, ui
             for (int hi = 0; hi < 2; hi++) {
                 const float dv = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x & 0xffffu)));
                 const float dm = __half2float(__ushort_as_half((unsigned short)(hdr[hi].x >> 16)));
-                *reinterpret_cast<float2*>(&meta[(i % kTcMetaStages) * kTcRows + 16 * wd + 8 * hi + g]) = make_float2(dv, dm);
+                *reinterpret_cast<float2*>(&meta[(i % META) * kTcRows + 16 * wd + 8 * hi + g]) = make_float2(dv, dm);
             }
         }
 #pragma unroll
@@ -369,7 +374,7 @@ __device__ __forceinline__ void tc_make4_q6(uint32_t q, __half2 sl, __half2 bl, 
 
 // Q6_K (unit layout in layout.h; lane ownership as in the prefill kernel's Q6_K stage): two operand planes per chunk,
 // plane 0 = sl * (q - 32), plane 1 = sh * (q - 32) with sc = 16 sh + sl.  Row meta carries d only.
-template <int A_STAGES, int CH>
+template <int A_STAGES, int CH, int RAW, int META>
 __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, const uint8_t* raw_stage, TcRowMeta* meta, int nb,
                                            int tiles_here, int wd, int lane)
 {
@@ -381,8 +386,8 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
     const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400)), k1032 = __half2half2(__ushort_as_half((unsigned short)0x6408));
     const __half2 km1056 = __half2half2(__ushort_as_half((unsigned short)0xE420));
     for (int i = 0; i < nb && !fail; i++) {
-        const int rs = i % kTcRawStages;
-        if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)i / kTcRawStages) & 1u)) { fail = 4; break; }
+        const int rs = i % RAW;
+        if (!mbar_wait(&bar->raw_full[rs], ((uint32_t)i / RAW) & 1u)) { fail = 4; break; }
         const uint8_t* u = raw_stage + rs * (8 * kQ6KUnit) + wd * kQ6KUnit;
         uint4 ql[2][2], qh[2], sc[2];
         uint32_t dpair = 0;
@@ -403,7 +408,7 @@ __device__ __forceinline__ int tc_make_q6k(TcBarriers* bar, uint8_t* a_stage, co
 #pragma unroll
             for (int hi = 0; hi < 2; hi++) {
                 const float dv = __half2float(__ushort_as_half((unsigned short)(hi ? (dpair >> 16) : (dpair & 0xffffu))));
-                *reinterpret_cast<float2*>(&meta[(i % kTcMetaStages) * kTcRows + 16 * wd + 8 * hi + g]) = make_float2(dv, 0.0f);
+                *reinterpret_cast<float2*>(&meta[(i % META) * kTcRows + 16 * wd + 8 * hi + g]) = make_float2(dv, 0.0f);
             }
         }
 #pragma unroll
@@ -472,8 +477,9 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     uint8_t* a2_tile = b_stage + kStages * kBStageBytes;      // Q4_K, Q5_K: the min step's operands
     uint8_t* b2_tile = a2_tile + (tc_has_mins(TY) ? kTcABytes : 0);
     uint8_t* raw_stage = a2_tile + tc_min_bytes(TY, N_TILE);
-    TcRowMeta* meta = reinterpret_cast<TcRowMeta*>(raw_stage + kTcRawStages * kTcRawBytes);   // [kTcMetaStages][128]
-    float* sums = reinterpret_cast<float*>(meta + kTcMetaStages * kTcRows);   // [2][kActs]: staged UP of a super-block
+    constexpr int kRaw = tc_raw_stages(TY, N_TILE), kMeta = tc_meta_stages(N_TILE);
+    TcRowMeta* meta = reinterpret_cast<TcRowMeta*>(raw_stage + kRaw * kTcRawBytes);   // [kMeta][128]
+    float* sums = reinterpret_cast<float*>(meta + kMeta * kTcRows);   // [2][kActs]: staged UP of a super-block
     TcBarriers* bar = reinterpret_cast<TcBarriers*>(sums + 2 * kTcSumFloats);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -482,7 +488,7 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     const int blk0 = blockIdx.z * blocks_per_split, nb = max(0, min(nblk, blk0 + blocks_per_split) - blk0);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kTcRawStages; i++) {
+        for (int i = 0; i < kRaw; i++) {
             mbar_init(&bar->raw_full[i], 1);
             mbar_init(&bar->raw_empty[i], kTcMakerWarps);
         }
@@ -517,8 +523,8 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
         // ---------------- weight producer (weights are immutable: no need to wait for the previous kernel)
         if (lane == 0) {
             for (int i = 0; i < nb; i++) {
-                const int rs = i % kTcRawStages;
-                if (!mbar_wait(&bar->raw_empty[rs], (((uint32_t)i / kTcRawStages) & 1u) ^ 1u)) { fail = 1; break; }
+                const int rs = i % kRaw;
+                if (!mbar_wait(&bar->raw_empty[rs], (((uint32_t)i / kRaw) & 1u) ^ 1u)) { fail = 1; break; }
                 mbar_expect_tx(&bar->raw_full[rs], (uint32_t)(tiles_here * kUnit));
                 for (int t = 0; t < tiles_here; t++) {
                     const int rt = gu16 > 0 ? (t < 4 ? 4 * (int)blockIdx.x + t : gu16 + 4 * (int)blockIdx.x + t - 4) : rt0 + t;
@@ -585,9 +591,9 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
     } else if (warp < kTcFirstDrain) {
         // ---------------- operand makers (per quant type, above)
         const int wd = warp - kTcFirstMaker;
-        if (TY == kGgmlQ4K) fail = tc_make_q4k<kStages, false>(bar, a_stage, a2_tile, raw_stage, meta, nb, tiles_here, wd, lane);
-        else if (TY == kGgmlQ5K) fail = tc_make_q4k<kStages, true>(bar, a_stage, a2_tile, raw_stage, meta, nb, tiles_here, wd, lane);
-        else fail = tc_make_q6k<kStages, kCh>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
+        if (TY == kGgmlQ4K) fail = tc_make_q4k<kStages, false, kRaw, kMeta>(bar, a_stage, a2_tile, raw_stage, meta, nb, tiles_here, wd, lane);
+        else if (TY == kGgmlQ5K) fail = tc_make_q4k<kStages, true, kRaw, kMeta>(bar, a_stage, a2_tile, raw_stage, meta, nb, tiles_here, wd, lane);
+        else fail = tc_make_q6k<kStages, kCh, kRaw, kMeta>(bar, a_stage, raw_stage, meta, nb, tiles_here, wd, lane);
     } else {
         // ---------------- drain: TMEM lane = weight row; columns 2b, 2b + 1 = the hi and lo limb of activation row act0 + b.
         // Two warps share a TMEM lane quarter; warp half h takes the groups of eight activation rows 2g + h.
@@ -638,7 +644,7 @@ gemv_tc_kernel(const uint8_t* __restrict__ units, const __grid_constant__ CUtens
             const uint4 b2v = load_b2(i + kAcc);   // in flight under the wait and the accumulator reads below
             if (!mbar_wait(&bar->acc_full[buf], ((uint32_t)i / kAcc) & 1u)) { fail = 6; break; }
             tc_fence_after();
-            const TcRowMeta rm = meta[(i % kTcMetaStages) * kTcRows + rloc];
+            const TcRowMeta rm = meta[(i % kMeta) * kTcRows + rloc];
             const float* sl = sums + (i & 1) * kTcSumFloats;
             const float ndmin = -rm.dmin;
 #pragma unroll
