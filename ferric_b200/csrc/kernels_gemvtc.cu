@@ -98,6 +98,21 @@ __host__ __device__ constexpr int tc_smem_bytes(uint32_t ty, int n_tile)
 {
     return tc_fixed_bytes(ty, n_tile) + tc_stages(ty, n_tile) * tc_stage_bytes(ty, n_tile);
 }
+// A row-meta slot of super-block j - META is rewritten by the makers at the start of super-block j.  By then they hold the
+// ring stages of j - 1, so the MMAs of super-block j - 1 - R have completed (R = the ring's depth in super-blocks), which
+// started only after the drain of j - 1 - R - A had handed its accumulator set back (A sets): META >= 1 + R + A.
+__host__ __device__ constexpr bool tc_meta_ok(uint32_t ty, int n_tile)
+{
+    return tc_meta_stages(n_tile) >= 1 + (tc_stages(ty, n_tile) * tc_chunks(ty, n_tile) + 3) / 4 + 256 / n_tile;
+}
+static_assert(tc_meta_ok(kGgmlQ4K, 64) && tc_meta_ok(kGgmlQ4K, 128) && tc_meta_ok(kGgmlQ5K, 64) && tc_meta_ok(kGgmlQ5K, 128) &&
+                  tc_meta_ok(kGgmlQ6K, 64) && tc_meta_ok(kGgmlQ6K, 128),
+              "row-meta ring depth");
+// The same count for the min step's A2 slots (four, slot i & 3 rewritten at the start of super-block i): the min MMA of
+// super-block i - 4 must be over, i.e. i - 4 <= i - 1 - R.
+static_assert((tc_stages(kGgmlQ4K, 64) * tc_chunks(kGgmlQ4K, 64) + 3) / 4 <= 3 && (tc_stages(kGgmlQ5K, 64) * tc_chunks(kGgmlQ5K, 64) + 3) / 4 <= 3 &&
+                  (tc_stages(kGgmlQ4K, 128) * tc_chunks(kGgmlQ4K, 128) + 3) / 4 <= 3,
+              "A2 slot ring depth");
 static_assert(tc_stages(kGgmlQ4K, 128) >= 2 && tc_stages(kGgmlQ4K, 64) >= 2 && tc_stages(kGgmlQ5K, 128) >= 2 && tc_stages(kGgmlQ5K, 64) >= 2 &&
                   tc_stages(kGgmlQ6K, 128) >= 2 && tc_stages(kGgmlQ6K, 64) >= 2,
               "ring depth");
