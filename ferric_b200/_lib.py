@@ -91,6 +91,7 @@ SIGNATURES = {
     "ferric_cuda_tp_add_rmsnorm_prepare_pushed": (_I32, [_P, _P, _I32, _P, _P, _P, C.c_float, _SZ, _P, _P]),
     "ferric_cuda_tp_allreduce_add_rmsnorm": (_I32, [_P, _P, _I32, _P, _P, _P, C.c_float, _SZ, _SZ, _P, _P]),
     "ferric_cuda_tp_allreduce_add_rmsnorm_steps": (_I32, [_P, _P, _I32, _P, _P, _P, C.c_float, _SZ, _SZ, _P, _P, _I32]),
+    "ferric_cuda_tp_matmul_scatter": (_I32, [_P, _P, _I32, _P, _P, _SZ, _SZ, _P]),
     "ferric_cuda_tp_status": (_I32, [_P, _P, C.POINTER(_I32)]),
     "ferric_cuda_tp_reset": (_I32, [_P, _P]),
     "ferric_cuda_tp_chain_matmul": (_I32, [_P, _P, _I32, C.POINTER(ChainLink), _SZ]),

@@ -199,8 +199,11 @@ int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, c
 // product and, for K-split or SwiGLU, a finish kernel.  `scratch` holds gemv_tc_scratch_bytes() bytes.
 bool gemv_tc_eligible(uint32_t ty, const DeviceWeights& w, size_t m);
 size_t gemv_tc_scratch_bytes(uint32_t ty, const DeviceWeights& w, size_t m, Epilogue epi, int sm_count);
+// With `scatter` (plain store, K cut across CTAs, rows a multiple of 4) the finish kernel stores the result not into y but, as
+// step 1 of the two-step pushed all-reduce, into the slice owners' memory, and *scattered says that it did.
 int32_t launch_gemv_tc(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y, size_t ldy,
-                       Epilogue epi, void* scratch, const GemvTuning& tune, int* launches);
+                       Epilogue epi, void* scratch, const GemvTuning& tune, int* launches, const WideDst* scatter = nullptr,
+                       bool* scattered = nullptr);
 // Synchronise the stream and fetch-and-clear the code a GEMM CTA left when one of its bounded waits ran out.
 int32_t gemm_status(cudaStream_t st, int* code);
 

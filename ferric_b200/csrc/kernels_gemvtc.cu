@@ -33,6 +33,7 @@
 #include "kernels.h"
 #include "layout.h"
 #include "tc_common.cuh"
+#include "tpwide.cuh"
 
 namespace ferric {
 
@@ -763,6 +764,28 @@ __global__ void tc_finish_kernel(const float* __restrict__ part, int splits, siz
     }
 }
 
+// The same sum of the K pieces, stored not into y but -- as step 1 of the two-step pushed all-reduce (kernels_tpwide.cu) --
+// into the stage-1 region of the rank that owns each slice of the flat [m x rows] result: the product scatters itself.
+__global__ void tc_finish_scatter_kernel(const float* __restrict__ part, int splits, size_t split_stride, size_t n, WideDst dst)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const unsigned stamp = wide_stamp(dst.epoch);
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
+        float4 v = *reinterpret_cast<const float4*>(part + i);
+        for (int s = 1; s < splits; s++) {
+            const float4 t = *reinterpret_cast<const float4*>(part + s * split_stride + i);
+            v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+        }
+        const size_t owner = i / dst.slice, off = i - owner * dst.slice;
+        uint2* base = nullptr;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; r++)
+            if ((size_t)r == owner) base = dst.stage1[r];   // static indices keep the table in the parameter space
+        store_pairs4(base + (size_t)(stamp & 1) * dst.parity_stride1 + off, v, stamp);
+    }
+}
+
 // ---------------------------------------------------------------- host side
 int* gemm_status_word();   // device address of the status word shared with the prefill kernel (kernels_gemm.cu)
 
@@ -861,8 +884,9 @@ size_t gemv_tc_scratch_bytes(uint32_t ty, const DeviceWeights& w, size_t m, Epil
 }
 
 int32_t launch_gemv_tc(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const float* x, size_t m, size_t ldx, float* y, size_t ldy,
-                       Epilogue epi, void* scratch, const GemvTuning& tune, int* launches)
+                       Epilogue epi, void* scratch, const GemvTuning& tune, int* launches, const WideDst* scatter, bool* scattered)
 {
+    if (scattered) *scattered = false;
     EncodeTiledFn enc = tc_encode_fn();
     if (!enc) {
         set_last_error("the CUDA driver does not export cuTensorMapEncodeTiled");
@@ -906,7 +930,16 @@ int32_t launch_gemv_tc(cudaStream_t st, uint32_t ty, const DeviceWeights& w, con
     }
     if (rc != kOk) return rc;
     *launches += 2;
-    if (p.needs_finish) {
+    if (p.needs_finish && scatter && epi == kEpiStore && w.rows % 4 == 0) {
+        // the K pieces are summed straight into the slice owners' memory (the flat result has row stride w.rows)
+        const size_t n = m * w.rows;
+        unsigned blocks = (unsigned)((n / 4 + 255) / 256);
+        if (blocks > 4u * (unsigned)tune.sm_count) blocks = 4u * (unsigned)tune.sm_count;
+        FERRIC_CUDA_TRY(launch_kernel(tc_finish_scatter_kernel, dim3(blocks), dim3(256), 0, st, tune.pdl, (const float*)part, p.splits,
+                                      split_stride, n, *scatter));
+        *launches += 1;
+        if (scattered) *scattered = true;
+    } else if (p.needs_finish) {
         const size_t total = m * (epi == kEpiSwiglu ? w.rows / 2 : w.rows);
         unsigned blocks = (unsigned)((total + 255) / 256);
         if (blocks > 4u * (unsigned)tune.sm_count) blocks = 4u * (unsigned)tune.sm_count;

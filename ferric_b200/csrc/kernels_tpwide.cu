@@ -12,30 +12,12 @@
 // number matches carries its value.  No multicast, no multimem: plain stores to peer addresses.
 #include "common.cuh"
 #include "kernels.h"
+#include "tpwide.cuh"
 
 namespace ferric {
 
 namespace {
 
-
-__device__ __forceinline__ unsigned wide_stamp(const unsigned* epoch)
-{
-    unsigned e;
-    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(e) : "l"(epoch));
-    return e + 1;
-}
-__device__ __forceinline__ void store_pairs4(uint2* dst, float4 v, unsigned stamp)
-{
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(__float_as_uint(v.x)), "r"(stamp),
-                 "r"(__float_as_uint(v.y)), "r"(stamp) : "memory");
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 2), "r"(__float_as_uint(v.z)), "r"(stamp),
-                 "r"(__float_as_uint(v.w)), "r"(stamp) : "memory");
-}
-__device__ __forceinline__ void load_pairs4(const uint2* src, uint4& a, uint4& b)
-{
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src));
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 2));
-}
 
 // x[n] -> slice s of every four-float group goes to rank s (slices of `slice` floats, a multiple of 4).
 __global__ void __launch_bounds__(256) wide_scatter_kernel(const float* __restrict__ x, size_t n, WideDst dst)

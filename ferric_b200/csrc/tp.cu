@@ -328,6 +328,28 @@ int32_t ferric_cuda_tp_add_rmsnorm_prepare_pushed(ferric_cuda_ctx* ctx, ferric_t
                             ctx->tune, PeerSum(), p);
 }
 
+// The addresses of exchange `kind` of the two-step pushed all-reduce, as this rank sees them.
+static void fill_wide_dst(const ferric_cuda_ctx* ctx, const ferric_tp_group* g, int kind, WideDst& w)
+{
+    const size_t pairs = wide_pairs(g->elems, g->world);
+    w.world = g->world;
+    w.rank = g->rank;
+    w.slice = wide_slice(g->elems, g->world);
+    w.parity_stride1 = w.parity_stride2 = pairs;
+    w.epoch = g->wide_epoch + kind;
+    w.ticket = g->wide_ticket + kind;
+    w.status = g->status;
+    if (ctx->tune.wait_spins > 0) w.wait_spins = ctx->tune.wait_spins;
+    uint8_t* local = reinterpret_cast<uint8_t*>(g->local);
+    w.recv1 = reinterpret_cast<const uint2*>(local + off_wide1(g->elems, g->world)) + (size_t)kind * 2 * pairs;
+    w.recv2 = reinterpret_cast<const uint2*>(local + off_wide2(g->elems, g->world)) + (size_t)kind * 2 * pairs;
+    for (int r = 0; r < g->world; r++) {
+        uint8_t* peer = reinterpret_cast<uint8_t*>(g->peer_base[r]);
+        w.stage1[r] = reinterpret_cast<uint2*>(peer + off_wide1(g->elems, g->world)) + (size_t)kind * 2 * pairs + (size_t)g->rank * w.slice;
+        w.stage2[r] = reinterpret_cast<uint2*>(peer + off_wide2(g->elems, g->world)) + (size_t)kind * 2 * pairs;
+    }
+}
+
 int32_t ferric_cuda_tp_allreduce_add_rmsnorm(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t kind, const float* partial_dev,
                                              const float* a_dev, const float* weight_dev, float eps, size_t rows, size_t d,
                                              float* sum_dev, float* norm_dev)
@@ -356,27 +378,59 @@ int32_t ferric_cuda_tp_allreduce_add_rmsnorm_steps(ferric_cuda_ctx* ctx, ferric_
     }
     if (rows * d == 0) return kOk;
     DeviceGuard guard(ctx->device);
-    const size_t pairs = wide_pairs(g->elems, g->world);
     WideDst w;
-    w.world = g->world;
-    w.rank = g->rank;
-    w.slice = wide_slice(g->elems, g->world);
-    w.parity_stride1 = w.parity_stride2 = pairs;
-    w.epoch = g->wide_epoch + kind;
-    w.ticket = g->wide_ticket + kind;
-    w.status = g->status;
-    if (ctx->tune.wait_spins > 0) w.wait_spins = ctx->tune.wait_spins;
-    uint8_t* local = reinterpret_cast<uint8_t*>(g->local);
-    w.recv1 = reinterpret_cast<const uint2*>(local + off_wide1(g->elems, g->world)) + (size_t)kind * 2 * pairs;
-    w.recv2 = reinterpret_cast<const uint2*>(local + off_wide2(g->elems, g->world)) + (size_t)kind * 2 * pairs;
-    for (int r = 0; r < g->world; r++) {
-        uint8_t* peer = reinterpret_cast<uint8_t*>(g->peer_base[r]);
-        w.stage1[r] = reinterpret_cast<uint2*>(peer + off_wide1(g->elems, g->world)) + (size_t)kind * 2 * pairs + (size_t)g->rank * w.slice;
-        w.stage2[r] = reinterpret_cast<uint2*>(peer + off_wide2(g->elems, g->world)) + (size_t)kind * 2 * pairs;
-    }
+    fill_wide_dst(ctx, g, kind, w);
     ctx->launches += (steps & 1) + ((steps >> 1) & 1) + ((steps >> 2) & 1);
     return launch_wide_allreduce_add_rmsnorm(ctx->stream, partial_dev, a_dev, weight_dev, eps, rows, d, sum_dev, norm_dev, w, ctx->tune,
                                              steps);
+}
+
+int32_t ferric_cuda_tp_matmul_scatter(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t kind, const ferric_qmatrix* qm,
+                                      const float* x_dev, size_t m, size_t ldx, int32_t* fused_out)
+{
+    if (fused_out) *fused_out = 0;
+    if (!ctx || !g || !qm || kind < 0 || kind > 1 || !g->connected || (m > 0 && !x_dev)) {
+        set_last_error("tp_matmul_scatter: NULL / unconnected argument or bad kind");
+        return kErrInvalidArg;
+    }
+    if (!has_prepared_form(qm->ty)) return kUnsupported;
+    if (ldx == 0) ldx = qm->w.cols;
+    if (ldx < qm->w.cols || (ldx & 3) || (reinterpret_cast<uintptr_t>(x_dev) & 15)) {
+        set_last_error("row stride ldx %zu must cover the row and be a multiple of 4, x 16-byte aligned", ldx);
+        return kErrShape;
+    }
+    if (m * qm->w.rows > g->elems || (qm->w.rows & 3)) {
+        set_last_error("exchange buffers hold %zu floats, %zu x %zu requested (rows must be a multiple of 4)", g->elems, m, qm->w.rows);
+        return kErrShape;
+    }
+    if (m == 0 || qm->w.rows == 0) return kOk;
+    if (qm->w.nblk == 0) {
+        set_last_error("tp_matmul_scatter: empty K range");
+        return kErrShape;
+    }
+    DeviceGuard guard(ctx->device);
+    WideDst w;
+    fill_wide_dst(ctx, g, kind, w);
+    float* part = g->part[kind];
+    int32_t rc;
+    bool fused = false;
+    if (gemv_tc_eligible(qm->ty, qm->w, m)) {
+        if ((rc = ensure_scratch(ctx, gemv_tc_scratch_bytes(qm->ty, qm->w, m, kEpiStore, ctx->tune.sm_count))) != kOk) return rc;
+        int launched = 0;
+        rc = launch_gemv_tc(ctx->stream, qm->ty, qm->w, x_dev, m, ldx, part, qm->w.rows, kEpiStore, ctx->scratch, ctx->tune, &launched, &w,
+                            &fused);
+        ctx->launches += launched;
+    } else {
+        if ((rc = ensure_scratch(ctx, frag_bytes(qm->ty, qm->w, m))) != kOk) return rc;
+        if ((rc = launch_prep(ctx->stream, qm->ty, qm->w, x_dev, m, ldx, ctx->scratch, ctx->tune)) != kOk) return rc;
+        ctx->launches += 2;
+        rc = launch_gemv(ctx->stream, qm->ty, qm->w, ctx->scratch, m, part, qm->w.rows, kEpiStore, ctx->tune);
+    }
+    if (rc != kOk) return rc;
+    if (fused_out) *fused_out = fused ? 1 : 0;
+    if (fused) return kOk;
+    ctx->launches++;
+    return launch_wide_allreduce_add_rmsnorm(ctx->stream, part, nullptr, nullptr, 0.0f, m, qm->w.rows, nullptr, nullptr, w, ctx->tune, 1);
 }
 
 int32_t ferric_cuda_tp_status(ferric_cuda_ctx* ctx, ferric_tp_group* g, int32_t* timed_out)

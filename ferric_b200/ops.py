@@ -539,6 +539,17 @@ class TPGroup:
                                                                     ptr(weight), float(eps), rows, d, ptr(sum_out), ptr(norm_out), steps),
                "tp_allreduce_add_rmsnorm")
 
+    def matmul_scatter(self, kind: int, qm: "QMatrix", x: torch.Tensor) -> bool:
+        """The row-parallel product x . W^T of this rank, scattered as step 1 of exchange `kind` of the two-step all-reduce
+        (by the product's own finish kernel where its K range is cut across CTAs: returns True); continue with
+        ``allreduce_add_rmsnorm(.., steps=6)``."""
+        assert x.dtype == torch.float32 and x.is_cuda and x.stride(-1) == 1
+        m = x.numel() // x.shape[-1]
+        fused = C.c_int32(0)
+        _check(self._lib.ferric_cuda_tp_matmul_scatter(self.ctx._h, self._h, kind, qm._h, x.data_ptr(), m,
+                                                       x.stride(0) if x.dim() > 1 else 0, C.byref(fused)), "tp_matmul_scatter")
+        return bool(fused.value)
+
     def matmul_push(self, kind: int, qm: "QMatrix", x: torch.Tensor) -> None:
         """The row-parallel product x . W^T of this rank, stored by the kernel's epilogue into every rank's receive
         region for exchange `kind` instead of a local buffer."""

@@ -235,19 +235,22 @@ class DecodeStack:
         c.add_rmsnorm(self.h, None, None, self.eps, norm_out=self.xn)
         for i, L in enumerate(self.layers):
             L.wqkv.matmul(self.xn, out=self.qkv)
-            L.wo.matmul(self.qkv[:, :p.q_rows], out=self.o)
-            if self.group is not None:      # the library's two-step pushed all-reduce, fused into add + rmsnorm
-                self.group.allreduce_add_rmsnorm(0, self.o, self.h, None, self.eps, sum_out=self.h, norm_out=self.xn)
+            if self.group is not None:      # the library's two-step pushed all-reduce, fused into add + rmsnorm; the
+                # product scatters its own result (step 1) where its K range is cut across CTAs
+                self.group.matmul_scatter(0, L.wo, self.qkv[:, :p.q_rows])
+                self.group.allreduce_add_rmsnorm(0, self.o, self.h, None, self.eps, sum_out=self.h, norm_out=self.xn, steps=6)
             else:
+                L.wo.matmul(self.qkv[:, :p.q_rows], out=self.o)
                 if self.all_reduce:
                     self.all_reduce(self.o)
                 c.add_rmsnorm(self.h, self.o, None, self.eps, sum_out=self.h, norm_out=self.xn)
             if L.wgu.try_matmul_swiglu(self.xn, out=self.f) is None:
                 raise RuntimeError("gate|up matrix is not fusable")
-            L.wdown.matmul(self.f, out=self.d)
             if self.group is not None:
-                self.group.allreduce_add_rmsnorm(1, self.d, self.h, None, self.eps, sum_out=self.h, norm_out=self.xn)
+                self.group.matmul_scatter(1, L.wdown, self.f)
+                self.group.allreduce_add_rmsnorm(1, self.d, self.h, None, self.eps, sum_out=self.h, norm_out=self.xn, steps=6)
             else:
+                L.wdown.matmul(self.f, out=self.d)
                 if self.all_reduce:
                     self.all_reduce(self.d)
                 c.add_rmsnorm(self.h, self.d, None, self.eps, sum_out=self.h, norm_out=self.xn)

@@ -461,6 +461,16 @@ int32_t ferric_cuda_tp_allreduce_add_rmsnorm_steps(ferric_cuda_ctx *ctx, ferric_
                                                    const float *partial_dev, const float *a_dev,
                                                    const float *weight_dev, float eps, size_t rows, size_t d,
                                                    float *sum_dev, float *norm_dev, int32_t steps);
+/* The row-parallel product of this rank, x[m, cols] . W^T, whose result goes straight into the scatter step of that
+ * exchange: where the product's K range is cut across CTAs (the tensor-core decode kernel on a matrix with few row
+ * tiles -- the o and down shards of a decoder layer), the kernel that adds the K pieces stores the sums, as the exchange's
+ * (value, number) pairs, into the slice owners' memory instead of a local buffer (*fused = 1); otherwise the product
+ * lands in the group's partial buffer and the scatter step runs after it (*fused = 0).  Either way step 1 is done:
+ * continue with ferric_cuda_tp_allreduce_add_rmsnorm_steps(.., steps = 2 | 4) (its partial_dev is not read then).
+ * No counterpart in the reference (its model parallelism only concatenates, crates/ferric-tensor/src/sched.rs:209-240).
+ * m x rows must fit the group's `elems`, rows a multiple of 4, x 16-byte aligned; ldx = 0 means dense rows. */
+int32_t ferric_cuda_tp_matmul_scatter(ferric_cuda_ctx *ctx, ferric_tp_group *g, int32_t kind, const ferric_qmatrix *qm,
+                                      const float *x_dev, size_t m, size_t ldx, int32_t *fused);
 /* A RESIDUAL chain link (ferric_cuda_chain_matmul) whose product is row-parallel: the epilogue pushes the partial
  * sums to every rank as ferric_cuda_tp_matmul_push does, and the link's job polls (bounded) all ranks' pairs for its
  * block in this rank's memory, adds them in rank order to h and prepares the next product -- product, all-reduce,

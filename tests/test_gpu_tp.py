@@ -194,6 +194,45 @@ def test_two_step_allreduce_many_ranks_in_one_process(world, cap_rows, rows, d):
         o.close()
 
 
+@pytest.mark.parametrize("world,ty,rows,cols_per_rank,m", [(2, 12, 512, 1024, 24), (4, 14, 640, 1024, 64), (3, 12, 19200, 256, 16),
+                                                          (2, 12, 512, 1024, 4)])
+def test_product_scatters_its_own_result_into_the_two_step_allreduce(world, ty, rows, cols_per_rank, m):
+    """`matmul_scatter`: each rank's row-parallel product goes straight into step 1 of the all-reduce -- by the product's own
+    finish kernel where its K range is cut across CTAs (few row tiles), by the scatter kernel after it otherwise (one K
+    piece: 19200 rows; or the GEMV path: 4 activation rows).  Ranks are groups of this process on one GPU, the steps run as
+    phases.  The result must equal add_rmsnorm(a, sum over ranks of the plain products), the sum bit for bit."""
+    import ferric_b200 as F
+    from ferric_b200 import synth
+
+    ctxs = [F.Context(0) for _ in range(world)]
+    grps = [F.TPGroup(ctxs[r], r, world, m, rows) for r in range(world)]
+    F.TPGroup.connect_local(grps)
+    gen = torch.Generator(device="cuda").manual_seed(world * 7 + m)
+    qms = [F.QMatrix.from_bytes(ctxs[r], synth.matrix(ty, rows, cols_per_rank, seed=50 + r), ty, rows, cols_per_rank) for r in range(world)]
+    for it, kind in enumerate((0, 1, 1)):
+        xs = [torch.randn(m, cols_per_rank, device="cuda", generator=gen) for _ in range(world)]
+        a = torch.randn(m, rows, device="cuda", generator=gen)
+        total = qms[0].matmul(xs[0]).clone()
+        for r in range(1, world):
+            total += qms[r].matmul(xs[r])
+        s_ref, n_ref = torch.empty_like(a), torch.empty_like(a)
+        ctxs[0].add_rmsnorm(a, total, None, 1e-6, sum_out=s_ref, norm_out=n_ref)
+        outs = [(torch.empty_like(a), torch.empty_like(a)) for _ in range(world)]
+        torch.cuda.synchronize()
+        fused = [grps[r].matmul_scatter(kind, qms[r], xs[r]) for r in range(world)]
+        assert all(f == (m >= 9 and rows < 19200) for f in fused), fused
+        for step in (2, 4):
+            torch.cuda.synchronize()
+            for r in range(world):
+                grps[r].allreduce_add_rmsnorm(kind, a, a, None, 1e-6, sum_out=outs[r][0], norm_out=outs[r][1], steps=step)
+        for r in range(world):
+            grps[r].check()
+            assert torch.equal(outs[r][0], s_ref), (it, r)
+            assert torch.allclose(outs[r][1], n_ref, rtol=2e-6, atol=1e-7), (it, r)
+    for o in qms + grps + ctxs:
+        o.close()
+
+
 # ---------------------------------------------------------------------------------- a peer that never arrives
 def _two_local_ranks(F, m, hid):
     ctxs = [F.Context(0) for _ in range(2)]
