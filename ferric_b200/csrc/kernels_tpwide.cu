@@ -92,7 +92,10 @@ __global__ void __launch_bounds__(256) wide_add_rmsnorm_kernel(const float* __re
     const size_t base = blockIdx.x * d;
     const uint2* pairs = dst.recv2 + (size_t)(stamp & 1) * dst.parity_stride2 + base;
     float ms = 0.0f;
-    for (size_t j = (size_t)threadIdx.x * 4; j < d; j += (size_t)blockDim.x * 4) {
+    // the row's sums stay in registers between the two passes where they fit (kKeep quads per thread: d <= 8192 at 256 threads)
+    constexpr int kKeep = 8;
+    float4 keep[kKeep];
+    auto consume = [&](size_t j) {
         uint4 pa, pb;
         int spins = 0;
         for (;;) {
@@ -108,7 +111,15 @@ __global__ void __launch_bounds__(256) wide_add_rmsnorm_kernel(const float* __re
                                      av.w + __uint_as_float(pb.z));
         *reinterpret_cast<float4*>(sum + base + j) = s;
         ms = fmaf(s.x, s.x, ms); ms = fmaf(s.y, s.y, ms); ms = fmaf(s.z, s.z, ms); ms = fmaf(s.w, s.w, ms);
+        return s;
+    };
+#pragma unroll
+    for (int k = 0; k < kKeep; k++) {
+        const size_t j = ((size_t)k * blockDim.x + threadIdx.x) * 4;
+        keep[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < d) keep[k] = consume(j);
     }
+    for (size_t j = ((size_t)kKeep * blockDim.x + threadIdx.x) * 4; j < d; j += (size_t)blockDim.x * 4) (void)consume(j);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ms += __shfl_xor_sync(0xffffffffu, ms, o);
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ms;
@@ -118,12 +129,18 @@ __global__ void __launch_bounds__(256) wide_add_rmsnorm_kernel(const float* __re
     for (int i = 0; i < 8; i++) tot += part[i];
     const float inv = 1.0f / sqrtf(tot / (float)d + eps);
     if (norm) {
-        for (size_t j = (size_t)threadIdx.x * 4; j < d; j += (size_t)blockDim.x * 4) {
-            const float4 s = *reinterpret_cast<const float4*>(sum + base + j);   // this thread's own stores
+        auto emit = [&](size_t j, const float4& s) {
             float4 wv = make_float4(1.f, 1.f, 1.f, 1.f);
             if (w) wv = *reinterpret_cast<const float4*>(w + j);
             *reinterpret_cast<float4*>(norm + base + j) = make_float4(s.x * inv * wv.x, s.y * inv * wv.y, s.z * inv * wv.z, s.w * inv * wv.w);
+        };
+#pragma unroll
+        for (int k = 0; k < kKeep; k++) {
+            const size_t j = ((size_t)k * blockDim.x + threadIdx.x) * 4;
+            if (j < d) emit(j, keep[k]);
         }
+        for (size_t j = ((size_t)kKeep * blockDim.x + threadIdx.x) * 4; j < d; j += (size_t)blockDim.x * 4)
+            emit(j, *reinterpret_cast<const float4*>(sum + base + j));   // this thread's own stores
     }
     __syncthreads();
     if (threadIdx.x == 0) {
