@@ -195,7 +195,7 @@ int32_t launch_add_rmsnorm(cudaStream_t st, const float* a, const float* b, cons
 size_t gemm_workspace_bytes(const DeviceWeights& w, size_t m, int sm_count);
 int32_t launch_gemm_bf16(cudaStream_t st, uint32_t ty, const DeviceWeights& w, const uint16_t* x_bf16, size_t m, size_t ldx,
                          float* y, size_t ldy, void* workspace, int sm_count);
-// Batched decode product on the tensor cores with exact integer arithmetic (Q4_K and Q6_K, m >= 9 by default): preparation,
+// Batched decode product on the tensor cores on integer-valued f16 operands (Q4_K, Q5_K from 9 rows, Q6_K from 13): preparation,
 // product and, for K-split or SwiGLU, a finish kernel.  `scratch` holds gemv_tc_scratch_bytes() bytes.
 bool gemv_tc_eligible(uint32_t ty, const DeviceWeights& w, size_t m);
 size_t gemv_tc_scratch_bytes(uint32_t ty, const DeviceWeights& w, size_t m, Epilogue epi, int sm_count);
