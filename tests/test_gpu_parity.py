@@ -395,11 +395,14 @@ def test_fused_add_rmsnorm_prepare(F, ctx, ty, m, d):
     qm.close()
 
 
-def test_decode_stack_step_matches_layerwise_oracle(F, ctx):
-    """Two small layers of the decode stack against the oracle, kernel by kernel semantics."""
+@pytest.mark.parametrize("batch", [2, 6, 12, 40])
+def test_decode_stack_step_matches_layerwise_oracle(F, ctx, batch):
+    """Two small layers of the decode stack against the oracle, kernel by kernel semantics: one GEMV pass (2 tokens, the
+    chained form), two passes (6), and the tensor-core decode kernel at its narrow and wide tile (12, 40 tokens: the
+    step for more than 8 tokens, with the fused SwiGLU finish and K cuts of these small matrices)."""
     from ferric_b200.stack import DecodeStack, TPPlan
     plan = TPPlan.make(1, 0, hidden=512, n_ff=768, q_out=512, kv_out=256)
-    st = DecodeStack(ctx, plan, n_layers=2, batch=2)
+    st = DecodeStack(ctx, plan, n_layers=2, batch=batch)
     rng = np.random.default_rng(8)
     raws = []
     for l in range(2):
@@ -408,7 +411,7 @@ def test_decode_stack_step_matches_layerwise_oracle(F, ctx):
         raws.append(list(zip(mats, raw)))
         st.add_layer(*[F.QMatrix.from_bytes(ctx, rw, ty, r, c) for (ty, r, c), rw in zip(mats, raw)])
     st.reserve()
-    h0 = rng.standard_normal((2, 512)).astype(np.float32)
+    h0 = rng.standard_normal((batch, 512)).astype(np.float32)
     st.h.copy_(torch.from_numpy(h0).cuda())
     got = st.step().cpu().numpy()
     h = h0.copy()
