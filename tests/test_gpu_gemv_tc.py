@@ -62,6 +62,7 @@ def run(F, ctx, raw, ty, rows, cols, x, swiglu=False):
     (12, 272, 512, 64),
     (12, 130, 768, 70),       # two activation tiles of the widest kind, the second nearly empty
     (12, 256, 512, 128),      # two full activation tiles
+    (12, 144, 512, 200),      # four activation tiles, the last partly filled
     (12, 256, 5120, 17),      # few row tiles, 20 super-blocks: K split + finish kernel
     (13, 200, 1024, 16),      # Q5_K: the Q4_K kernel with the fifth bit, ragged rows
     (13, 272, 512, 64),       # Q5_K, widest tile
@@ -145,14 +146,15 @@ def test_k_cut_repeats_bit_for_bit(F, ctx, ty, rows, cols, m):
     assert_close(first, ref, f"k cut ty{ty} {rows}x{cols} m{m}", exact_product(raw, ty, rows, cols, x))
 
 
+@pytest.mark.parametrize("ty", [12, 13])
 @pytest.mark.parametrize("m", [20, 40])
-def test_swiglu_fused_into_the_drain(F, ctx, m):
+def test_swiglu_fused_into_the_drain(F, ctx, m, ty):
     """With enough row tiles to fill the machine K is not cut, and each CTA pairs 64 gate rows with the 64 up rows of the
     same outputs and applies SwiGLU itself (no finish kernel)."""
     n_ff, cols = 64 * 150, 512
-    raw = synth.matrix(12, 2 * n_ff, cols, seed=31)
+    raw = synth.matrix(ty, 2 * n_ff, cols, seed=31)
     x = synth.activations(m, cols, seed=32)
-    qm = F.QMatrix.from_bytes(ctx, raw, 12, 2 * n_ff, cols)
+    qm = F.QMatrix.from_bytes(ctx, raw, ty, 2 * n_ff, cols)
     xd = torch.from_numpy(x).cuda()
     before = ctx.launches()
     got = qm.try_matmul_swiglu(xd).cpu().numpy()
@@ -160,9 +162,9 @@ def test_swiglu_fused_into_the_drain(F, ctx, m):
     assert qm.gemm_status() == 0
     qm.close()
     assert got.shape == (m, n_ff)
-    ref = O.swiglu(O.matmul_q(raw, 12, 2 * n_ff, cols, x, threads=NCPU), n_ff)
+    ref = O.swiglu(O.matmul_q(raw, ty, 2 * n_ff, cols, x, threads=NCPU), n_ff)
     assert np.abs(got - ref).max() <= 1e-4 * max(1.0, float(np.abs(ref).max()))
-    unfused = ctx.swiglu(torch.from_numpy(run(F, ctx, raw, 12, 2 * n_ff, cols, x)).cuda(), n_ff).cpu().numpy()
+    unfused = ctx.swiglu(torch.from_numpy(run(F, ctx, raw, ty, 2 * n_ff, cols, x)).cuda(), n_ff).cpu().numpy()
     assert np.abs(got - unfused).max() <= 1e-5 * np.abs(unfused).max()
 
 
