@@ -199,3 +199,27 @@ def test_same_result_as_the_gemv_passes(F, ctx, monkeypatch):
     halves = torch.cat([qm.matmul(xd[:8]), qm.matmul(xd[8:])]).cpu().numpy()   # 8 rows at a time: below the threshold, the GEMV
     qm.close()
     assert np.abs(got - halves).max() <= 1e-5 * np.abs(halves).max()
+
+
+@pytest.mark.parametrize("batch", [12, 64])
+def test_full_width_stack_replays_bit_for_bit(F, ctx, batch):
+    """Four layers of the full-size stack (every SM busy, K cuts, fused SwiGLU drain, both tiles) at 12 and 64 tokens: the
+    captured graph reproduces the eager step bit for bit on every replay, and no bounded wait runs out."""
+    from ferric_b200.stack import DecodeStack, TPPlan
+    st = DecodeStack(ctx, TPPlan.make(1, 0), n_layers=4, batch=batch)
+    st.build_synthetic(seed=3)
+    st.reserve()
+    gen = torch.Generator(device="cuda").manual_seed(batch)
+    h0 = torch.randn(st.h.shape, device="cuda", generator=gen)
+    st.h.copy_(h0)
+    ref = st.step().clone()
+    xn_ref = st.xn.clone()
+    assert bool(torch.isfinite(ref).all())
+    st.capture()
+    for _ in range(10):
+        st.h.copy_(h0)
+        out = st.run()
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref) and torch.equal(st.xn, xn_ref)
+    assert st.layers[0].wqkv.gemm_status() == 0
+    st.close()
