@@ -221,6 +221,43 @@ def test_config2_output_head_rows_sampled(F, ctx):
     qm.close()
 
 
+@pytest.mark.parametrize("m", [16, 64])
+def test_config1_products_at_many_rows_full_size_rows_sampled(F, ctx, m):
+    """The layer's two big products at their full size with 16 and 64 activation rows (the tensor-core decode kernel at
+    both tiles): gate|up 34816 x 5120 Q4_K with SwiGLU in the kernel's drain (every SM busy, two waves) and down
+    5120 x 17408 Q6_K with its K range cut across CTAs.  The oracle runs on sampled row spans."""
+    n_ff, cols = 17408, 5120
+    raw = synth.matrix_on_device(12, 2 * n_ff, cols, seed=5, device="cuda")
+    qm = F.QMatrix.from_device_bytes(ctx, raw, 12, 2 * n_ff, cols)
+    row_bytes = cols // 256 * 144
+    spans = [(0, 32), (8711, 8743), (n_ff - 32, n_ff)]
+    host = {s: (raw[s[0] * row_bytes:s[1] * row_bytes].cpu().numpy(),
+                raw[(n_ff + s[0]) * row_bytes:(n_ff + s[1]) * row_bytes].cpu().numpy()) for s in spans}
+    del raw
+    x = synth.activations(m, cols, seed=m)
+    y = qm.try_matmul_swiglu(torch.from_numpy(x).cuda()).cpu().numpy()
+    assert y.shape == (m, n_ff) and np.isfinite(y).all() and qm.gemm_status() == 0
+    for (lo, hi), (gate, up) in host.items():
+        both = np.concatenate([gate, up])
+        ref = O.swiglu(O.matmul_q(both, 12, 2 * (hi - lo), cols, x, threads=NCPU), hi - lo)
+        assert np.abs(y[:, lo:hi] - ref).max() <= 1e-4 * max(1.0, float(np.abs(ref).max())), (lo, hi)
+    qm.close()
+    rows, cols = 5120, 17408
+    raw = synth.matrix_on_device(14, rows, cols, seed=6, device="cuda")
+    qm = F.QMatrix.from_device_bytes(ctx, raw, 14, rows, cols)
+    row_bytes = cols // 256 * 210
+    spans = [(0, 48), (2500, 2548), (rows - 48, rows)]
+    host = {s: raw[s[0] * row_bytes:s[1] * row_bytes].cpu().numpy() for s in spans}
+    del raw
+    x = synth.activations(m, cols, seed=m + 1)
+    y = qm.matmul(torch.from_numpy(x).cuda()).cpu().numpy()
+    assert y.shape == (m, rows) and np.isfinite(y).all() and qm.gemm_status() == 0
+    for (lo, hi), rb in host.items():
+        ref = O.matmul_q(rb, 14, hi - lo, cols, x, threads=NCPU)
+        assert_close(y[:, lo:hi], ref, f"down m={m} rows {lo}:{hi}", exact_product(rb, 14, hi - lo, cols, x))
+    qm.close()
+
+
 @pytest.mark.parametrize("ty", [12, 13, 14, 8])
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 9, 16, 17, 33, 64])
 def test_batch_sizes(F, ctx, ty, m):
